@@ -1,0 +1,195 @@
+// Elementwise operators and comparison helpers for sm_100a.
+#include "common.cuh"
+
+namespace b200 {
+
+// out = x * sigmoid(x) * y in fp32, one rounding at the store
+// (swiglu_fwd_kernel, ops/suite/perf/swiglu_fwd.py:27-36).
+template <typename T>
+__global__ void __launch_bounds__(256)
+swiglu_vec_kernel(const T *__restrict__ x, int64_t xs, const T *__restrict__ y,
+                  int64_t ys, T *__restrict__ out, int64_t os, int64_t rows,
+                  int vec_per_row) {
+  constexpr int N = vec16<T>::N;
+  const int64_t total = rows * vec_per_row;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = i / vec_per_row;
+    const int64_t c = (i - r * vec_per_row) * N;
+    vec16<T> a, b, o;
+    a.raw = ld_stream16(x + r * xs + c);
+    b.raw = ld_stream16(y + r * ys + c);
+#pragma unroll
+    for (int j = 0; j < N; ++j) {
+      const float xf = io<T>::load(a.e[j]);
+      o.e[j] = io<T>::store(xf / (1.0f + __expf(-xf)) * io<T>::load(b.e[j]));
+    }
+    st_stream16(out + r * os + c, o.raw);
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+swiglu_scalar_kernel(const T *__restrict__ x, int64_t xs, const T *__restrict__ y,
+                     int64_t ys, T *__restrict__ out, int64_t os, int64_t rows,
+                     int64_t cols) {
+  const int64_t total = rows * cols;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = i / cols, c = i - r * cols;
+    const float xf = io<T>::load(x[r * xs + c]);
+    out[r * os + c] = io<T>::store(xf / (1.0f + expf(-xf)) * io<T>::load(y[r * ys + c]));
+  }
+}
+
+template <typename T>
+static int swiglu_dispatch(const b200_tensor *x, const b200_tensor *y, b200_tensor *out,
+                           cudaStream_t stream) {
+  constexpr int N = vec16<T>::N;
+  const int64_t rows = x->shape[0], cols = x->shape[1];
+  const bool aligned = cols % N == 0 && (x->stride[0] * sizeof(T)) % 16 == 0 &&
+                       (y->stride[0] * sizeof(T)) % 16 == 0 &&
+                       (out->stride[0] * sizeof(T)) % 16 == 0 &&
+                       (uintptr_t)x->data % 16 == 0 && (uintptr_t)y->data % 16 == 0 &&
+                       (uintptr_t)out->data % 16 == 0;
+  const int64_t items = aligned ? rows * (cols / N) : rows * cols;
+  int64_t blocks = (items + 255) / 256;
+  const int64_t cap = (int64_t)sm_count() * 16;
+  if (blocks > cap) blocks = cap;
+  if (aligned)
+    swiglu_vec_kernel<T><<<(unsigned)blocks, 256, 0, stream>>>(
+        (const T *)x->data, x->stride[0], (const T *)y->data, y->stride[0],
+        (T *)out->data, out->stride[0], rows, (int)(cols / N));
+  else
+    swiglu_scalar_kernel<T><<<(unsigned)blocks, 256, 0, stream>>>(
+        (const T *)x->data, x->stride[0], (const T *)y->data, y->stride[0],
+        (T *)out->data, out->stride[0], rows, cols);
+  B200_CUDA_OK(cudaGetLastError());
+  return B200_OK;
+}
+
+// np.isclose(a, b, rtol, atol, equal_nan) in fp32 plus max |a-b| in fp64 over
+// the elements that are not exactly equal
+// (ops/harness/opslib/devices/_cuda_compare.py:24-46).
+__global__ void __launch_bounds__(256)
+allclose_f32_kernel(const float *__restrict__ a, const float *__restrict__ b,
+                    int64_t n, float rtol, float atol, int equal_nan,
+                    unsigned long long *bad, unsigned long long *maxerr_bits) {
+  unsigned long long local_bad = 0;
+  double local_err = 0.0;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    const float av = a[i], bv = b[i];
+    const float b_abs = fabsf(bv);
+    const bool finite = b_abs < INFINITY;
+    bool close = ((fabsf(av - bv) <= (atol + rtol * b_abs)) && finite) || (av == bv);
+    bool equal = av == bv;
+    if (equal_nan) {
+      const bool both_nan = (av != av) && (bv != bv);
+      close = close || both_nan;
+      equal = equal || both_nan;
+    }
+    if (!close) ++local_bad;
+    if (!equal) {
+      const double d = fabs((double)av - (double)bv);
+      // NaN deltas order above every finite value as bit patterns, like the
+      // int64 atomic_max of the reference does
+      if (d != d || d > local_err) local_err = d;
+    }
+  }
+  if (local_bad) atomicAdd(bad, local_bad);
+  if (local_err != 0.0 || local_err != local_err)
+    atomicMax(maxerr_bits, (unsigned long long)__double_as_longlong(local_err));
+}
+
+__global__ void __launch_bounds__(256)
+bitwise_diff_kernel(const unsigned char *__restrict__ a, const unsigned char *__restrict__ b,
+                    size_t n, unsigned int *diff) {
+  unsigned int local = 0;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+       i += (size_t)gridDim.x * blockDim.x)
+    local |= (a[i] != b[i]);
+  if (local) atomicOr(diff, 1u);
+}
+
+}  // namespace b200
+
+extern "C" int b200_swiglu_fwd(const b200_tensor *x, const b200_tensor *y,
+                               b200_tensor *out, void *stream) {
+  using namespace b200;
+  int st;
+  if ((st = check_tensor(x, "x", 2)) || (st = check_tensor(y, "y", 2)) ||
+      (st = check_tensor(out, "out", 2)))
+    return st;
+  B200_REQUIRE(is_float_io(x->dtype), "x: dtype %u is not f16/bf16/f32", x->dtype);
+  B200_REQUIRE(y->dtype == x->dtype && out->dtype == x->dtype, "x/y/out dtypes differ");
+  const int64_t rows = x->shape[0], cols = x->shape[1];
+  B200_REQUIRE(y->shape[0] == rows && y->shape[1] == cols && out->shape[0] == rows &&
+               out->shape[1] == cols, "x/y/out shapes differ");
+  B200_REQUIRE(x->stride[1] == 1 && y->stride[1] == 1 && out->stride[1] == 1,
+               "unit column stride required");
+  if (rows == 0 || cols == 0) return B200_OK;
+  cudaStream_t s = (cudaStream_t)stream;
+  switch (x->dtype) {
+    case B200_DTYPE_FLOAT32: return swiglu_dispatch<float>(x, y, out, s);
+    case B200_DTYPE_FLOAT16: return swiglu_dispatch<__half>(x, y, out, s);
+    default: return swiglu_dispatch<__nv_bfloat16>(x, y, out, s);
+  }
+}
+
+extern "C" int b200_allclose_f32(const void *actual, const void *expected, int64_t count,
+                                 double rtol, double atol, int equal_nan,
+                                 int64_t *bad_count, double *max_abs_err, void *stream) {
+  using namespace b200;
+  if (bad_count == nullptr || max_abs_err == nullptr)
+    return fail(B200_USAGE, "null result pointer");
+  *bad_count = 0;
+  *max_abs_err = 0.0;
+  if (count == 0) return B200_OK;
+  B200_REQUIRE(count > 0 && actual != nullptr && expected != nullptr, "bad buffers");
+  cudaStream_t s = (cudaStream_t)stream;
+  unsigned long long *scratch = nullptr;
+  B200_CUDA_OK(cudaMalloc(&scratch, 16));
+  cudaMemsetAsync(scratch, 0, 16, s);
+  int64_t blocks = (count + 255) / 256;
+  const int64_t cap = (int64_t)sm_count() * 16;
+  if (blocks > cap) blocks = cap;
+  allclose_f32_kernel<<<(unsigned)blocks, 256, 0, s>>>(
+      (const float *)actual, (const float *)expected, count, (float)rtol, (float)atol,
+      equal_nan, scratch, scratch + 1);
+  unsigned long long host[2] = {0, 0};
+  cudaError_t err = cudaMemcpyAsync(host, scratch, 16, cudaMemcpyDeviceToHost, s);
+  if (err == cudaSuccess) err = cudaStreamSynchronize(s);
+  cudaFree(scratch);
+  if (err != cudaSuccess) return fail(B200_SYNC, "allclose: %s", cudaGetErrorString(err));
+  *bad_count = (int64_t)host[0];
+  double e;
+  memcpy(&e, &host[1], sizeof e);
+  *max_abs_err = e;
+  return B200_OK;
+}
+
+extern "C" int b200_bitwise_equal(const void *first, const void *other, size_t bytes,
+                                  int *equal, void *stream) {
+  using namespace b200;
+  if (equal == nullptr) return fail(B200_USAGE, "null result pointer");
+  *equal = 1;
+  if (bytes == 0) return B200_OK;
+  B200_REQUIRE(first != nullptr && other != nullptr, "null buffer");
+  cudaStream_t s = (cudaStream_t)stream;
+  unsigned int *flag = nullptr;
+  B200_CUDA_OK(cudaMalloc(&flag, 4));
+  cudaMemsetAsync(flag, 0, 4, s);
+  size_t blocks = (bytes + 255) / 256;
+  const size_t cap = (size_t)sm_count() * 16;
+  if (blocks > cap) blocks = cap;
+  bitwise_diff_kernel<<<(unsigned)blocks, 256, 0, s>>>(
+      (const unsigned char *)first, (const unsigned char *)other, bytes, flag);
+  unsigned int host = 0;
+  cudaError_t err = cudaMemcpyAsync(&host, flag, 4, cudaMemcpyDeviceToHost, s);
+  if (err == cudaSuccess) err = cudaStreamSynchronize(s);
+  cudaFree(flag);
+  if (err != cudaSuccess) return fail(B200_SYNC, "bitwise_equal: %s", cudaGetErrorString(err));
+  *equal = host ? 0 : 1;
+  return host ? B200_REPEAT_MISMATCH : B200_OK;
+}

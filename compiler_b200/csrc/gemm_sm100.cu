@@ -1,0 +1,549 @@
+// C = act(A @ B + bias) for sm_100a: TMA-fed tcgen05.mma tiles with the
+// accumulator in tensor memory and the epilogue fused behind it.
+//
+// Semantics follow matmul_kernel (ops/suite/perf/matmul.py:20-38) and
+// linear_act_kernel (ops/suite/perf/triton_linear_activation.py:27-49):
+// A [M,K] row-major, B [K,N] row-major, 16-bit operands, fp32 accumulation,
+// bias add and activation in fp32, one rounding at the store.
+//
+// Structure (one persistent CTA per SM, 192 threads):
+//   warp 4   producer: TMA loads of A (128x64, K-major) and B (64x256, four
+//            64-column boxes, N-major) into a 4-stage shared-memory ring
+//   warp 5   one elected lane issues tcgen05.mma 128x256x16 into one of two
+//            256-column TMEM accumulators and commits stage / tile barriers
+//   warps 0-3 epilogue: tcgen05.ld the finished accumulator (one row per
+//            thread), bias + activation, convert, 16-byte global stores
+// so the epilogue of tile i overlaps the main loop of tile i+1.  Out-of-range
+// rows / columns / K are zero-filled by TMA on load and predicated on store;
+// no out-of-range address is ever formed.
+#include "sm100.cuh"
+
+#include <mutex>
+
+namespace b200 {
+
+// ------------------------------------------------------------ tensor maps
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
+                                  const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
+                                  const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled_entry() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void *ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) ==
+            cudaSuccess && q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)ptr;
+  });
+  return fn;
+}
+
+int encode_tensor_map(CUtensorMap *out, uint32_t dtype, const void *base, int rank,
+                      const uint64_t *dims, const uint64_t *strides_bytes,
+                      const uint32_t *box) {
+  EncodeTiledFn fn = encode_tiled_entry();
+  if (fn == nullptr) return fail(B200_RESOURCE, "cuTensorMapEncodeTiled is not available");
+  CUtensorMapDataType dt;
+  switch (dtype) {
+    case B200_DTYPE_BFLOAT16: dt = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16; break;
+    case B200_DTYPE_FLOAT16: dt = CU_TENSOR_MAP_DATA_TYPE_FLOAT16; break;
+    case B200_DTYPE_FLOAT32: dt = CU_TENSOR_MAP_DATA_TYPE_FLOAT32; break;
+    default: return fail(B200_UNSUPPORTED, "no tensor map for dtype %u", dtype);
+  }
+  cuuint64_t gdims[5], gstrides[5];
+  cuuint32_t gbox[5], estr[5];
+  for (int i = 0; i < rank; ++i) {
+    gdims[i] = dims[i];
+    gbox[i] = box[i];
+    estr[i] = 1;
+    if (i > 0) gstrides[i - 1] = strides_bytes[i];
+  }
+  CUresult r = fn(out, dt, (cuuint32_t)rank, const_cast<void *>(base), gdims, gstrides, gbox, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(B200_REJECTED, "cuTensorMapEncodeTiled failed (%d)", (int)r);
+  return B200_OK;
+}
+
+namespace gemm {
+
+using namespace sm100;
+
+constexpr int BM = 128;
+constexpr int BN = 256;  // accumulator columns per tile (two 128-column halves when DUAL)
+constexpr int BK = 64;   // 64 16-bit elements = one 128-byte swizzle span
+constexpr int UMMA_K = 16;
+constexpr int STAGES = 4;
+constexpr int A_STAGE_BYTES = BM * BK * 2;    // 16 KiB
+constexpr int B_BOX_BYTES = BK * 64 * 2;      // one 64(K) x 64(N) box: 8 KiB
+constexpr int B_STAGE_BYTES = 4 * B_BOX_BYTES;  // 32 KiB
+constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+constexpr int TMEM_COLS = 512;
+constexpr int THREADS = 192;
+constexpr int GROUP_M = 16;  // m-blocks per raster group (L2 reuse of A and B)
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+
+struct Params {
+  int M, N, K;
+  int act;
+  int bias_kind;  // 0 none, B200_DTYPE_* otherwise
+  const void *bias;
+  void *c;
+  int64_t ldc;
+  uint32_t idesc;
+  int vector_store;  // rows of C are 16-byte aligned and N % 8 == 0 (N % 4 for f32)
+  unsigned int *status;
+};
+
+__device__ __forceinline__ float gelu_tanh_fast(float z) {
+  const float u = 0.7978845608028654f * (z + 0.044715f * z * z * z);
+  float t;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(u));
+  return 0.5f * z * (1.0f + t);
+}
+__device__ __forceinline__ float gelu_tanh_exact(float z) {
+  const float u = 0.7978845608028654f * (z + 0.044715f * z * z * z);
+  return 0.5f * z * (1.0f + tanhf(u));
+}
+__device__ __forceinline__ float gelu_erf(float z) {
+  return 0.5f * z * (1.0f + erff(z * 0.7071067811865476f));
+}
+
+template <typename OutT> __device__ __forceinline__ float activate(float z, int act) {
+  switch (act) {
+    case B200_ACT_GELU_ERF: return gelu_erf(z);
+    case B200_ACT_GELU_TANH:
+      return sizeof(OutT) == 2 ? gelu_tanh_fast(z) : gelu_tanh_exact(z);
+    case B200_ACT_LEAKY_RELU: return z >= 0.f ? z : 0.01f * z;
+    default: return z;
+  }
+}
+__device__ __forceinline__ float silu(float z) { return z / (1.0f + __expf(-z)); }
+
+__device__ __forceinline__ float load_bias(const void *bias, int kind, int col) {
+  if (kind == B200_DTYPE_FLOAT32) return ((const float *)bias)[col];
+  if (kind == B200_DTYPE_BFLOAT16) return __bfloat162float(((const __nv_bfloat16 *)bias)[col]);
+  return __half2float(((const __half *)bias)[col]);
+}
+
+// tile index -> block coordinates, grouped so that concurrently running CTAs
+// share A row-blocks and B column-blocks in L2
+__device__ __forceinline__ void tile_coords(int tile, int m_blocks, int n_blocks, int &mb,
+                                            int &nb) {
+  const int per_group = GROUP_M * n_blocks;
+  const int group = tile / per_group;
+  const int first_m = group * GROUP_M;
+  const int rows = min(GROUP_M, m_blocks - first_m);
+  const int in_group = tile - group * per_group;
+  mb = first_m + in_group % rows;
+  nb = in_group / rows;
+}
+
+template <typename OutT, bool DUAL>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
+                    const __grid_constant__ CUtensorMap tm_b,
+                    const __grid_constant__ CUtensorMap tm_b2, const Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t *smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+  const uint32_t a_smem = smem_base;
+  const uint32_t b_smem = smem_base + STAGES * A_STAGE_BYTES;
+  uint64_t *bars = reinterpret_cast<uint64_t *>(smem_gen + STAGES * STAGE_BYTES);
+  // barrier slots: full[STAGES], empty[STAGES], acc_full[2], acc_empty[2], drain
+  const uint32_t bar0 = smem_base + STAGES * STAGE_BYTES;
+  auto full_bar = [&](int s) { return bar0 + 8u * s; };
+  auto empty_bar = [&](int s) { return bar0 + 8u * (STAGES + s); };
+  auto acc_full_bar = [&](int a) { return bar0 + 8u * (2 * STAGES + a); };
+  auto acc_empty_bar = [&](int a) { return bar0 + 8u * (2 * STAGES + 2 + a); };
+  const uint32_t drain_bar = bar0 + 8u * (2 * STAGES + 4);
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * STAGES + 5);
+  volatile uint32_t *abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const WaitCtx ctx{abort_flag, p.status};
+
+  // output tile width in columns of C
+  constexpr int TILE_N = DUAL ? BN / 2 : BN;
+  const int m_blocks = (p.M + BM - 1) / BM;
+  const int n_blocks = (p.N + TILE_N - 1) / TILE_N;
+  const int num_tiles = m_blocks * n_blocks;
+  const int num_kb = (p.K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(acc_full_bar(a), 1);
+      mbar_init(acc_empty_bar(a), 4);
+    }
+    mbar_init(drain_bar, 1);
+    *abort_flag = 0u;
+    mbar_init_fence();
+  }
+  if (warp == 4 && lane == 0) {
+    tma_prefetch_desc(&tm_a);
+    tma_prefetch_desc(&tm_b);
+    if (DUAL) tma_prefetch_desc(&tm_b2);
+  }
+  if (warp == 5) tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 4) {
+    // ------------------------------------------------------------ producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      uint32_t issued_mask = 0, issued_parity = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+        int mb, nb;
+        tile_coords(tile, m_blocks, n_blocks, mb, nb);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(empty_bar(stage), phase ^ 1u, ctx, 1)) { ok = false; break; }
+          mbar_arrive_expect_tx(full_bar(stage), STAGE_BYTES);
+          tma_load_2d(a_smem + stage * A_STAGE_BYTES, &tm_a, full_bar(stage), kb * BK, mb * BM);
+          const uint32_t bdst = b_smem + stage * B_STAGE_BYTES;
+          if (DUAL) {
+            const int n0 = nb * TILE_N;
+            tma_load_2d(bdst, &tm_b, full_bar(stage), n0, kb * BK);
+            tma_load_2d(bdst + B_BOX_BYTES, &tm_b, full_bar(stage), n0 + 64, kb * BK);
+            tma_load_2d(bdst + 2 * B_BOX_BYTES, &tm_b2, full_bar(stage), n0, kb * BK);
+            tma_load_2d(bdst + 3 * B_BOX_BYTES, &tm_b2, full_bar(stage), n0 + 64, kb * BK);
+          } else {
+            const int n0 = nb * TILE_N;
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+              tma_load_2d(bdst + j * B_BOX_BYTES, &tm_b, full_bar(stage), n0 + 64 * j, kb * BK);
+          }
+          issued_mask |= 1u << stage;
+          issued_parity = (issued_parity & ~(1u << stage)) | (phase << stage);
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+      }
+      if (!ok) {
+        // copies already issued still target this CTA's shared memory: wait for
+        // them (bounded) before the CTA is allowed to exit
+        for (int s = 0; s < STAGES; ++s)
+          if (issued_mask & (1u << s)) mbar_wait_drain(full_bar(s), (issued_parity >> s) & 1u);
+      }
+    }
+  } else if (warp == 5) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+        if (!mbar_wait(acc_empty_bar(acc), acc_phase ^ 1u, ctx, 2)) { ok = false; break; }
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(full_bar(stage), phase, ctx, 3)) { ok = false; break; }
+          tc_fence_after_sync();
+          const uint64_t a_desc = make_smem_desc_sw128(a_smem + stage * A_STAGE_BYTES, 16, 1024);
+          const uint64_t b_desc =
+              make_smem_desc_sw128(b_smem + stage * B_STAGE_BYTES, B_BOX_BYTES, 1024);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            // A: +32 bytes along K inside the swizzle span; B: +16 K-rows of 128 bytes
+            mma_f16_ss(d_tmem, a_desc + (uint64_t)(k * ((UMMA_K * 2) >> 4)),
+                       b_desc + (uint64_t)(k * ((UMMA_K * 128) >> 4)), p.idesc,
+                       (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          tc_commit(empty_bar(stage));  // stage reusable once these MMAs retire
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+        if (!ok) break;
+        tc_commit(acc_full_bar(acc));  // accumulator complete
+        if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+      }
+      // every MMA issued above must retire before shared / tensor memory go away
+      tc_commit(drain_bar);
+      mbar_wait_drain(drain_bar, 0);
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    OutT *c = reinterpret_cast<OutT *>(p.c);
+    for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+      int mb, nb;
+      tile_coords(tile, m_blocks, n_blocks, mb, nb);
+      // the vote keeps the warp converged for the .sync.aligned TMEM loads below
+      if (!__all_sync(0xffffffffu, mbar_wait(acc_full_bar(acc), acc_phase, ctx, 4))) {
+        ok = false;
+        break;
+      }
+      tc_fence_after_sync();
+      const int row = mb * BM + warp * 32 + lane;
+      const bool row_ok = row < p.M;
+      const uint32_t t_row = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(acc * BN);
+      OutT *crow = c + (int64_t)row * p.ldc;
+#pragma unroll 1
+      for (int chunk = 0; chunk < TILE_N / 32; ++chunk) {
+        const int col0 = nb * TILE_N + chunk * 32;
+        if (col0 >= p.N) break;  // warp-uniform
+        uint32_t r[32];
+        float v[32];
+        tmem_ld_32x32b_x32(t_row + (uint32_t)(chunk * 32), r);
+        if (DUAL) {
+          uint32_t r2[32];
+          tmem_ld_32x32b_x32(t_row + (uint32_t)(TILE_N + chunk * 32), r2);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = silu(__uint_as_float(r[j])) * __uint_as_float(r2[j]);
+        } else {
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            float z = __uint_as_float(r[j]);
+            if (p.bias_kind != 0 && col0 + j < p.N) z += load_bias(p.bias, p.bias_kind, col0 + j);
+            v[j] = activate<OutT>(z, p.act);
+          }
+        }
+        if (row_ok) {
+          if (p.vector_store && col0 + 32 <= p.N) {
+            constexpr int PER = 16 / (int)sizeof(OutT);
+#pragma unroll
+            for (int q = 0; q < 32 / PER; ++q) {
+              vec16<OutT> o;
+#pragma unroll
+              for (int j = 0; j < PER; ++j) o.e[j] = io<OutT>::store(v[q * PER + j]);
+              *reinterpret_cast<uint4 *>(crow + col0 + q * PER) = o.raw;
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (col0 + j < p.N) crow[col0 + j] = io<OutT>::store(v[j]);
+          }
+        }
+      }
+      // this warp has drained its quarter of the accumulator
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(acc_empty_bar(acc));
+      if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 5) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ------------------------------------------------------------ CUDA-core path
+// Any dtype, any stride alignment: 32x32 tiles through shared memory, fp32 FMA
+// accumulation (IEEE for fp32 operands).  Serves shapes the tensor-core path
+// rejects (row pitch not a multiple of 16 bytes, fp32 operands).
+template <typename InT, typename OutT>
+__global__ void __launch_bounds__(256)
+gemm_simt_kernel(const InT *__restrict__ a, int64_t lda, const InT *__restrict__ b, int64_t ldb,
+                 const InT *__restrict__ b2, OutT *__restrict__ c, int64_t ldc, int M, int N,
+                 int K, const void *bias, int bias_kind, int act) {
+  __shared__ float sa[32][33];
+  __shared__ float sb[32][33];
+  __shared__ float sb2[32][33];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 32 x 8
+  const int m0 = blockIdx.y * 32, n0 = blockIdx.x * 32;
+  float acc[4] = {0.f, 0.f, 0.f, 0.f}, acc2[4] = {0.f, 0.f, 0.f, 0.f};
+  for (int k0 = 0; k0 < K; k0 += 32) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int r = ty + 8 * i;
+      const int am = m0 + r, ak = k0 + tx;
+      sa[r][tx] = (am < M && ak < K) ? io<InT>::load(a[(int64_t)am * lda + ak]) : 0.f;
+      const int bk = k0 + r, bn = n0 + tx;
+      const bool bok = bk < K && bn < N;
+      sb[r][tx] = bok ? io<InT>::load(b[(int64_t)bk * ldb + bn]) : 0.f;
+      if (b2 != nullptr) sb2[r][tx] = bok ? io<InT>::load(b2[(int64_t)bk * ldb + bn]) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll 8
+    for (int k = 0; k < 32; ++k) {
+      const float bv = sb[k][tx];
+      const float bv2 = b2 != nullptr ? sb2[k][tx] : 0.f;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float av = sa[ty + 8 * i][k];
+        acc[i] = fmaf(av, bv, acc[i]);
+        acc2[i] = fmaf(av, bv2, acc2[i]);
+      }
+    }
+    __syncthreads();
+  }
+  const int n = n0 + tx;
+  if (n >= N) return;
+  const float bias_v = bias_kind ? load_bias(bias, bias_kind, n) : 0.f;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int m = m0 + ty + 8 * i;
+    if (m >= M) continue;
+    float z;
+    if (act == B200_ACT_SWIGLU) {
+      z = acc[i] / (1.0f + expf(-acc[i])) * acc2[i];
+    } else {
+      z = acc[i] + bias_v;
+      switch (act) {
+        case B200_ACT_GELU_ERF: z = gelu_erf(z); break;
+        case B200_ACT_GELU_TANH: z = gelu_tanh_exact(z); break;
+        case B200_ACT_LEAKY_RELU: z = z >= 0.f ? z : 0.01f * z; break;
+        default: break;
+      }
+    }
+    c[(int64_t)m * ldc + n] = io<OutT>::store(z);
+  }
+}
+
+template <typename InT, typename OutT>
+static int launch_simt(const b200_tensor *a, const b200_tensor *b, const b200_tensor *b2,
+                       const b200_tensor *bias, b200_tensor *c, int act, cudaStream_t stream) {
+  const int M = (int)a->shape[0], K = (int)a->shape[1], N = (int)b->shape[1];
+  dim3 grid((N + 31) / 32, (M + 31) / 32);
+  B200_REQUIRE(grid.y <= 65535, "M too large for the CUDA-core path");
+  gemm_simt_kernel<InT, OutT><<<grid, 256, 0, stream>>>(
+      (const InT *)a->data, a->stride[0], (const InT *)b->data, b->stride[0],
+      b2 ? (const InT *)b2->data : nullptr, (OutT *)c->data, c->stride[0], M, N, K,
+      bias ? bias->data : nullptr, bias ? (int)bias->dtype : 0, act);
+  B200_CUDA_OK(cudaGetLastError());
+  return B200_OK;
+}
+
+template <typename OutT, bool DUAL>
+static int launch_tc(const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap &tb2,
+                     const Params &p, cudaStream_t stream) {
+  static bool configured[64] = {false};
+  int dev = 0;
+  B200_CUDA_OK(cudaGetDevice(&dev));
+  auto kernel = gemm_tcgen05_kernel<OutT, DUAL>;
+  if (dev < 64 && !configured[dev]) {
+    B200_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      SMEM_BYTES));
+    configured[dev] = true;
+  }
+  constexpr int TILE_N = DUAL ? BN / 2 : BN;
+  const int tiles = ((p.M + BM - 1) / BM) * ((p.N + TILE_N - 1) / TILE_N);
+  const int grid = tiles < sm_count() ? tiles : sm_count();
+  kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(ta, tb, tb2, p);
+  B200_CUDA_OK(cudaGetLastError());
+  return B200_OK;
+}
+
+}  // namespace gemm
+}  // namespace b200
+
+extern "C" int b200_gemm_bias_act(const b200_tensor *a, const b200_tensor *b,
+                                  const b200_tensor *b2, const b200_tensor *bias,
+                                  b200_tensor *c, int act, void *stream) {
+  using namespace b200;
+  using namespace b200::gemm;
+  int st;
+  if ((st = check_tensor(a, "a", 2)) || (st = check_tensor(b, "b", 2)) ||
+      (st = check_tensor(c, "c", 2)))
+    return st;
+  if (act < B200_ACT_NONE || act > B200_ACT_SWIGLU)
+    return fail(B200_USAGE, "act %d is not a b200_act value", act);
+  if (bias != nullptr && (st = check_tensor(bias, "bias", 1))) return st;
+  if (act == B200_ACT_SWIGLU) {
+    if (b2 == nullptr) return fail(B200_USAGE, "B200_ACT_SWIGLU needs the second B operand");
+    if ((st = check_tensor(b2, "b2", 2))) return st;
+    B200_REQUIRE(bias == nullptr, "B200_ACT_SWIGLU takes no bias");
+  } else if (b2 != nullptr) {
+    return fail(B200_USAGE, "b2 is only used with B200_ACT_SWIGLU");
+  }
+  B200_REQUIRE(is_float_io(a->dtype), "a: dtype %u is not f16/bf16/f32", a->dtype);
+  B200_REQUIRE(b->dtype == a->dtype, "a/b dtypes differ (%u/%u)", a->dtype, b->dtype);
+  B200_REQUIRE(c->dtype == a->dtype || c->dtype == B200_DTYPE_FLOAT32,
+               "c dtype %u must be a's dtype or f32", c->dtype);
+  const int64_t M = a->shape[0], K = a->shape[1], N = b->shape[1];
+  B200_REQUIRE(b->shape[0] == K, "a is [%lld,%lld] but b has %lld rows", (long long)M,
+               (long long)K, (long long)b->shape[0]);
+  B200_REQUIRE(c->shape[0] == M && c->shape[1] == N, "c shape is not [M,N]");
+  B200_REQUIRE(a->stride[1] == 1 && b->stride[1] == 1 && c->stride[1] == 1,
+               "a/b/c need unit column stride (row-major)");
+  B200_REQUIRE(a->stride[0] >= K && b->stride[0] >= N && c->stride[0] >= N,
+               "row stride below row width");
+  B200_REQUIRE(M < (1 << 30) && N < (1 << 30) && K < (1 << 30), "extent out of range");
+  if (b2 != nullptr) {
+    B200_REQUIRE(b2->dtype == b->dtype && b2->shape[0] == K && b2->shape[1] == N &&
+                 b2->stride[1] == 1 && b2->stride[0] == b->stride[0],
+                 "b2 must match b in dtype, shape and strides");
+  }
+  if (bias != nullptr) {
+    B200_REQUIRE(bias->shape[0] == N && bias->stride[0] == 1, "bias must be contiguous [N]");
+    B200_REQUIRE(bias->dtype == B200_DTYPE_FLOAT32 || bias->dtype == a->dtype,
+                 "bias dtype %u must be f32 or a's dtype", bias->dtype);
+  }
+  if (M == 0 || N == 0) return B200_OK;
+  cudaStream_t s = (cudaStream_t)stream;
+
+  const size_t es = dtype_size(a->dtype);
+  const bool tensor_core =
+      K > 0 && a->dtype != B200_DTYPE_FLOAT32 && (a->stride[0] * es) % 16 == 0 &&
+      (b->stride[0] * es) % 16 == 0 && (uintptr_t)a->data % 16 == 0 &&
+      (uintptr_t)b->data % 16 == 0 && (b2 == nullptr || (uintptr_t)b2->data % 16 == 0);
+  if (!tensor_core) {
+    if (a->dtype == B200_DTYPE_FLOAT32) return launch_simt<float, float>(a, b, b2, bias, c, act, s);
+    if (a->dtype == B200_DTYPE_FLOAT16) {
+      return c->dtype == B200_DTYPE_FLOAT32
+                 ? launch_simt<__half, float>(a, b, b2, bias, c, act, s)
+                 : launch_simt<__half, __half>(a, b, b2, bias, c, act, s);
+    }
+    return c->dtype == B200_DTYPE_FLOAT32
+               ? launch_simt<__nv_bfloat16, float>(a, b, b2, bias, c, act, s)
+               : launch_simt<__nv_bfloat16, __nv_bfloat16>(a, b, b2, bias, c, act, s);
+  }
+
+  CUtensorMap ta, tb, tb2;
+  {
+    const uint64_t dims[2] = {(uint64_t)K, (uint64_t)M};
+    const uint64_t strides[2] = {es, (uint64_t)a->stride[0] * es};
+    const uint32_t box[2] = {BK, BM};
+    if ((st = encode_tensor_map(&ta, a->dtype, a->data, 2, dims, strides, box))) return st;
+  }
+  {
+    const uint64_t dims[2] = {(uint64_t)N, (uint64_t)K};
+    const uint64_t strides[2] = {es, (uint64_t)b->stride[0] * es};
+    const uint32_t box[2] = {64, BK};
+    if ((st = encode_tensor_map(&tb, b->dtype, b->data, 2, dims, strides, box))) return st;
+    tb2 = tb;
+    if (b2 != nullptr &&
+        (st = encode_tensor_map(&tb2, b2->dtype, b2->data, 2, dims, strides, box)))
+      return st;
+  }
+  Params p;
+  p.M = (int)M; p.N = (int)N; p.K = (int)K;
+  p.act = act;
+  p.bias_kind = bias ? (int)bias->dtype : 0;
+  p.bias = bias ? bias->data : nullptr;
+  p.c = c->data;
+  p.ldc = c->stride[0];
+  p.idesc = sm100::make_idesc_f16(BM, BN, a->dtype == B200_DTYPE_BFLOAT16 ? 1 : 0, 0, 1);
+  const size_t cs = dtype_size(c->dtype);
+  p.vector_store = ((c->stride[0] * cs) % 16 == 0 && (uintptr_t)c->data % 16 == 0) ? 1 : 0;
+  p.status = device_status_word();
+  if (p.status == nullptr) return fail(B200_RESOURCE, "no status word on this device");
+
+  const bool dual = act == B200_ACT_SWIGLU;
+  if (c->dtype == B200_DTYPE_FLOAT32)
+    return dual ? launch_tc<float, true>(ta, tb, tb2, p, s) : launch_tc<float, false>(ta, tb, tb2, p, s);
+  if (c->dtype == B200_DTYPE_FLOAT16)
+    return dual ? launch_tc<__half, true>(ta, tb, tb2, p, s) : launch_tc<__half, false>(ta, tb, tb2, p, s);
+  return dual ? launch_tc<__nv_bfloat16, true>(ta, tb, tb2, p, s)
+              : launch_tc<__nv_bfloat16, false>(ta, tb, tb2, p, s);
+}

@@ -1,0 +1,55 @@
+// Row-wise reduction scaffolding shared by RMSNorm and softmax.
+//
+// A row is owned by a GROUP of G threads (G = 8..1024, a power of two); a CTA
+// of kThreads threads holds kThreads/G rows.  Each thread keeps up to VPT
+// 16-byte vectors of its row in registers, so the row is read from HBM exactly
+// once; vector slots past the row end are predicated off (the masked tail).
+#pragma once
+
+#include "common.cuh"
+
+namespace b200 {
+
+constexpr int kRowThreads = 256;
+
+struct SumOp {
+  static __device__ __forceinline__ float apply(float a, float b) { return a + b; }
+  static __device__ __forceinline__ float identity() { return 0.f; }
+};
+struct MaxOp {
+  static __device__ __forceinline__ float apply(float a, float b) { return fmaxf(a, b); }
+  static __device__ __forceinline__ float identity() { return -INFINITY; }
+};
+
+// Reduce `v` over the G consecutive threads that own one row.  `scratch` has
+// one float per warp of the CTA.  Every thread of the CTA must call this.
+template <int G, typename Op>
+__device__ __forceinline__ float group_reduce(float v, float *scratch) {
+  constexpr int kIntra = G < 32 ? G : 32;
+#pragma unroll
+  for (int o = kIntra / 2; o > 0; o >>= 1)
+    v = Op::apply(v, __shfl_xor_sync(0xffffffffu, v, o));
+  if constexpr (G > 32) {
+    const int warp = threadIdx.x >> 5;
+    __syncthreads();  // scratch may still be read from the previous reduction
+    if ((threadIdx.x & 31) == 0) scratch[warp] = v;
+    __syncthreads();
+    constexpr int kWarps = G / 32;
+    const int first = (threadIdx.x / G) * kWarps;
+    v = scratch[first];
+#pragma unroll
+    for (int i = 1; i < kWarps; ++i) v = Op::apply(v, scratch[first + i]);
+  }
+  return v;
+}
+
+// Picks the group size: the smallest power of two G in [8, 1024] with
+// G * vpt >= nvec.  Returns 0 when the row does not fit (caller falls back to
+// the looping kernel).
+inline int pick_group(int64_t nvec, int vpt) {
+  for (int g = 8; g <= 1024; g <<= 1)
+    if ((int64_t)g * vpt >= nvec) return g;
+  return 0;
+}
+
+}  // namespace b200

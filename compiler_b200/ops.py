@@ -1,0 +1,88 @@
+"""Python entry points of the native operators.
+
+Each function takes device arrays -- anything with ``data_ptr()``, ``shape`` and
+``dtype`` (a :class:`compiler_b200.device.B200Buffer` or a CUDA ``torch.Tensor``;
+a tensor's own strides are honoured) -- builds the ``b200_tensor`` descriptors
+and calls the C ABI on ``stream`` (a raw ``cudaStream_t`` integer, 0 = the
+default stream).  Nothing here computes: a rejected descriptor raises
+:class:`compiler_b200.runtime.abi.B200Error`.
+"""
+from __future__ import annotations
+
+import ctypes
+
+from compiler_b200.runtime import abi
+
+
+def _desc(array, shape=None, strides=None):
+    if array is None:
+        return None
+    shape = tuple(array.shape) if shape is None else tuple(shape)
+    if strides is None:
+        stride_fn = getattr(array, "stride", None)
+        if callable(stride_fn) and len(tuple(array.shape)) == len(shape):
+            strides = tuple(int(s) for s in stride_fn())
+    return abi.make_tensor(array.data_ptr(), shape, array.dtype, strides)
+
+
+def _ref(tensor):
+    return ctypes.byref(tensor) if tensor is not None else None
+
+
+def rmsnorm(x, w, y, rinv=None, eps=1e-6, *, x_row_stride=None, y_row_stride=None, stream=0):
+    """y = x * rsqrt(mean(x^2) + eps) * w per row; rinv[row] = the inverse rms.
+
+    Native form of rms_layernorm_forward_kernel
+    (ops/suite/perf/fast_rms_layernorm.py:19-44)."""
+    rows, cols = (int(v) for v in x.shape)
+    xd = _desc(x, strides=None if x_row_stride is None else (int(x_row_stride), 1))
+    yd = _desc(y, strides=None if y_row_stride is None else (int(y_row_stride), 1))
+    wd = _desc(w, shape=(cols,), strides=(1,))
+    rd = _desc(rinv, shape=(rows,), strides=(1,)) if rinv is not None else None
+    abi.check(abi.lib().b200_rmsnorm_fwd(_ref(xd), _ref(wd), _ref(yd), _ref(rd), float(eps),
+                                         stream))
+
+
+def softmax(x, y, *, causal_mod=False, row_offset=0, stream=0):
+    """Row softmax; with ``causal_mod`` columns > (row_offset+row) % n_cols are -inf.
+
+    Native form of softmax_kernel (ops/suite/perf/softmax.py:20-31) with the mask
+    expression of ops/suite/perf/attn_fwd_causal.py:46-47."""
+    xd, yd = _desc(x), _desc(y)
+    mask = abi.MASK_CAUSAL_MOD if causal_mod else abi.MASK_NONE
+    abi.check(abi.lib().b200_softmax_fwd(_ref(xd), _ref(yd), mask, int(row_offset), stream))
+
+
+def gemm(a, b, c, *, bias=None, act=abi.ACT_NONE, b2=None, stream=0):
+    """c = act(a @ b + bias); with ``act=ACT_SWIGLU``: c = silu(a @ b) * (a @ b2).
+
+    Native form of matmul_kernel (ops/suite/perf/matmul.py:20-38) and
+    linear_act_kernel (ops/suite/perf/triton_linear_activation.py:27-49)."""
+    ad, bd, cd = _desc(a), _desc(b), _desc(c)
+    b2d = _desc(b2) if b2 is not None else None
+    biasd = _desc(bias, shape=(int(b.shape[1]),), strides=(1,)) if bias is not None else None
+    abi.check(abi.lib().b200_gemm_bias_act(_ref(ad), _ref(bd), _ref(b2d), _ref(biasd), _ref(cd),
+                                           int(act), stream))
+
+
+def attention(q, k, v, o, *, lse=None, scale=None, causal=True, stream=0):
+    """o = softmax(scale * q k^T (+ causal mask)) v over [Z,H,N,D]; lse = log-sum-exp.
+
+    Native form of attn_fwd_causal_kernel (ops/suite/perf/attn_fwd_causal.py:19-57)."""
+    if scale is None:
+        scale = 1.0 / float(q.shape[-1]) ** 0.5
+    qd, kd, vd, od = _desc(q), _desc(k), _desc(v), _desc(o)
+    ld = _desc(lse) if lse is not None else None
+    abi.check(abi.lib().b200_attn_fwd(_ref(qd), _ref(kd), _ref(vd), _ref(od), _ref(ld),
+                                      float(scale), 1 if causal else 0, stream))
+
+
+def swiglu(x, y, out, *, stream=0):
+    """out = x * sigmoid(x) * y (swiglu_fwd_kernel, ops/suite/perf/swiglu_fwd.py:18-36)."""
+    xd, yd, od = _desc(x), _desc(y), _desc(out)
+    abi.check(abi.lib().b200_swiglu_fwd(_ref(xd), _ref(yd), _ref(od), stream))
+
+
+def device_status(stream=0) -> None:
+    """Drain ``stream`` and raise if a kernel recorded an expired wait."""
+    abi.check(abi.lib().b200_last_device_status(stream))

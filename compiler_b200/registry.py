@@ -1,0 +1,341 @@
+"""Kernel handle -> native operator resolution for ``B200Device.launch``.
+
+The harness hands ``launch`` the object in ``case["kernel"]`` -- a Triton
+``JITFunction`` / ``Autotuner`` whose ``.fn`` chain ends in the Python function
+(``_kernel_target``, ops/harness/opslib/device.py:213-222) -- plus the grid, the
+positional values in signature order and the keyword metas.  The registry keys
+an operator on the function's *name and parameter list* (what ``bind_arguments``
+itself inspects, device.py:232-260), rebinds the values by name, checks the
+structural preconditions the native kernel needs, and calls the C ABI.  It never
+calls ``kernel[grid]``, never compiles, and raises :class:`UnsupportedLaunch`
+(located: kernel name + the violated precondition) for anything else, the
+counterpart of a100c's ``PipelineError`` (a100c/driver.py:79-87).
+"""
+from __future__ import annotations
+
+import inspect
+
+from compiler_b200 import ops
+from compiler_b200.runtime import abi
+
+
+class UnsupportedLaunch(RuntimeError):
+    """A launch this backend has no native operator for (never a silent guess)."""
+
+    def __init__(self, kernel_name: str, construct: str, message: str):
+        super().__init__(f"{kernel_name}: {construct}: {message}")
+        self.kernel_name = kernel_name
+        self.construct = construct
+        self.message = message
+
+
+def kernel_target(kernel):
+    target = kernel
+    for _ in range(8):
+        if inspect.isfunction(target):
+            return target
+        nested = getattr(target, "fn", None)
+        if nested is None or nested is target:
+            return target
+        target = nested
+    return target
+
+
+def kernel_signature(kernel):
+    """(function name, parameter names, names the autotuner supplies itself)."""
+    target = kernel_target(kernel)
+    name = getattr(target, "__name__", type(target).__name__)
+    try:
+        parameters = inspect.signature(target).parameters
+    except (TypeError, ValueError):
+        parameters = {}
+    configs = getattr(kernel, "configs", None)
+    autotuned = set((getattr(configs[0], "kwargs", {}) or {}).keys()) if configs else set()
+    return name, parameters, autotuned
+
+
+def bind_by_name(kernel, positional, keywords):
+    """Inverse of ``bind_arguments``: positional values back to a name -> value map."""
+    name, parameters, autotuned = kernel_signature(kernel)
+    values = dict(keywords)
+    it = iter(positional)
+    for pname, parameter in parameters.items():
+        if pname in values:
+            continue  # supplied by keyword (constexpr metas usually are)
+        if parameter.kind == inspect.Parameter.KEYWORD_ONLY or pname in autotuned:
+            continue
+        try:
+            values[pname] = next(it)
+        except StopIteration:
+            if parameter.default is inspect.Parameter.empty:
+                raise UnsupportedLaunch(name, "arguments",
+                                        f"missing positional value for {pname!r}") from None
+            values[pname] = parameter.default
+    leftover = list(it)
+    if leftover:
+        raise UnsupportedLaunch(name, "arguments", f"{len(leftover)} surplus positional values")
+    return values
+
+
+def _require(cond, kernel_name, construct, message):
+    if not cond:
+        raise UnsupportedLaunch(kernel_name, construct, message)
+
+
+def _is_buffer(value):
+    return hasattr(value, "data_ptr") and hasattr(value, "shape")
+
+
+def _count(buffer):
+    n = 1
+    for extent in buffer.shape:
+        n *= int(extent)
+    return n
+
+
+def _grid_tuple(grid, meta=None):
+    if callable(grid):
+        grid = grid(meta or {})
+    grid = tuple(int(v) for v in grid)
+    return grid + (1,) * (3 - len(grid))
+
+
+class _View:
+    """A reshaped alias of a device buffer (same pointer, new logical shape)."""
+
+    def __init__(self, buffer, shape, strides=None):
+        self._buffer = buffer
+        self.shape = tuple(int(v) for v in shape)
+        self._strides = strides
+        self.dtype = buffer.dtype
+
+    def data_ptr(self):
+        return self._buffer.data_ptr()
+
+    def stride(self):
+        if self._strides is not None:
+            return tuple(self._strides)
+        out, running = [], 1
+        for extent in reversed(self.shape):
+            out.append(running)
+            running *= max(extent, 1)
+        return tuple(reversed(out))
+
+
+# --------------------------------------------------------------------- adapters
+def _rmsnorm(device, v, grid, name):
+    """rms_layernorm_forward_kernel (ops/suite/perf/fast_rms_layernorm.py:20-27)."""
+    rows = _grid_tuple(grid)[0]
+    n_cols = int(v["n_cols"])
+    _require(int(v.get("BLOCK_SIZE", n_cols)) >= n_cols, name, "BLOCK_SIZE",
+             "the reference program covers a row with one block: BLOCK_SIZE >= n_cols")
+    _require(int(v["W_row_stride"]) == 1 and int(v["r_row_stride"]) == 1, name, "strides",
+             "W_row_stride and r_row_stride must be 1")
+    xs, ys = int(v["X_row_stride"]), int(v["Y_row_stride"])
+    _require(xs >= n_cols and ys >= n_cols, name, "strides", "row stride below n_cols")
+    x = _View(v["X"], (rows, n_cols), (xs, 1))
+    y = _View(v["Y"], (rows, n_cols), (ys, 1))
+    ops.rmsnorm(x, _View(v["W"], (n_cols,)), y, _View(v["r"], (rows,)), float(v["eps"]),
+                stream=device.stream)
+
+
+def _rmsnorm_loop(device, v, grid, name):
+    """rms_norm_loop_kernel (ops/suite/dev/hidden__rms_norm_loop_kernel.py:10-46) and
+    rmsnorm_fwd_loop_kernel (ops/suite/dev/rmsnorm_fwd_loop_kernel.py:10-34)."""
+    rows = _grid_tuple(grid)[0]
+    n = int(v["N"])
+    _require(not v.get("zero_centered_gamma", False), name, "zero_centered_gamma",
+             "the (1 + w) weight form has no native operator")
+    rinv = v.get("INV_RMS", v.get("rsigma_ptr"))
+    w = v.get("w_ptr", v.get("weight_ptr"))
+    ops.rmsnorm(_View(v["in_ptr"], (rows, n)), _View(w, (n,)), _View(v["out_ptr"], (rows, n)),
+                _View(rinv, (rows,)), float(v["eps"]), stream=device.stream)
+
+
+def _softmax(device, v, grid, name):
+    """softmax_kernel (ops/suite/perf/softmax.py:21)."""
+    rows = _grid_tuple(grid)[0]
+    n_cols = int(v["n_cols"])
+    ops.softmax(_View(v["x_ptr"], (rows, n_cols)), _View(v["y_ptr"], (rows, n_cols)),
+                stream=device.stream)
+
+
+def _softmax_inner(device, v, grid, name):
+    """softmax_kernel_inner (ops/suite/dev/softmax_kernel_inner.py:12)."""
+    m, n = int(v["M"]), int(v["N"])
+    _require(_grid_tuple(grid)[0] == m, name, "grid", "expected one program per row")
+    ops.softmax(_View(v["input_ptr"], (m, n)), _View(v["output_ptr"], (m, n)),
+                stream=device.stream)
+
+
+def _masked_softmax(device, v, grid, name):
+    """Native handle: row softmax with the causal-mod mask (kernels.masked_softmax_kernel)."""
+    rows = _grid_tuple(grid)[0]
+    n_cols = int(v["n_cols"])
+    ops.softmax(_View(v["x_ptr"], (rows, n_cols)), _View(v["y_ptr"], (rows, n_cols)),
+                causal_mod=True, row_offset=int(v.get("row_offset", 0)), stream=device.stream)
+
+
+def _matmul_plain(device, v, grid, name):
+    """matmul_kernel (ops/suite/perf/matmul.py:21): contiguous row-major A, B, Y."""
+    m, n, k = int(v["M"]), int(v["N"]), int(v["K"])
+    ops.gemm(_View(v["a_ptr"], (m, k)), _View(v["b_ptr"], (k, n)), _View(v["y_ptr"], (m, n)),
+             stream=device.stream)
+
+
+def _row_major(v, name, prefix_pairs):
+    for rows_key, unit_key in prefix_pairs:
+        _require(int(v[unit_key]) == 1, name, unit_key,
+                 "only row-major operands (unit inner stride) have a native kernel")
+
+
+def _matmul_strided(device, v, grid, name):
+    """matmul_kernel (ops/suite/perf/matmul_triton2.py:27-30, matmul_triton_autotune.py:28-31)."""
+    m, n, k = int(v["M"]), int(v["N"]), int(v["K"])
+    _row_major(v, name, (("stride_am", "stride_ak"), ("stride_bk", "stride_bn"),
+                         ("stride_cm", "stride_cn")))
+    leaky = bool(v.get("LEAKY", False))
+    if leaky:
+        _require(abs(float(v.get("SLOPE", 0.01)) - 0.01) < 1e-12, name, "SLOPE",
+                 "the native leaky-ReLU epilogue uses slope 0.01")
+    ops.gemm(_View(v["a_ptr"], (m, k), (int(v["stride_am"]), 1)),
+             _View(v["b_ptr"], (k, n), (int(v["stride_bk"]), 1)),
+             _View(v["c_ptr"], (m, n), (int(v["stride_cm"]), 1)),
+             act=abi.ACT_LEAKY_RELU if leaky else abi.ACT_NONE, stream=device.stream)
+
+
+def _linear_act(device, v, grid, name):
+    """linear_act_kernel (ops/suite/perf/triton_linear_activation.py:28-30): bias + erf-GELU."""
+    m, n, k = int(v["M"]), int(v["N"]), int(v["K"])
+    _row_major(v, name, (("stride_xm", "stride_xk"), ("stride_wk", "stride_wn"),
+                         ("stride_ym", "stride_yn")))
+    ops.gemm(_View(v["x_ptr"], (m, k), (int(v["stride_xm"]), 1)),
+             _View(v["w_ptr"], (k, n), (int(v["stride_wk"]), 1)),
+             _View(v["y_ptr"], (m, n), (int(v["stride_ym"]), 1)),
+             bias=_View(v["b_ptr"], (n,)), act=abi.ACT_GELU_ERF, stream=device.stream)
+
+
+def _gemm_bias_act(device, v, grid, name):
+    """Native handle: C = act(A @ B + bias) with a selectable epilogue
+    (kernels.gemm_bias_act_kernel)."""
+    m, n, k = int(v["M"]), int(v["N"]), int(v["K"])
+    bias = v.get("bias_ptr")
+    ops.gemm(_View(v["a_ptr"], (m, k)), _View(v["b_ptr"], (k, n)), _View(v["c_ptr"], (m, n)),
+             bias=_View(bias, (n,)) if _is_buffer(bias) else None, act=int(v["ACT"]),
+             stream=device.stream)
+
+
+def _attention(device, v, grid, name):
+    """attn_fwd_causal_kernel (ops/suite/perf/attn_fwd_causal.py:20-28) and its twins."""
+    z, h, n = int(v["Z"]), int(v["H"]), int(v["N_CTX"])
+    d = int(v["HEAD_DIM"])
+    _require(int(v["stride_qk"]) == 1 and int(v["stride_kk"]) == 1 and
+             int(v["stride_vn"]) == 1 and int(v["stride_on"]) == 1, name, "strides",
+             "the head dimension must have unit stride")
+    g = _grid_tuple(grid)
+    _require(g[0] == n and g[1] == z * h, name, "grid", "expected grid (N_CTX, Z*H)")
+
+    def view(key, sz, sh, sm):
+        return _View(v[key], (z, h, n, d), (int(v[sz]), int(v[sh]), int(v[sm]), 1))
+
+    lse = v.get("lse_ptr")
+    ops.attention(view("q_ptr", "stride_qz", "stride_qh", "stride_qm"),
+                  view("k_ptr", "stride_kz", "stride_kh", "stride_kn"),
+                  view("v_ptr", "stride_vz", "stride_vh", "stride_vk"),
+                  view("out_ptr", "stride_oz", "stride_oh", "stride_om"),
+                  lse=_View(lse, (z, h, n)) if _is_buffer(lse) else None,
+                  scale=float(v["scale"]), causal=bool(v["CAUSAL"]), stream=device.stream)
+
+
+def _swiglu(device, v, grid, name):
+    """swiglu_fwd_kernel (ops/suite/perf/swiglu_fwd.py:27-28, swiglu_triton.py:19-20)."""
+    rows = _grid_tuple(grid, {"BLOCK_N": 32})[0]
+    cols = int(v["ncols"])
+    ops.swiglu(_View(v["X"], (rows, cols), (int(v["stride_x_row"]), 1)),
+               _View(v["Y"], (rows, cols), (int(v["stride_y_row"]), 1)),
+               _View(v["OUT"], (rows, cols), (int(v["stride_out_row"]), 1)),
+               stream=device.stream)
+
+
+def _swiglu_gemm(device, v, grid, name):
+    """Native handle: H = silu(X @ Wg) * (X @ Wu) in one kernel (kernels.swiglu_gemm_kernel)."""
+    m, n, k = int(v["M"]), int(v["N"]), int(v["K"])
+    ops.gemm(_View(v["x_ptr"], (m, k)), _View(v["wg_ptr"], (k, n)), _View(v["h_ptr"], (m, n)),
+             b2=_View(v["wu_ptr"], (k, n)), act=abi.ACT_SWIGLU, stream=device.stream)
+
+
+class Registry:
+    """(kernel name, parameter names) -> adapter."""
+
+    def __init__(self):
+        self._entries = {}
+
+    def register(self, name, parameters, adapter):
+        self._entries[(name, tuple(parameters))] = adapter
+
+    def resolve(self, kernel):
+        name, parameters, _ = kernel_signature(kernel)
+        adapter = self._entries.get((name, tuple(parameters)))
+        if adapter is None:
+            raise UnsupportedLaunch(
+                name, "kernel",
+                f"no native sm_100a operator is registered for signature "
+                f"({', '.join(parameters)}); nothing falls back to Triton or the host")
+        return name, adapter
+
+    def supports(self, kernel) -> bool:
+        name, parameters, _ = kernel_signature(kernel)
+        return (name, tuple(parameters)) in self._entries
+
+    def launch(self, device, kernel, grid, positional, keywords):
+        name, adapter = self.resolve(kernel)
+        values = bind_by_name(kernel, positional, keywords)
+        adapter(device, values, grid, name)
+
+
+_ATTN = ("q_ptr", "k_ptr", "v_ptr", "out_ptr", "Z", "H", "N_CTX", "scale",
+         "stride_qz", "stride_qh", "stride_qm", "stride_qk",
+         "stride_kz", "stride_kh", "stride_kn", "stride_kk",
+         "stride_vz", "stride_vh", "stride_vk", "stride_vn",
+         "stride_oz", "stride_oh", "stride_om", "stride_on",
+         "HEAD_DIM", "BLOCK_N", "CAUSAL")
+_MATMUL_STRIDED = ("a_ptr", "b_ptr", "c_ptr", "M", "N", "K", "stride_am", "stride_ak",
+                   "stride_bk", "stride_bn", "stride_cm", "stride_cn", "LEAKY", "SLOPE",
+                   "BLOCK_M", "BLOCK_N", "BLOCK_K")
+
+
+def default_registry() -> Registry:
+    from compiler_b200 import kernels
+    r = Registry()
+    r.register("rms_layernorm_forward_kernel",
+               ("Y", "Y_row_stride", "X", "X_row_stride", "W", "W_row_stride", "r",
+                "r_row_stride", "n_cols", "eps", "BLOCK_SIZE"), _rmsnorm)
+    r.register("rms_norm_loop_kernel",
+               ("out_ptr", "INV_RMS", "in_ptr", "w_ptr", "N", "eps", "TILE_N"), _rmsnorm_loop)
+    r.register("rmsnorm_fwd_loop_kernel",
+               ("out_ptr", "rsigma_ptr", "in_ptr", "weight_ptr", "N", "eps",
+                "zero_centered_gamma", "TILE_N"), _rmsnorm_loop)
+    r.register("softmax_kernel", ("x_ptr", "y_ptr", "n_cols", "BLOCK_N"), _softmax)
+    r.register("softmax_kernel_inner",
+               ("output_ptr", "input_ptr", "M", "N", "TILE_N", "ONE_TILE_PER_CTA"),
+               _softmax_inner)
+    r.register("matmul_kernel", ("a_ptr", "b_ptr", "y_ptr", "M", "N", "K"), _matmul_plain)
+    r.register("matmul_kernel", _MATMUL_STRIDED, _matmul_strided)
+    r.register("linear_act_kernel",
+               ("x_ptr", "w_ptr", "b_ptr", "y_ptr", "M", "N", "K", "stride_xm", "stride_xk",
+                "stride_wk", "stride_wn", "stride_ym", "stride_yn", "BLOCK_M", "BLOCK_N",
+                "BLOCK_K"), _linear_act)
+    for attn_name in ("attn_fwd_causal_kernel", "attention_forward_kernel", "attention_kernel",
+                      "context_attn_fwd_kernel"):
+        r.register(attn_name, _ATTN, _attention)
+    r.register("swiglu_fwd_kernel",
+               ("X", "Y", "OUT", "stride_x_row", "stride_y_row", "stride_out_row", "ncols",
+                "BLOCK_N"), _swiglu)
+    # native handles for the configurations no single reference kernel covers
+    for handle, adapter in ((kernels.masked_softmax_kernel, _masked_softmax),
+                            (kernels.gemm_bias_act_kernel, _gemm_bias_act),
+                            (kernels.attn_fwd_lse_kernel, _attention),
+                            (kernels.swiglu_gemm_kernel, _swiglu_gemm)):
+        name, parameters, _ = kernel_signature(handle)
+        r.register(name, tuple(parameters), adapter)
+    return r

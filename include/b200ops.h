@@ -1,0 +1,206 @@
+/* b200ops.h -- the C ABI of the sm_100a operator library (libb200ops.so).
+ *
+ * This is the single declaration of everything that crosses between the
+ * Python host (ctypes) and the CUDA kernels.  It plays the role that
+ * a100c/runtime/a100rt.h:1-218 plays between the a100c runtime and its
+ * generated operator programs: one header, plain C types, layout pins.
+ *
+ * Conventions
+ *   - every entry point validates its descriptors and RETURNS a status; it
+ *     never aborts, traps or launches a kernel on a rejected descriptor
+ *     (the "rejected bundle is never written" rule of
+ *     a100c/runtime/bundle.c:1-9);
+ *   - the caller owns all memory; `data` pointers are DEVICE pointers unless
+ *     a function says otherwise; strides are in ELEMENTS;
+ *   - `stream` is a cudaStream_t passed as void*; launches are asynchronous
+ *     and no entry point synchronises unless it says so;
+ *   - tensor-core kernels bound every device-side wait; when a wait expires
+ *     the kernel records B200_TIMEOUT in the library's per-device status
+ *     word, which b200_last_device_status() returns after the stream drains.
+ */
+#ifndef B200OPS_H
+#define B200OPS_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B200_ABI_VERSION 1
+
+/* Status codes.  0..6 keep the numbering of the a100c process exit codes
+ * (a100c/runtime/a100rt.h:49-55); 7.. are additions of this library. */
+enum b200_status {
+  B200_OK = 0,
+  B200_USAGE = 2,           /* argument outside the contract (null, bad enum) */
+  B200_REJECTED = 3,        /* descriptor violates a precondition */
+  B200_RESOURCE = 4,        /* allocation / CUDA runtime failure */
+  B200_REPEAT_MISMATCH = 5, /* repeats produced different outputs */
+  B200_SYNC = 6,            /* stream / device synchronisation failed */
+  B200_TIMEOUT = 7,         /* a bounded device-side wait expired */
+  B200_UNSUPPORTED = 8      /* valid request this build has no kernel for */
+};
+
+/* dtype codes: the a100rt_dtype numbering (a100c/runtime/a100rt.h:58-72). */
+enum b200_dtype {
+  B200_DTYPE_BOOL = 1,
+  B200_DTYPE_INT8 = 2,
+  B200_DTYPE_UINT8 = 3,
+  B200_DTYPE_INT16 = 4,
+  B200_DTYPE_UINT16 = 5,
+  B200_DTYPE_INT32 = 6,
+  B200_DTYPE_UINT32 = 7,
+  B200_DTYPE_INT64 = 8,
+  B200_DTYPE_UINT64 = 9,
+  B200_DTYPE_FLOAT16 = 10,
+  B200_DTYPE_BFLOAT16 = 11,
+  B200_DTYPE_FLOAT32 = 12,
+  B200_DTYPE_FLOAT64 = 13
+};
+
+/* One tensor argument (the role of struct a100rt_view,
+ * a100c/runtime/a100rt.h:79-92).  Dimensions beyond ndim are ignored. */
+typedef struct b200_tensor {
+  void *data;
+  int64_t shape[4];
+  int64_t stride[4]; /* in elements */
+  uint32_t dtype;    /* enum b200_dtype */
+  uint32_t ndim;
+} b200_tensor;
+
+typedef struct b200_device_props {
+  char name[64];
+  int32_t cc_major, cc_minor;
+  int32_t sm_count;
+  int32_t l2_bytes;
+  int64_t hbm_bytes;
+  int32_t smem_per_block_optin;
+  int32_t clock_khz;
+} b200_device_props;
+
+/* GEMM epilogue selector */
+enum b200_act {
+  B200_ACT_NONE = 0,
+  B200_ACT_GELU_ERF = 1,  /* 0.5 z (1 + erf(z / sqrt 2)), triton_linear_activation.py:46 */
+  B200_ACT_GELU_TANH = 2, /* 0.5 z (1 + tanh(0.79788456 (z + 0.044715 z^3))), geglu_tanh_triton.py:32-36 */
+  B200_ACT_LEAKY_RELU = 3,/* z >= 0 ? z : 0.01 z, matmul_triton2.py:77 */
+  B200_ACT_SWIGLU = 4     /* silu(a@b) * (a@b2): two B operands, swiglu_fwd.py:34-36 over two matmuls */
+};
+
+enum b200_mask {
+  B200_MASK_NONE = 0,
+  B200_MASK_CAUSAL_MOD = 1 /* keep col <= (row_offset + row) % n_cols, -inf elsewhere */
+};
+
+/* ---- library / device ------------------------------------------------- */
+int b200_abi_version(void);
+/* Text for a status code (the role of a100rt_reject_reason,
+ * a100c/runtime/bundle.c:59-88). */
+const char *b200_status_string(int status);
+/* Detail of the most recent non-OK return on this host thread. */
+const char *b200_last_error(void);
+/* Replaces the device discovery of ops/harness/opslib/devices/cuda.py:329-345. */
+int b200_device_query(int device, b200_device_props *out);
+int b200_set_device(int device);
+/* Reads (and clears) the per-device status word that kernels with bounded
+ * waits write; synchronises `stream` first. */
+int b200_last_device_status(void *stream);
+
+/* ---- memory, streams, events (torch-free Device plumbing; replaces the
+ *      cudaMalloc / pinned staging / event timer of
+ *      ops/harness/opslib/devices/cuda.py:71-123, 138-167, 186-262) -------- */
+int b200_malloc(void **out, size_t bytes);
+int b200_free(void *ptr);
+int b200_malloc_host(void **out, size_t bytes); /* pinned */
+int b200_free_host(void *ptr);
+int b200_memcpy_h2d(void *dst, const void *src, size_t bytes, void *stream);
+int b200_memcpy_d2h(void *dst, const void *src, size_t bytes, void *stream);
+int b200_memcpy_d2d(void *dst, const void *src, size_t bytes, void *stream);
+int b200_memset(void *dst, int value, size_t bytes, void *stream);
+int b200_stream_create(void **out);
+int b200_stream_destroy(void *stream);
+int b200_stream_sync(void *stream);
+int b200_device_sync(void);
+int b200_event_create(void **out);
+int b200_event_destroy(void *event);
+int b200_event_record(void *event, void *stream);
+int b200_event_elapsed_ms(void *start, void *stop, float *ms); /* syncs stop */
+
+/* ---- operators -------------------------------------------------------- */
+
+/* RMSNorm forward.  Replaces rms_layernorm_forward_kernel
+ * (ops/suite/perf/fast_rms_layernorm.py:19-44): per row
+ * inv = rsqrt(mean(x^2) + eps); y = x * inv * w; rinv[row] = inv.
+ * x,y: [rows, cols] with unit column stride; w: [cols]; rinv: [rows] or NULL.
+ * x/y/w/rinv share one dtype (f32, f16 or bf16); accumulation is fp32. */
+int b200_rmsnorm_fwd(const b200_tensor *x, const b200_tensor *w,
+                     b200_tensor *y, b200_tensor *rinv, float eps,
+                     void *stream);
+
+/* Row softmax with an optional index-computed mask.  Replaces softmax_kernel
+ * (ops/suite/perf/softmax.py:20-31) and, with B200_MASK_CAUSAL_MOD, the
+ * masking expression of ops/suite/perf/attn_fwd_causal.py:46-47 applied to a
+ * row softmax.  x,y: contiguous [rows, cols], same dtype (f32/f16/bf16);
+ * max and sum are fp32.  row_offset is the global index of local row 0 so a
+ * row shard masks by its global row. */
+int b200_softmax_fwd(const b200_tensor *x, b200_tensor *y, int mask_kind,
+                     int64_t row_offset, void *stream);
+
+/* C = act(A @ B + bias).  Replaces matmul_kernel (ops/suite/perf/matmul.py:20-38)
+ * and linear_act_kernel (ops/suite/perf/triton_linear_activation.py:27-49).
+ * A [M,K] row-major, B [K,N] row-major, C [M,N] row-major; A/B are f16 or
+ * bf16 (same type), accumulation fp32, C is A's type or f32; bias [N] may be
+ * NULL and is f32 or A's type.  b2 is the second B operand of
+ * B200_ACT_SWIGLU (NULL otherwise).  Shapes whose row pitches are not
+ * multiples of 16 bytes take a CUDA-core kernel instead of the tensor-core
+ * path; nothing is computed on the host. */
+int b200_gemm_bias_act(const b200_tensor *a, const b200_tensor *b,
+                       const b200_tensor *b2, const b200_tensor *bias,
+                       b200_tensor *c, int act, void *stream);
+
+/* Attention forward.  Replaces attn_fwd_causal_kernel
+ * (ops/suite/perf/attn_fwd_causal.py:19-57).  q,k,v,o: [Z,H,N,D] with unit
+ * last stride (f16/bf16); lse: [Z,H,N] f32 or NULL, natural log of the sum of
+ * exp of the scaled masked scores (ops/suite/dev/flash_varlen_fwd_kernel.py:309). */
+int b200_attn_fwd(const b200_tensor *q, const b200_tensor *k,
+                  const b200_tensor *v, b200_tensor *o, b200_tensor *lse,
+                  float scale, int causal, void *stream);
+
+/* out = x * sigmoid(x) * y elementwise.  Replaces swiglu_fwd_kernel
+ * (ops/suite/perf/swiglu_fwd.py:18-36).  [rows, cols], unit column stride. */
+int b200_swiglu_fwd(const b200_tensor *x, const b200_tensor *y,
+                    b200_tensor *out, void *stream);
+
+/* On-device allclose of two same-shape contiguous f32 buffers.  Replaces
+ * _allclose_kernel (ops/harness/opslib/devices/_cuda_compare.py:24-46).
+ * result[0] = number of violating elements, max_abs_err = max |a-b| over
+ * elements that are not exactly equal.  Synchronises `stream`. */
+int b200_allclose_f32(const void *actual, const void *expected, int64_t count,
+                      double rtol, double atol, int equal_nan,
+                      int64_t *bad_count, double *max_abs_err, void *stream);
+
+/* Runs `repeats` launches of an operator closure-free: restores `out` from
+ * nothing, compares launch r>0 bitwise with launch 0 (the --repeats check of
+ * a100c/runtime/main.c:117-152).  first/other: device buffers of `bytes`.
+ * Returns B200_REPEAT_MISMATCH when they differ.  Synchronises `stream`. */
+int b200_bitwise_equal(const void *first, const void *other, size_t bytes,
+                       int *equal, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+
+/* Layout pins: the ctypes Structures in compiler_b200/runtime/abi.py mirror
+ * these; a layout change must update both (a100rt.h:186-216 does the same for
+ * the assembly stub). */
+#ifdef __cplusplus
+static_assert(sizeof(b200_tensor) == 80, "b200_tensor layout");
+static_assert(offsetof(b200_tensor, shape) == 8, "b200_tensor.shape");
+static_assert(offsetof(b200_tensor, stride) == 40, "b200_tensor.stride");
+static_assert(offsetof(b200_tensor, dtype) == 72, "b200_tensor.dtype");
+static_assert(sizeof(b200_device_props) == 96, "b200_device_props layout");
+#endif
+
+#endif /* B200OPS_H */

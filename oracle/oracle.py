@@ -1,0 +1,217 @@
+"""CPU oracle: numpy restatement of the reference's ``ref`` functions.
+
+TEST INFRASTRUCTURE ONLY.  Nothing in ``compiler_b200/`` imports this module;
+it is the checker for ``tests/``, ``__graft_entry__.smoke()`` and the
+``cpu_baseline`` / ``--impl reference`` legs of ``bench.py``.
+
+Every function restates the float64 numpy oracle of one reference operator file
+(paths relative to the reference tree) and says which lines it follows.  Parity
+is PINNED: ``tests/test_oracle_golden.py`` checks each function against golden
+inputs/outputs produced by importing the reference's own operator modules
+(``tests/golden/make_golden.py``; fixtures in ``tests/golden/*.npz``), for every
+declared shape and dtype of those files.
+
+Inputs are expected in their host representation -- float32 values already
+rounded to bf16 for bf16 cases (ops/harness/opslib/case.py:223-232) -- and all
+arithmetic is float64, as in the reference.
+"""
+from __future__ import annotations
+
+import math
+
+import numpy as np
+
+try:  # scipy-backed erf, as ops/harness/opslib/mathref.py:42-52 prefers
+    from scipy.special import erf as _erf
+except Exception:  # noqa: BLE001 - same fallback as mathref.py:30-39
+    _erf = np.vectorize(math.erf, otypes=[np.float64])
+
+
+# ----------------------------------------------------------------- rounding
+def bf16_round(array) -> np.ndarray:
+    """float32 values rounded to bfloat16, round-to-nearest-even, NaN kept quiet.
+
+    Follows ``_bf16_host`` (ops/harness/opslib/case.py:214-220)."""
+    values = np.ascontiguousarray(array, dtype=np.float32)
+    bits = values.view(np.uint32)
+    rounded = (bits + np.uint32(0x7FFF) + ((bits >> 16) & np.uint32(1))) & np.uint32(0xFFFF0000)
+    rounded = np.where(np.isnan(values), bits | np.uint32(0x00400000), rounded)
+    return rounded.astype(np.uint32).view(np.float32)
+
+
+def to_storage(array, dtype: str) -> np.ndarray:
+    """Host representation of ``array`` in a case dtype (``_cast_float_array``,
+    ops/harness/opslib/case.py:223-232): bf16 -> rounded float32, else astype."""
+    if dtype == "bfloat16":
+        return bf16_round(array)
+    return np.ascontiguousarray(array, dtype=np.dtype(dtype))
+
+
+# ----------------------------------------------------------------- operators
+def rmsnorm_ref(x, w, eps):
+    """``ref`` of ops/suite/perf/fast_rms_layernorm.py:52-61.
+
+    Returns (Y, r) in float64: var = sum(x*x)/n_cols; inv = 1/sqrt(var+eps);
+    Y = (x*inv)*w; r = inv per row."""
+    x = np.asarray(x, dtype=np.float64)
+    w = np.asarray(w, dtype=np.float64)
+    n_cols = x.shape[1]
+    var = (x * x).sum(axis=1, keepdims=True) / n_cols
+    inv = 1.0 / np.sqrt(var + float(eps))
+    return (x * inv) * w[None, :], inv.reshape(-1)
+
+
+def softmax_ref(x):
+    """``ref`` of ops/suite/perf/softmax.py:40-45: e = exp(x - rowmax); e / sum(e)."""
+    x64 = np.asarray(x, dtype=np.float64)
+    e = np.exp(x64 - x64.max(-1, keepdims=True))
+    return e / e.sum(-1, keepdims=True)
+
+
+def masked_softmax_ref(x, row_offset: int = 0):
+    """softmax.ref (ops/suite/perf/softmax.py:40-45) applied to
+    ``np.where(mask, x, -inf)`` with the mask of attn_fwd_causal.ref
+    (ops/suite/perf/attn_fwd_causal.py:70-71): column c of global row g is kept
+    iff c <= g % n_cols.  A composition of two reference oracles; the reference
+    has no single file for it."""
+    x64 = np.asarray(x, dtype=np.float64)
+    rows, cols = x64.shape
+    limit = (np.arange(rows, dtype=np.int64) + int(row_offset)) % cols
+    mask = np.arange(cols, dtype=np.int64)[None, :] <= limit[:, None]
+    return softmax_ref(np.where(mask, x64, -np.inf))
+
+
+def matmul_ref(a, b):
+    """``ref`` of ops/suite/perf/matmul.py:46-50: float64 a @ b."""
+    return np.asarray(a, dtype=np.float64) @ np.asarray(b, dtype=np.float64)
+
+
+def gelu_erf(z):
+    """0.5 z (1 + erf(z/sqrt 2)) (ops/suite/perf/triton_linear_activation.py:62)."""
+    return 0.5 * z * (1.0 + _erf(z * 0.7071067811865476))
+
+
+def gelu_tanh(z):
+    """0.5 z (1 + tanh(0.79788456 (z + 0.044715 z^3))) (ops/suite/perf/geglu_tanh_triton.py:44-49)."""
+    return 0.5 * z * (1.0 + np.tanh(0.7978845608028654 * (z + 0.044715 * z * z * z)))
+
+
+def leaky_relu(z, slope=0.01):
+    """np.where(z >= 0, z, slope*z) (ops/suite/perf/matmul_triton2.py ref)."""
+    return np.where(z >= 0, z, slope * z)
+
+
+def linear_act_ref(x, w, bias=None, act: str = "gelu_erf"):
+    """``ref`` of ops/suite/perf/triton_linear_activation.py:56-63 (x @ w + b, erf-GELU),
+    with the activation selectable: "none", "gelu_erf", "gelu_tanh" (the formula of
+    ops/suite/perf/geglu_tanh_triton.py:44-49), "leaky_relu"."""
+    acc = matmul_ref(x, w)
+    if bias is not None:
+        acc = acc + np.asarray(bias, dtype=np.float64)[None, :]
+    if act == "none":
+        return acc
+    if act == "gelu_erf":
+        return gelu_erf(acc)
+    if act == "gelu_tanh":
+        return gelu_tanh(acc)
+    if act == "leaky_relu":
+        return leaky_relu(acc)
+    raise ValueError(f"unknown activation {act!r}")
+
+
+def attention_head_ref(q, k, v, scale, causal=True):
+    """One (batch, head) slice of ``ref`` of ops/suite/perf/attn_fwd_causal.py:63-76,
+    plus the log-sum-exp of ops/suite/dev/flash_varlen_fwd_kernel.py:412-418
+    (rowmax + log(sum(exp(scores - rowmax))) over the scaled, masked scores).
+
+    q, k, v: [N, D].  Returns (out [N, D], lse [N]) in float64.  Heads are
+    independent, so evaluating the reference per slice gives the same numbers as
+    its whole-tensor einsum while holding one [N, N] score matrix at a time."""
+    q = np.asarray(q, dtype=np.float64)
+    k = np.asarray(k, dtype=np.float64)
+    v = np.asarray(v, dtype=np.float64)
+    n = q.shape[0]
+    scores = (q @ k.T) * float(scale)
+    if causal:
+        scores = np.where(np.tril(np.ones((n, n), dtype=bool)), scores, -np.inf)
+    row_max = scores.max(axis=-1, keepdims=True)
+    p = np.exp(scores - row_max)
+    denom = p.sum(axis=-1, keepdims=True)
+    out = (p / denom) @ v
+    lse = row_max[:, 0] + np.log(denom[:, 0])
+    return out, lse
+
+
+def attention_ref(q, k, v, scale, causal=True):
+    """``ref`` of ops/suite/perf/attn_fwd_causal.py:63-76 over [Z,H,N,D], slice by slice."""
+    q = np.asarray(q)
+    z, h, n, d = q.shape
+    out = np.empty((z, h, n, d), dtype=np.float64)
+    lse = np.empty((z, h, n), dtype=np.float64)
+    for zi in range(z):
+        for hi in range(h):
+            out[zi, hi], lse[zi, hi] = attention_head_ref(q[zi, hi], k[zi, hi], v[zi, hi], scale,
+                                                          causal)
+    return out, lse
+
+
+def swiglu_ref(x, y):
+    """``ref`` of ops/suite/perf/swiglu_fwd.py:43-47: x / (1 + exp(-x)) * y."""
+    x = np.asarray(x, dtype=np.float64)
+    y = np.asarray(y, dtype=np.float64)
+    return x / (1.0 + np.exp(-x)) * y
+
+
+def swiglu_mlp_ref(x, wg, wu, wd, h_dtype: str | None = None):
+    """y = (silu(x @ Wg) * (x @ Wu)) @ Wd built from matmul.ref
+    (ops/suite/perf/matmul.py:46-50) and swiglu_fwd.ref (ops/suite/perf/swiglu_fwd.py:43-47).
+    The reference never performs this composition in one case and has no multi-device
+    path; the unsharded float64 result pins the tensor-parallel one end to end.
+    ``h_dtype``: optionally round the intermediate to its storage type first, to bound the
+    error a 16-bit intermediate buffer is allowed to add."""
+    h = swiglu_ref(matmul_ref(x, wg), matmul_ref(x, wu))
+    if h_dtype is not None:
+        h = to_storage(h.astype(np.float32), h_dtype).astype(np.float64)
+    return matmul_ref(h, wd)
+
+
+# ----------------------------------------------------------------- comparison
+DTYPE_TOLERANCES = {  # ops/harness/opslib/case.py:153-157
+    "float32": (1e-3, 1e-3),
+    "float16": (1e-2, 1e-2),
+    "bfloat16": (2e-2, 2e-2),
+}
+
+
+def compare(actual, expected, rtol, atol, equal_nan=True, name="output"):
+    """``_allclose_pass`` of ops/harness/opslib/compare.py:107-140: the verdict is
+    ``np.isclose(actual, expected)`` evaluated in the arrays' own dtypes; returns the
+    informational max |a-b| (float64, over elements that are not exactly equal) and
+    raises AssertionError listing the first violating flat indices."""
+    actual = np.asarray(actual)
+    expected = np.asarray(expected)
+    if actual.shape != expected.shape:
+        raise AssertionError(f"{name}: shape {actual.shape} != expected {expected.shape}")
+    a = actual.reshape(-1)
+    b = expected.reshape(-1)
+    chunk = 16 * 1024 * 1024
+    max_error = 0.0
+    violations = []
+    for start in range(0, a.size, chunk):
+        ca, cb = a[start:start + chunk], b[start:start + chunk]
+        close = np.isclose(ca, cb, rtol=rtol, atol=atol, equal_nan=equal_nan)
+        if not close.all():
+            violations.extend(int(i) + start for i in np.flatnonzero(~close)[:8])
+        with np.errstate(invalid="ignore", over="ignore"):
+            delta = np.abs(ca.astype(np.float64) - cb.astype(np.float64))
+            equal = ca == cb
+            if equal_nan:
+                equal = equal | (np.isnan(ca) & np.isnan(cb))
+            max_error = max(max_error, float(np.where(equal, 0.0, delta).max(initial=0.0)))
+    if violations:
+        first = violations[0]
+        raise AssertionError(
+            f"{name}: not close to tolerance rtol={rtol:g}, atol={atol:g}; first bad flat "
+            f"indices {violations[:8]}, e.g. output={a[first]!r} vs reference={b[first]!r}; "
+            f"max_abs_error={max_error:g}")
+    return max_error
