@@ -19,6 +19,7 @@
 #include "sm100.cuh"
 
 #include <mutex>
+#include <stdlib.h>
 
 namespace b200 {
 
@@ -96,6 +97,7 @@ struct Params {
   uint32_t idesc;
   int vector_store;  // rows of C are 16-byte aligned and N % 8 == 0 (N % 4 for f32)
   unsigned int *status;
+  uint32_t b_lbo, b_sbo;  // B-operand descriptor pitches (bytes)
 };
 
 __device__ __forceinline__ float gelu_tanh_fast(float z) {
@@ -254,7 +256,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
           tc_fence_after_sync();
           const uint64_t a_desc = make_smem_desc_sw128(a_smem + stage * A_STAGE_BYTES, 16, 1024);
           const uint64_t b_desc =
-              make_smem_desc_sw128(b_smem + stage * B_STAGE_BYTES, B_BOX_BYTES, 1024);
+              make_smem_desc_sw128(b_smem + stage * B_STAGE_BYTES, p.b_lbo, p.b_sbo);
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k) {
             // A: +32 bytes along K inside the swizzle span; B: +16 K-rows of 128 bytes
@@ -538,6 +540,12 @@ extern "C" int b200_gemm_bias_act(const b200_tensor *a, const b200_tensor *b,
   p.vector_store = ((c->stride[0] * cs) % 16 == 0 && (uintptr_t)c->data % 16 == 0) ? 1 : 0;
   p.status = device_status_word();
   if (p.status == nullptr) return fail(B200_RESOURCE, "no status word on this device");
+  p.b_lbo = B_BOX_BYTES;  // pitch between 64-column chunks of the B tile
+  p.b_sbo = 1024;         // pitch between groups of 8 K-rows
+  if (const char *e = getenv("B200OPS_GEMM_BDESC")) {  // bring-up override: "lbo,sbo"
+    unsigned lbo = 0, sbo = 0;
+    if (sscanf(e, "%u,%u", &lbo, &sbo) == 2) { p.b_lbo = lbo; p.b_sbo = sbo; }
+  }
 
   const bool dual = act == B200_ACT_SWIGLU;
   if (c->dtype == B200_DTYPE_FLOAT32)

@@ -235,6 +235,26 @@ class B200Device:
             abi.check(self._lib.b200_stream_sync(self.stream))
         return buffer
 
+    def copy_in(self, buffer, array, *, sync=False):
+        """Host array (ideally from ``pinned_empty``) -> an EXISTING device buffer of the
+        same storage type; asynchronous on the device stream unless ``sync``."""
+        array = np.ascontiguousarray(array)
+        if array.nbytes != buffer.nbytes:
+            raise ValueError(f"copy_in: {array.nbytes} host bytes into a {buffer.nbytes}-byte buffer")
+        abi.check(self._lib.b200_memcpy_h2d(buffer.ptr, array.ctypes.data, array.nbytes,
+                                            self.stream))
+        if sync:
+            abi.check(self._lib.b200_stream_sync(self.stream))
+
+    def copy_out(self, buffer, out: PinnedArray, *, sync=True):
+        """Device buffer -> page-locked host array, raw storage bytes (no bf16 widening)."""
+        if out.nbytes < buffer.nbytes:
+            raise ValueError("copy_out: destination is smaller than the buffer")
+        abi.check(self._lib.b200_memcpy_d2h(out.ptr, buffer.ptr, buffer.nbytes, self.stream))
+        if sync:
+            abi.check(self._lib.b200_stream_sync(self.stream))
+        return out.array
+
     def upload_aliased(self, group: dict, pointer_types: dict):
         """Upload host arrays that share one storage as ONE device allocation and
         return per-name views at the same byte offsets (device.py:397-406)."""

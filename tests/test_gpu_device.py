@@ -1,0 +1,101 @@
+"""``B200Device`` against the Device protocol, in the manner of the reference's own
+device tests (ops/harness/tests/test_cuda_device.py:33-180): transfer round trips per
+dtype, bf16 view vs cast, aliased staging, device-side compare equal to the host
+compare, the event timer, properties."""
+import numpy as np
+import pytest
+
+from compiler_b200 import harness, ops
+from compiler_b200.device import B200Buffer, from_bf16_bits, to_bf16_bits
+from oracle import oracle
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("dtype", ["float32", "float16", "int32", "int64", "uint8", "bool", "float64"])
+def test_roundtrip(device, dtype):
+    rng = np.random.default_rng(1)
+    host = (rng.standard_normal((37, 19)) * 50).astype(dtype)
+    buf = device.upload(host)
+    assert str(buf.dtype) == dtype and buf.shape == (37, 19) and buf.data_ptr() != 0
+    back = device.download(buf)
+    assert back.dtype == host.dtype and np.array_equal(back, host)
+
+
+def test_bf16_cast_and_view(device):
+    rng = np.random.default_rng(2)
+    host = rng.standard_normal(1000).astype(np.float32)
+    cast = device.upload(host, "bfloat16")
+    assert str(cast.dtype) == "bfloat16" and cast.nbytes == 2000
+    back = device.download(cast)
+    assert back.dtype == np.float32 and np.array_equal(back, oracle.bf16_round(host))
+    bits = to_bf16_bits(host)
+    view = device.upload(bits, "bfloat16")
+    assert np.array_equal(device.download(view), bits)  # uint16 hosts round-trip as bits
+    assert np.array_equal(from_bf16_bits(bits), oracle.bf16_round(host))
+    with pytest.raises(TypeError):
+        device.upload(host.astype(np.float64), "bfloat16")
+
+
+def test_dtype_markers_are_value_keyed(device):
+    a, b = device.alloc((4,), "float16"), device.alloc((8,), np.float16)
+    assert a.dtype is b.dtype and str(a.dtype) == "float16" and a.dtype.name == "float16"
+
+
+def test_alloc_release_and_empty(device):
+    bufs = {"x": device.alloc((0, 5), "float32"), "y": device.alloc((3,), "int32")}
+    assert device.download(bufs["x"]).shape == (0, 5)
+    device.release(bufs)
+    assert bufs["y"].ptr == 0
+
+
+def test_aliased_upload_is_one_allocation(device):
+    base = np.arange(64, dtype=np.float32)
+    group = {"whole": base, "tail": base[32:]}
+    out = device.upload_aliased(group, {})
+    assert out["tail"].data_ptr() - out["whole"].data_ptr() == 32 * 4
+    case = {"kernel": None, "args": {"whole": base, "tail": base[32:], "n": 3}}
+    groups = harness._alias_groups({"whole": base, "tail": base[32:], "other": np.zeros(3)})
+    assert sorted(map(sorted, groups)) == [["other"], ["tail", "whole"]]
+    assert np.array_equal(device.download(out["tail"]), base[32:])
+    del case
+
+
+def test_device_compare_matches_host_compare(device):
+    rng = np.random.default_rng(3)
+    ref = rng.standard_normal(100000).astype(np.float32)
+    got = ref.copy()
+    got[17] += 0.5
+    got[999] = np.nan
+    ref[5] = np.nan
+    got[5] = np.nan
+    policy = {"comparator": "allclose", "rtol": 1e-3, "atol": 1e-3, "equal_nan": True}
+    ok, err = device.compare(device.upload(got), ref, policy)
+    assert not ok
+    clean = ref.copy()
+    clean[3] += 1e-5
+    ok, err = device.compare(device.upload(clean), ref, policy)
+    host_err = oracle.compare(clean, ref, 1e-3, 1e-3)
+    assert ok and err == pytest.approx(host_err, rel=1e-12)
+    assert device.compare(device.upload(ref.astype(np.float16)), ref, policy) is None
+
+
+def test_timer_and_properties(device):
+    x = device.upload(np.ones((1024, 1024), np.float32))
+    y = device.alloc((1024, 1024), "float32")
+    with device.timer() as t:
+        ops.softmax(x, y)
+    assert t.seconds is not None and 0 < t.seconds < 1.0
+    props = device.properties()
+    assert props["sm_count"] > 0 and props["llc_bytes"] > 0 and "name" in props
+    device.synchronize()
+
+
+def test_pinned_transfers(device):
+    pinned = device.pinned_empty((256, 256), np.float32)
+    pinned.array[...] = np.arange(65536, dtype=np.float32).reshape(256, 256)
+    buf = device.upload(pinned.array, pinned=pinned)
+    out = device.pinned_empty((256, 256), np.float32)
+    back = device.download(buf, out=out)
+    assert np.array_equal(back, pinned.array)
+    assert isinstance(buf, B200Buffer)

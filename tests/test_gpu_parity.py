@@ -1,0 +1,312 @@
+"""GPU parity: the CUDA kernels, called through the C ABI, against the CPU oracle.
+
+Three layers, as the reference tests its devices (ops/harness/tests/
+test_cuda_device.py:185-211 runs its whole perf lane through the device):
+  1. every golden fixture (the reference's own cases and expected outputs) through
+     ``B200Device`` + ``stage_case`` + ``launch`` with the case's own tolerance;
+  2. seeded ragged sweeps per operator (1, tile-1, tile, tile+1, primes) with
+     poisoned outputs so an unwritten element fails;
+  3. the full-size configurations through size-independent properties plus
+     oracle checks on sampled rows / heads.
+Tolerances: fp32 RMSNorm rtol 1e-5; fp16 1e-2; bf16 2e-2 (ops/harness/opslib/case.py:153-157).
+"""
+import os
+import zlib
+
+import numpy as np
+import pytest
+
+import golden_cases
+from compiler_b200 import harness, kernels, ops
+from compiler_b200.runtime import abi
+from oracle import oracle
+
+pytestmark = pytest.mark.gpu
+
+TOL = {"float32": (1e-5, 1e-6), "float16": (1e-2, 1e-2), "bfloat16": (2e-2, 2e-2)}
+POISON = -7.0
+
+
+def _seed(*parts):
+    return zlib.crc32(repr(parts).encode())
+
+
+def _host(rng_values, dtype):
+    return oracle.to_storage(np.asarray(rng_values, dtype=np.float32), dtype)
+
+
+def _up(device, array, dtype):
+    return device.upload(array, dtype)
+
+
+def _poisoned(device, shape, dtype):
+    host = oracle.to_storage(np.full(shape, POISON, dtype=np.float32), dtype)
+    return device.upload(host, dtype)
+
+
+# ------------------------------------------------------------------ 1. golden
+@pytest.mark.parametrize("tag", golden_cases.tags())
+def test_golden_case_through_device(device, tag):
+    case, meta = golden_cases.load(tag)
+    actual = harness.run_case(case, device)
+    device.check_status()
+    for name in case["outputs"]:
+        policy = case["comparison"][name]
+        oracle.compare(actual[name], case["expected"][name], policy["rtol"], policy["atol"],
+                       equal_nan=policy.get("equal_nan", True), name=f"{tag}:{name}")
+
+
+# ------------------------------------------------------------------ 2. sweeps
+RMS_SHAPES = [(1, 1), (3, 5), (7, 67), (5, 128), (33, 1000), (64, 4096), (9, 4100), (130, 2048),
+              (3, 16384), (2, 40000)]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "float16", "bfloat16"])
+@pytest.mark.parametrize("shape", RMS_SHAPES)
+def test_rmsnorm_sweep(device, shape, dtype):
+    rng = np.random.default_rng(_seed(shape, dtype))
+    x = _host(rng.standard_normal(shape), dtype)
+    w = _host(rng.uniform(0.5, 1.5, shape[1]), dtype)
+    dx, dw = _up(device, x, dtype), _up(device, w, dtype)
+    dy, dr = _poisoned(device, shape, dtype), _poisoned(device, (shape[0],), dtype)
+    ops.rmsnorm(dx, dw, dy, dr, eps=1e-6)
+    y_ref, r_ref = oracle.rmsnorm_ref(x, w, 1e-6)
+    rtol, atol = TOL[dtype]
+    oracle.compare(device.download(dy).astype(np.float64), y_ref, rtol, atol, name="Y")
+    oracle.compare(device.download(dr).astype(np.float64), r_ref, rtol, atol, name="r")
+
+
+def test_rmsnorm_strided_rows_and_guard(device):
+    """Row pitch wider than the row: the gap must stay untouched (masked tails)."""
+    rng = np.random.default_rng(11)
+    rows, cols, pitch = 37, 1000, 1024
+    x = rng.standard_normal((rows, pitch)).astype(np.float32)
+    w = rng.uniform(0.5, 1.5, cols).astype(np.float32)
+    dx, dw = device.upload(x), device.upload(w)
+    dy = device.upload(np.full((rows, pitch), POISON, np.float32))
+    ops.rmsnorm(registry_view(dx, (rows, cols), (pitch, 1)), dw,
+                registry_view(dy, (rows, cols), (pitch, 1)), None, eps=1e-6)
+    y = device.download(dy)
+    y_ref, _ = oracle.rmsnorm_ref(x[:, :cols], w, 1e-6)
+    oracle.compare(y[:, :cols].astype(np.float64), y_ref, 1e-5, 1e-6)
+    assert (y[:, cols:] == POISON).all()
+
+
+def registry_view(buffer, shape, strides):
+    from compiler_b200.registry import _View
+    return _View(buffer, shape, strides)
+
+
+SOFTMAX_SHAPES = [(1, 1), (4, 16), (4, 97), (3, 1000), (64, 1024), (10, 4000), (6, 4104),
+                  (5, 8192), (2, 33000)]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "float16", "bfloat16"])
+@pytest.mark.parametrize("masked", [False, True])
+@pytest.mark.parametrize("shape", SOFTMAX_SHAPES)
+def test_softmax_sweep(device, shape, dtype, masked):
+    rng = np.random.default_rng(_seed(shape, dtype, masked))
+    x = _host(rng.standard_normal(shape) * 2, dtype)
+    dx, dy = _up(device, x, dtype), _poisoned(device, shape, dtype)
+    offset = 3 if masked else 0
+    ops.softmax(dx, dy, causal_mod=masked, row_offset=offset)
+    y = device.download(dy)
+    ref = oracle.masked_softmax_ref(x, offset) if masked else oracle.softmax_ref(x)
+    rtol, atol = (2e-3, 1e-6) if dtype == "float32" else TOL[dtype]
+    oracle.compare(y.astype(np.float64), ref, rtol, atol)
+    if masked:  # masked positions are written as exact zeros
+        assert (y[ref == 0] == 0).all()
+
+
+GEMM_SHAPES = [(128, 256, 64), (256, 512, 256), (1, 8, 8), (129, 264, 72), (257, 520, 200),
+               (100, 40, 24), (384, 1024, 1000), (130, 96, 8)]
+
+
+@pytest.mark.parametrize("dtype", ["bfloat16", "float16"])
+@pytest.mark.parametrize("act", ["none", "gelu_tanh", "gelu_erf", "leaky_relu"])
+@pytest.mark.parametrize("shape", GEMM_SHAPES)
+def test_gemm_sweep(device, shape, dtype, act):
+    m, n, k = shape
+    rng = np.random.default_rng(_seed(shape, dtype, act))
+    a = _host(rng.standard_normal((m, k)) / np.sqrt(k), dtype)
+    b = _host(rng.standard_normal((k, n)), dtype)
+    bias = _host(rng.normal(0, 0.1, n), dtype)
+    da, db, dbias = _up(device, a, dtype), _up(device, b, dtype), _up(device, bias, dtype)
+    dc = _poisoned(device, (m, n), dtype)
+    code = {"none": abi.ACT_NONE, "gelu_tanh": abi.ACT_GELU_TANH, "gelu_erf": abi.ACT_GELU_ERF,
+            "leaky_relu": abi.ACT_LEAKY_RELU}[act]
+    use_bias = act != "none"
+    ops.gemm(da, db, dc, bias=dbias if use_bias else None, act=code)
+    device.check_status()
+    ref = oracle.linear_act_ref(a, b, bias if use_bias else None, act)
+    oracle.compare(device.download(dc).astype(np.float64), ref, *TOL[dtype], name=f"C{shape}")
+
+
+@pytest.mark.parametrize("shape", [(128, 128, 64), (200, 264, 136), (256, 1024, 512)])
+def test_gemm_f32_bias_and_f32_output(device, shape):
+    m, n, k = shape
+    rng = np.random.default_rng(5)
+    a = _host(rng.standard_normal((m, k)) / np.sqrt(k), "bfloat16")
+    b = _host(rng.standard_normal((k, n)), "bfloat16")
+    bias = rng.normal(0, 0.1, n).astype(np.float32)
+    da, db = _up(device, a, "bfloat16"), _up(device, b, "bfloat16")
+    dbias = device.upload(bias)
+    dc = device.upload(np.full((m, n), POISON, np.float32))
+    ops.gemm(da, db, dc, bias=dbias, act=abi.ACT_GELU_TANH)
+    device.check_status()
+    ref = oracle.linear_act_ref(a, b, bias, "gelu_tanh")
+    oracle.compare(device.download(dc).astype(np.float64), ref, 2e-3, 2e-3)
+
+
+@pytest.mark.parametrize("shape", [(128, 128, 64), (130, 200, 72), (256, 384, 512)])
+def test_gemm_swiglu_dual(device, shape):
+    m, n, k = shape
+    rng = np.random.default_rng(6)
+    x = _host(rng.standard_normal((m, k)), "bfloat16")
+    wg = _host(rng.normal(0, 0.05, (k, n)), "bfloat16")
+    wu = _host(rng.normal(0, 0.05, (k, n)), "bfloat16")
+    dx, dg, du = (_up(device, t, "bfloat16") for t in (x, wg, wu))
+    dh = _poisoned(device, (m, n), "bfloat16")
+    ops.gemm(dx, dg, dh, b2=du, act=abi.ACT_SWIGLU)
+    device.check_status()
+    ref = oracle.swiglu_ref(oracle.matmul_ref(x, wg), oracle.matmul_ref(x, wu))
+    oracle.compare(device.download(dh).astype(np.float64), ref, 2e-2, 2e-2)
+
+
+def test_gemm_fp32_operands_take_the_ieee_path(device):
+    rng = np.random.default_rng(7)
+    a = rng.standard_normal((33, 47)).astype(np.float32)
+    b = rng.standard_normal((47, 29)).astype(np.float32)
+    da, db = device.upload(a), device.upload(b)
+    dc = device.upload(np.full((33, 29), POISON, np.float32))
+    ops.gemm(da, db, dc)
+    oracle.compare(device.download(dc).astype(np.float64), oracle.matmul_ref(a, b), 1e-5, 1e-5)
+
+
+ATTN_SHAPES = [(1, 2, 256, 128), (2, 1, 384, 64), (1, 2, 200, 128), (1, 1, 128, 128),
+               (1, 1, 640, 128), (1, 3, 77, 64)]
+
+
+@pytest.mark.parametrize("p_location", ["tmem", "smem"])
+@pytest.mark.parametrize("dtype", ["bfloat16", "float16"])
+@pytest.mark.parametrize("causal", [True, False])
+@pytest.mark.parametrize("shape", ATTN_SHAPES)
+def test_attention_sweep(device, shape, dtype, causal, p_location):
+    z, h, n, d = shape
+    rng = np.random.default_rng(_seed(shape, dtype, causal))
+    q, k, v = (_host(rng.standard_normal(shape), dtype) for _ in range(3))
+    dq, dk, dv = (_up(device, t, dtype) for t in (q, k, v))
+    do = _poisoned(device, shape, dtype)
+    dl = device.upload(np.full((z, h, n), POISON, np.float32))
+    scale = 1.0 / np.sqrt(d)
+    os.environ["B200OPS_ATTN_P"] = p_location
+    try:
+        ops.attention(dq, dk, dv, do, lse=dl, scale=scale, causal=causal)
+        device.check_status()
+    finally:
+        os.environ.pop("B200OPS_ATTN_P", None)
+    out_ref, lse_ref = oracle.attention_ref(q, k, v, scale, causal)
+    oracle.compare(device.download(do).astype(np.float64), out_ref, *TOL[dtype], name="out")
+    oracle.compare(device.download(dl).astype(np.float64), lse_ref, 1e-3, 1e-3, name="lse")
+
+
+@pytest.mark.parametrize("shape", [(1, 1, 8, 16), (2, 2, 16, 32), (1, 2, 100, 80)])
+def test_attention_cuda_core_path(device, shape):
+    z, h, n, d = shape
+    rng = np.random.default_rng(8)
+    q, k, v = (rng.standard_normal(shape).astype(np.float32) for _ in range(3))
+    dq, dk, dv = (device.upload(t) for t in (q, k, v))
+    do = device.upload(np.full(shape, POISON, np.float32))
+    dl = device.upload(np.full((z, h, n), POISON, np.float32))
+    ops.attention(dq, dk, dv, do, lse=dl, scale=0.25, causal=True)
+    out_ref, lse_ref = oracle.attention_ref(q, k, v, 0.25, True)
+    oracle.compare(device.download(do).astype(np.float64), out_ref, 1e-4, 1e-5)
+    oracle.compare(device.download(dl).astype(np.float64), lse_ref, 1e-4, 1e-5)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("shape", [(4, 64), (8, 128), (5, 99), (64, 1024), (33, 14336)])
+def test_swiglu_sweep(device, shape, dtype):
+    rng = np.random.default_rng(9)
+    x, y = (_host(rng.standard_normal(shape), dtype) for _ in range(2))
+    dx, dy = _up(device, x, dtype), _up(device, y, dtype)
+    dout = _poisoned(device, shape, dtype)
+    ops.swiglu(dx, dy, dout)
+    rtol, atol = (1e-4, 1e-5) if dtype == "float32" else TOL[dtype]
+    oracle.compare(device.download(dout).astype(np.float64), oracle.swiglu_ref(x, y), rtol, atol)
+
+
+# ------------------------------------------------------------------ native handles
+def test_native_handles_through_the_launch_surface(device):
+    """The BASELINE configurations use handles the registry resolves like any kernel."""
+    rng = np.random.default_rng(10)
+    rows, cols = 16, 4000
+    x = _host(rng.standard_normal((rows, cols)) * 2, "float16")
+    case = {"kernel": kernels.masked_softmax_kernel,
+            "args": {"x_ptr": x, "y_ptr": np.zeros_like(x), "n_cols": cols, "row_offset": 3990},
+            "meta": {}, "grid": (rows,), "outputs": ("y_ptr",)}
+    y = harness.run_case(case, device)["y_ptr"]
+    oracle.compare(y.astype(np.float64), oracle.masked_softmax_ref(x, 3990), 1e-2, 1e-2)
+
+    m, n, k = 96, 136, 72
+    a = _host(rng.standard_normal((m, k)) / np.sqrt(k), "bfloat16")
+    b = _host(rng.standard_normal((k, n)), "bfloat16")
+    bias = _host(rng.normal(0, 0.1, n), "bfloat16")
+    case = {"kernel": kernels.gemm_bias_act_kernel,
+            "args": {"a_ptr": a, "b_ptr": b, "bias_ptr": bias, "c_ptr": np.zeros((m, n), np.float32),
+                     "M": m, "N": n, "K": k},
+            "meta": {"ACT": abi.ACT_GELU_TANH}, "grid": (1,), "outputs": ("c_ptr",),
+            "pointer_dtypes": {name: "bfloat16" for name in ("a_ptr", "b_ptr", "bias_ptr", "c_ptr")}}
+    c = harness.run_case(case, device)["c_ptr"]
+    oracle.compare(c.astype(np.float64), oracle.linear_act_ref(a, b, bias, "gelu_tanh"), 2e-2, 2e-2)
+
+
+def test_compiled_kernel_callable(device):
+    """``make_compiler().compile_case(case)[grid](*args, **meta)`` launches the operator."""
+    from compiler_b200.factory import make_compiler
+    compiler = make_compiler()
+    rng = np.random.default_rng(12)
+    x = rng.standard_normal((8, 256)).astype(np.float32)
+    case, _ = golden_cases.load("softmax__4x16__float32")
+    artifact = compiler.compile_case(case).bind(device)
+    again = compiler.compile_case(case)
+    assert compiler.compile_count == 1 and compiler.cache_hits == 1 and again.cache_hit
+    assert again.identity == artifact.identity and len(artifact.sha256) == 64
+    dx, dy = device.upload(x), device.upload(np.zeros_like(x))
+    artifact[(8,)](dx, dy, 256, BLOCK_N=1024)
+    oracle.compare(device.download(dy).astype(np.float64), oracle.softmax_ref(x), 2e-3, 1e-6)
+
+
+def test_unknown_kernel_is_a_located_refusal(device):
+    from compiler_b200.registry import UnsupportedLaunch
+    handle = golden_cases.make_handle("mystery_kernel", ["a_ptr", "n"])
+    with pytest.raises(UnsupportedLaunch) as err:
+        device.launch(handle, (1,), [device.alloc((4,), "float32"), 4], {})
+    assert err.value.kernel_name == "mystery_kernel" and "no native" in err.value.message
+
+
+# ------------------------------------------------------------------ repeat consistency
+def test_repeat_launches_are_bitwise_identical(device):
+    """The --repeats check of a100c/runtime/main.c:117-152 for the pipelined kernels."""
+    import ctypes
+    rng = np.random.default_rng(13)
+    m, n, k = 512, 768, 1024
+    a = _host(rng.standard_normal((m, k)) / np.sqrt(k), "bfloat16")
+    b = _host(rng.standard_normal((k, n)), "bfloat16")
+    da, db = _up(device, a, "bfloat16"), _up(device, b, "bfloat16")
+    outs = [_poisoned(device, (m, n), "bfloat16") for _ in range(3)]
+    for out in outs:
+        ops.gemm(da, db, out, act=abi.ACT_GELU_TANH)
+    shape = (1, 4, 512, 128)
+    q, kk, v = (_host(rng.standard_normal(shape), "bfloat16") for _ in range(3))
+    dq, dk, dv = (_up(device, t, "bfloat16") for t in (q, kk, v))
+    attn = [_poisoned(device, shape, "bfloat16") for _ in range(3)]
+    for out in attn:
+        ops.attention(dq, dk, dv, out, causal=True)
+    device.check_status()
+    for group in (outs, attn):
+        for other in group[1:]:
+            equal = ctypes.c_int()
+            status = abi.lib().b200_bitwise_equal(group[0].ptr, other.ptr, group[0].nbytes,
+                                                  ctypes.byref(equal), 0)
+            assert status == abi.OK and equal.value == 1
