@@ -1,0 +1,98 @@
+"""Launch ONE operator a few times at a given shape -- the small, self-ending command to put
+under a profiler (``ncu -k regex:<kernel> -c 3 python -m compiler_b200.profile_case ...``) or to
+time a single shape by hand.
+
+    python -m compiler_b200.profile_case softmax   --shape 16384 4000 --dtype float16
+    python -m compiler_b200.profile_case rmsnorm   --shape 8192 4096  --dtype float32
+    python -m compiler_b200.profile_case gemm      --shape 8192 8192 8192
+    python -m compiler_b200.profile_case attention --shape 2 8 4096 128
+    python -m compiler_b200.profile_case swiglu_gemm --shape 4096 1792 4096
+
+Inputs are seeded random values generated on the host and uploaded through ``B200Device``
+(no torch); every launch is timed with CUDA events and the times are printed as JSON.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+
+import numpy as np
+
+from compiler_b200 import ops
+from compiler_b200.device import B200Device, to_bf16_bits
+from compiler_b200.runtime import abi
+
+
+def _upload(device, array, dtype):
+    if dtype == "bfloat16":
+        return device.upload(to_bf16_bits(array.astype(np.float32)), "bfloat16")
+    return device.upload(array.astype(dtype), dtype)
+
+
+def main(argv=None):
+    parser = argparse.ArgumentParser(description=__doc__.split("\n")[0])
+    parser.add_argument("op", choices=["softmax", "rmsnorm", "gemm", "attention", "swiglu_gemm"])
+    parser.add_argument("--shape", type=int, nargs="+", required=True)
+    parser.add_argument("--dtype", default=None)
+    parser.add_argument("--launches", type=int, default=3)
+    parser.add_argument("--device", type=int, default=0)
+    parser.add_argument("--no-mask", action="store_true", help="softmax/attention without mask")
+    args = parser.parse_args(argv)
+    device = B200Device(args.device)
+    rng = np.random.default_rng(0)
+    shape = tuple(args.shape)
+
+    if args.op == "softmax":
+        dtype = args.dtype or "float16"
+        x = _upload(device, rng.standard_normal(shape, dtype=np.float32) * 2, dtype)
+        y = device.alloc(shape, dtype)
+        launch = lambda: ops.softmax(x, y, causal_mod=not args.no_mask)  # noqa: E731
+        work = {"bytes": 2 * int(np.prod(shape)) * abi.DTYPE_SIZES[dtype]}
+    elif args.op == "rmsnorm":
+        dtype = args.dtype or "float32"
+        x = _upload(device, rng.standard_normal(shape, dtype=np.float32), dtype)
+        w = _upload(device, rng.uniform(0.5, 1.5, shape[1]).astype(np.float32), dtype)
+        y, r = device.alloc(shape, dtype), device.alloc((shape[0],), dtype)
+        launch = lambda: ops.rmsnorm(x, w, y, r, eps=1e-6)  # noqa: E731
+        work = {"bytes": 2 * int(np.prod(shape)) * abi.DTYPE_SIZES[dtype]}
+    elif args.op in ("gemm", "swiglu_gemm"):
+        dtype = args.dtype or "bfloat16"
+        m, n, k = shape
+        a = _upload(device, rng.standard_normal((m, k), dtype=np.float32) / np.sqrt(k), dtype)
+        b = _upload(device, rng.standard_normal((k, n), dtype=np.float32) / np.sqrt(k), dtype)
+        c = device.alloc((m, n), dtype)
+        if args.op == "gemm":
+            bias = _upload(device, rng.normal(0, 0.1, n).astype(np.float32), dtype)
+            launch = lambda: ops.gemm(a, b, c, bias=bias, act=abi.ACT_GELU_TANH)  # noqa: E731
+            work = {"flop": 2 * m * n * k}
+        else:
+            b2 = _upload(device, rng.standard_normal((k, n), dtype=np.float32) / np.sqrt(k), dtype)
+            launch = lambda: ops.gemm(a, b, c, b2=b2, act=abi.ACT_SWIGLU)  # noqa: E731
+            work = {"flop": 4 * m * n * k}
+    else:
+        dtype = args.dtype or "bfloat16"
+        z, h, n, d = shape
+        q, k, v = (_upload(device, rng.standard_normal(shape, dtype=np.float32), dtype)
+                   for _ in range(3))
+        o, lse = device.alloc(shape, dtype), device.alloc((z, h, n), "float32")
+        causal = not args.no_mask
+        launch = lambda: ops.attention(q, k, v, o, lse=lse, causal=causal)  # noqa: E731
+        work = {"flop": 4 * z * h * d * (n * (n + 1) // 2 if causal else n * n)}
+
+    times = []
+    for _ in range(args.launches):
+        with device.timer() as t:
+            launch()
+        times.append(t.seconds)
+    device.check_status()
+    record = {"op": args.op, "shape": shape, "dtype": dtype, "launch_seconds": times, **work}
+    best = min(times)
+    if "bytes" in work:
+        record["best_GBps"] = work["bytes"] / best / 1e9
+    else:
+        record["best_TFLOPs"] = work["flop"] / best / 1e12
+    print(json.dumps(record))
+
+
+if __name__ == "__main__":
+    main()
