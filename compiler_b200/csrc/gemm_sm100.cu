@@ -114,14 +114,12 @@ __device__ __forceinline__ float gelu_erf(float z) {
   return 0.5f * z * (1.0f + erff(z * 0.7071067811865476f));
 }
 
-template <typename OutT> __device__ __forceinline__ float activate(float z, int act) {
-  switch (act) {
-    case B200_ACT_GELU_ERF: return gelu_erf(z);
-    case B200_ACT_GELU_TANH:
-      return sizeof(OutT) == 2 ? gelu_tanh_fast(z) : gelu_tanh_exact(z);
-    case B200_ACT_LEAKY_RELU: return z >= 0.f ? z : 0.01f * z;
-    default: return z;
-  }
+template <typename OutT, int ACT> __device__ __forceinline__ float activate(float z) {
+  if constexpr (ACT == B200_ACT_GELU_ERF) return gelu_erf(z);
+  if constexpr (ACT == B200_ACT_GELU_TANH)
+    return sizeof(OutT) == 2 ? gelu_tanh_fast(z) : gelu_tanh_exact(z);
+  if constexpr (ACT == B200_ACT_LEAKY_RELU) return z >= 0.f ? z : 0.01f * z;
+  return z;
 }
 __device__ __forceinline__ float silu(float z) { return z / (1.0f + __expf(-z)); }
 
@@ -129,6 +127,117 @@ __device__ __forceinline__ float load_bias(const void *bias, int kind, int col) 
   if (kind == B200_DTYPE_FLOAT32) return ((const float *)bias)[col];
   if (kind == B200_DTYPE_BFLOAT16) return __bfloat162float(((const __nv_bfloat16 *)bias)[col]);
   return __half2float(((const __half *)bias)[col]);
+}
+
+// bias values of 32 consecutive columns starting at col0 (same for every thread
+// of the warp: the loads are broadcasts served by L1)
+__device__ __forceinline__ void load_bias_chunk(const void *bias, int kind, int col0, int n,
+                                                float (&b)[32]) {
+  if (kind == 0) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) b[j] = 0.f;
+    return;
+  }
+  if (col0 + 32 <= n && ((uintptr_t)bias & 15) == 0) {
+    if (kind == B200_DTYPE_FLOAT32) {
+      const float4 *src = reinterpret_cast<const float4 *>((const float *)bias + col0);
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {
+        const float4 t = __ldg(src + q);
+        b[4 * q] = t.x; b[4 * q + 1] = t.y; b[4 * q + 2] = t.z; b[4 * q + 3] = t.w;
+      }
+    } else {
+      const uint4 *src = reinterpret_cast<const uint4 *>((const uint16_t *)bias + col0);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const uint4 t = __ldg(src + q);
+        const uint32_t w[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          if (kind == B200_DTYPE_BFLOAT16) {
+            b[8 * q + 2 * i] = __uint_as_float(w[i] << 16);
+            b[8 * q + 2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+          } else {
+            const __half2 h = *reinterpret_cast<const __half2 *>(&w[i]);
+            b[8 * q + 2 * i] = __low2float(h);
+            b[8 * q + 2 * i + 1] = __high2float(h);
+          }
+        }
+      }
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) b[j] = col0 + j < n ? load_bias(bias, kind, col0 + j) : 0.f;
+  }
+}
+
+// convert and store 32 consecutive columns of one row
+template <typename OutT>
+__device__ __forceinline__ void store_chunk(OutT *crow, int col0, int n, bool vector_ok,
+                                            const float (&v)[32]) {
+  if (vector_ok && col0 + 32 <= n) {
+    constexpr int PER = 16 / (int)sizeof(OutT);
+#pragma unroll
+    for (int q = 0; q < 32 / PER; ++q) {
+      vec16<OutT> o;
+#pragma unroll
+      for (int j = 0; j < PER; ++j) o.e[j] = io<OutT>::store(v[q * PER + j]);
+      *reinterpret_cast<uint4 *>(crow + col0 + q * PER) = o.raw;
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (col0 + j < n) crow[col0 + j] = io<OutT>::store(v[j]);
+  }
+}
+
+// bias + activation + store of one 32-column chunk held in registers
+template <typename OutT, int ACT>
+__device__ __forceinline__ void finish_chunk(const uint32_t (&r)[32], const Params &p, OutT *crow,
+                                             int col0, bool row_ok) {
+  if (col0 >= p.N) return;  // warp-uniform
+  float b[32], v[32];
+  load_bias_chunk(p.bias, p.bias_kind, col0, p.N, b);
+#pragma unroll
+  for (int j = 0; j < 32; ++j) v[j] = activate<OutT, ACT>(__uint_as_float(r[j]) + b[j]);
+  if (row_ok) store_chunk<OutT>(crow, col0, p.N, p.vector_store != 0, v);
+}
+
+// Epilogue of one 128 x 256 accumulator for one warp (32 rows): the TMEM load of
+// chunk c+1 is in flight while chunk c is converted and stored.
+template <typename OutT, int ACT>
+__device__ __forceinline__ void epilogue_tile(uint32_t t_row, const Params &p, OutT *crow,
+                                              int col_base, bool row_ok) {
+  uint32_t ra[32], rb[32];
+  tmem_ld_32x32b_x32(t_row, ra);
+#pragma unroll 1
+  for (int chunk = 0; chunk < BN / 32; chunk += 2) {
+    tmem_ld_wait();
+    tmem_ld_32x32b_x32(t_row + (uint32_t)((chunk + 1) * 32), rb);
+    finish_chunk<OutT, ACT>(ra, p, crow, col_base + chunk * 32, row_ok);
+    tmem_ld_wait();
+    if (chunk + 2 < BN / 32) tmem_ld_32x32b_x32(t_row + (uint32_t)((chunk + 2) * 32), ra);
+    finish_chunk<OutT, ACT>(rb, p, crow, col_base + (chunk + 1) * 32, row_ok);
+  }
+}
+
+// DUAL: columns [0,128) hold x Wg, [128,256) hold x Wu; out = silu(g) * u
+template <typename OutT>
+__device__ __forceinline__ void epilogue_tile_dual(uint32_t t_row, const Params &p, OutT *crow,
+                                                   int col_base, bool row_ok) {
+#pragma unroll 1
+  for (int chunk = 0; chunk < BN / 64; ++chunk) {
+    const int col0 = col_base + chunk * 32;
+    uint32_t r[32], r2[32];
+    tmem_ld_32x32b_x32(t_row + (uint32_t)(chunk * 32), r);
+    tmem_ld_32x32b_x32(t_row + (uint32_t)(BN / 2 + chunk * 32), r2);
+    tmem_ld_wait();
+    if (col0 >= p.N) continue;  // warp-uniform
+    float v[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] = silu(__uint_as_float(r[j])) * __uint_as_float(r2[j]);
+    if (row_ok) store_chunk<OutT>(crow, col0, p.N, p.vector_store != 0, v);
+  }
 }
 
 // tile index -> block coordinates, grouped so that concurrently running CTAs
@@ -294,43 +403,24 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
       const bool row_ok = row < p.M;
       const uint32_t t_row = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(acc * BN);
       OutT *crow = c + (int64_t)row * p.ldc;
-#pragma unroll 1
-      for (int chunk = 0; chunk < TILE_N / 32; ++chunk) {
-        const int col0 = nb * TILE_N + chunk * 32;
-        if (col0 >= p.N) break;  // warp-uniform
-        uint32_t r[32];
-        float v[32];
-        tmem_ld_32x32b_x32(t_row + (uint32_t)(chunk * 32), r);
-        if (DUAL) {
-          uint32_t r2[32];
-          tmem_ld_32x32b_x32(t_row + (uint32_t)(TILE_N + chunk * 32), r2);
-          tmem_ld_wait();
-#pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = silu(__uint_as_float(r[j])) * __uint_as_float(r2[j]);
-        } else {
-          tmem_ld_wait();
-#pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            float z = __uint_as_float(r[j]);
-            if (p.bias_kind != 0 && col0 + j < p.N) z += load_bias(p.bias, p.bias_kind, col0 + j);
-            v[j] = activate<OutT>(z, p.act);
-          }
-        }
-        if (row_ok) {
-          if (p.vector_store && col0 + 32 <= p.N) {
-            constexpr int PER = 16 / (int)sizeof(OutT);
-#pragma unroll
-            for (int q = 0; q < 32 / PER; ++q) {
-              vec16<OutT> o;
-#pragma unroll
-              for (int j = 0; j < PER; ++j) o.e[j] = io<OutT>::store(v[q * PER + j]);
-              *reinterpret_cast<uint4 *>(crow + col0 + q * PER) = o.raw;
-            }
-          } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (col0 + j < p.N) crow[col0 + j] = io<OutT>::store(v[j]);
-          }
+      const int col_base = nb * TILE_N;
+      if constexpr (DUAL) {
+        epilogue_tile_dual<OutT>(t_row, p, crow, col_base, row_ok);
+      } else {
+        // one straight-line epilogue per activation: the choice is made per tile,
+        // not per element
+        switch (p.act) {
+          case B200_ACT_GELU_TANH:
+            epilogue_tile<OutT, B200_ACT_GELU_TANH>(t_row, p, crow, col_base, row_ok);
+            break;
+          case B200_ACT_GELU_ERF:
+            epilogue_tile<OutT, B200_ACT_GELU_ERF>(t_row, p, crow, col_base, row_ok);
+            break;
+          case B200_ACT_LEAKY_RELU:
+            epilogue_tile<OutT, B200_ACT_LEAKY_RELU>(t_row, p, crow, col_base, row_ok);
+            break;
+          default:
+            epilogue_tile<OutT, B200_ACT_NONE>(t_row, p, crow, col_base, row_ok);
         }
       }
       // this warp has drained its quarter of the accumulator

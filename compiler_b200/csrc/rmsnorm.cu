@@ -20,7 +20,7 @@ rmsnorm_rows_kernel(const T *__restrict__ x, int64_t x_stride,
   constexpr int kThreads = G > kRowThreads ? G : kRowThreads;
   constexpr int kRowsPerCta = kThreads / G;
   constexpr int N = vec16<T>::N;
-  __shared__ float scratch[kThreads / 32];
+  __shared__ float scratch[2 * (kThreads / 32)];
 
   const int lane = threadIdx.x % G;
   const int64_t row = (int64_t)blockIdx.x * kRowsPerCta + threadIdx.x / G;
@@ -42,7 +42,7 @@ rmsnorm_rows_kernel(const T *__restrict__ x, int64_t x_stride,
       }
     }
   }
-  acc = group_reduce<G, SumOp>(acc, scratch);
+  acc = group_reduce<G, SumOp>(acc, scratch, 0);
   const float inv = 1.0f / sqrtf(acc / (float)cols + eps);
   if (row_ok && lane == 0 && rinv != nullptr) rinv[row] = io<T>::store(inv);
 
@@ -69,7 +69,7 @@ rmsnorm_loop_kernel(const T *__restrict__ x, int64_t x_stride,
                     const T *__restrict__ w, int64_t w_stride,
                     T *__restrict__ y, int64_t y_stride, T *__restrict__ rinv,
                     int64_t rinv_stride, int cols, float eps) {
-  __shared__ float scratch[kRowThreads / 32];
+  __shared__ float scratch[2 * (kRowThreads / 32)];
   const int64_t row = blockIdx.x;
   const T *xrow = x + row * x_stride;
   float acc = 0.f;
@@ -77,7 +77,7 @@ rmsnorm_loop_kernel(const T *__restrict__ x, int64_t x_stride,
     const float f = io<T>::load(xrow[c]);
     acc = fmaf(f, f, acc);
   }
-  acc = group_reduce<kRowThreads, SumOp>(acc, scratch);
+  acc = group_reduce<kRowThreads, SumOp>(acc, scratch, 0);
   const float inv = 1.0f / sqrtf(acc / (float)cols + eps);
   if (threadIdx.x == 0 && rinv != nullptr) rinv[row * rinv_stride] = io<T>::store(inv);
   T *yrow = y + row * y_stride;

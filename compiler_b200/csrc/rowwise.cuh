@@ -22,23 +22,28 @@ struct MaxOp {
 };
 
 // Reduce `v` over the G consecutive threads that own one row.  `scratch` has
-// one float per warp of the CTA.  Every thread of the CTA must call this.
+// 2 x (one float per warp of the CTA); `buf` (0 or 1) selects the half, and
+// successive reductions in one kernel must alternate it: a thread can only
+// reach reduction k+2 after every thread of its group has passed the barrier
+// of reduction k+1, i.e. has finished reading the half reduction k wrote.
+// The barrier is a named one per row group, so the rows of a CTA do not wait
+// for each other.  Every thread of the group must call this.
 template <int G, typename Op>
-__device__ __forceinline__ float group_reduce(float v, float *scratch) {
+__device__ __forceinline__ float group_reduce(float v, float *scratch, int buf) {
   constexpr int kIntra = G < 32 ? G : 32;
 #pragma unroll
   for (int o = kIntra / 2; o > 0; o >>= 1)
     v = Op::apply(v, __shfl_xor_sync(0xffffffffu, v, o));
   if constexpr (G > 32) {
-    const int warp = threadIdx.x >> 5;
-    __syncthreads();  // scratch may still be read from the previous reduction
-    if ((threadIdx.x & 31) == 0) scratch[warp] = v;
-    __syncthreads();
     constexpr int kWarps = G / 32;
-    const int first = (threadIdx.x / G) * kWarps;
-    v = scratch[first];
+    const int group = threadIdx.x / G;
+    float *slot = scratch + buf * (blockDim.x >> 5);
+    if ((threadIdx.x & 31) == 0) slot[threadIdx.x >> 5] = v;
+    asm volatile("bar.sync %0, %1;" ::"r"(group + 1), "n"(G) : "memory");
+    const int first = group * kWarps;
+    v = slot[first];
 #pragma unroll
-    for (int i = 1; i < kWarps; ++i) v = Op::apply(v, scratch[first + i]);
+    for (int i = 1; i < kWarps; ++i) v = Op::apply(v, slot[first + i]);
   }
   return v;
 }

@@ -19,56 +19,142 @@ template <typename T> __device__ __forceinline__ float fast_exp(float v) {
 }
 template <> __device__ __forceinline__ float fast_exp<float>(float v) { return expf(v); }
 
+__device__ __forceinline__ float ex2_approx(float v) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(v));
+  return y;
+}
+
+// Per-type handling of one 16-byte vector of a row.
+template <typename T> struct RowVec;
+
+template <> struct RowVec<float> {
+  static constexpr int N = 4;
+  static __device__ __forceinline__ void mask_tail(uint4 &raw, int count) {
+    float *e = reinterpret_cast<float *>(&raw);
+#pragma unroll
+    for (int j = 0; j < N; ++j)
+      if (j >= count) e[j] = -INFINITY;
+  }
+  static __device__ __forceinline__ float vmax(const uint4 &raw) {
+    const float *e = reinterpret_cast<const float *>(&raw);
+    return fmaxf(fmaxf(e[0], e[1]), fmaxf(e[2], e[3]));
+  }
+  // f[j] = exp(x[j] - m); returns their sum
+  static __device__ __forceinline__ float exps(const uint4 &raw, float m, float, float (&f)[N]) {
+    const float *e = reinterpret_cast<const float *>(&raw);
+    float s = 0.f;
+#pragma unroll
+    for (int j = 0; j < N; ++j) {
+      f[j] = expf(e[j] - m);
+      s += f[j];
+    }
+    return s;
+  }
+  static __device__ __forceinline__ uint4 scaled(const float (&f)[N], float r) {
+    uint4 out;
+    float *o = reinterpret_cast<float *>(&out);
+#pragma unroll
+    for (int j = 0; j < N; ++j) o[j] = f[j] * r;
+    return out;
+  }
+};
+
+// 16-bit rows: the max is taken on packed pairs in the storage type (exact),
+// exp is one FFMA + one ex2 per element: 2^(x*log2e - m*log2e).
+template <typename T2, typename T1> struct RowVec16 {
+  static constexpr int N = 8;
+  static __device__ __forceinline__ void mask_tail(uint4 &raw, int count) {
+    T1 *e = reinterpret_cast<T1 *>(&raw);
+    const T1 ninf = io<T1>::store(-INFINITY);
+#pragma unroll
+    for (int j = 0; j < N; ++j)
+      if (j >= count) e[j] = ninf;
+  }
+  static __device__ __forceinline__ float vmax(const uint4 &raw) {
+    const T2 *p = reinterpret_cast<const T2 *>(&raw);
+    const T2 a = __hmax2(__hmax2(p[0], p[1]), __hmax2(p[2], p[3]));
+    return fmaxf(io<T1>::load(a.x), io<T1>::load(a.y));
+  }
+  static __device__ __forceinline__ float exps(const uint4 &raw, float, float neg_m_log2e,
+                                               float (&f)[N]) {
+    const T1 *e = reinterpret_cast<const T1 *>(&raw);
+    float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+    for (int j = 0; j < N; j += 2) {
+      f[j] = ex2_approx(fmaf(io<T1>::load(e[j]), 1.4426950408889634f, neg_m_log2e));
+      f[j + 1] = ex2_approx(fmaf(io<T1>::load(e[j + 1]), 1.4426950408889634f, neg_m_log2e));
+      s0 += f[j];
+      s1 += f[j + 1];
+    }
+    return s0 + s1;
+  }
+};
+template <> struct RowVec<__half> : RowVec16<__half2, __half> {
+  static __device__ __forceinline__ uint4 scaled(const float (&f)[8], float r) {
+    uint4 out;
+    __half2 *o = reinterpret_cast<__half2 *>(&out);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) o[j] = __floats2half2_rn(f[2 * j] * r, f[2 * j + 1] * r);
+    return out;
+  }
+};
+template <> struct RowVec<__nv_bfloat16> : RowVec16<__nv_bfloat162, __nv_bfloat16> {
+  static __device__ __forceinline__ uint4 scaled(const float (&f)[8], float r) {
+    uint4 out;
+    __nv_bfloat162 *o = reinterpret_cast<__nv_bfloat162 *>(&out);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) o[j] = __floats2bfloat162_rn(f[2 * j] * r, f[2 * j + 1] * r);
+    return out;
+  }
+};
+
 template <typename T, int G, int VPT>
 __global__ void __launch_bounds__((G > kRowThreads ? G : kRowThreads))
 softmax_rows_kernel(const T *__restrict__ x, T *__restrict__ y, int64_t rows,
                     int cols, int mask_kind, int64_t row_offset) {
   constexpr int kThreads = G > kRowThreads ? G : kRowThreads;
   constexpr int kRowsPerCta = kThreads / G;
-  constexpr int N = vec16<T>::N;
-  __shared__ float scratch[kThreads / 32];
+  using V = RowVec<T>;
+  constexpr int N = V::N;
+  __shared__ float scratch[2 * (kThreads / 32)];
 
   const int lane = threadIdx.x % G;
   const int64_t row = (int64_t)blockIdx.x * kRowsPerCta + threadIdx.x / G;
   const bool row_ok = row < rows;
   const int nvec = cols / N;
-  // number of kept columns in this row: [0, keep)
+  // kept columns of this row: [0, keep); vectors [0, full_vec) are kept whole,
+  // vector full_vec (if keep % N != 0) partly, everything after is masked
   int keep = cols;
   if (mask_kind == B200_MASK_CAUSAL_MOD && row_ok)
     keep = (int)((row_offset + row) % cols) + 1;
-  const int kept_vec = (keep + N - 1) / N;
+  const int full_vec = keep / N;
+  const int kept_vec = row_ok ? (keep + N - 1) / N : 0;
 
-  float f[VPT][N];
+  // the kept part of the row is loaded once and stays in registers; the masked
+  // part is never loaded and costs no arithmetic
+  uint4 raw[VPT];
   float m = -INFINITY;
   const T *xrow = x + row * (int64_t)cols;
 #pragma unroll
   for (int i = 0; i < VPT; ++i) {
     const int v = lane + i * G;
-    if (row_ok && v < kept_vec) {
-      vec16<T> xv;
-      xv.raw = ld_stream16(xrow + (int64_t)v * N);
-#pragma unroll
-      for (int j = 0; j < N; ++j) {
-        f[i][j] = (v * N + j < keep) ? io<T>::load(xv.e[j]) : -INFINITY;
-        m = fmaxf(m, f[i][j]);
-      }
-    } else {
-#pragma unroll
-      for (int j = 0; j < N; ++j) f[i][j] = -INFINITY;
+    if (v < kept_vec) {
+      raw[i] = ld_stream16(xrow + (int64_t)v * N);
+      if (v >= full_vec) V::mask_tail(raw[i], keep - v * N);
+      m = fmaxf(m, V::vmax(raw[i]));
     }
   }
-  m = group_reduce<G, MaxOp>(m, scratch);
-  // a row whose kept values are all -inf would give inf-inf: keep it NaN like
-  // the numpy formula does; with finite inputs m is finite here.
+  m = group_reduce<G, MaxOp>(m, scratch, 0);
+  const float neg_m_log2e = -m * 1.4426950408889634f;
+  float f[VPT][N];
   float s = 0.f;
 #pragma unroll
-  for (int i = 0; i < VPT; ++i)
-#pragma unroll
-    for (int j = 0; j < N; ++j) {
-      f[i][j] = fast_exp<T>(f[i][j] - m);
-      s += f[i][j];
-    }
-  s = group_reduce<G, SumOp>(s, scratch);
+  for (int i = 0; i < VPT; ++i) {
+    const int v = lane + i * G;
+    if (v < kept_vec) s += V::exps(raw[i], m, neg_m_log2e, f[i]);
+  }
+  s = group_reduce<G, SumOp>(s, scratch, 1);
   const float r = 1.0f / s;
 
   T *yrow = y + row * (int64_t)cols;
@@ -76,10 +162,8 @@ softmax_rows_kernel(const T *__restrict__ x, T *__restrict__ y, int64_t rows,
   for (int i = 0; i < VPT; ++i) {
     const int v = lane + i * G;
     if (row_ok && v < nvec) {
-      vec16<T> out;
-#pragma unroll
-      for (int j = 0; j < N; ++j) out.e[j] = io<T>::store(f[i][j] * r);
-      st_stream16(yrow + (int64_t)v * N, out.raw);
+      const uint4 out = v < kept_vec ? V::scaled(f[i], r) : make_uint4(0u, 0u, 0u, 0u);
+      st_stream16(yrow + (int64_t)v * N, out);
     }
   }
 }
@@ -90,7 +174,7 @@ template <typename T>
 __global__ void __launch_bounds__(kRowThreads)
 softmax_loop_kernel(const T *__restrict__ x, T *__restrict__ y, int cols,
                     int mask_kind, int64_t row_offset) {
-  __shared__ float scratch[kRowThreads / 32];
+  __shared__ float scratch[2 * (kRowThreads / 32)];
   const int64_t row = blockIdx.x;
   int keep = cols;
   if (mask_kind == B200_MASK_CAUSAL_MOD) keep = (int)((row_offset + row) % cols) + 1;
@@ -98,11 +182,11 @@ softmax_loop_kernel(const T *__restrict__ x, T *__restrict__ y, int cols,
   T *yrow = y + row * (int64_t)cols;
   float m = -INFINITY;
   for (int c = threadIdx.x; c < keep; c += kRowThreads) m = fmaxf(m, io<T>::load(xrow[c]));
-  m = group_reduce<kRowThreads, MaxOp>(m, scratch);
+  m = group_reduce<kRowThreads, MaxOp>(m, scratch, 0);
   float s = 0.f;
   for (int c = threadIdx.x; c < keep; c += kRowThreads)
     s += fast_exp<T>(io<T>::load(xrow[c]) - m);
-  s = group_reduce<kRowThreads, SumOp>(s, scratch);
+  s = group_reduce<kRowThreads, SumOp>(s, scratch, 1);
   const float r = 1.0f / s;
   for (int c = threadIdx.x; c < cols; c += kRowThreads)
     yrow[c] = io<T>::store(c < keep ? fast_exp<T>(io<T>::load(xrow[c]) - m) * r : 0.f);

@@ -37,6 +37,9 @@ def main(argv=None):
     parser.add_argument("--launches", type=int, default=3)
     parser.add_argument("--device", type=int, default=0)
     parser.add_argument("--no-mask", action="store_true", help="softmax/attention without mask")
+    parser.add_argument("--act", default="gelu_tanh", choices=["none", "gelu_tanh", "gelu_erf"],
+                        help="gemm epilogue")
+    parser.add_argument("--no-bias", action="store_true", help="gemm without the bias add")
     args = parser.parse_args(argv)
     device = B200Device(args.device)
     rng = np.random.default_rng(0)
@@ -62,8 +65,11 @@ def main(argv=None):
         b = _upload(device, rng.standard_normal((k, n), dtype=np.float32) / np.sqrt(k), dtype)
         c = device.alloc((m, n), dtype)
         if args.op == "gemm":
-            bias = _upload(device, rng.normal(0, 0.1, n).astype(np.float32), dtype)
-            launch = lambda: ops.gemm(a, b, c, bias=bias, act=abi.ACT_GELU_TANH)  # noqa: E731
+            bias = None if args.no_bias else _upload(
+                device, rng.normal(0, 0.1, n).astype(np.float32), dtype)
+            act = {"none": abi.ACT_NONE, "gelu_tanh": abi.ACT_GELU_TANH,
+                   "gelu_erf": abi.ACT_GELU_ERF}[args.act]
+            launch = lambda: ops.gemm(a, b, c, bias=bias, act=act)  # noqa: E731
             work = {"flop": 2 * m * n * k}
         else:
             b2 = _upload(device, rng.standard_normal((k, n), dtype=np.float32) / np.sqrt(k), dtype)
