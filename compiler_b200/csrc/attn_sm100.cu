@@ -17,6 +17,7 @@
 //            (tensor memory over the S columns, or shared memory), final
 //            normalisation and store of O and LSE
 // Every wait is bounded; an expired wait sets the status word and drains.
+#include "attn_pair_sm100.cuh"
 #include "attn_simt.cuh"
 #include "sm100.cuh"
 
@@ -513,6 +514,21 @@ extern "C" int b200_attn_fwd(const b200_tensor *q, const b200_tensor *k, const b
   p.idesc_pv = sm100::make_idesc_f16(BLOCK_M, (int)D, fmt, 0, 1);
   p.status = device_status_word();
   if (p.status == nullptr) return fail(B200_RESOURCE, "no status word on this device");
+  // B200OPS_ATTN_KERNEL=single selects the one-tile-per-CTA kernel; the default is the
+  // persistent two-tile kernel
+  const char *which = getenv("B200OPS_ATTN_KERNEL");
+  if (!(which != nullptr && which[0] == 's')) {
+    pair::Params pp;
+    pp.H = p.H; pp.N = p.N; pp.ZH = (int)(Z * H);
+    pp.scale_log2 = p.scale_log2; pp.causal = p.causal;
+    pp.o = p.o; pp.oz = p.oz; pp.oh = p.oh; pp.om = p.om; pp.lse = p.lse;
+    pp.idesc_qk = p.idesc_qk; pp.idesc_pv = p.idesc_pv; pp.status = p.status;
+    if (q->dtype == B200_DTYPE_BFLOAT16)
+      return D == 128 ? pair::launch<__nv_bfloat16, 128>(tq, tk, tv, pp, s)
+                      : pair::launch<__nv_bfloat16, 64>(tq, tk, tv, pp, s);
+    return D == 128 ? pair::launch<__half, 128>(tq, tk, tv, pp, s)
+                    : pair::launch<__half, 64>(tq, tk, tv, pp, s);
+  }
   const bool pt = p_in_tmem();
   const int zh = (int)(Z * H);
 #define B200_ATTN_TC(T, DD)                                                   \

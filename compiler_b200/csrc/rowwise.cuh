@@ -39,7 +39,20 @@ __device__ __forceinline__ float group_reduce(float v, float *scratch, int buf) 
     const int group = threadIdx.x / G;
     float *slot = scratch + buf * (blockDim.x >> 5);
     if ((threadIdx.x & 31) == 0) slot[threadIdx.x >> 5] = v;
-    asm volatile("bar.sync %0, %1;" ::"r"(group + 1), "n"(G) : "memory");
+    // literal barrier ids: a register id would make ptxas reserve all 16 hardware
+    // barriers per CTA and cap the CTAs per SM at 4
+    if constexpr (G >= kRowThreads) {
+      __syncthreads();
+    } else if constexpr (G == kRowThreads / 2) {
+      if (group == 0) asm volatile("bar.sync 1, %0;" ::"n"(G) : "memory");
+      else asm volatile("bar.sync 2, %0;" ::"n"(G) : "memory");
+    } else {
+      static_assert(G == kRowThreads / 4, "row groups are 64, 128 or >= 256 threads");
+      if (group == 0) asm volatile("bar.sync 1, %0;" ::"n"(G) : "memory");
+      else if (group == 1) asm volatile("bar.sync 2, %0;" ::"n"(G) : "memory");
+      else if (group == 2) asm volatile("bar.sync 3, %0;" ::"n"(G) : "memory");
+      else asm volatile("bar.sync 4, %0;" ::"n"(G) : "memory");
+    }
     const int first = group * kWarps;
     v = slot[first];
 #pragma unroll

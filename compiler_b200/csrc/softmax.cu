@@ -40,22 +40,18 @@ template <> struct RowVec<float> {
     const float *e = reinterpret_cast<const float *>(&raw);
     return fmaxf(fmaxf(e[0], e[1]), fmaxf(e[2], e[3]));
   }
-  // f[j] = exp(x[j] - m); returns their sum
-  static __device__ __forceinline__ float exps(const uint4 &raw, float m, float, float (&f)[N]) {
+  // sum of exp(x[j] - m)
+  static __device__ __forceinline__ float expsum(const uint4 &raw, float m, float) {
     const float *e = reinterpret_cast<const float *>(&raw);
-    float s = 0.f;
-#pragma unroll
-    for (int j = 0; j < N; ++j) {
-      f[j] = expf(e[j] - m);
-      s += f[j];
-    }
-    return s;
+    return (expf(e[0] - m) + expf(e[1] - m)) + (expf(e[2] - m) + expf(e[3] - m));
   }
-  static __device__ __forceinline__ uint4 scaled(const float (&f)[N], float r) {
+  // exp(x[j] - m) * r in the storage type
+  static __device__ __forceinline__ uint4 scaled(const uint4 &raw, float m, float, float r) {
+    const float *e = reinterpret_cast<const float *>(&raw);
     uint4 out;
     float *o = reinterpret_cast<float *>(&out);
 #pragma unroll
-    for (int j = 0; j < N; ++j) o[j] = f[j] * r;
+    for (int j = 0; j < N; ++j) o[j] = expf(e[j] - m) * r;
     return out;
   }
 };
@@ -76,41 +72,52 @@ template <typename T2, typename T1> struct RowVec16 {
     const T2 a = __hmax2(__hmax2(p[0], p[1]), __hmax2(p[2], p[3]));
     return fmaxf(io<T1>::load(a.x), io<T1>::load(a.y));
   }
-  static __device__ __forceinline__ float exps(const uint4 &raw, float, float neg_m_log2e,
-                                               float (&f)[N]) {
+  static __device__ __forceinline__ float e2(T1 x, float neg_m_log2e) {
+    return ex2_approx(fmaf(io<T1>::load(x), 1.4426950408889634f, neg_m_log2e));
+  }
+  static __device__ __forceinline__ float expsum(const uint4 &raw, float, float neg_m_log2e) {
     const T1 *e = reinterpret_cast<const T1 *>(&raw);
     float s0 = 0.f, s1 = 0.f;
 #pragma unroll
     for (int j = 0; j < N; j += 2) {
-      f[j] = ex2_approx(fmaf(io<T1>::load(e[j]), 1.4426950408889634f, neg_m_log2e));
-      f[j + 1] = ex2_approx(fmaf(io<T1>::load(e[j + 1]), 1.4426950408889634f, neg_m_log2e));
-      s0 += f[j];
-      s1 += f[j + 1];
+      s0 += e2(e[j], neg_m_log2e);
+      s1 += e2(e[j + 1], neg_m_log2e);
     }
     return s0 + s1;
   }
 };
+// The exponentials are recomputed for the store instead of being kept: 16 registers
+// of packed inputs per thread instead of 32 of fp32 results, which is what lets 8 CTAs
+// share an SM; the extra ex2 work rides on an otherwise idle pipe.
 template <> struct RowVec<__half> : RowVec16<__half2, __half> {
-  static __device__ __forceinline__ uint4 scaled(const float (&f)[8], float r) {
+  static __device__ __forceinline__ uint4 scaled(const uint4 &raw, float, float neg_m_log2e,
+                                                 float r) {
+    const __half *e = reinterpret_cast<const __half *>(&raw);
     uint4 out;
     __half2 *o = reinterpret_cast<__half2 *>(&out);
 #pragma unroll
-    for (int j = 0; j < 4; ++j) o[j] = __floats2half2_rn(f[2 * j] * r, f[2 * j + 1] * r);
+    for (int j = 0; j < 4; ++j)
+      o[j] = __floats2half2_rn(e2(e[2 * j], neg_m_log2e) * r, e2(e[2 * j + 1], neg_m_log2e) * r);
     return out;
   }
 };
 template <> struct RowVec<__nv_bfloat16> : RowVec16<__nv_bfloat162, __nv_bfloat16> {
-  static __device__ __forceinline__ uint4 scaled(const float (&f)[8], float r) {
+  static __device__ __forceinline__ uint4 scaled(const uint4 &raw, float, float neg_m_log2e,
+                                                 float r) {
+    const __nv_bfloat16 *e = reinterpret_cast<const __nv_bfloat16 *>(&raw);
     uint4 out;
     __nv_bfloat162 *o = reinterpret_cast<__nv_bfloat162 *>(&out);
 #pragma unroll
-    for (int j = 0; j < 4; ++j) o[j] = __floats2bfloat162_rn(f[2 * j] * r, f[2 * j + 1] * r);
+    for (int j = 0; j < 4; ++j)
+      o[j] = __floats2bfloat162_rn(e2(e[2 * j], neg_m_log2e) * r,
+                                   e2(e[2 * j + 1], neg_m_log2e) * r);
     return out;
   }
 };
 
 template <typename T, int G, int VPT>
-__global__ void __launch_bounds__((G > kRowThreads ? G : kRowThreads))
+__global__ void __launch_bounds__((G > kRowThreads ? G : kRowThreads),
+                                  (G > kRowThreads ? 1 : 8))
 softmax_rows_kernel(const T *__restrict__ x, T *__restrict__ y, int64_t rows,
                     int cols, int mask_kind, int64_t row_offset) {
   constexpr int kThreads = G > kRowThreads ? G : kRowThreads;
@@ -147,12 +154,11 @@ softmax_rows_kernel(const T *__restrict__ x, T *__restrict__ y, int64_t rows,
   }
   m = group_reduce<G, MaxOp>(m, scratch, 0);
   const float neg_m_log2e = -m * 1.4426950408889634f;
-  float f[VPT][N];
   float s = 0.f;
 #pragma unroll
   for (int i = 0; i < VPT; ++i) {
     const int v = lane + i * G;
-    if (v < kept_vec) s += V::exps(raw[i], m, neg_m_log2e, f[i]);
+    if (v < kept_vec) s += V::expsum(raw[i], m, neg_m_log2e);
   }
   s = group_reduce<G, SumOp>(s, scratch, 1);
   const float r = 1.0f / s;
@@ -162,7 +168,8 @@ softmax_rows_kernel(const T *__restrict__ x, T *__restrict__ y, int64_t rows,
   for (int i = 0; i < VPT; ++i) {
     const int v = lane + i * G;
     if (row_ok && v < nvec) {
-      const uint4 out = v < kept_vec ? V::scaled(f[i], r) : make_uint4(0u, 0u, 0u, 0u);
+      const uint4 out =
+          v < kept_vec ? V::scaled(raw[i], m, neg_m_log2e, r) : make_uint4(0u, 0u, 0u, 0u);
       st_stream16(yrow + (int64_t)v * N, out);
     }
   }

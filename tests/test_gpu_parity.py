@@ -184,14 +184,14 @@ def test_gemm_fp32_operands_take_the_ieee_path(device):
 
 
 ATTN_SHAPES = [(1, 2, 256, 128), (2, 1, 384, 64), (1, 2, 200, 128), (1, 1, 128, 128),
-               (1, 1, 640, 128), (1, 3, 77, 64)]
+               (1, 1, 640, 128), (1, 3, 77, 64), (3, 70, 512, 128), (1, 2, 1100, 64)]
 
 
-@pytest.mark.parametrize("p_location", ["tmem", "smem"])
+@pytest.mark.parametrize("variant", ["pair", "single-tmem", "single-smem"])
 @pytest.mark.parametrize("dtype", ["bfloat16", "float16"])
 @pytest.mark.parametrize("causal", [True, False])
 @pytest.mark.parametrize("shape", ATTN_SHAPES)
-def test_attention_sweep(device, shape, dtype, causal, p_location):
+def test_attention_sweep(device, shape, dtype, causal, variant):
     z, h, n, d = shape
     rng = np.random.default_rng(_seed(shape, dtype, causal))
     q, k, v = (_host(rng.standard_normal(shape), dtype) for _ in range(3))
@@ -199,12 +199,15 @@ def test_attention_sweep(device, shape, dtype, causal, p_location):
     do = _poisoned(device, shape, dtype)
     dl = device.upload(np.full((z, h, n), POISON, np.float32))
     scale = 1.0 / np.sqrt(d)
-    os.environ["B200OPS_ATTN_P"] = p_location
+    kernel, _, p_location = variant.partition("-")
+    os.environ["B200OPS_ATTN_KERNEL"] = kernel
+    os.environ["B200OPS_ATTN_P"] = p_location or "tmem"
     try:
         ops.attention(dq, dk, dv, do, lse=dl, scale=scale, causal=causal)
         device.check_status()
     finally:
         os.environ.pop("B200OPS_ATTN_P", None)
+        os.environ.pop("B200OPS_ATTN_KERNEL", None)
     out_ref, lse_ref = oracle.attention_ref(q, k, v, scale, causal)
     oracle.compare(device.download(do).astype(np.float64), out_ref, *TOL[dtype], name="out")
     oracle.compare(device.download(dl).astype(np.float64), lse_ref, 1e-3, 1e-3, name="lse")
