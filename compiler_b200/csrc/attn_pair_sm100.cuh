@@ -95,6 +95,48 @@ __device__ __forceinline__ float2 fadd2(float2 a, float2 b) {
   return *reinterpret_cast<float2 *>(&d);
 }
 
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+__device__ __forceinline__ float2 fsub2(float2 a, float2 b) {
+  unsigned long long d;
+  asm("sub.rn.f32x2 %0, %1, %2;"
+      : "=l"(d)
+      : "l"(*reinterpret_cast<unsigned long long *>(&a)),
+        "l"(*reinterpret_cast<unsigned long long *>(&b)));
+  return *reinterpret_cast<float2 *>(&d);
+}
+__device__ __forceinline__ float2 fadd2_rm(float2 a, float2 b) {  // round towards -inf
+  unsigned long long d;
+  asm("add.rm.f32x2 %0, %1, %2;"
+      : "=l"(d)
+      : "l"(*reinterpret_cast<unsigned long long *>(&a)),
+        "l"(*reinterpret_cast<unsigned long long *>(&b)));
+  return *reinterpret_cast<float2 *>(&d);
+}
+// 2^v for a pair, on the FMA / integer pipes instead of the special-function unit
+// (which is the busiest pipe of this kernel): v = floor(v) + f, 2^f by a cubic with
+// max relative error 8.6e-5 on [0,1) (below half an ulp of the 16-bit P it feeds),
+// 2^floor(v) by adding floor(v) to the exponent field.  floor(v) comes out of the low
+// mantissa bits of v + 1.5*2^23 rounded towards -inf.  Inputs below -127 (including
+// the -inf of masked keys) give a value below 2^-126, which P rounds to zero.
+__device__ __forceinline__ float2 exp2_poly2(float2 v) {
+  const float kMagic = 12582912.0f;
+  v.x = fmaxf(v.x, -127.0f);
+  v.y = fmaxf(v.y, -127.0f);
+  const float2 magic2 = make_float2(kMagic, kMagic);
+  const float2 t = fadd2_rm(v, magic2);
+  const float2 f = fsub2(v, fsub2(t, magic2));
+  float2 p2 = ffma2(f, make_float2(0.07706635445356369f, 0.07706635445356369f),
+                    make_float2(0.22764573991298676f, 0.22764573991298676f));
+  p2 = ffma2(p2, f, make_float2(0.6951166391372681f, 0.6951166391372681f));
+  p2 = ffma2(p2, f, make_float2(1.0f, 1.0f));
+  return make_float2(__uint_as_float(__float_as_uint(p2.x) + (__float_as_uint(t.x) << 23)),
+                     __uint_as_float(__float_as_uint(p2.y) + (__float_as_uint(t.y) << 23)));
+}
+
 template <typename T> __device__ __forceinline__ uint32_t pack2(float a, float b);
 template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float a, float b) {
   uint32_t r;
@@ -159,7 +201,8 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q,
   auto o_full = [&](int t) { return bar0 + 8u * (14 + t); };
   auto o_empty = [&](int t) { return bar0 + 8u * (16 + t); };
   const uint32_t drain_bar = bar0 + 8u * 18;
-  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem_gen + L::BAR_OFF + 8 * 19);
+  auto p2_full = [&](int t) { return bar0 + 8u * (19 + t); };  // second half of P
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem_gen + L::BAR_OFF + 8 * 21);
   volatile uint32_t *abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5;
@@ -178,9 +221,10 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q,
     }
     for (int t = 0; t < 2; ++t) {
       mbar_init(s_full(t), 1);
-      mbar_init(p_full(t), TILE_M);
+      mbar_init(p_full(t), TILE_M / 32);   // one arrival per softmax warp
+      mbar_init(p2_full(t), TILE_M / 32);
       mbar_init(o_full(t), 1);
-      mbar_init(o_empty(t), TILE_M);
+      mbar_init(o_empty(t), TILE_M / 32);
     }
     mbar_init(drain_bar, 1);
     *abort_flag = 0u;
@@ -250,82 +294,107 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q,
     }
   } else if (warp == 9) {
     // ---------------------------------------------------------------- MMA issuer
-    if (lane == 0) {
-      uint32_t kv_base = 0, item_n = 0;
-      uint32_t blocks[2] = {0, 0};  // key blocks each tile has been through (barrier phases)
-      uint32_t active[2] = {0, 0};  // items in which each tile had work (o_empty phase)
-      bool ok = true;
-      auto issue_qk = [&](int t, uint32_t s) {
-        const uint32_t d_tmem = tmem_base + (uint32_t)(t * S_COLS);
+    // The whole warp runs this loop (uniform control flow keeps the descriptor
+    // arithmetic cheap); one elected lane issues the MMAs and commits.
+    const bool leader = elect_one();
+    uint32_t kv_base = 0, item_n = 0;
+    uint32_t blocks[2] = {0, 0};  // key blocks each tile has been through (barrier phases)
+    uint32_t active[2] = {0, 0};  // items in which each tile had work (o_empty phase)
+    bool ok = true;
+    auto wait_all = [&](uint32_t bar, uint32_t parity, uint32_t site) {
+      return __all_sync(0xffffffffu, mbar_wait(bar, parity, ctx, site)) != 0;
+    };
+    // descriptor halves that never change: Q tiles, K / V stages
+    constexpr uint32_t kHi = desc_hi_sw128(1024);
+    const uint32_t q_lo0 = desc_lo_sw128(q_smem, 16);
+    const uint32_t k_lo0 = desc_lo_sw128(k_smem, 16);
+    const uint32_t v_lo0 = desc_lo_sw128(v_smem, L::BOX_BYTES);
+    constexpr uint32_t kTileStep = L::TILE_BYTES >> 4;
+    // S_t = Q_t K(s)^T
+    auto issue_qk = [&](int t, uint32_t s) {
+      const uint32_t d_tmem = tmem_base + (uint32_t)(t * S_COLS);
+      const uint32_t a_lo = q_lo0 + (uint32_t)t * kTileStep;
+      const uint32_t b_lo = k_lo0 + s * kTileStep;
+      if (leader) {
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t off = (uint32_t)((kk / 4) * L::BOX_BYTES + (kk % 4) * 32);
-          const uint64_t a_desc =
-              make_smem_desc_sw128(q_smem + t * L::TILE_BYTES + off, 16, 1024);
-          const uint64_t b_desc =
-              make_smem_desc_sw128(k_smem + s * L::TILE_BYTES + off, 16, 1024);
-          mma_f16_ss(d_tmem, a_desc, b_desc, p.idesc_qk, kk > 0 ? 1u : 0u);
+          constexpr uint32_t kBox = L::BOX_BYTES >> 4;
+          const uint32_t off = (uint32_t)(kk / 4) * kBox + (uint32_t)(kk % 4) * 2u;
+          mma_f16_ss(d_tmem, a_lo + off, kHi, b_lo + off, kHi, p.idesc_qk, kk > 0 ? 1u : 0u);
         }
         tc_commit(s_full(t));
-      };
-      auto issue_pv = [&](int t, uint32_t s, bool first) {
-        const uint32_t o_tmem = tmem_base + (uint32_t)(O_COL0 + t * S_COLS);
+      }
+    };
+    // O_t += P_t V(s) over the key rows [64 * half, 64 * half + 64) of the block
+    auto issue_pv_half = [&](int t, uint32_t s, bool first, int half) {
+      const uint32_t o_tmem = tmem_base + (uint32_t)(O_COL0 + t * S_COLS);
+      const uint32_t b_lo = v_lo0 + s * kTileStep;
+      const uint32_t a_tmem = tmem_base + (uint32_t)(t * S_COLS);
+      if (leader) {
 #pragma unroll
-        for (int kk = 0; kk < BLOCK_N / 16; ++kk) {
-          const uint64_t b_desc = make_smem_desc_sw128(
-              v_smem + s * L::TILE_BYTES + kk * 2048, L::BOX_BYTES, 1024);
-          const uint32_t a_tmem = tmem_base + (uint32_t)(t * S_COLS + kk * 8);
-          mma_f16_ts(o_tmem, a_tmem, b_desc, p.idesc_pv, (!first || kk > 0) ? 1u : 0u);
+        for (int k4 = 0; k4 < BLOCK_N / 32; ++k4) {
+          const int kk = half * (BLOCK_N / 32) + k4;
+          mma_f16_ts(o_tmem, a_tmem + (uint32_t)(kk * 8), b_lo + (uint32_t)(kk * (2048 >> 4)), kHi,
+                     p.idesc_pv, (!first || kk > 0) ? 1u : 0u);
         }
-        tc_commit(o_full(t));
-      };
-      for (int item = blockIdx.x; ok && item < num_items; item += gridDim.x, ++item_n) {
-        const Item it = decode_item(item, p);
-        if (!mbar_wait(q_full, item_n & 1u, ctx, 4)) { ok = false; break; }
-        {  // S(0) of both tiles
-          const uint32_t s = kv_base & 1u, ph = (kv_base >> 1) & 1u;
-          if (!mbar_wait(k_full(s), ph, ctx, 5)) { ok = false; break; }
-          tc_fence_after_sync();
-          if (it.nb[0] > 0) issue_qk(0, s);
-          if (it.nb[1] > 0) issue_qk(1, s);
-          tc_commit(k_empty(s));
-          if (it.nb_max == 1) tc_commit(q_empty);
-        }
-        for (int j = 0; ok && j < it.nb_max; ++j) {
-          const uint32_t kv = kv_base + (uint32_t)j;
-          const uint32_t s = kv & 1u, ph = (kv >> 1) & 1u;
-          const uint32_t s1 = (kv + 1) & 1u, ph1 = ((kv + 1) >> 1) & 1u;
-          const bool more = j + 1 < it.nb_max;
-          if (!mbar_wait(v_full(s), ph, ctx, 6)) { ok = false; break; }
+        if (half == 1) tc_commit(o_full(t));
+      }
+    };
+    auto commit = [&](uint32_t bar) {
+      if (leader) tc_commit(bar);
+    };
+    for (int item = blockIdx.x; ok && item < num_items; item += gridDim.x, ++item_n) {
+      const Item it = decode_item(item, p);
+      if (!wait_all(q_full, item_n & 1u, 4)) { ok = false; break; }
+      {  // S(0) of both tiles
+        const uint32_t s = kv_base & 1u, ph = (kv_base >> 1) & 1u;
+        if (!wait_all(k_full(s), ph, 5)) { ok = false; break; }
+        tc_fence_after_sync();
+        if (it.nb[0] > 0) issue_qk(0, s);
+        if (it.nb[1] > 0) issue_qk(1, s);
+        commit(k_empty(s));
+        if (it.nb_max == 1) commit(q_empty);
+      }
+      for (int j = 0; ok && j < it.nb_max; ++j) {
+        const uint32_t kv = kv_base + (uint32_t)j;
+        const uint32_t s = kv & 1u, ph = (kv >> 1) & 1u;
+        const uint32_t s1 = (kv + 1) & 1u, ph1 = ((kv + 1) >> 1) & 1u;
+        const bool more = j + 1 < it.nb_max;
+        if (!wait_all(v_full(s), ph, 6)) { ok = false; break; }
 #pragma unroll
-          for (int t = 0; t < 2; ++t) {
-            if (j < it.nb[t]) {
-              // the previous item's O of this tile must have been read out
-              if (j == 0 && !mbar_wait(o_empty(t), (active[t] & 1u) ^ 1u, ctx, 7)) { ok = false; break; }
-              if (!mbar_wait(p_full(t), blocks[t] & 1u, ctx, 8)) { ok = false; break; }
-              tc_fence_after_sync();
-              issue_pv(t, s, j == 0);
-              ++blocks[t];
-            }
-            if (t == 1) tc_commit(v_empty(s));
-            if (more) {
-              if (t == 0 && !mbar_wait(k_full(s1), ph1, ctx, 9)) { ok = false; break; }
-              tc_fence_after_sync();
-              if (j + 1 < it.nb[t]) issue_qk(t, s1);
-              if (t == 1) {
-                tc_commit(k_empty(s1));
-                if (j + 2 == it.nb_max) tc_commit(q_empty);  // last S of this item issued
-              }
+        for (int t = 0; t < 2; ++t) {
+          if (j < it.nb[t]) {
+            // the previous item's O of this tile must have been read out
+            if (j == 0 && !wait_all(o_empty(t), (active[t] & 1u) ^ 1u, 7)) { ok = false; break; }
+            if (!wait_all(p_full(t), blocks[t] & 1u, 8)) { ok = false; break; }
+            tc_fence_after_sync();
+            issue_pv_half(t, s, j == 0, 0);
+            if (!wait_all(p2_full(t), blocks[t] & 1u, 13)) { ok = false; break; }
+            tc_fence_after_sync();
+            issue_pv_half(t, s, j == 0, 1);
+            ++blocks[t];
+          }
+          if (t == 1) commit(v_empty(s));
+          if (more) {
+            if (t == 0 && !wait_all(k_full(s1), ph1, 9)) { ok = false; break; }
+            tc_fence_after_sync();
+            if (j + 1 < it.nb[t]) issue_qk(t, s1);
+            if (t == 1) {
+              commit(k_empty(s1));
+              if (j + 2 == it.nb_max) commit(q_empty);  // last S of this item issued
             }
           }
         }
-        kv_base += (uint32_t)it.nb_max;
-        active[0] += it.nb[0] > 0 ? 1u : 0u;
-        active[1] += it.nb[1] > 0 ? 1u : 0u;
       }
+      kv_base += (uint32_t)it.nb_max;
+      active[0] += it.nb[0] > 0 ? 1u : 0u;
+      active[1] += it.nb[1] > 0 ? 1u : 0u;
+    }
+    if (leader) {
       tc_commit(drain_bar);
       mbar_wait_drain(drain_bar, 0);
     }
+    __syncwarp();
   }
   } else {
     asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
@@ -373,12 +442,14 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q,
         }
         float mx0 = x[0], mx1 = x[1], mx2 = x[2], mx3 = x[3];
 #pragma unroll
-        for (int i = 4; i < BLOCK_N; i += 4) {
-          mx0 = fmaxf(mx0, x[i]);
-          mx1 = fmaxf(mx1, x[i + 1]);
-          mx2 = fmaxf(mx2, x[i + 2]);
-          mx3 = fmaxf(mx3, x[i + 3]);
+        for (int i = 4; i < BLOCK_N - 4; i += 8) {
+          mx0 = max3(mx0, x[i], x[i + 1]);
+          mx1 = max3(mx1, x[i + 2], x[i + 3]);
+          mx2 = max3(mx2, x[i + 4], x[i + 5]);
+          mx3 = max3(mx3, x[i + 6], x[i + 7]);
         }
+        mx0 = max3(mx0, x[BLOCK_N - 4], x[BLOCK_N - 3]);
+        mx1 = max3(mx1, x[BLOCK_N - 2], x[BLOCK_N - 1]);
         const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * p.scale_log2;
         // lazy rescale: the max used for exp2 is raised only when the true max
         // exceeds it by more than 2^kRescaleThreshold
@@ -410,26 +481,37 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q,
         l *= alpha;
         const float2 negm2 = make_float2(-m_used, -m_used);
         float2 sum_a = make_float2(0.f, 0.f), sum_b = make_float2(0.f, 0.f);
-        uint32_t packed[BLOCK_N / 2];
+        // P is handed over in two halves of 64 keys so that the first half of
+        // O += P V runs while the second half is still being exponentiated.  In every
+        // group of 8 keys one pair takes the polynomial exp2, three pairs the ex2 unit.
 #pragma unroll
-        for (int i = 0; i < BLOCK_N; i += 4) {
-          const float2 va = ffma2(make_float2(x[i], x[i + 1]), scale2, negm2);
-          const float2 vb = ffma2(make_float2(x[i + 2], x[i + 3]), scale2, negm2);
-          const float2 ea = make_float2(ex2(va.x), ex2(va.y));
-          const float2 eb = make_float2(ex2(vb.x), ex2(vb.y));
-          sum_a = fadd2(sum_a, ea);
-          sum_b = fadd2(sum_b, eb);
-          packed[i / 2] = pack2<T>(ea.x, ea.y);
-          packed[i / 2 + 1] = pack2<T>(eb.x, eb.y);
+        for (int half = 0; half < 2; ++half) {
+          uint32_t packed[32];
+#pragma unroll
+          for (int g = 0; g < 8; ++g) {
+            const int i = half * 64 + g * 8;
+            const float2 va = ffma2(make_float2(x[i], x[i + 1]), scale2, negm2);
+            const float2 vb = ffma2(make_float2(x[i + 2], x[i + 3]), scale2, negm2);
+            const float2 vc = ffma2(make_float2(x[i + 4], x[i + 5]), scale2, negm2);
+            const float2 vd = ffma2(make_float2(x[i + 6], x[i + 7]), scale2, negm2);
+            const float2 ea = make_float2(ex2(va.x), ex2(va.y));
+            const float2 eb = make_float2(ex2(vb.x), ex2(vb.y));
+            const float2 ec = make_float2(ex2(vc.x), ex2(vc.y));
+            const float2 ed = exp2_poly2(vd);
+            sum_a = fadd2(sum_a, fadd2(ea, ec));
+            sum_b = fadd2(sum_b, fadd2(eb, ed));
+            packed[g * 4] = pack2<T>(ea.x, ea.y);
+            packed[g * 4 + 1] = pack2<T>(eb.x, eb.y);
+            packed[g * 4 + 2] = pack2<T>(ec.x, ec.y);
+            packed[g * 4 + 3] = pack2<T>(ed.x, ed.y);
+          }
+          tmem_st_32x32b_x32(s_tmem + half * 32, packed);
+          tmem_st_wait();
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(half == 0 ? p_full(t) : p2_full(t));
         }
         l += (sum_a.x + sum_a.y) + (sum_b.x + sum_b.y);
-#pragma unroll
-        for (int c = 0; c < BLOCK_N / 64; ++c)
-          tmem_st_32x32b_x32(s_tmem + c * 32,
-                             reinterpret_cast<const uint32_t(&)[32]>(packed[c * 32]));
-        tmem_st_wait();
-        tc_fence_before_sync();
-        mbar_arrive(p_full(t));
       }
       if (!ok) break;
       // ---- epilogue of this tile: O / l, LSE
@@ -441,7 +523,8 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q,
         tmem_ld_32x32b_x32(o_tmem + c * 32, reinterpret_cast<uint32_t(&)[32]>(acc[c * 32]));
       tmem_ld_wait();
       tc_fence_before_sync();
-      mbar_arrive(o_empty(t));  // the issuer may overwrite O with the next item's first P V
+      __syncwarp();
+      if (lane == 0) mbar_arrive(o_empty(t));  // O may be overwritten by the next item's first P V
       if (row < p.N) {
         const float inv_l = 1.0f / l;
         T *orow = reinterpret_cast<T *>(p.o) + it.z * p.oz + it.h * p.oh + (int64_t)row * p.om;

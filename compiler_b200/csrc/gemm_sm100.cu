@@ -350,40 +350,53 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
     }
   } else if (warp == 5) {
     // ------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
-      int stage = 0;
-      uint32_t phase = 0;
-      int acc = 0;
-      uint32_t acc_phase = 0;
-      bool ok = true;
-      for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
-        if (!mbar_wait(acc_empty_bar(acc), acc_phase ^ 1u, ctx, 2)) { ok = false; break; }
+    // The whole warp runs the loop (uniform control flow keeps the descriptor
+    // arithmetic cheap); one elected lane issues the MMAs and commits.
+    const bool leader = elect_one();
+    int stage = 0;
+    uint32_t phase = 0;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    auto wait_all = [&](uint32_t bar, uint32_t parity, uint32_t site) {
+      return __all_sync(0xffffffffu, mbar_wait(bar, parity, ctx, site)) != 0;
+    };
+    // descriptor halves: only the low word moves, by constants
+    const uint32_t a_lo0 = desc_lo_sw128(a_smem, 16);
+    const uint32_t b_lo0 = desc_lo_sw128(b_smem, p.b_lbo);
+    constexpr uint32_t a_hi = desc_hi_sw128(1024);
+    const uint32_t b_hi = desc_hi_sw128(p.b_sbo);
+    for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+      if (!wait_all(acc_empty_bar(acc), acc_phase ^ 1u, 2)) { ok = false; break; }
+      tc_fence_after_sync();
+      const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
+      for (int kb = 0; kb < num_kb; ++kb) {
+        if (!wait_all(full_bar(stage), phase, 3)) { ok = false; break; }
         tc_fence_after_sync();
-        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
-        for (int kb = 0; kb < num_kb; ++kb) {
-          if (!mbar_wait(full_bar(stage), phase, ctx, 3)) { ok = false; break; }
-          tc_fence_after_sync();
-          const uint64_t a_desc = make_smem_desc_sw128(a_smem + stage * A_STAGE_BYTES, 16, 1024);
-          const uint64_t b_desc =
-              make_smem_desc_sw128(b_smem + stage * B_STAGE_BYTES, p.b_lbo, p.b_sbo);
+        const uint32_t a_lo = a_lo0 + (uint32_t)stage * (A_STAGE_BYTES >> 4);
+        const uint32_t b_lo = b_lo0 + (uint32_t)stage * (B_STAGE_BYTES >> 4);
+        if (leader) {
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k) {
             // A: +32 bytes along K inside the swizzle span; B: +16 K-rows of 128 bytes
-            mma_f16_ss(d_tmem, a_desc + (uint64_t)(k * ((UMMA_K * 2) >> 4)),
-                       b_desc + (uint64_t)(k * ((UMMA_K * 128) >> 4)), p.idesc,
+            mma_f16_ss(d_tmem, a_lo + (uint32_t)(k * ((UMMA_K * 2) >> 4)), a_hi,
+                       b_lo + (uint32_t)(k * ((UMMA_K * 128) >> 4)), b_hi, p.idesc,
                        (kb > 0 || k > 0) ? 1u : 0u);
           }
           tc_commit(empty_bar(stage));  // stage reusable once these MMAs retire
-          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
-        if (!ok) break;
-        tc_commit(acc_full_bar(acc));  // accumulator complete
-        if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+        if (++stage == STAGES) { stage = 0; phase ^= 1u; }
       }
-      // every MMA issued above must retire before shared / tensor memory go away
+      if (!ok) break;
+      if (leader) tc_commit(acc_full_bar(acc));  // accumulator complete
+      if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+    }
+    // every MMA issued above must retire before shared / tensor memory go away
+    if (leader) {
       tc_commit(drain_bar);
       mbar_wait_drain(drain_bar, 0);
     }
+    __syncwarp();
   } else {
     // ------------------------------------------------------------ epilogue
     int acc = 0;

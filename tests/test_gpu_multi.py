@@ -1,0 +1,84 @@
+"""Multi-GPU paths on real devices (skipped below 2 GPUs): the tensor-parallel SwiGLU MLP
+against the unsharded oracle, and row-sharded masked softmax with global row offsets.
+Each rank is a child process (torch.distributed, NCCL), launched the way bench.py is."""
+import os
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+
+pytestmark = pytest.mark.gpu
+ROOT = Path(__file__).resolve().parent.parent
+
+WORKER = r'''
+import os, sys
+import numpy as np
+import torch
+import torch.distributed as dist
+sys.path.insert(0, os.environ["B200_REPO"])
+from compiler_b200 import ops, shard, tp_mlp
+from compiler_b200.runtime import abi
+from oracle import oracle
+
+rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+torch.cuda.set_device(rank)
+abi.check(abi.lib().b200_set_device(rank))
+dist.init_process_group("nccl", device_id=torch.device("cuda", rank))
+
+def bf16(a):
+    return torch.from_numpy(oracle.bf16_round(a.astype(np.float32))).to(torch.bfloat16).cuda()
+
+rng = np.random.default_rng(5)                      # same stream on every rank
+hidden, ffn, m = 512, 1792, 300
+x = oracle.bf16_round(rng.standard_normal((m, hidden)).astype(np.float32))
+wg = oracle.bf16_round(rng.normal(0, 0.05, (hidden, ffn)).astype(np.float32))
+wu = oracle.bf16_round(rng.normal(0, 0.05, (hidden, ffn)).astype(np.float32))
+wd = oracle.bf16_round(rng.normal(0, 0.05, (ffn, hidden)).astype(np.float32))
+lo, hi = shard.column_range(ffn, rank, world)
+mlp = tp_mlp.TensorParallelMLP(bf16(wg[:, lo:hi]).contiguous(), bf16(wu[:, lo:hi]).contiguous(),
+                               bf16(wd[lo:hi]).contiguous(), chunks=3)
+y = torch.empty((m, hidden), device="cuda", dtype=torch.bfloat16)
+for _ in range(2):                                   # second call reuses the scratch buffer
+    mlp.forward(bf16(x), y)
+torch.cuda.synchronize()
+ops.device_status(torch.cuda.current_stream().cuda_stream)
+ref = oracle.swiglu_mlp_ref(x, wg, wu, wd)
+oracle.compare(y.float().cpu().numpy().astype(np.float64), ref, 2e-2, 2e-2, name="tp mlp")
+
+rows, cols = 64, 4000                                # row shards of one masked softmax
+xs = (rng.standard_normal((rows * world, cols)) * 2).astype(np.float16)
+rlo, rhi = shard.block_range(rows * world, rank, world)
+dx = torch.from_numpy(xs[rlo:rhi]).cuda()
+dy = torch.empty_like(dx)
+ops.softmax(dx, dy, causal_mod=True, row_offset=rlo, stream=torch.cuda.current_stream().cuda_stream)
+full = oracle.masked_softmax_ref(xs, 0)
+oracle.compare(dy.float().cpu().numpy().astype(np.float64), full[rlo:rhi], 1e-2, 1e-2, name="softmax shard")
+dist.barrier()
+dist.destroy_process_group()
+print(f"rank {rank} ok")
+'''
+
+
+def _gpu_count():
+    try:
+        import torch
+        return torch.cuda.device_count()
+    except Exception:  # noqa: BLE001
+        return 0
+
+
+@pytest.mark.timeout(600)
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_tp_mlp_and_row_shards(world, tmp_path):
+    if _gpu_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    script = tmp_path / "worker.py"
+    script.write_text(WORKER)
+    env = dict(os.environ, B200_REPO=str(ROOT), NCCL_NVLS_ENABLE="0")
+    result = subprocess.run(
+        [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
+         "--master-addr", "127.0.0.1", "--master-port", str(29500 + world), str(script)],
+        capture_output=True, text=True, env=env, timeout=540)
+    assert result.returncode == 0, result.stdout[-3000:] + result.stderr[-3000:]
+    assert result.stdout.count(" ok") == world
