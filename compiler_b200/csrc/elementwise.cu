@@ -102,6 +102,113 @@ allclose_f32_kernel(const float *__restrict__ a, const float *__restrict__ b,
     atomicMax(maxerr_bits, (unsigned long long)__double_as_longlong(local_err));
 }
 
+// ---- allclose without any allocation ----------------------------------------------
+// Scratch for b200_allclose_f32_static: one (bad count, max-error bits) pair per block.
+// It lives in the library image, so every GPU that loads the library carries these
+// 128 KiB until the process exits.
+constexpr int kStaticBlockElems = 256 * 64;   // elements one block compares
+constexpr int kStaticMaxBlocks = 8192;        // => at most 2^27 elements per call
+static __device__ __align__(256) unsigned long long g_allclose_static[2 * kStaticMaxBlocks];
+
+// Stage 1: block b compares its own slice and writes its pair to scratch[2b], [2b+1]
+// (every launched block writes, so nothing needs to start at zero here).
+__global__ void __launch_bounds__(256)
+allclose_partial_kernel(const float *__restrict__ a, const float *__restrict__ b, int64_t n,
+                        float rtol, float atol, int equal_nan, unsigned long long *scratch) {
+  __shared__ unsigned long long s_bad[8];
+  __shared__ unsigned long long s_err[8];
+  unsigned long long local_bad = 0, local_err = 0;  // error kept as double bits: they order like the values
+  const int64_t base = (int64_t)blockIdx.x * kStaticBlockElems;
+  for (int k = 0; k < kStaticBlockElems / 256; ++k) {
+    const int64_t i = base + (int64_t)k * 256 + threadIdx.x;
+    if (i >= n) break;
+    const float av = a[i], bv = b[i];
+    const float b_abs = fabsf(bv);
+    bool close = ((fabsf(av - bv) <= (atol + rtol * b_abs)) && b_abs < INFINITY) || (av == bv);
+    bool equal = av == bv;
+    if (equal_nan) {
+      const bool both_nan = (av != av) && (bv != bv);
+      close = close || both_nan;
+      equal = equal || both_nan;
+    }
+    if (!close) ++local_bad;
+    if (!equal) {
+      const unsigned long long bits =
+          (unsigned long long)__double_as_longlong(fabs((double)av - (double)bv));
+      if (bits > local_err) local_err = bits;
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    local_bad += __shfl_xor_sync(0xffffffffu, local_bad, o);
+    const unsigned long long other = __shfl_xor_sync(0xffffffffu, local_err, o);
+    if (other > local_err) local_err = other;
+  }
+  if ((threadIdx.x & 31) == 0) {
+    s_bad[threadIdx.x >> 5] = local_bad;
+    s_err[threadIdx.x >> 5] = local_err;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < 8; ++w) {
+      local_bad += s_bad[w];
+      if (s_err[w] > local_err) local_err = s_err[w];
+    }
+    scratch[2 * blockIdx.x] = local_bad;
+    scratch[2 * blockIdx.x + 1] = local_err;
+  }
+}
+
+// Stage 2: one block folds the per-block pairs into the pair at the END of the scratch
+// array (slots 2*blocks, 2*blocks+1 are never a block's own pair; the last pair of the
+// array is reserved for the result).
+__global__ void __launch_bounds__(256)
+allclose_final_kernel(unsigned long long *scratch, int blocks, unsigned long long *result) {
+  __shared__ unsigned long long s_bad[8];
+  __shared__ unsigned long long s_err[8];
+  unsigned long long bad = 0, err = 0;
+  for (int b = threadIdx.x; b < blocks; b += 256) {
+    bad += scratch[2 * b];
+    if (scratch[2 * b + 1] > err) err = scratch[2 * b + 1];
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    bad += __shfl_xor_sync(0xffffffffu, bad, o);
+    const unsigned long long other = __shfl_xor_sync(0xffffffffu, err, o);
+    if (other > err) err = other;
+  }
+  if ((threadIdx.x & 31) == 0) {
+    s_bad[threadIdx.x >> 5] = bad;
+    s_err[threadIdx.x >> 5] = err;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < 8; ++w) {
+      bad += s_bad[w];
+      if (s_err[w] > err) err = s_err[w];
+    }
+    result[0] = bad;
+    result[1] = err;
+  }
+}
+
+// Device address of the scratch array on the current device.  In host code the array's
+// name is only a stand-in for the symbol, not a device pointer: the address has to be
+// asked for, once per device, with that device current.
+static int allclose_static_scratch(unsigned long long **out) {
+  static unsigned long long *cached[64] = {nullptr};
+  int dev = 0;
+  B200_CUDA_OK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return fail(B200_RESOURCE, "device index %d out of range", dev);
+  if (cached[dev] == nullptr) {
+    unsigned long long *ptr = nullptr;
+    B200_CUDA_OK(cudaGetSymbolAddress((void **)&ptr, g_allclose_static));
+    cached[dev] = ptr;
+  }
+  *out = cached[dev];
+  return B200_OK;
+}
+
 __global__ void __launch_bounds__(256)
 bitwise_diff_kernel(const unsigned char *__restrict__ a, const unsigned char *__restrict__ b,
                     size_t n, unsigned int *diff) {
@@ -192,4 +299,43 @@ extern "C" int b200_bitwise_equal(const void *first, const void *other, size_t b
   if (err != cudaSuccess) return fail(B200_SYNC, "bitwise_equal: %s", cudaGetErrorString(err));
   *equal = host ? 0 : 1;
   return host ? B200_REPEAT_MISMATCH : B200_OK;
+}
+
+extern "C" int b200_allclose_f32_static(const void *actual, const void *expected, int64_t count,
+                                        double rtol, double atol, int equal_nan,
+                                        int64_t *bad_count, double *max_abs_err, void *stream) {
+  using namespace b200;
+  if (bad_count == nullptr || max_abs_err == nullptr)
+    return fail(B200_USAGE, "null result pointer");
+  *bad_count = 0;
+  *max_abs_err = 0.0;
+  if (count == 0) return B200_OK;
+  B200_REQUIRE(count > 0 && actual != nullptr && expected != nullptr, "bad buffers");
+  // the last pair of the array holds the result, the rest one pair per block
+  constexpr int64_t kMaxCount = (int64_t)(kStaticMaxBlocks - 1) * kStaticBlockElems;
+  B200_REQUIRE(count <= kMaxCount,
+               "count %lld exceeds the %lld elements the built-in scratch array covers; use "
+               "b200_allclose_f32 for larger buffers",
+               (long long)count, (long long)kMaxCount);
+  unsigned long long *scratch = nullptr;
+  int st = allclose_static_scratch(&scratch);
+  if (st != B200_OK) return st;
+  cudaStream_t s = (cudaStream_t)stream;
+  const int blocks = (int)((count + kStaticBlockElems - 1) / kStaticBlockElems);
+  unsigned long long *result = scratch + 2 * (kStaticMaxBlocks - 1);
+  allclose_partial_kernel<<<blocks, 256, 0, s>>>((const float *)actual, (const float *)expected,
+                                                 count, (float)rtol, (float)atol, equal_nan,
+                                                 scratch);
+  allclose_final_kernel<<<1, 256, 0, s>>>(scratch, blocks, result);
+  B200_CUDA_OK(cudaGetLastError());
+  unsigned long long host[2] = {0, 0};
+  cudaError_t err = cudaMemcpyAsync(host, result, sizeof host, cudaMemcpyDeviceToHost, s);
+  if (err == cudaSuccess) err = cudaStreamSynchronize(s);
+  if (err != cudaSuccess)
+    return fail(B200_SYNC, "allclose (static scratch): %s", cudaGetErrorString(err));
+  *bad_count = (int64_t)host[0];
+  double e;
+  memcpy(&e, &host[1], sizeof e);
+  *max_abs_err = e;
+  return B200_OK;
 }

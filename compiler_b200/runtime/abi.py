@@ -93,6 +93,8 @@ PROTOTYPES = {
     "b200_swiglu_fwd": (c_int, [_T, _T, _T, _PTR]),
     "b200_allclose_f32": (c_int, [_PTR, _PTR, c_int64, c_double, c_double, c_int,
                                   POINTER(c_int64), POINTER(c_double), _PTR]),
+    "b200_allclose_f32_static": (c_int, [_PTR, _PTR, c_int64, c_double, c_double, c_int,
+                                         POINTER(c_int64), POINTER(c_double), _PTR]),
     "b200_bitwise_equal": (c_int, [_PTR, _PTR, c_size_t, POINTER(c_int), _PTR]),
 }
 

@@ -181,6 +181,26 @@ int b200_allclose_f32(const void *actual, const void *expected, int64_t count,
                       double rtol, double atol, int equal_nan,
                       int64_t *bad_count, double *max_abs_err, void *stream);
 
+/* The same comparison as b200_allclose_f32 for callers that must not allocate device
+ * memory: code running while a stream capture is open, services whose memory pool owns the
+ * whole device, or latency-critical loops that cannot afford the device-wide
+ * synchronisation an allocation and a free imply.  (No counterpart in the reference: its
+ * device compare allocates three buffers per call, ops/harness/opslib/devices/cuda.py.)
+ * It calls no cudaMalloc / cudaFree and no allocating library routine.  Its scratch is a
+ * 128 KiB array built into the library image, present on every GPU that loads the
+ * library until the process exits; it covers at most 134,201,344 elements per call
+ * ((8192 - 1) blocks x 16384 elements) and a larger count is rejected with
+ * B200_REJECTED.  The first call on a device looks up the array's device address
+ * (cudaGetSymbolAddress, with that device current); make that first call before
+ * starting any stream capture.  All calls share the one array, which keeps the previous
+ * call's contents (each call overwrites every slot it later reads, so nothing has to be
+ * cleared); two calls that overlap on the GPU -- different streams, or several host
+ * threads -- race on it and must be serialised by the caller.  Results match
+ * b200_allclose_f32.  Synchronises `stream`. */
+int b200_allclose_f32_static(const void *actual, const void *expected, int64_t count,
+                             double rtol, double atol, int equal_nan,
+                             int64_t *bad_count, double *max_abs_err, void *stream);
+
 /* Runs `repeats` launches of an operator closure-free: restores `out` from
  * nothing, compares launch r>0 bitwise with launch 0 (the --repeats check of
  * a100c/runtime/main.c:117-152).  first/other: device buffers of `bytes`.
