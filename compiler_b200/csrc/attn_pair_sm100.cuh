@@ -178,6 +178,14 @@ __device__ __forceinline__ Item decode_item(int item, const Params &p) {
   return it;
 }
 
+// Work items are sorted heaviest first; round r of the persistent loop hands CTA c the
+// item r*G + c on even rounds and r*G + (G-1-c) on odd rounds, so the CTA that drew the
+// heaviest item of one round draws the lightest of the next and the totals even out.
+__device__ __forceinline__ int item_of_round(int round) {
+  const int g = (int)gridDim.x, c = (int)blockIdx.x;
+  return round * g + ((round & 1) ? g - 1 - c : c);
+}
+
 template <typename T, int D>
 __global__ void __launch_bounds__(THREADS, 1)
 attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q,
@@ -251,7 +259,7 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q,
       uint32_t kv_it = 0, item_n = 0;
       uint32_t issued = 0, parity = 0;  // bit s: K stage, bit 2+s: V stage, bit 4: Q
       bool ok = true;
-      for (int item = blockIdx.x; ok && item < num_items; item += gridDim.x, ++item_n) {
+      for (int round = 0, item; ok && (item = item_of_round(round)) < num_items; ++round, ++item_n) {
         const Item it = decode_item(item, p);
         if (!mbar_wait(q_empty, (item_n & 1u) ^ 1u, ctx, 1)) { ok = false; break; }
         mbar_arrive_expect_tx(q_full, 2 * L::TILE_BYTES);
@@ -343,7 +351,7 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q,
     auto commit = [&](uint32_t bar) {
       if (leader) tc_commit(bar);
     };
-    for (int item = blockIdx.x; ok && item < num_items; item += gridDim.x, ++item_n) {
+    for (int round = 0, item; ok && (item = item_of_round(round)) < num_items; ++round, ++item_n) {
       const Item it = decode_item(item, p);
       if (!wait_all(q_full, item_n & 1u, 4)) { ok = false; break; }
       {  // S(0) of both tiles
@@ -412,7 +420,7 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q,
       return __all_sync(0xffffffffu, mbar_wait(bar, parity, ctx, site)) != 0;
     };
     const float2 scale2 = make_float2(p.scale_log2, p.scale_log2);
-    for (int item = blockIdx.x; ok && item < num_items; item += gridDim.x) {
+    for (int round = 0, item; ok && (item = item_of_round(round)) < num_items; ++round) {
       const Item it = decode_item(item, p);
       const int nb = it.nb[t];
       if (nb == 0) continue;
@@ -424,32 +432,52 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q,
         if (!wait_all(s_full(t), blocks & 1u, 10)) { ok = false; break; }
         tc_fence_after_sync();
         float x[BLOCK_N];
-        {
-          uint32_t(&r)[BLOCK_N] = reinterpret_cast<uint32_t(&)[BLOCK_N]>(x);
-#pragma unroll
-          for (int c = 0; c < BLOCK_N / 32; ++c)
-            tmem_ld_32x32b_x32(s_tmem + c * 32, reinterpret_cast<uint32_t(&)[32]>(r[c * 32]));
-          tmem_ld_wait();
-        }
+        uint32_t(&xr)[BLOCK_N] = reinterpret_cast<uint32_t(&)[BLOCK_N]>(x);
+        // the row arrives in two halves; the max of the first half is taken while the
+        // second half is still on its way from tensor memory
+        tmem_ld_32x32b_x32(s_tmem, reinterpret_cast<uint32_t(&)[32]>(xr[0]));
+        tmem_ld_32x32b_x32(s_tmem + 32, reinterpret_cast<uint32_t(&)[32]>(xr[32]));
+        tmem_ld_wait();
+        tmem_ld_32x32b_x32(s_tmem + 64, reinterpret_cast<uint32_t(&)[32]>(xr[64]));
+        tmem_ld_32x32b_x32(s_tmem + 96, reinterpret_cast<uint32_t(&)[32]>(xr[96]));
         const int col0 = j * BLOCK_N;
         const bool diag = p.causal && (col0 + BLOCK_N - 1 > mt0);
         const bool ragged = col0 + BLOCK_N > p.N;
-        if (diag || ragged) {
-          const int limit = min(p.causal ? row : p.N - 1, p.N - 1);  // last kept column
+        const bool masked = diag || ragged;
+        const int limit = min(p.causal ? row : p.N - 1, p.N - 1) - col0;  // last kept column
+        float mx0, mx1, mx2, mx3;
+        {
+          if (masked) {
 #pragma unroll
-          for (int i = 0; i < BLOCK_N; ++i)
-            if (col0 + i > limit) x[i] = -INFINITY;
-        }
-        float mx0 = x[0], mx1 = x[1], mx2 = x[2], mx3 = x[3];
+            for (int i = 0; i < 64; ++i)
+              if (i > limit) x[i] = -INFINITY;
+          }
+          mx0 = x[0]; mx1 = x[1]; mx2 = x[2]; mx3 = x[3];
 #pragma unroll
-        for (int i = 4; i < BLOCK_N - 4; i += 8) {
-          mx0 = max3(mx0, x[i], x[i + 1]);
-          mx1 = max3(mx1, x[i + 2], x[i + 3]);
-          mx2 = max3(mx2, x[i + 4], x[i + 5]);
-          mx3 = max3(mx3, x[i + 6], x[i + 7]);
+          for (int i = 4; i < 60; i += 8) {
+            mx0 = max3(mx0, x[i], x[i + 1]);
+            mx1 = max3(mx1, x[i + 2], x[i + 3]);
+            mx2 = max3(mx2, x[i + 4], x[i + 5]);
+            mx3 = max3(mx3, x[i + 6], x[i + 7]);
+          }
+          mx0 = max3(mx0, x[60], x[61]);
+          mx1 = max3(mx1, x[62], x[63]);
         }
-        mx0 = max3(mx0, x[BLOCK_N - 4], x[BLOCK_N - 3]);
-        mx1 = max3(mx1, x[BLOCK_N - 2], x[BLOCK_N - 1]);
+        tmem_ld_wait();
+        {
+          if (masked) {
+#pragma unroll
+            for (int i = 64; i < BLOCK_N; ++i)
+              if (i > limit) x[i] = -INFINITY;
+          }
+#pragma unroll
+          for (int i = 64; i < BLOCK_N; i += 8) {
+            mx0 = max3(mx0, x[i], x[i + 1]);
+            mx1 = max3(mx1, x[i + 2], x[i + 3]);
+            mx2 = max3(mx2, x[i + 4], x[i + 5]);
+            mx3 = max3(mx3, x[i + 6], x[i + 7]);
+          }
+        }
         const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * p.scale_log2;
         // lazy rescale: the max used for exp2 is raised only when the true max
         // exceeds it by more than 2^kRescaleThreshold
