@@ -5,14 +5,13 @@
 // independent 128-row tiles in flight so the tensor core always has one tile's
 // MMAs to run while the other tile's rows are in their softmax:
 //
-//   warps 0-7   softmax + epilogue of tile 0: two threads per query row, one for keys
-//               [0,64) of each block (warps 0-3), one for keys [64,128) (warps 4-7)
-//   warps 8-15  the same for tile 1
-//   warp  16    TMA producer: Q (both tiles) per item, K / V blocks in 2-stage rings
+//   warps 0-3   softmax + epilogue of tile 0 (one query row per thread)
+//   warps 4-7   softmax + epilogue of tile 1
+//   warp  8     TMA producer: Q (both tiles) per item, K / V blocks in 2-stage rings
 //               shared by both tiles (K and V are read once per 256 rows)
-//   warps 18-19 idle (they complete the fifth warpgroup so that setmaxnreg can move
+//   warps 10-11 idle (they complete the third warpgroup so that setmaxnreg can move
 //               registers from it to the softmax warpgroups)
-//   warp  17    one lane issues tcgen05.mma in the order
+//   warp  9     one lane issues tcgen05.mma in the order
 //                 S0 = Q0 K(0)^T, S1 = Q1 K(0)^T, then per key block j:
 //                 O0 += P0(j) V(j), S0 = Q0 K(j+1)^T, O1 += P1(j) V(j), S1 = Q1 K(j+1)^T
 //
@@ -36,8 +35,7 @@ constexpr int TILE_M = 128;           // query rows per tile
 constexpr int CTA_M = 2 * TILE_M;     // query rows per work item
 constexpr int BLOCK_N = 128;          // keys per block
 constexpr int KV_STAGES = 2;
-constexpr int SOFTMAX_WARPS = 16;  // 2 tiles x 2 column halves x 4 warps
-constexpr int THREADS = (SOFTMAX_WARPS + 4) * 32;  // + {producer, issuer, 2 idle}
+constexpr int THREADS = 384;  // 3 warpgroups: softmax 0, softmax 1, {producer, issuer, 2 idle}
 constexpr int TMEM_COLS = 512;
 constexpr int S_COLS = 128;
 constexpr int O_COL0 = 2 * S_COLS;
@@ -61,10 +59,7 @@ template <int D> struct Smem {
   static constexpr int K_OFF = 2 * TILE_BYTES;
   static constexpr int V_OFF = K_OFF + KV_STAGES * TILE_BYTES;
   static constexpr int BAR_OFF = V_OFF + KV_STAGES * TILE_BYTES;
-  // after the barriers: the row-max / row-sum exchange between the two threads of a row,
-  // [parity][tile][half][128 rows] floats
-  static constexpr int XCHG_OFF = BAR_OFF + 256;
-  static constexpr int BYTES = XCHG_OFF + 2 * 2 * 2 * 128 * 4 + 1024;
+  static constexpr int BYTES = BAR_OFF + 256 + 1024;
 };
 
 __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap *tm, uint32_t bar,
@@ -237,30 +232,28 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q,
       mbar_init(p_full(t), TILE_M / 32);   // one arrival per softmax warp
       mbar_init(p2_full(t), TILE_M / 32);
       mbar_init(o_full(t), 1);
-      mbar_init(o_empty(t), 2 * TILE_M / 32);  // both column halves
+      mbar_init(o_empty(t), TILE_M / 32);
     }
     mbar_init(drain_bar, 1);
     *abort_flag = 0u;
     mbar_init_fence();
   }
-  if (warp == SOFTMAX_WARPS && lane == 0) {
+  if (warp == 8 && lane == 0) {
     tma_prefetch_desc(&tm_q);
     tma_prefetch_desc(&tm_k);
     tma_prefetch_desc(&tm_v);
   }
-  if (warp == SOFTMAX_WARPS + 1) tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
+  if (warp == 9) tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
 
   // Register budget: the softmax warpgroups hold a 128-wide fp32 row per thread, the
-  // producer / issuer warpgroup needs little; setmaxnreg moves the difference.  The pool is
-  // what the CTA was launched with (20 warps x 96 registers): 16 x 104 + 4 x 64 = 20 x 96.
-  // An increase beyond the pool would wait forever.
-  if (warp >= SOFTMAX_WARPS) {
-  asm volatile("setmaxnreg.dec.sync.aligned.u32 64;");
-  if (warp == SOFTMAX_WARPS) {
+  // producer / issuer warpgroup needs little; setmaxnreg moves the difference.
+  if (warp >= 8) {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
+  if (warp == 8) {
     // ---------------------------------------------------------------- producer
     if (lane == 0) {
       uint32_t kv_it = 0, item_n = 0;
@@ -307,7 +300,7 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q,
         }
       }
     }
-  } else if (warp == SOFTMAX_WARPS + 1) {
+  } else if (warp == 9) {
     // ---------------------------------------------------------------- MMA issuer
     // The whole warp runs this loop (uniform control flow keeps the descriptor
     // arithmetic cheap); one elected lane issues the MMAs and commits.
@@ -412,29 +405,14 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q,
     __syncwarp();
   }
   } else {
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 104;");
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
     // ---------------------------------------------------------------- softmax + epilogue
-    // Two threads share a query row: the thread of column half `hf` owns keys
-    // [64 hf, 64 hf + 64) of every block and columns [D/2 hf, D/2 hf + D/2) of O.  They
-    // agree on the row max through shared memory once per block (a named barrier over
-    // the 256 threads of the tile) and on the row sum once per item.
-    const int t = warp >> 3;            // tile
-    const int hf = (warp >> 2) & 1;     // column half
+    const int t = warp >> 2;                          // tile of this warpgroup
     const int row_in_tile = (warp & 3) * 32 + lane;   // == TMEM lane of this thread
     const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
-    const uint32_t s_tmem = tmem_base + lane_addr + (uint32_t)(t * S_COLS + hf * 64);
-    const uint32_t p_tmem = tmem_base + lane_addr + (uint32_t)(t * S_COLS + hf * 32);
-    const uint32_t o_tmem = tmem_base + lane_addr + (uint32_t)(O_COL0 + t * S_COLS + hf * (D / 2));
-    float *xchg = reinterpret_cast<float *>(smem_gen + L::XCHG_OFF);
-    auto slot = [&](uint32_t parity, int half) {
-      return xchg + ((parity * 2 + t) * 2 + half) * 128 + row_in_tile;
-    };
-    auto tile_sync = [&]() {  // the 256 threads of this tile
-      if (t == 0) asm volatile("bar.sync 1, 256;" ::: "memory");
-      else asm volatile("bar.sync 2, 256;" ::: "memory");
-    };
+    const uint32_t s_tmem = tmem_base + lane_addr + (uint32_t)(t * S_COLS);
+    const uint32_t o_tmem = tmem_base + lane_addr + (uint32_t)(O_COL0 + t * S_COLS);
     uint32_t blocks = 0;  // key blocks this tile has been through (barrier phases)
-    uint32_t xph = 0;     // exchange buffer parity
     bool ok = true;
     // warp-uniform wait: the vote keeps the warp converged for the .sync.aligned
     // tensor-memory accesses that follow
@@ -449,43 +427,58 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q,
       const int mt0 = it.m0 + t * TILE_M;
       const int row = mt0 + row_in_tile;
       float m_used = -INFINITY;  // running max in the scaled log2 domain
-      float l = 0.f;             // this thread's half of the row sum
+      float l = 0.f;
       for (int j = 0; j < nb; ++j, ++blocks) {
-        // a failed wait is CTA-wide (abort flag): every thread of the tile leaves here, so
-        // nobody is left waiting at the tile barrier below
         if (!wait_all(s_full(t), blocks & 1u, 10)) { ok = false; break; }
         tc_fence_after_sync();
-        float x[64];
-        uint32_t(&xr)[64] = reinterpret_cast<uint32_t(&)[64]>(x);
+        float x[BLOCK_N];
+        uint32_t(&xr)[BLOCK_N] = reinterpret_cast<uint32_t(&)[BLOCK_N]>(x);
+        // the row arrives in two halves; the max of the first half is taken while the
+        // second half is still on its way from tensor memory
         tmem_ld_32x32b_x32(s_tmem, reinterpret_cast<uint32_t(&)[32]>(xr[0]));
         tmem_ld_32x32b_x32(s_tmem + 32, reinterpret_cast<uint32_t(&)[32]>(xr[32]));
         tmem_ld_wait();
-        const int col0 = j * BLOCK_N + hf * 64;
-        const bool diag = p.causal && (j * BLOCK_N + BLOCK_N - 1 > mt0);
-        const bool ragged = j * BLOCK_N + BLOCK_N > p.N;
-        if (diag || ragged) {
-          const int limit = min(p.causal ? row : p.N - 1, p.N - 1) - col0;  // last kept column
+        tmem_ld_32x32b_x32(s_tmem + 64, reinterpret_cast<uint32_t(&)[32]>(xr[64]));
+        tmem_ld_32x32b_x32(s_tmem + 96, reinterpret_cast<uint32_t(&)[32]>(xr[96]));
+        const int col0 = j * BLOCK_N;
+        const bool diag = p.causal && (col0 + BLOCK_N - 1 > mt0);
+        const bool ragged = col0 + BLOCK_N > p.N;
+        const bool masked = diag || ragged;
+        const int limit = min(p.causal ? row : p.N - 1, p.N - 1) - col0;  // last kept column
+        float mx0, mx1, mx2, mx3;
+        {
+          if (masked) {
 #pragma unroll
-          for (int i = 0; i < 64; ++i)
-            if (i > limit) x[i] = -INFINITY;
-        }
-        float mx0 = x[0], mx1 = x[1], mx2 = x[2], mx3 = x[3];
+            for (int i = 0; i < 64; ++i)
+              if (i > limit) x[i] = -INFINITY;
+          }
+          mx0 = x[0]; mx1 = x[1]; mx2 = x[2]; mx3 = x[3];
 #pragma unroll
-        for (int i = 4; i < 60; i += 8) {
-          mx0 = max3(mx0, x[i], x[i + 1]);
-          mx1 = max3(mx1, x[i + 2], x[i + 3]);
-          mx2 = max3(mx2, x[i + 4], x[i + 5]);
-          mx3 = max3(mx3, x[i + 6], x[i + 7]);
+          for (int i = 4; i < 60; i += 8) {
+            mx0 = max3(mx0, x[i], x[i + 1]);
+            mx1 = max3(mx1, x[i + 2], x[i + 3]);
+            mx2 = max3(mx2, x[i + 4], x[i + 5]);
+            mx3 = max3(mx3, x[i + 6], x[i + 7]);
+          }
+          mx0 = max3(mx0, x[60], x[61]);
+          mx1 = max3(mx1, x[62], x[63]);
         }
-        mx0 = max3(mx0, x[60], x[61]);
-        mx1 = max3(mx1, x[62], x[63]);
-        float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
-        // agree on the row max with the thread that owns the other 64 keys.  The barrier
-        // also orders this thread's reads of S before the partner's write of P over them.
-        *slot(xph, hf) = mx;
-        tile_sync();
-        mx = fmaxf(mx, *slot(xph, hf ^ 1)) * p.scale_log2;
-        xph ^= 1u;
+        tmem_ld_wait();
+        {
+          if (masked) {
+#pragma unroll
+            for (int i = 64; i < BLOCK_N; ++i)
+              if (i > limit) x[i] = -INFINITY;
+          }
+#pragma unroll
+          for (int i = 64; i < BLOCK_N; i += 8) {
+            mx0 = max3(mx0, x[i], x[i + 1]);
+            mx1 = max3(mx1, x[i + 2], x[i + 3]);
+            mx2 = max3(mx2, x[i + 4], x[i + 5]);
+            mx3 = max3(mx3, x[i + 6], x[i + 7]);
+          }
+        }
+        const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * p.scale_log2;
         // lazy rescale: the max used for exp2 is raised only when the true max
         // exceeds it by more than 2^kRescaleThreshold
         float alpha = 1.0f;
@@ -503,7 +496,7 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q,
           if (!wait_all(o_full(t), (blocks - 1u) & 1u, 11)) { ok = false; break; }
           tc_fence_after_sync();
 #pragma unroll
-          for (int c = 0; c < D / 64; ++c) {
+          for (int c = 0; c < D / 32; ++c) {
             uint32_t r[32];
             tmem_ld_32x32b_x32(o_tmem + c * 32, r);
             tmem_ld_wait();
@@ -516,46 +509,45 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q,
         l *= alpha;
         const float2 negm2 = make_float2(-m_used, -m_used);
         float2 sum_a = make_float2(0.f, 0.f), sum_b = make_float2(0.f, 0.f);
-        // in every group of 8 keys one pair takes the polynomial exp2, three pairs the
-        // ex2 unit
-        uint32_t packed[32];
+        // P is handed over in two halves of 64 keys so that the first half of
+        // O += P V runs while the second half is still being exponentiated.  In every
+        // group of 8 keys one pair takes the polynomial exp2, three pairs the ex2 unit.
 #pragma unroll
-        for (int g = 0; g < 8; ++g) {
-          const int i = g * 8;
-          const float2 va = ffma2(make_float2(x[i], x[i + 1]), scale2, negm2);
-          const float2 vb = ffma2(make_float2(x[i + 2], x[i + 3]), scale2, negm2);
-          const float2 vc = ffma2(make_float2(x[i + 4], x[i + 5]), scale2, negm2);
-          const float2 vd = ffma2(make_float2(x[i + 6], x[i + 7]), scale2, negm2);
-          const float2 ea = make_float2(ex2(va.x), ex2(va.y));
-          const float2 eb = make_float2(ex2(vb.x), ex2(vb.y));
-          const float2 ec = make_float2(ex2(vc.x), ex2(vc.y));
-          const float2 ed = exp2_poly2(vd);
-          sum_a = fadd2(sum_a, fadd2(ea, ec));
-          sum_b = fadd2(sum_b, fadd2(eb, ed));
-          packed[g * 4] = pack2<T>(ea.x, ea.y);
-          packed[g * 4 + 1] = pack2<T>(eb.x, eb.y);
-          packed[g * 4 + 2] = pack2<T>(ec.x, ec.y);
-          packed[g * 4 + 3] = pack2<T>(ed.x, ed.y);
+        for (int half = 0; half < 2; ++half) {
+          uint32_t packed[32];
+#pragma unroll
+          for (int g = 0; g < 8; ++g) {
+            const int i = half * 64 + g * 8;
+            const float2 va = ffma2(make_float2(x[i], x[i + 1]), scale2, negm2);
+            const float2 vb = ffma2(make_float2(x[i + 2], x[i + 3]), scale2, negm2);
+            const float2 vc = ffma2(make_float2(x[i + 4], x[i + 5]), scale2, negm2);
+            const float2 vd = ffma2(make_float2(x[i + 6], x[i + 7]), scale2, negm2);
+            const float2 ea = make_float2(ex2(va.x), ex2(va.y));
+            const float2 eb = make_float2(ex2(vb.x), ex2(vb.y));
+            const float2 ec = make_float2(ex2(vc.x), ex2(vc.y));
+            const float2 ed = exp2_poly2(vd);
+            sum_a = fadd2(sum_a, fadd2(ea, ec));
+            sum_b = fadd2(sum_b, fadd2(eb, ed));
+            packed[g * 4] = pack2<T>(ea.x, ea.y);
+            packed[g * 4 + 1] = pack2<T>(eb.x, eb.y);
+            packed[g * 4 + 2] = pack2<T>(ec.x, ec.y);
+            packed[g * 4 + 3] = pack2<T>(ed.x, ed.y);
+          }
+          tmem_st_32x32b_x32(s_tmem + half * 32, packed);
+          tmem_st_wait();
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(half == 0 ? p_full(t) : p2_full(t));
         }
-        tmem_st_32x32b_x32(p_tmem, packed);
-        tmem_st_wait();
-        tc_fence_before_sync();
-        __syncwarp();
-        // keys [0,64) of the block are ready / keys [64,128) are ready
-        if (lane == 0) mbar_arrive(hf == 0 ? p_full(t) : p2_full(t));
         l += (sum_a.x + sum_a.y) + (sum_b.x + sum_b.y);
       }
       if (!ok) break;
       // ---- epilogue of this tile: O / l, LSE
-      *slot(xph, hf) = l;
-      tile_sync();
-      l += *slot(xph, hf ^ 1);
-      xph ^= 1u;
       if (!wait_all(o_full(t), (blocks - 1u) & 1u, 12)) { ok = false; break; }
       tc_fence_after_sync();
-      uint32_t acc[D / 2];
+      uint32_t acc[D];
 #pragma unroll
-      for (int c = 0; c < D / 64; ++c)
+      for (int c = 0; c < D / 32; ++c)
         tmem_ld_32x32b_x32(o_tmem + c * 32, reinterpret_cast<uint32_t(&)[32]>(acc[c * 32]));
       tmem_ld_wait();
       tc_fence_before_sync();
@@ -563,10 +555,9 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q,
       if (lane == 0) mbar_arrive(o_empty(t));  // O may be overwritten by the next item's first P V
       if (row < p.N) {
         const float inv_l = 1.0f / l;
-        T *orow = reinterpret_cast<T *>(p.o) + it.z * p.oz + it.h * p.oh + (int64_t)row * p.om +
-                  hf * (D / 2);
+        T *orow = reinterpret_cast<T *>(p.o) + it.z * p.oz + it.h * p.oh + (int64_t)row * p.om;
 #pragma unroll
-        for (int q = 0; q < D / 16; ++q) {
+        for (int q = 0; q < D / 8; ++q) {
           uint4 out;
           out.x = pack2<T>(__uint_as_float(acc[q * 8 + 0]) * inv_l, __uint_as_float(acc[q * 8 + 1]) * inv_l);
           out.y = pack2<T>(__uint_as_float(acc[q * 8 + 2]) * inv_l, __uint_as_float(acc[q * 8 + 3]) * inv_l);
@@ -574,7 +565,7 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q,
           out.w = pack2<T>(__uint_as_float(acc[q * 8 + 6]) * inv_l, __uint_as_float(acc[q * 8 + 7]) * inv_l);
           *reinterpret_cast<uint4 *>(orow + q * 8) = out;
         }
-        if (hf == 0 && p.lse != nullptr)
+        if (p.lse != nullptr)
           p.lse[(int64_t)it.zh * p.N + row] = m_used * 0.6931471805599453f + logf(l);
       }
     }
@@ -582,7 +573,7 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q,
 
   tc_fence_before_sync();
   __syncthreads();
-  if (warp == SOFTMAX_WARPS + 1) {
+  if (warp == 9) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, TMEM_COLS);
   }
