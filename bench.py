@@ -44,8 +44,13 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures summarised
 # under profiles/ (None until a capture exists for that kernel)
-NCU_TRAFFIC = {"softmax": None, "rmsnorm": None, "gemm_8192": None, "gemm_ragged": None,
-               "attention": None}
+NCU_TRAFFIC = {
+    "softmax": 140_785_000,        # profiles/softmax_rows_masked_fp16_16384x4000.md
+    "rmsnorm": 212_674_000,        # profiles/rmsnorm_rows_fp32_8192x4096.md
+    "gemm_8192": 1_134_959_000,    # profiles/gemm_tcgen05_bf16_8192x8192x8192.md
+    "gemm_ragged": 369_771_000,    # profiles/gemm_tcgen05_bf16_4097x11008x4096.md
+    "attention": 2_301_736_000,    # 4 x the [4,16,4096,128] capture, profiles/attn_fwd_pair_*.md
+}
 
 
 def load_peaks():
