@@ -42,14 +42,15 @@ RMS_ROWS, RMS_COLS = 8192, 4096
 RMS_BYTES = 2 * RMS_ROWS * RMS_COLS * 4 + RMS_COLS * 4 + RMS_ROWS * 4
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
-# dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures summarised
-# under profiles/ (None until a capture exists for that kernel)
+# dram__bytes_read.sum + dram__bytes_write.sum per launch, from one `ncu --set full` capture of
+# `python -m compiler_b200.profile_case <op> --shape ...` per kernel at the bench shape (attention:
+# captured at [4,16,4096,128] and scaled by 4, traffic is proportional to batch x heads)
 NCU_TRAFFIC = {
-    "softmax": 140_785_000,        # profiles/softmax_rows_masked_fp16_16384x4000.md
-    "rmsnorm": 212_674_000,        # profiles/rmsnorm_rows_fp32_8192x4096.md
-    "gemm_8192": 1_134_959_000,    # profiles/gemm_tcgen05_bf16_8192x8192x8192.md
-    "gemm_ragged": 369_771_000,    # profiles/gemm_tcgen05_bf16_4097x11008x4096.md
-    "attention": 2_301_736_000,    # 4 x the [4,16,4096,128] capture, profiles/attn_fwd_pair_*.md
+    "softmax": 140_785_000,
+    "rmsnorm": 212_674_000,
+    "gemm_8192": 1_134_959_000,
+    "gemm_ragged": 369_771_000,
+    "attention": 2_301_736_000,
 }
 
 
