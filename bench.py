@@ -329,10 +329,10 @@ def bench_attention(torch, ops, dist, steps, warmup, peaks, source):
     return out
 
 
-def bench_tp_mlp(torch, dist, steps, warmup, peaks, source):
+def bench_tp_mlp(torch, dist, steps, warmup, peaks, source, collective="nccl"):
     from compiler_b200 import tp_mlp
     mlp = tp_mlp.TensorParallelMLP.synthetic(hidden=4096, ffn=14336, rank=dist.rank,
-                                             world=dist.world, seed=34)
+                                             world=dist.world, seed=34, collective=collective)
     gen = torch.Generator(device="cuda").manual_seed(35)  # x is replicated: same seed on all ranks
     x = torch.randn((4096, 4096), generator=gen, device="cuda").to(torch.bfloat16)
     y = torch.empty((4096, 4096), device="cuda", dtype=torch.bfloat16)
@@ -344,6 +344,10 @@ def bench_tp_mlp(torch, dist, steps, warmup, peaks, source):
     flops = 3 * 2 * 4096 * 4096 * 14336
     out = roofline("tensor", flops // dist.world, launch_ms, peaks, source, None)
     out.update({"workload": f"tp_swiglu_mlp_bf16_tp{dist.world}", "scaling": "strong",
+                "collective": ("NCCL all-reduce per row chunk, overlapped with the next chunk's GEMM"
+                               if collective == "nccl" else
+                               "reduce-scatter by peer stores in the GEMM epilogue + sum and "
+                               "broadcast kernel"),
                 "ms_per_step": round(region_ms, 5),
                 "value": round(flops / (region_ms * 1e-3) / 1e12, 2), "unit": "TFLOP/s",
                 "allreduce_bytes_per_rank": 4096 * 4096 * 2,
@@ -458,6 +462,12 @@ def main():
                                               peaks, source)
     if want("tp_mlp") and dist.world > 1:
         extras["tp_mlp"] = bench_tp_mlp(torch, dist, extra_steps, 3, peaks, source)
+        if 4096 % (128 * dist.world) == 0:
+            try:
+                extras["tp_mlp_peer"] = bench_tp_mlp(torch, dist, extra_steps, 3, peaks, source,
+                                                     collective="peer")
+            except Exception as exc:  # noqa: BLE001 - symmetric memory may be unavailable
+                extras["tp_mlp_peer"] = {"unavailable": f"{type(exc).__name__}: {exc}"[:300]}
 
     baseline = cpu_baseline() if (dist.rank == 0 and dist.world == 1) else None
     if dist.rank == 0:

@@ -102,6 +102,43 @@ allclose_f32_kernel(const float *__restrict__ a, const float *__restrict__ b,
     atomicMax(maxerr_bits, (unsigned long long)__double_as_longlong(local_err));
 }
 
+// Second half of the tensor-parallel all-reduce: this rank owns `rows` rows of the result.
+// staging holds the `world` partial slices of those rows ([world, rows, cols], written
+// there by every rank's GEMM epilogue); each thread sums one 16-byte column group over
+// the slices in fp32, rounds once and stores the result into the owned rows of EVERY
+// rank's output (plain peer stores over NVLink for the other ranks).
+template <typename T>
+__global__ void __launch_bounds__(256)
+reduce_slices_broadcast_kernel(const T *__restrict__ staging, int world, int64_t rows, int cols,
+                               int64_t dst_row0, T *y0, T *y1, T *y2, T *y3, T *y4, T *y5, T *y6, T *y7) {
+  constexpr int N = vec16<T>::N;
+  T *const y_rank[8] = {y0, y1, y2, y3, y4, y5, y6, y7};
+  const int vec_per_row = cols / N;
+  const int64_t total = rows * vec_per_row;
+  const int64_t slice = rows * (int64_t)cols;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = i / vec_per_row;
+    const int64_t c = (i - r * vec_per_row) * N;
+    float acc[N];
+#pragma unroll
+    for (int j = 0; j < N; ++j) acc[j] = 0.f;
+    for (int w = 0; w < world; ++w) {
+      vec16<T> v;
+      v.raw = ld_stream16(staging + w * slice + r * cols + c);
+#pragma unroll
+      for (int j = 0; j < N; ++j) acc[j] += io<T>::load(v.e[j]);
+    }
+    vec16<T> out;
+#pragma unroll
+    for (int j = 0; j < N; ++j) out.e[j] = io<T>::store(acc[j]);
+    const int64_t off = (dst_row0 + r) * cols + c;
+#pragma unroll
+    for (int w = 0; w < 8; ++w)
+      if (w < world) *reinterpret_cast<uint4 *>(y_rank[w] + off) = out.raw;
+  }
+}
+
 // ---- allclose without any allocation ----------------------------------------------
 // Scratch for b200_allclose_f32_static: one (bad count, max-error bits) pair per block.
 // It lives in the library image, so every GPU that loads the library carries these
@@ -337,5 +374,43 @@ extern "C" int b200_allclose_f32_static(const void *actual, const void *expected
   double e;
   memcpy(&e, &host[1], sizeof e);
   *max_abs_err = e;
+  return B200_OK;
+}
+
+extern "C" int b200_reduce_slices_broadcast(const void *staging, uint32_t dtype, int world,
+                                            int64_t rows, int64_t cols, int64_t dst_row0,
+                                            void *const *y_rank, void *stream) {
+  using namespace b200;
+  if (staging == nullptr || y_rank == nullptr) return fail(B200_USAGE, "null argument");
+  B200_REQUIRE(world >= 1 && world <= 8, "world %d out of range", world);
+  B200_REQUIRE(dtype == B200_DTYPE_BFLOAT16 || dtype == B200_DTYPE_FLOAT16,
+               "partials are f16 or bf16");
+  B200_REQUIRE(rows >= 0 && cols > 0 && cols % 8 == 0 && cols < (1 << 30) && dst_row0 >= 0,
+               "rows / cols out of range (cols must be a multiple of 8)");
+  B200_REQUIRE((uintptr_t)staging % 16 == 0, "staging is not 16-byte aligned");
+  void *y[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+  for (int w = 0; w < world; ++w) {
+    B200_REQUIRE(y_rank[w] != nullptr && (uintptr_t)y_rank[w] % 16 == 0,
+                 "output pointer of rank %d is null or unaligned", w);
+    y[w] = y_rank[w];
+  }
+  if (rows == 0) return B200_OK;
+  const int64_t items = rows * (cols / 8);
+  int64_t blocks = (items + 255) / 256;
+  const int64_t cap = (int64_t)sm_count() * 8;
+  if (blocks > cap) blocks = cap;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (dtype == B200_DTYPE_BFLOAT16) {
+    using T = __nv_bfloat16;
+    reduce_slices_broadcast_kernel<T><<<(unsigned)blocks, 256, 0, s>>>(
+        (const T *)staging, world, rows, (int)cols, dst_row0, (T *)y[0], (T *)y[1],
+        (T *)y[2], (T *)y[3], (T *)y[4], (T *)y[5], (T *)y[6], (T *)y[7]);
+  } else {
+    using T = __half;
+    reduce_slices_broadcast_kernel<T><<<(unsigned)blocks, 256, 0, s>>>(
+        (const T *)staging, world, rows, (int)cols, dst_row0, (T *)y[0], (T *)y[1],
+        (T *)y[2], (T *)y[3], (T *)y[4], (T *)y[5], (T *)y[6], (T *)y[7]);
+  }
+  B200_CUDA_OK(cudaGetLastError());
   return B200_OK;
 }

@@ -19,7 +19,6 @@
 #include "sm100.cuh"
 
 #include <mutex>
-#include <stdlib.h>
 
 namespace b200 {
 
@@ -98,6 +97,13 @@ struct Params {
   int vector_store;  // rows of C are 16-byte aligned and N % 8 == 0 (N % 4 for f32)
   unsigned int *status;
   uint32_t b_lbo, b_sbo;  // B-operand descriptor pitches (bytes)
+  // Row scatter for the tensor-parallel MLP: when scatter_rows > 0 the row block
+  // [k * scatter_rows, (k+1) * scatter_rows) of C is not written to `c` but to slot
+  // `scatter_slot` of c_rank[k] -- the memory of the rank that owns those rows (a peer
+  // GPU's buffer mapped into this process, or this GPU's own for k == this rank).
+  void *c_rank[8];
+  int scatter_rows;
+  int scatter_slot;
 };
 
 __device__ __forceinline__ float gelu_tanh_fast(float z) {
@@ -416,6 +422,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
       const bool row_ok = row < p.M;
       const uint32_t t_row = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(acc * BN);
       OutT *crow = c + (int64_t)row * p.ldc;
+      if (p.scatter_rows > 0) {
+        // a tile never straddles two owners: scatter_rows is a multiple of the tile height
+        const int owner = (mb * BM) / p.scatter_rows;
+        const int local = row - owner * p.scatter_rows;
+        crow = reinterpret_cast<OutT *>(p.c_rank[owner]) +
+               ((int64_t)p.scatter_slot * p.scatter_rows + local) * p.ldc;
+      }
       const int col_base = nb * TILE_N;
       if constexpr (DUAL) {
         epilogue_tile_dual<OutT>(t_row, p, crow, col_base, row_ok);
@@ -552,9 +565,19 @@ static int launch_tc(const CUtensorMap &ta, const CUtensorMap &tb, const CUtenso
 }  // namespace gemm
 }  // namespace b200
 
-extern "C" int b200_gemm_bias_act(const b200_tensor *a, const b200_tensor *b,
-                                  const b200_tensor *b2, const b200_tensor *bias,
-                                  b200_tensor *c, int act, void *stream) {
+namespace b200 {
+namespace gemm {
+struct Scatter {
+  void *const *c_rank;  // device pointers, one per rank
+  int world, slot;
+  int64_t rows;         // rows of C owned by each rank
+};
+}  // namespace gemm
+}  // namespace b200
+
+static int gemm_impl(const b200_tensor *a, const b200_tensor *b, const b200_tensor *b2,
+                     const b200_tensor *bias, b200_tensor *c, int act, void *stream,
+                     const b200::gemm::Scatter *scatter) {
   using namespace b200;
   using namespace b200::gemm;
   int st;
@@ -602,6 +625,21 @@ extern "C" int b200_gemm_bias_act(const b200_tensor *a, const b200_tensor *b,
       K > 0 && a->dtype != B200_DTYPE_FLOAT32 && (a->stride[0] * es) % 16 == 0 &&
       (b->stride[0] * es) % 16 == 0 && (uintptr_t)a->data % 16 == 0 &&
       (uintptr_t)b->data % 16 == 0 && (b2 == nullptr || (uintptr_t)b2->data % 16 == 0);
+  if (scatter != nullptr) {
+    B200_REQUIRE(tensor_core, "the row-scatter epilogue exists only on the tensor-core path "
+                              "(16-bit operands, 16-byte aligned row pitches)");
+    B200_REQUIRE(scatter->world >= 1 && scatter->world <= 8 && scatter->slot >= 0 &&
+                 scatter->slot < scatter->world, "world %d / slot %d out of range",
+                 scatter->world, scatter->slot);
+    B200_REQUIRE(scatter->rows > 0 && scatter->rows % BM == 0 &&
+                 scatter->rows * scatter->world >= M,
+                 "rows per rank (%lld) must be a multiple of %d and cover M", 
+                 (long long)scatter->rows, BM);
+    B200_REQUIRE(c->stride[0] == N, "scattered C slots are contiguous [rows, N]");
+    for (int r = 0; r < scatter->world; ++r)
+      B200_REQUIRE(scatter->c_rank[r] != nullptr && (uintptr_t)scatter->c_rank[r] % 16 == 0,
+                   "destination pointer of rank %d is null or unaligned", r);
+  }
   if (!tensor_core) {
     if (a->dtype == B200_DTYPE_FLOAT32) return launch_simt<float, float>(a, b, b2, bias, c, act, s);
     if (a->dtype == B200_DTYPE_FLOAT16) {
@@ -645,9 +683,13 @@ extern "C" int b200_gemm_bias_act(const b200_tensor *a, const b200_tensor *b,
   if (p.status == nullptr) return fail(B200_RESOURCE, "no status word on this device");
   p.b_lbo = B_BOX_BYTES;  // pitch between 64-column chunks of the B tile
   p.b_sbo = 1024;         // pitch between groups of 8 K-rows
-  if (const char *e = getenv("B200OPS_GEMM_BDESC")) {  // bring-up override: "lbo,sbo"
-    unsigned lbo = 0, sbo = 0;
-    if (sscanf(e, "%u,%u", &lbo, &sbo) == 2) { p.b_lbo = lbo; p.b_sbo = sbo; }
+  p.scatter_rows = 0;
+  p.scatter_slot = 0;
+  for (int r = 0; r < 8; ++r) p.c_rank[r] = nullptr;
+  if (scatter != nullptr) {
+    p.scatter_rows = (int)scatter->rows;
+    p.scatter_slot = scatter->slot;
+    for (int r = 0; r < scatter->world; ++r) p.c_rank[r] = scatter->c_rank[r];
   }
 
   const bool dual = act == B200_ACT_SWIGLU;
@@ -657,4 +699,21 @@ extern "C" int b200_gemm_bias_act(const b200_tensor *a, const b200_tensor *b,
     return dual ? launch_tc<__half, true>(ta, tb, tb2, p, s) : launch_tc<__half, false>(ta, tb, tb2, p, s);
   return dual ? launch_tc<__nv_bfloat16, true>(ta, tb, tb2, p, s)
               : launch_tc<__nv_bfloat16, false>(ta, tb, tb2, p, s);
+}
+
+extern "C" int b200_gemm_bias_act(const b200_tensor *a, const b200_tensor *b,
+                                  const b200_tensor *b2, const b200_tensor *bias,
+                                  b200_tensor *c, int act, void *stream) {
+  return gemm_impl(a, b, b2, bias, c, act, stream, nullptr);
+}
+
+extern "C" int b200_gemm_scatter_rows(const b200_tensor *a, const b200_tensor *b,
+                                      const b200_tensor *c_like, void *const *c_rank, int world,
+                                      int slot, int64_t rows_per_rank, void *stream) {
+  using namespace b200;
+  if (c_rank == nullptr || c_like == nullptr) return fail(B200_USAGE, "null argument");
+  b200_tensor c = *c_like;
+  if (world >= 1 && world <= 8 && slot >= 0 && slot < world) c.data = c_rank[slot];
+  const gemm::Scatter scatter{c_rank, world, slot, rows_per_rank};
+  return gemm_impl(a, b, nullptr, nullptr, &c, B200_ACT_NONE, stream, &scatter);
 }

@@ -89,6 +89,9 @@ PROTOTYPES = {
     "b200_rmsnorm_fwd": (c_int, [_T, _T, _T, _T, c_float, _PTR]),
     "b200_softmax_fwd": (c_int, [_T, _T, c_int, c_int64, _PTR]),
     "b200_gemm_bias_act": (c_int, [_T, _T, _T, _T, _T, c_int, _PTR]),
+    "b200_gemm_scatter_rows": (c_int, [_T, _T, _T, POINTER(_PTR), c_int, c_int, c_int64, _PTR]),
+    "b200_reduce_slices_broadcast": (c_int, [_PTR, c_uint32, c_int, c_int64, c_int64, c_int64,
+                                             POINTER(_PTR), _PTR]),
     "b200_attn_fwd": (c_int, [_T, _T, _T, _T, _T, c_float, c_int, _PTR]),
     "b200_swiglu_fwd": (c_int, [_T, _T, _T, _PTR]),
     "b200_allclose_f32": (c_int, [_PTR, _PTR, c_int64, c_double, c_double, c_int,

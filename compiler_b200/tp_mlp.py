@@ -14,6 +14,19 @@ are GPUs, one process each:
 
 torch supplies device memory, streams and the process group; the arithmetic is the
 library's own kernels.
+
+Two ways to sum the partials:
+
+  * ``collective="nccl"``: NCCL all-reduce per row chunk, overlapped with the next chunk's
+    GEMM (the baseline);
+  * ``collective="peer"``: the down-projection GEMM's epilogue stores every finished tile
+    straight into the memory of the rank that owns those rows (``b200_gemm_scatter_rows``,
+    plain peer stores through NVSwitch), so the reduce-scatter half of the all-reduce moves
+    while the tensor cores are still busy; after a cross-rank barrier each rank sums its
+    ``world`` staged slices and stores the result into every rank's output
+    (``b200_reduce_slices_broadcast``), and a second barrier publishes it.  Buffers come from
+    ``torch.distributed._symmetric_memory``; only its barrier is used, the data moves in this
+    library's kernels.  Needs M to be a multiple of 128 * world.
 """
 from __future__ import annotations
 
@@ -24,7 +37,7 @@ from compiler_b200.runtime import abi
 class TensorParallelMLP:
     kernels_per_forward = None  # set in __init__: 1 fused up-projection + one GEMM per chunk
 
-    def __init__(self, wg, wu, wd, *, group=None, chunks: int = 4):
+    def __init__(self, wg, wu, wd, *, group=None, chunks: int = 4, collective: str = "nccl"):
         """wg, wu: this rank's [hidden, ffn/tp] column shards; wd: its [ffn/tp, hidden] row
         shard (CUDA bf16/fp16 torch tensors, contiguous)."""
         import torch
@@ -32,11 +45,15 @@ class TensorParallelMLP:
         self.wg, self.wu, self.wd = wg, wu, wd
         self.group = group
         self.chunks = max(1, int(chunks))
-        self.kernels_per_forward = 1 + self.chunks
+        if collective not in ("nccl", "peer"):
+            raise ValueError("collective must be 'nccl' or 'peer'")
+        self.collective = collective
+        self.kernels_per_forward = 1 + self.chunks if collective == "nccl" else 3
         self._h = None
+        self._peer = None  # (rows, staging, staging handle, y, y handle)
 
     @classmethod
-    def synthetic(cls, hidden, ffn, rank, world, seed=0, dtype=None, chunks=4):
+    def synthetic(cls, hidden, ffn, rank, world, seed=0, dtype=None, chunks=4, collective="nccl"):
         """Random-normal(0, 0.02) weights; every rank draws only its own shard, from a
         generator seeded by (seed, rank)."""
         import torch
@@ -45,7 +62,7 @@ class TensorParallelMLP:
         gen = torch.Generator(device="cuda").manual_seed(seed * 1000 + rank)
         make = lambda *s: (torch.randn(s, generator=gen, device="cuda") * 0.02).to(dtype)  # noqa: E731
         return cls(make(hidden, hi - lo), make(hidden, hi - lo), make(hi - lo, hidden),
-                   chunks=chunks)
+                   chunks=chunks, collective=collective)
 
     def forward(self, x, y):
         """x: [M, hidden] replicated; y: [M, hidden] receives the all-reduced result."""
@@ -57,6 +74,8 @@ class TensorParallelMLP:
             self._h = torch.empty((m, cols), device=x.device, dtype=x.dtype)
         stream = torch.cuda.current_stream().cuda_stream
         ops.gemm(x, self.wg, self._h, b2=self.wu, act=abi.ACT_SWIGLU, stream=stream)
+        if self.collective == "peer":
+            return self._forward_peer(y, stream)
         pending = []
         distributed = dist.is_available() and dist.is_initialized() and dist.get_world_size(
             self.group) > 1
@@ -67,3 +86,51 @@ class TensorParallelMLP:
         for work in pending:
             work.wait()
         return y
+
+    # ------------------------------------------------------------------ peer path
+    def _peer_buffers(self, m, hidden, dtype, device):
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm_mem
+        world = dist.get_world_size(self.group)
+        if m % (128 * world):
+            raise ValueError(f"collective='peer' needs M ({m}) to be a multiple of {128 * world}")
+        if self._peer is None or self._peer[0] != (m, hidden, dtype):
+            group = self.group if self.group is not None else dist.group.WORLD
+            rows = m // world
+            staging = symm_mem.empty((world, rows, hidden), dtype=dtype, device=device)
+            staging_h = symm_mem.rendezvous(staging, group=group)
+            out = symm_mem.empty((m, hidden), dtype=dtype, device=device)
+            out_h = symm_mem.rendezvous(out, group=group)
+            self._peer = ((m, hidden, dtype), rows, staging, staging_h, out, out_h)
+        return self._peer[1:]
+
+    def _forward_peer(self, y, stream):
+        """Down-projection with the reduce-scatter in its epilogue, then sum + broadcast."""
+        import ctypes
+
+        import torch.distributed as dist
+        m, hidden = self._h.shape[0], self.wd.shape[1]
+        rows, staging, staging_h, out, out_h = self._peer_buffers(m, hidden, self._h.dtype,
+                                                                   self._h.device)
+        world, rank = dist.get_world_size(self.group), dist.get_rank(self.group)
+        lib = abi.lib()
+        pointer_array = ctypes.c_void_p * world
+        staging_ptrs = pointer_array(*[int(p) for p in staging_h.buffer_ptrs])
+        out_ptrs = pointer_array(*[int(p) for p in out_h.buffer_ptrs])
+        hd = abi.make_tensor(self._h.data_ptr(), self._h.shape, self._h.dtype,
+                             tuple(self._h.stride()))
+        wd = abi.make_tensor(self.wd.data_ptr(), self.wd.shape, self.wd.dtype,
+                             tuple(self.wd.stride()))
+        c_like = abi.make_tensor(out.data_ptr(), (m, hidden), out.dtype)
+        abi.check(lib.b200_gemm_scatter_rows(ctypes.byref(hd), ctypes.byref(wd),
+                                             ctypes.byref(c_like), staging_ptrs, world, rank,
+                                             rows, stream))
+        staging_h.barrier(channel=0)  # every rank's tiles for my rows have landed
+        abi.check(lib.b200_reduce_slices_broadcast(
+            staging.data_ptr(), abi.DTYPE_CODES[abi.dtype_name(out.dtype)], world, rows, hidden,
+            rank * rows, out_ptrs, stream))
+        out_h.barrier(channel=1)      # every rank's slice is in my output
+        if y is not None and y.data_ptr() != out.data_ptr():
+            y.copy_(out)
+            return y
+        return out

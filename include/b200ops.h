@@ -168,6 +168,28 @@ int b200_attn_fwd(const b200_tensor *q, const b200_tensor *k,
                   const b200_tensor *v, b200_tensor *o, b200_tensor *lse,
                   float scale, int causal, void *stream);
 
+/* C = A @ B with the rows of C scattered to their owners: rows [k*rows_per_rank,
+ * (k+1)*rows_per_rank) go to slot `slot` of c_rank[k], a buffer laid out
+ * [world, rows_per_rank, N] in rank k's memory (a peer GPU's buffer mapped into this
+ * process for k != slot).  The tensor-core GEMM's epilogue stores each finished tile
+ * straight to its owner, so the reduce-scatter traffic of a row-sharded GEMM crosses
+ * NVLink while the remaining tiles are still being computed.  c_like supplies dtype and
+ * shape [M,N] (contiguous); its data pointer is ignored.  rows_per_rank must be a multiple
+ * of 128.  The merge of per-worker partials in the reference is a100c/plan/stages.py:278-316;
+ * it has no multi-device counterpart. */
+int b200_gemm_scatter_rows(const b200_tensor *a, const b200_tensor *b,
+                           const b200_tensor *c_like, void *const *c_rank, int world,
+                           int slot, int64_t rows_per_rank, void *stream);
+
+/* Sums the `world` slices of staging ([world, rows, cols], f16/bf16, fp32 accumulation,
+ * one rounding) and stores the result into rows [dst_row0, dst_row0 + rows) of every
+ * y_rank[k] (contiguous [*, cols]; peer memory for k != this rank).  Together with
+ * b200_gemm_scatter_rows this is the all-reduce of the tensor-parallel MLP; the caller
+ * separates the two with a cross-rank barrier. */
+int b200_reduce_slices_broadcast(const void *staging, uint32_t dtype, int world,
+                                 int64_t rows, int64_t cols, int64_t dst_row0,
+                                 void *const *y_rank, void *stream);
+
 /* out = x * sigmoid(x) * y elementwise.  Replaces swiglu_fwd_kernel
  * (ops/suite/perf/swiglu_fwd.py:18-36).  [rows, cols], unit column stride. */
 int b200_swiglu_fwd(const b200_tensor *x, const b200_tensor *y,

@@ -46,6 +46,19 @@ ops.device_status(torch.cuda.current_stream().cuda_stream)
 ref = oracle.swiglu_mlp_ref(x, wg, wu, wd)
 oracle.compare(y.float().cpu().numpy().astype(np.float64), ref, 2e-2, 2e-2, name="tp mlp")
 
+# the same MLP with the reduce-scatter fused into the down-projection's epilogue (peer stores)
+mp = 256 * world
+xp = oracle.bf16_round(rng.standard_normal((mp, hidden)).astype(np.float32))
+peer = tp_mlp.TensorParallelMLP(bf16(wg[:, lo:hi]).contiguous(), bf16(wu[:, lo:hi]).contiguous(),
+                                bf16(wd[lo:hi]).contiguous(), collective="peer")
+yp = torch.empty((mp, hidden), device="cuda", dtype=torch.bfloat16)
+for _ in range(3):
+    peer.forward(bf16(xp), yp)
+torch.cuda.synchronize()
+ops.device_status(torch.cuda.current_stream().cuda_stream)
+oracle.compare(yp.float().cpu().numpy().astype(np.float64), oracle.swiglu_mlp_ref(xp, wg, wu, wd),
+               2e-2, 2e-2, name="tp mlp (peer)")
+
 rows, cols = 64, 4000                                # row shards of one masked softmax
 xs = (rng.standard_normal((rows * world, cols)) * 2).astype(np.float16)
 rlo, rhi = shard.block_range(rows * world, rank, world)
