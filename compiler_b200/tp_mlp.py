@@ -17,8 +17,8 @@ library's own kernels.
 
 Two ways to sum the partials:
 
-  * ``collective="nccl"``: NCCL all-reduce per row chunk, overlapped with the next chunk's
-    GEMM (the baseline);
+  * ``collective="nccl"``: fp32 partials, NCCL all-reduce per row chunk overlapped with the
+    next chunk's GEMM, one rounding at the end (the baseline);
   * ``collective="peer"``: the down-projection GEMM's epilogue stores every finished tile
     straight into the memory of the rank that owns those rows (``b200_gemm_scatter_rows``,
     plain peer stores through NVSwitch), so the reduce-scatter half of the all-reduce moves
@@ -26,7 +26,8 @@ Two ways to sum the partials:
     ``world`` staged slices and stores the result into every rank's output
     (``b200_reduce_slices_broadcast``), and a second barrier publishes it.  Buffers come from
     ``torch.distributed._symmetric_memory``; only its barrier is used, the data moves in this
-    library's kernels.  Needs M to be a multiple of 128 * world.
+    library's kernels.  The staged partials are 16-bit, their sum is taken in fp32 (every
+    partial is rounded once, the running sum never).  Needs M to be a multiple of 128 * world.
 """
 from __future__ import annotations
 
@@ -50,6 +51,7 @@ class TensorParallelMLP:
         self.collective = collective
         self.kernels_per_forward = 1 + self.chunks if collective == "nccl" else 3
         self._h = None
+        self._partial = None
         self._peer = None  # (rows, staging, staging handle, y, y handle)
 
     @classmethod
@@ -76,15 +78,23 @@ class TensorParallelMLP:
         ops.gemm(x, self.wg, self._h, b2=self.wu, act=abi.ACT_SWIGLU, stream=stream)
         if self.collective == "peer":
             return self._forward_peer(y, stream)
-        pending = []
         distributed = dist.is_available() and dist.is_initialized() and dist.get_world_size(
             self.group) > 1
+        if not distributed:
+            ops.gemm(self._h, self.wd, y, stream=stream)
+            return y
+        # fp32 partials: a 16-bit ring all-reduce rounds the running sum at every hop, which
+        # at 4 ranks already exceeds the 2e-2 tolerance against the unsharded result
+        if self._partial is None or self._partial.shape != y.shape:
+            self._partial = torch.empty(y.shape, device=y.device, dtype=torch.float32)
+        pending = []
         for lo, hi in shard.row_chunks(m, self.chunks):
-            ops.gemm(self._h[lo:hi], self.wd, y[lo:hi], stream=stream)
-            if distributed:
-                pending.append(dist.all_reduce(y[lo:hi], group=self.group, async_op=True))
-        for work in pending:
+            ops.gemm(self._h[lo:hi], self.wd, self._partial[lo:hi], stream=stream)
+            pending.append((lo, hi, dist.all_reduce(self._partial[lo:hi], group=self.group,
+                                                    async_op=True)))
+        for lo, hi, work in pending:
             work.wait()
+            y[lo:hi].copy_(self._partial[lo:hi])  # one rounding to the storage type
         return y
 
     # ------------------------------------------------------------------ peer path

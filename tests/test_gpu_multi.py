@@ -12,7 +12,7 @@ pytestmark = pytest.mark.gpu
 ROOT = Path(__file__).resolve().parent.parent
 
 WORKER = r'''
-import os, sys
+import os, sys, traceback
 import numpy as np
 import torch
 import torch.distributed as dist
@@ -22,6 +22,10 @@ from compiler_b200.runtime import abi
 from oracle import oracle
 
 rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+def _report(kind, value, tb):
+    sys.stderr.write(f"[rank {rank}] " + "".join(traceback.format_exception(kind, value, tb))[-1500:] + "\n")
+    sys.stderr.flush()
+sys.excepthook = _report
 torch.cuda.set_device(rank)
 abi.check(abi.lib().b200_set_device(rank))
 dist.init_process_group("nccl", device_id=torch.device("cuda", rank))
@@ -93,5 +97,6 @@ def test_tp_mlp_and_row_shards(world, tmp_path):
         [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
          "--master-addr", "127.0.0.1", "--master-port", str(29500 + world), str(script)],
         capture_output=True, text=True, env=env, timeout=540)
-    assert result.returncode == 0, result.stdout[-3000:] + result.stderr[-3000:]
+    failures = "\n".join(line for line in result.stderr.splitlines() if line.startswith("[rank"))
+    assert result.returncode == 0, failures[-4000:] + result.stdout[-1500:] + result.stderr[-1500:]
     assert result.stdout.count(" ok") == world
