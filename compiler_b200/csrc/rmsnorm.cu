@@ -16,7 +16,7 @@ template <typename T, int G, int VPT>
 __global__ void __launch_bounds__((G > kRowThreads ? G : kRowThreads))
 rmsnorm_rows_kernel(const T *__restrict__ x, int64_t x_stride,
                     const T *__restrict__ w, T *__restrict__ y, int64_t y_stride,
-                    T *__restrict__ rinv, int64_t rows, int cols, float eps) {
+                    T *__restrict__ rinv, int64_t rows, int cols, float eps, float gamma_offset) {
   constexpr int kThreads = G > kRowThreads ? G : kRowThreads;
   constexpr int kRowsPerCta = kThreads / G;
   constexpr int N = vec16<T>::N;
@@ -55,7 +55,7 @@ rmsnorm_rows_kernel(const T *__restrict__ x, int64_t x_stride,
       wv.raw = *reinterpret_cast<const uint4 *>(w + (int64_t)v * N);
 #pragma unroll
       for (int j = 0; j < N; ++j)
-        out.e[j] = io<T>::store(io<T>::load(xv[i].e[j]) * inv * io<T>::load(wv.e[j]));
+        out.e[j] = io<T>::store(io<T>::load(xv[i].e[j]) * inv * (io<T>::load(wv.e[j]) + gamma_offset));
       st_stream16(yrow + (int64_t)v * N, out.raw);
     }
   }
@@ -68,7 +68,7 @@ __global__ void __launch_bounds__(kRowThreads)
 rmsnorm_loop_kernel(const T *__restrict__ x, int64_t x_stride,
                     const T *__restrict__ w, int64_t w_stride,
                     T *__restrict__ y, int64_t y_stride, T *__restrict__ rinv,
-                    int64_t rinv_stride, int cols, float eps) {
+                    int64_t rinv_stride, int cols, float eps, float gamma_offset) {
   __shared__ float scratch[2 * (kRowThreads / 32)];
   const int64_t row = blockIdx.x;
   const T *xrow = x + row * x_stride;
@@ -82,24 +82,24 @@ rmsnorm_loop_kernel(const T *__restrict__ x, int64_t x_stride,
   if (threadIdx.x == 0 && rinv != nullptr) rinv[row * rinv_stride] = io<T>::store(inv);
   T *yrow = y + row * y_stride;
   for (int c = threadIdx.x; c < cols; c += kRowThreads)
-    yrow[c] = io<T>::store(io<T>::load(xrow[c]) * inv * io<T>::load(w[c * w_stride]));
+    yrow[c] = io<T>::store(io<T>::load(xrow[c]) * inv * (io<T>::load(w[c * w_stride]) + gamma_offset));
 }
 
 template <typename T, int G, int VPT>
 static void launch_rows(const b200_tensor *x, const b200_tensor *w, b200_tensor *y,
-                        b200_tensor *rinv, float eps, cudaStream_t stream) {
+                        b200_tensor *rinv, float eps, float gamma_offset, cudaStream_t stream) {
   constexpr int kThreads = G > kRowThreads ? G : kRowThreads;
   constexpr int kRowsPerCta = kThreads / G;
   const int64_t rows = x->shape[0];
   const unsigned grid = (unsigned)((rows + kRowsPerCta - 1) / kRowsPerCta);
   rmsnorm_rows_kernel<T, G, VPT><<<grid, kThreads, 0, stream>>>(
       (const T *)x->data, x->stride[0], (const T *)w->data, (T *)y->data,
-      y->stride[0], rinv ? (T *)rinv->data : nullptr, rows, (int)x->shape[1], eps);
+      y->stride[0], rinv ? (T *)rinv->data : nullptr, rows, (int)x->shape[1], eps, gamma_offset);
 }
 
 template <typename T>
 static int dispatch(const b200_tensor *x, const b200_tensor *w, b200_tensor *y,
-                    b200_tensor *rinv, float eps, cudaStream_t stream) {
+                    b200_tensor *rinv, float eps, float gamma_offset, cudaStream_t stream) {
   constexpr int N = vec16<T>::N;
   constexpr int VPT = 4;
   const int64_t rows = x->shape[0], cols = x->shape[1];
@@ -110,19 +110,19 @@ static int dispatch(const b200_tensor *x, const b200_tensor *w, b200_tensor *y,
       w->stride[0] == 1 && (rinv == nullptr || rinv->stride[0] == 1);
   const int g = aligned ? pick_group(cols / N, VPT) : 0;
   switch (g) {
-    case 8: launch_rows<T, 8, VPT>(x, w, y, rinv, eps, stream); break;
-    case 16: launch_rows<T, 16, VPT>(x, w, y, rinv, eps, stream); break;
-    case 32: launch_rows<T, 32, VPT>(x, w, y, rinv, eps, stream); break;
-    case 64: launch_rows<T, 64, VPT>(x, w, y, rinv, eps, stream); break;
-    case 128: launch_rows<T, 128, VPT>(x, w, y, rinv, eps, stream); break;
-    case 256: launch_rows<T, 256, VPT>(x, w, y, rinv, eps, stream); break;
-    case 512: launch_rows<T, 512, VPT>(x, w, y, rinv, eps, stream); break;
-    case 1024: launch_rows<T, 1024, VPT>(x, w, y, rinv, eps, stream); break;
+    case 8: launch_rows<T, 8, VPT>(x, w, y, rinv, eps, gamma_offset, stream); break;
+    case 16: launch_rows<T, 16, VPT>(x, w, y, rinv, eps, gamma_offset, stream); break;
+    case 32: launch_rows<T, 32, VPT>(x, w, y, rinv, eps, gamma_offset, stream); break;
+    case 64: launch_rows<T, 64, VPT>(x, w, y, rinv, eps, gamma_offset, stream); break;
+    case 128: launch_rows<T, 128, VPT>(x, w, y, rinv, eps, gamma_offset, stream); break;
+    case 256: launch_rows<T, 256, VPT>(x, w, y, rinv, eps, gamma_offset, stream); break;
+    case 512: launch_rows<T, 512, VPT>(x, w, y, rinv, eps, gamma_offset, stream); break;
+    case 1024: launch_rows<T, 1024, VPT>(x, w, y, rinv, eps, gamma_offset, stream); break;
     default:
       rmsnorm_loop_kernel<T><<<(unsigned)rows, kRowThreads, 0, stream>>>(
           (const T *)x->data, x->stride[0], (const T *)w->data, w->stride[0],
           (T *)y->data, y->stride[0], rinv ? (T *)rinv->data : nullptr,
-          rinv ? rinv->stride[0] : 0, (int)cols, eps);
+          rinv ? rinv->stride[0] : 0, (int)cols, eps, gamma_offset);
   }
   B200_CUDA_OK(cudaGetLastError());
   return B200_OK;
@@ -130,9 +130,9 @@ static int dispatch(const b200_tensor *x, const b200_tensor *w, b200_tensor *y,
 
 }  // namespace b200
 
-extern "C" int b200_rmsnorm_fwd(const b200_tensor *x, const b200_tensor *w,
-                                b200_tensor *y, b200_tensor *rinv, float eps,
-                                void *stream) {
+extern "C" int b200_rmsnorm_fwd_ex(const b200_tensor *x, const b200_tensor *w,
+                                   b200_tensor *y, b200_tensor *rinv, float eps,
+                                   float gamma_offset, void *stream) {
   using namespace b200;
   int st;
   if ((st = check_tensor(x, "x", 2)) || (st = check_tensor(w, "w", 1)) ||
@@ -153,11 +153,18 @@ extern "C" int b200_rmsnorm_fwd(const b200_tensor *x, const b200_tensor *w,
   B200_REQUIRE(cols > 0 && cols < (1 << 30), "row width %lld out of range", (long long)cols);
   B200_REQUIRE(rows < (1LL << 31), "too many rows");
   B200_REQUIRE(!(eps < 0.f) && eps == eps, "eps must be a non-negative number");
+  B200_REQUIRE(gamma_offset == gamma_offset, "gamma_offset must be a number");
   if (rows == 0) return B200_OK;
   cudaStream_t s = (cudaStream_t)stream;
   switch (x->dtype) {
-    case B200_DTYPE_FLOAT32: return dispatch<float>(x, w, y, rinv, eps, s);
-    case B200_DTYPE_FLOAT16: return dispatch<__half>(x, w, y, rinv, eps, s);
-    default: return dispatch<__nv_bfloat16>(x, w, y, rinv, eps, s);
+    case B200_DTYPE_FLOAT32: return dispatch<float>(x, w, y, rinv, eps, gamma_offset, s);
+    case B200_DTYPE_FLOAT16: return dispatch<__half>(x, w, y, rinv, eps, gamma_offset, s);
+    default: return dispatch<__nv_bfloat16>(x, w, y, rinv, eps, gamma_offset, s);
   }
+}
+
+extern "C" int b200_rmsnorm_fwd(const b200_tensor *x, const b200_tensor *w,
+                                b200_tensor *y, b200_tensor *rinv, float eps,
+                                void *stream) {
+  return b200_rmsnorm_fwd_ex(x, w, y, rinv, eps, 0.0f, stream);
 }

@@ -29,7 +29,8 @@ def _ref(tensor):
     return ctypes.byref(tensor) if tensor is not None else None
 
 
-def rmsnorm(x, w, y, rinv=None, eps=1e-6, *, x_row_stride=None, y_row_stride=None, stream=0):
+def rmsnorm(x, w, y, rinv=None, eps=1e-6, *, x_row_stride=None, y_row_stride=None,
+            gamma_offset=0.0, stream=0):
     """y = x * rsqrt(mean(x^2) + eps) * w per row; rinv[row] = the inverse rms.
 
     Native form of rms_layernorm_forward_kernel
@@ -39,8 +40,8 @@ def rmsnorm(x, w, y, rinv=None, eps=1e-6, *, x_row_stride=None, y_row_stride=Non
     yd = _desc(y, strides=None if y_row_stride is None else (int(y_row_stride), 1))
     wd = _desc(w, shape=(cols,), strides=(1,))
     rd = _desc(rinv, shape=(rows,), strides=(1,)) if rinv is not None else None
-    abi.check(abi.lib().b200_rmsnorm_fwd(_ref(xd), _ref(wd), _ref(yd), _ref(rd), float(eps),
-                                         stream))
+    abi.check(abi.lib().b200_rmsnorm_fwd_ex(_ref(xd), _ref(wd), _ref(yd), _ref(rd), float(eps),
+                                            float(gamma_offset), stream))
 
 
 def softmax(x, y, *, causal_mod=False, row_offset=0, stream=0):
@@ -81,6 +82,31 @@ def swiglu(x, y, out, *, stream=0):
     """out = x * sigmoid(x) * y (swiglu_fwd_kernel, ops/suite/perf/swiglu_fwd.py:18-36)."""
     xd, yd, od = _desc(x), _desc(y), _desc(out)
     abi.check(abi.lib().b200_swiglu_fwd(_ref(xd), _ref(yd), _ref(od), stream))
+
+
+def softmax_variant(x, y, *, mul=None, log_input=False, stream=0):
+    """y = softmax(x) * mul (softmax_mul_kernel, ops/suite/perf/softmax_mul.py:21-32) or
+    y = softmax(log x) (softmax_log_kernel, ops/suite/perf/softmax_log.py:20-40)."""
+    xd, yd = _desc(x), _desc(y)
+    md = _desc(mul) if mul is not None else None
+    abi.check(abi.lib().b200_softmax_variant(_ref(xd), _ref(md), _ref(yd),
+                                             1 if log_input else 0, stream))
+
+
+def repeat_log_softmax(x, y, repeat, *, stream=0):
+    """y[row, p] = x[row, p // repeat] - logsumexp (fused_repeat_interleave_log_softmax_kernel,
+    ops/suite/perf/fused_repeat_interleave_log_softmax.py:19-31)."""
+    xd, yd = _desc(x), _desc(y)
+    abi.check(abi.lib().b200_repeat_log_softmax(_ref(xd), _ref(yd), int(repeat), stream))
+
+
+def elementwise(op, a, out, *, b=None, p0=0.0, p1=0.0, p2=0.0, stream=0):
+    """Flat GELU-family operators (``abi.EW_*``): gelu.py, add_gelu.py, geglu_tanh_triton.py and
+    dev/epilogue_kernel.py of the reference's corpus."""
+    ad, od = _desc(a), _desc(out)
+    bd = _desc(b) if b is not None else None
+    abi.check(abi.lib().b200_elementwise(int(op), _ref(ad), _ref(bd), _ref(od), float(p0),
+                                         float(p1), float(p2), stream))
 
 
 def device_status(stream=0) -> None:

@@ -144,12 +144,12 @@ def _rmsnorm_loop(device, v, grid, name):
     rmsnorm_fwd_loop_kernel (ops/suite/dev/rmsnorm_fwd_loop_kernel.py:10-34)."""
     rows = _grid_tuple(grid)[0]
     n = int(v["N"])
-    _require(not v.get("zero_centered_gamma", False), name, "zero_centered_gamma",
-             "the (1 + w) weight form has no native operator")
     rinv = v.get("INV_RMS", v.get("rsigma_ptr"))
     w = v.get("w_ptr", v.get("weight_ptr"))
     ops.rmsnorm(_View(v["in_ptr"], (rows, n)), _View(w, (n,)), _View(v["out_ptr"], (rows, n)),
-                _View(rinv, (rows,)), float(v["eps"]), stream=device.stream)
+                _View(rinv, (rows,)), float(v["eps"]),
+                gamma_offset=1.0 if v.get("zero_centered_gamma", False) else 0.0,
+                stream=device.stream)
 
 
 def _softmax(device, v, grid, name):
@@ -257,6 +257,65 @@ def _swiglu(device, v, grid, name):
                stream=device.stream)
 
 
+def _softmax_mul(device, v, grid, name):
+    """softmax_mul_kernel (ops/suite/perf/softmax_mul.py:21)."""
+    rows, n_cols = _grid_tuple(grid)[0], int(v["n_cols"])
+    ops.softmax_variant(_View(v["x_ptr"], (rows, n_cols)), _View(v["y_ptr"], (rows, n_cols)),
+                        mul=_View(v["o_ptr"], (rows, n_cols)), stream=device.stream)
+
+
+def _softmax_log(device, v, grid, name):
+    """softmax_log_kernel (ops/suite/perf/softmax_log.py:20)."""
+    rows, n_cols = _grid_tuple(grid)[0], int(v["n_cols"])
+    ops.softmax_variant(_View(v["x_ptr"], (rows, n_cols)), _View(v["y_ptr"], (rows, n_cols)),
+                        log_input=True, stream=device.stream)
+
+
+def _repeat_log_softmax(device, v, grid, name):
+    """fused_repeat_interleave_log_softmax_kernel
+    (ops/suite/perf/fused_repeat_interleave_log_softmax.py:19-20)."""
+    rows = _grid_tuple(grid)[0]
+    cols, repeat, length = int(v["COLS"]), int(v["R"]), int(v["L"])
+    _require(int(v.get("BE", length)) >= length, name, "BE",
+             "the reference program covers a row with one block: BE >= L")
+    ops.repeat_log_softmax(_View(v["x_ptr"], (rows, cols)), _View(v["y_ptr"], (rows, length)),
+                           repeat, stream=device.stream)
+
+
+def _gelu(device, v, grid, name):
+    """gelu_kernel (ops/suite/perf/gelu.py:21)."""
+    n = int(v["n_elements"])
+    ops.elementwise(abi.EW_GELU_ERF, _View(v["x_ptr"], (n,)), _View(v["y_ptr"], (n,)),
+                    stream=device.stream)
+
+
+def _add_gelu(device, v, grid, name):
+    """add_gelu_kernel (ops/suite/perf/add_gelu.py:21): the kernel body overrides its alpha
+    argument with 1.5 (:26), and so does this adapter."""
+    n = int(v["n_elements"])
+    ops.elementwise(abi.EW_ADD_GELU_ERF, _View(v["x_ptr"], (n,)), _View(v["y_ptr"], (n,)),
+                    b=_View(v["o_ptr"], (n,)), p0=1.5, stream=device.stream)
+
+
+def _geglu_tanh(device, v, grid, name):
+    """geglu_tanh_forward_kernel (ops/suite/perf/geglu_tanh_triton.py:19-20): rows of n_cols
+    elements at pitch `stride`; only the dense layout (stride == n_cols) has a flat kernel."""
+    rows, n_cols = _grid_tuple(grid)[0], int(v["n_cols"])
+    _require(int(v["stride"]) == n_cols, name, "stride", "rows must be dense (stride == n_cols)")
+    n = rows * n_cols
+    ops.elementwise(abi.EW_GEGLU_TANH, _View(v["a_ptr"], (n,)), _View(v["c_ptr"], (n,)),
+                    b=_View(v["b_ptr"], (n,)), stream=device.stream)
+
+
+def _epilogue(device, v, grid, name):
+    """epilogue_kernel (ops/suite/dev/epilogue_kernel.py:24): in place on out_ptr."""
+    n, n_cols = int(v["n_elements"]), int(v["n_cols"])
+    ops.elementwise(abi.EW_BIAS_SCALE_CLAMP_GELU, _View(v["out_ptr"], (n,)),
+                    _View(v["out_ptr"], (n,)), b=_View(v["bias_ptr"], (n_cols,)),
+                    p0=float(v["scale"]), p1=float(v["ht_min"]), p2=float(v["ht_max"]),
+                    stream=device.stream)
+
+
 def _swiglu_gemm(device, v, grid, name):
     """Native handle: H = silu(X @ Wg) * (X @ Wu) in one kernel (kernels.swiglu_gemm_kernel)."""
     m, n, k = int(v["M"]), int(v["N"]), int(v["K"])
@@ -331,6 +390,18 @@ def default_registry() -> Registry:
     r.register("swiglu_fwd_kernel",
                ("X", "Y", "OUT", "stride_x_row", "stride_y_row", "stride_out_row", "ncols",
                 "BLOCK_N"), _swiglu)
+    r.register("softmax_mul_kernel", ("x_ptr", "o_ptr", "y_ptr", "n_cols", "BLOCK_N"), _softmax_mul)
+    r.register("softmax_log_kernel", ("x_ptr", "y_ptr", "n_cols", "BLOCK_N"), _softmax_log)
+    r.register("fused_repeat_interleave_log_softmax_kernel",
+               ("x_ptr", "y_ptr", "COLS", "R", "L", "BE"), _repeat_log_softmax)
+    r.register("gelu_kernel", ("x_ptr", "y_ptr", "n_elements", "BLOCK_SIZE"), _gelu)
+    r.register("add_gelu_kernel", ("x_ptr", "o_ptr", "y_ptr", "alpha", "n_elements", "BLOCK"),
+               _add_gelu)
+    r.register("geglu_tanh_forward_kernel",
+               ("a_ptr", "b_ptr", "c_ptr", "stride", "n_cols", "BLOCK_SIZE"), _geglu_tanh)
+    r.register("epilogue_kernel",
+               ("out_ptr", "bias_ptr", "n_elements", "n_cols", "scale", "ht_min", "ht_max",
+                "BLOCK_SIZE"), _epilogue)
     # native handles for the configurations no single reference kernel covers
     for handle, adapter in ((kernels.masked_softmax_kernel, _masked_softmax),
                             (kernels.gemm_bias_act_kernel, _gemm_bias_act),

@@ -31,6 +31,7 @@ DTYPE_SIZES = {
 
 ACT_NONE, ACT_GELU_ERF, ACT_GELU_TANH, ACT_LEAKY_RELU, ACT_SWIGLU = 0, 1, 2, 3, 4
 MASK_NONE, MASK_CAUSAL_MOD = 0, 1
+EW_GELU_ERF, EW_ADD_GELU_ERF, EW_GEGLU_TANH, EW_BIAS_SCALE_CLAMP_GELU = 1, 2, 3, 4
 
 
 class Tensor(Structure):
@@ -87,7 +88,11 @@ PROTOTYPES = {
     "b200_event_record": (c_int, [_PTR, _PTR]),
     "b200_event_elapsed_ms": (c_int, [_PTR, _PTR, POINTER(c_float)]),
     "b200_rmsnorm_fwd": (c_int, [_T, _T, _T, _T, c_float, _PTR]),
+    "b200_rmsnorm_fwd_ex": (c_int, [_T, _T, _T, _T, c_float, c_float, _PTR]),
     "b200_softmax_fwd": (c_int, [_T, _T, c_int, c_int64, _PTR]),
+    "b200_softmax_variant": (c_int, [_T, _T, _T, c_int, _PTR]),
+    "b200_repeat_log_softmax": (c_int, [_T, _T, c_int, _PTR]),
+    "b200_elementwise": (c_int, [c_int, _T, _T, _T, c_float, c_float, c_float, _PTR]),
     "b200_gemm_bias_act": (c_int, [_T, _T, _T, _T, _T, c_int, _PTR]),
     "b200_gemm_scatter_rows": (c_int, [_T, _T, _T, POINTER(_PTR), c_int, c_int, c_int64, _PTR]),
     "b200_reduce_slices_broadcast": (c_int, [_PTR, c_uint32, c_int, c_int64, c_int64, c_int64,

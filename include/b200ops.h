@@ -139,6 +139,11 @@ int b200_rmsnorm_fwd(const b200_tensor *x, const b200_tensor *w,
                      b200_tensor *y, b200_tensor *rinv, float eps,
                      void *stream);
 
+/* The same with the weight taken as (w + gamma_offset): gamma_offset = 1 is the
+ * zero-centred gamma of rmsnorm_fwd_loop_kernel (ops/suite/dev/rmsnorm_fwd_loop_kernel.py:10-34). */
+int b200_rmsnorm_fwd_ex(const b200_tensor *x, const b200_tensor *w, b200_tensor *y,
+                        b200_tensor *rinv, float eps, float gamma_offset, void *stream);
+
 /* Row softmax with an optional index-computed mask.  Replaces softmax_kernel
  * (ops/suite/perf/softmax.py:20-31) and, with B200_MASK_CAUSAL_MOD, the
  * masking expression of ops/suite/perf/attn_fwd_causal.py:46-47 applied to a
@@ -147,6 +152,28 @@ int b200_rmsnorm_fwd(const b200_tensor *x, const b200_tensor *w,
  * row shard masks by its global row. */
 int b200_softmax_fwd(const b200_tensor *x, b200_tensor *y, int mask_kind,
                      int64_t row_offset, void *stream);
+
+/* Softmax variants over contiguous [rows, cols]: with `mul`, y = softmax(x) * mul
+ * (softmax_mul_kernel, ops/suite/perf/softmax_mul.py:21-32); with log_input, y =
+ * softmax(log x) and a NaN in log x makes its row NaN (softmax_log_kernel,
+ * ops/suite/perf/softmax_log.py:20-40).  mul may be NULL. */
+int b200_softmax_variant(const b200_tensor *x, const b200_tensor *mul, b200_tensor *y,
+                         int log_input, void *stream);
+
+/* y[row, p] = x[row, p / repeat] - logsumexp over p in [0, y.cols)
+ * (fused_repeat_interleave_log_softmax_kernel,
+ * ops/suite/perf/fused_repeat_interleave_log_softmax.py:19-31). */
+int b200_repeat_log_softmax(const b200_tensor *x, b200_tensor *y, int repeat, void *stream);
+
+/* Flat elementwise operators of the GELU family; a, b, out are 1-D contiguous. */
+enum b200_ewise {
+  B200_EW_GELU_ERF = 1,             /* gelu_kernel, ops/suite/perf/gelu.py:21-27 */
+  B200_EW_ADD_GELU_ERF = 2,         /* gelu(a + p0 * b): add_gelu_kernel, ops/suite/perf/add_gelu.py:21-30 */
+  B200_EW_GEGLU_TANH = 3,           /* gelu_tanh(a) * b: geglu_tanh_forward_kernel, ops/suite/perf/geglu_tanh_triton.py:19-37 */
+  B200_EW_BIAS_SCALE_CLAMP_GELU = 4 /* gelu(clamp((a + b[i % len(b)]) * p0, p1, p2)): epilogue_kernel, ops/suite/dev/epilogue_kernel.py:24-32 */
+};
+int b200_elementwise(int op, const b200_tensor *a, const b200_tensor *b, b200_tensor *out,
+                     float p0, float p1, float p2, void *stream);
 
 /* C = act(A @ B + bias).  Replaces matmul_kernel (ops/suite/perf/matmul.py:20-38)
  * and linear_act_kernel (ops/suite/perf/triton_linear_activation.py:27-49).

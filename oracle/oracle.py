@@ -175,6 +175,45 @@ def swiglu_mlp_ref(x, wg, wu, wd, h_dtype: str | None = None):
     return matmul_ref(h, wd)
 
 
+# ----------------------------------------------------------------- sibling operators
+def softmax_mul_ref(x, o):
+    """``ref`` of ops/suite/perf/softmax_mul.py: softmax(x) * o."""
+    return softmax_ref(x) * np.asarray(o, dtype=np.float64)
+
+
+def softmax_log_ref(x):
+    """``ref`` of ops/suite/perf/softmax_log.py: softmax(log x) (NaN rows stay NaN)."""
+    with np.errstate(divide="ignore", invalid="ignore"):
+        return softmax_ref(np.log(np.asarray(x, dtype=np.float64)))
+
+
+def repeat_log_softmax_ref(x, repeat, length=None):
+    """``ref`` of ops/suite/perf/fused_repeat_interleave_log_softmax.py: log-softmax of
+    np.repeat(x, R, axis=1) (the first ``length`` positions)."""
+    rep = np.repeat(np.asarray(x, dtype=np.float64), int(repeat), axis=1)
+    if length is not None:
+        rep = rep[:, :int(length)]
+    m = rep.max(axis=1, keepdims=True)
+    return rep - (m + np.log(np.exp(rep - m).sum(axis=1, keepdims=True)))
+
+
+def add_gelu_ref(x, o, alpha=1.5):
+    """``ref`` of ops/suite/perf/add_gelu.py: gelu_erf(x + 1.5 o)."""
+    return gelu_erf(np.asarray(x, dtype=np.float64) + alpha * np.asarray(o, dtype=np.float64))
+
+
+def geglu_tanh_ref(a, b):
+    """``ref`` of ops/suite/perf/geglu_tanh_triton.py:44-49: gelu_tanh(a) * b."""
+    return gelu_tanh(np.asarray(a, dtype=np.float64)) * np.asarray(b, dtype=np.float64)
+
+
+def epilogue_ref(x, bias, n_cols, scale, lo, hi):
+    """``ref`` of ops/suite/dev/epilogue_kernel.py: gelu_erf(clip((x + bias) * scale, lo, hi))."""
+    x = np.asarray(x, dtype=np.float64).reshape(-1, int(n_cols))
+    y = (x + np.asarray(bias, dtype=np.float64)[None, :]) * float(scale)
+    return gelu_erf(np.minimum(np.maximum(y, float(lo)), float(hi))).reshape(-1)
+
+
 # ----------------------------------------------------------------- comparison
 DTYPE_TOLERANCES = {  # ops/harness/opslib/case.py:153-157
     "float32": (1e-3, 1e-3),

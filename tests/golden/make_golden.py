@@ -36,6 +36,19 @@ OPERATORS = {
     "perf/swiglu_fwd.py": [(64, 1024)],
     "dev/softmax_kernel_inner.py": [],
     "dev/hidden__rms_norm_loop_kernel.py": [],
+    # sibling kernels of the five families
+    "perf/softmax_mul.py": [],
+    "perf/softmax_log.py": [],
+    "perf/fused_repeat_interleave_log_softmax.py": [],
+    "perf/gelu.py": [],
+    "perf/add_gelu.py": [],
+    "perf/geglu_tanh_triton.py": [],
+    "perf/swiglu_triton.py": [],
+    "perf/matmul_triton_autotune.py": [],
+    "perf/attention_forward_triton.py": [],
+    "perf/attention_kernel.py": [],
+    "dev/epilogue_kernel.py": [],
+    "dev/rmsnorm_fwd_loop_kernel.py": [],
 }
 MID_DTYPES = ("bfloat16",)  # mid-size shapes are stored for one dtype to keep fixtures small
 

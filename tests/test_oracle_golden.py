@@ -134,3 +134,86 @@ def test_lse_definition():
     out, lse = oracle.attention_head_ref(q, k, v, 0.3, causal=True)
     s = np.where(np.tril(np.ones((12, 12), bool)), (q @ k.T) * 0.3, -np.inf)
     np.testing.assert_allclose(lse, np.log(np.exp(s).sum(-1)), rtol=1e-12)
+
+
+# ------------------------------------------------------------------ sibling operators
+def _check(case, name, value):
+    """The oracle against a fixture, with the fixture's own policy (some of these files'
+    refs compute in the storage dtype, so exact float64 agreement is not defined)."""
+    policy = case["comparison"][name]
+    expected = case["expected"][name]
+    oracle.compare(np.asarray(value).astype(expected.dtype), expected, policy["rtol"],
+                   policy["atol"], name=name)
+
+
+@pytest.mark.parametrize("tag", golden_cases.tags("softmax_mul"))
+def test_softmax_mul(tag):
+    case, _ = golden_cases.load(tag)
+    _check(case, "y_ptr", oracle.softmax_mul_ref(case["args"]["x_ptr"], case["args"]["o_ptr"]))
+
+
+@pytest.mark.parametrize("tag", golden_cases.tags("softmax_log"))
+def test_softmax_log(tag):
+    case, _ = golden_cases.load(tag)
+    _check(case, "y_ptr", oracle.softmax_log_ref(case["args"]["x_ptr"]))
+
+
+@pytest.mark.parametrize("tag", golden_cases.tags("fused_repeat_interleave_log_softmax"))
+def test_repeat_log_softmax(tag):
+    case, _ = golden_cases.load(tag)
+    a = case["args"]
+    _check(case, "y_ptr", oracle.repeat_log_softmax_ref(a["x_ptr"], a["R"], a["L"]))
+
+
+@pytest.mark.parametrize("tag", golden_cases.tags("gelu"))
+def test_gelu(tag):
+    case, _ = golden_cases.load(tag)
+    _check(case, "y_ptr", oracle.gelu_erf(case["args"]["x_ptr"].astype(np.float64)))
+
+
+@pytest.mark.parametrize("tag", golden_cases.tags("add_gelu"))
+def test_add_gelu(tag):
+    case, _ = golden_cases.load(tag)
+    _check(case, "y_ptr", oracle.add_gelu_ref(case["args"]["x_ptr"], case["args"]["o_ptr"]))
+
+
+@pytest.mark.parametrize("tag", golden_cases.tags("geglu_tanh_triton"))
+def test_geglu_tanh(tag):
+    case, _ = golden_cases.load(tag)
+    _check(case, "c_ptr", oracle.geglu_tanh_ref(case["args"]["a_ptr"], case["args"]["b_ptr"]))
+
+
+@pytest.mark.parametrize("tag", golden_cases.tags("epilogue_kernel"))
+def test_epilogue(tag):
+    case, _ = golden_cases.load(tag)
+    a = case["args"]
+    _check(case, "out_ptr", oracle.epilogue_ref(a["out_ptr"], a["bias_ptr"], a["n_cols"], a["scale"],
+                                                a["ht_min"], a["ht_max"]))
+
+
+@pytest.mark.parametrize("tag", golden_cases.tags("rmsnorm_fwd_loop_kernel"))
+def test_rmsnorm_zero_centred_gamma(tag):
+    case, _ = golden_cases.load(tag)
+    a = case["args"]
+    rows, n = case["grid"][0], a["N"]
+    offset = 1.0 if case["meta"].get("zero_centered_gamma") else 0.0
+    y, r = oracle.rmsnorm_ref(a["in_ptr"].reshape(rows, n), a["weight_ptr"][:n].astype(np.float64) + offset,
+                              a["eps"])
+    _check(case, "out_ptr", y.reshape(-1))
+    _check(case, "rsigma_ptr", r)
+
+
+@pytest.mark.parametrize("tag", golden_cases.tags("swiglu_triton") + golden_cases.tags("matmul_triton_autotune")
+                         + golden_cases.tags("attention_forward_triton") + golden_cases.tags("attention_kernel"))
+def test_twins(tag):
+    case, _ = golden_cases.load(tag)
+    a = case["args"]
+    if tag.startswith("swiglu"):
+        _check(case, "OUT", oracle.swiglu_ref(a["X"], a["Y"]))
+    elif tag.startswith("matmul"):
+        act = "leaky_relu" if case["meta"].get("LEAKY") else "none"
+        _check(case, "c_ptr", oracle.linear_act_ref(a["a_ptr"], a["b_ptr"], None, act))
+    else:
+        out, _ = oracle.attention_ref(a["q_ptr"], a["k_ptr"], a["v_ptr"], a["scale"],
+                                      causal=bool(case["meta"]["CAUSAL"]))
+        _check(case, "out_ptr", out)
