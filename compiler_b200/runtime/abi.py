@@ -118,9 +118,17 @@ def lib() -> ctypes.CDLL:
     with _lock:
         if _lib is not None:
             return _lib
+        import os
+        from pathlib import Path
+
         from compiler_b200 import build as _build
         path = _build.LIB_PATH
-        if not _build.is_current():
+        override = os.environ.get("B200OPS_LIBRARY")  # a prebuilt library to load as is
+        if override:
+            path = Path(override)
+            if not path.is_file():
+                raise RuntimeError(f"B200OPS_LIBRARY={override} does not exist")
+        elif not _build.is_current():
             try:
                 path = _build.build()
             except Exception as exc:  # noqa: BLE001
