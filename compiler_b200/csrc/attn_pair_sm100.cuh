@@ -1,8 +1,8 @@
 // Attention forward, two query tiles per CTA (256 query rows), persistent.
 //
 // Same arithmetic as attn_fwd_tcgen05_kernel; the schedule differs.  A CTA owns
-// work items (256 query rows of one batch*head), heaviest first, and keeps two
-// independent 128-row tiles in flight so the tensor core always has one tile's
+// work items (256 query rows of one batch*head; see item_at for their order) and keeps
+// two independent 128-row tiles in flight so the tensor core always has one tile's
 // MMAs to run while the other tile's rows are in their softmax:
 //
 //   warps 0-3   softmax + epilogue of tile 0 (one query row per thread)
@@ -34,7 +34,8 @@ using namespace sm100;
 constexpr int TILE_M = 128;           // query rows per tile
 constexpr int CTA_M = 2 * TILE_M;     // query rows per work item
 constexpr int BLOCK_N = 128;          // keys per block
-constexpr int KV_STAGES = 2;
+constexpr int KV_STAGES = 2;          // K ring
+constexpr int V_STAGES = 2;           // V ring (a third stage was measured: no gain)
 constexpr int THREADS = 384;  // 3 warpgroups: softmax 0, softmax 1, {producer, issuer, 2 idle}
 constexpr int TMEM_COLS = 512;
 constexpr int S_COLS = 128;
@@ -49,10 +50,9 @@ constexpr float kRescaleThreshold = 8.0f;
 
 struct Params {
   int H, N, ZH;
+  int wave_heads;  // (batch, head) pairs whose K / V are meant to share the L2 at one time
   float scale_log2;  // scale * log2(e)
   int causal;
-  void *o;
-  int64_t oz, oh, om;
   float *lse;
   uint32_t idesc_qk, idesc_pv;
   unsigned int *status;
@@ -64,7 +64,8 @@ template <int D> struct Smem {
   static constexpr int Q_OFF = 0;                          // two tiles
   static constexpr int K_OFF = 2 * TILE_BYTES;
   static constexpr int V_OFF = K_OFF + KV_STAGES * TILE_BYTES;
-  static constexpr int BAR_OFF = V_OFF + KV_STAGES * TILE_BYTES;
+  static constexpr int O_OFF = V_OFF + V_STAGES * TILE_BYTES;  // staging of one finished O tile
+  static constexpr int BAR_OFF = O_OFF + TILE_BYTES;
   static constexpr int BYTES = BAR_OFF + 256 + 1024;
 };
 
@@ -75,6 +76,13 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap *tm,
       " [%0], [%1, {%3, %4, %5, %6}], [%2];" ::"r"(dst),
       "l"((uint64_t)tm), "r"(bar), "r"(x), "r"(y), "r"(z), "r"(w)
       : "memory");
+}
+
+__device__ __forceinline__ void tma_store_4d(const CUtensorMap *tm, uint32_t src, int x, int y,
+                                             int z, int w) {
+  asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];" ::
+                   "l"((uint64_t)tm), "r"(src), "r"(x), "r"(y), "r"(z), "r"(w)
+               : "memory");
 }
 
 __device__ __forceinline__ float ex2(float x) {
@@ -162,11 +170,27 @@ struct Item {
   int nb_max;
 };
 
-__device__ __forceinline__ Item decode_item(int item, const Params &p) {
+// The n-th step of this CTA's persistent loop.  Work is dealt out in units of two items
+// of one (batch, head): the query block of rank r from the bottom and the one of rank r
+// from the top.  Under the causal mask the pair visits num_qb + 1 key blocks whatever r
+// is, so dealing units round-robin balances the CTAs to within one unit.  Units are
+// ordered wave by wave (a wave = wave_heads heads, all of their units, pair rank by pair
+// rank): the CTAs running at one time read the K / V of the same few heads, and a block
+// fetched by one of them is an L2 hit for the others.
+// Returns 0 past the end, 1 with `it` filled, 2 for the missing half of an odd middle.
+__device__ __forceinline__ int item_at(int n, const Params &p, Item &it) {
   const int num_qb = (p.N + CTA_M - 1) / CTA_M;
-  Item it;
-  const int qb = num_qb - 1 - item / p.ZH;  // heaviest query blocks first
-  it.zh = item % p.ZH;
+  const int pairs = (num_qb + 1) / 2;
+  const int u = (n >> 1) * (int)gridDim.x + (int)blockIdx.x;
+  if (u >= pairs * p.ZH) return 0;
+  const int per_wave = p.wave_heads * pairs;
+  const int wave = u / per_wave, k = u - wave * per_wave;
+  const int zh0 = wave * p.wave_heads;
+  const int heads = min(p.wave_heads, p.ZH - zh0);
+  const int r = k / heads;
+  const int qb = (n & 1) ? r : num_qb - 1 - r;
+  if ((n & 1) && r == num_qb - 1 - r) return 2;
+  it.zh = zh0 + k % heads;
   it.z = it.zh / p.H;
   it.h = it.zh % p.H;
   it.m0 = qb * CTA_M;
@@ -181,15 +205,7 @@ __device__ __forceinline__ Item decode_item(int item, const Params &p) {
     }
   }
   it.nb_max = max(it.nb[0], it.nb[1]);
-  return it;
-}
-
-// Work items are sorted heaviest first; round r of the persistent loop hands CTA c the
-// item r*G + c on even rounds and r*G + (G-1-c) on odd rounds, so the CTA that drew the
-// heaviest item of one round draws the lightest of the next and the totals even out.
-__device__ __forceinline__ int item_of_round(int round) {
-  const int g = (int)gridDim.x, c = (int)blockIdx.x;
-  return round * g + ((round & 1) ? g - 1 - c : c);
+  return 1;
 }
 
 #ifdef B200_ATTN_TIMING
@@ -200,7 +216,8 @@ template <typename T, int D>
 __global__ void __launch_bounds__(THREADS, 1)
 attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q,
                      const __grid_constant__ CUtensorMap tm_k,
-                     const __grid_constant__ CUtensorMap tm_v, const Params p) {
+                     const __grid_constant__ CUtensorMap tm_v,
+                     const __grid_constant__ CUtensorMap tm_o, const Params p) {
   using L = Smem<D>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -208,25 +225,27 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q,
   const uint32_t q_smem = smem_base + L::Q_OFF;
   const uint32_t k_smem = smem_base + L::K_OFF;
   const uint32_t v_smem = smem_base + L::V_OFF;
+  const uint32_t o_stage = smem_base + L::O_OFF;
   const uint32_t bar0 = smem_base + L::BAR_OFF;
   const uint32_t q_full = bar0, q_empty = bar0 + 8;
   auto k_full = [&](uint32_t s) { return bar0 + 8u * (2 + s); };
   auto k_empty = [&](uint32_t s) { return bar0 + 8u * (4 + s); };
-  auto v_full = [&](uint32_t s) { return bar0 + 8u * (6 + s); };
-  auto v_empty = [&](uint32_t s) { return bar0 + 8u * (8 + s); };
+  auto v_full = [&](uint32_t s) { return bar0 + 8u * (23 + s); };
+  auto v_empty = [&](uint32_t s) { return bar0 + 8u * (23 + V_STAGES + s); };
+  const uint32_t staged = bar0 + 8u * 21;      // a finished O tile sits in the staging buffer
+  const uint32_t stage_free = bar0 + 8u * 22;  // its copy to global memory has read it
   auto s_full = [&](int t) { return bar0 + 8u * (10 + t); };
   auto p_full = [&](int t) { return bar0 + 8u * (12 + t); };
   auto o_full = [&](int t) { return bar0 + 8u * (14 + t); };
   auto o_empty = [&](int t) { return bar0 + 8u * (16 + t); };
   const uint32_t drain_bar = bar0 + 8u * 18;
   auto p2_full = [&](int t) { return bar0 + 8u * (19 + t); };  // second half of P
-  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem_gen + L::BAR_OFF + 8 * 21);
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem_gen + L::BAR_OFF + 8 * (23 + 2 * V_STAGES));
   volatile uint32_t *abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const WaitCtx ctx{abort_flag, p.status};
-  const int num_items = ((p.N + CTA_M - 1) / CTA_M) * p.ZH;
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
@@ -234,6 +253,8 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q,
     for (int s = 0; s < KV_STAGES; ++s) {
       mbar_init(k_full(s), 1);
       mbar_init(k_empty(s), 1);
+    }
+    for (int s = 0; s < V_STAGES; ++s) {
       mbar_init(v_full(s), 1);
       mbar_init(v_empty(s), 1);
     }
@@ -245,6 +266,8 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q,
       mbar_init(o_empty(t), TILE_M / 32);
     }
     mbar_init(drain_bar, 1);
+    mbar_init(staged, TILE_M / 32);
+    mbar_init(stage_free, 1);
     *abort_flag = 0u;
     mbar_init_fence();
   }
@@ -252,6 +275,7 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q,
     tma_prefetch_desc(&tm_q);
     tma_prefetch_desc(&tm_k);
     tma_prefetch_desc(&tm_v);
+    tma_prefetch_desc(&tm_o);
   }
   if (warp == 9) tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
   tc_fence_before_sync();
@@ -267,10 +291,13 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q,
     // ---------------------------------------------------------------- producer
     if (lane == 0) {
       uint32_t kv_it = 0, item_n = 0;
-      uint32_t issued = 0, parity = 0;  // bit s: K stage, bit 2+s: V stage, bit 4: Q
+      uint32_t issued = 0, parity = 0;  // bit s: K stage, bit 2+s: V stage, bit 8: Q
       bool ok = true;
-      for (int round = 0, item; ok && (item = item_of_round(round)) < num_items; ++round, ++item_n) {
-        const Item it = decode_item(item, p);
+      for (int n = 0; ok; ++n) {
+        Item it;
+        const int step = item_at(n, p, it);
+        if (step == 0) break;
+        if (step == 2) continue;
         if (!mbar_wait(q_empty, (item_n & 1u) ^ 1u, ctx, 1)) { ok = false; break; }
         mbar_arrive_expect_tx(q_full, 2 * L::TILE_BYTES);
 #pragma unroll
@@ -279,8 +306,8 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q,
           for (int b = 0; b < D / 64; ++b)
             tma_load_4d(q_smem + t * L::TILE_BYTES + b * L::BOX_BYTES, &tm_q, q_full, b * 64,
                         it.m0 + t * TILE_M, it.h, it.z);
-        issued |= 16u;
-        parity = (parity & ~16u) | ((item_n & 1u) << 4);
+        issued |= 256u;
+        parity = (parity & ~256u) | ((item_n & 1u) << 8);
         for (int j = 0; j < it.nb_max; ++j, ++kv_it) {
           const uint32_t s = kv_it & 1u, ph = (kv_it >> 1) & 1u;
           if (!mbar_wait(k_empty(s), ph ^ 1u, ctx, 2)) { ok = false; break; }
@@ -291,23 +318,25 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q,
                         j * BLOCK_N, it.h, it.z);
           issued |= 1u << s;
           parity = (parity & ~(1u << s)) | (ph << s);
-          if (!mbar_wait(v_empty(s), ph ^ 1u, ctx, 3)) { ok = false; break; }
-          mbar_arrive_expect_tx(v_full(s), L::TILE_BYTES);
+          const uint32_t vs = kv_it % V_STAGES, vph = (kv_it / V_STAGES) & 1u;
+          if (!mbar_wait(v_empty(vs), vph ^ 1u, ctx, 3)) { ok = false; break; }
+          mbar_arrive_expect_tx(v_full(vs), L::TILE_BYTES);
 #pragma unroll
           for (int b = 0; b < D / 64; ++b)
-            tma_load_4d(v_smem + s * L::TILE_BYTES + b * L::BOX_BYTES, &tm_v, v_full(s), b * 64,
+            tma_load_4d(v_smem + vs * L::TILE_BYTES + b * L::BOX_BYTES, &tm_v, v_full(vs), b * 64,
                         j * BLOCK_N, it.h, it.z);
-          issued |= 4u << s;
-          parity = (parity & ~(4u << s)) | (ph << (2 + s));
+          issued |= 4u << vs;
+          parity = (parity & ~(4u << vs)) | (vph << (2 + vs));
         }
+        ++item_n;
       }
       if (!ok) {
         // copies already issued still target this CTA's shared memory
-        if (issued & 16u) mbar_wait_drain(q_full, (parity >> 4) & 1u);
-        for (uint32_t s = 0; s < KV_STAGES; ++s) {
+        if (issued & 256u) mbar_wait_drain(q_full, (parity >> 8) & 1u);
+        for (uint32_t s = 0; s < KV_STAGES; ++s)
           if (issued & (1u << s)) mbar_wait_drain(k_full(s), (parity >> s) & 1u);
+        for (uint32_t s = 0; s < V_STAGES; ++s)
           if (issued & (4u << s)) mbar_wait_drain(v_full(s), (parity >> (2 + s)) & 1u);
-        }
       }
     }
   } else if (warp == 9) {
@@ -372,8 +401,11 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q,
     auto commit = [&](uint32_t bar) {
       if (leader) tc_commit(bar);
     };
-    for (int round = 0, item; ok && (item = item_of_round(round)) < num_items; ++round, ++item_n) {
-      const Item it = decode_item(item, p);
+    for (int n = 0; ok; ++n) {
+      Item it;
+      const int step = item_at(n, p, it);
+      if (step == 0) break;
+      if (step == 2) continue;
       if (!wait_all(q_full, item_n & 1u, 4)) { ok = false; break; }
       {  // S(0) of both tiles
         const uint32_t s = kv_base & 1u, ph = (kv_base >> 1) & 1u;
@@ -389,7 +421,8 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q,
         const uint32_t s = kv & 1u, ph = (kv >> 1) & 1u;
         const uint32_t s1 = (kv + 1) & 1u, ph1 = ((kv + 1) >> 1) & 1u;
         const bool more = j + 1 < it.nb_max;
-        if (!wait_all(v_full(s), ph, 6)) { ok = false; break; }
+        const uint32_t vs = kv % V_STAGES, vph = (kv / V_STAGES) & 1u;
+        if (!wait_all(v_full(vs), vph, 6)) { ok = false; break; }
 #pragma unroll
         for (int t = 0; t < 2; ++t) {
           if (j < it.nb[t]) {
@@ -397,13 +430,13 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q,
             if (j == 0 && !wait_all(o_empty(t), (active[t] & 1u) ^ 1u, 7)) { ok = false; break; }
             if (!wait_all(p_full(t), blocks[t] & 1u, 8)) { ok = false; break; }
             tc_fence_after_sync();
-            issue_pv_half(t, s, j == 0, 0);
+            issue_pv_half(t, vs, j == 0, 0);
             if (!wait_all(p2_full(t), blocks[t] & 1u, 13)) { ok = false; break; }
             tc_fence_after_sync();
-            issue_pv_half(t, s, j == 0, 1);
+            issue_pv_half(t, vs, j == 0, 1);
             ++blocks[t];
           }
-          if (t == 1) commit(v_empty(s));
+          if (t == 1) commit(v_empty(vs));
           if (more) {
             if (t == 0 && !wait_all(k_full(s1), ph1, 9)) { ok = false; break; }
             tc_fence_after_sync();
@@ -418,6 +451,7 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q,
       kv_base += (uint32_t)it.nb_max;
       active[0] += it.nb[0] > 0 ? 1u : 0u;
       active[1] += it.nb[1] > 0 ? 1u : 0u;
+      ++item_n;
     }
     if (leader) {
       tc_commit(drain_bar);
@@ -431,6 +465,34 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q,
       dbg[0] = (float)(clock64() - t_begin);
     }
 #endif
+  } else if (warp == 10) {
+    // ---------------------------------------------------------------- O store
+    // Finished O tiles reach global memory as bulk tensor copies out of the staging
+    // buffer: the softmax warps fill it in the order tile 0, tile 1 of each item, one
+    // lane here copies it out and hands it back.
+    if (lane == 0) {
+      uint32_t e = 0;  // tiles stored so far (barrier phases)
+      bool ok = true;
+      for (int n = 0; ok; ++n) {
+        Item it;
+        const int step = item_at(n, p, it);
+        if (step == 0) break;
+        if (step == 2) continue;
+#pragma unroll
+        for (int t = 0; t < 2; ++t) {
+          if (it.nb[t] == 0) continue;
+          if (!mbar_wait(staged, e & 1u, ctx, 17)) { ok = false; break; }
+#pragma unroll
+          for (int b = 0; b < D / 64; ++b)
+            tma_store_4d(&tm_o, o_stage + b * L::BOX_BYTES, b * 64, it.m0 + t * TILE_M, it.h, it.z);
+          tma_store_commit();
+          tma_store_wait_read<0>();
+          mbar_arrive(stage_free);
+          ++e;
+        }
+      }
+      tma_store_wait<0>();
+    }
   }
   } else {
     asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
@@ -441,6 +503,7 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q,
     const uint32_t s_tmem = tmem_base + lane_addr + (uint32_t)(t * S_COLS);
     const uint32_t o_tmem = tmem_base + lane_addr + (uint32_t)(O_COL0 + t * S_COLS);
     uint32_t blocks = 0;  // key blocks this tile has been through (barrier phases)
+    uint32_t stored = 0;  // O tiles (of either tile) staged before the current item
     bool ok = true;
     // warp-uniform wait: the vote keeps the warp converged for the .sync.aligned
     // tensor-memory accesses that follow
@@ -462,9 +525,15 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q,
 #define TICK(i)
 #endif
     const float2 scale2 = make_float2(p.scale_log2, p.scale_log2);
-    for (int round = 0, item; ok && (item = item_of_round(round)) < num_items; ++round) {
-      const Item it = decode_item(item, p);
+    for (int n = 0; ok; ++n) {
+      Item it;
+      const int step = item_at(n, p, it);
+      if (step == 0) break;
+      if (step == 2) continue;
       const int nb = it.nb[t];
+      // this tile's place in the order in which O tiles pass through the staging buffer
+      const uint32_t e = stored + ((t == 1 && it.nb[0] > 0) ? 1u : 0u);
+      stored += (it.nb[0] > 0 ? 1u : 0u) + (it.nb[1] > 0 ? 1u : 0u);
       if (nb == 0) continue;
       const int mt0 = it.m0 + t * TILE_M;
       const int row = mt0 + row_in_tile;
@@ -610,19 +679,27 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q,
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(o_empty(t));  // O may be overwritten by the next item's first P V
-      if (row < p.N) {
+      // the staging buffer is free once the copy of the tile before this one has read it
+      if (e > 0 && !wait_all(stage_free, (e - 1u) & 1u, 16)) { ok = false; break; }
+      {
         const float inv_l = 1.0f / l;
-        T *orow = reinterpret_cast<T *>(p.o) + it.z * p.oz + it.h * p.oh + (int64_t)row * p.om;
+        // rows of 128 B in the 128-byte swizzle the tensor map expects: 16-byte chunk c of
+        // row r sits at chunk c ^ (r % 8), so the 32 rows of a warp spread over all banks
+        const uint32_t row_smem = o_stage + (uint32_t)row_in_tile * 128u;
+        const uint32_t sw = (uint32_t)row_in_tile & 7u;
 #pragma unroll
         for (int q = 0; q < D / 8; ++q) {
-          uint4 out;
-          out.x = pack2<T>(__uint_as_float(acc[q * 8 + 0]) * inv_l, __uint_as_float(acc[q * 8 + 1]) * inv_l);
-          out.y = pack2<T>(__uint_as_float(acc[q * 8 + 2]) * inv_l, __uint_as_float(acc[q * 8 + 3]) * inv_l);
-          out.z = pack2<T>(__uint_as_float(acc[q * 8 + 4]) * inv_l, __uint_as_float(acc[q * 8 + 5]) * inv_l);
-          out.w = pack2<T>(__uint_as_float(acc[q * 8 + 6]) * inv_l, __uint_as_float(acc[q * 8 + 7]) * inv_l);
-          *reinterpret_cast<uint4 *>(orow + q * 8) = out;
+          const uint32_t x0 = pack2<T>(__uint_as_float(acc[q * 8 + 0]) * inv_l, __uint_as_float(acc[q * 8 + 1]) * inv_l);
+          const uint32_t x1 = pack2<T>(__uint_as_float(acc[q * 8 + 2]) * inv_l, __uint_as_float(acc[q * 8 + 3]) * inv_l);
+          const uint32_t x2 = pack2<T>(__uint_as_float(acc[q * 8 + 4]) * inv_l, __uint_as_float(acc[q * 8 + 5]) * inv_l);
+          const uint32_t x3 = pack2<T>(__uint_as_float(acc[q * 8 + 6]) * inv_l, __uint_as_float(acc[q * 8 + 7]) * inv_l);
+          const uint32_t addr = row_smem + (uint32_t)(q / 8) * L::BOX_BYTES + ((((uint32_t)q & 7u) ^ sw) << 4);
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(x0), "r"(x1), "r"(x2), "r"(x3) : "memory");
         }
-        if (p.lse != nullptr)
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(staged);
+        if (row < p.N && p.lse != nullptr)
           p.lse[(int64_t)it.zh * p.N + row] = m_used * 0.6931471805599453f + logf(l);
       }
       TICK(7)
@@ -645,7 +722,7 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q,
 
 template <typename T, int D>
 static int launch(const CUtensorMap &tq, const CUtensorMap &tk, const CUtensorMap &tv,
-                  const Params &p, cudaStream_t stream) {
+                  const CUtensorMap &to, const Params &p, cudaStream_t stream) {
   static bool configured[64] = {false};
   int dev = 0;
   B200_CUDA_OK(cudaGetDevice(&dev));
@@ -655,9 +732,18 @@ static int launch(const CUtensorMap &tq, const CUtensorMap &tk, const CUtensorMa
     B200_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     configured[dev] = true;
   }
-  const int items = ((p.N + CTA_M - 1) / CTA_M) * p.ZH;
-  const int grid = items < sm_count() ? items : sm_count();
-  kernel<<<grid, THREADS, smem, stream>>>(tq, tk, tv, p);
+  const int num_qb = (p.N + CTA_M - 1) / CTA_M;
+  const int units = ((num_qb + 1) / 2) * p.ZH;  // pairs of query blocks
+  const int grid = units < sm_count() ? units : sm_count();
+  Params pw = p;
+  // heads per wave: about 8 MiB of K and V (measured on [8,32,4096,128]: 4 heads per wave
+  // 1135 TFLOP/s causal, 16 heads 1122, 64 heads 1076; B200OPS_ATTN_WAVE overrides)
+  static const int wave_env = getenv("B200OPS_ATTN_WAVE") ? atoi(getenv("B200OPS_ATTN_WAVE")) : 0;
+  const int64_t kv_bytes = 2 * (int64_t)p.N * D * (int64_t)sizeof(T);
+  pw.wave_heads = wave_env > 0 ? wave_env : (int)((8 << 20) / kv_bytes);
+  if (pw.wave_heads < 1) pw.wave_heads = 1;
+  if (pw.wave_heads > p.ZH) pw.wave_heads = p.ZH;
+  kernel<<<grid, THREADS, smem, stream>>>(tq, tk, tv, to, pw);
   B200_CUDA_OK(cudaGetLastError());
   return B200_OK;
 }

@@ -521,13 +521,15 @@ extern "C" int b200_attn_fwd(const b200_tensor *q, const b200_tensor *k, const b
     pair::Params pp;
     pp.H = p.H; pp.N = p.N; pp.ZH = (int)(Z * H);
     pp.scale_log2 = p.scale_log2; pp.causal = p.causal;
-    pp.o = p.o; pp.oz = p.oz; pp.oh = p.oh; pp.om = p.om; pp.lse = p.lse;
+    pp.lse = p.lse;
     pp.idesc_qk = p.idesc_qk; pp.idesc_pv = p.idesc_pv; pp.status = p.status;
+    CUtensorMap to;
+    if ((st = encode_qkv(&to, o))) return st;
     if (q->dtype == B200_DTYPE_BFLOAT16)
-      return D == 128 ? pair::launch<__nv_bfloat16, 128>(tq, tk, tv, pp, s)
-                      : pair::launch<__nv_bfloat16, 64>(tq, tk, tv, pp, s);
-    return D == 128 ? pair::launch<__half, 128>(tq, tk, tv, pp, s)
-                    : pair::launch<__half, 64>(tq, tk, tv, pp, s);
+      return D == 128 ? pair::launch<__nv_bfloat16, 128>(tq, tk, tv, to, pp, s)
+                      : pair::launch<__nv_bfloat16, 64>(tq, tk, tv, to, pp, s);
+    return D == 128 ? pair::launch<__half, 128>(tq, tk, tv, to, pp, s)
+                    : pair::launch<__half, 64>(tq, tk, tv, to, pp, s);
   }
   const bool pt = p_in_tmem();
   const int zh = (int)(Z * H);
