@@ -9,11 +9,16 @@
 //   warps 4-7   softmax + epilogue of tile 1
 //   warp  8     TMA producer: Q (both tiles) per item, K / V blocks in 2-stage rings
 //               shared by both tiles (K and V are read once per 256 rows)
-//   warps 10-11 idle (they complete the third warpgroup so that setmaxnreg can move
+//   warp  10    one lane copies finished O tiles from a staging buffer in shared memory
+//               to global memory (bulk tensor stores)
+//   warp  11    idle (it completes the third warpgroup so that setmaxnreg can move
 //               registers from it to the softmax warpgroups)
-//   warp  9     one lane issues tcgen05.mma in the order
-//                 S0 = Q0 K(0)^T, S1 = Q1 K(0)^T, then per key block j:
+//   warp  9     issues tcgen05.mma (whole warp in the loop, one elected lane issuing) in the
+//               order S0 = Q0 K(0)^T, S1 = Q1 K(0)^T, then per key block j:
 //                 O0 += P0(j) V(j), S0 = Q0 K(j+1)^T, O1 += P1(j) V(j), S1 = Q1 K(j+1)^T
+//               and, when the causal mask leaves tile 0 without a block in the item's last
+//               step, the next item's S0 = Q0 K(0)^T in that slot (Q has one barrier pair
+//               per tile for this)
 //
 // Tensor memory (512 columns): S0 | S1 | O0 | O1, 128 columns each; P(j) overwrites
 // the first 64 columns of its own S buffer as packed 16-bit pairs, so S(j+1) of a
@@ -227,7 +232,8 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q,
   const uint32_t v_smem = smem_base + L::V_OFF;
   const uint32_t o_stage = smem_base + L::O_OFF;
   const uint32_t bar0 = smem_base + L::BAR_OFF;
-  const uint32_t q_full = bar0, q_empty = bar0 + 8;
+  auto q_full = [&](int t) { return bar0 + 8u * t; };           // one pair per tile, so that
+  auto q_empty = [&](int t) { return bar0 + 8u * (27 + t); };   // tile 0 can move on alone
   auto k_full = [&](uint32_t s) { return bar0 + 8u * (2 + s); };
   auto k_empty = [&](uint32_t s) { return bar0 + 8u * (4 + s); };
   auto v_full = [&](uint32_t s) { return bar0 + 8u * (23 + s); };
@@ -240,7 +246,7 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q,
   auto o_empty = [&](int t) { return bar0 + 8u * (16 + t); };
   const uint32_t drain_bar = bar0 + 8u * 18;
   auto p2_full = [&](int t) { return bar0 + 8u * (19 + t); };  // second half of P
-  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem_gen + L::BAR_OFF + 8 * (23 + 2 * V_STAGES));
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem_gen + L::BAR_OFF + 8 * 29);
   volatile uint32_t *abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5;
@@ -248,8 +254,6 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q,
   const WaitCtx ctx{abort_flag, p.status};
 
   if (threadIdx.x == 0) {
-    mbar_init(q_full, 1);
-    mbar_init(q_empty, 1);
     for (int s = 0; s < KV_STAGES; ++s) {
       mbar_init(k_full(s), 1);
       mbar_init(k_empty(s), 1);
@@ -259,6 +263,8 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q,
       mbar_init(v_empty(s), 1);
     }
     for (int t = 0; t < 2; ++t) {
+      mbar_init(q_full(t), 1);
+      mbar_init(q_empty(t), 1);
       mbar_init(s_full(t), 1);
       mbar_init(p_full(t), TILE_M / 32);   // one arrival per softmax warp
       mbar_init(p2_full(t), TILE_M / 32);
@@ -291,23 +297,25 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q,
     // ---------------------------------------------------------------- producer
     if (lane == 0) {
       uint32_t kv_it = 0, item_n = 0;
-      uint32_t issued = 0, parity = 0;  // bit s: K stage, bit 2+s: V stage, bit 8: Q
+      uint32_t issued = 0, parity = 0;  // bit s: K stage, bit 2+s: V stage, bit 8+t: Q tile
       bool ok = true;
       for (int n = 0; ok; ++n) {
         Item it;
         const int step = item_at(n, p, it);
         if (step == 0) break;
         if (step == 2) continue;
-        if (!mbar_wait(q_empty, (item_n & 1u) ^ 1u, ctx, 1)) { ok = false; break; }
-        mbar_arrive_expect_tx(q_full, 2 * L::TILE_BYTES);
 #pragma unroll
-        for (int t = 0; t < 2; ++t)
+        for (int t = 0; t < 2; ++t) {
+          if (!mbar_wait(q_empty(t), (item_n & 1u) ^ 1u, ctx, 1)) { ok = false; break; }
+          mbar_arrive_expect_tx(q_full(t), L::TILE_BYTES);
 #pragma unroll
           for (int b = 0; b < D / 64; ++b)
-            tma_load_4d(q_smem + t * L::TILE_BYTES + b * L::BOX_BYTES, &tm_q, q_full, b * 64,
+            tma_load_4d(q_smem + t * L::TILE_BYTES + b * L::BOX_BYTES, &tm_q, q_full(t), b * 64,
                         it.m0 + t * TILE_M, it.h, it.z);
-        issued |= 256u;
-        parity = (parity & ~256u) | ((item_n & 1u) << 8);
+          issued |= 256u << t;
+          parity = (parity & ~(256u << t)) | ((item_n & 1u) << (8 + t));
+        }
+        if (!ok) break;
         for (int j = 0; j < it.nb_max; ++j, ++kv_it) {
           const uint32_t s = kv_it & 1u, ph = (kv_it >> 1) & 1u;
           if (!mbar_wait(k_empty(s), ph ^ 1u, ctx, 2)) { ok = false; break; }
@@ -332,7 +340,8 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q,
       }
       if (!ok) {
         // copies already issued still target this CTA's shared memory
-        if (issued & 256u) mbar_wait_drain(q_full, (parity >> 8) & 1u);
+        for (int t = 0; t < 2; ++t)
+          if (issued & (256u << t)) mbar_wait_drain(q_full(t), (parity >> (8 + t)) & 1u);
         for (uint32_t s = 0; s < KV_STAGES; ++s)
           if (issued & (1u << s)) mbar_wait_drain(k_full(s), (parity >> s) & 1u);
         for (uint32_t s = 0; s < V_STAGES; ++s)
@@ -401,20 +410,38 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q,
     auto commit = [&](uint32_t bar) {
       if (leader) tc_commit(bar);
     };
-    for (int n = 0; ok; ++n) {
-      Item it;
-      const int step = item_at(n, p, it);
-      if (step == 0) break;
-      if (step == 2) continue;
-      if (!wait_all(q_full, item_n & 1u, 4)) { ok = false; break; }
+    // the item after the current one is known one item ahead: when tile 0 runs out of key
+    // blocks before tile 1 (causal mask), the next item's first S of tile 0 is issued in the
+    // otherwise idle slot instead of waiting for tile 1's last block
+    auto fetch = [&](int &n, Item &out) {
+      for (;; ++n) {
+        const int step = item_at(n, p, out);
+        if (step == 0) return false;
+        if (step == 1) { ++n; return true; }
+      }
+    };
+    int n_next = 0;
+    Item it, nx;
+    bool has = fetch(n_next, it);
+    bool early0 = false;  // S(0) of tile 0 of the current item was issued during the last one
+    while (ok && has) {
+      const bool has_nx = fetch(n_next, nx);
+      bool early_next = false;
       {  // S(0) of both tiles
         const uint32_t s = kv_base & 1u, ph = (kv_base >> 1) & 1u;
+        if (!early0) {
+          if (!wait_all(q_full(0), item_n & 1u, 4)) { ok = false; break; }
+          if (!wait_all(k_full(s), ph, 5)) { ok = false; break; }
+          tc_fence_after_sync();
+          if (it.nb[0] > 0) issue_qk(0, s);
+          if (it.nb[0] <= 1) commit(q_empty(0));
+        }
+        if (!wait_all(q_full(1), item_n & 1u, 4)) { ok = false; break; }
         if (!wait_all(k_full(s), ph, 5)) { ok = false; break; }
         tc_fence_after_sync();
-        if (it.nb[0] > 0) issue_qk(0, s);
         if (it.nb[1] > 0) issue_qk(1, s);
         commit(k_empty(s));
-        if (it.nb_max == 1) commit(q_empty);
+        if (it.nb[1] <= 1) commit(q_empty(1));
       }
       for (int j = 0; ok && j < it.nb_max; ++j) {
         const uint32_t kv = kv_base + (uint32_t)j;
@@ -435,16 +462,26 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q,
             tc_fence_after_sync();
             issue_pv_half(t, vs, j == 0, 1);
             ++blocks[t];
+          } else if (t == 0 && !more && has_nx && nx.nb[0] > 0) {
+            // tile 0 has no block j and nothing follows in this item
+            const uint32_t kvn = kv_base + (uint32_t)it.nb_max;
+            const uint32_t sn = kvn & 1u, phn = (kvn >> 1) & 1u;
+            if (!wait_all(q_full(0), (item_n + 1u) & 1u, 4)) { ok = false; break; }
+            if (!wait_all(k_full(sn), phn, 5)) { ok = false; break; }
+            tc_fence_after_sync();
+            issue_qk(0, sn);
+            if (nx.nb[0] <= 1) commit(q_empty(0));
+            early_next = true;
           }
           if (t == 1) commit(v_empty(vs));
           if (more) {
             if (t == 0 && !wait_all(k_full(s1), ph1, 9)) { ok = false; break; }
             tc_fence_after_sync();
-            if (j + 1 < it.nb[t]) issue_qk(t, s1);
-            if (t == 1) {
-              commit(k_empty(s1));
-              if (j + 2 == it.nb_max) commit(q_empty);  // last S of this item issued
+            if (j + 1 < it.nb[t]) {
+              issue_qk(t, s1);
+              if (j + 2 == it.nb[t]) commit(q_empty(t));  // last S of this tile in this item
             }
+            if (t == 1) commit(k_empty(s1));
           }
         }
       }
@@ -452,6 +489,9 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q,
       active[0] += it.nb[0] > 0 ? 1u : 0u;
       active[1] += it.nb[1] > 0 ? 1u : 0u;
       ++item_n;
+      it = nx;
+      has = has_nx;
+      early0 = early_next;
     }
     if (leader) {
       tc_commit(drain_bar);

@@ -83,7 +83,6 @@ constexpr int B_STAGE_BYTES = 4 * B_BOX_BYTES;  // 32 KiB
 constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
 constexpr int TMEM_COLS = 512;
 constexpr int THREADS = 192;
-constexpr int GROUP_M = 16;  // m-blocks per raster group (L2 reuse of A and B)
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
 
 struct Params {
@@ -104,6 +103,7 @@ struct Params {
   void *c_rank[8];
   int scatter_rows;
   int scatter_slot;
+  int group_m;  // m-blocks per raster group
 };
 
 __device__ __forceinline__ float gelu_tanh_fast(float z) {
@@ -248,12 +248,12 @@ __device__ __forceinline__ void epilogue_tile_dual(uint32_t t_row, const Params 
 
 // tile index -> block coordinates, grouped so that concurrently running CTAs
 // share A row-blocks and B column-blocks in L2
-__device__ __forceinline__ void tile_coords(int tile, int m_blocks, int n_blocks, int &mb,
-                                            int &nb) {
-  const int per_group = GROUP_M * n_blocks;
+__device__ __forceinline__ void tile_coords(int tile, int m_blocks, int n_blocks, int group_m,
+                                            int &mb, int &nb) {
+  const int per_group = group_m * n_blocks;
   const int group = tile / per_group;
-  const int first_m = group * GROUP_M;
-  const int rows = min(GROUP_M, m_blocks - first_m);
+  const int first_m = group * group_m;
+  const int rows = min(group_m, m_blocks - first_m);
   const int in_group = tile - group * per_group;
   mb = first_m + in_group % rows;
   nb = in_group / rows;
@@ -324,7 +324,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
       bool ok = true;
       for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
         int mb, nb;
-        tile_coords(tile, m_blocks, n_blocks, mb, nb);
+        tile_coords(tile, m_blocks, n_blocks, p.group_m, mb, nb);
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1u, ctx, 1)) { ok = false; break; }
           mbar_arrive_expect_tx(full_bar(stage), STAGE_BYTES);
@@ -411,7 +411,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
     OutT *c = reinterpret_cast<OutT *>(p.c);
     for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
       int mb, nb;
-      tile_coords(tile, m_blocks, n_blocks, mb, nb);
+      tile_coords(tile, m_blocks, n_blocks, p.group_m, mb, nb);
       // the vote keeps the warp converged for the .sync.aligned TMEM loads below
       if (!__all_sync(0xffffffffu, mbar_wait(acc_full_bar(acc), acc_phase, ctx, 4))) {
         ok = false;
@@ -685,6 +685,21 @@ static int gemm_impl(const b200_tensor *a, const b200_tensor *b, const b200_tens
   p.b_sbo = 1024;         // pitch between groups of 8 K-rows
   p.scatter_rows = 0;
   p.scatter_slot = 0;
+  {
+    // Raster groups: as many m-blocks as keep a group's rows of A (group_m x 128 x K)
+    // within about 40 MiB, the part of the L2 that was seen to hold a panel while B streams
+    // past it; the groups are evened out.  8192^3: 4 groups of 16 m-blocks;
+    // 4097 x 11008 x 4096: one group, A read from memory once (1330 -> 1370 TFLOP/s).
+    static const int group_env =
+        getenv("B200OPS_GEMM_GROUP_M") ? atoi(getenv("B200OPS_GEMM_GROUP_M")) : 0;
+    const int m_blocks = (int)((M + BM - 1) / BM);
+    const int64_t block_bytes = (int64_t)BM * K * (int64_t)dtype_size(a->dtype);
+    int gmax = (int)(((int64_t)40 << 20) / (block_bytes > 0 ? block_bytes : 1));
+    if (gmax < 4) gmax = 4;
+    const int groups = (m_blocks + gmax - 1) / gmax;
+    p.group_m = group_env > 0 ? group_env : (m_blocks + groups - 1) / (groups > 0 ? groups : 1);
+    if (p.group_m < 1) p.group_m = 1;
+  }
   for (int r = 0; r < 8; ++r) p.c_rank[r] = nullptr;
   if (scatter != nullptr) {
     p.scatter_rows = (int)scatter->rows;
