@@ -49,8 +49,8 @@ NCU_TRAFFIC = {
     "softmax": 140_785_000,
     "rmsnorm": 212_674_000,
     "gemm_8192": 1_134_959_000,
-    "gemm_ragged": 369_771_000,
-    "attention": 2_301_736_000,
+    "gemm_ragged": 197_744_000,
+    "attention": 1_036_044_000,
 }
 
 
@@ -82,7 +82,7 @@ class ClockSampler:
         try:
             self._proc = subprocess.Popen(
                 ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
-                 "-lms", "100", "-i", str(self._index)],
+                 "-lms", "25", "-i", str(self._index)],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             return
@@ -109,10 +109,9 @@ class ClockSampler:
             except subprocess.TimeoutExpired:
                 self._proc.kill()
 
-    def summary(self, t0, t1):
+    def summary(self, t0, t1, label="headline timed region"):
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         window = [s for s in self.samples if t0 <= s["t"] <= t1]
-        label = "headline timed region"
         if not window:  # region shorter than the sampling period: use the loaded samples
             busy = [s for s in self.samples if s["power"] > 250.0]
             window, label = (busy or self.samples), "whole run, samples under load"
@@ -268,8 +267,9 @@ def bench_rmsnorm(torch, ops, dist, steps, warmup, peaks, source):
     def launch(i):
         ops.rmsnorm(xs[i % nsets], w, ys[i % nsets], r, eps=1e-6, stream=stream)
 
-    region_ms, launch_ms, _ = time_steps(torch, dist, launch, steps, warmup)
+    region_ms, launch_ms, window = time_steps(torch, dist, launch, steps, warmup)
     out = roofline("hbm", RMS_BYTES, launch_ms, peaks, source, NCU_TRAFFIC["rmsnorm"])
+    out["window"] = window
     out.update({"workload": "rmsnorm_fp32_8192x4096", "ms_per_step": round(region_ms, 5),
                 "value": round(RMS_BYTES * dist.world / (region_ms * 1e-3) / 1e9, 2),
                 "unit": "GB/s", "gpu_launches": steps})
@@ -293,10 +293,11 @@ def bench_gemm(torch, ops, dist, steps, warmup, peaks, source, shape, key):
         a, b, c = sets[i % nsets]
         ops.gemm(a, b, c, bias=bias, act=abi.ACT_GELU_TANH, stream=stream)
 
-    region_ms, launch_ms, _ = time_steps(torch, dist, launch, steps, warmup)
+    region_ms, launch_ms, window = time_steps(torch, dist, launch, steps, warmup)
     ops.device_status(stream)
     flops = 2 * m * n * k
     out = roofline("tensor", flops, launch_ms, peaks, source, NCU_TRAFFIC[key])
+    out["window"] = window
     out.update({"workload": f"gemm_bf16_bias_gelu_tanh_{m}x{n}x{k}",
                 "ms_per_step": round(region_ms, 5),
                 "value": round(flops * dist.world / (region_ms * 1e-3) / 1e12, 2),
@@ -316,10 +317,11 @@ def bench_attention(torch, ops, dist, steps, warmup, peaks, source):
     def launch(i):
         ops.attention(q, k, v, o, lse=lse, scale=1.0 / d ** 0.5, causal=True, stream=stream)
 
-    region_ms, launch_ms, _ = time_steps(torch, dist, launch, steps, warmup)
+    region_ms, launch_ms, window = time_steps(torch, dist, launch, steps, warmup)
     ops.device_status(stream)
     flops = 4 * z * h * d * n * (n + 1) // 2  # causal-exact: 2 matmuls over the kept triangle
     out = roofline("tensor", flops, launch_ms, peaks, source, NCU_TRAFFIC["attention"])
+    out["window"] = window
     out.update({"workload": "attn_fwd_causal_bf16_8x32x4096x128", "flop_convention": "causal-exact",
                 "ms_per_step": round(region_ms, 5),
                 "value": round(flops * dist.world / (region_ms * 1e-3) / 1e12, 2),
@@ -338,9 +340,10 @@ def bench_tp_mlp(torch, dist, steps, warmup, peaks, source, collective="nccl"):
     def launch(i):
         mlp.forward(x, y)
 
-    region_ms, launch_ms, _ = time_steps(torch, dist, launch, steps, warmup)
+    region_ms, launch_ms, window = time_steps(torch, dist, launch, steps, warmup)
     flops = 3 * 2 * 4096 * 4096 * 14336
     out = roofline("tensor", flops // dist.world, launch_ms, peaks, source, None)
+    out["window"] = window
     out.update({"workload": f"tp_swiglu_mlp_bf16_tp{dist.world}", "scaling": "strong",
                 "collective": ("NCCL all-reduce per row chunk, overlapped with the next chunk's GEMM"
                                if collective == "nccl" else
@@ -411,7 +414,7 @@ def reference_arm(args):
 def main():
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
-    parser.add_argument("--steps", type=int, default=2000)
+    parser.add_argument("--steps", type=int, default=6000)
     parser.add_argument("--warmup", type=int, default=20)
     parser.add_argument("--impl", default="native", choices=["native", "reference"])
     parser.add_argument("--ops", default="all",
@@ -468,9 +471,16 @@ def main():
                 extras["tp_mlp_peer"] = {"unavailable": f"{type(exc).__name__}: {exc}"[:300]}
 
     baseline = cpu_baseline() if (dist.rank == 0 and dist.world == 1) else None
+    if dist.rank != 0:
+        for extra in extras.values():
+            extra.pop("window", None)
     if dist.rank == 0:
         sampler.stop()
         clocks = sampler.summary(*head["window"])
+        for extra in extras.values():  # each operator's own clock record
+            if "window" in extra:
+                extra["clocks"] = sampler.summary(*extra.pop("window"),
+                                                  label="this operator's timed region")
         value = SOFTMAX_BYTES * dist.world / (head["region_ms"] * 1e-3) / 1e9
         line = {
             "metric": "masked_softmax_fp16_hbm_throughput", "value": round(value, 2),
