@@ -67,18 +67,28 @@ def load_peaks():
 
 # --------------------------------------------------------------------------- clocks
 class ClockSampler:
-    """nvidia-smi samples (SM clock, power, throttle reasons) while kernels run."""
+    """SM clock, power and throttle reasons sampled while kernels run: NVML polled from a
+    thread every 2 ms (read-only queries), or ``nvidia-smi -lms`` lines where NVML cannot be
+    loaded.  Each sample carries the flags hw_slowdown, hw_thermal_slowdown,
+    sw_thermal_slowdown, sw_power_cap in that order."""
     QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
              "clocks_event_reasons.sw_power_cap")
+    # nvmlClocksEventReason bits: hw slowdown, hw thermal, sw thermal, sw power cap
+    REASON_BITS = (0x8, 0x40, 0x20, 0x4)
 
-    def __init__(self, index: int):
+    def __init__(self, index: int, uuid: str | None = None):
         self.samples = []
+        self.source = None
         self._proc = None
         self._thread = None
         self._index = index
+        self._uuid = uuid
+        self._stop = threading.Event()
 
     def start(self):
+        if self._start_nvml():
+            return
         try:
             self._proc = subprocess.Popen(
                 ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
@@ -86,8 +96,43 @@ class ClockSampler:
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             return
+        self.source = "nvidia-smi"
         self._thread = threading.Thread(target=self._read, daemon=True)
         self._thread.start()
+
+    def _start_nvml(self):
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            handle = None
+            if self._uuid:
+                try:
+                    handle = pynvml.nvmlDeviceGetHandleByUUID(self._uuid.encode())
+                except Exception:  # noqa: BLE001 - unknown spelling of the id: use the index
+                    handle = None
+            if handle is None:
+                handle = pynvml.nvmlDeviceGetHandleByIndex(self._index)
+            max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(handle, pynvml.NVML_CLOCK_SM))
+        except Exception:  # noqa: BLE001 - no NVML here: fall back to nvidia-smi
+            return False
+
+        def poll():
+            while not self._stop.is_set():
+                try:
+                    mhz = float(pynvml.nvmlDeviceGetClockInfo(handle, pynvml.NVML_CLOCK_SM))
+                    watts = pynvml.nvmlDeviceGetPowerUsage(handle) / 1000.0
+                    mask = int(pynvml.nvmlDeviceGetCurrentClocksEventReasons(handle))
+                except Exception:  # noqa: BLE001
+                    break
+                flags = ["Active" if mask & bit else "Not Active" for bit in self.REASON_BITS]
+                self.samples.append({"t": time.monotonic(), "sm": mhz, "max": max_mhz,
+                                     "power": watts, "flags": flags})
+                time.sleep(0.002)
+
+        self.source = "nvml"
+        self._thread = threading.Thread(target=poll, daemon=True)
+        self._thread.start()
+        return True
 
     def _read(self):
         for line in self._proc.stdout:
@@ -102,6 +147,9 @@ class ClockSampler:
                 continue
 
     def stop(self):
+        self._stop.set()
+        if self._thread is not None and self.source == "nvml":
+            self._thread.join(timeout=2)
         if self._proc is not None:
             self._proc.terminate()
             try:
@@ -117,12 +165,13 @@ class ClockSampler:
             window, label = (busy or self.samples), "whole run, samples under load"
         if not window:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0,
-                    "window": "nvidia-smi gave no samples"}
+                    "window": "no clock samples"}
         reasons = sorted({names[i] for s in window for i, f in enumerate(s["flags"])
                           if f.lower().startswith("active")})
         return {"sm_mhz": float(np.median([s["sm"] for s in window])),
                 "sm_max_mhz": float(window[0]["max"]), "reasons": reasons,
-                "samples": len(window), "window": label,
+                "sm_min_mhz": float(min(s["sm"] for s in window)),
+                "samples": len(window), "window": label, "source": self.source,
                 "power_w_max": float(max(s["power"] for s in window))}
 
 
@@ -435,7 +484,8 @@ def main():
     dist.init(torch)
     peaks, source = load_peaks()
     warmup = max(args.warmup, 3)
-    sampler = ClockSampler(dist.local_rank)
+    uuid = getattr(torch.cuda.get_device_properties(dist.local_rank), "uuid", None)
+    sampler = ClockSampler(dist.local_rank, f"GPU-{uuid}" if uuid is not None else None)
     if dist.rank == 0:
         sampler.start()
 

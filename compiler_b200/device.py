@@ -134,11 +134,13 @@ class PinnedArray:
 
 class EventTimer:
     """``with device.timer() as t: launch()`` -> ``t.seconds`` from CUDA events on
-    the device's stream (CudaEventTimer, ops/harness/opslib/devices/cuda.py:138-167)."""
+    the device's stream (CudaEventTimer, ops/harness/opslib/devices/cuda.py:138-167).
+    One timer serves any number of ``with`` blocks; its events live until it is closed
+    or collected."""
 
     def __init__(self, stream=0):
         self._stream = stream
-        self.seconds = None
+        self._seconds = None
         lib = abi.lib()
         start, stop = ctypes.c_void_p(), ctypes.c_void_p()
         abi.check(lib.b200_event_create(ctypes.byref(start)))
@@ -154,16 +156,38 @@ class EventTimer:
         abi.check(lib.b200_event_record(self._stop, self._stream))
         ms = ctypes.c_float()
         abi.check(lib.b200_event_elapsed_ms(self._start, self._stop, ctypes.byref(ms)))
-        self.seconds = ms.value * 1e-3
-        lib.b200_event_destroy(self._start)
-        lib.b200_event_destroy(self._stop)
+        self._seconds = ms.value * 1e-3
         return False
+
+    @property
+    def seconds(self):
+        if self._seconds is None:
+            raise RuntimeError("timer read before its context exited")
+        return self._seconds
+
+    def close(self):
+        if self._start is not None:
+            lib = abi.lib()
+            lib.b200_event_destroy(self._start)
+            lib.b200_event_destroy(self._stop)
+            self._start = self._stop = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:  # noqa: BLE001 - interpreter shutdown
+            pass
+
+
+def _KEEP(*_objects):  # noqa: N802 - a no-op plan step that only holds references
+    return abi.OK
 
 
 class B200Device:
     """Compiler device for one B200 (``make_device("compiler_b200.device:make_device")``)."""
 
     name = "b200-native"
+    PLAN_LIMIT = 512  # bound launches remembered per device
 
     def __init__(self, device_id: int = 0, registry=None):
         from compiler_b200 import registry as _registry
@@ -174,6 +198,7 @@ class B200Device:
         self.stream = 0  # launches and copies share the default stream: ordered
         self._pinned = None
         self.launch_count = 0
+        self._plans = {}
 
     # ------------------------------------------------------------ lifecycle
     def alloc(self, shape, dtype):
@@ -316,8 +341,47 @@ class B200Device:
     def launch(self, kernel, grid, positional, keywords):
         """Resolve ``kernel`` to its native operator and enqueue it.  No Triton, no
         host arithmetic; an unknown kernel raises ``UnsupportedLaunch``."""
-        self.registry.launch(self, kernel, grid, positional, keywords)
+        key = self._plan_key(kernel, grid, positional, keywords)
+        plan = self._plans.get(key) if key is not None else None
+        if plan is not None:
+            abi.replay(plan)
+        elif key is None:
+            self.registry.launch(self, kernel, grid, positional, keywords)
+        else:
+            with abi.recording() as recorded:
+                self.registry.launch(self, kernel, grid, positional, keywords)
+            if len(self._plans) >= self.PLAN_LIMIT:
+                self._plans.clear()
+            # the plan keeps the kernel object alive, so its id cannot name another kernel
+            self._plans[key] = recorded.calls + [(_KEEP, (kernel,))]
         self.launch_count += 1
+
+    @staticmethod
+    def _plan_key(kernel, grid, positional, keywords):
+        """What a bound launch depends on: the kernel object, the grid, and per argument the
+        device address, shape and dtype of a buffer or the value of a scalar.  Binding the
+        same key again would rebuild the same library calls, so they are recorded once and
+        replayed (a repeated launch then costs a few microseconds of host time instead of the
+        whole binding path -- benchmarks time launches back to back).  ``None`` = not
+        cacheable (a callable grid, an argument that does not hash)."""
+        if callable(grid):
+            return None
+        parts = [id(kernel), tuple(grid)]
+        try:
+            for value in list(positional) + sorted(keywords.items()):
+                name = None
+                if isinstance(value, tuple):
+                    name, value = value
+                if isinstance(value, B200Buffer):
+                    value = ("buffer", value.ptr, value.shape, str(value.dtype))
+                elif hasattr(value, "data_ptr"):
+                    return None  # foreign device arrays: strides are not part of the key
+                parts.append((name, value))
+            key = tuple(parts)
+            hash(key)
+        except TypeError:
+            return None
+        return key
 
     def check_status(self):
         """Drain the stream and raise if a kernel's bounded wait expired."""

@@ -110,9 +110,56 @@ _lock = threading.Lock()
 _lib = None
 
 
+class _Recorder:
+    """Stands in for the library while a launch is being recorded: every entry point called
+    through it runs as usual and is logged with its (ctypes) arguments."""
+
+    def __init__(self, real):
+        self._real = real
+        self.calls = []
+
+    def __getattr__(self, name):
+        fn = getattr(self._real, name)
+
+        def call(*args):
+            self.calls.append((fn, args))
+            return fn(*args)
+        return call
+
+
+_recorder = None
+
+
+class recording:  # noqa: N801 - used as ``with abi.recording() as plan:``
+    """Log the library calls made inside the block.  ``plan.calls`` can be replayed with
+    :func:`replay` as long as the buffers the calls point at are alive and unmoved: the
+    descriptors are kept by the log, the device memory they name is not.  One recording at a
+    time, on the thread that launches."""
+
+    def __enter__(self):
+        global _recorder
+        if _recorder is not None:
+            raise RuntimeError("a launch recording is already open")
+        _recorder = _Recorder(lib())
+        return _recorder
+
+    def __exit__(self, *exc):
+        global _recorder
+        _recorder = None
+        return False
+
+
+def replay(calls) -> None:
+    """Issue recorded library calls again, checking every status."""
+    for fn, args in calls:
+        check(fn(*args))
+
+
 def lib() -> ctypes.CDLL:
     """Build (if stale) and load the library; raises when that is impossible."""
     global _lib
+    if _recorder is not None:
+        return _recorder
     if _lib is not None:
         return _lib
     with _lock:

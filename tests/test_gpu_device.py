@@ -116,3 +116,44 @@ def test_row_pipeline_matches_single_launch(device):
     ops.softmax(dx, dy, causal_mod=True, row_offset=123)
     assert np.array_equal(out, device.download(dy))
     oracle.compare(out.astype(np.float64), oracle.masked_softmax_ref(hx.array, 123), 1e-2, 1e-2)
+
+
+def test_repeated_launches_replay_the_bound_calls(device):
+    """A launch is bound once per (kernel, grid, buffers, scalars): later launches replay the
+    recorded library calls, read the buffers' current contents, and a different buffer or
+    scalar binds anew; a rejected launch leaves nothing behind."""
+    import golden_cases
+    from compiler_b200.registry import UnsupportedLaunch
+    case, _ = golden_cases.load("softmax__4x97__float32")
+    staged = harness.stage_case(case, device)
+    before = len(device._plans)
+    staged.launch()
+    assert len(device._plans) == before + 1
+    first = staged.outputs()["y_ptr"]
+    x = np.asarray(case["args"]["x_ptr"], dtype=np.float32)
+    oracle.compare(first, oracle.softmax_ref(x), 2e-3, 2e-3)
+    # same buffers, new contents: the replayed launch computes on what is there now
+    device.copy_in(staged.buffer("x_ptr"), np.ascontiguousarray(-x), sync=True)
+    count = device.launch_count
+    staged.launch()
+    assert len(device._plans) == before + 1 and device.launch_count == count + 1
+    oracle.compare(staged.outputs()["y_ptr"], oracle.softmax_ref(-x), 2e-3, 2e-3)
+    # another staging of the same case has other buffers: a second plan
+    other = harness.stage_case(case, device)
+    other.launch()
+    assert len(device._plans) == before + 2
+    oracle.compare(other.outputs()["y_ptr"], oracle.softmax_ref(x), 2e-3, 2e-3)
+    # one timer serves many launches (the benchmark runner keeps one for all its samples)
+    timer = device.timer()
+    seconds = []
+    for _ in range(5):
+        with timer:
+            staged.launch()
+        seconds.append(timer.seconds)
+    assert all(0 < s < 1.0 for s in seconds)
+    timer.close()
+    unknown = golden_cases.make_handle("no_such_kernel", ["x_ptr", "y_ptr"])
+    size = len(device._plans)
+    with pytest.raises(UnsupportedLaunch):
+        device.launch(unknown, (1,), [staged.buffer("x_ptr"), staged.buffer("y_ptr")], {})
+    assert len(device._plans) == size
