@@ -378,6 +378,30 @@ def bench_attention(torch, ops, dist, steps, warmup, peaks, source):
     return out
 
 
+def bench_attention_decode(torch, ops, dist, steps, warmup, peaks, source):
+    """One query row per (batch, head) against a K / V cache of 4096 keys: the K and V of
+    8 x 32 heads are 537 MB, read once per launch (four times the L2)."""
+    stream = torch.cuda.current_stream().cuda_stream
+    rows, n, d = 8 * 32, 4096, 128
+    gen = torch.Generator(device="cuda").manual_seed(36 + dist.rank)
+    q = torch.randn((rows, d), generator=gen, device="cuda").to(torch.bfloat16)
+    k, v = (torch.randn((rows, n, d), generator=gen, device="cuda").to(torch.bfloat16)
+            for _ in range(2))
+    o = torch.empty_like(q)
+
+    def launch(i):
+        ops.attention_decode(q, k, v, o, scale=1.0 / d ** 0.5, stream=stream)
+
+    region_ms, launch_ms, window = time_steps(torch, dist, launch, steps, warmup)
+    nbytes = 2 * rows * n * d * 2
+    out = roofline("hbm", nbytes, launch_ms, peaks, source, None)
+    out["window"] = window
+    out.update({"workload": "attn_decode_bf16_256rows_4096keys_128", "ms_per_step": round(region_ms, 5),
+                "value": round(nbytes * dist.world / (region_ms * 1e-3) / 1e9, 2),
+                "unit": "GB/s", "gpu_launches": 2 * steps})
+    return out
+
+
 def bench_tp_mlp(torch, dist, steps, warmup, peaks, source, collective="nccl"):
     from compiler_b200 import tp_mlp
     mlp = tp_mlp.TensorParallelMLP.synthetic(hidden=4096, ffn=14336, rank=dist.rank,
@@ -467,7 +491,7 @@ def main():
     parser.add_argument("--warmup", type=int, default=20)
     parser.add_argument("--impl", default="native", choices=["native", "reference"])
     parser.add_argument("--ops", default="all",
-                        help="comma list of extra operators: rmsnorm,gemm,gemm_ragged,attention,"
+                        help="comma list of extra operators: rmsnorm,gemm,gemm_ragged,attention,attention_decode,"
                              "tp_mlp,none,all")
     args = parser.parse_args()
     if args.impl == "reference":
@@ -511,6 +535,9 @@ def main():
     if want("attention"):
         extras["attention"] = bench_attention(torch, ops, dist, max(3, min(args.steps, 10)), 3,
                                               peaks, source)
+    if want("attention_decode"):
+        extras["attention_decode"] = bench_attention_decode(torch, ops, dist, extra_steps, 3,
+                                                            peaks, source)
     if want("tp_mlp") and dist.world > 1:
         extras["tp_mlp"] = bench_tp_mlp(torch, dist, extra_steps, 3, peaks, source)
         if 4096 % (128 * dist.world) == 0:

@@ -78,6 +78,18 @@ def attention(q, k, v, o, *, lse=None, scale=None, causal=True, stream=0):
                                       float(scale), 1 if causal else 0, stream))
 
 
+def attention_decode(q, k, v, out, *, scale=None, stream=0):
+    """out[b] = softmax(scale * K[b // group] q[b]) V[b // group]; q/out [B, D], k/v
+    [B // group, N, D].
+
+    Native form of flash_decode_kernel (ops/suite/perf/flash_decode.py:21-49)."""
+    if scale is None:
+        scale = 1.0 / float(q.shape[-1]) ** 0.5
+    qd, kd, vd, od = _desc(q), _desc(k), _desc(v), _desc(out)
+    abi.check(abi.lib().b200_attn_decode(_ref(qd), _ref(kd), _ref(vd), _ref(od), float(scale),
+                                         stream))
+
+
 def swiglu(x, y, out, *, stream=0):
     """out = x * sigmoid(x) * y (swiglu_fwd_kernel, ops/suite/perf/swiglu_fwd.py:18-36)."""
     xd, yd, od = _desc(x), _desc(y), _desc(out)

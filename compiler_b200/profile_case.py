@@ -6,6 +6,7 @@ time a single shape by hand.
     python -m compiler_b200.profile_case rmsnorm   --shape 8192 4096  --dtype float32
     python -m compiler_b200.profile_case gemm      --shape 8192 8192 8192
     python -m compiler_b200.profile_case attention --shape 2 8 4096 128
+    python -m compiler_b200.profile_case attention_decode --shape 256 4096 128
     python -m compiler_b200.profile_case swiglu_gemm --shape 4096 1792 4096
 
 Inputs are seeded random values generated on the host and uploaded through ``B200Device``
@@ -31,10 +32,14 @@ def _upload(device, array, dtype):
 
 def main(argv=None):
     parser = argparse.ArgumentParser(description=__doc__.split("\n")[0])
-    parser.add_argument("op", choices=["softmax", "rmsnorm", "gemm", "attention", "swiglu_gemm"])
+    parser.add_argument("op", choices=["softmax", "rmsnorm", "gemm", "attention", "attention_decode",
+                                       "swiglu_gemm"])
     parser.add_argument("--shape", type=int, nargs="+", required=True)
     parser.add_argument("--dtype", default=None)
     parser.add_argument("--launches", type=int, default=3)
+    parser.add_argument("--repeat", type=int, default=1,
+                        help="launches per timed sample, back to back (hides the host's launch "
+                             "latency for kernels of tens of microseconds); times are per launch")
     parser.add_argument("--device", type=int, default=0)
     parser.add_argument("--no-mask", action="store_true", help="softmax/attention without mask")
     parser.add_argument("--act", default="gelu_tanh", choices=["none", "gelu_tanh", "gelu_erf"],
@@ -75,6 +80,15 @@ def main(argv=None):
             b2 = _upload(device, rng.standard_normal((k, n), dtype=np.float32) / np.sqrt(k), dtype)
             launch = lambda: ops.gemm(a, b, c, b2=b2, act=abi.ACT_SWIGLU)  # noqa: E731
             work = {"flop": 4 * m * n * k}
+    elif args.op == "attention_decode":
+        dtype = args.dtype or "bfloat16"
+        rows, n, d = shape
+        q = _upload(device, rng.standard_normal((rows, d), dtype=np.float32), dtype)
+        k, v = (_upload(device, rng.standard_normal((rows, n, d), dtype=np.float32), dtype)
+                for _ in range(2))
+        o = device.alloc((rows, d), dtype)
+        launch = lambda: ops.attention_decode(q, k, v, o)  # noqa: E731
+        work = {"bytes": 2 * rows * n * d * abi.DTYPE_SIZES[dtype]}
     else:
         dtype = args.dtype or "bfloat16"
         z, h, n, d = shape
@@ -88,8 +102,9 @@ def main(argv=None):
     times = []
     for _ in range(args.launches):
         with device.timer() as t:
-            launch()
-        times.append(t.seconds)
+            for _ in range(max(1, args.repeat)):
+                launch()
+        times.append(t.seconds / max(1, args.repeat))
     device.check_status()
     record = {"op": args.op, "shape": shape, "dtype": dtype, "launch_seconds": times, **work}
     best = min(times)

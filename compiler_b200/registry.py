@@ -247,6 +247,21 @@ def _attention(device, v, grid, name):
                   scale=float(v["scale"]), causal=bool(v["CAUSAL"]), stream=device.stream)
 
 
+def _flash_decode(device, v, grid, name):
+    """flash_decode_kernel (ops/suite/perf/flash_decode.py:21-23): one query row per program."""
+    rows = _grid_tuple(grid)[0]
+    n, d = int(v["N_CTX"]), int(v["HEAD_DIM"])
+    _require(int(v["stride_kk"]) == 1 and int(v["stride_vn"]) == 1, name, "strides",
+             "the head dimension must have unit stride")
+    _require(rows % int(v["H"]) == 0, name, "grid", "expected one program per (batch, head)")
+    ops.attention_decode(
+        _View(v["Q"], (rows, d), (int(v["stride_qh"]), 1)),
+        _View(v["K"], (rows, n, d), (int(v["stride_kh"]), int(v["stride_kn"]), 1)),
+        _View(v["V"], (rows, n, d), (int(v["stride_vh"]), int(v["stride_vk"]), 1)),
+        _View(v["Out"], (rows, d), (int(v["stride_oh"]), 1)),
+        scale=float(v["scale"]), stream=device.stream)
+
+
 def _swiglu(device, v, grid, name):
     """swiglu_fwd_kernel (ops/suite/perf/swiglu_fwd.py:27-28, swiglu_triton.py:19-20)."""
     rows = _grid_tuple(grid, {"BLOCK_N": 32})[0]
@@ -387,6 +402,10 @@ def default_registry() -> Registry:
     for attn_name in ("attn_fwd_causal_kernel", "attention_forward_kernel", "attention_kernel",
                       "context_attn_fwd_kernel"):
         r.register(attn_name, _ATTN, _attention)
+    r.register("flash_decode_kernel",
+               ("Q", "K", "V", "Out", "stride_qh", "stride_kh", "stride_kn", "stride_kk",
+                "stride_vh", "stride_vk", "stride_vn", "stride_oh", "H", "N_CTX", "scale",
+                "HEAD_DIM", "BLOCK_N"), _flash_decode)
     r.register("swiglu_fwd_kernel",
                ("X", "Y", "OUT", "stride_x_row", "stride_y_row", "stride_out_row", "ncols",
                 "BLOCK_N"), _swiglu)

@@ -195,6 +195,21 @@ int b200_attn_fwd(const b200_tensor *q, const b200_tensor *k,
                   const b200_tensor *v, b200_tensor *o, b200_tensor *lse,
                   float scale, int causal, void *stream);
 
+/* Decode-side attention: one query row per (batch, head) against that head's K / V
+ * cache.  Replaces flash_decode_kernel (ops/suite/perf/flash_decode.py:21-49):
+ * out[b] = softmax(scale * K[b / group] q[b]) V[b / group].  q, out: [B, D]; k, v:
+ * [B / group, N, D] with unit last stride (f16 / bf16 / f32, all the same type); group =
+ * B / k->shape[0] query rows share one K / V head (1 for flash_decode; the grouped-query
+ * layout of ops/suite/dev/gqa.py:29 otherwise).  Head sizes 16 / 32 / 64 / 128 with
+ * 16-byte aligned rows take the streaming kernel (the keys of all rows dealt to one wave
+ * of CTAs in equal ranges; rows cut between CTAs are merged by a second small kernel from
+ * softmax states kept in a few hundred KiB of stream-ordered scratch, cudaMallocAsync /
+ * cudaFreeAsync on `stream`); anything else takes a one-CTA-per-row kernel limited to
+ * 49152 keys. */
+int b200_attn_decode(const b200_tensor *q, const b200_tensor *k,
+                     const b200_tensor *v, b200_tensor *out, float scale,
+                     void *stream);
+
 /* C = A @ B with the rows of C scattered to their owners: rows [k*rows_per_rank,
  * (k+1)*rows_per_rank) go to slot `slot` of c_rank[k], a buffer laid out
  * [world, rows_per_rank, N] in rank k's memory (a peer GPU's buffer mapped into this

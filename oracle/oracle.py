@@ -155,6 +155,22 @@ def attention_ref(q, k, v, scale, causal=True):
     return out, lse
 
 
+def flash_decode_ref(q, k, v, scale, group: int = 1):
+    """One query row per (batch, head): out[b] = softmax(scale * K[b // group] q[b]) V[b // group]
+    (ref of ops/suite/perf/flash_decode.py:57-70; ``group`` > 1 is the head mapping of
+    ops/suite/dev/gqa.py:29).  q [B, D], k / v [B // group, N, D] -> [B, D] float64."""
+    q = np.asarray(q, dtype=np.float64)
+    k = np.asarray(k, dtype=np.float64)
+    v = np.asarray(v, dtype=np.float64)
+    out = np.zeros(q.shape)
+    for b in range(q.shape[0]):
+        s = (k[b // group] @ q[b]) * float(scale)
+        s = s - s.max()
+        p = np.exp(s)
+        out[b] = (p / p.sum()) @ v[b // group]
+    return out
+
+
 def swiglu_ref(x, y):
     """``ref`` of ops/suite/perf/swiglu_fwd.py:43-47: x / (1 + exp(-x)) * y."""
     x = np.asarray(x, dtype=np.float64)

@@ -2,7 +2,9 @@
 
 Run in a container that has the reference tree (it is imported read-only):
 
-    python tests/golden/make_golden.py /path/to/reference
+    python tests/golden/make_golden.py /path/to/reference [operator file ...]
+
+(operator files as listed in ``OPERATORS``; with none, every fixture is rewritten.)
 
 For every hot-path operator file it calls the file's own ``make_case(shape,
 dtype, seed)`` for each declared shape (plus one audited mid-size shape) and each
@@ -49,6 +51,8 @@ OPERATORS = {
     "perf/attention_kernel.py": [],
     "dev/epilogue_kernel.py": [],
     "dev/rmsnorm_fwd_loop_kernel.py": [],
+    # decode-side attention
+    "perf/flash_decode.py": [(1, 8, 256, 64)],
 }
 MID_DTYPES = ("bfloat16",)  # mid-size shapes are stored for one dtype to keep fixtures small
 
@@ -58,8 +62,11 @@ def main(reference_root: str) -> None:
     sys.path.insert(0, str(root / "ops" / "harness"))
     from opslib import runner  # noqa: E402  (the reference's loader)
 
-    index = {}
+    only = set(sys.argv[2:])  # optional: operator files to (re)generate, others stay as they are
+    index = json.loads((HERE / "index.json").read_text()) if only else {}
     for rel, extra in OPERATORS.items():
+        if only and rel not in only:
+            continue
         module = runner.load_operator(root / "ops" / "suite" / rel)
         stem = Path(rel).stem
         cases = [(tuple(s), d) for s in module.SHAPES for d in module.DTYPES]

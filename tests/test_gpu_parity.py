@@ -227,6 +227,72 @@ def test_attention_cuda_core_path(device, shape):
     oracle.compare(device.download(dl).astype(np.float64), lse_ref, 1e-4, 1e-5)
 
 
+DECODE_SHAPES = [  # (query rows B, group, N_CTX, head_dim)
+    (1, 1, 1, 16), (3, 1, 7, 32), (4, 1, 255, 64), (4, 1, 256, 128), (2, 1, 1000, 128),
+    (5, 1, 4097, 64), (1, 1, 32768, 128),      # one row: its keys are split over a cluster
+    (8, 4, 513, 128), (6, 2, 2048, 64),        # grouped-query layout
+    (3, 1, 300, 24), (2, 2, 77, 80),           # head sizes of the one-CTA-per-row kernel
+]
+
+
+@pytest.mark.parametrize("dtype", ["bfloat16", "float16", "float32"])
+@pytest.mark.parametrize("shape", DECODE_SHAPES)
+def test_attention_decode_sweep(device, shape, dtype):
+    rows, group, n, d = shape
+    rng = np.random.default_rng(_seed(shape, dtype))
+    q = _host(rng.standard_normal((rows, d)), dtype)
+    k = _host(rng.standard_normal((rows // group, n, d)), dtype)
+    v = _host(rng.standard_normal((rows // group, n, d)), dtype)
+    dq, dk, dv = (_up(device, t, dtype) for t in (q, k, v))
+    do = _poisoned(device, (rows, d), dtype)
+    scale = 1.0 / np.sqrt(d)
+    ops.attention_decode(dq, dk, dv, do, scale=scale)
+    ref = oracle.flash_decode_ref(q, k, v, scale, group)
+    rtol, atol = (1e-4, 1e-5) if dtype == "float32" else TOL[dtype]
+    oracle.compare(device.download(do).astype(np.float64), ref, rtol, atol, name="out")
+
+
+def test_attention_decode_strided_cache_and_rejections(device):
+    """K / V as slices of a longer cache (row pitch > head size), an unaligned pitch (generic
+    kernel), and descriptors the entry point refuses before anything is launched."""
+    from compiler_b200.runtime.abi import B200Error
+    rng = np.random.default_rng(41)
+    rows, n, d, pitch = 4, 600, 64, 96
+    q = _host(rng.standard_normal((rows, d)), "bfloat16")
+    cache_k = _host(rng.standard_normal((rows, n, pitch)), "bfloat16")
+    cache_v = _host(rng.standard_normal((rows, n, pitch)), "bfloat16")
+    dq, dk, dv = (_up(device, t, "bfloat16") for t in (q, cache_k, cache_v))
+    do = _poisoned(device, (rows, d), "bfloat16")
+    scale = 0.125
+
+    class Slice:  # the first d columns of every cache row
+        def __init__(self, buffer, offset=0):
+            self.buffer, self.shape, self.dtype, self.offset = buffer, (rows, n, d), buffer.dtype, offset
+
+        def data_ptr(self):
+            return self.buffer.data_ptr() + 2 * self.offset
+
+        def stride(self):
+            return (n * pitch, pitch, 1)
+
+    ops.attention_decode(dq, Slice(dk), Slice(dv), do, scale=scale)
+    ref = oracle.flash_decode_ref(q, cache_k[..., :d], cache_v[..., :d], scale)
+    oracle.compare(device.download(do).astype(np.float64), ref, *TOL["bfloat16"])
+    # columns [3, 3 + d): rows start 6 bytes off a 16-byte boundary
+    do2 = _poisoned(device, (rows, d), "bfloat16")
+    ops.attention_decode(dq, Slice(dk, 3), Slice(dv, 3), do2, scale=scale)
+    ref = oracle.flash_decode_ref(q, cache_k[..., 3:3 + d], cache_v[..., 3:3 + d], scale)
+    oracle.compare(device.download(do2).astype(np.float64), ref, *TOL["bfloat16"])
+    with pytest.raises(B200Error):   # 3 query rows cannot share 2 K/V heads
+        ops.attention_decode(_up(device, q[:3], "bfloat16"),
+                             _up(device, cache_k[:2, :, :d].copy(), "bfloat16"),
+                             _up(device, cache_v[:2, :, :d].copy(), "bfloat16"),
+                             _poisoned(device, (3, d), "bfloat16"), scale=scale)
+    with pytest.raises(B200Error):   # softmax over no keys
+        empty = device.alloc((rows, 0, d), "bfloat16")
+        ops.attention_decode(dq, empty, empty, do, scale=scale)
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("shape", [(4, 64), (8, 128), (5, 99), (64, 1024), (33, 14336)])
 def test_swiglu_sweep(device, shape, dtype):

@@ -100,6 +100,17 @@ def test_attention(tag):
     assert np.isfinite(lse).all()
 
 
+@pytest.mark.parametrize("tag", golden_cases.tags("flash_decode"))
+def test_flash_decode(tag):
+    case, meta = golden_cases.load(tag)
+    a = case["args"]
+    z_h, d = a["Q"].shape[0] * a["Q"].shape[1], a["Q"].shape[2]
+    out = oracle.flash_decode_ref(a["Q"].reshape(z_h, d), a["K"].reshape(z_h, -1, d),
+                                  a["V"].reshape(z_h, -1, d), a["scale"])
+    expected = case["expected"]["Out"]
+    _assert_same(out.reshape(expected.shape).astype(expected.dtype), expected, meta["dtype"])
+
+
 @pytest.mark.parametrize("tag", golden_cases.tags("swiglu_fwd"))
 def test_swiglu(tag):
     case, meta = golden_cases.load(tag)
