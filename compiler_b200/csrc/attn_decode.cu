@@ -18,14 +18,18 @@
 //   * work is dealt in equal byte ranges, not rows (see decode_stream_kernel): one wave of
 //     resident CTAs streams the whole launch, whether it has 8 rows of 32768 keys or 2048
 //     rows of 1024; rows cut between CTAs are finished by a small fix-up kernel from states
-//     parked in a stream-ordered scratch allocation (cudaMallocAsync / cudaFreeAsync on the
-//     caller's stream).
+//     parked in a scratch buffer that belongs to the launching stream (a few hundred KiB,
+//     allocated the first time a stream is used and kept).
 // Anything the fast kernel does not take (head sizes other than 16/32/64/128, rows that are
 // not 16-byte aligned) runs decode_generic_kernel: one CTA per row, scores kept in shared
 // memory -- still on the GPU.
 #include <cooperative_groups.h>
 
 #include <stdlib.h>
+
+#include <map>
+#include <mutex>
+#include <utility>
 
 #include "common.cuh"
 
@@ -134,23 +138,27 @@ decode_stream_kernel(const Params p) {
 #pragma unroll
     for (int i = 0; i < VEC; ++i) acc[i] = 0.f;
 
-    constexpr int STEP = UNROLL * KPL;  // keys per warp per iteration
-    for (int base = key0 + warp * STEP; base < key1; base += WARPS * STEP) {
-      uint4 kr[UNROLL], vr[UNROLL];
-      bool ok[UNROLL];
+    // The loop is software-pipelined: the K loads of step i+1 are issued as soon as the
+    // dot products of step i have consumed the K registers, the V loads of step i+1 as soon
+    // as the accumulation has consumed the V registers, so loads are in flight during all of
+    // the arithmetic.
+    constexpr int STEP = UNROLL * KPL;  // keys per warp per step
+    uint4 kr[UNROLL], vr[UNROLL];
+    auto load_rows = [&](const T *rows, int64_t pitch, int base, uint4 (&dst)[UNROLL]) {
 #pragma unroll
       for (int t = 0; t < UNROLL; ++t) {
         const int key = base + t * KPL + sub;
-        ok[t] = key < key1;
-        kr[t] = ok[t] ? ld_stream16(kbase + (int64_t)key * p.k_row + part * VEC)
-                      : make_uint4(0, 0, 0, 0);
+        dst[t] = key < key1 ? ld_stream16(rows + (int64_t)key * pitch + part * VEC)
+                            : make_uint4(0, 0, 0, 0);
       }
-#pragma unroll
-      for (int t = 0; t < UNROLL; ++t) {
-        const int key = base + t * KPL + sub;
-        vr[t] = ok[t] ? ld_stream16(vbase + (int64_t)key * p.v_row + part * VEC)
-                      : make_uint4(0, 0, 0, 0);
-      }
+    };
+    int base = key0 + warp * STEP;
+    if (base < key1) {
+      load_rows(kbase, p.k_row, base, kr);
+      load_rows(vbase, p.v_row, base, vr);
+    }
+    for (; base < key1; base += WARPS * STEP) {
+      const int next = base + WARPS * STEP;
       float s[UNROLL];
 #pragma unroll
       for (int t = 0; t < UNROLL; ++t) {
@@ -161,8 +169,9 @@ decode_stream_kernel(const Params p) {
         for (int i = 0; i < VEC; ++i) dot = fmaf(qf[i], kf[i], dot);
 #pragma unroll
         for (int o = LPK / 2; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-        s[t] = ok[t] ? dot : -INFINITY;
+        s[t] = (base + t * KPL + sub < key1) ? dot : -INFINITY;
       }
+      if (next < key1) load_rows(kbase, p.k_row, next, kr);
       float m_n = m;
 #pragma unroll
       for (int t = 0; t < UNROLL; ++t) m_n = fmaxf(m_n, s[t]);
@@ -182,6 +191,7 @@ decode_stream_kernel(const Params p) {
         }
         m = m_n;
       }
+      if (next < key1) load_rows(vbase, p.v_row, next, vr);
     }
 
     // lane groups of the warp: afterwards every lane group holds the warp's state for its
@@ -300,26 +310,46 @@ decode_generic_kernel(const Params p, int D) {
   }
 }
 
+// Softmax states of rows cut between CTAs: [ctas][2][D + 2] floats, at most
+// kMaxResident * 2 * 130.  One buffer per (device, stream), allocated the first time that
+// stream launches a decode and kept: launches on one stream are ordered, so they can share
+// it; launches on different streams never do.
+constexpr int kMaxResident = 4 * 160;
+static float *stream_scratch(cudaStream_t stream) {
+  static std::mutex lock;
+  static std::map<std::pair<int, cudaStream_t>, float *> buffers;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return nullptr;
+  std::lock_guard<std::mutex> guard(lock);
+  auto key = std::make_pair(dev, stream);
+  auto found = buffers.find(key);
+  if (found != buffers.end()) return found->second;
+  void *ptr = nullptr;
+  if (cudaMalloc(&ptr, (size_t)kMaxResident * 2 * (128 + 2) * sizeof(float)) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return nullptr;
+  }
+  buffers[key] = reinterpret_cast<float *>(ptr);
+  return buffers[key];
+}
+
 template <typename T, int D>
 static int launch_stream(const Params &p, int rows, cudaStream_t stream) {
   Params ps = p;
   ps.units_per_row = (p.N + UNIT_KEYS - 1) / UNIT_KEYS;
   ps.units = ps.units_per_row * rows;
   const int64_t resident = (int64_t)ctas_per_sm<T>() * sm_count();
-  const int ctas = (int)(ps.units < resident ? ps.units : resident);
-  // softmax states of cut rows: stream-ordered, so launches on other streams never share it
-  void *scratch = nullptr;
-  B200_CUDA_OK(cudaMallocAsync(&scratch, (size_t)ctas * 2 * (D + 2) * sizeof(float), stream));
-  ps.scratch = reinterpret_cast<float *>(scratch);
+  int ctas = (int)(ps.units < resident ? ps.units : resident);
+  if (ctas > kMaxResident) ctas = kMaxResident;
+  ps.scratch = stream_scratch(stream);
+  if (ps.scratch == nullptr) return fail(B200_RESOURCE, "no scratch for the decode kernel");
   decode_stream_kernel<T, D><<<ctas, THREADS, 0, stream>>>(ps);
   cudaError_t err = cudaGetLastError();
   if (err == cudaSuccess && ctas > 1) {
     decode_fixup_kernel<T, D><<<ctas, D < 32 ? 32 : D, 0, stream>>>(ps, ctas);
     err = cudaGetLastError();
   }
-  const cudaError_t freed = cudaFreeAsync(scratch, stream);
   B200_CUDA_OK(err);
-  B200_CUDA_OK(freed);
   return B200_OK;
 }
 

@@ -55,6 +55,7 @@ constexpr float kRescaleThreshold = 8.0f;
 
 struct Params {
   int H, N, ZH;
+  int kv_group;    // query heads per K / V head
   int wave_heads;  // (batch, head) pairs whose K / V are meant to share the L2 at one time
   float scale_log2;  // scale * log2(e)
   int causal;
@@ -323,7 +324,7 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q,
 #pragma unroll
           for (int b = 0; b < D / 64; ++b)
             tma_load_4d(k_smem + s * L::TILE_BYTES + b * L::BOX_BYTES, &tm_k, k_full(s), b * 64,
-                        j * BLOCK_N, it.h, it.z);
+                        j * BLOCK_N, it.h / p.kv_group, it.z);
           issued |= 1u << s;
           parity = (parity & ~(1u << s)) | (ph << s);
           const uint32_t vs = kv_it % V_STAGES, vph = (kv_it / V_STAGES) & 1u;
@@ -332,7 +333,7 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q,
 #pragma unroll
           for (int b = 0; b < D / 64; ++b)
             tma_load_4d(v_smem + vs * L::TILE_BYTES + b * L::BOX_BYTES, &tm_v, v_full(vs), b * 64,
-                        j * BLOCK_N, it.h, it.z);
+                        j * BLOCK_N, it.h / p.kv_group, it.z);
           issued |= 4u << vs;
           parity = (parity & ~(4u << vs)) | (vph << (2 + vs));
         }

@@ -16,7 +16,7 @@ constexpr int kSimtMaxKeys = 8192;  // scores of one row are staged in shared me
 template <typename T>
 __global__ void __launch_bounds__(kSimtThreads)
 attn_simt_kernel(const T *__restrict__ q, const T *__restrict__ k, const T *__restrict__ v,
-                 T *__restrict__ o, float *__restrict__ lse, int H, int N, int D,
+                 T *__restrict__ o, float *__restrict__ lse, int H, int kv_group, int N, int D,
                  int64_t qz, int64_t qh, int64_t qm, int64_t kz, int64_t kh, int64_t kn,
                  int64_t vz, int64_t vh, int64_t vn, int64_t oz, int64_t oh, int64_t om,
                  float scale, int causal) {
@@ -28,8 +28,8 @@ attn_simt_kernel(const T *__restrict__ q, const T *__restrict__ k, const T *__re
   const int zh = blockIdx.y;
   const int z = zh / H, h = zh % H;
   const T *qp = q + z * qz + h * qh + (int64_t)m * qm;
-  const T *kp = k + z * kz + h * kh;
-  const T *vp = v + z * vz + h * vh;
+  const T *kp = k + z * kz + (h / kv_group) * kh;
+  const T *vp = v + z * vz + (h / kv_group) * vh;
   const int keys = causal ? m + 1 : N;
   for (int d = threadIdx.x; d < D; d += kSimtThreads) qrow[d] = io<T>::load(qp[d]);
   __syncthreads();

@@ -41,6 +41,7 @@ constexpr float kRescaleThreshold = 8.0f;
 
 struct Params {
   int H, N;
+  int kv_group;  // query heads per K / V head (1 = one K / V head per query head)
   float scale_log2;  // scale * log2(e)
   int causal;
   void *o;
@@ -173,7 +174,7 @@ attn_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
 #pragma unroll
         for (int b = 0; b < D / 64; ++b)
           tma_load_4d(k_smem + s * L::TILE_BYTES + b * L::BOX_BYTES, &tm_k, k_full(s), b * 64,
-                      j * BLOCK_N, h, z);
+                      j * BLOCK_N, h / p.kv_group, z);
         issued |= 1u << s;
         parity = (parity & ~(1u << s)) | (ph << s);
         if (!mbar_wait(v_empty(s), ph ^ 1u, ctx, 2)) { ok = false; break; }
@@ -181,7 +182,7 @@ attn_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
 #pragma unroll
         for (int b = 0; b < D / 64; ++b)
           tma_load_4d(v_smem + s * L::TILE_BYTES + b * L::BOX_BYTES, &tm_v, v_full(s), b * 64,
-                      j * BLOCK_N, h, z);
+                      j * BLOCK_N, h / p.kv_group, z);
         issued |= 4u << s;
         parity = (parity & ~(4u << s)) | (ph << (2 + s));
       }
@@ -450,10 +451,18 @@ extern "C" int b200_attn_fwd(const b200_tensor *q, const b200_tensor *k, const b
   B200_REQUIRE(k->dtype == q->dtype && v->dtype == q->dtype && o->dtype == q->dtype,
                "q/k/v/o dtypes differ");
   const int64_t Z = q->shape[0], H = q->shape[1], N = q->shape[2], D = q->shape[3];
-  for (const b200_tensor *t : {k, v, (const b200_tensor *)o}) {
-    B200_REQUIRE(t->shape[0] == Z && t->shape[1] == H && t->shape[2] == N && t->shape[3] == D,
-                 "q/k/v/o shapes differ (self-attention: K/V length = N_CTX)");
+  B200_REQUIRE(o->shape[0] == Z && o->shape[1] == H && o->shape[2] == N && o->shape[3] == D,
+               "o must have q's shape");
+  // K / V may have fewer heads: query head h reads K / V head h / (H / H_KV), the grouping
+  // of gqa_kernel (ops/suite/dev/gqa.py:27-32)
+  const int64_t HKV = k->shape[1];
+  for (const b200_tensor *t : {k, v}) {
+    B200_REQUIRE(t->shape[0] == Z && t->shape[1] == HKV && t->shape[2] == N && t->shape[3] == D,
+                 "k and v must be [Z, H_KV, N_CTX, D] (self-attention: K/V length = N_CTX)");
   }
+  B200_REQUIRE(HKV > 0 ? H % HKV == 0 : H == 0, "query heads %lld are not a multiple of K/V heads %lld",
+               (long long)H, (long long)HKV);
+  const int kv_group = HKV > 0 ? (int)(H / HKV) : 1;
   B200_REQUIRE(q->stride[3] == 1 && k->stride[3] == 1 && v->stride[3] == 1 && o->stride[3] == 1,
                "last-dim stride must be 1");
   B200_REQUIRE(D >= 1 && D <= 512, "head_dim %lld out of range", (long long)D);
@@ -485,7 +494,7 @@ extern "C" int b200_attn_fwd(const b200_tensor *q, const b200_tensor *k, const b
 #define B200_ATTN_SIMT(T)                                                                    \
   attn_simt_kernel<T><<<grid, kSimtThreads, smem, s>>>(                                      \
       (const T *)q->data, (const T *)k->data, (const T *)v->data, (T *)o->data,              \
-      lse ? (float *)lse->data : nullptr, (int)H, (int)N, (int)D, q->stride[0], q->stride[1], \
+      lse ? (float *)lse->data : nullptr, (int)H, kv_group, (int)N, (int)D, q->stride[0], q->stride[1], \
       q->stride[2], k->stride[0], k->stride[1], k->stride[2], v->stride[0], v->stride[1],    \
       v->stride[2], o->stride[0], o->stride[1], o->stride[2], scale, causal ? 1 : 0)
     if (q->dtype == B200_DTYPE_FLOAT32) B200_ATTN_SIMT(float);
@@ -502,6 +511,7 @@ extern "C" int b200_attn_fwd(const b200_tensor *q, const b200_tensor *k, const b
   Params p;
   p.H = (int)H;
   p.N = (int)N;
+  p.kv_group = kv_group;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.causal = causal ? 1 : 0;
   p.o = o->data;
@@ -519,7 +529,7 @@ extern "C" int b200_attn_fwd(const b200_tensor *q, const b200_tensor *k, const b
   const char *which = getenv("B200OPS_ATTN_KERNEL");
   if (!(which != nullptr && which[0] == 's')) {
     pair::Params pp;
-    pp.H = p.H; pp.N = p.N; pp.ZH = (int)(Z * H);
+    pp.H = p.H; pp.N = p.N; pp.ZH = (int)(Z * H); pp.kv_group = kv_group;
     pp.scale_log2 = p.scale_log2; pp.causal = p.causal;
     pp.lse = p.lse;
     pp.idesc_qk = p.idesc_qk; pp.idesc_pv = p.idesc_pv; pp.status = p.status;

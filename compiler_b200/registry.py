@@ -247,6 +247,27 @@ def _attention(device, v, grid, name):
                   scale=float(v["scale"]), causal=bool(v["CAUSAL"]), stream=device.stream)
 
 
+def _gqa(device, v, grid, name):
+    """gqa_kernel (ops/suite/dev/gqa.py:19-58): non-causal attention, GROUP query heads per
+    K / V head; batch and head share one stride, so both are folded into the head axis."""
+    n, d, group = int(v["N_CTX"]), int(v["HEAD_DIM"]), int(v["GROUP"])
+    hq, hkv = int(v["H_Q"]), int(v["H_KV"])
+    _require(hq == hkv * group, name, "GROUP", "H_Q must be H_KV * GROUP")
+    _require(int(v["stride_qk"]) == 1 and int(v["stride_kk"]) == 1 and
+             int(v["stride_vn"]) == 1 and int(v["stride_on"]) == 1, name, "strides",
+             "the head dimension must have unit stride")
+    rows = _grid_tuple(grid)[1]          # Z * H_Q
+    _require(rows % hq == 0, name, "grid", "expected grid (cdiv(N_CTX, BLOCK_N), Z*H_Q)")
+    kv_rows = rows // group
+
+    def view(key, heads, sh, sm):
+        return _View(v[key], (1, heads, n, d), (heads * int(v[sh]), int(v[sh]), int(v[sm]), 1))
+
+    ops.attention(view("Q", rows, "stride_qh", "stride_qm"), view("K", kv_rows, "stride_kh", "stride_kn"),
+                  view("V", kv_rows, "stride_vh", "stride_vk"), view("Out", rows, "stride_oh", "stride_om"),
+                  scale=float(v["scale"]), causal=False, stream=device.stream)
+
+
 def _flash_decode(device, v, grid, name):
     """flash_decode_kernel (ops/suite/perf/flash_decode.py:21-23): one query row per program."""
     rows = _grid_tuple(grid)[0]
@@ -402,6 +423,11 @@ def default_registry() -> Registry:
     for attn_name in ("attn_fwd_causal_kernel", "attention_forward_kernel", "attention_kernel",
                       "context_attn_fwd_kernel"):
         r.register(attn_name, _ATTN, _attention)
+    r.register("gqa_kernel",
+               ("Q", "K", "V", "Out", "stride_qh", "stride_qm", "stride_qk", "stride_kh",
+                "stride_kn", "stride_kk", "stride_vh", "stride_vk", "stride_vn", "stride_oh",
+                "stride_om", "stride_on", "H_Q", "H_KV", "N_CTX", "scale", "GROUP", "HEAD_DIM",
+                "BLOCK_N"), _gqa)
     r.register("flash_decode_kernel",
                ("Q", "K", "V", "Out", "stride_qh", "stride_kh", "stride_kn", "stride_kk",
                 "stride_vh", "stride_vk", "stride_vn", "stride_oh", "H", "N_CTX", "scale",

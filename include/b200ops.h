@@ -188,8 +188,10 @@ int b200_gemm_bias_act(const b200_tensor *a, const b200_tensor *b,
                        b200_tensor *c, int act, void *stream);
 
 /* Attention forward.  Replaces attn_fwd_causal_kernel
- * (ops/suite/perf/attn_fwd_causal.py:19-57).  q,k,v,o: [Z,H,N,D] with unit
- * last stride (f16/bf16); lse: [Z,H,N] f32 or NULL, natural log of the sum of
+ * (ops/suite/perf/attn_fwd_causal.py:19-57).  q,o: [Z,H,N,D], k,v: [Z,H_KV,N,D]
+ * with unit last stride; H_KV divides H and query head h reads K / V head
+ * h / (H / H_KV) (H_KV == H for the kernels above; fewer K / V heads is gqa_kernel,
+ * ops/suite/dev/gqa.py:19-58).  lse: [Z,H,N] f32 or NULL, natural log of the sum of
  * exp of the scaled masked scores (ops/suite/dev/flash_varlen_fwd_kernel.py:309). */
 int b200_attn_fwd(const b200_tensor *q, const b200_tensor *k,
                   const b200_tensor *v, b200_tensor *o, b200_tensor *lse,
@@ -203,8 +205,8 @@ int b200_attn_fwd(const b200_tensor *q, const b200_tensor *k,
  * layout of ops/suite/dev/gqa.py:29 otherwise).  Head sizes 16 / 32 / 64 / 128 with
  * 16-byte aligned rows take the streaming kernel (the keys of all rows dealt to one wave
  * of CTAs in equal ranges; rows cut between CTAs are merged by a second small kernel from
- * softmax states kept in a few hundred KiB of stream-ordered scratch, cudaMallocAsync /
- * cudaFreeAsync on `stream`); anything else takes a one-CTA-per-row kernel limited to
+ * softmax states kept in a 650 KiB scratch buffer that the library allocates once per
+ * (device, stream) on the first call and keeps); anything else takes a one-CTA-per-row kernel limited to
  * 49152 keys. */
 int b200_attn_decode(const b200_tensor *q, const b200_tensor *k,
                      const b200_tensor *v, b200_tensor *out, float scale,

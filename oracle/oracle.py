@@ -155,6 +155,15 @@ def attention_ref(q, k, v, scale, causal=True):
     return out, lse
 
 
+def gqa_attention_ref(q, k, v, scale, causal=False):
+    """Attention with fewer K / V heads than query heads: query head h reads K / V head
+    h // (H_Q // H_KV) (ref of ops/suite/dev/gqa.py:69-85).  q [Z,H_Q,N,D], k / v
+    [Z,H_KV,N,D] -> (out, lse) like ``attention_ref``."""
+    group = np.asarray(q).shape[1] // np.asarray(k).shape[1]
+    return attention_ref(q, np.repeat(np.asarray(k), group, axis=1),
+                         np.repeat(np.asarray(v), group, axis=1), scale, causal)
+
+
 def flash_decode_ref(q, k, v, scale, group: int = 1):
     """One query row per (batch, head): out[b] = softmax(scale * K[b // group] q[b]) V[b // group]
     (ref of ops/suite/perf/flash_decode.py:57-70; ``group`` > 1 is the head mapping of

@@ -213,6 +213,35 @@ def test_attention_sweep(device, shape, dtype, causal, variant):
     oracle.compare(device.download(dl).astype(np.float64), lse_ref, 1e-3, 1e-3, name="lse")
 
 
+@pytest.mark.parametrize("variant", ["pair", "single"])
+@pytest.mark.parametrize("causal", [True, False])
+@pytest.mark.parametrize("shape", [(2, 8, 2, 300, 64), (1, 6, 3, 512, 128), (2, 4, 1, 129, 128)])
+def test_attention_grouped_kv_heads(device, shape, causal, variant):
+    """Fewer K / V heads than query heads (the head mapping of ops/suite/dev/gqa.py:27-32) on
+    the tensor-core kernels."""
+    z, hq, hkv, n, d = shape
+    rng = np.random.default_rng(_seed(shape, causal))
+    q = _host(rng.standard_normal((z, hq, n, d)), "bfloat16")
+    k, v = (_host(rng.standard_normal((z, hkv, n, d)), "bfloat16") for _ in range(2))
+    dq, dk, dv = (_up(device, t, "bfloat16") for t in (q, k, v))
+    do = _poisoned(device, (z, hq, n, d), "bfloat16")
+    dl = device.upload(np.full((z, hq, n), POISON, np.float32))
+    scale = 1.0 / np.sqrt(d)
+    os.environ["B200OPS_ATTN_KERNEL"] = variant
+    try:
+        ops.attention(dq, dk, dv, do, lse=dl, scale=scale, causal=causal)
+        device.check_status()
+    finally:
+        os.environ.pop("B200OPS_ATTN_KERNEL", None)
+    out_ref, lse_ref = oracle.gqa_attention_ref(q, k, v, scale, causal)
+    oracle.compare(device.download(do).astype(np.float64), out_ref, *TOL["bfloat16"], name="out")
+    oracle.compare(device.download(dl).astype(np.float64), lse_ref, 1e-3, 1e-3, name="lse")
+    from compiler_b200.runtime.abi import B200Error
+    with pytest.raises(B200Error):  # 3 K/V heads do not divide 8 query heads
+        bad = device.alloc((z, 3, n, d), "bfloat16") if hq % 3 else device.alloc((z, 5, n, d), "bfloat16")
+        ops.attention(dq, bad, bad, do, scale=scale, causal=causal)
+
+
 @pytest.mark.parametrize("shape", [(1, 1, 8, 16), (2, 2, 16, 32), (1, 2, 100, 80)])
 def test_attention_cuda_core_path(device, shape):
     z, h, n, d = shape

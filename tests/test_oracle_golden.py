@@ -100,6 +100,15 @@ def test_attention(tag):
     assert np.isfinite(lse).all()
 
 
+@pytest.mark.parametrize("tag", golden_cases.tags("gqa"))
+def test_gqa(tag):
+    case, meta = golden_cases.load(tag)
+    a = case["args"]
+    out, _ = oracle.gqa_attention_ref(a["Q"], a["K"], a["V"], a["scale"], causal=False)
+    expected = case["expected"]["Out"]
+    _assert_same(out.astype(expected.dtype), expected, meta["dtype"])
+
+
 @pytest.mark.parametrize("tag", golden_cases.tags("flash_decode"))
 def test_flash_decode(tag):
     case, meta = golden_cases.load(tag)
