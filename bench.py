@@ -51,6 +51,7 @@ NCU_TRAFFIC = {
     "gemm_8192": 1_134_959_000,
     "gemm_ragged": 197_744_000,
     "attention": 1_036_044_000,
+    "attention_decode": 540_428_000,
 }
 
 
@@ -394,7 +395,7 @@ def bench_attention_decode(torch, ops, dist, steps, warmup, peaks, source):
 
     region_ms, launch_ms, window = time_steps(torch, dist, launch, steps, warmup)
     nbytes = 2 * rows * n * d * 2
-    out = roofline("hbm", nbytes, launch_ms, peaks, source, None)
+    out = roofline("hbm", nbytes, launch_ms, peaks, source, NCU_TRAFFIC["attention_decode"])
     out["window"] = window
     out.update({"workload": "attn_decode_bf16_256rows_4096keys_128", "ms_per_step": round(region_ms, 5),
                 "value": round(nbytes * dist.world / (region_ms * 1e-3) / 1e9, 2),
