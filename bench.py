@@ -522,7 +522,13 @@ def main():
     extras = {}
 
     def want(name):
-        return "none" not in wanted and ("all" in wanted or name in wanted)
+        if "none" in wanted or not ("all" in wanted or name in wanted):
+            return False
+        # each operator is timed alone, as the burst peaks it is compared with were: let the
+        # board's power average settle after the previous operator's burst
+        torch.cuda.synchronize()
+        time.sleep(1.0)
+        return True
 
     if want("rmsnorm"):
         extras["rmsnorm"] = bench_rmsnorm(torch, ops, dist, max(extra_steps, min(args.steps, 200)),
