@@ -273,7 +273,7 @@ def bench_softmax(torch, ops, dist, steps, warmup, peaks, source):
 
 def bench_softmax_e2e(dist, steps, warmup):
     """Host buffers -> device -> kernel -> host, every step, through the library's public host
-    API (``compiler_b200.pipeline``): the rows are cut into chunks on three streams so the
+    API (``compiler_b200.pipeline``): the rows are cut into chunks on two streams so the
     two PCIe directions and the kernel overlap.  Timed with the host clock around the call
     (several streams take part; the call returns when the result is in host memory)."""
     from compiler_b200 import pipeline
@@ -283,7 +283,7 @@ def bench_softmax_e2e(dist, steps, warmup):
     hx = device.pinned_empty((ROWS, COLS), np.float16)
     hx.array[...] = (rng.standard_normal((ROWS, COLS), dtype=np.float32) * 2).astype(np.float16)
     hy = device.pinned_empty((ROWS, COLS), np.float16)
-    pipe = pipeline.RowPipeline(device, ROWS, COLS, "float16", chunks=16, streams=4)
+    pipe = pipeline.RowPipeline(device, ROWS, COLS, "float16", chunks=8, streams=2)
     offset = dist.rank * ROWS
 
     for _ in range(warmup):
@@ -300,7 +300,7 @@ def bench_softmax_e2e(dist, steps, warmup):
     pipe.close()
     return {"value": round(SOFTMAX_BYTES * dist.world / (ms * 1e-3) / 1e9, 2), "unit": "GB/s",
             "h2d_bytes_per_step": ROWS * COLS * 2, "d2h_bytes_per_step": ROWS * COLS * 2,
-            "ms_per_step": round(ms, 4), "steps": steps, "chunks": 16, "streams": 4,
+            "ms_per_step": round(ms, 4), "steps": steps, "chunks": 8, "streams": 2,
             "timer": "host clock around the blocking call",
             "result_check_rowsum64": round(checksum, 3)}
 
