@@ -61,7 +61,9 @@ constexpr int kFirstKeys = B200_ATTN_FIRST_KEYS;  // multiple of 32 (a 16-column
 #endif
 
 struct Params {
-  int H, N, ZH;
+  int H, N, ZH;   // N = query rows per head
+  int NK;          // keys per head (= N under the causal mask)
+  int64_t lse_z, lse_h;  // element strides of lse over batch and head
   int kv_group;    // query heads per K / V head
   int wave_heads;  // (batch, head) pairs whose K / V are meant to share the L2 at one time
   float scale_log2;  // scale * log2(e)
@@ -213,7 +215,7 @@ __device__ __forceinline__ int item_at(int n, const Params &p, Item &it) {
     if (mt0 >= p.N) {
       it.nb[t] = 0;
     } else {
-      const int kv_len = p.causal ? min(p.N, mt0 + TILE_M) : p.N;
+      const int kv_len = p.causal ? min(p.NK, mt0 + TILE_M) : p.NK;
       it.nb[t] = (kv_len + BLOCK_N - 1) / BLOCK_N;
     }
   }
@@ -610,9 +612,9 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q,
         tmem_ld_32x32b_x32(s_tmem + 96, reinterpret_cast<uint32_t(&)[32]>(xr[96]));
         const int col0 = j * BLOCK_N;
         const bool diag = p.causal && (col0 + BLOCK_N - 1 > mt0);
-        const bool ragged = col0 + BLOCK_N > p.N;
+        const bool ragged = col0 + BLOCK_N > p.NK;
         const bool masked = diag || ragged;
-        const int limit = min(p.causal ? row : p.N - 1, p.N - 1) - col0;  // last kept column
+        const int limit = min(p.causal ? row : p.NK - 1, p.NK - 1) - col0;  // last kept column
         float mx0, mx1, mx2, mx3;
         {
           if (masked) {
@@ -759,7 +761,7 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q,
         __syncwarp();
         if (lane == 0) mbar_arrive(staged);
         if (row < p.N && p.lse != nullptr)
-          p.lse[(int64_t)it.zh * p.N + row] = m_used * 0.6931471805599453f + logf(l);
+          p.lse[it.z * p.lse_z + it.h * p.lse_h + row] = m_used * 0.6931471805599453f + logf(l);
       }
       TICK(7)
     }
@@ -798,7 +800,7 @@ static int launch(const CUtensorMap &tq, const CUtensorMap &tk, const CUtensorMa
   // heads per wave: about 8 MiB of K and V (measured on [8,32,4096,128]: 4 heads per wave
   // 1135 TFLOP/s causal, 16 heads 1122, 64 heads 1076; B200OPS_ATTN_WAVE overrides)
   static const int wave_env = getenv("B200OPS_ATTN_WAVE") ? atoi(getenv("B200OPS_ATTN_WAVE")) : 0;
-  const int64_t kv_bytes = 2 * (int64_t)p.N * D * (int64_t)sizeof(T);
+  const int64_t kv_bytes = 2 * (int64_t)p.NK * D * (int64_t)sizeof(T);
   pw.wave_heads = wave_env > 0 ? wave_env : (int)((8 << 20) / kv_bytes);
   if (pw.wave_heads < 1) pw.wave_heads = 1;
   if (pw.wave_heads > p.ZH) pw.wave_heads = p.ZH;

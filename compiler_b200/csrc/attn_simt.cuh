@@ -16,13 +16,14 @@ constexpr int kSimtMaxKeys = 8192;  // scores of one row are staged in shared me
 template <typename T>
 __global__ void __launch_bounds__(kSimtThreads)
 attn_simt_kernel(const T *__restrict__ q, const T *__restrict__ k, const T *__restrict__ v,
-                 T *__restrict__ o, float *__restrict__ lse, int H, int kv_group, int N, int D,
+                 T *__restrict__ o, float *__restrict__ lse, int64_t lse_z, int64_t lse_h, int H,
+                 int kv_group, int N, int NK, int D,
                  int64_t qz, int64_t qh, int64_t qm, int64_t kz, int64_t kh, int64_t kn,
                  int64_t vz, int64_t vh, int64_t vn, int64_t oz, int64_t oh, int64_t om,
                  float scale, int causal) {
   extern __shared__ float sm[];
-  float *scores = sm;            // [N]
-  float *qrow = sm + N;          // [D]
+  float *scores = sm;            // [NK]
+  float *qrow = sm + NK;         // [D]
   __shared__ float red[kSimtThreads / 32];
   const int m = blockIdx.x;
   const int zh = blockIdx.y;
@@ -30,7 +31,7 @@ attn_simt_kernel(const T *__restrict__ q, const T *__restrict__ k, const T *__re
   const T *qp = q + z * qz + h * qh + (int64_t)m * qm;
   const T *kp = k + z * kz + (h / kv_group) * kh;
   const T *vp = v + z * vz + (h / kv_group) * vh;
-  const int keys = causal ? m + 1 : N;
+  const int keys = causal ? m + 1 : NK;
   for (int d = threadIdx.x; d < D; d += kSimtThreads) qrow[d] = io<T>::load(qp[d]);
   __syncthreads();
   float mx = -INFINITY;
@@ -66,7 +67,7 @@ attn_simt_kernel(const T *__restrict__ q, const T *__restrict__ k, const T *__re
     for (int j = 0; j < keys; ++j) acc = fmaf(scores[j], io<T>::load(vp[(int64_t)j * vn + d]), acc);
     op[d] = io<T>::store(acc * inv);
   }
-  if (lse != nullptr && threadIdx.x == 0) lse[(int64_t)zh * N + m] = mx + logf(sum);
+  if (lse != nullptr && threadIdx.x == 0) lse[z * lse_z + h * lse_h + m] = mx + logf(sum);
 }
 
 }  // namespace attn

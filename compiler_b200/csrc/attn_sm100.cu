@@ -40,7 +40,9 @@ constexpr int O_COL0 = 2 * S_COLS;
 constexpr float kRescaleThreshold = 8.0f;
 
 struct Params {
-  int H, N;
+  int H, N;      // N = query rows per head
+  int NK;        // keys per head (= N under the causal mask)
+  int64_t lse_z, lse_h;  // element strides of lse over batch and head
   int kv_group;  // query heads per K / V head (1 = one K / V head per query head)
   float scale_log2;  // scale * log2(e)
   int causal;
@@ -126,7 +128,7 @@ attn_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
   const int zh = blockIdx.y;
   const int z = zh / p.H, h = zh % p.H;
   const int m0 = qb * BLOCK_M;
-  const int kv_len = p.causal ? min(p.N, m0 + BLOCK_M) : p.N;
+  const int kv_len = p.causal ? min(p.NK, m0 + BLOCK_M) : p.NK;
   const int nblocks = (kv_len + BLOCK_N - 1) / BLOCK_N;
 
   if (threadIdx.x == 0) {
@@ -284,9 +286,9 @@ attn_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
       }
       const int col0 = j * BLOCK_N;
       const bool diag = p.causal && (col0 + BLOCK_N - 1 > m0);
-      const bool ragged = col0 + BLOCK_N > p.N;
+      const bool ragged = col0 + BLOCK_N > p.NK;
       if (diag || ragged) {
-        const int limit = min(p.causal ? row : p.N - 1, p.N - 1);  // last kept column
+        const int limit = min(p.causal ? row : p.NK - 1, p.NK - 1);  // last kept column
 #pragma unroll
         for (int i = 0; i < BLOCK_N; ++i)
           if (col0 + i > limit) x[i] = -INFINITY;
@@ -387,7 +389,7 @@ attn_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
         }
       }
       if (p.lse != nullptr && row < p.N)
-        p.lse[(int64_t)zh * p.N + row] = m_used * 0.6931471805599453f + logf(l);
+        p.lse[z * p.lse_z + h * p.lse_h + row] = m_used * 0.6931471805599453f + logf(l);
     }
   }
 
@@ -456,10 +458,15 @@ extern "C" int b200_attn_fwd(const b200_tensor *q, const b200_tensor *k, const b
   // K / V may have fewer heads: query head h reads K / V head h / (H / H_KV), the grouping
   // of gqa_kernel (ops/suite/dev/gqa.py:27-32)
   const int64_t HKV = k->shape[1];
+  // ... and another length: N_K keys per head (non-causal only; the dense, unmasked case
+  // of flash_varlen_fwd_kernel, ops/suite/dev/flash_varlen_fwd_kernel.py:370-418)
+  const int64_t NK = k->shape[2];
   for (const b200_tensor *t : {k, v}) {
-    B200_REQUIRE(t->shape[0] == Z && t->shape[1] == HKV && t->shape[2] == N && t->shape[3] == D,
-                 "k and v must be [Z, H_KV, N_CTX, D] (self-attention: K/V length = N_CTX)");
+    B200_REQUIRE(t->shape[0] == Z && t->shape[1] == HKV && t->shape[2] == NK && t->shape[3] == D,
+                 "k and v must both be [Z, H_KV, N_K, D]");
   }
+  B200_REQUIRE(!causal || NK == N, "the causal mask needs as many keys as query rows");
+  B200_REQUIRE(NK < (1 << 24), "N_K out of range");
   B200_REQUIRE(HKV > 0 ? H % HKV == 0 : H == 0, "query heads %lld are not a multiple of K/V heads %lld",
                (long long)H, (long long)HKV);
   const int kv_group = HKV > 0 ? (int)(H / HKV) : 1;
@@ -471,10 +478,10 @@ extern "C" int b200_attn_fwd(const b200_tensor *q, const b200_tensor *k, const b
   if (lse != nullptr) {
     B200_REQUIRE(lse->dtype == B200_DTYPE_FLOAT32, "lse must be f32");
     B200_REQUIRE(lse->shape[0] == Z && lse->shape[1] == H && lse->shape[2] == N &&
-                 lse->stride[2] == 1 && lse->stride[1] == N && lse->stride[0] == H * N,
-                 "lse must be contiguous [Z,H,N]");
+                 lse->stride[2] == 1, "lse must be [Z,H,N] with unit last stride");
   }
   if (Z * H == 0 || N == 0) return B200_OK;
+  B200_REQUIRE(NK > 0, "N_K must be positive: softmax over no keys is undefined");
   cudaStream_t s = (cudaStream_t)stream;
 
   const size_t es = dtype_size(q->dtype);
@@ -487,14 +494,15 @@ extern "C" int b200_attn_fwd(const b200_tensor *q, const b200_tensor *k, const b
                            (uintptr_t)o->data % 16 == 0 && (o->stride[0] * es) % 16 == 0 &&
                            (o->stride[1] * es) % 16 == 0 && (o->stride[2] * es) % 16 == 0;
   if (!tensor_core) {
-    B200_REQUIRE(N <= kSimtMaxKeys, "N_CTX %lld exceeds the CUDA-core path's limit %d",
-                 (long long)N, kSimtMaxKeys);
-    const size_t smem = (size_t)(N + D) * sizeof(float);
+    B200_REQUIRE(NK <= kSimtMaxKeys, "N_K %lld exceeds the CUDA-core path's limit %d",
+                 (long long)NK, kSimtMaxKeys);
+    const size_t smem = (size_t)(NK + D) * sizeof(float);
     dim3 grid((unsigned)N, (unsigned)(Z * H));
 #define B200_ATTN_SIMT(T)                                                                    \
   attn_simt_kernel<T><<<grid, kSimtThreads, smem, s>>>(                                      \
       (const T *)q->data, (const T *)k->data, (const T *)v->data, (T *)o->data,              \
-      lse ? (float *)lse->data : nullptr, (int)H, kv_group, (int)N, (int)D, q->stride[0], q->stride[1], \
+      lse ? (float *)lse->data : nullptr, lse ? lse->stride[0] : 0, lse ? lse->stride[1] : 0,   \
+      (int)H, kv_group, (int)N, (int)NK, (int)D, q->stride[0], q->stride[1],                    \
       q->stride[2], k->stride[0], k->stride[1], k->stride[2], v->stride[0], v->stride[1],    \
       v->stride[2], o->stride[0], o->stride[1], o->stride[2], scale, causal ? 1 : 0)
     if (q->dtype == B200_DTYPE_FLOAT32) B200_ATTN_SIMT(float);
@@ -511,6 +519,9 @@ extern "C" int b200_attn_fwd(const b200_tensor *q, const b200_tensor *k, const b
   Params p;
   p.H = (int)H;
   p.N = (int)N;
+  p.NK = (int)NK;
+  p.lse_z = lse ? lse->stride[0] : 0;
+  p.lse_h = lse ? lse->stride[1] : 0;
   p.kv_group = kv_group;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.causal = causal ? 1 : 0;
@@ -529,7 +540,8 @@ extern "C" int b200_attn_fwd(const b200_tensor *q, const b200_tensor *k, const b
   const char *which = getenv("B200OPS_ATTN_KERNEL");
   if (!(which != nullptr && which[0] == 's')) {
     pair::Params pp;
-    pp.H = p.H; pp.N = p.N; pp.ZH = (int)(Z * H); pp.kv_group = kv_group;
+    pp.H = p.H; pp.N = p.N; pp.NK = p.NK; pp.ZH = (int)(Z * H); pp.kv_group = kv_group;
+    pp.lse_z = p.lse_z; pp.lse_h = p.lse_h;
     pp.scale_log2 = p.scale_log2; pp.causal = p.causal;
     pp.lse = p.lse;
     pp.idesc_qk = p.idesc_qk; pp.idesc_pv = p.idesc_pv; pp.status = p.status;

@@ -341,7 +341,8 @@ class B200Device:
     def launch(self, kernel, grid, positional, keywords):
         """Resolve ``kernel`` to its native operator and enqueue it.  No Triton, no
         host arithmetic; an unknown kernel raises ``UnsupportedLaunch``."""
-        key = self._plan_key(kernel, grid, positional, keywords)
+        key = (None if self.registry.reads_device(kernel)
+               else self._plan_key(kernel, grid, positional, keywords))
         plan = self._plans.get(key) if key is not None else None
         if plan is not None:
             abi.replay(plan)

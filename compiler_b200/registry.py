@@ -103,14 +103,15 @@ def _grid_tuple(grid, meta=None):
 class _View:
     """A reshaped alias of a device buffer (same pointer, new logical shape)."""
 
-    def __init__(self, buffer, shape, strides=None):
+    def __init__(self, buffer, shape, strides=None, offset=0):
         self._buffer = buffer
         self.shape = tuple(int(v) for v in shape)
         self._strides = strides
         self.dtype = buffer.dtype
+        self._offset = int(offset)  # elements past the start of the buffer
 
     def data_ptr(self):
-        return self._buffer.data_ptr()
+        return self._buffer.data_ptr() + self._offset * abi.DTYPE_SIZES[abi.dtype_name(self.dtype)]
 
     def stride(self):
         if self._strides is not None:
@@ -268,6 +269,55 @@ def _gqa(device, v, grid, name):
                   scale=float(v["scale"]), causal=False, stream=device.stream)
 
 
+def _flash_varlen(device, v, grid, name):
+    """flash_varlen_fwd_kernel (ops/suite/dev/flash_varlen_fwd_kernel.py:21-335), the dense
+    case its reference covers (:370-418): packed sequences addressed through cu_seqlens (or
+    fixed lengths with batch strides), query and key lengths that differ, h / hk query heads
+    per K / V head, log-sum-exp laid out [h, total_q].  One launch of the attention operator
+    per sequence, on strided views of the packed buffers.  The sequence boundaries are read
+    back from the device, so this launch is bound afresh every time."""
+    for flag in ("is_softcap", "is_dropout", "return_softmax", "is_causal", "is_local",
+                 "is_paged", "is_alibi", "seqlenq_ngroups_swapped", "is_seqused_k"):
+        _require(not v.get(flag, False), name, flag,
+                 "only the dense, unmasked variant has a native operator")
+    h, hk, d, batches = int(v["h"]), int(v["hk"]), int(v["d"]), int(v["b"])
+    _require(hk > 0 and h % hk == 0, name, "hk", "h must be a multiple of hk")
+    total_q = int(v["total_q"])
+    bounds = {}
+    for side in ("q", "k"):
+        if v.get(f"is_cu_seqlens_{side}", False):
+            bounds[side] = [int(x) for x in device.download(v[f"cu_seqlens_{side}_ptr"])]
+            _require(len(bounds[side]) >= batches + 1, name, f"cu_seqlens_{side}_ptr",
+                     "needs b + 1 entries")
+    for batch in range(batches):
+        span = {}
+        for side, rows in (("q", "q"), ("k", "k"), ("v", "k"), ("o", "q")):
+            if rows in bounds:
+                start, stop = bounds[rows][batch], bounds[rows][batch + 1]
+                span[side] = (start * int(v[f"{side}_row_stride"]), stop - start, start)
+            else:
+                length = int(v[f"seqlen_{rows}"])
+                span[side] = (batch * int(v[f"{side}_batch_stride"]), length, batch * length)
+        q_len, k_len = span["q"][1], span["k"][1]
+        if q_len <= 0:
+            continue
+        _require(k_len > 0, name, "cu_seqlens_k_ptr", "a sequence without keys")
+
+        def view(side, heads, length):
+            head, row = int(v[f"{side}_head_stride"]), int(v[f"{side}_row_stride"])
+            return _View(v[f"{side}_ptr"], (1, heads, length, d), (heads * head, head, row, 1),
+                         offset=span[side][0])
+
+        lse = _View(v["softmax_lse_ptr"], (1, h, q_len), (h * total_q, total_q, 1),
+                    offset=span["q"][2])
+        ops.attention(view("q", h, q_len), view("k", hk, k_len), view("v", hk, k_len),
+                      view("o", h, q_len), lse=lse, scale=float(v["scale_softmax"]),
+                      causal=False, stream=device.stream)
+
+
+_flash_varlen.reads_device = True
+
+
 def _flash_decode(device, v, grid, name):
     """flash_decode_kernel (ops/suite/perf/flash_decode.py:21-23): one query row per program."""
     rows = _grid_tuple(grid)[0]
@@ -378,6 +428,12 @@ class Registry:
                 f"({', '.join(parameters)}); nothing falls back to Triton or the host")
         return name, adapter
 
+    def reads_device(self, kernel) -> bool:
+        """True when binding this kernel's launch reads device memory back (its library calls
+        then depend on more than the arguments, and must not be replayed)."""
+        name, parameters, _ = kernel_signature(kernel)
+        return bool(getattr(self._entries.get((name, tuple(parameters))), "reads_device", False))
+
     def supports(self, kernel) -> bool:
         name, parameters, _ = kernel_signature(kernel)
         return (name, tuple(parameters)) in self._entries
@@ -397,6 +453,22 @@ _ATTN = ("q_ptr", "k_ptr", "v_ptr", "out_ptr", "Z", "H", "N_CTX", "scale",
 _MATMUL_STRIDED = ("a_ptr", "b_ptr", "c_ptr", "M", "N", "K", "stride_am", "stride_ak",
                    "stride_bk", "stride_bn", "stride_cm", "stride_cn", "LEAKY", "SLOPE",
                    "BLOCK_M", "BLOCK_N", "BLOCK_K")
+
+
+_VARLEN = (
+    "q_ptr", "k_ptr", "v_ptr", "o_ptr", "p_ptr", "softmax_lse_ptr", "q_row_stride",
+    "k_row_stride", "v_row_stride", "q_head_stride", "k_head_stride", "v_head_stride",
+    "o_row_stride", "o_head_stride", "q_batch_stride", "k_batch_stride",
+    "v_batch_stride", "o_batch_stride", "is_cu_seqlens_q", "cu_seqlens_q_ptr",
+    "is_cu_seqlens_k", "cu_seqlens_k_ptr", "is_seqused_k", "seqused_k_ptr", "b", "bk",
+    "h", "hk", "h_hk_ratio", "seqlen_q", "seqlen_k", "seqlen_q_rounded",
+    "seqlen_k_rounded", "d", "d_rounded", "is_softcap", "softcap", "scale_softmax",
+    "scale_softmax_log2", "is_dropout", "p_dropout", "rp_dropout",
+    "p_dropout_in_uint8_t", "philox_args", "return_softmax", "is_causal", "is_local",
+    "window_size_left", "window_size_right", "seqlenq_ngroups_swapped", "is_paged",
+    "is_alibi", "alibi_slopes_ptr", "alibi_slopes_batch_stride", "total_q",
+    "page_table_ptr", "page_table_batch_stride", "block_size", "k_page_stride",
+    "BLOCK_M", "BLOCK_N", "BLOCK_K", "KERNEL_NUM_WARPS", "PIPELINE_STAGES")
 
 
 def default_registry() -> Registry:
@@ -423,6 +495,7 @@ def default_registry() -> Registry:
     for attn_name in ("attn_fwd_causal_kernel", "attention_forward_kernel", "attention_kernel",
                       "context_attn_fwd_kernel"):
         r.register(attn_name, _ATTN, _attention)
+    r.register("flash_varlen_fwd_kernel", _VARLEN, _flash_varlen)
     r.register("gqa_kernel",
                ("Q", "K", "V", "Out", "stride_qh", "stride_qm", "stride_qk", "stride_kh",
                 "stride_kn", "stride_kk", "stride_vh", "stride_vk", "stride_vn", "stride_oh",

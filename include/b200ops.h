@@ -188,10 +188,13 @@ int b200_gemm_bias_act(const b200_tensor *a, const b200_tensor *b,
                        b200_tensor *c, int act, void *stream);
 
 /* Attention forward.  Replaces attn_fwd_causal_kernel
- * (ops/suite/perf/attn_fwd_causal.py:19-57).  q,o: [Z,H,N,D], k,v: [Z,H_KV,N,D]
+ * (ops/suite/perf/attn_fwd_causal.py:19-57).  q,o: [Z,H,N,D], k,v: [Z,H_KV,N_K,D]
  * with unit last stride; H_KV divides H and query head h reads K / V head
  * h / (H / H_KV) (H_KV == H for the kernels above; fewer K / V heads is gqa_kernel,
- * ops/suite/dev/gqa.py:19-58).  lse: [Z,H,N] f32 or NULL, natural log of the sum of
+ * ops/suite/dev/gqa.py:19-58).  N_K may differ from N when causal == 0 (one sequence of
+ * flash_varlen_fwd_kernel, ops/suite/dev/flash_varlen_fwd_kernel.py:370-418); the causal
+ * mask needs N_K == N.  lse: [Z,H,N] f32 with unit last stride (any batch / head
+ * strides) or NULL, natural log of the sum of
  * exp of the scaled masked scores (ops/suite/dev/flash_varlen_fwd_kernel.py:309). */
 int b200_attn_fwd(const b200_tensor *q, const b200_tensor *k,
                   const b200_tensor *v, b200_tensor *o, b200_tensor *lse,

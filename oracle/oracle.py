@@ -164,6 +164,29 @@ def gqa_attention_ref(q, k, v, scale, causal=False):
                          np.repeat(np.asarray(v), group, axis=1), scale, causal)
 
 
+def varlen_attention_ref(q, k, v, cu_q, cu_k, scale):
+    """Dense attention over packed sequences (ref of
+    ops/suite/dev/flash_varlen_fwd_kernel.py:370-418): q [total_q, H, D], k / v
+    [total_k, H_K, D], sequence b owns rows cu[b]:cu[b+1]; query head h reads K / V head
+    h // (H // H_K).  Returns (out [total_q, H, D], lse [H, total_q]) in float64."""
+    q = np.asarray(q, dtype=np.float64)
+    k = np.asarray(k, dtype=np.float64)
+    v = np.asarray(v, dtype=np.float64)
+    ratio = q.shape[1] // k.shape[1]
+    out = np.zeros(q.shape)
+    lse = np.zeros((q.shape[1], q.shape[0]))
+    for b in range(len(cu_q) - 1):
+        q0, q1, k0, k1 = int(cu_q[b]), int(cu_q[b + 1]), int(cu_k[b]), int(cu_k[b + 1])
+        for h in range(q.shape[1]):
+            s = (q[q0:q1, h] @ k[k0:k1, h // ratio].T) * float(scale)
+            mx = s.max(axis=1, keepdims=True)
+            w = np.exp(s - mx)
+            den = w.sum(axis=1, keepdims=True)
+            out[q0:q1, h] = (w / den) @ v[k0:k1, h // ratio]
+            lse[h, q0:q1] = mx[:, 0] + np.log(den[:, 0])
+    return out, lse
+
+
 def flash_decode_ref(q, k, v, scale, group: int = 1):
     """One query row per (batch, head): out[b] = softmax(scale * K[b // group] q[b]) V[b // group]
     (ref of ops/suite/perf/flash_decode.py:57-70; ``group`` > 1 is the head mapping of

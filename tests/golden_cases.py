@@ -42,6 +42,15 @@ def make_handle(name, parameters, autotuned=()):
     return _Autotuner(fn, autotuned) if autotuned else _Jit(fn)
 
 
+def kernel_parameters(kernel):
+    """Parameter names of a stand-in kernel object."""
+    import inspect
+    target = kernel
+    while not inspect.isfunction(target):
+        target = target.fn
+    return list(inspect.signature(target).parameters)
+
+
 def tags(prefix=None, dtype=None):
     out = []
     for tag, info in sorted(INDEX.items()):

@@ -242,6 +242,96 @@ def test_attention_grouped_kv_heads(device, shape, causal, variant):
         ops.attention(dq, bad, bad, do, scale=scale, causal=causal)
 
 
+@pytest.mark.parametrize("variant", ["pair", "single"])
+@pytest.mark.parametrize("shape", [(2, 4, 2, 300, 517, 64), (1, 2, 2, 129, 64, 128), (1, 3, 1, 640, 1000, 128)])
+def test_attention_other_key_length(device, shape, variant):
+    """N_K keys for N query rows (non-causal), with the log-sum-exp written through strides."""
+    z, hq, hkv, n, nk, d = shape
+    rng = np.random.default_rng(_seed(shape))
+    q = _host(rng.standard_normal((z, hq, n, d)), "bfloat16")
+    k, v = (_host(rng.standard_normal((z, hkv, nk, d)), "bfloat16") for _ in range(2))
+    dq, dk, dv = (_up(device, t, "bfloat16") for t in (q, k, v))
+    do = _poisoned(device, (z, hq, n, d), "bfloat16")
+    pad = 7  # lse rows are n + pad apart
+    dl = device.upload(np.full((z, hq, n + pad), POISON, np.float32))
+
+    class Strided:
+        shape, dtype = (z, hq, n), dl.dtype
+
+        def data_ptr(self):
+            return dl.data_ptr()
+
+        def stride(self):
+            return (hq * (n + pad), n + pad, 1)
+
+    scale = 1.0 / np.sqrt(d)
+    os.environ["B200OPS_ATTN_KERNEL"] = variant
+    try:
+        ops.attention(dq, dk, dv, do, lse=Strided(), scale=scale, causal=False)
+        device.check_status()
+        from compiler_b200.runtime.abi import B200Error
+        with pytest.raises(B200Error):  # the causal mask needs N_K == N
+            ops.attention(dq, dk, dv, do, scale=scale, causal=True)
+    finally:
+        os.environ.pop("B200OPS_ATTN_KERNEL", None)
+    group = hq // hkv
+    out_ref, lse_ref = oracle.attention_ref(q, np.repeat(k, group, axis=1), np.repeat(v, group, axis=1),
+                                            scale, False) if n == nk else (None, None)
+    if out_ref is None:
+        out_ref = np.zeros((z, hq, n, d))
+        lse_ref = np.zeros((z, hq, n))
+        for zz in range(z):
+            for h in range(hq):
+                s_ = (q[zz, h].astype(np.float64) @ k[zz, h // group].astype(np.float64).T) * scale
+                mx = s_.max(axis=1, keepdims=True)
+                w = np.exp(s_ - mx)
+                out_ref[zz, h] = (w / w.sum(axis=1, keepdims=True)) @ v[zz, h // group].astype(np.float64)
+                lse_ref[zz, h] = mx[:, 0] + np.log(w.sum(axis=1))
+    oracle.compare(device.download(do).astype(np.float64), out_ref, *TOL["bfloat16"], name="out")
+    got_lse = device.download(dl)
+    oracle.compare(got_lse[..., :n].astype(np.float64), lse_ref, 1e-3, 1e-3, name="lse")
+    assert np.all(got_lse[..., n:] == POISON)  # the padding between rows is untouched
+
+
+def test_varlen_attention_through_the_launch_surface(device):
+    """flash_varlen_fwd_kernel's dense case at tensor-core sizes: packed sequences, query and
+    key lengths that differ, two query heads per K / V head, lse laid out [h, total_q]."""
+    from compiler_b200.registry import _VARLEN
+    case, _ = golden_cases.load("flash_varlen_fwd_kernel__2x17x19x4x2x16__bfloat16")
+    h, hk, d = 4, 2, 64
+    q_len, k_len = [300, 129, 64], [500, 200, 130]
+    cu_q = np.concatenate(([0], np.cumsum(q_len))).astype(np.int32)
+    cu_k = np.concatenate(([0], np.cumsum(k_len))).astype(np.int32)
+    total_q, total_k = int(cu_q[-1]), int(cu_k[-1])
+    rng = np.random.default_rng(77)
+    q = _host(rng.normal(0, 0.5, (total_q, h, d)), "bfloat16")
+    k = _host(rng.normal(0, 0.5, (total_k, hk, d)), "bfloat16")
+    v = _host(rng.normal(0, 0.5, (total_k, hk, d)), "bfloat16")
+    scale = 1.0 / np.sqrt(d)
+    args = dict(case["args"])
+    args.update({"q_ptr": q.reshape(-1), "k_ptr": k.reshape(-1), "v_ptr": v.reshape(-1),
+                 "o_ptr": np.zeros(total_q * h * d, np.float32),
+                 "softmax_lse_ptr": np.zeros(h * total_q, np.float32),
+                 "q_row_stride": h * d, "o_row_stride": h * d, "k_row_stride": hk * d,
+                 "v_row_stride": hk * d, "q_head_stride": d, "k_head_stride": d,
+                 "v_head_stride": d, "o_head_stride": d, "cu_seqlens_q_ptr": cu_q,
+                 "cu_seqlens_k_ptr": cu_k, "b": 3, "bk": 3, "seqlen_q": max(q_len),
+                 "seqlen_k": max(k_len), "total_q": total_q})
+    case = dict(case, args=args, grid=(19, 3, h),
+                meta={**case["meta"], "h": h, "hk": hk, "h_hk_ratio": h // hk, "d": d,
+                      "d_rounded": d, "scale_softmax": float(scale)})
+    assert tuple(golden_cases.kernel_parameters(case["kernel"])) == _VARLEN
+    before = len(device._plans)
+    got = harness.run_case(case, device)
+    device.check_status()
+    assert len(device._plans) == before  # sequence bounds are read back: never replayed
+    out_ref, lse_ref = oracle.varlen_attention_ref(q, k, v, cu_q, cu_k, scale)
+    oracle.compare(got["o_ptr"].reshape(total_q, h, d).astype(np.float64), out_ref,
+                   *TOL["bfloat16"], name="o")
+    oracle.compare(got["softmax_lse_ptr"].reshape(h, total_q).astype(np.float64), lse_ref,
+                   1e-3, 1e-3, name="lse")
+
+
 @pytest.mark.parametrize("shape", [(1, 1, 8, 16), (2, 2, 16, 32), (1, 2, 100, 80)])
 def test_attention_cuda_core_path(device, shape):
     z, h, n, d = shape

@@ -109,6 +109,24 @@ def test_gqa(tag):
     _assert_same(out.astype(expected.dtype), expected, meta["dtype"])
 
 
+@pytest.mark.parametrize("tag", golden_cases.tags("flash_varlen_fwd_kernel"))
+def test_flash_varlen(tag):
+    case, meta = golden_cases.load(tag)
+    a, m = case["args"], case["meta"]
+    h, hk, d = m["h"], m["hk"], m["d"]
+    cu_q, cu_k = a["cu_seqlens_q_ptr"], a["cu_seqlens_k_ptr"]
+    total_q, total_k = int(cu_q[-1]), int(cu_k[-1])
+    q = np.asarray(a["q_ptr"])[:total_q * h * d].reshape(total_q, h, d)
+    k = np.asarray(a["k_ptr"])[:total_k * hk * d].reshape(total_k, hk, d)
+    v = np.asarray(a["v_ptr"])[:total_k * hk * d].reshape(total_k, hk, d)
+    out, lse = oracle.varlen_attention_ref(q, k, v, cu_q, cu_k, m["scale_softmax"])
+    want_o = np.asarray(case["expected"]["o_ptr"])[:total_q * h * d].reshape(total_q, h, d)
+    want_l = np.asarray(case["expected"]["softmax_lse_ptr"])[:h * total_q].reshape(h, total_q)
+    # the reference's ref computes in float32: agree to its rounding, not bit for bit
+    np.testing.assert_allclose(out, want_o.astype(np.float64), rtol=2e-2 if meta["dtype"] != "float32" else 1e-5, atol=1e-2 if meta["dtype"] != "float32" else 1e-5)
+    np.testing.assert_allclose(lse, want_l.astype(np.float64), rtol=1e-4, atol=1e-4)
+
+
 @pytest.mark.parametrize("tag", golden_cases.tags("flash_decode"))
 def test_flash_decode(tag):
     case, meta = golden_cases.load(tag)
