@@ -85,6 +85,8 @@ constexpr int TMEM_COLS = 512;
 constexpr int THREADS = 192;
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
 
+constexpr int kActLogSoftmax = 100;  // internal epilogue code: row log-softmax (N <= 256)
+
 struct Params {
   int M, N, K;
   int act;
@@ -96,6 +98,8 @@ struct Params {
   int vector_store;  // rows of C are 16-byte aligned and N % 8 == 0 (N % 4 for f32)
   unsigned int *status;
   uint32_t b_lbo, b_sbo;  // B-operand descriptor pitches (bytes)
+  uint32_t b_kstep;       // descriptor advance per UMMA_K step, in 16-byte units
+  int b_kmajor;           // B is given as [N, K] (rows of K): one 64(K) x 256(N) box per stage
   // Row scatter for the tensor-parallel MLP: when scatter_rows > 0 the row block
   // [k * scatter_rows, (k+1) * scatter_rows) of C is not written to `c` but to slot
   // `scatter_slot` of c_rank[k] -- the memory of the rank that owns those rows (a peer
@@ -227,6 +231,44 @@ __device__ __forceinline__ void epilogue_tile(uint32_t t_row, const Params &p, O
   }
 }
 
+// Row log-softmax over the N <= 256 columns of the one column block (the epilogue of
+// log_softmax_linear_kernel, ops/suite/perf/log_softmax_linear.py:32-35): the thread that
+// owns a row reads its accumulator three times from tensor memory -- max, sum of
+// exponentials, y = z - max - log(sum) -- instead of keeping 256 values in registers.
+template <typename OutT>
+__device__ __forceinline__ void epilogue_tile_log_softmax(uint32_t t_row, const Params &p,
+                                                          OutT *crow, bool row_ok) {
+  const int chunks = (p.N + 31) / 32;
+  float mx = -INFINITY;
+  for (int c = 0; c < chunks; ++c) {
+    uint32_t r[32];
+    tmem_ld_32x32b_x32(t_row + (uint32_t)(c * 32), r);
+    tmem_ld_wait();
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (c * 32 + j < p.N) mx = fmaxf(mx, __uint_as_float(r[j]));
+  }
+  float sum = 0.f;
+  for (int c = 0; c < chunks; ++c) {
+    uint32_t r[32];
+    tmem_ld_32x32b_x32(t_row + (uint32_t)(c * 32), r);
+    tmem_ld_wait();
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (c * 32 + j < p.N) sum += expf(__uint_as_float(r[j]) - mx);
+  }
+  const float shift = mx + logf(sum);
+  for (int c = 0; c < chunks; ++c) {
+    uint32_t r[32];
+    tmem_ld_32x32b_x32(t_row + (uint32_t)(c * 32), r);
+    tmem_ld_wait();
+    float v[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) - shift;
+    if (row_ok) store_chunk<OutT>(crow, c * 32, p.N, p.vector_store != 0, v);
+  }
+}
+
 // DUAL: columns [0,128) hold x Wg, [128,256) hold x Wu; out = silu(g) * u
 template <typename OutT>
 __device__ __forceinline__ void epilogue_tile_dual(uint32_t t_row, const Params &p, OutT *crow,
@@ -336,6 +378,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
             tma_load_2d(bdst + B_BOX_BYTES, &tm_b, full_bar(stage), n0 + 64, kb * BK);
             tma_load_2d(bdst + 2 * B_BOX_BYTES, &tm_b2, full_bar(stage), n0, kb * BK);
             tma_load_2d(bdst + 3 * B_BOX_BYTES, &tm_b2, full_bar(stage), n0 + 64, kb * BK);
+          } else if (p.b_kmajor) {
+            // B rows are rows of K: one box of 64 (K) x 256 (N), laid out like the A tile
+            tma_load_2d(bdst, &tm_b, full_bar(stage), kb * BK, nb * TILE_N);
           } else {
             const int n0 = nb * TILE_N;
 #pragma unroll
@@ -372,6 +417,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
     const uint32_t b_lo0 = desc_lo_sw128(b_smem, p.b_lbo);
     constexpr uint32_t a_hi = desc_hi_sw128(1024);
     const uint32_t b_hi = desc_hi_sw128(p.b_sbo);
+    const uint32_t b_kstep = p.b_kstep;
     for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
       if (!wait_all(acc_empty_bar(acc), acc_phase ^ 1u, 2)) { ok = false; break; }
       tc_fence_after_sync();
@@ -384,9 +430,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
         if (leader) {
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k) {
-            // A: +32 bytes along K inside the swizzle span; B: +16 K-rows of 128 bytes
+            // A: +32 bytes along K inside the swizzle span; B: +16 K-rows of 128 bytes when
+            // its rows are rows of N, +32 bytes like A when they are rows of K
             mma_f16_ss(d_tmem, a_lo + (uint32_t)(k * ((UMMA_K * 2) >> 4)), a_hi,
-                       b_lo + (uint32_t)(k * ((UMMA_K * 128) >> 4)), b_hi, p.idesc,
+                       b_lo + (uint32_t)k * b_kstep, b_hi, p.idesc,
                        (kb > 0 || k > 0) ? 1u : 0u);
           }
           tc_commit(empty_bar(stage));  // stage reusable once these MMAs retire
@@ -436,6 +483,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
         // one straight-line epilogue per activation: the choice is made per tile,
         // not per element
         switch (p.act) {
+          case kActLogSoftmax:
+            epilogue_tile_log_softmax<OutT>(t_row, p, crow, row_ok);
+            break;
           case B200_ACT_GELU_TANH:
             epilogue_tile<OutT, B200_ACT_GELU_TANH>(t_row, p, crow, col_base, row_ok);
             break;
@@ -575,16 +625,50 @@ struct Scatter {
 }  // namespace gemm
 }  // namespace b200
 
+// y[row] = log_softmax(x[row] . w[n], n < N) for operands the tensor-core path does not take
+// (fp32, unaligned rows): one CTA per row, thread n owns output n.
+namespace b200 {
+namespace gemm {
+template <typename T, typename OutT>
+__global__ void __launch_bounds__(256)
+linear_log_softmax_simt_kernel(const T *__restrict__ x, const T *__restrict__ w,
+                               OutT *__restrict__ y, int N, int K, int64_t ldx, int64_t ldw,
+                               int64_t ldy) {
+  __shared__ float red[8];
+  const int row = blockIdx.x, n = threadIdx.x;
+  const T *xr = x + (int64_t)row * ldx;
+  float z = 0.f;
+  if (n < N) {
+    const T *wr = w + (int64_t)n * ldw;
+    for (int k = 0; k < K; ++k) z = fmaf(io<T>::load(xr[k]), io<T>::load(wr[k]), z);
+  }
+  float mx = warp_max(n < N ? z : -INFINITY);
+  if ((n & 31) == 0) red[n >> 5] = mx;
+  __syncthreads();
+  mx = red[0];
+  for (int i = 1; i < 8; ++i) mx = fmaxf(mx, red[i]);
+  __syncthreads();
+  float sum = warp_sum(n < N ? expf(z - mx) : 0.f);
+  if ((n & 31) == 0) red[n >> 5] = sum;
+  __syncthreads();
+  sum = 0.f;
+  for (int i = 0; i < 8; ++i) sum += red[i];
+  if (n < N) y[(int64_t)row * ldy + n] = io<OutT>::store(z - mx - logf(sum));
+}
+}  // namespace gemm
+}  // namespace b200
+
+// b_rows_are_n: B is given as [N, K] (the weight layout of a linear layer) instead of [K, N].
 static int gemm_impl(const b200_tensor *a, const b200_tensor *b, const b200_tensor *b2,
                      const b200_tensor *bias, b200_tensor *c, int act, void *stream,
-                     const b200::gemm::Scatter *scatter) {
+                     const b200::gemm::Scatter *scatter, bool b_rows_are_n = false) {
   using namespace b200;
   using namespace b200::gemm;
   int st;
   if ((st = check_tensor(a, "a", 2)) || (st = check_tensor(b, "b", 2)) ||
       (st = check_tensor(c, "c", 2)))
     return st;
-  if (act < B200_ACT_NONE || act > B200_ACT_SWIGLU)
+  if ((act < B200_ACT_NONE || act > B200_ACT_SWIGLU) && act != kActLogSoftmax)
     return fail(B200_USAGE, "act %d is not a b200_act value", act);
   if (bias != nullptr && (st = check_tensor(bias, "bias", 1))) return st;
   if (act == B200_ACT_SWIGLU) {
@@ -598,13 +682,16 @@ static int gemm_impl(const b200_tensor *a, const b200_tensor *b, const b200_tens
   B200_REQUIRE(b->dtype == a->dtype, "a/b dtypes differ (%u/%u)", a->dtype, b->dtype);
   B200_REQUIRE(c->dtype == a->dtype || c->dtype == B200_DTYPE_FLOAT32,
                "c dtype %u must be a's dtype or f32", c->dtype);
-  const int64_t M = a->shape[0], K = a->shape[1], N = b->shape[1];
-  B200_REQUIRE(b->shape[0] == K, "a is [%lld,%lld] but b has %lld rows", (long long)M,
-               (long long)K, (long long)b->shape[0]);
+  const int64_t M = a->shape[0], K = a->shape[1], N = b->shape[b_rows_are_n ? 0 : 1];
+  B200_REQUIRE(b->shape[b_rows_are_n ? 1 : 0] == K, "a is [%lld,%lld] but b has K = %lld",
+               (long long)M, (long long)K, (long long)b->shape[b_rows_are_n ? 1 : 0]);
+  if (act == kActLogSoftmax)
+    B200_REQUIRE(N >= 1 && N <= BN && bias == nullptr && b2 == nullptr && scatter == nullptr,
+                 "the row log-softmax epilogue takes 1..%d output columns, no bias", BN);
   B200_REQUIRE(c->shape[0] == M && c->shape[1] == N, "c shape is not [M,N]");
   B200_REQUIRE(a->stride[1] == 1 && b->stride[1] == 1 && c->stride[1] == 1,
                "a/b/c need unit column stride (row-major)");
-  B200_REQUIRE(a->stride[0] >= K && b->stride[0] >= N && c->stride[0] >= N,
+  B200_REQUIRE(a->stride[0] >= K && b->stride[0] >= (b_rows_are_n ? K : N) && c->stride[0] >= N,
                "row stride below row width");
   B200_REQUIRE(M < (1 << 30) && N < (1 << 30) && K < (1 << 30), "extent out of range");
   if (b2 != nullptr) {
@@ -640,7 +727,23 @@ static int gemm_impl(const b200_tensor *a, const b200_tensor *b, const b200_tens
       B200_REQUIRE(scatter->c_rank[r] != nullptr && (uintptr_t)scatter->c_rank[r] % 16 == 0,
                    "destination pointer of rank %d is null or unaligned", r);
   }
+  if (!tensor_core && act == kActLogSoftmax) {
+    B200_REQUIRE(b_rows_are_n, "the CUDA-core log-softmax path takes B as [N, K]");
+#define B200_LLS(T, OutT)                                                                   \
+  linear_log_softmax_simt_kernel<T, OutT><<<(unsigned)M, 256, 0, s>>>(                      \
+      (const T *)a->data, (const T *)b->data, (OutT *)c->data, (int)N, (int)K, a->stride[0], \
+      b->stride[0], c->stride[0])
+    if (a->dtype == B200_DTYPE_FLOAT32) B200_LLS(float, float);
+    else if (a->dtype == B200_DTYPE_FLOAT16 && c->dtype == B200_DTYPE_FLOAT32) B200_LLS(__half, float);
+    else if (a->dtype == B200_DTYPE_FLOAT16) B200_LLS(__half, __half);
+    else if (c->dtype == B200_DTYPE_FLOAT32) B200_LLS(__nv_bfloat16, float);
+    else B200_LLS(__nv_bfloat16, __nv_bfloat16);
+#undef B200_LLS
+    B200_CUDA_OK(cudaGetLastError());
+    return B200_OK;
+  }
   if (!tensor_core) {
+    B200_REQUIRE(!b_rows_are_n, "B as [N, K] is taken by the tensor-core path only");
     if (a->dtype == B200_DTYPE_FLOAT32) return launch_simt<float, float>(a, b, b2, bias, c, act, s);
     if (a->dtype == B200_DTYPE_FLOAT16) {
       return c->dtype == B200_DTYPE_FLOAT32
@@ -659,7 +762,13 @@ static int gemm_impl(const b200_tensor *a, const b200_tensor *b, const b200_tens
     const uint32_t box[2] = {BK, BM};
     if ((st = encode_tensor_map(&ta, a->dtype, a->data, 2, dims, strides, box))) return st;
   }
-  {
+  if (b_rows_are_n) {
+    const uint64_t dims[2] = {(uint64_t)K, (uint64_t)N};
+    const uint64_t strides[2] = {es, (uint64_t)b->stride[0] * es};
+    const uint32_t box[2] = {BK, BN};
+    if ((st = encode_tensor_map(&tb, b->dtype, b->data, 2, dims, strides, box))) return st;
+    tb2 = tb;
+  } else {
     const uint64_t dims[2] = {(uint64_t)N, (uint64_t)K};
     const uint64_t strides[2] = {es, (uint64_t)b->stride[0] * es};
     const uint32_t box[2] = {64, BK};
@@ -676,13 +785,16 @@ static int gemm_impl(const b200_tensor *a, const b200_tensor *b, const b200_tens
   p.bias = bias ? bias->data : nullptr;
   p.c = c->data;
   p.ldc = c->stride[0];
-  p.idesc = sm100::make_idesc_f16(BM, BN, a->dtype == B200_DTYPE_BFLOAT16 ? 1 : 0, 0, 1);
+  p.idesc = sm100::make_idesc_f16(BM, BN, a->dtype == B200_DTYPE_BFLOAT16 ? 1 : 0, 0,
+                                  b_rows_are_n ? 0 : 1);
   const size_t cs = dtype_size(c->dtype);
   p.vector_store = ((c->stride[0] * cs) % 16 == 0 && (uintptr_t)c->data % 16 == 0) ? 1 : 0;
   p.status = device_status_word();
   if (p.status == nullptr) return fail(B200_RESOURCE, "no status word on this device");
-  p.b_lbo = B_BOX_BYTES;  // pitch between 64-column chunks of the B tile
-  p.b_sbo = 1024;         // pitch between groups of 8 K-rows
+  p.b_kmajor = b_rows_are_n ? 1 : 0;
+  p.b_lbo = b_rows_are_n ? 16 : B_BOX_BYTES;  // [K,N]: pitch between 64-column chunks of the tile
+  p.b_sbo = 1024;                             // pitch between groups of 8 rows
+  p.b_kstep = b_rows_are_n ? (UMMA_K * 2) >> 4 : (UMMA_K * 128) >> 4;
   p.scatter_rows = 0;
   p.scatter_slot = 0;
   {
@@ -731,4 +843,9 @@ extern "C" int b200_gemm_scatter_rows(const b200_tensor *a, const b200_tensor *b
   if (world >= 1 && world <= 8 && slot >= 0 && slot < world) c.data = c_rank[slot];
   const gemm::Scatter scatter{c_rank, world, slot, rows_per_rank};
   return gemm_impl(a, b, nullptr, nullptr, &c, B200_ACT_NONE, stream, &scatter);
+}
+
+extern "C" int b200_linear_log_softmax(const b200_tensor *x, const b200_tensor *w, b200_tensor *y,
+                                       void *stream) {
+  return gemm_impl(x, w, nullptr, nullptr, y, b200::gemm::kActLogSoftmax, stream, nullptr, true);
 }

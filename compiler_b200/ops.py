@@ -66,6 +66,14 @@ def gemm(a, b, c, *, bias=None, act=abi.ACT_NONE, b2=None, stream=0):
                                            int(act), stream))
 
 
+def linear_log_softmax(x, w, y, *, stream=0):
+    """y = log_softmax(x @ w.T) per row; x [M,K], w [N,K], N <= 256.
+
+    Native form of log_softmax_linear_kernel (ops/suite/perf/log_softmax_linear.py:19-35)."""
+    xd, wd, yd = _desc(x), _desc(w), _desc(y)
+    abi.check(abi.lib().b200_linear_log_softmax(_ref(xd), _ref(wd), _ref(yd), stream))
+
+
 def attention(q, k, v, o, *, lse=None, scale=None, causal=True, stream=0):
     """o = softmax(scale * q k^T (+ causal mask)) v over [Z,H,N,D]; lse = log-sum-exp.
 

@@ -33,6 +33,7 @@ def _upload(device, array, dtype):
 def main(argv=None):
     parser = argparse.ArgumentParser(description=__doc__.split("\n")[0])
     parser.add_argument("op", choices=["softmax", "rmsnorm", "gemm", "attention", "attention_decode",
+                                       "linear_log_softmax",
                                        "swiglu_gemm"])
     parser.add_argument("--shape", type=int, nargs="+", required=True)
     parser.add_argument("--dtype", default=None)
@@ -80,6 +81,14 @@ def main(argv=None):
             b2 = _upload(device, rng.standard_normal((k, n), dtype=np.float32) / np.sqrt(k), dtype)
             launch = lambda: ops.gemm(a, b, c, b2=b2, act=abi.ACT_SWIGLU)  # noqa: E731
             work = {"flop": 4 * m * n * k}
+    elif args.op == "linear_log_softmax":
+        dtype = args.dtype or "bfloat16"
+        m, n, k = shape
+        x = _upload(device, rng.standard_normal((m, k), dtype=np.float32), dtype)
+        w = _upload(device, rng.standard_normal((n, k), dtype=np.float32) / np.sqrt(k), dtype)
+        y = device.alloc((m, n), dtype)
+        launch = lambda: ops.linear_log_softmax(x, w, y)  # noqa: E731
+        work = {"bytes": (m * k + n * k + m * n) * abi.DTYPE_SIZES[dtype]}
     elif args.op == "attention_decode":
         dtype = args.dtype or "bfloat16"
         rows, n, d = shape

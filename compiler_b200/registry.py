@@ -216,6 +216,16 @@ def _linear_act(device, v, grid, name):
              bias=_View(v["b_ptr"], (n,)), act=abi.ACT_GELU_ERF, stream=device.stream)
 
 
+def _log_softmax_linear(device, v, grid, name):
+    """log_softmax_linear_kernel (ops/suite/perf/log_softmax_linear.py:19): one program per row,
+    contiguous x [rows, K], w [N, K], y [rows, N]."""
+    rows = _grid_tuple(grid)[0]
+    k, n = int(v["K"]), int(v["N"])
+    _require(n <= 64, name, "N", "the reference program covers at most 64 outputs")
+    ops.linear_log_softmax(_View(v["x_ptr"], (rows, k)), _View(v["w_ptr"], (n, k)),
+                           _View(v["y_ptr"], (rows, n)), stream=device.stream)
+
+
 def _gemm_bias_act(device, v, grid, name):
     """Native handle: C = act(A @ B + bias) with a selectable epilogue
     (kernels.gemm_bias_act_kernel)."""
@@ -495,6 +505,8 @@ def default_registry() -> Registry:
     for attn_name in ("attn_fwd_causal_kernel", "attention_forward_kernel", "attention_kernel",
                       "context_attn_fwd_kernel"):
         r.register(attn_name, _ATTN, _attention)
+    r.register("log_softmax_linear_kernel", ("x_ptr", "w_ptr", "y_ptr", "K", "N"),
+               _log_softmax_linear)
     r.register("flash_varlen_fwd_kernel", _VARLEN, _flash_varlen)
     r.register("gqa_kernel",
                ("Q", "K", "V", "Out", "stride_qh", "stride_qm", "stride_qk", "stride_kh",

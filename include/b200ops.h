@@ -187,6 +187,15 @@ int b200_gemm_bias_act(const b200_tensor *a, const b200_tensor *b,
                        const b200_tensor *b2, const b200_tensor *bias,
                        b200_tensor *c, int act, void *stream);
 
+/* y = log_softmax(x @ w^T) over the output columns.  Replaces log_softmax_linear_kernel
+ * (ops/suite/perf/log_softmax_linear.py:19-35): x [M,K], w [N,K] (a linear layer's weight:
+ * rows of K), y [M,N] in x's type or f32, 1 <= N <= 256.  16-bit operands with 16-byte
+ * aligned rows run the tensor-core GEMM with w fed as a K-major operand and the row
+ * log-softmax done in the epilogue on the accumulator (no intermediate [M,N] matrix);
+ * other operands take a CUDA-core kernel. */
+int b200_linear_log_softmax(const b200_tensor *x, const b200_tensor *w, b200_tensor *y,
+                            void *stream);
+
 /* Attention forward.  Replaces attn_fwd_causal_kernel
  * (ops/suite/perf/attn_fwd_causal.py:19-57).  q,o: [Z,H,N,D], k,v: [Z,H_KV,N_K,D]
  * with unit last stride; H_KV divides H and query head h reads K / V head

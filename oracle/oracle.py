@@ -155,6 +155,14 @@ def attention_ref(q, k, v, scale, causal=True):
     return out, lse
 
 
+def log_softmax_linear_ref(x, w):
+    """log_softmax(x @ w.T) over the last axis (ref of
+    ops/suite/perf/log_softmax_linear.py:45-51), float64."""
+    z = np.asarray(x, dtype=np.float64) @ np.asarray(w, dtype=np.float64).T
+    m = z.max(-1, keepdims=True)
+    return z - m - np.log(np.exp(z - m).sum(-1, keepdims=True))
+
+
 def gqa_attention_ref(q, k, v, scale, causal=False):
     """Attention with fewer K / V heads than query heads: query head h reads K / V head
     h // (H_Q // H_KV) (ref of ops/suite/dev/gqa.py:69-85).  q [Z,H_Q,N,D], k / v

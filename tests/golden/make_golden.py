@@ -55,6 +55,8 @@ OPERATORS = {
     "perf/flash_decode.py": [(1, 8, 256, 64)],
     "dev/gqa.py": [],
     "dev/flash_varlen_fwd_kernel.py": [],
+    # GEMM with a reduction epilogue
+    "perf/log_softmax_linear.py": [(64, 1024)],
 }
 MID_DTYPES = ("bfloat16",)  # mid-size shapes are stored for one dtype to keep fixtures small
 

@@ -346,6 +346,36 @@ def test_attention_cuda_core_path(device, shape):
     oracle.compare(device.download(dl).astype(np.float64), lse_ref, 1e-4, 1e-5)
 
 
+@pytest.mark.parametrize("out_dtype", ["same", "float32"])
+@pytest.mark.parametrize("dtype", ["bfloat16", "float16", "float32"])
+@pytest.mark.parametrize("shape", [(1, 1, 64), (100, 24, 1000), (300, 64, 4096), (129, 200, 512),
+                                   (4096, 256, 256), (257, 33, 72), (64, 24, 33)])
+def test_linear_log_softmax_sweep(device, shape, dtype, out_dtype):
+    """y = log_softmax(x @ w.T): the tensor-core GEMM with w as a K-major operand and the
+    reduction in its epilogue; fp32 and unaligned rows on the CUDA-core kernel."""
+    m, n, k = shape
+    rng = np.random.default_rng(_seed(shape, dtype))
+    x = _host(rng.standard_normal((m, k)), dtype)
+    w = _host(rng.standard_normal((n, k)) / np.sqrt(k) * 3, dtype)
+    dx, dw = _up(device, x, dtype), _up(device, w, dtype)
+    ydt = dtype if out_dtype == "same" else "float32"
+    dy = _poisoned(device, (m, n), ydt)
+    ops.linear_log_softmax(dx, dw, dy)
+    device.check_status()
+    ref = oracle.log_softmax_linear_ref(x, w)
+    rtol, atol = (2e-3, 2e-3) if dtype == "float32" else ((2e-2, 2e-2) if ydt != "float32" else (5e-3, 5e-3))
+    oracle.compare(device.download(dy).astype(np.float64), ref, rtol, atol, name="y")
+
+
+def test_linear_log_softmax_rejections(device):
+    from compiler_b200.runtime.abi import B200Error
+    x = _up(device, _host(np.zeros((8, 64)), "bfloat16"), "bfloat16")
+    with pytest.raises(B200Error):  # more outputs than one column block
+        ops.linear_log_softmax(x, device.alloc((257, 64), "bfloat16"), device.alloc((8, 257), "bfloat16"))
+    with pytest.raises(B200Error):  # K mismatch
+        ops.linear_log_softmax(x, device.alloc((24, 32), "bfloat16"), device.alloc((8, 24), "bfloat16"))
+
+
 DECODE_SHAPES = [  # (query rows B, group, N_CTX, head_dim)
     (1, 1, 1, 16), (3, 1, 7, 32), (4, 1, 255, 64), (4, 1, 256, 128), (2, 1, 1000, 128),
     (5, 1, 4097, 64), (1, 1, 32768, 128),      # one row: its keys are split over a cluster

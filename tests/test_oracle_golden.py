@@ -109,6 +109,14 @@ def test_gqa(tag):
     _assert_same(out.astype(expected.dtype), expected, meta["dtype"])
 
 
+@pytest.mark.parametrize("tag", golden_cases.tags("log_softmax_linear"))
+def test_log_softmax_linear(tag):
+    case, meta = golden_cases.load(tag)
+    y = oracle.log_softmax_linear_ref(case["args"]["x_ptr"], case["args"]["w_ptr"])
+    expected = case["expected"]["y_ptr"]
+    _assert_same(y.astype(expected.dtype), expected, meta["dtype"])
+
+
 @pytest.mark.parametrize("tag", golden_cases.tags("flash_varlen_fwd_kernel"))
 def test_flash_varlen(tag):
     case, meta = golden_cases.load(tag)
