@@ -100,6 +100,7 @@ struct Params {
   uint32_t b_lbo, b_sbo;  // B-operand descriptor pitches (bytes)
   uint32_t b_kstep;       // descriptor advance per UMMA_K step, in 16-byte units
   int b_kmajor;           // B is given as [N, K] (rows of K): one 64(K) x 256(N) box per stage
+  const float *row_scale; // optional [M] factors applied to the accumulator rows before the bias
   // Row scatter for the tensor-parallel MLP: when scatter_rows > 0 the row block
   // [k * scatter_rows, (k+1) * scatter_rows) of C is not written to `c` but to slot
   // `scatter_slot` of c_rank[k] -- the memory of the rank that owns those rows (a peer
@@ -204,12 +205,13 @@ __device__ __forceinline__ void store_chunk(OutT *crow, int col0, int n, bool ve
 // bias + activation + store of one 32-column chunk held in registers
 template <typename OutT, int ACT>
 __device__ __forceinline__ void finish_chunk(const uint32_t (&r)[32], const Params &p, OutT *crow,
-                                             int col0, bool row_ok) {
+                                             int col0, bool row_ok, float row_mul) {
   if (col0 >= p.N) return;  // warp-uniform
   float b[32], v[32];
   load_bias_chunk(p.bias, p.bias_kind, col0, p.N, b);
 #pragma unroll
-  for (int j = 0; j < 32; ++j) v[j] = activate<OutT, ACT>(__uint_as_float(r[j]) + b[j]);
+  for (int j = 0; j < 32; ++j)
+    v[j] = activate<OutT, ACT>(fmaf(__uint_as_float(r[j]), row_mul, b[j]));
   if (row_ok) store_chunk<OutT>(crow, col0, p.N, p.vector_store != 0, v);
 }
 
@@ -217,17 +219,17 @@ __device__ __forceinline__ void finish_chunk(const uint32_t (&r)[32], const Para
 // chunk c+1 is in flight while chunk c is converted and stored.
 template <typename OutT, int ACT>
 __device__ __forceinline__ void epilogue_tile(uint32_t t_row, const Params &p, OutT *crow,
-                                              int col_base, bool row_ok) {
+                                              int col_base, bool row_ok, float row_mul) {
   uint32_t ra[32], rb[32];
   tmem_ld_32x32b_x32(t_row, ra);
 #pragma unroll 1
   for (int chunk = 0; chunk < BN / 32; chunk += 2) {
     tmem_ld_wait();
     tmem_ld_32x32b_x32(t_row + (uint32_t)((chunk + 1) * 32), rb);
-    finish_chunk<OutT, ACT>(ra, p, crow, col_base + chunk * 32, row_ok);
+    finish_chunk<OutT, ACT>(ra, p, crow, col_base + chunk * 32, row_ok, row_mul);
     tmem_ld_wait();
     if (chunk + 2 < BN / 32) tmem_ld_32x32b_x32(t_row + (uint32_t)((chunk + 2) * 32), ra);
-    finish_chunk<OutT, ACT>(rb, p, crow, col_base + (chunk + 1) * 32, row_ok);
+    finish_chunk<OutT, ACT>(rb, p, crow, col_base + (chunk + 1) * 32, row_ok, row_mul);
   }
 }
 
@@ -477,6 +479,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
                ((int64_t)p.scatter_slot * p.scatter_rows + local) * p.ldc;
       }
       const int col_base = nb * TILE_N;
+      const float row_mul = (p.row_scale != nullptr && row_ok) ? p.row_scale[row] : 1.0f;
       if constexpr (DUAL) {
         epilogue_tile_dual<OutT>(t_row, p, crow, col_base, row_ok);
       } else {
@@ -487,16 +490,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
             epilogue_tile_log_softmax<OutT>(t_row, p, crow, row_ok);
             break;
           case B200_ACT_GELU_TANH:
-            epilogue_tile<OutT, B200_ACT_GELU_TANH>(t_row, p, crow, col_base, row_ok);
+            epilogue_tile<OutT, B200_ACT_GELU_TANH>(t_row, p, crow, col_base, row_ok, row_mul);
             break;
           case B200_ACT_GELU_ERF:
-            epilogue_tile<OutT, B200_ACT_GELU_ERF>(t_row, p, crow, col_base, row_ok);
+            epilogue_tile<OutT, B200_ACT_GELU_ERF>(t_row, p, crow, col_base, row_ok, row_mul);
             break;
           case B200_ACT_LEAKY_RELU:
-            epilogue_tile<OutT, B200_ACT_LEAKY_RELU>(t_row, p, crow, col_base, row_ok);
+            epilogue_tile<OutT, B200_ACT_LEAKY_RELU>(t_row, p, crow, col_base, row_ok, row_mul);
             break;
           default:
-            epilogue_tile<OutT, B200_ACT_NONE>(t_row, p, crow, col_base, row_ok);
+            epilogue_tile<OutT, B200_ACT_NONE>(t_row, p, crow, col_base, row_ok, row_mul);
         }
       }
       // this warp has drained its quarter of the accumulator
@@ -523,7 +526,7 @@ template <typename InT, typename OutT>
 __global__ void __launch_bounds__(256)
 gemm_simt_kernel(const InT *__restrict__ a, int64_t lda, const InT *__restrict__ b, int64_t ldb,
                  const InT *__restrict__ b2, OutT *__restrict__ c, int64_t ldc, int M, int N,
-                 int K, const void *bias, int bias_kind, int act) {
+                 int K, const void *bias, int bias_kind, int act, const float *row_scale) {
   __shared__ float sa[32][33];
   __shared__ float sb[32][33];
   __shared__ float sb2[32][33];
@@ -566,7 +569,7 @@ gemm_simt_kernel(const InT *__restrict__ a, int64_t lda, const InT *__restrict__
     if (act == B200_ACT_SWIGLU) {
       z = acc[i] / (1.0f + expf(-acc[i])) * acc2[i];
     } else {
-      z = acc[i] + bias_v;
+      z = fmaf(acc[i], row_scale != nullptr ? row_scale[m] : 1.0f, bias_v);
       switch (act) {
         case B200_ACT_GELU_ERF: z = gelu_erf(z); break;
         case B200_ACT_GELU_TANH: z = gelu_tanh_exact(z); break;
@@ -580,14 +583,15 @@ gemm_simt_kernel(const InT *__restrict__ a, int64_t lda, const InT *__restrict__
 
 template <typename InT, typename OutT>
 static int launch_simt(const b200_tensor *a, const b200_tensor *b, const b200_tensor *b2,
-                       const b200_tensor *bias, b200_tensor *c, int act, cudaStream_t stream) {
+                       const b200_tensor *bias, b200_tensor *c, int act, cudaStream_t stream,
+                       const float *row_scale = nullptr) {
   const int M = (int)a->shape[0], K = (int)a->shape[1], N = (int)b->shape[1];
   dim3 grid((N + 31) / 32, (M + 31) / 32);
   B200_REQUIRE(grid.y <= 65535, "M too large for the CUDA-core path");
   gemm_simt_kernel<InT, OutT><<<grid, 256, 0, stream>>>(
       (const InT *)a->data, a->stride[0], (const InT *)b->data, b->stride[0],
       b2 ? (const InT *)b2->data : nullptr, (OutT *)c->data, c->stride[0], M, N, K,
-      bias ? bias->data : nullptr, bias ? (int)bias->dtype : 0, act);
+      bias ? bias->data : nullptr, bias ? (int)bias->dtype : 0, act, row_scale);
   B200_CUDA_OK(cudaGetLastError());
   return B200_OK;
 }
@@ -661,7 +665,8 @@ linear_log_softmax_simt_kernel(const T *__restrict__ x, const T *__restrict__ w,
 // b_rows_are_n: B is given as [N, K] (the weight layout of a linear layer) instead of [K, N].
 static int gemm_impl(const b200_tensor *a, const b200_tensor *b, const b200_tensor *b2,
                      const b200_tensor *bias, b200_tensor *c, int act, void *stream,
-                     const b200::gemm::Scatter *scatter, bool b_rows_are_n = false) {
+                     const b200::gemm::Scatter *scatter, bool b_rows_are_n = false,
+                     const float *row_scale = nullptr) {
   using namespace b200;
   using namespace b200::gemm;
   int st;
@@ -744,15 +749,15 @@ static int gemm_impl(const b200_tensor *a, const b200_tensor *b, const b200_tens
   }
   if (!tensor_core) {
     B200_REQUIRE(!b_rows_are_n, "B as [N, K] is taken by the tensor-core path only");
-    if (a->dtype == B200_DTYPE_FLOAT32) return launch_simt<float, float>(a, b, b2, bias, c, act, s);
+    if (a->dtype == B200_DTYPE_FLOAT32) return launch_simt<float, float>(a, b, b2, bias, c, act, s, row_scale);
     if (a->dtype == B200_DTYPE_FLOAT16) {
       return c->dtype == B200_DTYPE_FLOAT32
-                 ? launch_simt<__half, float>(a, b, b2, bias, c, act, s)
-                 : launch_simt<__half, __half>(a, b, b2, bias, c, act, s);
+                 ? launch_simt<__half, float>(a, b, b2, bias, c, act, s, row_scale)
+                 : launch_simt<__half, __half>(a, b, b2, bias, c, act, s, row_scale);
     }
     return c->dtype == B200_DTYPE_FLOAT32
-               ? launch_simt<__nv_bfloat16, float>(a, b, b2, bias, c, act, s)
-               : launch_simt<__nv_bfloat16, __nv_bfloat16>(a, b, b2, bias, c, act, s);
+               ? launch_simt<__nv_bfloat16, float>(a, b, b2, bias, c, act, s, row_scale)
+               : launch_simt<__nv_bfloat16, __nv_bfloat16>(a, b, b2, bias, c, act, s, row_scale);
   }
 
   CUtensorMap ta, tb, tb2;
@@ -791,6 +796,7 @@ static int gemm_impl(const b200_tensor *a, const b200_tensor *b, const b200_tens
   p.vector_store = ((c->stride[0] * cs) % 16 == 0 && (uintptr_t)c->data % 16 == 0) ? 1 : 0;
   p.status = device_status_word();
   if (p.status == nullptr) return fail(B200_RESOURCE, "no status word on this device");
+  p.row_scale = row_scale;
   p.b_kmajor = b_rows_are_n ? 1 : 0;
   p.b_lbo = b_rows_are_n ? 16 : B_BOX_BYTES;  // [K,N]: pitch between 64-column chunks of the tile
   p.b_sbo = 1024;                             // pitch between groups of 8 rows
@@ -848,4 +854,107 @@ extern "C" int b200_gemm_scatter_rows(const b200_tensor *a, const b200_tensor *b
 extern "C" int b200_linear_log_softmax(const b200_tensor *x, const b200_tensor *w, b200_tensor *y,
                                        void *stream) {
   return gemm_impl(x, w, nullptr, nullptr, y, b200::gemm::kActLogSoftmax, stream, nullptr, true);
+}
+
+// ---- RMS-normalised matmul ----------------------------------------------------------
+namespace b200 {
+namespace gemm {
+
+// rinv[row] = rsqrt(mean(x[row]^2) + eps)
+template <typename T>
+__global__ void __launch_bounds__(256)
+row_rinv_kernel(const T *__restrict__ x, int64_t ldx, int K, float eps, float *__restrict__ rinv) {
+  __shared__ float red[8];
+  const T *xr = x + (int64_t)blockIdx.x * ldx;
+  float sum = 0.f;
+  constexpr int PER = 16 / (int)sizeof(T);
+  if ((ldx * (int64_t)sizeof(T)) % 16 == 0 && (uintptr_t)x % 16 == 0) {
+    const int vecs = K / PER;
+    for (int i = threadIdx.x; i < vecs; i += 256) {
+      vec16<T> v;
+      v.raw = ld_stream16(xr + i * PER);
+#pragma unroll
+      for (int j = 0; j < PER; ++j) {
+        const float f = io<T>::load(v.e[j]);
+        sum = fmaf(f, f, sum);
+      }
+    }
+    for (int k = vecs * PER + threadIdx.x; k < K; k += 256) {
+      const float f = io<T>::load(xr[k]);
+      sum = fmaf(f, f, sum);
+    }
+  } else {
+    for (int k = threadIdx.x; k < K; k += 256) {
+      const float f = io<T>::load(xr[k]);
+      sum = fmaf(f, f, sum);
+    }
+  }
+  sum = warp_sum(sum);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = sum;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float total = 0.f;
+    for (int i = 0; i < 8; ++i) total += red[i];
+    rinv[blockIdx.x] = rsqrtf(total / (float)K + eps);
+  }
+}
+
+// out[k, n] = g[k] * w[k, n], one rounding
+template <typename T>
+__global__ void __launch_bounds__(256)
+scale_rows_kernel(const T *__restrict__ w, int64_t ldw, const T *__restrict__ g, T *__restrict__ out,
+                  int64_t ldo, int K, int N) {
+  for (int k = blockIdx.y; k < K; k += gridDim.y) {
+    const float gk = io<T>::load(g[k]);
+    for (int n = blockIdx.x * 256 + threadIdx.x; n < N; n += gridDim.x * 256)
+      out[(int64_t)k * ldo + n] = io<T>::store(gk * io<T>::load(w[(int64_t)k * ldw + n]));
+  }
+}
+
+template <typename T>
+static int rms_matmul_prepare(const b200_tensor *x, const b200_tensor *g, const b200_tensor *w,
+                              b200_tensor *scaled_w, float *rinv, float eps, cudaStream_t s) {
+  const int M = (int)x->shape[0], K = (int)x->shape[1], N = (int)w->shape[1];
+  row_rinv_kernel<T><<<M, 256, 0, s>>>((const T *)x->data, x->stride[0], K, eps, rinv);
+  B200_CUDA_OK(cudaGetLastError());
+  dim3 grid((unsigned)((N + 255) / 256 < 64 ? (N + 255) / 256 : 64), (unsigned)(K < 4096 ? K : 4096));
+  scale_rows_kernel<T><<<grid, 256, 0, s>>>((const T *)w->data, w->stride[0], (const T *)g->data,
+                                            (T *)scaled_w->data, scaled_w->stride[0], K, N);
+  B200_CUDA_OK(cudaGetLastError());
+  return B200_OK;
+}
+
+}  // namespace gemm
+}  // namespace b200
+
+extern "C" int b200_rms_matmul(const b200_tensor *x, const b200_tensor *g, const b200_tensor *w,
+                               b200_tensor *out, float eps, b200_tensor *scratch_w,
+                               b200_tensor *scratch_rinv, void *stream) {
+  using namespace b200;
+  int st;
+  if ((st = check_tensor(x, "x", 2)) || (st = check_tensor(g, "g", 1)) ||
+      (st = check_tensor(w, "w", 2)) || (st = check_tensor(out, "out", 2)) ||
+      (st = check_tensor(scratch_w, "scratch_w", 2)) ||
+      (st = check_tensor(scratch_rinv, "scratch_rinv", 1)))
+    return st;
+  B200_REQUIRE(is_float_io(x->dtype) && w->dtype == x->dtype && g->dtype == x->dtype &&
+               scratch_w->dtype == x->dtype, "x, g, w and scratch_w must share one float type");
+  const int64_t M = x->shape[0], K = x->shape[1], N = w->shape[1];
+  B200_REQUIRE(w->shape[0] == K && g->shape[0] == K && g->stride[0] == 1, "g must be contiguous [K], w [K,N]");
+  B200_REQUIRE(x->stride[1] == 1 && w->stride[1] == 1 && x->stride[0] >= K && w->stride[0] >= N,
+               "x and w need unit column stride");
+  B200_REQUIRE(scratch_w->shape[0] == K && scratch_w->shape[1] == N && scratch_w->stride[1] == 1 &&
+               scratch_w->stride[0] >= N, "scratch_w must be [K,N]");
+  B200_REQUIRE(scratch_rinv->dtype == B200_DTYPE_FLOAT32 && scratch_rinv->shape[0] >= M &&
+               scratch_rinv->stride[0] == 1, "scratch_rinv must be f32 [>= M]");
+  B200_REQUIRE(eps == eps && eps >= 0.f, "eps must be non-negative");
+  B200_REQUIRE(K > 0, "K must be positive");
+  if (M == 0 || N == 0) return B200_OK;
+  cudaStream_t s = (cudaStream_t)stream;
+  float *rinv = (float *)scratch_rinv->data;
+  if (x->dtype == B200_DTYPE_FLOAT32) st = gemm::rms_matmul_prepare<float>(x, g, w, scratch_w, rinv, eps, s);
+  else if (x->dtype == B200_DTYPE_FLOAT16) st = gemm::rms_matmul_prepare<__half>(x, g, w, scratch_w, rinv, eps, s);
+  else st = gemm::rms_matmul_prepare<__nv_bfloat16>(x, g, w, scratch_w, rinv, eps, s);
+  if (st) return st;
+  return gemm_impl(x, scratch_w, nullptr, nullptr, out, B200_ACT_NONE, stream, nullptr, false, rinv);
 }

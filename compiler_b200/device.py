@@ -199,6 +199,7 @@ class B200Device:
         self._pinned = None
         self.launch_count = 0
         self._plans = {}
+        self._workspaces = {}
 
     # ------------------------------------------------------------ lifecycle
     def alloc(self, shape, dtype):
@@ -209,6 +210,22 @@ class B200Device:
         out = ctypes.c_void_p()
         abi.check(self._lib.b200_malloc(ctypes.byref(out), nbytes))
         return B200Buffer(out.value, target, shape, nbytes)
+
+    def workspace(self, key, specs):
+        """Scratch buffers an operator needs besides its arguments, allocated once per
+        ``key`` and kept with the device (``specs`` = ((shape, dtype), ...)).  Launches on one
+        device share the device's stream, so they can share the buffers."""
+        found = self._workspaces.get(key)
+        if found is None:
+            if len(self._workspaces) >= 16:  # shapes change: drop the old scratch
+                for buffers in self._workspaces.values():
+                    for buffer in buffers:
+                        buffer.free()
+                self._workspaces.clear()
+                self._plans.clear()  # recorded launches may point at the freed scratch
+            found = self._workspaces[key] = tuple(self.alloc(shape, dtype)
+                                                  for shape, dtype in specs)
+        return found
 
     def release(self, buffers):
         """Free staged buffers now (benchmarks call this per entry)."""

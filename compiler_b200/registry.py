@@ -216,6 +216,29 @@ def _linear_act(device, v, grid, name):
              bias=_View(v["b_ptr"], (n,)), act=abi.ACT_GELU_ERF, stream=device.stream)
 
 
+def _rms_matmul(device, v, grid, name):
+    """rms_matmul_rbe_kernel (ops/suite/dev/rms_matmul_rbe.py:18-30) without the rotary
+    epilogue: batches of [M,K] rows against one [K,N] weight."""
+    _require(not v.get("RBE_EPILOGUE", False) and not v.get("USE_FP8", False), name,
+             "RBE_EPILOGUE", "the rotary epilogue and the fp8 path have no native operator")
+    m, n, k = int(v["M"]), int(v["N"]), int(v["K"])
+    batches = _grid_tuple(grid)[0]
+    _require(int(v["stride_x_k"]) == 1 and int(v["stride_w_n"]) == 1 and
+             int(v["stride_out_n"]) == 1 and int(v["stride_rms_w"]) == 1, name, "strides",
+             "only unit inner strides have a native kernel")
+    xm, om = int(v["stride_x_m"]), int(v["stride_out_m"])
+    _require(batches == 1 or (int(v["stride_x_batch"]) == m * xm and
+                              int(v["stride_out_batch"]) == m * om), name, "strides",
+             "batches must follow each other without gaps")
+    rows = batches * m
+    scratch = device.workspace(("rms_matmul", k, n, rows, str(v["w_ptr"].dtype)),
+                               (((k, n), v["w_ptr"].dtype), ((rows,), "float32")))
+    ops.rms_matmul(_View(v["x_ptr"], (rows, k), (xm, 1)), _View(v["rms_w_ptr"], (k,)),
+                   _View(v["w_ptr"], (k, n), (int(v["stride_w_k"]), 1)),
+                   _View(v["out_ptr"], (rows, n), (om, 1)), scratch[0], scratch[1],
+                   eps=float(v["EPS"]), stream=device.stream)
+
+
 def _log_softmax_linear(device, v, grid, name):
     """log_softmax_linear_kernel (ops/suite/perf/log_softmax_linear.py:19): one program per row,
     contiguous x [rows, K], w [N, K], y [rows, N]."""
@@ -505,6 +528,12 @@ def default_registry() -> Registry:
     for attn_name in ("attn_fwd_causal_kernel", "attention_forward_kernel", "attention_kernel",
                       "context_attn_fwd_kernel"):
         r.register(attn_name, _ATTN, _attention)
+    r.register("rms_matmul_rbe_kernel",
+               ("x_ptr", "w_ptr", "rms_w_ptr", "out_ptr", "M", "N", "K", "stride_x_batch",
+                "stride_x_m", "stride_x_k", "stride_w_k", "stride_w_n", "stride_rms_w",
+                "stride_out_batch", "stride_out_m", "stride_out_n", "start_token_position",
+                "USE_FP8", "RBE_EPILOGUE", "THETA", "EPS", "BLOCK_SIZE_M", "BLOCK_SIZE_N",
+                "BLOCK_SIZE_K"), _rms_matmul)
     r.register("log_softmax_linear_kernel", ("x_ptr", "w_ptr", "y_ptr", "K", "N"),
                _log_softmax_linear)
     r.register("flash_varlen_fwd_kernel", _VARLEN, _flash_varlen)

@@ -187,6 +187,17 @@ int b200_gemm_bias_act(const b200_tensor *a, const b200_tensor *b,
                        const b200_tensor *b2, const b200_tensor *bias,
                        b200_tensor *c, int act, void *stream);
 
+/* out = rsqrt(mean(x^2, row) + eps) * ((x * g) @ w): RMS normalisation folded into a matmul.
+ * Replaces rms_matmul_rbe_kernel without its rotary epilogue
+ * (ops/suite/dev/rms_matmul_rbe.py:18-63).  x [M,K], g [K], w [K,N], out [M,N] (x's type or
+ * f32).  Two small kernels write rinv[M] (f32) and g-scaled weights into caller-provided
+ * scratch (scratch_w [K,N] in x's type, scratch_rinv f32 [>= M]); the tensor-core GEMM then
+ * runs x @ scratch_w and multiplies each accumulator row by rinv in its epilogue, so the
+ * normalised activations are never written. */
+int b200_rms_matmul(const b200_tensor *x, const b200_tensor *g, const b200_tensor *w,
+                    b200_tensor *out, float eps, b200_tensor *scratch_w,
+                    b200_tensor *scratch_rinv, void *stream);
+
 /* y = log_softmax(x @ w^T) over the output columns.  Replaces log_softmax_linear_kernel
  * (ops/suite/perf/log_softmax_linear.py:19-35): x [M,K], w [N,K] (a linear layer's weight:
  * rows of K), y [M,N] in x's type or f32, 1 <= N <= 256.  16-bit operands with 16-byte

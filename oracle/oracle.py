@@ -155,6 +155,14 @@ def attention_ref(q, k, v, scale, causal=True):
     return out, lse
 
 
+def rms_matmul_ref(x, g, w, eps):
+    """rsqrt(mean(x^2) + eps) * ((x * g) @ w) (ref of ops/suite/dev/rms_matmul_rbe.py:70-80),
+    float64; x [..., K], g [K], w [K, N]."""
+    x = np.asarray(x, dtype=np.float64)
+    acc = (x * np.asarray(g, dtype=np.float64)) @ np.asarray(w, dtype=np.float64)
+    return acc / np.sqrt((x * x).sum(axis=-1, keepdims=True) / x.shape[-1] + float(eps))
+
+
 def log_softmax_linear_ref(x, w):
     """log_softmax(x @ w.T) over the last axis (ref of
     ops/suite/perf/log_softmax_linear.py:45-51), float64."""

@@ -367,6 +367,29 @@ def test_linear_log_softmax_sweep(device, shape, dtype, out_dtype):
     oracle.compare(device.download(dy).astype(np.float64), ref, rtol, atol, name="y")
 
 
+@pytest.mark.parametrize("dtype", ["bfloat16", "float16", "float32"])
+@pytest.mark.parametrize("shape", [(1, 8, 64), (300, 136, 512), (1024, 1000, 4096), (129, 72, 100)])
+def test_rms_matmul_sweep(device, shape, dtype):
+    """out = rinv(x) * ((x * g) @ w): row factor applied in the GEMM epilogue."""
+    m, n, k = shape
+    rng = np.random.default_rng(_seed(shape, dtype))
+    x = _host(rng.standard_normal((m, k)) * 0.5, dtype)
+    g = _host(rng.standard_normal(k) * 0.2 + 1.0, dtype)
+    w = _host(rng.standard_normal((k, n)) * 0.5, dtype)
+    dx, dg, dw = (_up(device, t, dtype) for t in (x, g, w))
+    do = _poisoned(device, (m, n), dtype)
+    sw, sr = device.alloc((k, n), dtype), device.alloc((m,), "float32")
+    ops.rms_matmul(dx, dg, dw, do, sw, sr, eps=1e-5)
+    device.check_status()
+    ref = oracle.rms_matmul_ref(x, g, w, 1e-5)
+    # 16-bit: the products g*w are rounded once before the dot product (the reference rounds
+    # x*g instead: the same error size); K such errors of about 2^-9 * 0.25 add up in a row
+    rtol, atol = (1e-4, 5e-5 * np.sqrt(k)) if dtype == "float32" else (2e-2, 5e-3 * np.sqrt(k))
+    oracle.compare(device.download(do).astype(np.float64), ref, rtol, atol, name="out")
+    rinv_ref = 1.0 / np.sqrt((x.astype(np.float64) ** 2).mean(axis=1) + 1e-5)
+    oracle.compare(device.download(sr).astype(np.float64), rinv_ref, 1e-5, 1e-6, name="rinv")
+
+
 def test_linear_log_softmax_rejections(device):
     from compiler_b200.runtime.abi import B200Error
     x = _up(device, _host(np.zeros((8, 64)), "bfloat16"), "bfloat16")

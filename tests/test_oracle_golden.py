@@ -109,6 +109,15 @@ def test_gqa(tag):
     _assert_same(out.astype(expected.dtype), expected, meta["dtype"])
 
 
+@pytest.mark.parametrize("tag", golden_cases.tags("rms_matmul_rbe"))
+def test_rms_matmul(tag):
+    case, meta = golden_cases.load(tag)
+    a = case["args"]
+    out = oracle.rms_matmul_ref(a["x_ptr"], a["rms_w_ptr"], a["w_ptr"], a["EPS"])
+    expected = case["expected"]["out_ptr"]
+    _assert_same(out.astype(expected.dtype), expected, meta["dtype"])
+
+
 @pytest.mark.parametrize("tag", golden_cases.tags("log_softmax_linear"))
 def test_log_softmax_linear(tag):
     case, meta = golden_cases.load(tag)
