@@ -217,3 +217,78 @@ extern "C" int b200_repeat_log_softmax(const b200_tensor *x, b200_tensor *y, int
   B200_CUDA_OK(cudaGetLastError());
   return B200_OK;
 }
+
+// ---- int8 weights -> floats: out[k, n] = b[k, n] * scale[n] --------------------------------
+// dequantize_kernel (ops/suite/perf/dequantize_matmul.py:27-40).  One thread converts 16
+// consecutive columns (one 16-byte load of int8, 16-byte stores) when the rows allow it.
+namespace b200 {
+namespace {
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+dequantize_kernel(const int8_t *__restrict__ b, int64_t ldb, const T *__restrict__ scale,
+                  T *__restrict__ out, int64_t ldo, int K, int N, int vector_ok) {
+  const int groups = (N + 15) / 16;
+  const int64_t total = (int64_t)K * groups;
+  for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < total; i += (int64_t)gridDim.x * 256) {
+    const int k = (int)(i / groups), n0 = (int)(i % groups) * 16;
+    const int8_t *src = b + (int64_t)k * ldb + n0;
+    T *dst = out + (int64_t)k * ldo + n0;
+    if (vector_ok && n0 + 16 <= N) {
+      const uint4 raw = ld_stream16(src);
+      const int8_t *q = reinterpret_cast<const int8_t *>(&raw);
+      constexpr int PER = 16 / (int)sizeof(T);
+#pragma unroll
+      for (int v = 0; v < 16 / PER; ++v) {
+        vec16<T> o;
+#pragma unroll
+        for (int j = 0; j < PER; ++j)
+          o.e[j] = io<T>::store((float)q[v * PER + j] * io<T>::load(scale[n0 + v * PER + j]));
+        *reinterpret_cast<uint4 *>(dst + v * PER) = o.raw;
+      }
+    } else {
+      for (int j = 0; j < 16 && n0 + j < N; ++j)
+        dst[j] = io<T>::store((float)src[j] * io<T>::load(scale[n0 + j]));
+    }
+  }
+}
+
+}  // namespace
+}  // namespace b200
+
+extern "C" int b200_dequantize_cols(const b200_tensor *b, const b200_tensor *scale, b200_tensor *out,
+                                    void *stream) {
+  using namespace b200;
+  int st;
+  if ((st = check_tensor(b, "b", 2)) || (st = check_tensor(scale, "scale", 1)) ||
+      (st = check_tensor(out, "out", 2)))
+    return st;
+  B200_REQUIRE(b->dtype == B200_DTYPE_INT8, "b must be int8");
+  B200_REQUIRE(is_float_io(out->dtype) && scale->dtype == out->dtype,
+               "scale and out must share f16/bf16/f32");
+  const int64_t K = b->shape[0], N = b->shape[1];
+  B200_REQUIRE(out->shape[0] == K && out->shape[1] == N && scale->shape[0] == N &&
+               scale->stride[0] == 1, "out must be [K,N] and scale contiguous [N]");
+  B200_REQUIRE(b->stride[1] == 1 && out->stride[1] == 1 && b->stride[0] >= N && out->stride[0] >= N,
+               "b and out need unit column stride");
+  B200_REQUIRE(K < (1LL << 31) && N < (1LL << 31), "extent out of range");
+  if (K == 0 || N == 0) return B200_OK;
+  const size_t es = dtype_size(out->dtype);
+  const int vector_ok = (uintptr_t)b->data % 16 == 0 && b->stride[0] % 16 == 0 &&
+                        (uintptr_t)out->data % 16 == 0 && (out->stride[0] * es) % 16 == 0;
+  const int64_t work = K * ((N + 15) / 16);
+  int64_t blocks = (work + 255) / 256;
+  const int64_t cap = (int64_t)sm_count() * 16;
+  if (blocks > cap) blocks = cap;
+  cudaStream_t s = (cudaStream_t)stream;
+#define B200_DQ(T)                                                                              \
+  dequantize_kernel<T><<<(unsigned)blocks, 256, 0, s>>>((const int8_t *)b->data, b->stride[0],  \
+                                                        (const T *)scale->data, (T *)out->data, \
+                                                        out->stride[0], (int)K, (int)N, vector_ok)
+  if (out->dtype == B200_DTYPE_FLOAT32) B200_DQ(float);
+  else if (out->dtype == B200_DTYPE_FLOAT16) B200_DQ(__half);
+  else B200_DQ(__nv_bfloat16);
+#undef B200_DQ
+  B200_CUDA_OK(cudaGetLastError());
+  return B200_OK;
+}

@@ -66,6 +66,13 @@ def gemm(a, b, c, *, bias=None, act=abi.ACT_NONE, b2=None, stream=0):
                                            int(act), stream))
 
 
+def dequantize_cols(b, scale, out, *, stream=0):
+    """out[k, n] = int8 b[k, n] * scale[n] (dequantize_kernel,
+    ops/suite/perf/dequantize_matmul.py:27-40)."""
+    bd, sd, od = _desc(b), _desc(scale), _desc(out)
+    abi.check(abi.lib().b200_dequantize_cols(_ref(bd), _ref(sd), _ref(od), stream))
+
+
 def rms_matmul(x, g, w, out, scratch_w, scratch_rinv, eps=1e-5, *, stream=0):
     """out = rsqrt(mean(x^2) + eps) * ((x * g) @ w); scratch_w [K,N] (x's type) and
     scratch_rinv (float32, >= M) are workspace the caller owns.

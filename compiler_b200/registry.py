@@ -216,6 +216,17 @@ def _linear_act(device, v, grid, name):
              bias=_View(v["b_ptr"], (n,)), act=abi.ACT_GELU_ERF, stream=device.stream)
 
 
+def _dequantize(device, v, grid, name):
+    """dequantize_kernel (ops/suite/perf/dequantize_matmul.py:27-29)."""
+    k, n = int(v["K"]), int(v["N"])
+    _require(int(v["stride_bn"]) == 1 and int(v["stride_fpbn"]) == 1, name, "strides",
+             "only unit column strides have a native kernel")
+    ops.dequantize_cols(_View(v["b_ptr"], (k, n), (int(v["stride_bk"]), 1)),
+                        _View(v["b_scale_ptr"], (n,)),
+                        _View(v["fpb_ptr"], (k, n), (int(v["stride_fpbk"]), 1)),
+                        stream=device.stream)
+
+
 def _rms_matmul(device, v, grid, name):
     """rms_matmul_rbe_kernel (ops/suite/dev/rms_matmul_rbe.py:18-30) without the rotary
     epilogue: batches of [M,K] rows against one [K,N] weight."""
@@ -528,6 +539,9 @@ def default_registry() -> Registry:
     for attn_name in ("attn_fwd_causal_kernel", "attention_forward_kernel", "attention_kernel",
                       "context_attn_fwd_kernel"):
         r.register(attn_name, _ATTN, _attention)
+    r.register("dequantize_kernel",
+               ("b_ptr", "b_scale_ptr", "fpb_ptr", "K", "N", "stride_bk", "stride_bn",
+                "stride_fpbk", "stride_fpbn", "BLOCK_K", "BLOCK_N"), _dequantize)
     r.register("rms_matmul_rbe_kernel",
                ("x_ptr", "w_ptr", "rms_w_ptr", "out_ptr", "M", "N", "K", "stride_x_batch",
                 "stride_x_m", "stride_x_k", "stride_w_k", "stride_w_n", "stride_rms_w",

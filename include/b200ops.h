@@ -187,6 +187,12 @@ int b200_gemm_bias_act(const b200_tensor *a, const b200_tensor *b,
                        const b200_tensor *b2, const b200_tensor *bias,
                        b200_tensor *c, int act, void *stream);
 
+/* out[k,n] = b[k,n] * scale[n]: int8 weights to floats.  Replaces dequantize_kernel
+ * (ops/suite/perf/dequantize_matmul.py:27-40).  b int8 [K,N], scale [N] and out [K,N] in one
+ * float type, unit column strides. */
+int b200_dequantize_cols(const b200_tensor *b, const b200_tensor *scale, b200_tensor *out,
+                         void *stream);
+
 /* out = rsqrt(mean(x^2, row) + eps) * ((x * g) @ w): RMS normalisation folded into a matmul.
  * Replaces rms_matmul_rbe_kernel without its rotary epilogue
  * (ops/suite/dev/rms_matmul_rbe.py:18-63).  x [M,K], g [K], w [K,N], out [M,N] (x's type or

@@ -155,6 +155,11 @@ def attention_ref(q, k, v, scale, causal=True):
     return out, lse
 
 
+def dequantize_ref(b, scale):
+    """int8 b [K,N] times scale [N] (ref of ops/suite/perf/dequantize_matmul.py:49-52)."""
+    return np.asarray(b, dtype=np.float64) * np.asarray(scale, dtype=np.float64)[None, :]
+
+
 def rms_matmul_ref(x, g, w, eps):
     """rsqrt(mean(x^2) + eps) * ((x * g) @ w) (ref of ops/suite/dev/rms_matmul_rbe.py:70-80),
     float64; x [..., K], g [K], w [K, N]."""

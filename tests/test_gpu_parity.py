@@ -390,6 +390,21 @@ def test_rms_matmul_sweep(device, shape, dtype):
     oracle.compare(device.download(sr).astype(np.float64), rinv_ref, 1e-5, 1e-6, name="rinv")
 
 
+@pytest.mark.parametrize("dtype", ["bfloat16", "float16", "float32"])
+@pytest.mark.parametrize("shape", [(1, 1), (33, 33), (64, 4096), (257, 1000), (1024, 11008)])
+def test_dequantize_sweep(device, shape, dtype):
+    k, n = shape
+    rng = np.random.default_rng(_seed(shape, dtype))
+    b = rng.integers(-127, 128, (k, n)).astype(np.int8)
+    scale = _host(rng.random(n), dtype)
+    db, ds = device.upload(b), _up(device, scale, dtype)
+    do = _poisoned(device, (k, n), dtype)
+    ops.dequantize_cols(db, ds, do)
+    ref = oracle.dequantize_ref(b, scale)
+    rtol = 1e-6 if dtype == "float32" else (1e-3 if dtype == "float16" else 8e-3)
+    oracle.compare(device.download(do).astype(np.float64), ref, rtol, 1e-6, name="out")
+
+
 def test_linear_log_softmax_rejections(device):
     from compiler_b200.runtime.abi import B200Error
     x = _up(device, _host(np.zeros((8, 64)), "bfloat16"), "bfloat16")

@@ -109,6 +109,14 @@ def test_gqa(tag):
     _assert_same(out.astype(expected.dtype), expected, meta["dtype"])
 
 
+@pytest.mark.parametrize("tag", golden_cases.tags("dequantize_matmul"))
+def test_dequantize(tag):
+    case, meta = golden_cases.load(tag)
+    out = oracle.dequantize_ref(case["args"]["b_ptr"], case["args"]["b_scale_ptr"])
+    expected = case["expected"]["fpb_ptr"]
+    _assert_same(out.astype(expected.dtype), expected, meta["dtype"])
+
+
 @pytest.mark.parametrize("tag", golden_cases.tags("rms_matmul_rbe"))
 def test_rms_matmul(tag):
     case, meta = golden_cases.load(tag)
