@@ -86,6 +86,18 @@ constexpr int THREADS = 192;
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
 
 constexpr int kActLogSoftmax = 100;  // internal epilogue code: row log-softmax (N <= 256)
+constexpr int kActGroupNormMin = 101;  // internal: group norm over column groups, row minimum
+
+// Group normalisation over groups of `group` consecutive columns followed by the minimum of
+// each row, merged into mins[] with an atomic minimum (the epilogue of
+// fused_gemm_gn_min_kernel, ops/suite/dev/fused_gemm_gn_min_kernel.py:45-59).
+struct GroupNormMin {
+  const void *gamma, *beta;  // [N], kind = dtype code
+  int kind;
+  int group;                 // 8, 16, 32 or 64 columns
+  float eps;
+  float *mins;               // [M], holds the running minimum (start it at +inf)
+};
 
 struct Params {
   int M, N, K;
@@ -101,6 +113,7 @@ struct Params {
   uint32_t b_kstep;       // descriptor advance per UMMA_K step, in 16-byte units
   int b_kmajor;           // B is given as [N, K] (rows of K): one 64(K) x 256(N) box per stage
   const float *row_scale; // optional [M] factors applied to the accumulator rows before the bias
+  GroupNormMin gn;        // used with kActGroupNormMin
   // Row scatter for the tensor-parallel MLP: when scatter_rows > 0 the row block
   // [k * scatter_rows, (k+1) * scatter_rows) of C is not written to `c` but to slot
   // `scatter_slot` of c_rank[k] -- the memory of the rank that owns those rows (a peer
@@ -269,6 +282,68 @@ __device__ __forceinline__ void epilogue_tile_log_softmax(uint32_t t_row, const 
     for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) - shift;
     if (row_ok) store_chunk<OutT>(crow, c * 32, p.N, p.vector_store != 0, v);
   }
+}
+
+// minimum of floats through integer atomics: non-negative values order like ints, negative
+// ones in reverse like unsigned ints
+__device__ __forceinline__ void atomic_min_float(float *addr, float v) {
+  if (v >= 0.f) atomicMin(reinterpret_cast<int *>(addr), __float_as_int(v));
+  else atomicMax(reinterpret_cast<unsigned int *>(addr), __float_as_uint(v));
+}
+
+// group norm + row minimum over W = max(GS, 32) columns held in registers
+template <int GS, int W>
+__device__ __forceinline__ float gn_min_block(const float (&z)[W], const Params &p, int col0) {
+  float lowest = INFINITY;
+#pragma unroll
+  for (int g = 0; g < W / GS; ++g) {
+    float mean = 0.f;
+#pragma unroll
+    for (int j = 0; j < GS; ++j) mean += z[g * GS + j];
+    mean *= 1.0f / GS;
+    float var = 0.f;
+#pragma unroll
+    for (int j = 0; j < GS; ++j) {
+      const float d = z[g * GS + j] - mean;
+      var = fmaf(d, d, var);
+    }
+    const float rstd = rsqrtf(var * (1.0f / GS) + p.gn.eps);
+#pragma unroll
+    for (int j = 0; j < GS; ++j) {
+      const int col = col0 + g * GS + j;
+      const float out = (z[g * GS + j] - mean) * rstd * load_bias(p.gn.gamma, p.gn.kind, col) +
+                        load_bias(p.gn.beta, p.gn.kind, col);
+      lowest = fminf(lowest, out);
+    }
+  }
+  return lowest;
+}
+
+// Epilogue of fused_gemm_gn_min_kernel: bias, group norm over groups of GS columns (a group
+// lies inside one thread's row, so the statistics are plain per-thread arithmetic), row
+// minimum, one atomic minimum per row and column block.  N % GS == 0.
+template <int GS>
+__device__ __forceinline__ void epilogue_tile_gn_min(uint32_t t_row, const Params &p, int row,
+                                                     int col_base, bool row_ok) {
+  constexpr int W = GS > 32 ? GS : 32;
+  float lowest = INFINITY;
+#pragma unroll 1
+  for (int c0 = 0; c0 < BN; c0 += W) {
+    if (col_base + c0 >= p.N) break;  // warp-uniform
+    float z[W];
+#pragma unroll
+    for (int part = 0; part < W / 32; ++part) {
+      uint32_t r[32];
+      tmem_ld_32x32b_x32(t_row + (uint32_t)(c0 + part * 32), r);
+      tmem_ld_wait();
+      float b[32];
+      load_bias_chunk(p.bias, p.bias_kind, col_base + c0 + part * 32, p.N, b);
+#pragma unroll
+      for (int j = 0; j < 32; ++j) z[part * 32 + j] = __uint_as_float(r[j]) + b[j];
+    }
+    lowest = fminf(lowest, gn_min_block<GS, W>(z, p, col_base + c0));
+  }
+  if (row_ok) atomic_min_float(p.gn.mins + row, lowest);
 }
 
 // DUAL: columns [0,128) hold x Wg, [128,256) hold x Wu; out = silu(g) * u
@@ -489,6 +564,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
           case kActLogSoftmax:
             epilogue_tile_log_softmax<OutT>(t_row, p, crow, row_ok);
             break;
+          case kActGroupNormMin:
+            if (p.gn.group == 8) epilogue_tile_gn_min<8>(t_row, p, row, col_base, row_ok);
+            else if (p.gn.group == 16) epilogue_tile_gn_min<16>(t_row, p, row, col_base, row_ok);
+            else if (p.gn.group == 32) epilogue_tile_gn_min<32>(t_row, p, row, col_base, row_ok);
+            else epilogue_tile_gn_min<64>(t_row, p, row, col_base, row_ok);
+            break;
           case B200_ACT_GELU_TANH:
             epilogue_tile<OutT, B200_ACT_GELU_TANH>(t_row, p, crow, col_base, row_ok, row_mul);
             break;
@@ -526,7 +607,8 @@ template <typename InT, typename OutT>
 __global__ void __launch_bounds__(256)
 gemm_simt_kernel(const InT *__restrict__ a, int64_t lda, const InT *__restrict__ b, int64_t ldb,
                  const InT *__restrict__ b2, OutT *__restrict__ c, int64_t ldc, int M, int N,
-                 int K, const void *bias, int bias_kind, int act, const float *row_scale) {
+                 int K, const void *bias, int bias_kind, int act, const float *row_scale,
+                 GroupNormMin gn) {
   __shared__ float sa[32][33];
   __shared__ float sb[32][33];
   __shared__ float sb2[32][33];
@@ -577,6 +659,17 @@ gemm_simt_kernel(const InT *__restrict__ a, int64_t lda, const InT *__restrict__
         default: break;
       }
     }
+    if (gn.mins != nullptr) {
+      // a 32-column tile is one group (gn.group == 32, N % 32 == 0): the lanes of this warp
+      // hold the group's 32 values of row m
+      const float mean = warp_sum(z) * (1.0f / 32);
+      const float d = z - mean;
+      const float rstd = rsqrtf(warp_sum(d * d) * (1.0f / 32) + gn.eps);
+      const float out = d * rstd * load_bias(gn.gamma, gn.kind, n) + load_bias(gn.beta, gn.kind, n);
+      const float lowest = -warp_max(-out);
+      if (tx == 0) atomic_min_float(gn.mins + m, lowest);
+      continue;
+    }
     c[(int64_t)m * ldc + n] = io<OutT>::store(z);
   }
 }
@@ -584,14 +677,20 @@ gemm_simt_kernel(const InT *__restrict__ a, int64_t lda, const InT *__restrict__
 template <typename InT, typename OutT>
 static int launch_simt(const b200_tensor *a, const b200_tensor *b, const b200_tensor *b2,
                        const b200_tensor *bias, b200_tensor *c, int act, cudaStream_t stream,
-                       const float *row_scale = nullptr) {
+                       const float *row_scale = nullptr, const GroupNormMin *gn = nullptr) {
   const int M = (int)a->shape[0], K = (int)a->shape[1], N = (int)b->shape[1];
+  GroupNormMin gn_args = {nullptr, nullptr, 0, 0, 0.f, nullptr};
+  if (gn != nullptr) {
+    B200_REQUIRE(gn->group == 32 && N % 32 == 0,
+                 "the CUDA-core path takes groups of exactly 32 columns");
+    gn_args = *gn;
+  }
   dim3 grid((N + 31) / 32, (M + 31) / 32);
   B200_REQUIRE(grid.y <= 65535, "M too large for the CUDA-core path");
   gemm_simt_kernel<InT, OutT><<<grid, 256, 0, stream>>>(
       (const InT *)a->data, a->stride[0], (const InT *)b->data, b->stride[0],
       b2 ? (const InT *)b2->data : nullptr, (OutT *)c->data, c->stride[0], M, N, K,
-      bias ? bias->data : nullptr, bias ? (int)bias->dtype : 0, act, row_scale);
+      bias ? bias->data : nullptr, bias ? (int)bias->dtype : 0, act, row_scale, gn_args);
   B200_CUDA_OK(cudaGetLastError());
   return B200_OK;
 }
@@ -666,14 +765,16 @@ linear_log_softmax_simt_kernel(const T *__restrict__ x, const T *__restrict__ w,
 static int gemm_impl(const b200_tensor *a, const b200_tensor *b, const b200_tensor *b2,
                      const b200_tensor *bias, b200_tensor *c, int act, void *stream,
                      const b200::gemm::Scatter *scatter, bool b_rows_are_n = false,
-                     const float *row_scale = nullptr) {
+                     const float *row_scale = nullptr,
+                     const b200::gemm::GroupNormMin *gn = nullptr) {
   using namespace b200;
   using namespace b200::gemm;
   int st;
   if ((st = check_tensor(a, "a", 2)) || (st = check_tensor(b, "b", 2)) ||
       (st = check_tensor(c, "c", 2)))
     return st;
-  if ((act < B200_ACT_NONE || act > B200_ACT_SWIGLU) && act != kActLogSoftmax)
+  if ((act < B200_ACT_NONE || act > B200_ACT_SWIGLU) && act != kActLogSoftmax &&
+      act != kActGroupNormMin)
     return fail(B200_USAGE, "act %d is not a b200_act value", act);
   if (bias != nullptr && (st = check_tensor(bias, "bias", 1))) return st;
   if (act == B200_ACT_SWIGLU) {
@@ -749,15 +850,15 @@ static int gemm_impl(const b200_tensor *a, const b200_tensor *b, const b200_tens
   }
   if (!tensor_core) {
     B200_REQUIRE(!b_rows_are_n, "B as [N, K] is taken by the tensor-core path only");
-    if (a->dtype == B200_DTYPE_FLOAT32) return launch_simt<float, float>(a, b, b2, bias, c, act, s, row_scale);
+    if (a->dtype == B200_DTYPE_FLOAT32) return launch_simt<float, float>(a, b, b2, bias, c, act, s, row_scale, gn);
     if (a->dtype == B200_DTYPE_FLOAT16) {
       return c->dtype == B200_DTYPE_FLOAT32
-                 ? launch_simt<__half, float>(a, b, b2, bias, c, act, s, row_scale)
-                 : launch_simt<__half, __half>(a, b, b2, bias, c, act, s, row_scale);
+                 ? launch_simt<__half, float>(a, b, b2, bias, c, act, s, row_scale, gn)
+                 : launch_simt<__half, __half>(a, b, b2, bias, c, act, s, row_scale, gn);
     }
     return c->dtype == B200_DTYPE_FLOAT32
-               ? launch_simt<__nv_bfloat16, float>(a, b, b2, bias, c, act, s, row_scale)
-               : launch_simt<__nv_bfloat16, __nv_bfloat16>(a, b, b2, bias, c, act, s, row_scale);
+               ? launch_simt<__nv_bfloat16, float>(a, b, b2, bias, c, act, s, row_scale, gn)
+               : launch_simt<__nv_bfloat16, __nv_bfloat16>(a, b, b2, bias, c, act, s, row_scale, gn);
   }
 
   CUtensorMap ta, tb, tb2;
@@ -797,6 +898,7 @@ static int gemm_impl(const b200_tensor *a, const b200_tensor *b, const b200_tens
   p.status = device_status_word();
   if (p.status == nullptr) return fail(B200_RESOURCE, "no status word on this device");
   p.row_scale = row_scale;
+  p.gn = gn != nullptr ? *gn : GroupNormMin{nullptr, nullptr, 0, 0, 0.f, nullptr};
   p.b_kmajor = b_rows_are_n ? 1 : 0;
   p.b_lbo = b_rows_are_n ? 16 : B_BOX_BYTES;  // [K,N]: pitch between 64-column chunks of the tile
   p.b_sbo = 1024;                             // pitch between groups of 8 rows
@@ -957,4 +1059,39 @@ extern "C" int b200_rms_matmul(const b200_tensor *x, const b200_tensor *g, const
   else st = gemm::rms_matmul_prepare<__nv_bfloat16>(x, g, w, scratch_w, rinv, eps, s);
   if (st) return st;
   return gemm_impl(x, scratch_w, nullptr, nullptr, out, B200_ACT_NONE, stream, nullptr, false, rinv);
+}
+
+extern "C" int b200_gemm_groupnorm_rowmin(const b200_tensor *x, const b200_tensor *w,
+                                          const b200_tensor *bias, const b200_tensor *gamma,
+                                          const b200_tensor *beta, b200_tensor *mins,
+                                          int group_size, float eps, void *stream) {
+  using namespace b200;
+  int st;
+  if ((st = check_tensor(x, "x", 2)) || (st = check_tensor(w, "w", 2)) ||
+      (st = check_tensor(gamma, "gamma", 1)) || (st = check_tensor(beta, "beta", 1)) ||
+      (st = check_tensor(mins, "mins", 1)))
+    return st;
+  const int64_t M = x->shape[0], N = w->shape[1];
+  B200_REQUIRE(group_size == 8 || group_size == 16 || group_size == 32 || group_size == 64,
+               "group_size %d is not 8, 16, 32 or 64", group_size);
+  B200_REQUIRE(N % group_size == 0, "N %lld is not a multiple of the group size %d",
+               (long long)N, group_size);
+  B200_REQUIRE(gamma->shape[0] == N && beta->shape[0] == N && gamma->stride[0] == 1 &&
+               beta->stride[0] == 1 && gamma->dtype == beta->dtype &&
+               (gamma->dtype == B200_DTYPE_FLOAT32 || gamma->dtype == x->dtype),
+               "gamma and beta must be contiguous [N] in f32 or x's type");
+  B200_REQUIRE(mins->dtype == B200_DTYPE_FLOAT32 && mins->shape[0] == M && mins->stride[0] == 1,
+               "mins must be contiguous f32 [M]");
+  B200_REQUIRE(eps == eps && eps >= 0.f, "eps must be non-negative");
+  gemm::GroupNormMin gn = {gamma->data, beta->data, (int)gamma->dtype, group_size, eps,
+                           (float *)mins->data};
+  // the product is never stored: this descriptor only carries the shape and an f32 type
+  b200_tensor c = {};
+  c.data = mins->data;
+  c.ndim = 2;
+  c.dtype = B200_DTYPE_FLOAT32;
+  c.shape[0] = M; c.shape[1] = N;
+  c.stride[0] = N; c.stride[1] = 1;
+  return gemm_impl(x, w, nullptr, bias, &c, b200::gemm::kActGroupNormMin, stream, nullptr, false,
+                   nullptr, &gn);
 }

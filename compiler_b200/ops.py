@@ -66,6 +66,21 @@ def gemm(a, b, c, *, bias=None, act=abi.ACT_NONE, b2=None, stream=0):
                                            int(act), stream))
 
 
+def gemm_groupnorm_rowmin(x, w, gamma, beta, mins, *, bias=None, group_size=32, eps=1e-5,
+                          stream=0):
+    """mins[m] = min(mins[m], min over n of GroupNorm(x @ w + bias)[m, n]) with groups of
+    ``group_size`` columns (fused_gemm_gn_min_kernel,
+    ops/suite/dev/fused_gemm_gn_min_kernel.py:26-59)."""
+    n = int(w.shape[1])
+    xd, wd, md = _desc(x), _desc(w), _desc(mins)
+    gd = _desc(gamma, shape=(n,), strides=(1,))
+    bd = _desc(beta, shape=(n,), strides=(1,))
+    biasd = _desc(bias, shape=(n,), strides=(1,)) if bias is not None else None
+    abi.check(abi.lib().b200_gemm_groupnorm_rowmin(_ref(xd), _ref(wd), _ref(biasd), _ref(gd),
+                                                   _ref(bd), _ref(md), int(group_size),
+                                                   float(eps), stream))
+
+
 def dequantize_cols(b, scale, out, *, stream=0):
     """out[k, n] = int8 b[k, n] * scale[n] (dequantize_kernel,
     ops/suite/perf/dequantize_matmul.py:27-40)."""

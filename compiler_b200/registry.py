@@ -216,6 +216,19 @@ def _linear_act(device, v, grid, name):
              bias=_View(v["b_ptr"], (n,)), act=abi.ACT_GELU_ERF, stream=device.stream)
 
 
+def _gemm_gn_min(device, v, grid, name):
+    """fused_gemm_gn_min_kernel (ops/suite/dev/fused_gemm_gn_min_kernel.py:26): row-major
+    X [M,K], W [K,N]."""
+    m, n, k = int(v["M"]), int(v["N"]), int(v["K"])
+    _require(int(v["stride_xk"]) == 1 and int(v["stride_wn"]) == 1, name, "strides",
+             "only row-major X and W have a native kernel")
+    ops.gemm_groupnorm_rowmin(
+        _View(v["X_ptr"], (m, k), (int(v["stride_xm"]), 1)),
+        _View(v["W_ptr"], (k, n), (int(v["stride_wk"]), 1)), _View(v["Gamma_ptr"], (n,)),
+        _View(v["Beta_ptr"], (n,)), _View(v["Mins_ptr"], (m,)), bias=_View(v["B_ptr"], (n,)),
+        group_size=int(v["GROUP_SIZE"]), eps=float(v["eps"]), stream=device.stream)
+
+
 def _dequantize(device, v, grid, name):
     """dequantize_kernel (ops/suite/perf/dequantize_matmul.py:27-29)."""
     k, n = int(v["K"]), int(v["N"])
@@ -539,6 +552,10 @@ def default_registry() -> Registry:
     for attn_name in ("attn_fwd_causal_kernel", "attention_forward_kernel", "attention_kernel",
                       "context_attn_fwd_kernel"):
         r.register(attn_name, _ATTN, _attention)
+    r.register("fused_gemm_gn_min_kernel",
+               ("X_ptr", "W_ptr", "B_ptr", "Gamma_ptr", "Beta_ptr", "Mins_ptr", "M", "N", "K",
+                "stride_xm", "stride_xk", "stride_wn", "stride_wk", "eps", "BLOCK_M", "BLOCK_N",
+                "BLOCK_K", "GROUP_SIZE", "GROUP_M"), _gemm_gn_min)
     r.register("dequantize_kernel",
                ("b_ptr", "b_scale_ptr", "fpb_ptr", "K", "N", "stride_bk", "stride_bn",
                 "stride_fpbk", "stride_fpbn", "BLOCK_K", "BLOCK_N"), _dequantize)

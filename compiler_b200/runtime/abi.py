@@ -100,6 +100,7 @@ PROTOTYPES = {
     "b200_attn_fwd": (c_int, [_T, _T, _T, _T, _T, c_float, c_int, _PTR]),
     "b200_attn_decode": (c_int, [_T, _T, _T, _T, c_float, _PTR]),
     "b200_linear_log_softmax": (c_int, [_T, _T, _T, _PTR]),
+    "b200_gemm_groupnorm_rowmin": (c_int, [_T, _T, _T, _T, _T, _T, c_int, c_float, _PTR]),
     "b200_dequantize_cols": (c_int, [_T, _T, _T, _PTR]),
     "b200_rms_matmul": (c_int, [_T, _T, _T, _T, c_float, _T, _T, _PTR]),
     "b200_swiglu_fwd": (c_int, [_T, _T, _T, _PTR]),

@@ -187,6 +187,18 @@ int b200_gemm_bias_act(const b200_tensor *a, const b200_tensor *b,
                        const b200_tensor *b2, const b200_tensor *bias,
                        b200_tensor *c, int act, void *stream);
 
+/* mins[m] = min(mins[m], min_n GroupNorm(x @ w + bias)[m, n]): a GEMM whose epilogue
+ * normalises groups of group_size consecutive columns (mean / variance inside the group,
+ * gamma, beta) and keeps only the minimum of each row.  Replaces fused_gemm_gn_min_kernel
+ * (ops/suite/dev/fused_gemm_gn_min_kernel.py:26-59).  x [M,K], w [K,N], bias / gamma / beta
+ * [N] (bias may be NULL), mins f32 [M] (set it to +inf first: the kernel merges with an
+ * atomic minimum, as the reference does); group_size 8 / 16 / 32 / 64 dividing N (32 only on
+ * the CUDA-core path that fp32 operands take).  The [M,N] product is never written. */
+int b200_gemm_groupnorm_rowmin(const b200_tensor *x, const b200_tensor *w,
+                               const b200_tensor *bias, const b200_tensor *gamma,
+                               const b200_tensor *beta, b200_tensor *mins, int group_size,
+                               float eps, void *stream);
+
 /* out[k,n] = b[k,n] * scale[n]: int8 weights to floats.  Replaces dequantize_kernel
  * (ops/suite/perf/dequantize_matmul.py:27-40).  b int8 [K,N], scale [N] and out [K,N] in one
  * float type, unit column strides. */

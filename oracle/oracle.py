@@ -155,6 +155,22 @@ def attention_ref(q, k, v, scale, causal=True):
     return out, lse
 
 
+def gemm_groupnorm_rowmin_ref(x, w, bias, gamma, beta, group_size, eps):
+    """Row minimum of GroupNorm(x @ w + bias) with groups of ``group_size`` columns (ref of
+    ops/suite/dev/fused_gemm_gn_min_kernel.py:88-105), float64 [M]."""
+    x = np.asarray(x, dtype=np.float64)
+    w = np.asarray(w, dtype=np.float64)
+    m, n = x.shape[0], w.shape[1]
+    acc = x @ w + (0.0 if bias is None else np.asarray(bias, dtype=np.float64)[None, :])
+    acc3 = acc.reshape(m, n // group_size, group_size)
+    mean = acc3.mean(axis=2)
+    rstd = 1.0 / np.sqrt(acc3.var(axis=2) + float(eps))
+    out = ((acc3 - mean[:, :, None]) * rstd[:, :, None]
+           * np.asarray(gamma, dtype=np.float64).reshape(n // group_size, group_size)[None]
+           + np.asarray(beta, dtype=np.float64).reshape(n // group_size, group_size)[None])
+    return out.min(axis=(1, 2))
+
+
 def dequantize_ref(b, scale):
     """int8 b [K,N] times scale [N] (ref of ops/suite/perf/dequantize_matmul.py:49-52)."""
     return np.asarray(b, dtype=np.float64) * np.asarray(scale, dtype=np.float64)[None, :]

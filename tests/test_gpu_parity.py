@@ -405,6 +405,33 @@ def test_dequantize_sweep(device, shape, dtype):
     oracle.compare(device.download(do).astype(np.float64), ref, rtol, 1e-6, name="out")
 
 
+@pytest.mark.parametrize("dtype", ["bfloat16", "float16", "float32"])
+@pytest.mark.parametrize("shape", [(64, 128, 128, 32), (37, 192, 96, 32), (300, 512, 256, 64),
+                                   (129, 320, 72, 16), (1000, 1024, 512, 8), (5, 64, 40, 32)])
+def test_gemm_groupnorm_rowmin_sweep(device, shape, dtype):
+    """GEMM + bias + group norm over column groups + row minimum, nothing but mins written.
+    Operands on a 1/16 grid as in the reference's case, so the products are exact in 16 bits."""
+    m, n, k, gs = shape
+    if dtype == "float32" and gs != 32:
+        pytest.skip("the CUDA-core path takes groups of 32")
+    rng = np.random.default_rng(_seed(shape, dtype))
+    x = _host(rng.integers(-16, 16, (m, k)) / 16, dtype)
+    w = _host(rng.integers(-16, 16, (k, n)) / 16, dtype)
+    bias = _host(rng.integers(-8, 9, n) / 16, dtype)
+    gamma = _host(rng.integers(8, 24, n) / 16, dtype)
+    beta = _host(rng.integers(-8, 9, n) / 16, dtype)
+    x[0, :] = 0  # a row whose groups have (almost) no variance
+    dx, dw, db, dg, dbt = (_up(device, t, dtype) for t in (x, w, bias, gamma, beta))
+    start = np.full(m, np.inf, np.float32)
+    start[m // 2] = -100.0  # an existing minimum must survive
+    dm = device.upload(start)
+    ops.gemm_groupnorm_rowmin(dx, dw, dg, dbt, dm, bias=db, group_size=gs, eps=1e-5)
+    device.check_status()
+    ref = oracle.gemm_groupnorm_rowmin_ref(x, w, bias, gamma, beta, gs, 1e-5)
+    ref[m // 2] = min(ref[m // 2], -100.0)
+    oracle.compare(device.download(dm).astype(np.float64), ref, 5e-3, 5e-3, name="mins")
+
+
 def test_linear_log_softmax_rejections(device):
     from compiler_b200.runtime.abi import B200Error
     x = _up(device, _host(np.zeros((8, 64)), "bfloat16"), "bfloat16")

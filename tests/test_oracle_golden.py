@@ -109,6 +109,18 @@ def test_gqa(tag):
     _assert_same(out.astype(expected.dtype), expected, meta["dtype"])
 
 
+@pytest.mark.parametrize("tag", golden_cases.tags("fused_gemm_gn_min_kernel"))
+def test_gemm_groupnorm_rowmin(tag):
+    case, meta = golden_cases.load(tag)
+    a = case["args"]
+    m, n, k = int(a["M"]), int(a["N"]), int(a["K"])
+    mins = oracle.gemm_groupnorm_rowmin_ref(
+        np.asarray(a["X_ptr"]).reshape(m, k), np.asarray(a["W_ptr"]).reshape(k, n), a["B_ptr"],
+        a["Gamma_ptr"], a["Beta_ptr"], int(case["meta"]["GROUP_SIZE"]), a["eps"])
+    expected = case["expected"]["Mins_ptr"]
+    _assert_same(mins.astype(expected.dtype), expected, meta["dtype"])
+
+
 @pytest.mark.parametrize("tag", golden_cases.tags("dequantize_matmul"))
 def test_dequantize(tag):
     case, meta = golden_cases.load(tag)
