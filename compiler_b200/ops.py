@@ -92,8 +92,7 @@ def rms_matmul(x, g, w, out, scratch_w, scratch_rinv, eps=1e-5, *, stream=0):
     """out = rsqrt(mean(x^2) + eps) * ((x * g) @ w); scratch_w [K,N] (x's type) and
     scratch_rinv (float32, >= M) are workspace the caller owns.
 
-    Native form of rms_matmul_rbe_kernel without the rotary epilogue
-    (ops/suite/dev/rms_matmul_rbe.py:18-63)."""
+    Native form of rms_matmul_rbe_kernel (ops/suite/dev/rms_matmul_rbe.py:18-63)."""
     xd, gd, wd, od = _desc(x), _desc(g), _desc(w), _desc(out)
     sw, sr = _desc(scratch_w), _desc(scratch_rinv)
     abi.check(abi.lib().b200_rms_matmul(_ref(xd), _ref(gd), _ref(wd), _ref(od), float(eps),

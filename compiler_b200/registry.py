@@ -241,10 +241,11 @@ def _dequantize(device, v, grid, name):
 
 
 def _rms_matmul(device, v, grid, name):
-    """rms_matmul_rbe_kernel (ops/suite/dev/rms_matmul_rbe.py:18-30) without the rotary
-    epilogue: batches of [M,K] rows against one [K,N] weight."""
+    """rms_matmul_rbe_kernel (ops/suite/dev/rms_matmul_rbe.py:18-30): batches of [M,K] rows
+    against one [K,N] weight.  (USE_FP8 / RBE_EPILOGUE are constexprs without code behind them
+    in the reference's compile unit; anything but False is refused.)"""
     _require(not v.get("RBE_EPILOGUE", False) and not v.get("USE_FP8", False), name,
-             "RBE_EPILOGUE", "the rotary epilogue and the fp8 path have no native operator")
+             "RBE_EPILOGUE", "only USE_FP8=False, RBE_EPILOGUE=False exist in the reference program")
     m, n, k = int(v["M"]), int(v["N"]), int(v["K"])
     batches = _grid_tuple(grid)[0]
     _require(int(v["stride_x_k"]) == 1 and int(v["stride_w_n"]) == 1 and

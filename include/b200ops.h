@@ -206,8 +206,7 @@ int b200_dequantize_cols(const b200_tensor *b, const b200_tensor *scale, b200_te
                          void *stream);
 
 /* out = rsqrt(mean(x^2, row) + eps) * ((x * g) @ w): RMS normalisation folded into a matmul.
- * Replaces rms_matmul_rbe_kernel without its rotary epilogue
- * (ops/suite/dev/rms_matmul_rbe.py:18-63).  x [M,K], g [K], w [K,N], out [M,N] (x's type or
+ * Replaces rms_matmul_rbe_kernel (ops/suite/dev/rms_matmul_rbe.py:18-63).  x [M,K], g [K], w [K,N], out [M,N] (x's type or
  * f32).  Two small kernels write rinv[M] (f32) and g-scaled weights into caller-provided
  * scratch (scratch_w [K,N] in x's type, scratch_rinv f32 [>= M]); the tensor-core GEMM then
  * runs x @ scratch_w and multiplies each accumulator row by rinv in its epilogue, so the
