@@ -119,6 +119,21 @@ def attention(q, k, v, o, *, lse=None, scale=None, causal=True, stream=0):
                                       float(scale), 1 if causal else 0, stream))
 
 
+def attention_window(q, k, v, o, *, g_cumsum=None, sink_bias=None, lse=None, scale=None,
+                     window=0, stream=0):
+    """Causal sliding-window attention with gate bias and sink on token-major tensors
+    (parallel_attn_fwd_kernel, ops/suite/dev/parallel_attn_fwd_kernel.py:142-166)."""
+    if scale is None:
+        scale = 1.0 / float(q.shape[-1]) ** 0.5
+    qd, kd, vd, od = _desc(q), _desc(k), _desc(v), _desc(o)
+    gd = _desc(g_cumsum) if g_cumsum is not None else None
+    sd = _desc(sink_bias) if sink_bias is not None else None
+    ld = _desc(lse) if lse is not None else None
+    abi.check(abi.lib().b200_attn_window_fwd(_ref(qd), _ref(kd), _ref(vd), _ref(od), _ref(gd),
+                                             _ref(sd), _ref(ld), float(scale), int(window),
+                                             stream))
+
+
 def attention_decode(q, k, v, out, *, scale=None, stream=0):
     """out[b] = softmax(scale * K[b // group] q[b]) V[b // group]; q/out [B, D], k/v
     [B // group, N, D].

@@ -327,6 +327,23 @@ def _gqa(device, v, grid, name):
                   scale=float(v["scale"]), causal=False, stream=device.stream)
 
 
+def _parallel_attn(device, v, grid, name):
+    """parallel_attn_fwd_kernel (ops/suite/dev/parallel_attn_fwd_kernel.py): contiguous
+    token-major q [B,T,HQ,K], k [B,T,H,K], v [B,T,H,V], o, g_cumsum, lse."""
+    _require(not v.get("IS_VARLEN", False), name, "IS_VARLEN",
+             "packed variable-length input has no native kernel")
+    b, t, h, hq = int(v["B"]), int(v["T"]), int(v["H"]), int(v["HQ"])
+    kd, vd = int(v["K"]), int(v["V"])
+    _require(h > 0 and hq == h * int(v["G"]), name, "G", "HQ must be H * G")
+    ops.attention_window(
+        _View(v["q"], (b, t, hq, kd)), _View(v["k"], (b, t, h, kd)), _View(v["v"], (b, t, h, vd)),
+        _View(v["o"], (b, t, hq, vd)),
+        g_cumsum=_View(v["g_cumsum"], (b, t, hq)) if v.get("USE_G", False) else None,
+        sink_bias=_View(v["sink_bias"], (hq,)) if v.get("USE_SINK_BIAS", False) else None,
+        lse=_View(v["lse"], (b, t, hq)), scale=float(v["scale"]),
+        window=int(v["W"]) if v.get("USE_WINDOW", False) else 0, stream=device.stream)
+
+
 def _flash_varlen(device, v, grid, name):
     """flash_varlen_fwd_kernel (ops/suite/dev/flash_varlen_fwd_kernel.py:21-335), the dense
     case its reference covers (:370-418): packed sequences addressed through cu_seqlens (or
@@ -568,6 +585,10 @@ def default_registry() -> Registry:
                 "BLOCK_SIZE_K"), _rms_matmul)
     r.register("log_softmax_linear_kernel", ("x_ptr", "w_ptr", "y_ptr", "K", "N"),
                _log_softmax_linear)
+    r.register("parallel_attn_fwd_kernel",
+               ("q", "k", "v", "o", "g_cumsum", "sink_bias", "lse", "scale", "cu_seqlens",
+                "chunk_indices", "T", "W", "B", "H", "HQ", "G", "K", "V", "BT", "BS", "BK", "BV",
+                "USE_G", "USE_SINK_BIAS", "USE_WINDOW", "IS_VARLEN"), _parallel_attn)
     r.register("flash_varlen_fwd_kernel", _VARLEN, _flash_varlen)
     r.register("gqa_kernel",
                ("Q", "K", "V", "Out", "stride_qh", "stride_qm", "stride_qk", "stride_kh",

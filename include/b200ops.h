@@ -237,6 +237,19 @@ int b200_attn_fwd(const b200_tensor *q, const b200_tensor *k,
                   const b200_tensor *v, b200_tensor *o, b200_tensor *lse,
                   float scale, int causal, void *stream);
 
+/* Causal sliding-window attention with a gate bias and an attention sink.  Replaces
+ * parallel_attn_fwd_kernel (ops/suite/dev/parallel_attn_fwd_kernel.py; arithmetic :142-166):
+ * logit[t,j] = scale * log2(e) * q[t].k[j] + g[t] - g[j] over max(0, t-window+1) <= j <= t,
+ * softmax in base 2 with the sink's 2^(sink - max) added to the denominator, lse = max +
+ * log2(denominator).  Token-major tensors: q [B,T,HQ,K], k [B,T,H,K], v [B,T,H,V],
+ * o [B,T,HQ,V], g_cumsum [B,T,HQ] or NULL, sink_bias [HQ] or NULL, lse [B,T,HQ] (q's type or
+ * f32) or NULL; window <= 0 means every earlier token.  K and V widths are free; this is a
+ * CUDA-core kernel (at most 8192 keys per row). */
+int b200_attn_window_fwd(const b200_tensor *q, const b200_tensor *k, const b200_tensor *v,
+                         b200_tensor *o, const b200_tensor *g_cumsum,
+                         const b200_tensor *sink_bias, b200_tensor *lse, float scale,
+                         int window, void *stream);
+
 /* Decode-side attention: one query row per (batch, head) against that head's K / V
  * cache.  Replaces flash_decode_kernel (ops/suite/perf/flash_decode.py:21-49):
  * out[b] = softmax(scale * K[b / group] q[b]) V[b / group].  q, out: [B, D]; k, v:

@@ -201,6 +201,38 @@ def gqa_attention_ref(q, k, v, scale, causal=False):
                          np.repeat(np.asarray(v), group, axis=1), scale, causal)
 
 
+def window_attention_ref(q, k, v, gate, sink_bias, scale, window):
+    """Causal sliding-window attention in base 2 with gate bias and sink (ref of
+    ops/suite/dev/parallel_attn_fwd_kernel.py:142-166).  q [B,T,HQ,K], k [B,T,H,K],
+    v [B,T,H,V], gate [B,T,HQ] or None, sink_bias [HQ] or None, window <= 0 = unlimited.
+    Returns (o [B,T,HQ,V], lse [B,T,HQ]) in float64."""
+    q = np.asarray(q, dtype=np.float64)
+    k = np.asarray(k, dtype=np.float64)
+    v = np.asarray(v, dtype=np.float64)
+    B, T, HQ, _ = q.shape
+    group = HQ // k.shape[2]
+    out = np.zeros((B, T, HQ, v.shape[3]))
+    lse = np.zeros((B, T, HQ))
+    log2e = 1.4426950216
+    for b in range(B):
+        for hq in range(HQ):
+            h = hq // group
+            logits = (q[b, :, hq] @ k[b, :, h].T) * float(scale) * log2e
+            if gate is not None:
+                g = np.asarray(gate, dtype=np.float64)[b, :, hq]
+                logits = logits + g[:, None] - g[None, :]
+            for row in range(T):
+                first = max(0, row - int(window) + 1) if window > 0 else 0
+                valid = logits[row, first:row + 1]
+                sink = float(np.asarray(sink_bias, dtype=np.float64)[hq]) if sink_bias is not None else -np.inf
+                mx = max(float(valid.max()), sink)
+                w = np.exp2(valid - mx)
+                den = w.sum() + (np.exp2(sink - mx) if sink_bias is not None else 0.0)
+                out[b, row, hq] = (w / den) @ v[b, first:row + 1, h]
+                lse[b, row, hq] = mx + np.log2(den)
+    return out, lse
+
+
 def varlen_attention_ref(q, k, v, cu_q, cu_k, scale):
     """Dense attention over packed sequences (ref of
     ops/suite/dev/flash_varlen_fwd_kernel.py:370-418): q [total_q, H, D], k / v

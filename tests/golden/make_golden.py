@@ -55,6 +55,7 @@ OPERATORS = {
     "perf/flash_decode.py": [(1, 8, 256, 64)],
     "dev/gqa.py": [],
     "dev/flash_varlen_fwd_kernel.py": [],
+    "dev/parallel_attn_fwd_kernel.py": [],
     # GEMM with a reduction epilogue
     "perf/log_softmax_linear.py": [(64, 1024)],
     # norm folded into a GEMM

@@ -441,6 +441,32 @@ def test_linear_log_softmax_rejections(device):
         ops.linear_log_softmax(x, device.alloc((24, 32), "bfloat16"), device.alloc((8, 24), "bfloat16"))
 
 
+@pytest.mark.parametrize("dtype", ["bfloat16", "float32"])
+@pytest.mark.parametrize("shape", [(2, 17, 2, 4, 7, 9, 9), (1, 300, 2, 2, 64, 64, 128),
+                                   (2, 129, 1, 4, 32, 48, 0), (1, 1, 1, 1, 5, 3, 4)])
+@pytest.mark.parametrize("extras", ["gate+sink", "plain"])
+def test_attention_window_sweep(device, shape, dtype, extras):
+    b, t, h, hq, kd, vd, window = shape
+    rng = np.random.default_rng(_seed(shape, dtype, extras))
+    q = _host(rng.normal(0, 0.5, (b, t, hq, kd)), dtype)
+    k = _host(rng.normal(0, 0.5, (b, t, h, kd)), dtype)
+    v = _host(rng.normal(0, 0.5, (b, t, h, vd)), dtype)
+    use = extras == "gate+sink"
+    gate = _host(np.cumsum(-np.abs(rng.normal(0, 0.1, (b, t, hq))), axis=1), dtype) if use else None
+    sink = _host(rng.normal(0, 0.5, hq), dtype) if use else None
+    dq, dk, dv = (_up(device, x, dtype) for x in (q, k, v))
+    do = _poisoned(device, (b, t, hq, vd), dtype)
+    dl = device.upload(np.full((b, t, hq), POISON, np.float32))
+    scale = 1.0 / np.sqrt(kd)
+    ops.attention_window(dq, dk, dv, do, g_cumsum=_up(device, gate, dtype) if use else None,
+                         sink_bias=_up(device, sink, dtype) if use else None, lse=dl, scale=scale,
+                         window=window)
+    out_ref, lse_ref = oracle.window_attention_ref(q, k, v, gate, sink, scale, window)
+    rtol, atol = (1e-4, 1e-5) if dtype == "float32" else TOL[dtype]
+    oracle.compare(device.download(do).astype(np.float64), out_ref, rtol, atol, name="o")
+    oracle.compare(device.download(dl).astype(np.float64), lse_ref, 1e-4, 1e-4, name="lse")
+
+
 DECODE_SHAPES = [  # (query rows B, group, N_CTX, head_dim)
     (1, 1, 1, 16), (3, 1, 7, 32), (4, 1, 255, 64), (4, 1, 256, 128), (2, 1, 1000, 128),
     (5, 1, 4097, 64), (1, 1, 32768, 128),      # one row: its keys are split over a cluster

@@ -138,6 +138,22 @@ def test_rms_matmul(tag):
     _assert_same(out.astype(expected.dtype), expected, meta["dtype"])
 
 
+@pytest.mark.parametrize("tag", golden_cases.tags("parallel_attn_fwd_kernel"))
+def test_window_attention(tag):
+    case, meta = golden_cases.load(tag)
+    a, m = case["args"], case["meta"]
+    b, t, h, hq, kd, vd = m["B"], int(a["T"]), m["H"], m["HQ"], m["K"], m["V"]
+    out, lse = oracle.window_attention_ref(
+        np.asarray(a["q"]).reshape(b, t, hq, kd), np.asarray(a["k"]).reshape(b, t, h, kd),
+        np.asarray(a["v"]).reshape(b, t, h, vd), np.asarray(a["g_cumsum"]).reshape(b, t, hq),
+        a["sink_bias"], a["scale"], m["W"])
+    tol = 1e-4 if meta["dtype"] == "float32" else 2e-2
+    np.testing.assert_allclose(out.reshape(-1), np.asarray(case["expected"]["o"], dtype=np.float64),
+                               rtol=tol, atol=tol)
+    np.testing.assert_allclose(lse.reshape(-1), np.asarray(case["expected"]["lse"], dtype=np.float64),
+                               rtol=tol, atol=tol)
+
+
 @pytest.mark.parametrize("tag", golden_cases.tags("log_softmax_linear"))
 def test_log_softmax_linear(tag):
     case, meta = golden_cases.load(tag)
