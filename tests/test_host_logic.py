@@ -67,10 +67,13 @@ def test_bind_by_name_accepts_keyword_metas_and_rejects_surplus():
 
 
 def test_reference_harness_binding_agrees(tmp_path):
-    """With the reference tree present, its own bind_arguments gives the same lists."""
+    """With the reference tree present (``REFERENCE_ROOT``, or next to this repository), its
+    own bind_arguments gives the same lists."""
+    import os
     import sys
     from pathlib import Path
-    root = Path("/root/reference/ops/harness")
+    base = os.environ.get("REFERENCE_ROOT") or str(Path(__file__).resolve().parents[2] / "reference")
+    root = Path(base) / "ops" / "harness"
     if not root.is_dir():
         pytest.skip("reference tree not present on this host")
     sys.path.insert(0, str(root))
