@@ -62,7 +62,7 @@ constexpr int kFirstKeys = B200_ATTN_FIRST_KEYS;  // multiple of 32 (a 16-column
 
 struct Params {
   int H, N, ZH;   // N = query rows per head
-  int NK;          // keys per head (= N under the causal mask)
+  int NK;          // keys per head; under the causal mask query row i sees keys <= i + NK - N
   int64_t lse_z, lse_h;  // element strides of lse over batch and head
   int kv_group;    // query heads per K / V head
   int wave_heads;  // (batch, head) pairs whose K / V are meant to share the L2 at one time
@@ -215,7 +215,7 @@ __device__ __forceinline__ int item_at(int n, const Params &p, Item &it) {
     if (mt0 >= p.N) {
       it.nb[t] = 0;
     } else {
-      const int kv_len = p.causal ? min(p.NK, mt0 + TILE_M) : p.NK;
+      const int kv_len = p.causal ? min(p.NK, mt0 + TILE_M + (p.NK - p.N)) : p.NK;
       it.nb[t] = (kv_len + BLOCK_N - 1) / BLOCK_N;
     }
   }
@@ -611,10 +611,10 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q,
         tmem_ld_32x32b_x32(s_tmem + 64, reinterpret_cast<uint32_t(&)[32]>(xr[64]));
         tmem_ld_32x32b_x32(s_tmem + 96, reinterpret_cast<uint32_t(&)[32]>(xr[96]));
         const int col0 = j * BLOCK_N;
-        const bool diag = p.causal && (col0 + BLOCK_N - 1 > mt0);
+        const bool diag = p.causal && (col0 + BLOCK_N - 1 > mt0 + (p.NK - p.N));
         const bool ragged = col0 + BLOCK_N > p.NK;
         const bool masked = diag || ragged;
-        const int limit = min(p.causal ? row : p.NK - 1, p.NK - 1) - col0;  // last kept column
+        const int limit = min(p.causal ? row + (p.NK - p.N) : p.NK - 1, p.NK - 1) - col0;  // last kept column
         float mx0, mx1, mx2, mx3;
         {
           if (masked) {

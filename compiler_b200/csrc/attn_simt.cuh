@@ -31,7 +31,7 @@ attn_simt_kernel(const T *__restrict__ q, const T *__restrict__ k, const T *__re
   const T *qp = q + z * qz + h * qh + (int64_t)m * qm;
   const T *kp = k + z * kz + (h / kv_group) * kh;
   const T *vp = v + z * vz + (h / kv_group) * vh;
-  const int keys = causal ? m + 1 : NK;
+  const int keys = causal ? min(NK, m + 1 + (NK - N)) : NK;
   for (int d = threadIdx.x; d < D; d += kSimtThreads) qrow[d] = io<T>::load(qp[d]);
   __syncthreads();
   float mx = -INFINITY;

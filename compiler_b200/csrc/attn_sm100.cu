@@ -41,7 +41,7 @@ constexpr float kRescaleThreshold = 8.0f;
 
 struct Params {
   int H, N;      // N = query rows per head
-  int NK;        // keys per head (= N under the causal mask)
+  int NK;        // keys per head; under the causal mask query row i sees keys <= i + NK - N
   int64_t lse_z, lse_h;  // element strides of lse over batch and head
   int kv_group;  // query heads per K / V head (1 = one K / V head per query head)
   float scale_log2;  // scale * log2(e)
@@ -128,7 +128,7 @@ attn_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
   const int zh = blockIdx.y;
   const int z = zh / p.H, h = zh % p.H;
   const int m0 = qb * BLOCK_M;
-  const int kv_len = p.causal ? min(p.NK, m0 + BLOCK_M) : p.NK;
+  const int kv_len = p.causal ? min(p.NK, m0 + BLOCK_M + (p.NK - p.N)) : p.NK;
   const int nblocks = (kv_len + BLOCK_N - 1) / BLOCK_N;
 
   if (threadIdx.x == 0) {
@@ -285,10 +285,10 @@ attn_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
         for (int i = 0; i < 32; ++i) x[c * 32 + i] = __uint_as_float(r[i]);
       }
       const int col0 = j * BLOCK_N;
-      const bool diag = p.causal && (col0 + BLOCK_N - 1 > m0);
+      const bool diag = p.causal && (col0 + BLOCK_N - 1 > m0 + (p.NK - p.N));
       const bool ragged = col0 + BLOCK_N > p.NK;
       if (diag || ragged) {
-        const int limit = min(p.causal ? row : p.NK - 1, p.NK - 1);  // last kept column
+        const int limit = min(p.causal ? row + (p.NK - p.N) : p.NK - 1, p.NK - 1);  // last kept column
 #pragma unroll
         for (int i = 0; i < BLOCK_N; ++i)
           if (col0 + i > limit) x[i] = -INFINITY;
@@ -458,14 +458,15 @@ extern "C" int b200_attn_fwd(const b200_tensor *q, const b200_tensor *k, const b
   // K / V may have fewer heads: query head h reads K / V head h / (H / H_KV), the grouping
   // of gqa_kernel (ops/suite/dev/gqa.py:27-32)
   const int64_t HKV = k->shape[1];
-  // ... and another length: N_K keys per head (non-causal only; the dense, unmasked case
-  // of flash_varlen_fwd_kernel, ops/suite/dev/flash_varlen_fwd_kernel.py:370-418)
+  // ... and another length: N_K keys per head (one sequence of flash_varlen_fwd_kernel,
+  // ops/suite/dev/flash_varlen_fwd_kernel.py).  The causal mask is then aligned to the last
+  // key: row i sees keys <= i + N_K - N (:138, window_size_right = 0)
   const int64_t NK = k->shape[2];
   for (const b200_tensor *t : {k, v}) {
     B200_REQUIRE(t->shape[0] == Z && t->shape[1] == HKV && t->shape[2] == NK && t->shape[3] == D,
                  "k and v must both be [Z, H_KV, N_K, D]");
   }
-  B200_REQUIRE(!causal || NK == N, "the causal mask needs as many keys as query rows");
+  B200_REQUIRE(!causal || NK >= N, "the causal mask needs at least as many keys as query rows");
   B200_REQUIRE(NK < (1 << 24), "N_K out of range");
   B200_REQUIRE(HKV > 0 ? H % HKV == 0 : H == 0, "query heads %lld are not a multiple of K/V heads %lld",
                (long long)H, (long long)HKV);

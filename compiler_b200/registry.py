@@ -346,15 +346,16 @@ def _parallel_attn(device, v, grid, name):
 
 def _flash_varlen(device, v, grid, name):
     """flash_varlen_fwd_kernel (ops/suite/dev/flash_varlen_fwd_kernel.py:21-335), the dense
-    case its reference covers (:370-418): packed sequences addressed through cu_seqlens (or
+    case its reference covers (:370-418) and the causal one (mask aligned to the last key,
+    :138; key length >= query length): packed sequences addressed through cu_seqlens (or
     fixed lengths with batch strides), query and key lengths that differ, h / hk query heads
     per K / V head, log-sum-exp laid out [h, total_q].  One launch of the attention operator
     per sequence, on strided views of the packed buffers.  The sequence boundaries are read
     back from the device, so this launch is bound afresh every time."""
-    for flag in ("is_softcap", "is_dropout", "return_softmax", "is_causal", "is_local",
-                 "is_paged", "is_alibi", "seqlenq_ngroups_swapped", "is_seqused_k"):
+    for flag in ("is_softcap", "is_dropout", "return_softmax", "is_local", "is_paged", "is_alibi",
+                 "seqlenq_ngroups_swapped", "is_seqused_k"):
         _require(not v.get(flag, False), name, flag,
-                 "only the dense, unmasked variant has a native operator")
+                 "only the dense and the causal variants have a native operator")
     h, hk, d, batches = int(v["h"]), int(v["hk"]), int(v["d"]), int(v["b"])
     _require(hk > 0 and h % hk == 0, name, "hk", "h must be a multiple of hk")
     total_q = int(v["total_q"])
@@ -387,7 +388,7 @@ def _flash_varlen(device, v, grid, name):
                     offset=span["q"][2])
         ops.attention(view("q", h, q_len), view("k", hk, k_len), view("v", hk, k_len),
                       view("o", h, q_len), lse=lse, scale=float(v["scale_softmax"]),
-                      causal=False, stream=device.stream)
+                      causal=bool(v.get("is_causal", False)), stream=device.stream)
 
 
 _flash_varlen.reads_device = True

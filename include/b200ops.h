@@ -228,9 +228,9 @@ int b200_linear_log_softmax(const b200_tensor *x, const b200_tensor *w, b200_ten
  * (ops/suite/perf/attn_fwd_causal.py:19-57).  q,o: [Z,H,N,D], k,v: [Z,H_KV,N_K,D]
  * with unit last stride; H_KV divides H and query head h reads K / V head
  * h / (H / H_KV) (H_KV == H for the kernels above; fewer K / V heads is gqa_kernel,
- * ops/suite/dev/gqa.py:19-58).  N_K may differ from N when causal == 0 (one sequence of
- * flash_varlen_fwd_kernel, ops/suite/dev/flash_varlen_fwd_kernel.py:370-418); the causal
- * mask needs N_K == N.  lse: [Z,H,N] f32 with unit last stride (any batch / head
+ * ops/suite/dev/gqa.py:19-58).  N_K may differ from N (one sequence of
+ * flash_varlen_fwd_kernel, ops/suite/dev/flash_varlen_fwd_kernel.py); the causal mask then
+ * needs N_K >= N and is aligned to the last key: row i sees keys <= i + N_K - N (:138).  lse: [Z,H,N] f32 with unit last stride (any batch / head
  * strides) or NULL, natural log of the sum of
  * exp of the scaled masked scores (ops/suite/dev/flash_varlen_fwd_kernel.py:309). */
 int b200_attn_fwd(const b200_tensor *q, const b200_tensor *k,

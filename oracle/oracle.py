@@ -124,16 +124,18 @@ def attention_head_ref(q, k, v, scale, causal=True):
     plus the log-sum-exp of ops/suite/dev/flash_varlen_fwd_kernel.py:412-418
     (rowmax + log(sum(exp(scores - rowmax))) over the scaled, masked scores).
 
-    q, k, v: [N, D].  Returns (out [N, D], lse [N]) in float64.  Heads are
+    q: [N, D]; k, v: [N_K, D].  With N_K != N the causal mask is aligned to the last key:
+    row i sees keys <= i + N_K - N (ops/suite/dev/flash_varlen_fwd_kernel.py:138).
+    Returns (out [N, D], lse [N]) in float64.  Heads are
     independent, so evaluating the reference per slice gives the same numbers as
     its whole-tensor einsum while holding one [N, N] score matrix at a time."""
     q = np.asarray(q, dtype=np.float64)
     k = np.asarray(k, dtype=np.float64)
     v = np.asarray(v, dtype=np.float64)
-    n = q.shape[0]
+    n, nk = q.shape[0], k.shape[0]
     scores = (q @ k.T) * float(scale)
     if causal:
-        scores = np.where(np.tril(np.ones((n, n), dtype=bool)), scores, -np.inf)
+        scores = np.where(np.tril(np.ones((n, nk), dtype=bool), nk - n), scores, -np.inf)
     row_max = scores.max(axis=-1, keepdims=True)
     p = np.exp(scores - row_max)
     denom = p.sum(axis=-1, keepdims=True)

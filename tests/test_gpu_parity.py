@@ -243,11 +243,15 @@ def test_attention_grouped_kv_heads(device, shape, causal, variant):
 
 
 @pytest.mark.parametrize("variant", ["pair", "single"])
-@pytest.mark.parametrize("shape", [(2, 4, 2, 300, 517, 64), (1, 2, 2, 129, 64, 128), (1, 3, 1, 640, 1000, 128)])
-def test_attention_other_key_length(device, shape, variant):
-    """N_K keys for N query rows (non-causal), with the log-sum-exp written through strides."""
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("shape", [(2, 4, 2, 300, 517, 64), (1, 2, 2, 129, 64, 128),
+                                   (1, 3, 1, 640, 1000, 128), (1, 2, 1, 100, 1200, 128)])
+def test_attention_other_key_length(device, shape, causal, variant):
+    """N_K keys for N query rows, the causal mask aligned to the last key (row i sees keys
+    <= i + N_K - N), the log-sum-exp written through strides."""
+    from compiler_b200.runtime.abi import B200Error
     z, hq, hkv, n, nk, d = shape
-    rng = np.random.default_rng(_seed(shape))
+    rng = np.random.default_rng(_seed(shape, causal))
     q = _host(rng.standard_normal((z, hq, n, d)), "bfloat16")
     k, v = (_host(rng.standard_normal((z, hkv, nk, d)), "bfloat16") for _ in range(2))
     dq, dk, dv = (_up(device, t, "bfloat16") for t in (q, k, v))
@@ -267,30 +271,34 @@ def test_attention_other_key_length(device, shape, variant):
     scale = 1.0 / np.sqrt(d)
     os.environ["B200OPS_ATTN_KERNEL"] = variant
     try:
-        ops.attention(dq, dk, dv, do, lse=Strided(), scale=scale, causal=False)
+        if causal and nk < n:
+            with pytest.raises(B200Error):  # rows without any visible key
+                ops.attention(dq, dk, dv, do, scale=scale, causal=True)
+            return
+        ops.attention(dq, dk, dv, do, lse=Strided(), scale=scale, causal=causal)
         device.check_status()
-        from compiler_b200.runtime.abi import B200Error
-        with pytest.raises(B200Error):  # the causal mask needs N_K == N
-            ops.attention(dq, dk, dv, do, scale=scale, causal=True)
     finally:
         os.environ.pop("B200OPS_ATTN_KERNEL", None)
-    group = hq // hkv
-    out_ref, lse_ref = oracle.attention_ref(q, np.repeat(k, group, axis=1), np.repeat(v, group, axis=1),
-                                            scale, False) if n == nk else (None, None)
-    if out_ref is None:
-        out_ref = np.zeros((z, hq, n, d))
-        lse_ref = np.zeros((z, hq, n))
-        for zz in range(z):
-            for h in range(hq):
-                s_ = (q[zz, h].astype(np.float64) @ k[zz, h // group].astype(np.float64).T) * scale
-                mx = s_.max(axis=1, keepdims=True)
-                w = np.exp(s_ - mx)
-                out_ref[zz, h] = (w / w.sum(axis=1, keepdims=True)) @ v[zz, h // group].astype(np.float64)
-                lse_ref[zz, h] = mx[:, 0] + np.log(w.sum(axis=1))
+    out_ref, lse_ref = oracle.gqa_attention_ref(q, k, v, scale, causal)
     oracle.compare(device.download(do).astype(np.float64), out_ref, *TOL["bfloat16"], name="out")
     got_lse = device.download(dl)
     oracle.compare(got_lse[..., :n].astype(np.float64), lse_ref, 1e-3, 1e-3, name="lse")
     assert np.all(got_lse[..., n:] == POISON)  # the padding between rows is untouched
+
+
+@pytest.mark.parametrize("shape", [(2, 17, 40, 16), (1, 33, 33, 80)])
+def test_attention_other_key_length_cuda_core(device, shape):
+    """The same mask rule on the CUDA-core kernel (fp32)."""
+    z, n, nk, d = shape
+    rng = np.random.default_rng(_seed(shape))
+    q = rng.standard_normal((z, 2, n, d)).astype(np.float32)
+    k, v = (rng.standard_normal((z, 2, nk, d)).astype(np.float32) for _ in range(2))
+    dq, dk, dv = (device.upload(t) for t in (q, k, v))
+    do = device.upload(np.full((z, 2, n, d), POISON, np.float32))
+    for causal in (False, True):
+        ops.attention(dq, dk, dv, do, scale=0.25, causal=causal)
+        out_ref, _ = oracle.attention_ref(q, k, v, 0.25, causal)
+        oracle.compare(device.download(do).astype(np.float64), out_ref, 1e-4, 1e-5)
 
 
 def test_varlen_attention_through_the_launch_surface(device):
