@@ -108,6 +108,15 @@ int b200_set_device(int device);
  * waits write; synchronises `stream` first. */
 int b200_last_device_status(void *stream);
 
+/* Self-test of the bounded device-side wait: launches one CTA whose two waiters wait on a
+ * barrier that nothing completes.  The wait expires after its limit (about 2 s), records
+ * B200_TIMEOUT in the status word, and the kernel returns normally.  *gave_up = 1 when both
+ * waiters gave up as they must; the next b200_last_device_status() then reports
+ * B200_TIMEOUT (site 31) and clears it.  No reference counterpart (the reference's runtime
+ * has no device-side waits); it exists so that the failure path can be exercised without a
+ * fault. */
+int b200_wait_selftest(unsigned int *gave_up, void *stream);
+
 /* ---- memory, streams, events (torch-free Device plumbing; replaces the
  *      cudaMalloc / pinned staging / event timer of
  *      ops/harness/opslib/devices/cuda.py:71-123, 138-167, 186-262) -------- */

@@ -157,3 +157,26 @@ def test_repeated_launches_replay_the_bound_calls(device):
     with pytest.raises(UnsupportedLaunch):
         device.launch(unknown, (1,), [staged.buffer("x_ptr"), staged.buffer("y_ptr")], {})
     assert len(device._plans) == size
+
+
+def test_bounded_wait_expires_and_the_context_survives(device):
+    """The failure path of the device-side waits, without a fault: a wait on a barrier that
+    nothing completes gives up after its limit, the status word reports B200_TIMEOUT with the
+    waiter's site, reading it clears it, and the next launch on the same context is correct."""
+    import ctypes
+    import time
+    from compiler_b200.runtime import abi
+    gave_up = ctypes.c_uint32(0)
+    start = time.perf_counter()
+    abi.check(abi.lib().b200_wait_selftest(ctypes.byref(gave_up), None))
+    elapsed = time.perf_counter() - start
+    assert gave_up.value == 1
+    assert 1.0 < elapsed < 10.0  # the limit is about two seconds, not forever
+    with pytest.raises(abi.B200Error) as caught:
+        device.check_status()
+    assert caught.value.status == abi.TIMEOUT and "site 31" in str(caught.value)
+    device.check_status()  # cleared by the read
+    x = np.random.default_rng(12).standard_normal((64, 1000)).astype(np.float32)
+    dx, dy = device.upload(x), device.alloc(x.shape, "float32")
+    ops.softmax(dx, dy)
+    oracle.compare(device.download(dy).astype(np.float64), oracle.softmax_ref(x), 2e-3, 2e-3)
