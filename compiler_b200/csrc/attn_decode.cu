@@ -28,6 +28,7 @@
 #include <stdlib.h>
 
 #include <map>
+#include <type_traits>
 #include <mutex>
 #include <utility>
 
@@ -64,11 +65,28 @@ __device__ __forceinline__ float ex2f(float x) {
 template <typename T> __device__ __forceinline__ float pow2(float x) { return ex2f(x); }
 template <> __device__ __forceinline__ float pow2<float>(float x) { return exp2f(x); }
 
+// 16 bytes -> floats.  16-bit pairs are widened with one shift / mask (bf16) or one packed
+// conversion (f16) per word.
 template <typename T, int VEC>
 __device__ __forceinline__ void unpack(const uint4 &raw, float (&f)[VEC]) {
-  const T *e = reinterpret_cast<const T *>(&raw);
+  const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+  if constexpr (sizeof(T) == 4) {
 #pragma unroll
-  for (int i = 0; i < VEC; ++i) f[i] = io<T>::load(e[i]);
+    for (int i = 0; i < 4; ++i) f[i] = __uint_as_float(w[i]);
+  } else if constexpr (std::is_same<T, __nv_bfloat16>::value) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      f[2 * i] = __uint_as_float(w[i] << 16);
+      f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 pair = __half22float2(*reinterpret_cast<const __half2 *>(&w[i]));
+      f[2 * i] = pair.x;
+      f[2 * i + 1] = pair.y;
+    }
+  }
 }
 
 // merge (m_b, l_b, acc_b) into (m, l, acc); either side may be empty (m = -inf, l = 0)
