@@ -174,3 +174,35 @@ extern "C" int b200_event_elapsed_ms(void *start, void *stop, float *ms) {
   B200_CUDA_OK(cudaEventElapsedTime(ms, (cudaEvent_t)start, (cudaEvent_t)stop));
   return B200_OK;
 }
+
+// ---- CUDA graphs: a captured sequence of launches replayed with one call -----------------
+extern "C" int b200_stream_wait_event(void *stream, void *event) {
+  B200_CUDA_OK(cudaStreamWaitEvent((cudaStream_t)stream, (cudaEvent_t)event, 0));
+  return B200_OK;
+}
+extern "C" int b200_graph_begin_capture(void *stream) {
+  if (stream == nullptr) return b200::fail(B200_USAGE, "capture needs a created stream, not the default one");
+  B200_CUDA_OK(cudaStreamBeginCapture((cudaStream_t)stream, cudaStreamCaptureModeThreadLocal));
+  return B200_OK;
+}
+extern "C" int b200_graph_end_capture(void *stream, void **graph_exec) {
+  if (graph_exec == nullptr) return b200::fail(B200_USAGE, "null out pointer");
+  *graph_exec = nullptr;
+  cudaGraph_t graph = nullptr;
+  B200_CUDA_OK(cudaStreamEndCapture((cudaStream_t)stream, &graph));
+  cudaGraphExec_t exec = nullptr;
+  const cudaError_t err = cudaGraphInstantiate(&exec, graph, 0);
+  cudaGraphDestroy(graph);
+  B200_CUDA_OK(err);
+  *graph_exec = (void *)exec;
+  return B200_OK;
+}
+extern "C" int b200_graph_launch(void *graph_exec, void *stream) {
+  if (graph_exec == nullptr) return b200::fail(B200_USAGE, "null graph");
+  B200_CUDA_OK(cudaGraphLaunch((cudaGraphExec_t)graph_exec, (cudaStream_t)stream));
+  return B200_OK;
+}
+extern "C" int b200_graph_destroy(void *graph_exec) {
+  if (graph_exec != nullptr) B200_CUDA_OK(cudaGraphExecDestroy((cudaGraphExec_t)graph_exec));
+  return B200_OK;
+}

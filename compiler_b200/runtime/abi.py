@@ -98,6 +98,11 @@ PROTOTYPES = {
     "b200_reduce_slices_broadcast": (c_int, [_PTR, c_uint32, c_int, c_int64, c_int64, c_int64,
                                              POINTER(_PTR), _PTR]),
     "b200_attn_fwd": (c_int, [_T, _T, _T, _T, _T, c_float, c_int, _PTR]),
+    "b200_stream_wait_event": (c_int, [_PTR, _PTR]),
+    "b200_graph_begin_capture": (c_int, [_PTR]),
+    "b200_graph_end_capture": (c_int, [_PTR, POINTER(c_void_p)]),
+    "b200_graph_launch": (c_int, [_PTR, _PTR]),
+    "b200_graph_destroy": (c_int, [_PTR]),
     "b200_wait_selftest": (c_int, [POINTER(c_uint32), _PTR]),
     "b200_attn_window_fwd": (c_int, [_T, _T, _T, _T, _T, _T, _T, c_float, c_int, _PTR]),
     "b200_attn_decode": (c_int, [_T, _T, _T, _T, c_float, _PTR]),

@@ -108,6 +108,23 @@ int b200_set_device(int device);
  * waits write; synchronises `stream` first. */
 int b200_last_device_status(void *stream);
 
+/* CUDA graphs: launches enqueued on `stream` between begin and end are recorded instead of
+ * run, and the instantiated graph replays them with one call -- for loops of short kernels
+ * whose cost is launch latency (the reference has no counterpart: its runtime launches one
+ * program per process).  `stream` must come from b200_stream_create.  Other streams join a
+ * capture through b200_event_record on the capturing stream + b200_stream_wait_event on
+ * theirs, and must be joined back the same way before the capture ends.  Every operator
+ * used inside a capture must have run once on this device before -- b200_attn_decode once on
+ * the capturing stream -- (first calls set kernel attributes and allocate the status word /
+ * scratch, which a capture forbids); the entry
+ * points that synchronise (memcpy with NULL stream, *_sync, b200_last_device_status,
+ * b200_allclose_f32) cannot be captured. */
+int b200_stream_wait_event(void *stream, void *event);
+int b200_graph_begin_capture(void *stream);
+int b200_graph_end_capture(void *stream, void **graph_exec);
+int b200_graph_launch(void *graph_exec, void *stream);
+int b200_graph_destroy(void *graph_exec);
+
 /* Self-test of the bounded device-side wait: launches one CTA whose two waiters wait on a
  * barrier that nothing completes.  The wait expires after its limit (about 2 s), records
  * B200_TIMEOUT in the status word, and the kernel returns normally.  *gave_up = 1 when both

@@ -180,3 +180,47 @@ def test_bounded_wait_expires_and_the_context_survives(device):
     dx, dy = device.upload(x), device.alloc(x.shape, "float32")
     ops.softmax(dx, dy)
     oracle.compare(device.download(dy).astype(np.float64), oracle.softmax_ref(x), 2e-3, 2e-3)
+
+
+def test_captured_launches_replay_as_one_graph(device):
+    """A sequence of operator launches recorded into a CUDA graph gives the same bytes as the
+    direct launches, on every replay and with the inputs changed between replays."""
+    from compiler_b200 import graph
+    from compiler_b200.runtime import abi
+    rng = np.random.default_rng(21)
+    rows, cols, sets = 256, 4000, 3
+    xs = [(rng.standard_normal((rows, cols)) * 2).astype(np.float16) for _ in range(sets)]
+    dxs = [device.upload(x) for x in xs]
+    dys = [device.alloc((rows, cols), "float16") for _ in range(sets)]
+    a = oracle.to_storage(rng.standard_normal((256, 128)).astype(np.float32) / 8, "bfloat16")
+    b = oracle.to_storage(rng.standard_normal((128, 512)).astype(np.float32), "bfloat16")
+    da, db = device.upload(a, "bfloat16"), device.upload(b, "bfloat16")
+    dc = device.alloc((256, 512), "bfloat16")
+    stream = graph.Stream()
+    # every operator once outside the capture (first calls configure kernels)
+    ops.softmax(dxs[0], dys[0], causal_mod=True, stream=stream.handle)
+    ops.gemm(da, db, dc, act=abi.ACT_GELU_TANH, stream=stream.handle)
+    stream.synchronize()
+    with graph.capture(stream) as g:
+        for i in range(12):
+            ops.softmax(dxs[i % sets], dys[i % sets], causal_mod=True, row_offset=7,
+                        stream=stream.handle)
+        ops.gemm(da, db, dc, act=abi.ACT_GELU_TANH, stream=stream.handle)
+    for replay in range(2):
+        for y in dys:
+            device.copy_in(y, np.zeros((rows, cols), np.float16), sync=True)
+        g.launch(stream)
+        stream.synchronize()
+        for x, dy in zip(xs, dys):
+            oracle.compare(device.download(dy).astype(np.float64), oracle.masked_softmax_ref(x, 7),
+                           1e-2, 1e-2)
+        oracle.compare(device.download(dc).astype(np.float64),
+                       oracle.linear_act_ref(a, b, None, "gelu_tanh"), 2e-2, 2e-2)
+        # new contents in the same buffers: the next replay must see them
+        xs = [(-x).astype(np.float16) for x in xs]
+        for x, dx in zip(xs, dxs):
+            device.copy_in(dx, x, sync=True)
+    with pytest.raises(abi.B200Error):  # the default stream cannot be captured
+        abi.check(abi.lib().b200_graph_begin_capture(None))
+    g.close()
+    stream.close()
