@@ -599,6 +599,219 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
   }
 }
 
+// ------------------------------------------------------------ CTA-pair kernel
+// The same persistent pipeline for a cluster of two CTAs that share one 256 x 256 tile of C:
+// each CTA loads its 128 rows of A and its 128 of the 256 columns of B, the even CTA issues
+// tcgen05.mma.cta_group::2 (M = 256), and each CTA's tensor memory receives the 256 columns of
+// its own 128 rows.  Per tile and SM the operand bytes read from shared memory and brought in
+// from L2 drop by a third against the one-CTA kernel (B is not duplicated in the two SMs).
+// Barriers: full[s] lives in the even CTA and counts the bytes of both CTAs' copies; empty[s]
+// and acc_full[a] exist in both CTAs and get one commit each; acc_empty[a] lives in the even
+// CTA and takes the arrivals of the eight epilogue warps of the pair.
+constexpr int PAIR_STAGES = 6;
+constexpr int PAIR_B_STAGE_BYTES = 2 * B_BOX_BYTES;                      // 16 KiB
+constexpr int PAIR_STAGE_BYTES = A_STAGE_BYTES + PAIR_B_STAGE_BYTES;     // 32 KiB per CTA
+constexpr int PAIR_SMEM_BYTES = PAIR_STAGES * PAIR_STAGE_BYTES + 1024 + 256;
+
+template <typename OutT>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
+gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
+                 const __grid_constant__ CUtensorMap tm_b, const Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t *smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+  const uint32_t a_smem = smem_base;
+  const uint32_t b_smem = smem_base + PAIR_STAGES * A_STAGE_BYTES;
+  uint64_t *bars = reinterpret_cast<uint64_t *>(smem_gen + PAIR_STAGES * PAIR_STAGE_BYTES);
+  const uint32_t bar0 = smem_base + PAIR_STAGES * PAIR_STAGE_BYTES;
+  auto full_bar = [&](int s) { return bar0 + 8u * s; };
+  auto empty_bar = [&](int s) { return bar0 + 8u * (PAIR_STAGES + s); };
+  auto acc_full_bar = [&](int a) { return bar0 + 8u * (2 * PAIR_STAGES + a); };
+  auto acc_empty_bar = [&](int a) { return bar0 + 8u * (2 * PAIR_STAGES + 2 + a); };
+  const uint32_t drain_bar = bar0 + 8u * (2 * PAIR_STAGES + 4);
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * PAIR_STAGES + 5);
+  volatile uint32_t *abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_cta_rank();  // 0: issues the MMAs of the pair
+  const WaitCtx ctx{abort_flag, p.status};
+
+  const int m_pairs = (p.M + 2 * BM - 1) / (2 * BM);
+  const int n_blocks = (p.N + BN - 1) / BN;
+  const int num_tiles = m_pairs * n_blocks;
+  const int num_kb = (p.K + BK - 1) / BK;
+  const int first_tile = (int)(blockIdx.x >> 1);
+  const int tile_step = (int)(gridDim.x >> 1);
+  const int group_pairs = (p.group_m + 1) / 2;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < PAIR_STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(acc_full_bar(a), 1);
+      mbar_init(acc_empty_bar(a), 8);
+    }
+    mbar_init(drain_bar, 1);
+    *abort_flag = 0u;
+    mbar_init_fence();
+  }
+  if (warp == 4 && lane == 0) {
+    tma_prefetch_desc(&tm_a);
+    tma_prefetch_desc(&tm_b);
+  }
+  if (warp == 5) tmem_alloc_pair(smem_u32(tmem_slot), TMEM_COLS);
+  tc_fence_before_sync();
+  __syncthreads();
+  // the peer's barriers must be initialised before anything of this CTA reaches them
+  cluster_arrive();
+  cluster_wait();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 4) {
+    // ------------------------------------------------------------ producer (both CTAs)
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      uint32_t issued_mask = 0, issued_parity = 0;
+      bool ok = true;
+      for (int tile = first_tile; ok && tile < num_tiles; tile += tile_step) {
+        int mp, nb;
+        tile_coords(tile, m_pairs, n_blocks, group_pairs, mp, nb);
+        const int row0 = (mp * 2 + (int)rank) * BM;
+        const int col0 = nb * BN + (int)rank * (BN / 2);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(empty_bar(stage), phase ^ 1u, ctx, 1)) { ok = false; break; }
+          if (rank == 0) mbar_arrive_expect_tx(full_bar(stage), 2 * PAIR_STAGE_BYTES);
+          const uint32_t full0 = map_to_cta(full_bar(stage), 0);
+          tma_load_2d_pair(a_smem + stage * A_STAGE_BYTES, &tm_a, full0, kb * BK, row0);
+          const uint32_t bdst = b_smem + stage * PAIR_B_STAGE_BYTES;
+          tma_load_2d_pair(bdst, &tm_b, full0, col0, kb * BK);
+          tma_load_2d_pair(bdst + B_BOX_BYTES, &tm_b, full0, col0 + 64, kb * BK);
+          issued_mask |= 1u << stage;
+          issued_parity = (issued_parity & ~(1u << stage)) | (phase << stage);
+          if (++stage == PAIR_STAGES) { stage = 0; phase ^= 1u; }
+        }
+      }
+      if (!ok && rank == 0) {
+        for (int s = 0; s < PAIR_STAGES; ++s)
+          if (issued_mask & (1u << s)) mbar_wait_drain(full_bar(s), (issued_parity >> s) & 1u);
+      }
+    }
+  } else if (warp == 5) {
+    // ------------------------------------------------------------ MMA issuer (even CTA)
+    if (rank == 0) {
+      const bool leader = elect_one();
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      auto wait_all = [&](uint32_t bar, uint32_t parity, uint32_t site) {
+        return __all_sync(0xffffffffu, mbar_wait(bar, parity, ctx, site)) != 0;
+      };
+      const uint32_t a_lo0 = desc_lo_sw128(a_smem, 16);
+      const uint32_t b_lo0 = desc_lo_sw128(b_smem, B_BOX_BYTES);
+      constexpr uint32_t hi = desc_hi_sw128(1024);
+      constexpr uint32_t b_kstep = (UMMA_K * 128) >> 4;
+      const uint32_t peer_bar0 = map_to_cta(bar0, 1);
+      for (int tile = first_tile; ok && tile < num_tiles; tile += tile_step) {
+        if (!wait_all(acc_empty_bar(acc), acc_phase ^ 1u, 2)) { ok = false; break; }
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!wait_all(full_bar(stage), phase, 3)) { ok = false; break; }
+          tc_fence_after_sync();
+          const uint32_t a_lo = a_lo0 + (uint32_t)stage * (A_STAGE_BYTES >> 4);
+          const uint32_t b_lo = b_lo0 + (uint32_t)stage * (PAIR_B_STAGE_BYTES >> 4);
+          if (leader) {
+#pragma unroll
+            for (int k = 0; k < BK / UMMA_K; ++k)
+              mma_f16_ss_pair(d_tmem, a_lo + (uint32_t)(k * ((UMMA_K * 2) >> 4)), hi,
+                              b_lo + (uint32_t)k * b_kstep, hi, p.idesc,
+                              (kb > 0 || k > 0) ? 1u : 0u);
+            // the stage is reusable in both CTAs once these MMAs retire
+            tc_commit_pair(empty_bar(stage));
+            tc_commit_pair(peer_bar0 + (empty_bar(stage) - bar0));
+          }
+          if (++stage == PAIR_STAGES) { stage = 0; phase ^= 1u; }
+        }
+        if (!ok) break;
+        if (leader) {
+          tc_commit_pair(acc_full_bar(acc));
+          tc_commit_pair(peer_bar0 + (acc_full_bar(acc) - bar0));
+        }
+        if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+      }
+      if (leader) {
+        tc_commit_pair(drain_bar);
+        mbar_wait_drain(drain_bar, 0);
+      }
+      __syncwarp();
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (both CTAs)
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    OutT *c = reinterpret_cast<OutT *>(p.c);
+    const uint32_t acc_empty0 = map_to_cta(acc_empty_bar(0), 0);
+    for (int tile = first_tile; ok && tile < num_tiles; tile += tile_step) {
+      int mp, nb;
+      tile_coords(tile, m_pairs, n_blocks, group_pairs, mp, nb);
+      if (!__all_sync(0xffffffffu, mbar_wait(acc_full_bar(acc), acc_phase, ctx, 4))) {
+        ok = false;
+        break;
+      }
+      tc_fence_after_sync();
+      const int mb = mp * 2 + (int)rank;
+      const int row = mb * BM + warp * 32 + lane;
+      const bool row_ok = row < p.M;
+      const uint32_t t_row = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(acc * BN);
+      OutT *crow = c + (int64_t)row * p.ldc;
+      if (p.scatter_rows > 0) {
+        const int owner = (mb * BM) / p.scatter_rows;
+        const int local = row - owner * p.scatter_rows;
+        crow = reinterpret_cast<OutT *>(p.c_rank[owner]) +
+               ((int64_t)p.scatter_slot * p.scatter_rows + local) * p.ldc;
+      }
+      const int col_base = nb * BN;
+      const float row_mul = (p.row_scale != nullptr && row_ok) ? p.row_scale[row] : 1.0f;
+      switch (p.act) {
+        case B200_ACT_GELU_TANH:
+          epilogue_tile<OutT, B200_ACT_GELU_TANH>(t_row, p, crow, col_base, row_ok, row_mul);
+          break;
+        case B200_ACT_GELU_ERF:
+          epilogue_tile<OutT, B200_ACT_GELU_ERF>(t_row, p, crow, col_base, row_ok, row_mul);
+          break;
+        case B200_ACT_LEAKY_RELU:
+          epilogue_tile<OutT, B200_ACT_LEAKY_RELU>(t_row, p, crow, col_base, row_ok, row_mul);
+          break;
+        default:
+          epilogue_tile<OutT, B200_ACT_NONE>(t_row, p, crow, col_base, row_ok, row_mul);
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(acc_empty0 + 8u * (uint32_t)acc);
+      if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+    }
+  }
+
+  // neither CTA may leave while the pair's MMAs can still read its shared memory or write
+  // its tensor memory: the even CTA has drained them before it arrives here
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_arrive();
+  cluster_wait();
+  if (warp == 5) {
+    tc_fence_after_sync();
+    tmem_dealloc_pair(tmem_base, TMEM_COLS);
+  }
+}
+
 // ------------------------------------------------------------ CUDA-core path
 // Any dtype, any stride alignment: 32x32 tiles through shared memory, fp32 FMA
 // accumulation (IEEE for fp32 operands).  Serves shapes the tensor-core path
@@ -711,6 +924,42 @@ static int launch_tc(const CUtensorMap &ta, const CUtensorMap &tb, const CUtenso
   const int tiles = ((p.M + BM - 1) / BM) * ((p.N + TILE_N - 1) / TILE_N);
   const int grid = tiles < sm_count() ? tiles : sm_count();
   kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(ta, tb, tb2, p);
+  B200_CUDA_OK(cudaGetLastError());
+  return B200_OK;
+}
+
+template <typename OutT>
+static int launch_pair(const CUtensorMap &ta, const CUtensorMap &tb, const Params &p,
+                       cudaStream_t stream) {
+  static bool configured[64] = {false};
+  static int max_clusters[64] = {0};
+  int dev = 0;
+  B200_CUDA_OK(cudaGetDevice(&dev));
+  auto kernel = gemm_pair_kernel<OutT>;
+  if (dev >= 64) return fail(B200_RESOURCE, "device index %d out of range", dev);
+  if (!configured[dev]) {
+    B200_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      PAIR_SMEM_BYTES));
+    cudaLaunchConfig_t probe = {};
+    probe.gridDim = dim3((unsigned)sm_count());
+    probe.blockDim = dim3(THREADS);
+    probe.dynamicSmemBytes = PAIR_SMEM_BYTES;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
+    probe.attrs = &attr;
+    probe.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kernel, &probe) != cudaSuccess) {
+      (void)cudaGetLastError();
+      n = 0;
+    }
+    max_clusters[dev] = n > 0 ? n : sm_count() / 2;
+    configured[dev] = true;
+  }
+  const int tiles = ((p.M + 2 * BM - 1) / (2 * BM)) * ((p.N + BN - 1) / BN);
+  const int clusters = tiles < max_clusters[dev] ? tiles : max_clusters[dev];
+  kernel<<<2 * clusters, THREADS, PAIR_SMEM_BYTES, stream>>>(ta, tb, p);
   B200_CUDA_OK(cudaGetLastError());
   return B200_OK;
 }
@@ -928,6 +1177,22 @@ static int gemm_impl(const b200_tensor *a, const b200_tensor *b, const b200_tens
   }
 
   const bool dual = act == B200_ACT_SWIGLU;
+  {
+    // CTA pairs (256 x 256 tiles) for B given as [K, N] with the plain epilogues, when there
+    // are enough pair tiles to fill the GPU; B200OPS_GEMM_PAIR=0 / 1 forces the choice.
+    static const int pair_env =
+        getenv("B200OPS_GEMM_PAIR") ? atoi(getenv("B200OPS_GEMM_PAIR")) : -1;
+    const int64_t pair_tiles = ((M + 2 * BM - 1) / (2 * BM)) * ((N + BN - 1) / BN);
+    const bool plain = !dual && !b_rows_are_n && act != kActLogSoftmax && act != kActGroupNormMin;
+    const bool use_pair = plain && (pair_env >= 0 ? pair_env != 0 : pair_tiles >= sm_count());
+    if (use_pair) {
+      Params q = p;
+      q.idesc = sm100::make_idesc_f16(2 * BM, BN, a->dtype == B200_DTYPE_BFLOAT16 ? 1 : 0, 0, 1);
+      if (c->dtype == B200_DTYPE_FLOAT32) return launch_pair<float>(ta, tb, q, s);
+      if (c->dtype == B200_DTYPE_FLOAT16) return launch_pair<__half>(ta, tb, q, s);
+      return launch_pair<__nv_bfloat16>(ta, tb, q, s);
+    }
+  }
   if (c->dtype == B200_DTYPE_FLOAT32)
     return dual ? launch_tc<float, true>(ta, tb, tb2, p, s) : launch_tc<float, false>(ta, tb, tb2, p, s);
   if (c->dtype == B200_DTYPE_FLOAT16)

@@ -142,6 +142,33 @@ def test_gemm_sweep(device, shape, dtype, act):
     oracle.compare(device.download(dc).astype(np.float64), ref, *TOL[dtype], name=f"C{shape}")
 
 
+# Shapes with at least one 256 x 256 tile per pair of SMs take the CTA-pair kernel: whole
+# tiles, a ragged edge in both directions, a last row block whose second CTA is all padding,
+# and K shorter / longer than the six-stage ring.
+PAIR_SHAPES = [(3328, 3072, 192), (3300, 3096, 200), (3072 + 100, 3328, 64), (2048, 5000, 520),
+               (2050, 4872, 8)]
+
+
+@pytest.mark.parametrize("dtype,act", [("bfloat16", "gelu_tanh"), ("float16", "none"),
+                                        ("bfloat16", "leaky_relu")])
+@pytest.mark.parametrize("shape", PAIR_SHAPES)
+def test_gemm_pair_tiles(device, shape, dtype, act):
+    m, n, k = shape
+    rng = np.random.default_rng(_seed(shape, dtype, act))
+    a = _host(rng.standard_normal((m, k)) / np.sqrt(k), dtype)
+    b = _host(rng.standard_normal((k, n)), dtype)
+    bias = _host(rng.normal(0, 0.1, n), dtype)
+    da, db, dbias = _up(device, a, dtype), _up(device, b, dtype), _up(device, bias, dtype)
+    dc = _poisoned(device, (m, n), dtype)
+    code = {"none": abi.ACT_NONE, "gelu_tanh": abi.ACT_GELU_TANH,
+            "leaky_relu": abi.ACT_LEAKY_RELU}[act]
+    use_bias = act != "none"
+    ops.gemm(da, db, dc, bias=dbias if use_bias else None, act=code)
+    device.check_status()
+    ref = oracle.linear_act_ref(a, b, bias if use_bias else None, act)
+    oracle.compare(device.download(dc).astype(np.float64), ref, *TOL[dtype], name=f"C{shape}")
+
+
 @pytest.mark.parametrize("shape", [(128, 128, 64), (200, 264, 136), (256, 1024, 512)])
 def test_gemm_f32_bias_and_f32_output(device, shape):
     m, n, k = shape
