@@ -48,8 +48,8 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 NCU_TRAFFIC = {
     "softmax": 140_785_000,
     "rmsnorm": 212_674_000,
-    "gemm_8192": 1_134_959_000,
-    "gemm_ragged": 197_744_000,
+    "gemm_8192": 1_181_803_000,
+    "gemm_ragged": 203_472_000,
     "attention": 1_036_044_000,
     "attention_decode": 540_428_000,
 }
