@@ -365,6 +365,39 @@ __device__ __forceinline__ void epilogue_tile_dual(uint32_t t_row, const Params 
   }
 }
 
+// Epilogue of one accumulator for one warp: one straight-line body per activation, chosen per
+// tile and not per element.
+template <typename OutT, bool DUAL>
+__device__ __forceinline__ void run_epilogue(uint32_t t_row, const Params &p, OutT *crow, int row,
+                                             int col_base, bool row_ok, float row_mul) {
+  if constexpr (DUAL) {
+    epilogue_tile_dual<OutT>(t_row, p, crow, col_base, row_ok);
+  } else {
+    switch (p.act) {
+      case kActLogSoftmax:
+        epilogue_tile_log_softmax<OutT>(t_row, p, crow, row_ok);
+        break;
+      case kActGroupNormMin:
+        if (p.gn.group == 8) epilogue_tile_gn_min<8>(t_row, p, row, col_base, row_ok);
+        else if (p.gn.group == 16) epilogue_tile_gn_min<16>(t_row, p, row, col_base, row_ok);
+        else if (p.gn.group == 32) epilogue_tile_gn_min<32>(t_row, p, row, col_base, row_ok);
+        else epilogue_tile_gn_min<64>(t_row, p, row, col_base, row_ok);
+        break;
+      case B200_ACT_GELU_TANH:
+        epilogue_tile<OutT, B200_ACT_GELU_TANH>(t_row, p, crow, col_base, row_ok, row_mul);
+        break;
+      case B200_ACT_GELU_ERF:
+        epilogue_tile<OutT, B200_ACT_GELU_ERF>(t_row, p, crow, col_base, row_ok, row_mul);
+        break;
+      case B200_ACT_LEAKY_RELU:
+        epilogue_tile<OutT, B200_ACT_LEAKY_RELU>(t_row, p, crow, col_base, row_ok, row_mul);
+        break;
+      default:
+        epilogue_tile<OutT, B200_ACT_NONE>(t_row, p, crow, col_base, row_ok, row_mul);
+    }
+  }
+}
+
 // tile index -> block coordinates, grouped so that concurrently running CTAs
 // share A row-blocks and B column-blocks in L2
 __device__ __forceinline__ void tile_coords(int tile, int m_blocks, int n_blocks, int group_m,
@@ -555,34 +588,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
       }
       const int col_base = nb * TILE_N;
       const float row_mul = (p.row_scale != nullptr && row_ok) ? p.row_scale[row] : 1.0f;
-      if constexpr (DUAL) {
-        epilogue_tile_dual<OutT>(t_row, p, crow, col_base, row_ok);
-      } else {
-        // one straight-line epilogue per activation: the choice is made per tile,
-        // not per element
-        switch (p.act) {
-          case kActLogSoftmax:
-            epilogue_tile_log_softmax<OutT>(t_row, p, crow, row_ok);
-            break;
-          case kActGroupNormMin:
-            if (p.gn.group == 8) epilogue_tile_gn_min<8>(t_row, p, row, col_base, row_ok);
-            else if (p.gn.group == 16) epilogue_tile_gn_min<16>(t_row, p, row, col_base, row_ok);
-            else if (p.gn.group == 32) epilogue_tile_gn_min<32>(t_row, p, row, col_base, row_ok);
-            else epilogue_tile_gn_min<64>(t_row, p, row, col_base, row_ok);
-            break;
-          case B200_ACT_GELU_TANH:
-            epilogue_tile<OutT, B200_ACT_GELU_TANH>(t_row, p, crow, col_base, row_ok, row_mul);
-            break;
-          case B200_ACT_GELU_ERF:
-            epilogue_tile<OutT, B200_ACT_GELU_ERF>(t_row, p, crow, col_base, row_ok, row_mul);
-            break;
-          case B200_ACT_LEAKY_RELU:
-            epilogue_tile<OutT, B200_ACT_LEAKY_RELU>(t_row, p, crow, col_base, row_ok, row_mul);
-            break;
-          default:
-            epilogue_tile<OutT, B200_ACT_NONE>(t_row, p, crow, col_base, row_ok, row_mul);
-        }
-      }
+      run_epilogue<OutT, DUAL>(t_row, p, crow, row, col_base, row_ok, row_mul);
       // this warp has drained its quarter of the accumulator
       tc_fence_before_sync();
       __syncwarp();
@@ -613,10 +619,11 @@ constexpr int PAIR_B_STAGE_BYTES = 2 * B_BOX_BYTES;                      // 16 K
 constexpr int PAIR_STAGE_BYTES = A_STAGE_BYTES + PAIR_B_STAGE_BYTES;     // 32 KiB per CTA
 constexpr int PAIR_SMEM_BYTES = PAIR_STAGES * PAIR_STAGE_BYTES + 1024 + 256;
 
-template <typename OutT>
+template <typename OutT, bool DUAL>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
-                 const __grid_constant__ CUtensorMap tm_b, const Params p) {
+                 const __grid_constant__ CUtensorMap tm_b,
+                 const __grid_constant__ CUtensorMap tm_b2, const Params p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t *smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -637,8 +644,11 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
   const uint32_t rank = cluster_cta_rank();  // 0: issues the MMAs of the pair
   const WaitCtx ctx{abort_flag, p.status};
 
+  // DUAL: the even CTA holds the 128 columns of the first B operand, the odd CTA those of the
+  // second, so every accumulator row has x Wg in columns [0,128) and x Wu in [128,256)
+  constexpr int TILE_N = DUAL ? BN / 2 : BN;
   const int m_pairs = (p.M + 2 * BM - 1) / (2 * BM);
-  const int n_blocks = (p.N + BN - 1) / BN;
+  const int n_blocks = (p.N + TILE_N - 1) / TILE_N;
   const int num_tiles = m_pairs * n_blocks;
   const int num_kb = (p.K + BK - 1) / BK;
   const int first_tile = (int)(blockIdx.x >> 1);
@@ -660,7 +670,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
   }
   if (warp == 4 && lane == 0) {
     tma_prefetch_desc(&tm_a);
-    tma_prefetch_desc(&tm_b);
+    tma_prefetch_desc(DUAL && rank == 1 ? &tm_b2 : &tm_b);
   }
   if (warp == 5) tmem_alloc_pair(smem_u32(tmem_slot), TMEM_COLS);
   tc_fence_before_sync();
@@ -682,15 +692,16 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
         int mp, nb;
         tile_coords(tile, m_pairs, n_blocks, group_pairs, mp, nb);
         const int row0 = (mp * 2 + (int)rank) * BM;
-        const int col0 = nb * BN + (int)rank * (BN / 2);
+        const int col0 = DUAL ? nb * TILE_N : nb * BN + (int)rank * (BN / 2);
+        const CUtensorMap *bmap = (DUAL && rank == 1) ? &tm_b2 : &tm_b;
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1u, ctx, 1)) { ok = false; break; }
           if (rank == 0) mbar_arrive_expect_tx(full_bar(stage), 2 * PAIR_STAGE_BYTES);
           const uint32_t full0 = map_to_cta(full_bar(stage), 0);
           tma_load_2d_pair(a_smem + stage * A_STAGE_BYTES, &tm_a, full0, kb * BK, row0);
           const uint32_t bdst = b_smem + stage * PAIR_B_STAGE_BYTES;
-          tma_load_2d_pair(bdst, &tm_b, full0, col0, kb * BK);
-          tma_load_2d_pair(bdst + B_BOX_BYTES, &tm_b, full0, col0 + 64, kb * BK);
+          tma_load_2d_pair(bdst, bmap, full0, col0, kb * BK);
+          tma_load_2d_pair(bdst + B_BOX_BYTES, bmap, full0, col0 + 64, kb * BK);
           issued_mask |= 1u << stage;
           issued_parity = (issued_parity & ~(1u << stage)) | (phase << stage);
           if (++stage == PAIR_STAGES) { stage = 0; phase ^= 1u; }
@@ -778,21 +789,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
         crow = reinterpret_cast<OutT *>(p.c_rank[owner]) +
                ((int64_t)p.scatter_slot * p.scatter_rows + local) * p.ldc;
       }
-      const int col_base = nb * BN;
+      const int col_base = nb * TILE_N;
       const float row_mul = (p.row_scale != nullptr && row_ok) ? p.row_scale[row] : 1.0f;
-      switch (p.act) {
-        case B200_ACT_GELU_TANH:
-          epilogue_tile<OutT, B200_ACT_GELU_TANH>(t_row, p, crow, col_base, row_ok, row_mul);
-          break;
-        case B200_ACT_GELU_ERF:
-          epilogue_tile<OutT, B200_ACT_GELU_ERF>(t_row, p, crow, col_base, row_ok, row_mul);
-          break;
-        case B200_ACT_LEAKY_RELU:
-          epilogue_tile<OutT, B200_ACT_LEAKY_RELU>(t_row, p, crow, col_base, row_ok, row_mul);
-          break;
-        default:
-          epilogue_tile<OutT, B200_ACT_NONE>(t_row, p, crow, col_base, row_ok, row_mul);
-      }
+      run_epilogue<OutT, DUAL>(t_row, p, crow, row, col_base, row_ok, row_mul);
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(acc_empty0 + 8u * (uint32_t)acc);
@@ -928,14 +927,14 @@ static int launch_tc(const CUtensorMap &ta, const CUtensorMap &tb, const CUtenso
   return B200_OK;
 }
 
-template <typename OutT>
-static int launch_pair(const CUtensorMap &ta, const CUtensorMap &tb, const Params &p,
-                       cudaStream_t stream) {
+template <typename OutT, bool DUAL>
+static int launch_pair(const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap &tb2,
+                       const Params &p, cudaStream_t stream) {
   static bool configured[64] = {false};
   static int max_clusters[64] = {0};
   int dev = 0;
   B200_CUDA_OK(cudaGetDevice(&dev));
-  auto kernel = gemm_pair_kernel<OutT>;
+  auto kernel = gemm_pair_kernel<OutT, DUAL>;
   if (dev >= 64) return fail(B200_RESOURCE, "device index %d out of range", dev);
   if (!configured[dev]) {
     B200_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -957,9 +956,10 @@ static int launch_pair(const CUtensorMap &ta, const CUtensorMap &tb, const Param
     max_clusters[dev] = n > 0 ? n : sm_count() / 2;
     configured[dev] = true;
   }
-  const int tiles = ((p.M + 2 * BM - 1) / (2 * BM)) * ((p.N + BN - 1) / BN);
+  constexpr int TILE_N = DUAL ? BN / 2 : BN;
+  const int tiles = ((p.M + 2 * BM - 1) / (2 * BM)) * ((p.N + TILE_N - 1) / TILE_N);
   const int clusters = tiles < max_clusters[dev] ? tiles : max_clusters[dev];
-  kernel<<<2 * clusters, THREADS, PAIR_SMEM_BYTES, stream>>>(ta, tb, p);
+  kernel<<<2 * clusters, THREADS, PAIR_SMEM_BYTES, stream>>>(ta, tb, tb2, p);
   B200_CUDA_OK(cudaGetLastError());
   return B200_OK;
 }
@@ -1178,19 +1178,25 @@ static int gemm_impl(const b200_tensor *a, const b200_tensor *b, const b200_tens
 
   const bool dual = act == B200_ACT_SWIGLU;
   {
-    // CTA pairs (256 x 256 tiles) for B given as [K, N] with the plain epilogues, when there
-    // are enough pair tiles to fill the GPU; B200OPS_GEMM_PAIR=0 / 1 forces the choice.
+    // CTA pairs (256-row tiles) for B given as [K, N], when the pair tiles fill at least one
+    // wave of SM pairs; B200OPS_GEMM_PAIR=0 / 1 forces the choice.
     static const int pair_env =
         getenv("B200OPS_GEMM_PAIR") ? atoi(getenv("B200OPS_GEMM_PAIR")) : -1;
-    const int64_t pair_tiles = ((M + 2 * BM - 1) / (2 * BM)) * ((N + BN - 1) / BN);
-    const bool plain = !dual && !b_rows_are_n && act != kActLogSoftmax && act != kActGroupNormMin;
-    const bool use_pair = plain && (pair_env >= 0 ? pair_env != 0 : pair_tiles >= sm_count());
+    const int tile_n = dual ? BN / 2 : BN;
+    const int64_t pair_tiles = ((M + 2 * BM - 1) / (2 * BM)) * ((N + tile_n - 1) / tile_n);
+    const bool use_pair = !b_rows_are_n && act != kActLogSoftmax &&
+                          (pair_env >= 0 ? pair_env != 0 : pair_tiles >= sm_count() / 2);
     if (use_pair) {
       Params q = p;
       q.idesc = sm100::make_idesc_f16(2 * BM, BN, a->dtype == B200_DTYPE_BFLOAT16 ? 1 : 0, 0, 1);
-      if (c->dtype == B200_DTYPE_FLOAT32) return launch_pair<float>(ta, tb, q, s);
-      if (c->dtype == B200_DTYPE_FLOAT16) return launch_pair<__half>(ta, tb, q, s);
-      return launch_pair<__nv_bfloat16>(ta, tb, q, s);
+      if (c->dtype == B200_DTYPE_FLOAT32)
+        return dual ? launch_pair<float, true>(ta, tb, tb2, q, s)
+                    : launch_pair<float, false>(ta, tb, tb2, q, s);
+      if (c->dtype == B200_DTYPE_FLOAT16)
+        return dual ? launch_pair<__half, true>(ta, tb, tb2, q, s)
+                    : launch_pair<__half, false>(ta, tb, tb2, q, s);
+      return dual ? launch_pair<__nv_bfloat16, true>(ta, tb, tb2, q, s)
+                  : launch_pair<__nv_bfloat16, false>(ta, tb, tb2, q, s);
     }
   }
   if (c->dtype == B200_DTYPE_FLOAT32)
