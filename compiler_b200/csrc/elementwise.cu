@@ -3,6 +3,10 @@
 
 namespace b200 {
 
+// siblings.cu: the flat 16-byte-vector form, four vectors of each operand in flight per thread
+void swiglu_flat(uint32_t dtype, const void *x, const void *y, void *out, int64_t n,
+                 cudaStream_t s);
+
 // out = x * sigmoid(x) * y in fp32, one rounding at the store
 // (swiglu_fwd_kernel, ops/suite/perf/swiglu_fwd.py:27-36).
 template <typename T>
@@ -52,6 +56,12 @@ static int swiglu_dispatch(const b200_tensor *x, const b200_tensor *y, b200_tens
                        (out->stride[0] * sizeof(T)) % 16 == 0 &&
                        (uintptr_t)x->data % 16 == 0 && (uintptr_t)y->data % 16 == 0 &&
                        (uintptr_t)out->data % 16 == 0;
+  if (aligned && (rows == 1 || (x->stride[0] == cols && y->stride[0] == cols &&
+                                out->stride[0] == cols))) {
+    swiglu_flat(x->dtype, x->data, y->data, out->data, rows * cols, stream);
+    B200_CUDA_OK(cudaGetLastError());
+    return B200_OK;
+  }
   const int64_t items = aligned ? rows * (cols / N) : rows * cols;
   int64_t blocks = (items + 255) / 256;
   const int64_t cap = (int64_t)sm_count() * 16;

@@ -5,6 +5,10 @@
 
 namespace b200 {
 
+// softmax.cu: the register-resident row kernel in its mul / log forms
+bool softmax_variant_rows(const b200_tensor *x, const b200_tensor *mul, b200_tensor *y,
+                          int log_input, cudaStream_t stream);
+
 __device__ __forceinline__ float gelu_erf_f(float z) {
   return 0.5f * z * (1.0f + erff(z * 0.7071067811865476f));
 }
@@ -21,7 +25,7 @@ __device__ __forceinline__ float gelu_tanh_f(float z) {
 template <typename T, int OP>
 __global__ void __launch_bounds__(256)
 elementwise_kernel(const T *__restrict__ a, const T *__restrict__ b, T *__restrict__ out,
-                   int64_t n, int64_t n_cols, float p0, float p1, float p2) {
+                   int64_t n, int64_t n_cols, float p0, float p1, float p2, int64_t first) {
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
        i += (int64_t)gridDim.x * blockDim.x) {
     const float x = io<T>::load(a[i]);
@@ -33,7 +37,7 @@ elementwise_kernel(const T *__restrict__ a, const T *__restrict__ b, T *__restri
     } else if constexpr (OP == B200_EW_GEGLU_TANH) {
       y = gelu_tanh_f(x) * io<T>::load(b[i]);
     } else {
-      float z = (x + io<T>::load(b[i % n_cols])) * p0;
+      float z = (x + io<T>::load(b[(first + i) % n_cols])) * p0;
       z = fminf(fmaxf(z, p1), p2);
       y = gelu_erf_f(z);
     }
@@ -41,15 +45,128 @@ elementwise_kernel(const T *__restrict__ a, const T *__restrict__ b, T *__restri
   }
 }
 
+// erf for 16-bit results: Abramowitz-Stegun 7.1.26, |error| <= 1.5e-7 (a 16-bit result
+// carries 8 or 11 bits), one reciprocal and one ex2 instead of erff's polynomial pair.
+__device__ __forceinline__ float erf_short(float x) {
+  const float ax = fabsf(x);
+  const float t = __fdividef(1.0f, fmaf(0.3275911f, ax, 1.0f));
+  float poly = fmaf(1.061405429f, t, -1.453152027f);
+  poly = fmaf(poly, t, 1.421413741f);
+  poly = fmaf(poly, t, -0.284496736f);
+  poly = fmaf(poly, t, 0.254829592f);
+  const float y = 1.0f - poly * t * exp2f(-1.4426950408889634f * ax * ax);
+  return copysignf(y, x);
+}
+template <typename T> __device__ __forceinline__ float gelu_erf_t(float z) {
+  if constexpr (sizeof(T) == 4) return gelu_erf_f(z);
+  return 0.5f * z * (1.0f + erf_short(z * 0.7071067811865476f));
+}
+template <typename T> __device__ __forceinline__ float gelu_tanh_t(float z) {
+  if constexpr (sizeof(T) == 4) return gelu_tanh_f(z);
+  float t;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+  return 0.5f * z * (1.0f + t);
+}
+
+constexpr int kEwSwiglu = 100;  // internal: x * sigmoid(x) * b (b200_swiglu_fwd on contiguous rows)
+
+template <typename T, int OP> __device__ __forceinline__ float ew_apply(float x, float o, float p0,
+                                                                        float p1, float p2) {
+  if constexpr (OP == B200_EW_GELU_ERF) return gelu_erf_t<T>(x);
+  if constexpr (OP == B200_EW_ADD_GELU_ERF) return gelu_erf_t<T>(x + p0 * o);
+  if constexpr (OP == B200_EW_GEGLU_TANH) return gelu_tanh_t<T>(x) * o;
+  if constexpr (OP == kEwSwiglu) {
+    if constexpr (sizeof(T) == 4) return x / (1.0f + __expf(-x)) * o;
+    return __fdividef(x, 1.0f + __expf(-x)) * o;
+  }
+  const float z = fminf(fmaxf((x + o) * p0, p1), p2);
+  return gelu_erf_t<T>(z);
+}
+
+// The same operators on 16-byte vectors: every thread has U vectors of each operand in
+// flight before it starts on the arithmetic.  a, b, out 16-byte aligned; the bias of
+// BIAS_SCALE_CLAMP_GELU is n_cols long with n_cols a multiple of the vector length, so a
+// vector never wraps.  Elements past the last whole vector are left to the caller.
+template <typename T, int OP, int U>
+__global__ void __launch_bounds__(256)
+elementwise_vec_kernel(const T *__restrict__ a, const T *__restrict__ b, T *__restrict__ out,
+                       int64_t nvec, int64_t n_cols, float p0, float p1, float p2) {
+  constexpr int N = vec16<T>::N;
+  constexpr bool kHasB = OP != B200_EW_GELU_ERF;
+  constexpr bool kBias = OP == B200_EW_BIAS_SCALE_CLAMP_GELU;
+  const int64_t tile = 256 * U;
+  const bool narrow = nvec * N < ((int64_t)1 << 32);
+  for (int64_t base = (int64_t)blockIdx.x * tile; base < nvec; base += (int64_t)gridDim.x * tile) {
+    vec16<T> va[U], vb[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int64_t v = base + u * 256 + threadIdx.x;
+      if (v < nvec) {
+        va[u].raw = ld_stream16(a + v * N);
+        if constexpr (kBias) {
+          // 32-bit remainder when the range allows it: the 64-bit one costs more than the GELU
+          const int64_t col = narrow ? (int64_t)((uint32_t)(v * N) % (uint32_t)n_cols)
+                                     : (v * N) % n_cols;
+          vb[u].raw = __ldg(reinterpret_cast<const uint4 *>(b + col));
+        } else if constexpr (kHasB) {
+          vb[u].raw = ld_stream16(b + v * N);
+        }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int64_t v = base + u * 256 + threadIdx.x;
+      if (v < nvec) {
+        vec16<T> o;
+#pragma unroll
+        for (int j = 0; j < N; ++j)
+          o.e[j] = io<T>::store(ew_apply<T, OP>(io<T>::load(va[u].e[j]),
+                                                kHasB ? io<T>::load(vb[u].e[j]) : 0.f, p0, p1, p2));
+        st_stream16(out + v * N, o.raw);
+      }
+    }
+  }
+}
+
+template <typename T, int OP>
+static void launch_elementwise_op(const T *a, const T *b, T *out, int64_t n, int64_t n_cols,
+                                  float p0, float p1, float p2, cudaStream_t s) {
+  constexpr int N = vec16<T>::N;
+  constexpr int U = 4;
+  const bool vec_ok = (uintptr_t)a % 16 == 0 && (uintptr_t)out % 16 == 0 &&
+                      (b == nullptr || (uintptr_t)b % 16 == 0) &&
+                      (OP != B200_EW_BIAS_SCALE_CLAMP_GELU || n_cols % N == 0);
+  const int64_t nvec = vec_ok ? n / N : 0;
+  if (nvec > 0) {
+    int64_t blocks = (nvec + 256 * U - 1) / (256 * U);
+    const int64_t cap = (int64_t)sm_count() * 8;
+    if (blocks > cap) blocks = cap;
+    elementwise_vec_kernel<T, OP, U><<<(unsigned)blocks, 256, 0, s>>>(a, b, out, nvec, n_cols, p0,
+                                                                    p1, p2);
+  }
+  const int64_t done = nvec * N;
+  if (done < n) {
+    // the ragged end (or everything, for unaligned operands): scalar kernel
+    if constexpr (OP != kEwSwiglu) {
+      const int64_t rest = n - done;
+      int64_t blocks = (rest + 255) / 256;
+      const int64_t cap = (int64_t)sm_count() * 16;
+      if (blocks > cap) blocks = cap;
+      const T *bb = b;
+      if (OP != B200_EW_BIAS_SCALE_CLAMP_GELU && b != nullptr) bb = b + done;
+      // done is a multiple of n_cols' vector length, not of n_cols: the bias index of the
+      // scalar kernel is (done + i) % n_cols, which its `first` argument carries
+      elementwise_kernel<T, OP><<<(unsigned)blocks, 256, 0, s>>>(a + done, bb, out + done, rest,
+                                                                 n_cols, p0, p1, p2, done);
+    }
+  }
+}
+
 template <typename T>
 static int launch_elementwise(int op, const void *a, const void *b, void *out, int64_t n,
                               int64_t n_cols, float p0, float p1, float p2, cudaStream_t s) {
-  int64_t blocks = (n + 255) / 256;
-  const int64_t cap = (int64_t)sm_count() * 16;
-  if (blocks > cap) blocks = cap;
-#define B200_EW(OP)                                                                          \
-  elementwise_kernel<T, OP><<<(unsigned)blocks, 256, 0, s>>>((const T *)a, (const T *)b,     \
-                                                             (T *)out, n, n_cols, p0, p1, p2)
+#define B200_EW(OP) \
+  launch_elementwise_op<T, OP>((const T *)a, (const T *)b, (T *)out, n, n_cols, p0, p1, p2, s)
   switch (op) {
     case B200_EW_GELU_ERF: B200_EW(B200_EW_GELU_ERF); break;
     case B200_EW_ADD_GELU_ERF: B200_EW(B200_EW_ADD_GELU_ERF); break;
@@ -59,6 +176,22 @@ static int launch_elementwise(int op, const void *a, const void *b, void *out, i
 #undef B200_EW
   B200_CUDA_OK(cudaGetLastError());
   return B200_OK;
+}
+
+// x * sigmoid(x) * y over a flat contiguous range (elementwise.cu: b200_swiglu_fwd);
+// n must be a multiple of the 16-byte vector length and the pointers 16-byte aligned
+void swiglu_flat(uint32_t dtype, const void *x, const void *y, void *out, int64_t n,
+                 cudaStream_t s) {
+  if (dtype == B200_DTYPE_FLOAT32)
+    launch_elementwise_op<float, kEwSwiglu>((const float *)x, (const float *)y, (float *)out, n, 1,
+                                            0.f, 0.f, 0.f, s);
+  else if (dtype == B200_DTYPE_FLOAT16)
+    launch_elementwise_op<__half, kEwSwiglu>((const __half *)x, (const __half *)y, (__half *)out,
+                                             n, 1, 0.f, 0.f, 0.f, s);
+  else
+    launch_elementwise_op<__nv_bfloat16, kEwSwiglu>((const __nv_bfloat16 *)x,
+                                                    (const __nv_bfloat16 *)y,
+                                                    (__nv_bfloat16 *)out, n, 1, 0.f, 0.f, 0.f, s);
 }
 
 // Row softmax variants, one CTA per row, scalar passes (rows re-read from L2):
@@ -122,6 +255,62 @@ repeat_log_softmax_kernel(const T *__restrict__ x, T *__restrict__ y, int cols, 
     yrow[p] = io<T>::store(io<T>::load(xrow[p / repeat]) - lse);
 }
 
+// The same with 16-byte loads and stores: the input row is read twice (the second time from
+// L1 / L2) and every output vector is assembled from the one or two inputs it repeats.
+// x rows and y rows 16-byte aligned, cols and length multiples of the vector length.
+template <typename T>
+__global__ void __launch_bounds__(kRowThreads)
+repeat_log_softmax_vec_kernel(const T *__restrict__ x, T *__restrict__ y, int cols, int repeat,
+                              int length) {
+  constexpr int N = vec16<T>::N;
+  __shared__ float scratch[2 * (kRowThreads / 32)];
+  const int64_t row = blockIdx.x;
+  const T *xrow = x + row * (int64_t)cols;
+  T *yrow = y + row * (int64_t)length;
+  const int used = (length + repeat - 1) / repeat;  // inputs that reach the output
+  const int in_vec = (used + N - 1) / N;
+  float m = -INFINITY;
+  for (int v = threadIdx.x; v < in_vec; v += kRowThreads) {
+    vec16<T> a;
+    a.raw = __ldg(reinterpret_cast<const uint4 *>(xrow) + v);
+#pragma unroll
+    for (int j = 0; j < N; ++j)
+      if (v * N + j < used) m = fmaxf(m, io<T>::load(a.e[j]));
+  }
+  m = group_reduce<kRowThreads, MaxOp>(m, scratch, 0);
+  float s = 0.f;
+  for (int v = threadIdx.x; v < in_vec; v += kRowThreads) {
+    vec16<T> a;
+    a.raw = __ldg(reinterpret_cast<const uint4 *>(xrow) + v);
+#pragma unroll
+    for (int j = 0; j < N; ++j) {
+      const int c = v * N + j;
+      // input c is repeated `repeat` times, the last used one possibly fewer
+      const int count = min(repeat, length - c * repeat);
+      if (c < used) s += (float)count * expf(io<T>::load(a.e[j]) - m);
+    }
+  }
+  s = group_reduce<kRowThreads, SumOp>(s, scratch, 1);
+  const float lse = m + logf(s);
+  const int out_vec = length / N;
+  for (int v = threadIdx.x; v < out_vec; v += kRowThreads) {
+    int c = (v * N) / repeat;
+    int rem = (v * N) - c * repeat;
+    float cur = io<T>::load(xrow[c]) - lse;
+    vec16<T> o;
+#pragma unroll
+    for (int j = 0; j < N; ++j) {
+      o.e[j] = io<T>::store(cur);
+      if (++rem == repeat) {
+        rem = 0;
+        ++c;
+        if (j + 1 < N && c < cols) cur = io<T>::load(xrow[c]) - lse;
+      }
+    }
+    st_stream16(yrow + (int64_t)v * N, o.raw);
+  }
+}
+
 }  // namespace b200
 
 using namespace b200;
@@ -180,6 +369,10 @@ extern "C" int b200_softmax_variant(const b200_tensor *x, const b200_tensor *mul
   B200_REQUIRE(cols > 0 && cols < (1 << 30) && rows < (1LL << 31), "extent out of range");
   if (rows == 0) return B200_OK;
   cudaStream_t s = (cudaStream_t)stream;
+  if (softmax_variant_rows(x, mul, y, log_input, s)) {
+    B200_CUDA_OK(cudaGetLastError());
+    return B200_OK;
+  }
 #define B200_SV(T)                                                                         \
   softmax_variant_kernel<T><<<(unsigned)rows, kRowThreads, 0, s>>>(                        \
       (const T *)x->data, mul ? (const T *)mul->data : nullptr, (T *)y->data, (int)cols,   \
@@ -207,9 +400,19 @@ extern "C" int b200_repeat_log_softmax(const b200_tensor *x, b200_tensor *y, int
   B200_REQUIRE(cols < (1 << 30) && length < (1 << 30) && rows < (1LL << 31), "extent out of range");
   if (rows == 0) return B200_OK;
   cudaStream_t s = (cudaStream_t)stream;
-#define B200_RL(T)                                                                  \
-  repeat_log_softmax_kernel<T><<<(unsigned)rows, kRowThreads, 0, s>>>(              \
-      (const T *)x->data, (T *)y->data, (int)cols, repeat, (int)length)
+  const size_t es = dtype_size(x->dtype);
+  const int64_t per_vec = 16 / (int64_t)es;
+  const bool vec_ok = (uintptr_t)x->data % 16 == 0 && (uintptr_t)y->data % 16 == 0 &&
+                      cols % per_vec == 0 && length % per_vec == 0;
+#define B200_RL(T)                                                                      \
+  do {                                                                                  \
+    if (vec_ok)                                                                         \
+      repeat_log_softmax_vec_kernel<T><<<(unsigned)rows, kRowThreads, 0, s>>>(          \
+          (const T *)x->data, (T *)y->data, (int)cols, repeat, (int)length);            \
+    else                                                                                \
+      repeat_log_softmax_kernel<T><<<(unsigned)rows, kRowThreads, 0, s>>>(              \
+          (const T *)x->data, (T *)y->data, (int)cols, repeat, (int)length);            \
+  } while (0)
   if (x->dtype == B200_DTYPE_FLOAT32) B200_RL(float);
   else if (x->dtype == B200_DTYPE_FLOAT16) B200_RL(__half);
   else B200_RL(__nv_bfloat16);
@@ -223,6 +426,42 @@ extern "C" int b200_repeat_log_softmax(const b200_tensor *x, b200_tensor *y, int
 // consecutive columns (one 16-byte load of int8, 16-byte stores) when the rows allow it.
 namespace b200 {
 namespace {
+
+// The aligned case: a thread owns 16 consecutive columns, keeps their 16 scales in registers
+// and walks down the rows (blockIdx.y strides over them, four rows in flight), so there is no
+// index division and the scales are read once per thread.
+template <typename T>
+__global__ void __launch_bounds__(256)
+dequantize_cols_kernel(const int8_t *__restrict__ b, int64_t ldb, const T *__restrict__ scale,
+                       T *__restrict__ out, int64_t ldo, int K, int groups) {
+  constexpr int PER = 16 / (int)sizeof(T);
+  constexpr int R = 4;
+  const int g = blockIdx.x * 256 + threadIdx.x;
+  if (g >= groups) return;
+  const int n0 = g * 16;
+  float sc[16];
+#pragma unroll
+  for (int j = 0; j < 16; ++j) sc[j] = io<T>::load(scale[n0 + j]);
+  for (int k0 = blockIdx.y * R; k0 < K; k0 += gridDim.y * R) {
+    uint4 raw[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+      if (k0 + r < K) raw[r] = ld_stream16(b + (int64_t)(k0 + r) * ldb + n0);
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      if (k0 + r >= K) break;
+      const int8_t *q = reinterpret_cast<const int8_t *>(&raw[r]);
+      T *dst = out + (int64_t)(k0 + r) * ldo + n0;
+#pragma unroll
+      for (int v = 0; v < 16 / PER; ++v) {
+        vec16<T> o;
+#pragma unroll
+        for (int j = 0; j < PER; ++j) o.e[j] = io<T>::store((float)q[v * PER + j] * sc[v * PER + j]);
+        st_stream16(dst + v * PER, o.raw);
+      }
+    }
+  }
+}
 
 template <typename T>
 __global__ void __launch_bounds__(256)
@@ -281,10 +520,23 @@ extern "C" int b200_dequantize_cols(const b200_tensor *b, const b200_tensor *sca
   const int64_t cap = (int64_t)sm_count() * 16;
   if (blocks > cap) blocks = cap;
   cudaStream_t s = (cudaStream_t)stream;
+  const bool by_columns = vector_ok && N % 16 == 0;  // N > 0 here, so at least one group
+  const int groups = (int)(N / 16);
+  const unsigned gx = by_columns ? (unsigned)((groups + 255) / 256) : 1u;
+  int64_t gy = ((int64_t)sm_count() * 8 + gx - 1) / gx;
+  if (gy > (K + 3) / 4) gy = (K + 3) / 4;
+  if (gy > 65535) gy = 65535;
 #define B200_DQ(T)                                                                              \
-  dequantize_kernel<T><<<(unsigned)blocks, 256, 0, s>>>((const int8_t *)b->data, b->stride[0],  \
-                                                        (const T *)scale->data, (T *)out->data, \
-                                                        out->stride[0], (int)K, (int)N, vector_ok)
+  do {                                                                                          \
+    if (by_columns)                                                                             \
+      dequantize_cols_kernel<T><<<dim3(gx, (unsigned)gy), 256, 0, s>>>(                         \
+          (const int8_t *)b->data, b->stride[0], (const T *)scale->data, (T *)out->data,        \
+          out->stride[0], (int)K, groups);                                                      \
+    else                                                                                        \
+      dequantize_kernel<T><<<(unsigned)blocks, 256, 0, s>>>(                                    \
+          (const int8_t *)b->data, b->stride[0], (const T *)scale->data, (T *)out->data,        \
+          out->stride[0], (int)K, (int)N, vector_ok);                                           \
+  } while (0)
   if (out->dtype == B200_DTYPE_FLOAT32) B200_DQ(float);
   else if (out->dtype == B200_DTYPE_FLOAT16) B200_DQ(__half);
   else B200_DQ(__nv_bfloat16);

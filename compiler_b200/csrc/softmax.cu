@@ -7,9 +7,11 @@
 // (ops/suite/perf/attn_fwd_causal.py:46-47): they add 0 to the sum and are
 // written as 0.  Column 0 is always kept, so no row is fully masked.
 //
-// HBM-bound: the row stays in registers between max, sum and the store; the
-// masked part of a row is never loaded (its output is a constant 0), so the
-// DRAM read traffic is below the algorithmic 2 B/element of an fp16 read.
+// HBM-bound: the row stays in registers between max, sum and the store (the
+// exponentials are computed once, in fp32); the masked part of a row is never
+// loaded (its output is a constant 0), so the DRAM read traffic is below the
+// algorithmic 2 B/element of an fp16 read.  The same kernel serves the variants
+// softmax(x) * mul and softmax(log x) of the reference's corpus.
 #include "rowwise.cuh"
 
 namespace b200 {
@@ -40,18 +42,25 @@ template <> struct RowVec<float> {
     const float *e = reinterpret_cast<const float *>(&raw);
     return fmaxf(fmaxf(e[0], e[1]), fmaxf(e[2], e[3]));
   }
-  // sum of exp(x[j] - m)
-  static __device__ __forceinline__ float expsum(const uint4 &raw, float m, float) {
-    const float *e = reinterpret_cast<const float *>(&raw);
-    return (expf(e[0] - m) + expf(e[1] - m)) + (expf(e[2] - m) + expf(e[3] - m));
+  // e[j] = exp(x[j] - m) (log_input: x[j] holds log x already); returns their sum
+  static __device__ __forceinline__ float exps(const uint4 &raw, float m, float, float (&e)[N]) {
+    const float *x = reinterpret_cast<const float *>(&raw);
+#pragma unroll
+    for (int j = 0; j < N; ++j) e[j] = expf(x[j] - m);
+    return (e[0] + e[1]) + (e[2] + e[3]);
   }
-  // exp(x[j] - m) * r in the storage type
-  static __device__ __forceinline__ uint4 scaled(const uint4 &raw, float m, float, float r) {
-    const float *e = reinterpret_cast<const float *>(&raw);
+  static __device__ __forceinline__ void unpack(const uint4 &raw, float (&f)[N]) {
+    const float *x = reinterpret_cast<const float *>(&raw);
+#pragma unroll
+    for (int j = 0; j < N; ++j) f[j] = x[j];
+  }
+  // e[j] * r (* mul[j]) in the storage type
+  static __device__ __forceinline__ uint4 scaled(const float (&e)[N], float r, const uint4 *mul) {
     uint4 out;
     float *o = reinterpret_cast<float *>(&out);
+    const float *w = reinterpret_cast<const float *>(mul);
 #pragma unroll
-    for (int j = 0; j < N; ++j) o[j] = expf(e[j] - m) * r;
+    for (int j = 0; j < N; ++j) o[j] = mul ? e[j] * r * w[j] : e[j] * r;
     return out;
   }
 };
@@ -72,54 +81,82 @@ template <typename T2, typename T1> struct RowVec16 {
     const T2 a = __hmax2(__hmax2(p[0], p[1]), __hmax2(p[2], p[3]));
     return fmaxf(io<T1>::load(a.x), io<T1>::load(a.y));
   }
-  static __device__ __forceinline__ float e2(T1 x, float neg_m_log2e) {
-    return ex2_approx(fmaf(io<T1>::load(x), 1.4426950408889634f, neg_m_log2e));
-  }
-  static __device__ __forceinline__ float expsum(const uint4 &raw, float, float neg_m_log2e) {
-    const T1 *e = reinterpret_cast<const T1 *>(&raw);
+  // e[j] = 2^(x[j] * log2e - m * log2e): one FFMA + one ex2 per element; returns their sum
+  static __device__ __forceinline__ float exps(const uint4 &raw, float, float neg_m_log2e,
+                                               float (&e)[N]) {
+    const T1 *x = reinterpret_cast<const T1 *>(&raw);
     float s0 = 0.f, s1 = 0.f;
 #pragma unroll
     for (int j = 0; j < N; j += 2) {
-      s0 += e2(e[j], neg_m_log2e);
-      s1 += e2(e[j + 1], neg_m_log2e);
+      e[j] = ex2_approx(fmaf(io<T1>::load(x[j]), 1.4426950408889634f, neg_m_log2e));
+      e[j + 1] = ex2_approx(fmaf(io<T1>::load(x[j + 1]), 1.4426950408889634f, neg_m_log2e));
+      s0 += e[j];
+      s1 += e[j + 1];
     }
     return s0 + s1;
   }
+  static __device__ __forceinline__ void unpack(const uint4 &raw, float (&f)[N]) {
+    const T1 *x = reinterpret_cast<const T1 *>(&raw);
+#pragma unroll
+    for (int j = 0; j < N; ++j) f[j] = io<T1>::load(x[j]);
+  }
 };
-// The exponentials are recomputed for the store instead of being kept: 16 registers
-// of packed inputs per thread instead of 32 of fp32 results, which is what lets 8 CTAs
-// share an SM; the extra ex2 work rides on an otherwise idle pipe.
+// The exponentials are computed once, in fp32, and kept for the store: the packed inputs
+// are dead after that pass, so a thread holds 32 fp32 results instead of 16 packed words.
 template <> struct RowVec<__half> : RowVec16<__half2, __half> {
-  static __device__ __forceinline__ uint4 scaled(const uint4 &raw, float, float neg_m_log2e,
-                                                 float r) {
-    const __half *e = reinterpret_cast<const __half *>(&raw);
+  static __device__ __forceinline__ uint4 scaled(const float (&e)[8], float r, const uint4 *mul) {
     uint4 out;
     __half2 *o = reinterpret_cast<__half2 *>(&out);
+    const __half2 *w = reinterpret_cast<const __half2 *>(mul);
 #pragma unroll
-    for (int j = 0; j < 4; ++j)
-      o[j] = __floats2half2_rn(e2(e[2 * j], neg_m_log2e) * r, e2(e[2 * j + 1], neg_m_log2e) * r);
+    for (int j = 0; j < 4; ++j) {
+      float a = e[2 * j] * r, b = e[2 * j + 1] * r;
+      if (mul) {
+        a *= __low2float(w[j]);
+        b *= __high2float(w[j]);
+      }
+      o[j] = __floats2half2_rn(a, b);
+    }
     return out;
   }
 };
 template <> struct RowVec<__nv_bfloat16> : RowVec16<__nv_bfloat162, __nv_bfloat16> {
-  static __device__ __forceinline__ uint4 scaled(const uint4 &raw, float, float neg_m_log2e,
-                                                 float r) {
-    const __nv_bfloat16 *e = reinterpret_cast<const __nv_bfloat16 *>(&raw);
+  static __device__ __forceinline__ uint4 scaled(const float (&e)[8], float r, const uint4 *mul) {
     uint4 out;
     __nv_bfloat162 *o = reinterpret_cast<__nv_bfloat162 *>(&out);
+    const __nv_bfloat162 *w = reinterpret_cast<const __nv_bfloat162 *>(mul);
 #pragma unroll
-    for (int j = 0; j < 4; ++j)
-      o[j] = __floats2bfloat162_rn(e2(e[2 * j], neg_m_log2e) * r,
-                                   e2(e[2 * j + 1], neg_m_log2e) * r);
+    for (int j = 0; j < 4; ++j) {
+      float a = e[2 * j] * r, b = e[2 * j + 1] * r;
+      if (mul) {
+        a *= __low2float(w[j]);
+        b *= __high2float(w[j]);
+      }
+      o[j] = __floats2bfloat162_rn(a, b);
+    }
     return out;
   }
 };
 
-template <typename T, int G, int VPT>
+// MODE: the plain (optionally masked) softmax, softmax(x) * mul, or softmax(log x).
+constexpr int kSoftmaxPlain = 0, kSoftmaxMul = 1, kSoftmaxLog = 2;
+
+// softmax(log x) needs no logarithm: log is monotone, so max(log x) = log(max x) and
+// exp(log x - log max) = x / max.  What the logarithm adds is its domain: a negative or NaN
+// input makes log x NaN and, through the row maximum, the whole row NaN
+// (ops/suite/perf/softmax_log.py:27-31); all-zero and infinite rows come out NaN by the
+// arithmetic itself (0 / 0, inf / inf), as they do in the reference.
+//
+// KEEP: the exponentials are computed once, in fp32, and kept for the store (32 registers of
+// results per thread for 16-bit rows, four CTAs of 256 threads per SM).  Without it they are
+// recomputed for the store from the 16 registers of packed inputs, which lets eight CTAs share
+// an SM: the choice for masked rows, where half of the row on average is never loaded or
+// exponentiated and the kernel lives on the loads in flight.
+template <typename T, int G, int VPT, int MODE, bool KEEP>
 __global__ void __launch_bounds__((G > kRowThreads ? G : kRowThreads),
-                                  (G > kRowThreads ? 1 : 8))
-softmax_rows_kernel(const T *__restrict__ x, T *__restrict__ y, int64_t rows,
-                    int cols, int mask_kind, int64_t row_offset) {
+                                  (G > kRowThreads ? 1 : (KEEP ? 4 : 8)))
+softmax_rows_kernel(const T *__restrict__ x, const T *__restrict__ mul, T *__restrict__ y,
+                    int64_t rows, int cols, int mask_kind, int64_t row_offset) {
   constexpr int kThreads = G > kRowThreads ? G : kRowThreads;
   constexpr int kRowsPerCta = kThreads / G;
   using V = RowVec<T>;
@@ -133,24 +170,39 @@ softmax_rows_kernel(const T *__restrict__ x, T *__restrict__ y, int64_t rows,
   // kept columns of this row: [0, keep); vectors [0, full_vec) are kept whole,
   // vector full_vec (if keep % N != 0) partly, everything after is masked
   int keep = cols;
-  if (mask_kind == B200_MASK_CAUSAL_MOD && row_ok)
+  if (MODE == kSoftmaxPlain && mask_kind == B200_MASK_CAUSAL_MOD && row_ok)
     keep = (int)((row_offset + row) % cols) + 1;
   const int full_vec = keep / N;
   const int kept_vec = row_ok ? (keep + N - 1) / N : 0;
 
-  // the kept part of the row is loaded once and stays in registers; the masked
-  // part is never loaded and costs no arithmetic
+  // the kept part of the row is loaded once; the masked part is never loaded and costs
+  // no arithmetic
+  static_assert(KEEP || MODE == kSoftmaxPlain, "the variants keep their exponentials");
   uint4 raw[VPT];
+  float e[KEEP ? VPT : 1][N];
   float m = -INFINITY;
+  bool bad = false;
   const T *xrow = x + row * (int64_t)cols;
 #pragma unroll
   for (int i = 0; i < VPT; ++i) {
     const int v = lane + i * G;
     if (v < kept_vec) {
       raw[i] = ld_stream16(xrow + (int64_t)v * N);
-      if (v >= full_vec) V::mask_tail(raw[i], keep - v * N);
-      m = fmaxf(m, V::vmax(raw[i]));
+      if constexpr (MODE == kSoftmaxLog) {
+        V::unpack(raw[i], e[i]);
+#pragma unroll
+        for (int j = 0; j < N; ++j) {
+          bad = bad || !(e[i][j] >= 0.f);
+          m = fmaxf(m, e[i][j]);
+        }
+      } else {
+        if (v >= full_vec) V::mask_tail(raw[i], keep - v * N);
+        m = fmaxf(m, V::vmax(raw[i]));
+      }
     }
+  }
+  if constexpr (MODE == kSoftmaxLog) {
+    if (bad) m = INFINITY;  // poisons the row below: x * (1 / inf) sums to 0, 0 * inf = NaN
   }
   m = group_reduce<G, MaxOp>(m, scratch, 0);
   const float neg_m_log2e = -m * 1.4426950408889634f;
@@ -158,19 +210,158 @@ softmax_rows_kernel(const T *__restrict__ x, T *__restrict__ y, int64_t rows,
 #pragma unroll
   for (int i = 0; i < VPT; ++i) {
     const int v = lane + i * G;
-    if (v < kept_vec) s += V::expsum(raw[i], m, neg_m_log2e);
+    if (v < kept_vec) {
+      if constexpr (MODE == kSoftmaxLog) {
+#pragma unroll
+        for (int j = 0; j < N; ++j) {
+          e[i][j] = sizeof(T) == 4 ? e[i][j] / m : e[i][j] * (1.0f / m);
+          s += e[i][j];
+        }
+      } else {
+        s += V::exps(raw[i], m, neg_m_log2e, e[KEEP ? i : 0]);
+      }
+    }
   }
   s = group_reduce<G, SumOp>(s, scratch, 1);
-  const float r = 1.0f / s;
+  float r = 1.0f / s;
+  if constexpr (MODE == kSoftmaxLog) {
+    if (m == INFINITY) r = __int_as_float(0x7fc00000);  // a NaN, negative or infinite input
+  }
 
   T *yrow = y + row * (int64_t)cols;
+  if constexpr (MODE == kSoftmaxMul) {
+    const T *mrow = mul + row * (int64_t)cols;
+    uint4 w[VPT];
 #pragma unroll
-  for (int i = 0; i < VPT; ++i) {
-    const int v = lane + i * G;
-    if (row_ok && v < nvec) {
-      const uint4 out =
-          v < kept_vec ? V::scaled(raw[i], m, neg_m_log2e, r) : make_uint4(0u, 0u, 0u, 0u);
-      st_stream16(yrow + (int64_t)v * N, out);
+    for (int i = 0; i < VPT; ++i) {
+      const int v = lane + i * G;
+      if (v < kept_vec) w[i] = ld_stream16(mrow + (int64_t)v * N);
+    }
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int v = lane + i * G;
+      if (v < kept_vec) st_stream16(yrow + (int64_t)v * N, V::scaled(e[i], r, &w[i]));
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int v = lane + i * G;
+      if (row_ok && v < nvec) {
+        uint4 out = make_uint4(0u, 0u, 0u, 0u);
+        if (v < kept_vec) {
+          if constexpr (!KEEP) V::exps(raw[i], m, neg_m_log2e, e[0]);
+          out = V::scaled(e[KEEP ? i : 0], r, nullptr);
+        }
+        st_stream16(yrow + (int64_t)v * N, out);
+      }
+    }
+  }
+}
+
+// The unmasked forms for many rows: a persistent CTA walks down the rows and has the
+// next row's vectors in flight while it reduces, exponentiates and stores the current one, so
+// the load latency is hidden by the arithmetic of the row before instead of by other CTAs.
+// Three CTAs of 256 threads per SM (the two rows in flight per thread take about 80 registers),
+// two for the form with the multiplier, which also holds that row's vectors.
+constexpr int stream_ctas_per_sm(int mode) { return mode == kSoftmaxMul ? 2 : 3; }
+
+template <typename T, int G, int VPT, int MODE>
+__global__ void __launch_bounds__(kRowThreads, stream_ctas_per_sm(MODE))
+softmax_stream_kernel(const T *__restrict__ x, const T *__restrict__ mul, T *__restrict__ y,
+                      int64_t rows, int cols) {
+  static_assert(G <= kRowThreads, "one row per group of at most a CTA");
+  constexpr int kRowsPerCta = kRowThreads / G;
+  using V = RowVec<T>;
+  constexpr int N = V::N;
+  __shared__ float scratch[2 * (kRowThreads / 32)];
+
+  const int lane = threadIdx.x % G;
+  const int nvec = cols / N;
+  const int64_t stride = (int64_t)gridDim.x * kRowsPerCta;
+  int64_t row = (int64_t)blockIdx.x * kRowsPerCta + threadIdx.x / G;
+
+  uint4 next[VPT];
+  if (row < rows) {
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int v = lane + i * G;
+      if (v < nvec) next[i] = ld_stream16(x + row * (int64_t)cols + (int64_t)v * N);
+    }
+  }
+  for (; row < rows; row += stride) {
+    uint4 raw[VPT];
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) raw[i] = next[i];
+    if (row + stride < rows) {
+      const T *ahead = x + (row + stride) * (int64_t)cols;
+#pragma unroll
+      for (int i = 0; i < VPT; ++i) {
+        const int v = lane + i * G;
+        if (v < nvec) next[i] = ld_stream16(ahead + (int64_t)v * N);
+      }
+    }
+    uint4 w[MODE == kSoftmaxMul ? VPT : 1];
+    if constexpr (MODE == kSoftmaxMul) {
+      const T *mrow = mul + row * (int64_t)cols;
+#pragma unroll
+      for (int i = 0; i < VPT; ++i) {
+        const int v = lane + i * G;
+        if (v < nvec) w[i] = ld_stream16(mrow + (int64_t)v * N);
+      }
+    }
+
+    float e[VPT][N];
+    float m = -INFINITY;
+    bool bad = false;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int v = lane + i * G;
+      if (v < nvec) {
+        if constexpr (MODE == kSoftmaxLog) {
+          V::unpack(raw[i], e[i]);
+#pragma unroll
+          for (int j = 0; j < N; ++j) {
+            bad = bad || !(e[i][j] >= 0.f);
+            m = fmaxf(m, e[i][j]);
+          }
+        } else {
+          m = fmaxf(m, V::vmax(raw[i]));
+        }
+      }
+    }
+    if constexpr (MODE == kSoftmaxLog) {
+      if (bad) m = INFINITY;
+    }
+    m = group_reduce<G, MaxOp>(m, scratch, 0);
+    const float neg_m_log2e = -m * 1.4426950408889634f;
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int v = lane + i * G;
+      if (v < nvec) {
+        if constexpr (MODE == kSoftmaxLog) {
+#pragma unroll
+          for (int j = 0; j < N; ++j) {
+            e[i][j] = sizeof(T) == 4 ? e[i][j] / m : e[i][j] * (1.0f / m);
+            s += e[i][j];
+          }
+        } else {
+          s += V::exps(raw[i], m, neg_m_log2e, e[i]);
+        }
+      }
+    }
+    s = group_reduce<G, SumOp>(s, scratch, 1);
+    float r = 1.0f / s;
+    if constexpr (MODE == kSoftmaxLog) {
+      if (m == INFINITY) r = __int_as_float(0x7fc00000);
+    }
+    T *yrow = y + row * (int64_t)cols;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int v = lane + i * G;
+      if (v < nvec)
+        st_stream16(yrow + (int64_t)v * N,
+                    V::scaled(e[i], r, MODE == kSoftmaxMul ? &w[MODE == kSoftmaxMul ? i : 0] : nullptr));
     }
   }
 }
@@ -199,41 +390,86 @@ softmax_loop_kernel(const T *__restrict__ x, T *__restrict__ y, int cols,
     yrow[c] = io<T>::store(c < keep ? fast_exp<T>(io<T>::load(xrow[c]) - m) * r : 0.f);
 }
 
-template <typename T, int G, int VPT>
-static void launch_rows(const b200_tensor *x, b200_tensor *y, int mask_kind,
-                        int64_t row_offset, cudaStream_t stream) {
+template <typename T, int G, int VPT, int MODE, bool KEEP>
+static void launch_rows(const b200_tensor *x, const b200_tensor *mul, b200_tensor *y,
+                        int mask_kind, int64_t row_offset, cudaStream_t stream) {
   constexpr int kThreads = G > kRowThreads ? G : kRowThreads;
   constexpr int kRowsPerCta = kThreads / G;
   const int64_t rows = x->shape[0];
   const unsigned grid = (unsigned)((rows + kRowsPerCta - 1) / kRowsPerCta);
-  softmax_rows_kernel<T, G, VPT><<<grid, kThreads, 0, stream>>>(
-      (const T *)x->data, (T *)y->data, rows, (int)x->shape[1], mask_kind, row_offset);
+  if constexpr (G <= kRowThreads) {
+    // unmasked rows, more than one wave of resident CTAs: the pipelined persistent form
+    // (B200OPS_SOFTMAX_STREAM=0 keeps the one-row-per-group kernel).  Masked rows stay with
+    // the one-row-per-group kernel: their cost is the stores, rows differ in length, and
+    // eight small CTAs per SM measured faster there (39.0 against 47.6 us at 16384 x 4000).
+    static const bool allow =
+        !(getenv("B200OPS_SOFTMAX_STREAM") && atoi(getenv("B200OPS_SOFTMAX_STREAM")) == 0);
+    const unsigned resident = (unsigned)(sm_count() * stream_ctas_per_sm(MODE));
+    if (allow && mask_kind == B200_MASK_NONE && grid > resident) {
+      softmax_stream_kernel<T, G, VPT, MODE><<<resident, kRowThreads, 0, stream>>>(
+          (const T *)x->data, mul ? (const T *)mul->data : nullptr, (T *)y->data, rows,
+          (int)x->shape[1]);
+      return;
+    }
+  }
+  softmax_rows_kernel<T, G, VPT, MODE, KEEP><<<grid, kThreads, 0, stream>>>(
+      (const T *)x->data, mul ? (const T *)mul->data : nullptr, (T *)y->data, rows,
+      (int)x->shape[1], mask_kind, row_offset);
+}
+
+// true when the register-resident kernel took the row shape; false: the caller runs its
+// looping kernel
+template <typename T, int MODE, bool KEEP>
+static bool dispatch_rows(const b200_tensor *x, const b200_tensor *mul, b200_tensor *y,
+                          int mask_kind, int64_t row_offset, cudaStream_t stream) {
+  constexpr int N = vec16<T>::N;
+  constexpr int VPT = 4;
+  const int64_t cols = x->shape[1];
+  const bool aligned = cols % N == 0 && ((uintptr_t)x->data % 16) == 0 &&
+                       ((uintptr_t)y->data % 16) == 0 &&
+                       (mul == nullptr || ((uintptr_t)mul->data % 16) == 0);
+  const int g = aligned ? pick_group(cols / N, VPT) : 0;
+  switch (g) {
+    case 8: launch_rows<T, 8, VPT, MODE, KEEP>(x, mul, y, mask_kind, row_offset, stream); break;
+    case 16: launch_rows<T, 16, VPT, MODE, KEEP>(x, mul, y, mask_kind, row_offset, stream); break;
+    case 32: launch_rows<T, 32, VPT, MODE, KEEP>(x, mul, y, mask_kind, row_offset, stream); break;
+    case 64: launch_rows<T, 64, VPT, MODE, KEEP>(x, mul, y, mask_kind, row_offset, stream); break;
+    case 128: launch_rows<T, 128, VPT, MODE, KEEP>(x, mul, y, mask_kind, row_offset, stream); break;
+    case 256: launch_rows<T, 256, VPT, MODE, KEEP>(x, mul, y, mask_kind, row_offset, stream); break;
+    case 512: launch_rows<T, 512, VPT, MODE, KEEP>(x, mul, y, mask_kind, row_offset, stream); break;
+    case 1024: launch_rows<T, 1024, VPT, MODE, KEEP>(x, mul, y, mask_kind, row_offset, stream); break;
+    default: return false;
+  }
+  return true;
 }
 
 template <typename T>
 static int dispatch(const b200_tensor *x, b200_tensor *y, int mask_kind,
                     int64_t row_offset, cudaStream_t stream) {
-  constexpr int N = vec16<T>::N;
-  constexpr int VPT = 4;
-  const int64_t rows = x->shape[0], cols = x->shape[1];
-  const bool aligned = cols % N == 0 && ((uintptr_t)x->data % 16) == 0 &&
-                       ((uintptr_t)y->data % 16) == 0;
-  const int g = aligned ? pick_group(cols / N, VPT) : 0;
-  switch (g) {
-    case 8: launch_rows<T, 8, VPT>(x, y, mask_kind, row_offset, stream); break;
-    case 16: launch_rows<T, 16, VPT>(x, y, mask_kind, row_offset, stream); break;
-    case 32: launch_rows<T, 32, VPT>(x, y, mask_kind, row_offset, stream); break;
-    case 64: launch_rows<T, 64, VPT>(x, y, mask_kind, row_offset, stream); break;
-    case 128: launch_rows<T, 128, VPT>(x, y, mask_kind, row_offset, stream); break;
-    case 256: launch_rows<T, 256, VPT>(x, y, mask_kind, row_offset, stream); break;
-    case 512: launch_rows<T, 512, VPT>(x, y, mask_kind, row_offset, stream); break;
-    case 1024: launch_rows<T, 1024, VPT>(x, y, mask_kind, row_offset, stream); break;
-    default:
-      softmax_loop_kernel<T><<<(unsigned)rows, kRowThreads, 0, stream>>>(
-          (const T *)x->data, (T *)y->data, (int)cols, mask_kind, row_offset);
-  }
+  const bool taken =
+      mask_kind == B200_MASK_NONE
+          ? dispatch_rows<T, kSoftmaxPlain, true>(x, nullptr, y, mask_kind, row_offset, stream)
+          : dispatch_rows<T, kSoftmaxPlain, false>(x, nullptr, y, mask_kind, row_offset, stream);
+  if (!taken)
+    softmax_loop_kernel<T><<<(unsigned)x->shape[0], kRowThreads, 0, stream>>>(
+        (const T *)x->data, (T *)y->data, (int)x->shape[1], mask_kind, row_offset);
   B200_CUDA_OK(cudaGetLastError());
   return B200_OK;
+}
+
+// softmax(x) * mul and softmax(log x) for rows that fit the register-resident kernel;
+// returns false (nothing launched) for the others
+bool softmax_variant_rows(const b200_tensor *x, const b200_tensor *mul, b200_tensor *y,
+                          int log_input, cudaStream_t stream) {
+#define B200_SVR(T)                                                                      \
+  (log_input ? dispatch_rows<T, kSoftmaxLog, true>(x, nullptr, y, B200_MASK_NONE, 0, stream)  \
+             : dispatch_rows<T, kSoftmaxMul, true>(x, mul, y, B200_MASK_NONE, 0, stream))
+  if (mul == nullptr && !log_input) return false;
+  if (mul != nullptr && log_input) return false;
+  if (x->dtype == B200_DTYPE_FLOAT32) return B200_SVR(float);
+  if (x->dtype == B200_DTYPE_FLOAT16) return B200_SVR(__half);
+  return B200_SVR(__nv_bfloat16);
+#undef B200_SVR
 }
 
 }  // namespace b200

@@ -428,7 +428,8 @@ def test_rms_matmul_sweep(device, shape, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["bfloat16", "float16", "float32"])
-@pytest.mark.parametrize("shape", [(1, 1), (33, 33), (64, 4096), (257, 1000), (1024, 11008)])
+@pytest.mark.parametrize("shape", [(1, 1), (33, 33), (64, 4096), (257, 1000), (1024, 11008),
+                                   (1027, 8192), (3, 16)])
 def test_dequantize_sweep(device, shape, dtype):
     k, n = shape
     rng = np.random.default_rng(_seed(shape, dtype))
@@ -571,7 +572,8 @@ def test_attention_decode_strided_cache_and_rejections(device):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("shape", [(4, 64), (8, 128), (5, 99), (64, 1024), (33, 14336)])
+@pytest.mark.parametrize("shape", [(4, 64), (8, 128), (5, 99), (64, 1024), (33, 14336),
+                                   (1031, 4096)])
 def test_swiglu_sweep(device, shape, dtype):
     rng = np.random.default_rng(9)
     x, y = (_host(rng.standard_normal(shape), dtype) for _ in range(2))
@@ -580,6 +582,99 @@ def test_swiglu_sweep(device, shape, dtype):
     ops.swiglu(dx, dy, dout)
     rtol, atol = (1e-4, 1e-5) if dtype == "float32" else TOL[dtype]
     oracle.compare(device.download(dout).astype(np.float64), oracle.swiglu_ref(x, y), rtol, atol)
+
+
+VARIANT_SHAPES = [(4, 16), (4, 97), (3, 1000), (64, 1024), (10, 4000), (6, 4104), (5, 8192),
+                  (2, 33000), (3, 70000)]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "float16", "bfloat16"])
+@pytest.mark.parametrize("shape", VARIANT_SHAPES)
+def test_softmax_mul_sweep(device, shape, dtype):
+    rng = np.random.default_rng(_seed(shape, dtype, "mul"))
+    x = _host(rng.standard_normal(shape) * 2, dtype)
+    o = _host(rng.uniform(-2, 2, shape), dtype)
+    dx, do, dy = _up(device, x, dtype), _up(device, o, dtype), _poisoned(device, shape, dtype)
+    ops.softmax_variant(dx, dy, mul=do)
+    rtol, atol = (2e-3, 1e-6) if dtype == "float32" else TOL[dtype]
+    oracle.compare(device.download(dy).astype(np.float64), oracle.softmax_mul_ref(x, o), rtol, atol)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "float16", "bfloat16"])
+@pytest.mark.parametrize("shape", VARIANT_SHAPES)
+def test_softmax_log_sweep(device, shape, dtype):
+    """softmax(log x): positive rows, rows with zeros (log 0 = -inf: weight 0), and the rows
+    the reference turns into NaN as a whole: a negative entry, a NaN entry, an infinite entry,
+    an all-zero row (ops/suite/perf/softmax_log.py:27-31)."""
+    rows, cols = shape
+    rng = np.random.default_rng(_seed(shape, dtype, "log"))
+    x = rng.uniform(0.05, 4.0, shape).astype(np.float32)
+    x[0, :: 3] = 0.0
+    if rows > 1:
+        x[1, cols // 2] = -1.0
+    if rows > 2:
+        x[2, cols - 1] = np.nan
+    if rows > 3:
+        x[3, 0] = np.inf
+    if rows > 4:
+        x[4, :] = 0.0
+    x = _host(x, dtype)
+    dx, dy = _up(device, x, dtype), _poisoned(device, shape, dtype)
+    ops.softmax_variant(dx, dy, log_input=True)
+    y = device.download(dy).astype(np.float64)
+    ref = oracle.softmax_log_ref(x)
+    rtol, atol = (2e-3, 1e-6) if dtype == "float32" else TOL[dtype]
+    oracle.compare(y, ref, rtol, atol, equal_nan=True)
+    for r in range(1, min(rows, 5)):
+        assert np.isnan(y[r]).all(), f"row {r} must be NaN as a whole"
+    assert not np.isnan(y[0]).any()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "float16", "bfloat16"])
+@pytest.mark.parametrize("case", [((4, 16), 2, None), ((3, 100), 3, 299), ((5, 1000), 4, None),
+                                  ((64, 1024), 4, None), ((7, 1024), 8, 8000), ((3, 513), 5, 2560),
+                                  ((2, 4096), 1, None), ((2, 20000), 4, None)])
+def test_repeat_log_softmax_sweep(device, case, dtype):
+    shape, repeat, length = case
+    rng = np.random.default_rng(_seed(case, dtype))
+    x = _host(rng.standard_normal(shape) * 2, dtype)
+    out_len = shape[1] * repeat if length is None else length
+    dx, dy = _up(device, x, dtype), _poisoned(device, (shape[0], out_len), dtype)
+    ops.repeat_log_softmax(dx, dy, repeat)
+    ref = oracle.repeat_log_softmax_ref(x, repeat, out_len)
+    rtol, atol = (1e-4, 1e-5) if dtype == "float32" else TOL[dtype]
+    # the log-probabilities are of size log(length): the 16-bit tolerance is on their scale
+    if dtype != "float32":
+        atol = max(atol, 2 * rtol * np.log(out_len))
+    oracle.compare(device.download(dy).astype(np.float64), ref, rtol, atol)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "float16", "bfloat16"])
+@pytest.mark.parametrize("n", [1, 7, 8, 1000, 4099, 1 << 20, (1 << 20) + 13])
+def test_elementwise_family_sweep(device, n, dtype):
+    """The flat GELU family over lengths with and without a ragged end of the 16-byte vectors."""
+    rng = np.random.default_rng(_seed(n, dtype))
+    a = _host(rng.standard_normal(n) * 2, dtype)
+    b = _host(rng.standard_normal(n), dtype)
+    da, db = _up(device, a, dtype), _up(device, b, dtype)
+    rtol, atol = (1e-4, 1e-5) if dtype == "float32" else TOL[dtype]
+
+    def run(op, second=None, **params):
+        dout = _poisoned(device, (n,), dtype)
+        ops.elementwise(op, da, dout, b=second, **params)
+        return device.download(dout).astype(np.float64)
+
+    oracle.compare(run(abi.EW_GELU_ERF), oracle.gelu_erf(a.astype(np.float64)), rtol, atol)
+    oracle.compare(run(abi.EW_ADD_GELU_ERF, db, p0=1.5), oracle.add_gelu_ref(a, b, 1.5), rtol, atol)
+    oracle.compare(run(abi.EW_GEGLU_TANH, db), oracle.geglu_tanh_ref(a, b), rtol, atol)
+    for n_cols in (1, 8, 24, 1000):
+        if n % n_cols:
+            continue
+        bias = _host(rng.standard_normal(n_cols), dtype)
+        dbias = _up(device, bias, dtype)
+        ref = oracle.epilogue_ref(a, bias, n_cols, 0.75, -1.5, 2.0)
+        oracle.compare(run(abi.EW_BIAS_SCALE_CLAMP_GELU, dbias, p0=0.75, p1=-1.5, p2=2.0), ref,
+                       rtol, atol)
 
 
 # ------------------------------------------------------------------ native handles
