@@ -1177,6 +1177,14 @@ static int gemm_impl(const b200_tensor *a, const b200_tensor *b, const b200_tens
   }
 
   const bool dual = act == B200_ACT_SWIGLU;
+  if (!dual && N < BN && act != kActGroupNormMin) {
+    // one column block narrower than the tile: the MMAs take only the columns that exist
+    // (rounded up to the instruction's granule of 16) instead of 256 -- a [65536, 4096] x
+    // [4096, 64] product is then bound by reading x, not by the tensor pipe
+    const int n_mma = (int)((N + 15) / 16 * 16);
+    p.idesc = sm100::make_idesc_f16(BM, n_mma, a->dtype == B200_DTYPE_BFLOAT16 ? 1 : 0, 0,
+                                    b_rows_are_n ? 0 : 1);
+  }
   {
     // CTA pairs (256-row tiles) for B given as [K, N], when the pair tiles fill at least one
     // wave of SM pairs; B200OPS_GEMM_PAIR=0 / 1 forces the choice.
@@ -1184,8 +1192,10 @@ static int gemm_impl(const b200_tensor *a, const b200_tensor *b, const b200_tens
         getenv("B200OPS_GEMM_PAIR") ? atoi(getenv("B200OPS_GEMM_PAIR")) : -1;
     const int tile_n = dual ? BN / 2 : BN;
     const int64_t pair_tiles = ((M + 2 * BM - 1) / (2 * BM)) * ((N + tile_n - 1) / tile_n);
+    // (a pair always multiplies 256 columns: not for outputs of at most half a tile)
     const bool use_pair = !b_rows_are_n && act != kActLogSoftmax &&
-                          (pair_env >= 0 ? pair_env != 0 : pair_tiles >= sm_count() / 2);
+                          (pair_env >= 0 ? pair_env != 0
+                                         : pair_tiles >= sm_count() / 2 && N > tile_n / 2);
     if (use_pair) {
       Params q = p;
       q.idesc = sm100::make_idesc_f16(2 * BM, BN, a->dtype == B200_DTYPE_BFLOAT16 ? 1 : 0, 0, 1);

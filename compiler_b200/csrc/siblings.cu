@@ -256,30 +256,34 @@ repeat_log_softmax_kernel(const T *__restrict__ x, T *__restrict__ y, int cols, 
 }
 
 // The same with 16-byte loads and stores: the input row is read twice (the second time from
-// L1 / L2) and every output vector is assembled from the one or two inputs it repeats.
-// x rows and y rows 16-byte aligned, cols and length multiples of the vector length.
-template <typename T>
+// L1 / L2) and every output vector is assembled from the one or two inputs it repeats.  A row
+// belongs to a group of G threads (256 / G rows per CTA), sized so that a thread has about four
+// output vectors.  x rows and y rows 16-byte aligned, cols and length multiples of the vector
+// length.
+template <typename T, int G>
 __global__ void __launch_bounds__(kRowThreads)
-repeat_log_softmax_vec_kernel(const T *__restrict__ x, T *__restrict__ y, int cols, int repeat,
-                              int length) {
+repeat_log_softmax_vec_kernel(const T *__restrict__ x, T *__restrict__ y, int64_t rows, int cols,
+                              int repeat, int length) {
   constexpr int N = vec16<T>::N;
   __shared__ float scratch[2 * (kRowThreads / 32)];
-  const int64_t row = blockIdx.x;
+  const int lane = threadIdx.x % G;
+  const int64_t row = (int64_t)blockIdx.x * (kRowThreads / G) + threadIdx.x / G;
+  if (row >= rows) return;  // the whole group leaves: its barrier has no other member
   const T *xrow = x + row * (int64_t)cols;
   T *yrow = y + row * (int64_t)length;
   const int used = (length + repeat - 1) / repeat;  // inputs that reach the output
   const int in_vec = (used + N - 1) / N;
   float m = -INFINITY;
-  for (int v = threadIdx.x; v < in_vec; v += kRowThreads) {
+  for (int v = lane; v < in_vec; v += G) {
     vec16<T> a;
     a.raw = __ldg(reinterpret_cast<const uint4 *>(xrow) + v);
 #pragma unroll
     for (int j = 0; j < N; ++j)
       if (v * N + j < used) m = fmaxf(m, io<T>::load(a.e[j]));
   }
-  m = group_reduce<kRowThreads, MaxOp>(m, scratch, 0);
+  m = group_reduce<G, MaxOp>(m, scratch, 0);
   float s = 0.f;
-  for (int v = threadIdx.x; v < in_vec; v += kRowThreads) {
+  for (int v = lane; v < in_vec; v += G) {
     vec16<T> a;
     a.raw = __ldg(reinterpret_cast<const uint4 *>(xrow) + v);
 #pragma unroll
@@ -290,10 +294,10 @@ repeat_log_softmax_vec_kernel(const T *__restrict__ x, T *__restrict__ y, int co
       if (c < used) s += (float)count * expf(io<T>::load(a.e[j]) - m);
     }
   }
-  s = group_reduce<kRowThreads, SumOp>(s, scratch, 1);
+  s = group_reduce<G, SumOp>(s, scratch, 1);
   const float lse = m + logf(s);
   const int out_vec = length / N;
-  for (int v = threadIdx.x; v < out_vec; v += kRowThreads) {
+  for (int v = lane; v < out_vec; v += G) {
     int c = (v * N) / repeat;
     int rem = (v * N) - c * repeat;
     float cur = io<T>::load(xrow[c]) - lse;
@@ -309,6 +313,23 @@ repeat_log_softmax_vec_kernel(const T *__restrict__ x, T *__restrict__ y, int co
     }
     st_stream16(yrow + (int64_t)v * N, o.raw);
   }
+}
+
+template <typename T>
+static void launch_repeat_vec(const b200_tensor *x, b200_tensor *y, int repeat, cudaStream_t s) {
+  constexpr int N = vec16<T>::N;
+  const int64_t rows = x->shape[0];
+  const int cols = (int)x->shape[1], length = (int)y->shape[1];
+  const int out_vec = length / N;
+#define B200_RLV(G)                                                                         \
+  repeat_log_softmax_vec_kernel<T, G><<<(unsigned)((rows + kRowThreads / G - 1) / (kRowThreads / G)), \
+                                        kRowThreads, 0, s>>>((const T *)x->data, (T *)y->data, rows, \
+                                                             cols, repeat, length)
+  if (out_vec <= 32 * 4) B200_RLV(32);
+  else if (out_vec <= 64 * 4) B200_RLV(64);
+  else if (out_vec <= 128 * 4) B200_RLV(128);
+  else B200_RLV(256);
+#undef B200_RLV
 }
 
 }  // namespace b200
@@ -407,8 +428,7 @@ extern "C" int b200_repeat_log_softmax(const b200_tensor *x, b200_tensor *y, int
 #define B200_RL(T)                                                                      \
   do {                                                                                  \
     if (vec_ok)                                                                         \
-      repeat_log_softmax_vec_kernel<T><<<(unsigned)rows, kRowThreads, 0, s>>>(          \
-          (const T *)x->data, (T *)y->data, (int)cols, repeat, (int)length);            \
+      launch_repeat_vec<T>(x, y, repeat, s);                                            \
     else                                                                                \
       repeat_log_softmax_kernel<T><<<(unsigned)rows, kRowThreads, 0, s>>>(              \
           (const T *)x->data, (T *)y->data, (int)cols, repeat, (int)length);            \
@@ -427,38 +447,53 @@ extern "C" int b200_repeat_log_softmax(const b200_tensor *x, b200_tensor *y, int
 namespace b200 {
 namespace {
 
-// The aligned case: a thread owns 16 consecutive columns, keeps their 16 scales in registers
-// and walks down the rows (blockIdx.y strides over them, four rows in flight), so there is no
-// index division and the scales are read once per thread.
+// Byte `lane` of `biased` (an int8 with its sign bit flipped, i.e. value + 128) as a float:
+// the byte is placed into the low mantissa bits of 2^23 (one byte permute) and 2^23 + 128 is
+// subtracted -- exact, and on the full-rate pipes instead of the integer-to-float converter.
+__device__ __forceinline__ float int8_lane_to_float(uint32_t biased, int lane) {
+  return __uint_as_float(__byte_perm(biased, 0x4B000000u, 0x7440u + (uint32_t)lane)) - 8388736.0f;
+}
+
+// The aligned case: a thread owns the columns of one 16-byte output vector (8 for 16-bit
+// results, 4 for fp32), keeps their scales in registers and walks down the rows (blockIdx.y
+// strides over them, eight rows in flight), so there is no index division, the scales are read
+// once per thread, and a warp reads and writes whole contiguous segments of a row.
 template <typename T>
 __global__ void __launch_bounds__(256)
 dequantize_cols_kernel(const int8_t *__restrict__ b, int64_t ldb, const T *__restrict__ scale,
                        T *__restrict__ out, int64_t ldo, int K, int groups) {
   constexpr int PER = 16 / (int)sizeof(T);
-  constexpr int R = 4;
+  constexpr int R = 8;
   const int g = blockIdx.x * 256 + threadIdx.x;
   if (g >= groups) return;
-  const int n0 = g * 16;
-  float sc[16];
+  const int n0 = g * PER;
+  float sc[PER];
 #pragma unroll
-  for (int j = 0; j < 16; ++j) sc[j] = io<T>::load(scale[n0 + j]);
+  for (int j = 0; j < PER; ++j) sc[j] = io<T>::load(scale[n0 + j]);
   for (int k0 = blockIdx.y * R; k0 < K; k0 += gridDim.y * R) {
-    uint4 raw[R];
+    uint32_t raw[R][PER / 4];
 #pragma unroll
-    for (int r = 0; r < R; ++r)
-      if (k0 + r < K) raw[r] = ld_stream16(b + (int64_t)(k0 + r) * ldb + n0);
+    for (int r = 0; r < R; ++r) {
+      if (k0 + r < K) {
+        const int8_t *src = b + (int64_t)(k0 + r) * ldb + n0;
+        if constexpr (PER == 8) {
+          const uint2 t = __ldg(reinterpret_cast<const uint2 *>(src));
+          raw[r][0] = t.x;
+          raw[r][1] = t.y;
+        } else {
+          raw[r][0] = __ldg(reinterpret_cast<const uint32_t *>(src));
+        }
+      }
+    }
 #pragma unroll
     for (int r = 0; r < R; ++r) {
       if (k0 + r >= K) break;
-      const int8_t *q = reinterpret_cast<const int8_t *>(&raw[r]);
-      T *dst = out + (int64_t)(k0 + r) * ldo + n0;
+      vec16<T> o;
 #pragma unroll
-      for (int v = 0; v < 16 / PER; ++v) {
-        vec16<T> o;
-#pragma unroll
-        for (int j = 0; j < PER; ++j) o.e[j] = io<T>::store((float)q[v * PER + j] * sc[v * PER + j]);
-        st_stream16(dst + v * PER, o.raw);
-      }
+      for (int j = 0; j < PER; ++j)
+        // sign bit flipped: the byte becomes value + 128 as unsigned
+        o.e[j] = io<T>::store(int8_lane_to_float(raw[r][j >> 2] ^ 0x80808080u, j & 3) * sc[j]);
+      st_stream16(out + (int64_t)(k0 + r) * ldo + n0, o.raw);
     }
   }
 }
@@ -521,10 +556,10 @@ extern "C" int b200_dequantize_cols(const b200_tensor *b, const b200_tensor *sca
   if (blocks > cap) blocks = cap;
   cudaStream_t s = (cudaStream_t)stream;
   const bool by_columns = vector_ok && N % 16 == 0;  // N > 0 here, so at least one group
-  const int groups = (int)(N / 16);
+  const int groups = (int)(N / (16 / (int64_t)es));  // one 16-byte output vector per thread
   const unsigned gx = by_columns ? (unsigned)((groups + 255) / 256) : 1u;
   int64_t gy = ((int64_t)sm_count() * 8 + gx - 1) / gx;
-  if (gy > (K + 3) / 4) gy = (K + 3) / 4;
+  if (gy > (K + 7) / 8) gy = (K + 7) / 8;
   if (gy > 65535) gy = 65535;
 #define B200_DQ(T)                                                                              \
   do {                                                                                          \
