@@ -183,9 +183,14 @@ softmax_rows_kernel(const T *__restrict__ x, const T *__restrict__ mul, T *__res
   float m = -INFINITY;
   bool bad = false;
   const T *xrow = x + row * (int64_t)cols;
+  T *yrow = y + row * (int64_t)cols;
 #pragma unroll
   for (int i = 0; i < VPT; ++i) {
     const int v = lane + i * G;
+    // the zeros of the masked columns depend on nothing: they leave while the loads are in
+    // flight, instead of queueing behind both reductions with the rest of the row
+    if (MODE == kSoftmaxPlain && row_ok && v >= kept_vec && v < nvec)
+      st_stream16(yrow + (int64_t)v * N, make_uint4(0u, 0u, 0u, 0u));
     if (v < kept_vec) {
       raw[i] = ld_stream16(xrow + (int64_t)v * N);
       if constexpr (MODE == kSoftmaxLog) {
@@ -228,7 +233,6 @@ softmax_rows_kernel(const T *__restrict__ x, const T *__restrict__ mul, T *__res
     if (m == INFINITY) r = __int_as_float(0x7fc00000);  // a NaN, negative or infinite input
   }
 
-  T *yrow = y + row * (int64_t)cols;
   if constexpr (MODE == kSoftmaxMul) {
     const T *mrow = mul + row * (int64_t)cols;
     uint4 w[VPT];
@@ -246,13 +250,9 @@ softmax_rows_kernel(const T *__restrict__ x, const T *__restrict__ mul, T *__res
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
       const int v = lane + i * G;
-      if (row_ok && v < nvec) {
-        uint4 out = make_uint4(0u, 0u, 0u, 0u);
-        if (v < kept_vec) {
-          if constexpr (!KEEP) V::exps(raw[i], m, neg_m_log2e, e[0]);
-          out = V::scaled(e[KEEP ? i : 0], r, nullptr);
-        }
-        st_stream16(yrow + (int64_t)v * N, out);
+      if (v < kept_vec) {
+        if constexpr (!KEEP) V::exps(raw[i], m, neg_m_log2e, e[0]);
+        st_stream16(yrow + (int64_t)v * N, V::scaled(e[KEEP ? i : 0], r, nullptr));
       }
     }
   }
