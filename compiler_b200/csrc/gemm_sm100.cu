@@ -1294,15 +1294,45 @@ scale_rows_kernel(const T *__restrict__ w, int64_t ldw, const T *__restrict__ g,
   }
 }
 
+// the same on 16-byte vectors (rows of w and out 16-byte aligned, N a multiple of the vector)
+template <typename T>
+__global__ void __launch_bounds__(256)
+scale_rows_vec_kernel(const T *__restrict__ w, int64_t ldw, const T *__restrict__ g,
+                      T *__restrict__ out, int64_t ldo, int K, int nvec) {
+  constexpr int PER = 16 / (int)sizeof(T);
+  for (int k = blockIdx.y; k < K; k += gridDim.y) {
+    const float gk = io<T>::load(g[k]);
+    for (int v = blockIdx.x * 256 + threadIdx.x; v < nvec; v += gridDim.x * 256) {
+      vec16<T> a, o;
+      a.raw = ld_stream16(w + (int64_t)k * ldw + (int64_t)v * PER);
+#pragma unroll
+      for (int j = 0; j < PER; ++j) o.e[j] = io<T>::store(gk * io<T>::load(a.e[j]));
+      *reinterpret_cast<uint4 *>(out + (int64_t)k * ldo + (int64_t)v * PER) = o.raw;
+    }
+  }
+}
+
 template <typename T>
 static int rms_matmul_prepare(const b200_tensor *x, const b200_tensor *g, const b200_tensor *w,
                               b200_tensor *scaled_w, float *rinv, float eps, cudaStream_t s) {
   const int M = (int)x->shape[0], K = (int)x->shape[1], N = (int)w->shape[1];
   row_rinv_kernel<T><<<M, 256, 0, s>>>((const T *)x->data, x->stride[0], K, eps, rinv);
   B200_CUDA_OK(cudaGetLastError());
-  dim3 grid((unsigned)((N + 255) / 256 < 64 ? (N + 255) / 256 : 64), (unsigned)(K < 4096 ? K : 4096));
-  scale_rows_kernel<T><<<grid, 256, 0, s>>>((const T *)w->data, w->stride[0], (const T *)g->data,
-                                            (T *)scaled_w->data, scaled_w->stride[0], K, N);
+  constexpr int PER = 16 / (int)sizeof(T);
+  const bool vec_ok = N % PER == 0 && w->stride[0] % PER == 0 && scaled_w->stride[0] % PER == 0 &&
+                      (uintptr_t)w->data % 16 == 0 && (uintptr_t)scaled_w->data % 16 == 0;
+  if (vec_ok) {
+    const int nvec = N / PER;
+    dim3 grid((unsigned)((nvec + 255) / 256 < 16 ? (nvec + 255) / 256 : 16),
+              (unsigned)(K < 2048 ? K : 2048));
+    scale_rows_vec_kernel<T><<<grid, 256, 0, s>>>((const T *)w->data, w->stride[0],
+                                                  (const T *)g->data, (T *)scaled_w->data,
+                                                  scaled_w->stride[0], K, nvec);
+  } else {
+    dim3 grid((unsigned)((N + 255) / 256 < 64 ? (N + 255) / 256 : 64), (unsigned)(K < 4096 ? K : 4096));
+    scale_rows_kernel<T><<<grid, 256, 0, s>>>((const T *)w->data, w->stride[0], (const T *)g->data,
+                                              (T *)scaled_w->data, scaled_w->stride[0], K, N);
+  }
   B200_CUDA_OK(cudaGetLastError());
   return B200_OK;
 }
