@@ -365,6 +365,30 @@ def bench_softmax_e2e(dist, steps, warmup):
             "result_check_rowsum64": round(checksum, 3)}
 
 
+def bench_softmax_unmasked(torch, ops, dist, steps, warmup, peaks, source):
+    """The headline's shape without the mask (the reference's softmax.py operator itself):
+    every element is read and written, so algorithmic bytes and DRAM traffic coincide."""
+    stream = torch.cuda.current_stream().cuda_stream
+    nsets = 4
+    gen = torch.Generator(device="cuda").manual_seed(35 + dist.rank)
+    xs = [(torch.randn((ROWS, COLS), generator=gen, device="cuda") * 2).to(torch.float16)
+          for _ in range(nsets)]
+    ys = [torch.empty_like(x) for x in xs]
+
+    def launch_on(handle, i):
+        ops.softmax(xs[i % nsets], ys[i % nsets], stream=handle)
+
+    _, launch_ms, _ = time_steps(torch, dist, lambda i: launch_on(stream, i), steps, warmup)
+    region_ms, window = time_graph_region(torch, dist, launch_on, steps, warmup)
+    out = roofline("hbm", SOFTMAX_BYTES, region_ms, peaks, source, None)
+    out["launch_ms_event_pairs"] = round(launch_ms, 5)
+    out["window"] = window
+    out.update({"workload": "softmax_fp16_16384x4000_unmasked", "ms_per_step": round(region_ms, 5),
+                "value": round(SOFTMAX_BYTES * dist.world / (region_ms * 1e-3) / 1e9, 2),
+                "unit": "GB/s", "gpu_launches": steps})
+    return out
+
+
 def bench_rmsnorm(torch, ops, dist, steps, warmup, peaks, source):
     stream = torch.cuda.current_stream().cuda_stream
     nsets = 4
@@ -561,7 +585,7 @@ def main():
     parser.add_argument("--warmup", type=int, default=20)
     parser.add_argument("--impl", default="native", choices=["native", "reference"])
     parser.add_argument("--ops", default="all",
-                        help="comma list of extra operators: rmsnorm,gemm,gemm_ragged,attention,attention_decode,"
+                        help="comma list of extra operators: softmax_unmasked,rmsnorm,gemm,gemm_ragged,attention,attention_decode,"
                              "tp_mlp,none,all")
     args = parser.parse_args()
     if args.impl == "reference":
@@ -599,6 +623,9 @@ def main():
         time.sleep(1.0)
         return True
 
+    if want("softmax_unmasked"):
+        extras["softmax_unmasked"] = bench_softmax_unmasked(
+            torch, ops, dist, max(extra_steps, min(args.steps, 200)), warmup, peaks, source)
     if want("rmsnorm"):
         extras["rmsnorm"] = bench_rmsnorm(torch, ops, dist, max(extra_steps, min(args.steps, 200)),
                                           warmup, peaks, source)
