@@ -138,6 +138,13 @@ template <> struct RowVec<__nv_bfloat16> : RowVec16<__nv_bfloat162, __nv_bfloat1
   }
 };
 
+// (row_offset + row) % cols.  The kept width of a masked row stands before its loads, and a
+// 64-bit remainder is a long dependent sequence: take the 32-bit one whenever the row index fits.
+__device__ __forceinline__ int row_mod(int64_t index, int cols) {
+  if (index < ((int64_t)1 << 32)) return (int)((uint32_t)index % (uint32_t)cols);
+  return (int)(index % cols);
+}
+
 // MODE: the plain (optionally masked) softmax, softmax(x) * mul, or softmax(log x).
 constexpr int kSoftmaxPlain = 0, kSoftmaxMul = 1, kSoftmaxLog = 2;
 
@@ -171,7 +178,7 @@ softmax_rows_kernel(const T *__restrict__ x, const T *__restrict__ mul, T *__res
   // vector full_vec (if keep % N != 0) partly, everything after is masked
   int keep = cols;
   if (MODE == kSoftmaxPlain && mask_kind == B200_MASK_CAUSAL_MOD && row_ok)
-    keep = (int)((row_offset + row) % cols) + 1;
+    keep = row_mod(row_offset + row, cols) + 1;
   const int full_vec = keep / N;
   const int kept_vec = row_ok ? (keep + N - 1) / N : 0;
 
@@ -268,7 +275,7 @@ constexpr int stream_ctas_per_sm(int mode) { return mode == kSoftmaxMul ? 2 : 3;
 template <typename T, int G, int VPT, int MODE>
 __global__ void __launch_bounds__(kRowThreads, stream_ctas_per_sm(MODE))
 softmax_stream_kernel(const T *__restrict__ x, const T *__restrict__ mul, T *__restrict__ y,
-                      int64_t rows, int cols) {
+                      int64_t rows, int cols, int mask_kind, int64_t row_offset) {
   static_assert(G <= kRowThreads, "one row per group of at most a CTA");
   constexpr int kRowsPerCta = kRowThreads / G;
   using V = RowVec<T>;
@@ -279,25 +286,39 @@ softmax_stream_kernel(const T *__restrict__ x, const T *__restrict__ mul, T *__r
   const int nvec = cols / N;
   const int64_t stride = (int64_t)gridDim.x * kRowsPerCta;
   int64_t row = (int64_t)blockIdx.x * kRowsPerCta + threadIdx.x / G;
+  // masked rows: row r keeps its first (row_offset + r) % cols + 1 columns; the remainder is
+  // taken once and then advanced by the stride between this group's rows
+  const bool masked = MODE == kSoftmaxPlain && mask_kind == B200_MASK_CAUSAL_MOD;
+  const int step_mod = masked ? row_mod(stride, cols) : 0;
+  int keep_next = masked ? row_mod(row_offset + row, cols) + 1 : cols;
 
   uint4 next[VPT];
   if (row < rows) {
+    const int kv = (keep_next + N - 1) / N;
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
       const int v = lane + i * G;
-      if (v < nvec) next[i] = ld_stream16(x + row * (int64_t)cols + (int64_t)v * N);
+      if (v < kv) next[i] = ld_stream16(x + row * (int64_t)cols + (int64_t)v * N);
     }
   }
   for (; row < rows; row += stride) {
+    const int keep = keep_next;
+    const int full_vec = keep / N;
+    const int kept_vec = (keep + N - 1) / N;
+    if (masked) {
+      keep_next += step_mod;  // keep - 1 is the remainder: stay in [1, cols]
+      if (keep_next > cols) keep_next -= cols;
+    }
     uint4 raw[VPT];
 #pragma unroll
     for (int i = 0; i < VPT; ++i) raw[i] = next[i];
     if (row + stride < rows) {
       const T *ahead = x + (row + stride) * (int64_t)cols;
+      const int kv = (keep_next + N - 1) / N;
 #pragma unroll
       for (int i = 0; i < VPT; ++i) {
         const int v = lane + i * G;
-        if (v < nvec) next[i] = ld_stream16(ahead + (int64_t)v * N);
+        if (v < kv) next[i] = ld_stream16(ahead + (int64_t)v * N);
       }
     }
     uint4 w[MODE == kSoftmaxMul ? VPT : 1];
@@ -313,10 +334,14 @@ softmax_stream_kernel(const T *__restrict__ x, const T *__restrict__ mul, T *__r
     float e[VPT][N];
     float m = -INFINITY;
     bool bad = false;
+    T *yrow = y + row * (int64_t)cols;
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
       const int v = lane + i * G;
-      if (v < nvec) {
+      // the zeros of the masked columns depend on nothing
+      if (masked && v >= kept_vec && v < nvec)
+        st_stream16(yrow + (int64_t)v * N, make_uint4(0u, 0u, 0u, 0u));
+      if (v < kept_vec) {
         if constexpr (MODE == kSoftmaxLog) {
           V::unpack(raw[i], e[i]);
 #pragma unroll
@@ -325,6 +350,7 @@ softmax_stream_kernel(const T *__restrict__ x, const T *__restrict__ mul, T *__r
             m = fmaxf(m, e[i][j]);
           }
         } else {
+          if (masked && v >= full_vec) V::mask_tail(raw[i], keep - v * N);
           m = fmaxf(m, V::vmax(raw[i]));
         }
       }
@@ -338,7 +364,7 @@ softmax_stream_kernel(const T *__restrict__ x, const T *__restrict__ mul, T *__r
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
       const int v = lane + i * G;
-      if (v < nvec) {
+      if (v < kept_vec) {
         if constexpr (MODE == kSoftmaxLog) {
 #pragma unroll
           for (int j = 0; j < N; ++j) {
@@ -355,11 +381,10 @@ softmax_stream_kernel(const T *__restrict__ x, const T *__restrict__ mul, T *__r
     if constexpr (MODE == kSoftmaxLog) {
       if (m == INFINITY) r = __int_as_float(0x7fc00000);
     }
-    T *yrow = y + row * (int64_t)cols;
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
       const int v = lane + i * G;
-      if (v < nvec)
+      if (v < kept_vec)
         st_stream16(yrow + (int64_t)v * N,
                     V::scaled(e[i], r, MODE == kSoftmaxMul ? &w[MODE == kSoftmaxMul ? i : 0] : nullptr));
     }
@@ -399,16 +424,18 @@ static void launch_rows(const b200_tensor *x, const b200_tensor *mul, b200_tenso
   const unsigned grid = (unsigned)((rows + kRowsPerCta - 1) / kRowsPerCta);
   if constexpr (G <= kRowThreads) {
     // unmasked rows, more than one wave of resident CTAs: the pipelined persistent form
-    // (B200OPS_SOFTMAX_STREAM=0 keeps the one-row-per-group kernel).  Masked rows stay with
+    // (B200OPS_SOFTMAX_STREAM=0 keeps the one-row-per-group kernel, 2 sends masked rows
+    // through the pipelined one as well).  Masked rows stay with
     // the one-row-per-group kernel: their cost is the stores, rows differ in length, and
-    // eight small CTAs per SM measured faster there (39.0 against 47.6 us at 16384 x 4000).
-    static const bool allow =
-        !(getenv("B200OPS_SOFTMAX_STREAM") && atoi(getenv("B200OPS_SOFTMAX_STREAM")) == 0);
+    // eight small CTAs per SM measured faster there (39.0 against 42.8 us at 16384 x 4000).
+    static const int choice =
+        getenv("B200OPS_SOFTMAX_STREAM") ? atoi(getenv("B200OPS_SOFTMAX_STREAM")) : 1;
     const unsigned resident = (unsigned)(sm_count() * stream_ctas_per_sm(MODE));
-    if (allow && mask_kind == B200_MASK_NONE && grid > resident) {
+    const bool take = choice == 2 || (choice == 1 && mask_kind == B200_MASK_NONE);
+    if (take && grid > resident) {
       softmax_stream_kernel<T, G, VPT, MODE><<<resident, kRowThreads, 0, stream>>>(
           (const T *)x->data, mul ? (const T *)mul->data : nullptr, (T *)y->data, rows,
-          (int)x->shape[1]);
+          (int)x->shape[1], mask_kind, row_offset);
       return;
     }
   }
