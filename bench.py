@@ -46,7 +46,7 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 # `python -m compiler_b200.profile_case <op> --shape ...` per kernel at the bench shape (attention:
 # captured at [4,16,4096,128] and scaled by 4, traffic is proportional to batch x heads)
 NCU_TRAFFIC = {
-    "softmax": 140_785_000,
+    "softmax": 141_064_000,
     "rmsnorm": 212_674_000,
     "gemm_8192": 1_181_803_000,
     "gemm_ragged": 203_472_000,
