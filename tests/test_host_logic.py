@@ -181,3 +181,93 @@ def test_compile_case_refuses_unknown_kernels():
     with pytest.raises(UnsupportedLaunch):
         compiler.compile_case(case)
     assert compiler.compile_count == 0
+
+
+# ------------------------------------------------------------------ graph capture (host logic)
+class _FakeGraphLib:
+    """Stands in for the C ABI: records the calls of compiler_b200.graph without a GPU."""
+
+    def __init__(self, end_status=0):
+        self.calls = []
+        self.end_status = end_status
+
+    def b200_stream_create(self, out):
+        out._obj.value = 0x1000
+        self.calls.append("stream_create")
+        return 0
+
+    def b200_stream_destroy(self, stream):
+        self.calls.append("stream_destroy")
+        return 0
+
+    def b200_stream_sync(self, stream):
+        self.calls.append("stream_sync")
+        return 0
+
+    def b200_graph_begin_capture(self, stream):
+        self.calls.append("begin")
+        return 0
+
+    def b200_graph_end_capture(self, stream, out):
+        self.calls.append("end")
+        if self.end_status == 0:
+            out._obj.value = 0x2000
+        return self.end_status
+
+    def b200_graph_launch(self, graph, stream):
+        self.calls.append("launch")
+        return 0
+
+    def b200_graph_destroy(self, graph):
+        self.calls.append("destroy")
+        return 0
+
+    def b200_last_error(self):
+        return b"capture failed"
+
+
+def test_graph_capture_records_launches_and_releases(monkeypatch):
+    from compiler_b200 import graph
+    from compiler_b200.runtime import abi
+
+    fake = _FakeGraphLib()
+    monkeypatch.setattr(abi, "lib", lambda: fake)
+    stream = graph.Stream()
+    with graph.capture(stream) as g:
+        with pytest.raises(RuntimeError):
+            g.launch(stream)  # not ready inside the block
+    g.launch(stream)
+    g.launch(stream)
+    g.close()
+    g.close()  # idempotent
+    stream.close()
+    assert fake.calls == ["stream_create", "begin", "end", "launch", "launch", "destroy",
+                          "stream_destroy"]
+
+
+def test_graph_capture_is_closed_and_discarded_when_the_block_raises(monkeypatch):
+    from compiler_b200 import graph
+    from compiler_b200.runtime import abi
+
+    fake = _FakeGraphLib()
+    monkeypatch.setattr(abi, "lib", lambda: fake)
+    stream = graph.Stream()
+    with pytest.raises(ValueError):
+        with graph.capture(stream):
+            raise ValueError("the block failed")
+    # the capture was ended (the stream must not stay in capture mode) and its graph dropped
+    assert fake.calls[-2:] == ["end", "destroy"]
+    stream.close()
+
+
+def test_graph_capture_reports_a_failed_end(monkeypatch):
+    from compiler_b200 import graph
+    from compiler_b200.runtime import abi
+
+    fake = _FakeGraphLib(end_status=4)
+    monkeypatch.setattr(abi, "lib", lambda: fake)
+    stream = graph.Stream()
+    with pytest.raises(Exception):
+        with graph.capture(stream):
+            pass
+    stream.close()
