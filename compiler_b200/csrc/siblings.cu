@@ -315,6 +315,69 @@ repeat_log_softmax_vec_kernel(const T *__restrict__ x, T *__restrict__ y, int64_
   }
 }
 
+// Short input rows (at most one 16-byte vector per thread of the group): the vector stays in
+// registers between the maximum and the sum, and the row goes to shared memory as floats once,
+// so the output pass reads its repeated inputs from there instead of from global memory.
+template <typename T, int G>
+__global__ void __launch_bounds__(kRowThreads)
+repeat_log_softmax_cached_kernel(const T *__restrict__ x, T *__restrict__ y, int64_t rows,
+                                 int cols, int repeat, int length) {
+  constexpr int N = vec16<T>::N;
+  constexpr int kRows = kRowThreads / G;
+  __shared__ float scratch[2 * (kRowThreads / 32)];
+  __shared__ float cache[kRows][G * N];  // the used part of each row
+  const int lane = threadIdx.x % G;
+  const int group = threadIdx.x / G;
+  const int64_t row = (int64_t)blockIdx.x * kRows + group;
+  if (row >= rows) return;  // the whole group leaves: its barrier has no other member
+  const T *xrow = x + row * (int64_t)cols;
+  T *yrow = y + row * (int64_t)length;
+  const int used = (length + repeat - 1) / repeat;  // inputs that reach the output, <= G * N
+  float f[N];
+  float m = -INFINITY;
+  if (lane * N < used) {
+    vec16<T> a;
+    a.raw = ld_stream16(xrow + lane * N);
+#pragma unroll
+    for (int j = 0; j < N; ++j) {
+      f[j] = io<T>::load(a.e[j]);
+      cache[group][lane * N + j] = f[j];
+      if (lane * N + j < used) m = fmaxf(m, f[j]);
+    }
+  }
+  m = group_reduce<G, MaxOp>(m, scratch, 0);
+  float s = 0.f;
+  if (lane * N < used) {
+#pragma unroll
+    for (int j = 0; j < N; ++j) {
+      const int c = lane * N + j;
+      const int count = min(repeat, length - c * repeat);  // the last used input may repeat less
+      if (c < used) s += (float)count * expf(f[j] - m);
+    }
+  }
+  // the reduction's barrier also publishes the cached row to the whole group
+  s = group_reduce<G, SumOp>(s, scratch, 1);
+  if constexpr (G <= 32) __syncwarp();
+  const float lse = m + logf(s);
+  const int out_vec = length / N;
+  for (int v = lane; v < out_vec; v += G) {
+    int c = (v * N) / repeat;
+    int rem = (v * N) - c * repeat;
+    float cur = cache[group][c] - lse;
+    vec16<T> o;
+#pragma unroll
+    for (int j = 0; j < N; ++j) {
+      o.e[j] = io<T>::store(cur);
+      if (++rem == repeat) {
+        rem = 0;
+        ++c;
+        if (j + 1 < N && c < used) cur = cache[group][c] - lse;
+      }
+    }
+    st_stream16(yrow + (int64_t)v * N, o.raw);
+  }
+}
+
 template <typename T>
 static void launch_repeat_vec(const b200_tensor *x, b200_tensor *y, int repeat, cudaStream_t s) {
   constexpr int N = vec16<T>::N;
@@ -325,10 +388,18 @@ static void launch_repeat_vec(const b200_tensor *x, b200_tensor *y, int repeat, 
   repeat_log_softmax_vec_kernel<T, G><<<(unsigned)((rows + kRowThreads / G - 1) / (kRowThreads / G)), \
                                         kRowThreads, 0, s>>>((const T *)x->data, (T *)y->data, rows, \
                                                              cols, repeat, length)
-  if (out_vec <= 32 * 4) B200_RLV(32);
-  else if (out_vec <= 64 * 4) B200_RLV(64);
-  else if (out_vec <= 128 * 4) B200_RLV(128);
+  const int used = (length + repeat - 1) / repeat;
+#define B200_RLC(G)                                                                         \
+  repeat_log_softmax_cached_kernel<T, G><<<(unsigned)((rows + kRowThreads / G - 1) / (kRowThreads / G)), \
+                                           kRowThreads, 0, s>>>((const T *)x->data, (T *)y->data, rows, \
+                                                                cols, repeat, length)
+  // the cached form when a group's threads hold the used inputs in one vector each
+  if (out_vec <= 32 * 4) { if (used <= 32 * N) B200_RLC(32); else B200_RLV(32); }
+  else if (out_vec <= 64 * 4) { if (used <= 64 * N) B200_RLC(64); else B200_RLV(64); }
+  else if (out_vec <= 128 * 4) { if (used <= 128 * N) B200_RLC(128); else B200_RLV(128); }
+  else if (used <= 256 * N) B200_RLC(256);
   else B200_RLV(256);
+#undef B200_RLC
 #undef B200_RLV
 }
 
