@@ -49,17 +49,18 @@ elementwise_kernel(const T *__restrict__ a, const T *__restrict__ b, T *__restri
 // carries 8 or 11 bits), one reciprocal and one ex2 instead of erff's polynomial pair.
 __device__ __forceinline__ float erf_short(float x) {
   const float ax = fabsf(x);
-  const float t = __fdividef(1.0f, fmaf(0.3275911f, ax, 1.0f));
+  float t, e;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(t) : "f"(fmaf(0.3275911f, ax, 1.0f)));
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(-1.4426950408889634f * ax * ax));
   float poly = fmaf(1.061405429f, t, -1.453152027f);
   poly = fmaf(poly, t, 1.421413741f);
   poly = fmaf(poly, t, -0.284496736f);
   poly = fmaf(poly, t, 0.254829592f);
-  const float y = 1.0f - poly * t * exp2f(-1.4426950408889634f * ax * ax);
-  return copysignf(y, x);
+  return copysignf(fmaf(-poly * t, e, 1.0f), x);
 }
 template <typename T> __device__ __forceinline__ float gelu_erf_t(float z) {
   if constexpr (sizeof(T) == 4) return gelu_erf_f(z);
-  return 0.5f * z * (1.0f + erf_short(z * 0.7071067811865476f));
+  return z * fmaf(0.5f, erf_short(z * 0.7071067811865476f), 0.5f);
 }
 template <typename T> __device__ __forceinline__ float gelu_tanh_t(float z) {
   if constexpr (sizeof(T) == 4) return gelu_tanh_f(z);
