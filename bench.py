@@ -3,22 +3,26 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--ops LIST]
 
 Headline workload (the JSON line's ``value``): row-wise masked softmax fp16 over
-X[16384, 4000] with the causal-mod mask, one launch per step, inputs resident in HBM.
-With N > 1 (launched under torchrun, one rank per GPU) every rank runs that workload
-on its own rows -- rows are independent, no collective -- and ``value`` is the sum over
-ranks divided by the slowest rank's time (weak scaling).
+X[16384, 4000] with the causal-mod mask, inputs resident in HBM.  One STEP is one replay of a
+CUDA graph of 100 launches (100 passes over the workload on rotating buffer sets), so K = 20
+steps are a timed region of about 80 ms whatever K is.  With N > 1 (launched under torchrun,
+one rank per GPU) every rank runs that workload on its own rows -- rows are independent, no
+collective -- and ``value`` is the sum over ranks divided by the slowest rank's time (weak
+scaling); the ``strong`` block of the same line times the BASELINE tensor split N ways.
 
-The same line carries ``roofline`` (algorithmic bytes per launch / CUDA-event launch
-time against the measured HBM copy bandwidth), ``e2e`` (host buffers in pinned memory,
-host->device copy + launch + device->host copy inside the timed region, through
-``B200Device``), ``cpu_baseline`` (the numpy oracle on a bounded row sample, rank 0 at
-N=1 only), ``clocks`` (nvidia-smi samples taken while the kernels ran) and ``ops``: the
-other operators of the path (RMSNorm fp32, bf16 GEMM + bias + GELU square and ragged,
-causal attention forward, and at N > 1 the tensor-parallel SwiGLU MLP), each with its own
-roofline.
+The same line carries ``roofline`` (algorithmic bytes per launch / average launch duration
+against the measured HBM copy bandwidth, plus the same with the bytes the mask makes
+necessary), ``e2e`` (host buffers in pinned memory, host->device copy + launch + device->host
+copy inside the timed region, through the library's host API), ``cpu_baseline`` (the numpy
+oracle over the whole workload on the host cores, rank 0 at N=1 only), ``clocks`` (samples
+taken while the kernels ran) and ``ops``: the other operators of the path (RMSNorm fp32, bf16
+GEMM + bias + GELU square and ragged, causal attention forward, decode attention, the sibling
+kernels, and the tensor-parallel SwiGLU MLP with a parity check and per-phase times), each
+with its own roofline.
 
 ``--impl reference`` times the reference's CPU implementation of the headline workload
-(the numpy float64 oracle) on the host cores and prints the same line shape.
+(the numpy float64 oracle, whole workload per step) on the host cores and prints the same
+line shape.
 """
 from __future__ import annotations
 
@@ -29,6 +33,7 @@ import subprocess
 import sys
 import threading
 import time
+from concurrent.futures import ThreadPoolExecutor
 from pathlib import Path
 
 import numpy as np
@@ -37,22 +42,32 @@ ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
 ROWS, COLS = 16384, 4000
-SOFTMAX_BYTES = 2 * ROWS * COLS * 2          # read X + write Y, fp16
+SOFTMAX_BYTES = 2 * ROWS * COLS * 2          # read X + write Y, fp16 (the algorithmic count)
 RMS_ROWS, RMS_COLS = 8192, 4096
 RMS_BYTES = 2 * RMS_ROWS * RMS_COLS * 4 + RMS_COLS * 4 + RMS_ROWS * 4
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+LAUNCHES_PER_STEP = 100                       # launches in the graph that is one step
 
-# dram__bytes_read.sum + dram__bytes_write.sum per launch, from one `ncu --set full` capture of
-# `python -m compiler_b200.profile_case <op> --shape ...` per kernel at the bench shape (attention:
-# captured at [4,16,4096,128] and scaled by 4, traffic is proportional to batch x heads)
+# dram__bytes_read.sum + dram__bytes_write.sum per launch from ncu captures of
+# `python -m compiler_b200.profile_case <op> --shape ...` at the bench shape (attention:
+# captured at [4,16,4096,128] and scaled by 4, traffic is proportional to batch x heads).
+# softmax: launches 5..8 of a run over four rotating buffer sets, i.e. with the write-backs of
+# the launches before them -- the steady state, not a first launch into a clean L2.
 NCU_TRAFFIC = {
-    "softmax": 141_064_000,
+    "softmax": 197_000_000,
     "rmsnorm": 212_674_000,
     "gemm_8192": 1_181_803_000,
     "gemm_ragged": 203_472_000,
     "attention": 1_036_044_000,
     "attention_decode": 540_428_000,
 }
+
+
+def softmax_necessary_bytes(rows=ROWS, cols=COLS, row_offset=0):
+    """Bytes the mask makes necessary: row g keeps g % cols + 1 columns (2 B each) and every
+    output element is written."""
+    kept = (np.arange(rows, dtype=np.int64) + row_offset) % cols + 1
+    return int(kept.sum()) * 2 + rows * cols * 2
 
 
 def load_peaks():
@@ -195,13 +210,22 @@ class Dist:
             import torch.distributed as dist
             dist.barrier()
 
-    def max(self, value: float) -> float:
+    def _reduce(self, value: float, op_name: str) -> float:
         if not self.enabled:
             return value
         import torch.distributed as dist
         t = self.torch.tensor([value], dtype=self.torch.float64, device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dist.all_reduce(t, op=getattr(dist.ReduceOp, op_name))
         return float(t.item())
+
+    def max(self, value: float) -> float:
+        return self._reduce(value, "MAX")
+
+    def min(self, value: float) -> float:
+        return self._reduce(value, "MIN")
+
+    def sum(self, value: float) -> float:
+        return self._reduce(value, "SUM")
 
     def finish(self):
         if self.enabled:
@@ -209,10 +233,11 @@ class Dist:
             dist.destroy_process_group()
 
 
-def time_steps(torch, dist, launch, steps, warmup):
-    """W untimed steps, then exactly K timed steps between barrier+synchronize pairs.
-    Returns (ms per step over the whole region, max over ranks; mean per-launch ms from
-    CUDA-event pairs around each launch on the launching stream; wall-clock window)."""
+def time_event_pairs(torch, dist, launch, launches, warmup):
+    """Mean duration of single launches, each between its own pair of CUDA events on the
+    launching stream (the records between launches keep consecutive kernels from overlapping
+    their ramp-up and tail).  Also returns the whole region / launches (max over ranks) and
+    the wall-clock window."""
     for i in range(warmup):
         launch(i)
     torch.cuda.synchronize()
@@ -220,10 +245,10 @@ def time_steps(torch, dist, launch, steps, warmup):
     torch.cuda.synchronize()
     begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     pairs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
-             for _ in range(steps)]
+             for _ in range(launches)]
     t0 = time.monotonic()
     begin.record()
-    for i in range(steps):
+    for i in range(launches):
         pairs[i][0].record()
         launch(warmup + i)
         pairs[i][1].record()
@@ -232,32 +257,29 @@ def time_steps(torch, dist, launch, steps, warmup):
     dist.barrier()
     torch.cuda.synchronize()
     t1 = time.monotonic()
-    region_ms = dist.max(begin.elapsed_time(end)) / steps
+    region_ms = dist.max(begin.elapsed_time(end)) / launches
     launch_ms = float(np.mean([a.elapsed_time(b) for a, b in pairs]))
     return region_ms, launch_ms, (t0, t1)
 
 
-GRAPH_LAUNCHES = 100
-
-
-def time_graph_region(torch, dist, launch_on, steps, warmup):
-    """Exactly ``steps`` launches between barrier + synchronize pairs, issued as replays of a
-    captured graph of GRAPH_LAUNCHES launches (plus single launches for the remainder) on a
-    stream of the library; timed with CUDA events on that stream, max over ranks.
-    ``launch_on(stream_handle, i)`` enqueues step i.  Returns (ms per step, wall-clock window)."""
+def time_graph_steps(torch, dist, launch_on, steps, warmup, per_step):
+    """``warmup`` untimed steps, then exactly ``steps`` timed steps between barrier +
+    synchronize pairs.  A step is one replay of a captured graph of ``per_step`` launches on a
+    stream of the library; CUDA events on that stream bracket the region, max over ranks.
+    ``launch_on(stream_handle, i)`` enqueues launch i.  Returns (ms per step, window)."""
     import ctypes
     from compiler_b200 import graph
     from compiler_b200.runtime import abi
     lib = abi.lib()
     stream = graph.Stream()
-    for i in range(warmup):
+    for i in range(3):
         launch_on(stream.handle, i)
     stream.synchronize()
-    per_graph = min(GRAPH_LAUNCHES, steps)
     with graph.capture(stream) as g:
-        for i in range(per_graph):
+        for i in range(per_step):
             launch_on(stream.handle, i)
-    g.launch(stream)  # one untimed replay
+    for _ in range(max(1, warmup)):
+        g.launch(stream)
     stream.synchronize()
     begin, end = ctypes.c_void_p(), ctypes.c_void_p()
     abi.check(lib.b200_event_create(ctypes.byref(begin)))
@@ -267,10 +289,8 @@ def time_graph_region(torch, dist, launch_on, steps, warmup):
     torch.cuda.synchronize()
     t0 = time.monotonic()
     abi.check(lib.b200_event_record(begin, stream._ptr))
-    for _ in range(steps // per_graph):
+    for _ in range(steps):
         g.launch(stream)
-    for i in range(steps % per_graph):
-        launch_on(stream.handle, i)
     abi.check(lib.b200_event_record(end, stream._ptr))
     stream.synchronize()
     torch.cuda.synchronize()
@@ -295,40 +315,162 @@ def roofline(bound, algorithmic, launch_ms, peaks, source, traffic, sustained=Fa
         achieved = algorithmic / (launch_ms * 1e-3) / 1e12
         peak = peaks["bf16_tflops_sustained" if sustained else "bf16_tflops"]
         unit = "TFLOP/s"
-    return {"bound": bound, "achieved": round(achieved, 2), "peak": peak, "unit": unit,
-            "frac": round(achieved / peak, 4), "peak_source": f"of {source}", "traffic": traffic,
-            "algorithmic_per_launch": algorithmic, "launch_ms": round(launch_ms, 5)}
+    out = {"bound": bound, "achieved": round(achieved, 2), "peak": peak, "unit": unit,
+           "frac": round(achieved / peak, 4), "peak_source": f"of {source}", "traffic": traffic,
+           "algorithmic_per_launch": algorithmic, "launch_ms": round(launch_ms, 5)}
+    if bound == "tensor":
+        out["peak_kind"] = "sustained" if sustained else "burst"
+    return out
+
+
+def hbm_op(torch, dist, launch_on, steps, warmup, nbytes, peaks, source, traffic, workload,
+           launches_per_launch=1):
+    """A bandwidth-bound operator: event-pair launches first, then ``steps`` steps of
+    LAUNCHES_PER_STEP graph-replayed launches (the figure the roofline uses)."""
+    stream = torch.cuda.current_stream().cuda_stream
+    _, pair_ms, _ = time_event_pairs(torch, dist, lambda i: launch_on(stream, i), 50, 5)
+    step_ms, window = time_graph_steps(torch, dist, launch_on, steps, warmup, LAUNCHES_PER_STEP)
+    launch_ms = step_ms / LAUNCHES_PER_STEP
+    out = roofline("hbm", nbytes, launch_ms, peaks, source, traffic)
+    out["launch_ms_event_pairs"] = round(pair_ms, 5)
+    out["frac_event_pairs"] = round(nbytes / (pair_ms * 1e-3) / 1e9 / peaks["hbm_gbs"], 4)
+    out["window"] = window
+    out.update({"workload": workload, "ms_per_step": round(step_ms, 4), "steps": steps,
+                "launches_per_step": LAUNCHES_PER_STEP,
+                "value": round(nbytes * dist.world / (launch_ms * 1e-3) / 1e9, 2),
+                "unit": "GB/s",
+                "gpu_launches": steps * LAUNCHES_PER_STEP * launches_per_launch})
+    return out
+
+
+def tensor_op(torch, dist, launch_on, launches, flops, peaks, source, traffic, workload,
+              sustained_seconds=1.5):
+    """A tensor-core-bound operator.  ``burst``: ``launches`` graph-replayed launches after
+    a pause, compared with the burst peak (the cuBLAS figure that was timed the same way);
+    ``sustained``: about ``sustained_seconds`` of back-to-back launches under the power cap,
+    compared with the sustained peak."""
+    stream = torch.cuda.current_stream().cuda_stream
+    _, pair_ms, _ = time_event_pairs(torch, dist, lambda i: launch_on(stream, i),
+                                     min(launches, 10), 3)
+    torch.cuda.synchronize()
+    time.sleep(1.0)  # let the board's power average settle: the burst peak was taken that way
+    step_ms, window = time_graph_steps(torch, dist, launch_on, 1, 1, launches)
+    launch_ms = step_ms / launches
+    out = roofline("tensor", flops, launch_ms, peaks, source, traffic)
+    out["launch_ms_event_pairs"] = round(pair_ms, 5)
+    out["window"] = window
+    out.update({"workload": workload, "ms_per_step": round(launch_ms, 5),
+                "value": round(flops * dist.world / (launch_ms * 1e-3) / 1e12, 2),
+                "unit": "TFLOP/s", "gpu_launches": launches})
+    if sustained_seconds > 0:
+        per_step = 20
+        steps = max(2, int(sustained_seconds * 1e3 / (launch_ms * per_step)) + 1)
+        s_ms, s_window = time_graph_steps(torch, dist, launch_on, steps, 2, per_step)
+        s_launch = s_ms / per_step
+        rate = flops / (s_launch * 1e-3) / 1e12
+        out["sustained"] = {"achieved": round(rate, 2), "peak": peaks["bf16_tflops_sustained"],
+                            "frac": round(rate / peaks["bf16_tflops_sustained"], 4),
+                            "launch_ms": round(s_launch, 5), "launches": steps * per_step,
+                            "seconds": round(s_ms * steps * 1e-3, 3), "window": s_window}
+        out["gpu_launches"] += steps * per_step
+    return out
 
 
 # --------------------------------------------------------------------------- workloads
-def bench_softmax(torch, ops, dist, steps, warmup, peaks, source):
-    stream = torch.cuda.current_stream().cuda_stream
-    nsets = 4  # rotating buffer sets: 4 x 262 MB of traffic between reuses of a buffer > 126 MB L2
-    gen = torch.Generator(device="cuda").manual_seed(30 + dist.rank)
-    xs = [(torch.randn((ROWS, COLS), generator=gen, device="cuda") * 2).to(torch.float16)
+def softmax_buffers(torch, rows, seed, nsets=4):
+    """Rotating buffer sets: 4 x 262 MB of traffic between reuses of a buffer > 126 MB L2."""
+    gen = torch.Generator(device="cuda").manual_seed(seed)
+    xs = [(torch.randn((rows, COLS), generator=gen, device="cuda") * 2).to(torch.float16)
           for _ in range(nsets)]
-    ys = [torch.empty_like(x) for x in xs]
+    return xs, [torch.empty_like(x) for x in xs]
+
+
+def check_softmax_rows(torch, dist, ops, x, y, offset, sample):
+    """Oracle check of a few rows of one launch (outside every timed region)."""
+    from oracle import oracle
+    y.zero_()
+    ops.softmax(x, y, causal_mod=True, row_offset=offset,
+                stream=torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    worst, ok = 0.0, True
+    for r in sample:
+        got = y[r:r + 1].float().cpu().numpy().astype(np.float64)
+        ref = oracle.masked_softmax_ref(x[r:r + 1].cpu().numpy(), offset + r)
+        err = float(np.abs(got - ref).max())
+        worst = max(worst, err)
+        keep = (offset + r) % COLS + 1
+        ok = ok and bool(np.isclose(got, ref, rtol=1e-2, atol=1e-2).all()) \
+            and not got[0, keep:].any()
+    return {"ok": bool(dist.min(1.0 if ok else 0.0) == 1.0),
+            "max_abs_err": dist.max(worst), "rows_per_rank": len(sample),
+            "oracle": "masked_softmax_ref, rtol = atol = 1e-2, masked outputs exactly 0"}
+
+
+def bench_softmax(torch, ops, dist, steps, warmup, peaks, source):
+    xs, ys = softmax_buffers(torch, ROWS, 30 + dist.rank)
     offset = dist.rank * ROWS  # this rank's rows of the N-times-larger job
+    nsets = len(xs)
 
     def launch_on(handle, i):
         ops.softmax(xs[i % nsets], ys[i % nsets], causal_mod=True, row_offset=offset,
                     stream=handle)
 
-    def launch(i):
-        launch_on(stream, i)
+    out = hbm_op(torch, dist, launch_on, steps, warmup, SOFTMAX_BYTES, peaks, source,
+                 NCU_TRAFFIC["softmax"], "masked_softmax_fp16_16384x4000")
+    necessary = softmax_necessary_bytes(ROWS, COLS, offset)
+    rate = necessary / (out["launch_ms"] * 1e-3) / 1e9
+    out.update({"necessary_bytes_per_launch": necessary, "achieved_dram": round(rate, 2),
+                "frac_dram": round(rate / peaks["hbm_gbs"], 4),
+                "note": "frac counts the whole tensor read and written (the algorithmic "
+                        "figure); frac_dram counts the bytes the mask makes necessary (kept "
+                        "columns read, every output written), which is what crosses HBM"})
+    out["parity"] = check_softmax_rows(torch, dist, ops, xs[0], ys[0], offset,
+                                       [0, 1, 3999 - offset % COLS, ROWS - 1])
+    return out
 
-    # pass 1: CUDA-event pairs around single launches (reported beside the roofline; the
-    # records between launches keep consecutive kernels from overlapping their ramps)
-    _, launch_ms, _ = time_steps(torch, dist, launch, min(steps, 500), warmup)
-    ops.device_status(stream)
-    # pass 2, the timed region of the headline: exactly `steps` launches, replayed from CUDA
-    # graphs of GRAPH_LAUNCHES launches each (the loop is launch-latency bound: a 40 us kernel
-    # against a few microseconds of host work per launch), CUDA events around the region;
-    # region / steps is the average launch duration the roofline uses
-    region_ms, window = time_graph_region(torch, dist, launch_on, steps, warmup)
-    roof = roofline("hbm", SOFTMAX_BYTES, region_ms, peaks, source, NCU_TRAFFIC["softmax"])
-    roof["launch_ms_event_pairs"] = round(launch_ms, 5)
-    return {"region_ms": region_ms, "launch_ms": launch_ms, "window": window, "roofline": roof}
+
+def bench_softmax_strong(torch, ops, dist, steps, warmup, peaks, source):
+    """The BASELINE tensor [16384, 4000] split into N contiguous row blocks, one per rank
+    (global row offsets), same protocol: what the fixed problem costs on N GPUs."""
+    rows = ROWS // dist.world
+    xs, ys = softmax_buffers(torch, rows, 40 + dist.rank, nsets=4 * dist.world)
+    offset = dist.rank * rows
+    nsets = len(xs)
+
+    def launch_on(handle, i):
+        ops.softmax(xs[i % nsets], ys[i % nsets], causal_mod=True, row_offset=offset,
+                    stream=handle)
+
+    step_ms, _ = time_graph_steps(torch, dist, launch_on, steps, warmup, LAUNCHES_PER_STEP)
+    launch_ms = step_ms / LAUNCHES_PER_STEP
+    rate = SOFTMAX_BYTES / (launch_ms * 1e-3) / 1e9
+    return {"scaling": "strong", "rows_per_gpu": rows, "launch_ms": round(launch_ms, 5),
+            "value": round(rate, 2), "unit": "GB/s",
+            "frac_of_n_gpus": round(rate / (peaks["hbm_gbs"] * dist.world), 4),
+            "parity": check_softmax_rows(torch, dist, ops, xs[0], ys[0], offset,
+                                         [0, 1, rows // 2, rows - 1])}
+
+
+def _copy_rates(device, dist, hx, hy, x, y, reps=5):
+    """Pinned host <-> device copies alone, all ranks at once: what the host side gives each
+    rank with nothing else in the way (GB/s per rank, slowest rank)."""
+    from compiler_b200.runtime import abi
+    lib = abi.lib()
+    rates = {}
+    for name in ("h2d", "d2h"):
+        device.synchronize()
+        dist.barrier()
+        t0 = time.perf_counter()
+        for _ in range(reps):
+            if name == "h2d":
+                abi.check(lib.b200_memcpy_h2d(x.ptr, hx.ptr, x.nbytes, device.stream))
+            else:
+                abi.check(lib.b200_memcpy_d2h(hy.ptr, y.ptr, y.nbytes, device.stream))
+        device.synchronize()
+        seconds = dist.max(time.perf_counter() - t0) / reps
+        dist.barrier()
+        rates[name] = round(x.nbytes / seconds / 1e9, 2)
+    return rates
 
 
 def bench_softmax_e2e(dist, steps, warmup):
@@ -357,66 +499,63 @@ def bench_softmax_e2e(dist, steps, warmup):
     ms = dist.max((time.perf_counter() - t0) * 1e3) / steps
     dist.barrier()
     checksum = float(hy.array[:64].astype(np.float64).sum())  # rows sum to 1 -> 64
+    copies = _copy_rates(device, dist, hx, hy, pipe.x, pipe.y)
     pipe.close()
+    nbytes = ROWS * COLS * 2
     return {"value": round(SOFTMAX_BYTES * dist.world / (ms * 1e-3) / 1e9, 2), "unit": "GB/s",
-            "h2d_bytes_per_step": ROWS * COLS * 2, "d2h_bytes_per_step": ROWS * COLS * 2,
+            "h2d_bytes_per_step": nbytes, "d2h_bytes_per_step": nbytes,
             "ms_per_step": round(ms, 4), "steps": steps, "chunks": 8, "streams": 2,
             "timer": "host clock around the blocking call",
-            "result_check_rowsum64": round(checksum, 3)}
+            "result_check_rowsum64": round(checksum, 3),
+            "copy_only_gbs_per_rank": copies,
+            "copy_bound_ms": round(max(nbytes / (copies["h2d"] * 1e6),
+                                       nbytes / (copies["d2h"] * 1e6)), 4),
+            "limit": "each step moves 131 MB in and 131 MB out per rank over PCIe; "
+                     "copy_only_gbs_per_rank is what the host side gives a rank when all "
+                     "ranks copy at once, copy_bound_ms the step time that alone allows"}
 
 
 def bench_softmax_unmasked(torch, ops, dist, steps, warmup, peaks, source):
     """The headline's shape without the mask (the reference's softmax.py operator itself):
     every element is read and written, so algorithmic bytes and DRAM traffic coincide."""
-    stream = torch.cuda.current_stream().cuda_stream
-    nsets = 4
-    gen = torch.Generator(device="cuda").manual_seed(35 + dist.rank)
-    xs = [(torch.randn((ROWS, COLS), generator=gen, device="cuda") * 2).to(torch.float16)
-          for _ in range(nsets)]
-    ys = [torch.empty_like(x) for x in xs]
+    xs, ys = softmax_buffers(torch, ROWS, 35 + dist.rank)
+    nsets = len(xs)
 
     def launch_on(handle, i):
         ops.softmax(xs[i % nsets], ys[i % nsets], stream=handle)
 
-    _, launch_ms, _ = time_steps(torch, dist, lambda i: launch_on(stream, i), steps, warmup)
-    region_ms, window = time_graph_region(torch, dist, launch_on, steps, warmup)
-    out = roofline("hbm", SOFTMAX_BYTES, region_ms, peaks, source, None)
-    out["launch_ms_event_pairs"] = round(launch_ms, 5)
-    out["window"] = window
-    out.update({"workload": "softmax_fp16_16384x4000_unmasked", "ms_per_step": round(region_ms, 5),
-                "value": round(SOFTMAX_BYTES * dist.world / (region_ms * 1e-3) / 1e9, 2),
-                "unit": "GB/s", "gpu_launches": steps})
-    return out
+    return hbm_op(torch, dist, launch_on, steps, warmup, SOFTMAX_BYTES, peaks, source, None,
+                  "softmax_fp16_16384x4000_unmasked")
 
 
-def bench_rmsnorm(torch, ops, dist, steps, warmup, peaks, source):
-    stream = torch.cuda.current_stream().cuda_stream
-    nsets = 4
+def bench_rmsnorm(torch, ops, dist, steps, warmup, peaks, source, strong=False):
+    rows = RMS_ROWS // dist.world if strong else RMS_ROWS
+    nsets = 4 * (dist.world if strong else 1)
     gen = torch.Generator(device="cuda").manual_seed(31 + dist.rank)
-    xs = [torch.randn((RMS_ROWS, RMS_COLS), generator=gen, device="cuda") for _ in range(nsets)]
+    xs = [torch.randn((rows, RMS_COLS), generator=gen, device="cuda") for _ in range(nsets)]
     w = torch.rand((RMS_COLS,), generator=gen, device="cuda") + 0.5
     ys = [torch.empty_like(x) for x in xs]
-    r = torch.empty((RMS_ROWS,), device="cuda")
+    r = torch.empty((rows,), device="cuda")
 
     def launch_on(handle, i):
         ops.rmsnorm(xs[i % nsets], w, ys[i % nsets], r, eps=1e-6, stream=handle)
 
-    _, launch_ms, _ = time_steps(torch, dist, lambda i: launch_on(stream, i), steps, warmup)
-    region_ms, window = time_graph_region(torch, dist, launch_on, steps, warmup)
-    out = roofline("hbm", RMS_BYTES, region_ms, peaks, source, NCU_TRAFFIC["rmsnorm"])
-    out["launch_ms_event_pairs"] = round(launch_ms, 5)
-    out["window"] = window
-    out.update({"workload": "rmsnorm_fp32_8192x4096", "ms_per_step": round(region_ms, 5),
-                "value": round(RMS_BYTES * dist.world / (region_ms * 1e-3) / 1e9, 2),
-                "unit": "GB/s", "gpu_launches": steps})
-    return out
+    if strong:
+        step_ms, _ = time_graph_steps(torch, dist, launch_on, steps, warmup, LAUNCHES_PER_STEP)
+        launch_ms = step_ms / LAUNCHES_PER_STEP
+        rate = RMS_BYTES / (launch_ms * 1e-3) / 1e9
+        return {"scaling": "strong", "rows_per_gpu": rows, "launch_ms": round(launch_ms, 5),
+                "value": round(rate, 2), "unit": "GB/s",
+                "frac_of_n_gpus": round(rate / (peaks["hbm_gbs"] * dist.world), 4)}
+    return hbm_op(torch, dist, launch_on, steps, warmup, RMS_BYTES, peaks, source,
+                  NCU_TRAFFIC["rmsnorm"], "rmsnorm_fp32_8192x4096")
 
 
-def bench_gemm(torch, ops, dist, steps, warmup, peaks, source, shape, key):
+def bench_gemm(torch, ops, dist, launches, peaks, source, shape, key, strong=False):
     from compiler_b200.runtime import abi
-    stream = torch.cuda.current_stream().cuda_stream
-    m, n, k = shape
-    nsets = 2  # A, B, C rotate: > 126 MB L2 between reuses
+    m_full, n, k = shape
+    m = -(-m_full // dist.world) if strong else m_full   # row blocks of A / C
+    nsets = 2 if not strong else 2 * dist.world  # A, B, C rotate: > 126 MB L2 between reuses
     gen = torch.Generator(device="cuda").manual_seed(32 + dist.rank)
     sets = []
     for _ in range(nsets):
@@ -429,23 +568,23 @@ def bench_gemm(torch, ops, dist, steps, warmup, peaks, source, shape, key):
         a, b, c = sets[i % nsets]
         ops.gemm(a, b, c, bias=bias, act=abi.ACT_GELU_TANH, stream=handle)
 
-    _, launch_ms, _ = time_steps(torch, dist, lambda i: launch_on(stream, i), steps, warmup)
-    ops.device_status(stream)
-    region_ms, window = time_graph_region(torch, dist, launch_on, steps, warmup)
-    flops = 2 * m * n * k
-    out = roofline("tensor", flops, region_ms, peaks, source, NCU_TRAFFIC[key])
-    out["launch_ms_event_pairs"] = round(launch_ms, 5)
-    out["window"] = window
-    out.update({"workload": f"gemm_bf16_bias_gelu_tanh_{m}x{n}x{k}",
-                "ms_per_step": round(region_ms, 5),
-                "value": round(flops * dist.world / (region_ms * 1e-3) / 1e12, 2),
-                "unit": "TFLOP/s", "gpu_launches": steps})
-    return out
+    flops = 2 * m_full * n * k
+    if strong:
+        time.sleep(1.0)
+        step_ms, _ = time_graph_steps(torch, dist, launch_on, 1, 1, launches)
+        launch_ms = step_ms / launches
+        rate = flops / (launch_ms * 1e-3) / 1e12
+        return {"scaling": "strong", "rows_per_gpu": m, "launch_ms": round(launch_ms, 5),
+                "value": round(rate, 2), "unit": "TFLOP/s",
+                "frac_of_n_gpus": round(rate / (peaks["bf16_tflops"] * dist.world), 4)}
+    return tensor_op(torch, dist, launch_on, launches, flops, peaks, source, NCU_TRAFFIC[key],
+                     f"gemm_bf16_bias_gelu_tanh_{m_full}x{n}x{k}",
+                     sustained_seconds=1.5 if key == "gemm_8192" else 0)
 
 
-def bench_attention(torch, ops, dist, steps, warmup, peaks, source):
-    stream = torch.cuda.current_stream().cuda_stream
-    z, h, n, d = 8, 32, 4096, 128
+def bench_attention(torch, ops, dist, launches, peaks, source, strong=False):
+    z_full, h, n, d = 8, 32, 4096, 128
+    z = max(1, z_full // dist.world) if strong else z_full  # batch x heads blocks
     gen = torch.Generator(device="cuda").manual_seed(33 + dist.rank)
     q, k, v = (torch.randn((z, h, n, d), generator=gen, device="cuda").to(torch.bfloat16)
                for _ in range(3))
@@ -455,24 +594,24 @@ def bench_attention(torch, ops, dist, steps, warmup, peaks, source):
     def launch_on(handle, i):
         ops.attention(q, k, v, o, lse=lse, scale=1.0 / d ** 0.5, causal=True, stream=handle)
 
-    _, launch_ms, _ = time_steps(torch, dist, lambda i: launch_on(stream, i), steps, warmup)
-    ops.device_status(stream)
-    region_ms, window = time_graph_region(torch, dist, launch_on, steps, warmup)
-    flops = 4 * z * h * d * n * (n + 1) // 2  # causal-exact: 2 matmuls over the kept triangle
-    out = roofline("tensor", flops, region_ms, peaks, source, NCU_TRAFFIC["attention"])
-    out["launch_ms_event_pairs"] = round(launch_ms, 5)
-    out["window"] = window
-    out.update({"workload": "attn_fwd_causal_bf16_8x32x4096x128", "flop_convention": "causal-exact",
-                "ms_per_step": round(region_ms, 5),
-                "value": round(flops * dist.world / (region_ms * 1e-3) / 1e12, 2),
-                "unit": "TFLOP/s", "gpu_launches": steps})
+    flops = 4 * z_full * h * d * n * (n + 1) // 2  # causal-exact: 2 matmuls over the kept triangle
+    if strong:
+        time.sleep(1.0)
+        step_ms, _ = time_graph_steps(torch, dist, launch_on, 1, 1, launches)
+        launch_ms = step_ms / launches
+        rate = flops / (launch_ms * 1e-3) / 1e12
+        return {"scaling": "strong", "batch_per_gpu": z, "launch_ms": round(launch_ms, 5),
+                "value": round(rate, 2), "unit": "TFLOP/s",
+                "frac_of_n_gpus": round(rate / (peaks["bf16_tflops"] * dist.world), 4)}
+    out = tensor_op(torch, dist, launch_on, launches, flops, peaks, source,
+                    NCU_TRAFFIC["attention"], "attn_fwd_causal_bf16_8x32x4096x128")
+    out["flop_convention"] = "causal-exact"
     return out
 
 
 def bench_attention_decode(torch, ops, dist, steps, warmup, peaks, source):
     """One query row per (batch, head) against a K / V cache of 4096 keys: the K and V of
     8 x 32 heads are 537 MB, read once per launch (four times the L2)."""
-    stream = torch.cuda.current_stream().cuda_stream
     rows, n, d = 8 * 32, 4096, 128
     gen = torch.Generator(device="cuda").manual_seed(36 + dist.rank)
     q = torch.randn((rows, d), generator=gen, device="cuda").to(torch.bfloat16)
@@ -483,94 +622,331 @@ def bench_attention_decode(torch, ops, dist, steps, warmup, peaks, source):
     def launch_on(handle, i):
         ops.attention_decode(q, k, v, o, scale=1.0 / d ** 0.5, stream=handle)
 
-    _, launch_ms, _ = time_steps(torch, dist, lambda i: launch_on(stream, i), steps, warmup)
-    region_ms, window = time_graph_region(torch, dist, launch_on, steps, warmup)
     nbytes = 2 * rows * n * d * 2
-    out = roofline("hbm", nbytes, region_ms, peaks, source, NCU_TRAFFIC["attention_decode"])
-    out["launch_ms_event_pairs"] = round(launch_ms, 5)
-    out["window"] = window
-    out.update({"workload": "attn_decode_bf16_256rows_4096keys_128", "ms_per_step": round(region_ms, 5),
-                "value": round(nbytes * dist.world / (region_ms * 1e-3) / 1e9, 2),
-                "unit": "GB/s", "gpu_launches": 2 * steps})
-    return out
+    return hbm_op(torch, dist, launch_on, steps, warmup, nbytes, peaks, source,
+                  NCU_TRAFFIC["attention_decode"], "attn_decode_bf16_256rows_4096keys_128",
+                  launches_per_launch=2)
 
 
-def bench_tp_mlp(torch, dist, steps, warmup, peaks, source, collective="nccl"):
+# --------------------------------------------------------------------------- TP MLP
+MLP_M, MLP_HIDDEN, MLP_FFN = 4096, 4096, 14336
+
+
+def _mlp_expected_rows(torch, dist, mlp, x, rows):
+    """float64 oracle of the selected rows of y from the gathered weight shards (rank 0
+    computes, every rank receives)."""
+    import torch.distributed as tdist
+    from oracle import oracle
+
+    def gathered(t, dim):
+        if not dist.enabled:
+            return t
+        parts = [torch.empty_like(t) for _ in range(dist.world)]
+        tdist.all_gather(parts, t.contiguous())
+        return torch.cat(parts, dim=dim)
+
+    wg, wu, wd = gathered(mlp.wg, 1), gathered(mlp.wu, 1), gathered(mlp.wd, 0)
+    expected = torch.empty((len(rows), MLP_HIDDEN), dtype=torch.float64, device="cuda")
+    if dist.rank == 0:
+        host = lambda t: t.float().cpu().numpy()  # noqa: E731
+        ref = oracle.swiglu_mlp_ref(host(x[rows]), host(wg), host(wu), host(wd))
+        expected.copy_(torch.from_numpy(ref))
+    del wg, wu, wd
+    if dist.enabled:
+        tdist.broadcast(expected, src=0)
+    return expected.cpu().numpy()
+
+
+def bench_tp_mlp(torch, ops, dist, launches, peaks, source, collective):
+    """y = (silu(x Wg) * (x Wu)) Wd with the ffn dimension sharded over the ranks (strong
+    scaling: the problem is fixed).  Outside the timed region every rank compares a spread of
+    rows of ITS y with the float64 oracle of the unsharded MLP, and one more pass records a
+    CUDA event after each phase."""
     from compiler_b200 import tp_mlp
-    mlp = tp_mlp.TensorParallelMLP.synthetic(hidden=4096, ffn=14336, rank=dist.rank,
+    mlp = tp_mlp.TensorParallelMLP.synthetic(hidden=MLP_HIDDEN, ffn=MLP_FFN, rank=dist.rank,
                                              world=dist.world, seed=34, collective=collective)
     gen = torch.Generator(device="cuda").manual_seed(35)  # x is replicated: same seed on all ranks
-    x = torch.randn((4096, 4096), generator=gen, device="cuda").to(torch.bfloat16)
-    y = torch.empty((4096, 4096), device="cuda", dtype=torch.bfloat16)
+    x = torch.randn((MLP_M, MLP_HIDDEN), generator=gen, device="cuda").to(torch.bfloat16)
+    stream = torch.cuda.current_stream().cuda_stream
+    result = {}
+    # the NCCL path (and one GPU) writes into a caller's buffer; the peer and in-switch paths
+    # return their own symmetric output buffer
+    y_buf = (torch.empty((MLP_M, MLP_HIDDEN), device="cuda", dtype=torch.bfloat16)
+             if (collective == "nccl" or not dist.enabled) else None)
 
     def launch(i):
-        mlp.forward(x, y)
+        result["y"] = mlp.forward(x, y_buf)
 
-    region_ms, launch_ms, window = time_steps(torch, dist, launch, steps, warmup)
-    flops = 3 * 2 * 4096 * 4096 * 14336
+    region_ms, launch_ms, window = time_event_pairs(torch, dist, launch, launches, 3)
+    ops.device_status(stream)
+
+    # ---- parity: first and last row of every owner's block, tile edges, against the oracle
+    block = MLP_M // max(dist.world, 1)
+    rows = sorted({r for k in range(dist.world) for r in (k * block, (k + 1) * block - 1)}
+                  | {127, 128, 255, 256, MLP_M // 2 + 3})
+    result["y"].zero_()
+    torch.cuda.synchronize()
+    dist.barrier()
+    y = mlp.forward(x, y_buf)
+    torch.cuda.synchronize()
+    ops.device_status(stream)
+    got = y[rows].float().cpu().numpy().astype(np.float64)
+    expected = _mlp_expected_rows(torch, dist, mlp, x, rows)
+    err = float(np.abs(got - expected).max())
+    ok = bool(np.isclose(got, expected, rtol=2e-2, atol=2e-2).all())
+    parity = {"ok": bool(dist.min(1.0 if ok else 0.0) == 1.0), "max_abs_err": dist.max(err),
+              "rows": len(rows), "checked_on": "every rank's own output",
+              "oracle": "swiglu_mlp_ref (float64, unsharded), rtol = atol = 2e-2"}
+
+    # ---- per-phase times: events after each phase of `launches` further passes
+    names, samples = [], []
+    for _ in range(launches):
+        marks = [torch.cuda.Event(enable_timing=True)]
+        marks[0].record()
+        labels = []
+
+        def mark(name, marks=marks, labels=labels):
+            event = torch.cuda.Event(enable_timing=True)
+            event.record()
+            marks.append(event)
+            labels.append(name)
+
+        mlp.forward(x, y_buf, mark=mark)
+        torch.cuda.synchronize()
+        names = labels
+        samples.append([marks[i].elapsed_time(marks[i + 1]) for i in range(len(labels))])
+    phases = {name: round(dist.max(float(np.mean([s[i] for s in samples]))), 5)
+              for i, name in enumerate(names)}
+
+    flops = 3 * 2 * MLP_M * MLP_HIDDEN * MLP_FFN
     out = roofline("tensor", flops // dist.world, launch_ms, peaks, source, None)
     out["window"] = window
+    described = {
+        "nccl": "fp32 partials, NCCL all-reduce per row chunk overlapped with the next chunk's GEMM",
+        "peer": "reduce-scatter by peer stores in the GEMM epilogue + sum and broadcast kernel",
+        "nvls": "16-bit partials in symmetric memory, in-switch sum and broadcast "
+                "(multimem.ld_reduce / multimem.st), result returned in place",
+        "none": "one GPU: the two GEMMs alone (anchor of the strong-scaling curve)",
+    }
+    partial_bytes = MLP_M * MLP_HIDDEN * (4 if collective == "nccl" else 2)
     out.update({"workload": f"tp_swiglu_mlp_bf16_tp{dist.world}", "scaling": "strong",
-                "collective": ("NCCL all-reduce per row chunk, overlapped with the next chunk's GEMM"
-                               if collective == "nccl" else
-                               "reduce-scatter by peer stores in the GEMM epilogue + sum and "
-                               "broadcast kernel"),
+                "collective": described[collective if dist.enabled else "none"],
                 "ms_per_step": round(region_ms, 5),
                 "value": round(flops / (region_ms * 1e-3) / 1e12, 2), "unit": "TFLOP/s",
-                "allreduce_bytes_per_rank": 4096 * 4096 * 2,
-                "gpu_launches": steps * mlp.kernels_per_forward})
+                "allreduce_bytes_per_rank": partial_bytes if dist.enabled else 0,
+                "parity": parity, "phases_ms": phases,
+                "gpu_launches": (3 + 2 * launches + 1) * mlp.kernels_per_forward})
+    if not parity["ok"]:
+        out["value"] = None
+        out["invalid"] = "the result does not match the oracle; the rate is withheld"
     return out
+
+
+# --------------------------------------------------------------------------- siblings
+def bench_siblings(torch, ops, peaks):
+    """Rates of the sibling kernels at sizes well above the L2: four rotating buffer sets,
+    20 launches per CUDA graph, two replays timed with CUDA events on the capturing stream;
+    bytes are the algorithmic ones (every operand read once, the result written once)."""
+    import ctypes
+    from compiler_b200 import graph
+    from compiler_b200.runtime import abi
+    lib = abi.lib()
+    rows, cols, sets_default, launches = 16384, 4096, 4, 20
+    stream = graph.Stream()
+    S = stream.handle
+    records = {}
+
+    def timed(launch, sets):
+        for i in range(3):
+            launch(i % sets)
+        stream.synchronize()
+        with graph.capture(stream) as g:
+            for i in range(launches):
+                launch(i % sets)
+        g.launch(stream)
+        stream.synchronize()
+        begin, end = ctypes.c_void_p(), ctypes.c_void_p()
+        abi.check(lib.b200_event_create(ctypes.byref(begin)))
+        abi.check(lib.b200_event_create(ctypes.byref(end)))
+        abi.check(lib.b200_event_record(begin, stream._ptr))
+        g.launch(stream)
+        g.launch(stream)
+        abi.check(lib.b200_event_record(end, stream._ptr))
+        stream.synchronize()
+        ms = ctypes.c_float()
+        abi.check(lib.b200_event_elapsed_ms(begin, end, ctypes.byref(ms)))
+        lib.b200_event_destroy(begin)
+        lib.b200_event_destroy(end)
+        g.close()
+        return ms.value / (2 * launches)
+
+    def report(name, launch, nbytes=None, flop=None, sets=sets_default):
+        ms = timed(launch, sets)
+        record = {"us_per_launch": round(ms * 1e3, 2)}
+        if nbytes:
+            rate = nbytes / ms / 1e6
+            record.update({"GBps": round(rate, 1), "frac": round(rate / peaks["hbm_gbs"], 3)})
+        if flop:
+            rate = flop / ms / 1e9
+            record.update({"TFLOPs": round(rate, 1), "frac": round(rate / peaks["bf16_tflops"], 3)})
+        records[name] = record
+
+    def rnd(shape, dtype, scale=1.0):
+        return (torch.randn(shape, device="cuda") * scale).to(dtype)
+
+    torch.manual_seed(0)
+    for dtype, tag, es in ((torch.bfloat16, "bf16", 2), (torch.float32, "f32", 4)):
+        n = rows * cols
+        xs = [rnd((rows, cols), dtype) for _ in range(sets_default)]
+        ys = [rnd((rows, cols), dtype) for _ in range(sets_default)]
+        outs = [torch.empty((rows, cols), device="cuda", dtype=dtype) for _ in range(sets_default)]
+        flat = lambda t: t.view(-1)  # noqa: E731
+        report(f"swiglu_{tag}", lambda i: ops.swiglu(xs[i], ys[i], outs[i], stream=S), 3 * n * es)
+        report(f"gelu_erf_{tag}", lambda i: ops.elementwise(
+            abi.EW_GELU_ERF, flat(xs[i]), flat(outs[i]), stream=S), 2 * n * es)
+        report(f"add_gelu_erf_{tag}", lambda i: ops.elementwise(
+            abi.EW_ADD_GELU_ERF, flat(xs[i]), flat(outs[i]), b=flat(ys[i]), p0=1.5, stream=S),
+            3 * n * es)
+        report(f"geglu_tanh_{tag}", lambda i: ops.elementwise(
+            abi.EW_GEGLU_TANH, flat(xs[i]), flat(outs[i]), b=flat(ys[i]), stream=S), 3 * n * es)
+        bias = rnd((cols,), dtype)
+        report(f"bias_scale_clamp_gelu_{tag}", lambda i: ops.elementwise(
+            abi.EW_BIAS_SCALE_CLAMP_GELU, flat(xs[i]), flat(outs[i]), b=bias, p0=0.5, p1=-1.0,
+            p2=1.0, stream=S), 2 * n * es)
+        report(f"softmax_{tag}", lambda i: ops.softmax(xs[i], outs[i], stream=S), 2 * n * es)
+        report(f"softmax_mul_{tag}", lambda i: ops.softmax_variant(
+            xs[i], outs[i], mul=ys[i], stream=S), 3 * n * es)
+        positive = [x.abs() + 0.1 for x in xs]
+        report(f"softmax_log_{tag}", lambda i: ops.softmax_variant(
+            positive[i], outs[i], log_input=True, stream=S), 2 * n * es)
+        del positive
+        w = rnd((cols,), dtype)
+        report(f"rmsnorm_zero_centred_gamma_{tag}", lambda i: ops.rmsnorm(
+            xs[i], w, outs[i], None, eps=1e-6, gamma_offset=1.0, stream=S), 2 * n * es)
+        quarter = [rnd((rows, cols // 4), dtype) for _ in range(sets_default)]
+        report(f"repeat4_log_softmax_{tag}", lambda i: ops.repeat_log_softmax(
+            quarter[i], outs[i], 4, stream=S), (n // 4 + n) * es)
+        del xs, ys, outs, quarter
+        torch.cuda.empty_cache()
+
+    k, n = 16384, 8192
+    q = [torch.randint(-128, 127, (k, n), device="cuda", dtype=torch.int8)
+         for _ in range(sets_default)]
+    scale = rnd((n,), torch.bfloat16)
+    deq = [torch.empty((k, n), device="cuda", dtype=torch.bfloat16) for _ in range(sets_default)]
+    report("dequantize_int8_to_bf16", lambda i: ops.dequantize_cols(q[i], scale, deq[i], stream=S),
+           k * n * 3)
+    del q, deq
+    torch.cuda.empty_cache()
+
+    m, k, n = 8192, 4096, 8192
+    xs = [rnd((m, k), torch.bfloat16) for _ in range(3)]
+    w = rnd((k, n), torch.bfloat16, 0.02)
+    w2 = rnd((k, n), torch.bfloat16, 0.02)
+    g = rnd((k,), torch.bfloat16)
+    outs = [torch.empty((m, n), device="cuda", dtype=torch.bfloat16) for _ in range(3)]
+    scratch_w = torch.empty((k, n), device="cuda", dtype=torch.bfloat16)
+    scratch_r = torch.empty((m,), device="cuda")
+    report("rms_matmul_bf16_8192x8192x4096", lambda i: ops.rms_matmul(
+        xs[i], g, w, outs[i], scratch_w, scratch_r, stream=S), flop=2 * m * n * k, sets=3)
+    gamma, beta, bias = (rnd((n,), torch.bfloat16) for _ in range(3))
+    mins = torch.full((m,), float("inf"), device="cuda")
+    report("gemm_groupnorm_rowmin_bf16_8192x8192x4096", lambda i: ops.gemm_groupnorm_rowmin(
+        xs[i], w, gamma, beta, mins, bias=bias, group_size=32, stream=S), flop=2 * m * n * k,
+        sets=3)
+    report("gemm_swiglu_dual_bf16_8192x8192x4096", lambda i: ops.gemm(
+        xs[i], w, outs[i], b2=w2, act=abi.ACT_SWIGLU, stream=S), flop=4 * m * n * k, sets=3)
+    del xs, outs, w, w2, scratch_w
+    torch.cuda.empty_cache()
+    big = 65536
+    x2 = [rnd((big, 4096), torch.bfloat16) for _ in range(3)]
+    wl = rnd((64, 4096), torch.bfloat16, 0.02)
+    y2 = [torch.empty((big, 64), device="cuda", dtype=torch.bfloat16) for _ in range(3)]
+    report("linear_log_softmax_bf16_65536x64x4096", lambda i: ops.linear_log_softmax(
+        x2[i], wl, y2[i], stream=S), (big * 4096 + big * 64 + 64 * 4096) * 2, sets=3)
+    stream.synchronize()
+    ops.device_status(S)
+    stream.close()
+    return {"protocol": "graphs of 20 launches on rotating buffer sets, two replays timed; "
+                        "fractions of the measured copy rate / cuBLAS bf16 burst rate",
+            "kernels": records, "gpu_launches": len(records) * (3 + 3 * launches)}
 
 
 # --------------------------------------------------------------------------- CPU legs
-def cpu_softmax_sample(rows):
-    """The numpy oracle on the first `rows` rows of the headline workload."""
-    from oracle import oracle
-    rng = np.random.default_rng(30)
-    x = (rng.standard_normal((rows, COLS), dtype=np.float32) * 2).astype(np.float16)
-    t0 = time.perf_counter()
-    y = oracle.masked_softmax_ref(x, 0).astype(np.float16)
-    return time.perf_counter() - t0, y
+def headline_config():
+    return {"workload": "masked_softmax_fp16_16384x4000",
+            "mask": "col > row % 4000 -> -inf", "io_dtype": "f16",
+            "rows_per_gpu": ROWS, "sharding": "rows, no collective",
+            "l2": "4 rotating buffer sets (1.05 GB) between reuses, L2 is 126 MB",
+            "launching": f"native arm: one step = one replay of a CUDA graph of "
+                         f"{LAUNCHES_PER_STEP} launches; reference arm: one step = one pass"}
+
+
+class CpuReference:
+    """The reference's CPU implementation of the headline workload: the numpy float64 oracle
+    over all 16384 x 4000 elements per pass.  Rows are independent, so the rows are cut into
+    blocks that a pool of threads works through (numpy releases the GIL inside its loops), the
+    way the reference's own split_ref (ops/harness/opslib/case.py:591-632) runs row-independent
+    oracles; the thread count is reported."""
+    BLOCK = 256
+
+    def __init__(self):
+        rng = np.random.default_rng(30)
+        self.x = (rng.standard_normal((ROWS, COLS), dtype=np.float32) * 2).astype(np.float16)
+        self.y = np.empty_like(self.x)
+        self.threads = max(1, len(os.sched_getaffinity(0)))
+        self.pool = ThreadPoolExecutor(max_workers=self.threads)
+
+    def _block(self, lo):
+        from oracle import oracle
+        hi = min(lo + self.BLOCK, ROWS)
+        self.y[lo:hi] = oracle.masked_softmax_ref(self.x[lo:hi], lo).astype(np.float16)
+
+    def one_pass(self) -> float:
+        t0 = time.perf_counter()
+        list(self.pool.map(self._block, range(0, ROWS, self.BLOCK)))
+        return time.perf_counter() - t0
+
+    def measure(self, steps, warmup):
+        for _ in range(max(1, warmup)):
+            self.one_pass()
+        times = [self.one_pass() for _ in range(steps)]
+        return float(np.mean(times)), times
+
+    def describe(self, steps, seconds):
+        return (f"numpy float64 oracle over all {ROWS} x {COLS} elements per pass, rows in "
+                f"blocks of {self.BLOCK} on {self.threads} threads, mean of {steps} passes "
+                f"({seconds:.3f} s each)")
 
 
 def cpu_baseline():
-    # about ten seconds of host work: an eighth of the workload's rows per repetition
-    rows, elapsed, reps = 2048, 0.0, 0
-    best = None
-    while elapsed < 10.0 and reps < 64:
-        t, _ = cpu_softmax_sample(rows)
-        best = t if best is None else min(best, t)
-        elapsed += t
-        reps += 1
-    return {"value": round(2 * rows * COLS * 2 / best / 1e9, 4), "unit": "GB/s", "cores": 1,
-            "kind": "port",
-            "sample": f"numpy float64 oracle on {rows} of {ROWS} rows x {COLS} cols, best of "
-                      f"{reps} ({best:.3f} s); elementwise numpy is single-threaded",
+    ref = CpuReference()
+    steps = 5
+    seconds, _ = ref.measure(steps, 1)
+    return {"value": round(SOFTMAX_BYTES / seconds / 1e9, 4), "unit": "GB/s",
+            "cores": ref.threads, "kind": "port", "sample": ref.describe(steps, seconds),
             "host_cores_available": len(os.sched_getaffinity(0))}
 
 
 def reference_arm(args):
     """Reference arm: the reference's CPU implementation (numpy float64 ``ref``, restated in
-    oracle/oracle.py) of the headline workload on the host cores."""
+    oracle/oracle.py) of the headline workload on the host cores, the whole workload per
+    step, with the protocol of ``cpu_baseline``."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    rows = 1024
-    for _ in range(max(args.warmup, 1)):
-        cpu_softmax_sample(rows)
-    times = [cpu_softmax_sample(rows)[0] for _ in range(args.steps)]
-    ms = float(np.mean(times)) * 1e3
-    value = round(2 * rows * COLS * 2 / (ms * 1e-3) / 1e9, 4)
+    ref = CpuReference()
+    seconds, _ = ref.measure(args.steps, max(args.warmup, 1))
+    value = round(SOFTMAX_BYTES / seconds / 1e9, 4)
     line = {
         "impl": "reference", "metric": "masked_softmax_fp16_hbm_throughput", "value": value,
         "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": round(ms, 3), "higher_is_better": True, "scaling": "weak",
+        "ms_per_step": round(seconds * 1e3, 3), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f64", "data": "synthetic",
-        "config": {"workload": "masked_softmax_fp16_16384x4000",
-                   "step": f"numpy oracle on a {rows}-row sample of the workload"},
-        "cpu_baseline": {"value": value, "unit": "GB/s", "cores": 1, "kind": "port",
-                         "sample": f"{rows} of {ROWS} rows per step; the reference's ref() is "
-                                   "single-threaded elementwise numpy"},
+        "config": headline_config(),
+        "step": "one pass of the numpy oracle over the whole workload",
+        "cpu_baseline": {"value": value, "unit": "GB/s", "cores": ref.threads, "kind": "port",
+                         "sample": ref.describe(args.steps, seconds)},
         "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -581,12 +957,13 @@ def reference_arm(args):
 def main():
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
-    parser.add_argument("--steps", type=int, default=6000)
-    parser.add_argument("--warmup", type=int, default=20)
+    parser.add_argument("--steps", type=int, default=20,
+                        help=f"timed steps of the headline; one step = {LAUNCHES_PER_STEP} launches")
+    parser.add_argument("--warmup", type=int, default=5)
     parser.add_argument("--impl", default="native", choices=["native", "reference"])
     parser.add_argument("--ops", default="all",
-                        help="comma list of extra operators: softmax_unmasked,rmsnorm,gemm,gemm_ragged,attention,attention_decode,"
-                             "tp_mlp,none,all")
+                        help="comma list of extra operators: softmax_unmasked,rmsnorm,gemm,"
+                             "gemm_ragged,attention,attention_decode,siblings,tp_mlp,none,all")
     args = parser.parse_args()
     if args.impl == "reference":
         reference_arm(args)
@@ -602,16 +979,21 @@ def main():
     dist.init(torch)
     peaks, source = load_peaks()
     warmup = max(args.warmup, 3)
+    steps = max(1, args.steps)
     uuid = getattr(torch.cuda.get_device_properties(dist.local_rank), "uuid", None)
     sampler = ClockSampler(dist.local_rank, f"GPU-{uuid}" if uuid is not None else None)
     if dist.rank == 0:
         sampler.start()
 
-    head = bench_softmax(torch, ops, dist, args.steps, warmup, peaks, source)
-    e2e = bench_softmax_e2e(dist, min(args.steps, 20), 3)
+    head = bench_softmax(torch, ops, dist, steps, warmup, peaks, source)
+    strong = None
+    if dist.enabled:
+        strong = bench_softmax_strong(torch, ops, dist, min(steps, 20), 3, peaks, source)
+    e2e = bench_softmax_e2e(dist, min(steps, 20), 3)
 
     wanted = args.ops.split(",")
-    extra_steps = max(3, min(args.steps, 20))
+    op_steps = max(3, min(steps, 20))   # steps of LAUNCHES_PER_STEP launches for the HBM-bound ops
+    launches = 20                       # launches of the tensor-core ops' burst region
     extras = {}
 
     def want(name):
@@ -624,36 +1006,62 @@ def main():
         return True
 
     if want("softmax_unmasked"):
-        extras["softmax_unmasked"] = bench_softmax_unmasked(
-            torch, ops, dist, max(extra_steps, min(args.steps, 200)), warmup, peaks, source)
+        extras["softmax_unmasked"] = bench_softmax_unmasked(torch, ops, dist, op_steps, 3, peaks,
+                                                            source)
     if want("rmsnorm"):
-        extras["rmsnorm"] = bench_rmsnorm(torch, ops, dist, max(extra_steps, min(args.steps, 200)),
-                                          warmup, peaks, source)
+        extras["rmsnorm"] = bench_rmsnorm(torch, ops, dist, op_steps, 3, peaks, source)
+        if dist.enabled:
+            extras["rmsnorm"]["strong"] = bench_rmsnorm(torch, ops, dist, op_steps, 3, peaks,
+                                                        source, strong=True)
     if want("gemm"):
-        extras["gemm"] = bench_gemm(torch, ops, dist, extra_steps, 3, peaks, source,
+        extras["gemm"] = bench_gemm(torch, ops, dist, launches, peaks, source,
                                     (8192, 8192, 8192), "gemm_8192")
+        if dist.enabled:
+            extras["gemm"]["strong"] = bench_gemm(torch, ops, dist, launches, peaks, source,
+                                                  (8192, 8192, 8192), "gemm_8192", strong=True)
     if want("gemm_ragged"):
-        extras["gemm_ragged"] = bench_gemm(torch, ops, dist, extra_steps, 3, peaks, source,
+        extras["gemm_ragged"] = bench_gemm(torch, ops, dist, launches, peaks, source,
                                            (4097, 11008, 4096), "gemm_ragged")
+        if dist.enabled:
+            extras["gemm_ragged"]["strong"] = bench_gemm(
+                torch, ops, dist, launches, peaks, source, (4097, 11008, 4096), "gemm_ragged",
+                strong=True)
     if want("attention"):
-        extras["attention"] = bench_attention(torch, ops, dist, max(3, min(args.steps, 10)), 3,
-                                              peaks, source)
+        extras["attention"] = bench_attention(torch, ops, dist, 10, peaks, source)
+        if dist.enabled:
+            extras["attention"]["strong"] = bench_attention(torch, ops, dist, 10, peaks, source,
+                                                            strong=True)
     if want("attention_decode"):
-        extras["attention_decode"] = bench_attention_decode(torch, ops, dist, extra_steps, 3,
-                                                            peaks, source)
-    if want("tp_mlp") and dist.world > 1:
-        extras["tp_mlp"] = bench_tp_mlp(torch, dist, extra_steps, 3, peaks, source)
-        if 4096 % (128 * dist.world) == 0:
-            try:
-                extras["tp_mlp_peer"] = bench_tp_mlp(torch, dist, extra_steps, 3, peaks, source,
-                                                     collective="peer")
-            except Exception as exc:  # noqa: BLE001 - symmetric memory may be unavailable
-                extras["tp_mlp_peer"] = {"unavailable": f"{type(exc).__name__}: {exc}"[:300]}
+        extras["attention_decode"] = bench_attention_decode(torch, ops, dist, op_steps, 3, peaks,
+                                                            source)
+    if want("tp_mlp"):
+        if not dist.enabled:
+            extras["tp_mlp"] = bench_tp_mlp(torch, ops, dist, launches, peaks, source, "nccl")
+        else:
+            for key, collective in (("tp_mlp", "nccl"), ("tp_mlp_peer", "peer"),
+                                    ("tp_mlp_nvls", "nvls")):
+                if collective == "peer" and MLP_M % (128 * dist.world):
+                    continue
+                time.sleep(0.5)
+                try:
+                    extras[key] = bench_tp_mlp(torch, ops, dist, launches, peaks, source,
+                                               collective)
+                except Exception as exc:  # noqa: BLE001 - symmetric memory / NVLS may be unavailable
+                    extras[key] = {"unavailable": f"{type(exc).__name__}: {exc}"[:300]}
+    if want("siblings") and not dist.enabled:
+        extras["siblings"] = bench_siblings(torch, ops, peaks)
 
     baseline = cpu_baseline() if (dist.rank == 0 and dist.world == 1) else None
+
+    def strip(entry):
+        entry.pop("window", None)
+        for sub in entry.values():
+            if isinstance(sub, dict):
+                sub.pop("window", None)
+
     if dist.rank != 0:
         for extra in extras.values():
-            extra.pop("window", None)
+            strip(extra)
     if dist.rank == 0:
         sampler.stop()
         clocks = sampler.summary(*head["window"])
@@ -661,20 +1069,29 @@ def main():
             if "window" in extra:
                 extra["clocks"] = sampler.summary(*extra.pop("window"),
                                                   label="this operator's timed region")
-        value = SOFTMAX_BYTES * dist.world / (head["region_ms"] * 1e-3) / 1e9
+            sustained = extra.get("sustained")
+            if isinstance(sustained, dict) and "window" in sustained:
+                sustained["clocks"] = sampler.summary(*sustained.pop("window"),
+                                                      label="the sustained region")
+            strip(extra)
+        launch_ms = head["launch_ms"]
+        value = SOFTMAX_BYTES * dist.world / (launch_ms * 1e-3) / 1e9
+        roof = {k: head[k] for k in ("bound", "achieved", "peak", "unit", "frac", "peak_source",
+                                     "traffic", "algorithmic_per_launch", "launch_ms",
+                                     "launch_ms_event_pairs", "frac_event_pairs",
+                                     "necessary_bytes_per_launch", "achieved_dram", "frac_dram",
+                                     "note")}
+        config = headline_config()
         line = {
             "metric": "masked_softmax_fp16_hbm_throughput", "value": round(value, 2),
-            "unit": "GB/s", "n_gpus": dist.world, "steps": args.steps, "warmup": warmup,
-            "ms_per_step": round(head["region_ms"], 5), "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": "masked_softmax_fp16_16384x4000",
-                       "mask": "col > row % 4000 -> -inf", "io_dtype": "f16",
-                       "rows_per_gpu": ROWS, "sharding": "rows, no collective",
-                       "l2": "4 rotating buffer sets (1.05 GB) between reuses, L2 is 126 MB",
-                       "launching": f"CUDA graphs of {GRAPH_LAUNCHES} launches"},
-            "roofline": head["roofline"], "e2e": e2e, "gpu_launches": args.steps,
-            "clocks": clocks, "ops": extras,
+            "unit": "GB/s", "n_gpus": dist.world, "steps": steps, "warmup": warmup,
+            "ms_per_step": round(head["ms_per_step"], 4), "launches_per_step": LAUNCHES_PER_STEP,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+            "data": "synthetic", "config": config, "roofline": roof, "parity": head["parity"],
+            "e2e": e2e, "gpu_launches": head["gpu_launches"], "clocks": clocks, "ops": extras,
         }
+        if strong is not None:
+            line["strong"] = strong
         if baseline is not None:
             line["cpu_baseline"] = baseline
         print(json.dumps(line))

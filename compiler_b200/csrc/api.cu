@@ -139,7 +139,10 @@ extern "C" int b200_stream_create(void **out) {
   return B200_OK;
 }
 extern "C" int b200_stream_destroy(void *stream) {
-  if (stream != nullptr) B200_CUDA_OK(cudaStreamDestroy((cudaStream_t)stream));
+  if (stream != nullptr) {
+    b200::release_stream_scratch((cudaStream_t)stream);
+    B200_CUDA_OK(cudaStreamDestroy((cudaStream_t)stream));
+  }
   return B200_OK;
 }
 extern "C" int b200_stream_sync(void *stream) {

@@ -333,22 +333,23 @@ decode_generic_kernel(const Params p, int D) {
 // stream launches a decode and kept: launches on one stream are ordered, so they can share
 // it; launches on different streams never do.
 constexpr int kMaxResident = 4 * 160;
+static std::mutex g_scratch_lock;
+static std::map<std::pair<int, cudaStream_t>, float *> g_scratch;
+
 static float *stream_scratch(cudaStream_t stream) {
-  static std::mutex lock;
-  static std::map<std::pair<int, cudaStream_t>, float *> buffers;
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) return nullptr;
-  std::lock_guard<std::mutex> guard(lock);
+  std::lock_guard<std::mutex> guard(g_scratch_lock);
   auto key = std::make_pair(dev, stream);
-  auto found = buffers.find(key);
-  if (found != buffers.end()) return found->second;
+  auto found = g_scratch.find(key);
+  if (found != g_scratch.end()) return found->second;
   void *ptr = nullptr;
   if (cudaMalloc(&ptr, (size_t)kMaxResident * 2 * (128 + 2) * sizeof(float)) != cudaSuccess) {
     (void)cudaGetLastError();
     return nullptr;
   }
-  buffers[key] = reinterpret_cast<float *>(ptr);
-  return buffers[key];
+  g_scratch[key] = reinterpret_cast<float *>(ptr);
+  return g_scratch[key];
 }
 
 template <typename T, int D>
@@ -401,6 +402,24 @@ static int launch_typed(const Params &p, int rows, int D, bool aligned, cudaStre
 }
 
 }  // namespace decode
+
+// Called by b200_stream_destroy before the stream goes away: the decode scratch kept for
+// (current device, stream) is freed, so streams created per use do not accumulate buffers and
+// a later stream that gets the same handle value starts without one.
+void release_stream_scratch(cudaStream_t stream) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return;
+  float *ptr = nullptr;
+  {
+    std::lock_guard<std::mutex> guard(decode::g_scratch_lock);
+    auto found = decode::g_scratch.find(std::make_pair(dev, stream));
+    if (found == decode::g_scratch.end()) return;
+    ptr = found->second;
+    decode::g_scratch.erase(found);
+  }
+  (void)cudaStreamSynchronize(stream);  // its last decode may still be reading the buffer
+  (void)cudaFree(ptr);
+}
 }  // namespace b200
 
 extern "C" int b200_attn_decode(const b200_tensor *q, const b200_tensor *k, const b200_tensor *v,

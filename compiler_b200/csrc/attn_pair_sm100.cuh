@@ -223,10 +223,6 @@ __device__ __forceinline__ int item_at(int n, const Params &p, Item &it) {
   return 1;
 }
 
-#ifdef B200_ATTN_TIMING
-__device__ float g_attn_dbg[148 * 64];
-#endif
-
 template <typename T, int D>
 __global__ void __launch_bounds__(THREADS, 1)
 attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q,
@@ -367,20 +363,9 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q,
     uint32_t blocks[2] = {0, 0};  // key blocks each tile has been through (barrier phases)
     uint32_t active[2] = {0, 0};  // items in which each tile had work (o_empty phase)
     bool ok = true;
-#ifdef B200_ATTN_TIMING
-    long long tacc[16] = {0};
-    const long long t_begin = clock64();
-    auto wait_all = [&](uint32_t bar, uint32_t parity, uint32_t site) {
-      const long long t0 = clock64();
-      const bool r = __all_sync(0xffffffffu, mbar_wait(bar, parity, ctx, site)) != 0;
-      tacc[site] += clock64() - t0;
-      return r;
-    };
-#else
     auto wait_all = [&](uint32_t bar, uint32_t parity, uint32_t site) {
       return __all_sync(0xffffffffu, mbar_wait(bar, parity, ctx, site)) != 0;
     };
-#endif
     // descriptor halves that never change: Q tiles, K / V stages
     constexpr uint32_t kHi = desc_hi_sw128(1024);
     const uint32_t q_lo0 = desc_lo_sw128(q_smem, 16);
@@ -508,13 +493,6 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q,
       mbar_wait_drain(drain_bar, 0);
     }
     __syncwarp();
-#ifdef B200_ATTN_TIMING
-    if (lane == 0) {
-      float *dbg = g_attn_dbg + (int64_t)blockIdx.x * 64;
-      for (int i = 0; i < 16; ++i) dbg[i] = (float)tacc[i];
-      dbg[0] = (float)(clock64() - t_begin);
-    }
-#endif
   } else if (warp == 10) {
     // ---------------------------------------------------------------- O store
     // Finished O tiles reach global memory as bulk tensor copies out of the staging
@@ -567,13 +545,6 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q,
       return __all_sync(0xffffffffu, mbar_wait(bar, parity, ctx, site)) != 0;
 #endif
     };
-#ifdef B200_ATTN_TIMING
-    long long sacc[8] = {0};
-    long long tk = clock64();
-#define TICK(i) { const long long now_ = clock64(); sacc[i] += now_ - tk; tk = now_; }
-#else
-#define TICK(i)
-#endif
     const float2 scale2 = make_float2(p.scale_log2, p.scale_log2);
     for (int n = 0; ok; ++n) {
       Item it;
@@ -590,10 +561,8 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q,
       float m_used = -INFINITY;  // running max in the scaled log2 domain
       float l = 0.f;
       for (int j = 0; j < nb; ++j, ++blocks) {
-        TICK(0)
         if (!wait_all(s_full(t), blocks & 1u, 10)) { ok = false; break; }
         tc_fence_after_sync();
-        TICK(1)
 #ifdef B200_ATTN_SKIP_SOFTMAX
         tc_fence_before_sync();
         __syncwarp();
@@ -607,7 +576,6 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q,
         tmem_ld_32x32b_x32(s_tmem, reinterpret_cast<uint32_t(&)[32]>(xr[0]));
         tmem_ld_32x32b_x32(s_tmem + 32, reinterpret_cast<uint32_t(&)[32]>(xr[32]));
         tmem_ld_wait();
-        TICK(2)
         tmem_ld_32x32b_x32(s_tmem + 64, reinterpret_cast<uint32_t(&)[32]>(xr[64]));
         tmem_ld_32x32b_x32(s_tmem + 96, reinterpret_cast<uint32_t(&)[32]>(xr[96]));
         const int col0 = j * BLOCK_N;
@@ -649,7 +617,6 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q,
           }
         }
         const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * p.scale_log2;
-        TICK(3)
         // lazy rescale: the max used for exp2 is raised only when the true max
         // exceeds it by more than 2^kRescaleThreshold
         float alpha = 1.0f;
@@ -722,15 +689,12 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q,
           tc_fence_before_sync();
           __syncwarp();
           if (lane == 0) mbar_arrive(half == 0 ? p_full(t) : p2_full(t));
-          TICK(4 + half)
         }
         l += (sum_a.x + sum_a.y) + (sum_b.x + sum_b.y);
       }
       if (!ok) break;
-      TICK(0)
       // ---- epilogue of this tile: O / l, LSE
       if (!wait_all(o_full(t), (blocks - 1u) & 1u, 12)) { ok = false; break; }
-      TICK(6)
       tc_fence_after_sync();
       uint32_t acc[D];
 #pragma unroll
@@ -763,14 +727,7 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q,
         if (row < p.N && p.lse != nullptr)
           p.lse[it.z * p.lse_z + it.h * p.lse_h + row] = m_used * 0.6931471805599453f + logf(l);
       }
-      TICK(7)
     }
-#ifdef B200_ATTN_TIMING
-    if (lane == 0 && (warp & 3) == 0) {
-      float *dbg = g_attn_dbg + (int64_t)blockIdx.x * 64 + 16 + t * 8;
-      for (int i = 0; i < 8; ++i) dbg[i] = (float)sacc[i];
-    }
-#endif
   }
 
   tc_fence_before_sync();

@@ -564,8 +564,3 @@ extern "C" int b200_attn_fwd(const b200_tensor *q, const b200_tensor *k, const b
 #undef B200_ATTN_TC
 }
 
-#ifdef B200_ATTN_TIMING
-extern "C" int b200_debug_attn_timing(float *host_out) {
-  return (int)cudaMemcpyFromSymbol(host_out, b200::attn::pair::g_attn_dbg, sizeof(float) * 148 * 64);
-}
-#endif

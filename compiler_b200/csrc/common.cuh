@@ -74,6 +74,9 @@ inline int check_tensor(const b200_tensor *t, const char *name, uint32_t ndim) {
 // Per-device status word written by kernels whose bounded waits expired.
 unsigned int *device_status_word();  // device pointer for the current device
 
+// Frees the decode-attention scratch kept for (current device, stream), if any (attn_decode.cu).
+void release_stream_scratch(cudaStream_t stream);
+
 inline int sm_count() {
   static int cached[64] = {0};
   int dev = 0;

@@ -349,8 +349,12 @@ class B200Device:
         return buffer.data_ptr()
 
     def synchronize(self):
+        """Block until the device is idle, then read the device status word: a kernel whose
+        bounded wait expired returns normally with an unfinished result, so the one hook the
+        harness protocol and the measuring lane call must be the one that raises for it."""
         abi.check(self._lib.b200_stream_sync(self.stream))
         abi.check(self._lib.b200_device_sync())
+        abi.check(self._lib.b200_last_device_status(self.stream))
 
     def timer(self):
         return EventTimer(self.stream)

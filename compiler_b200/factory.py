@@ -31,17 +31,32 @@ from compiler_b200 import registry as _registry
 from compiler_b200.runtime import abi
 
 
+# Environment switches of the native library that change WHICH kernel runs a launch (the
+# library reads each once, at its first use in the process).
+KERNEL_SWITCHES = ("B200OPS_ATTN_KERNEL", "B200OPS_ATTN_P", "B200OPS_ATTN_WAVE",
+                   "B200OPS_GEMM_PAIR", "B200OPS_GEMM_GROUP_M", "B200OPS_SOFTMAX_STREAM")
+
+
+def _kernel_switches() -> dict:
+    return {name: os.environ.get(name, "") for name in KERNEL_SWITCHES}
+
+
 @dataclass
 class PlanOptions:
-    """Options that change which kernel runs; every field is part of the identity
-    (``CompileOptions.identity_part``, a100c/driver.py:222-244).  Environment
-    overrides use the ``B200OPS_`` prefix."""
-    attn_p_location: str = field(
-        default_factory=lambda: os.environ.get("B200OPS_ATTN_P", "tmem"))
+    """Options that change which kernel runs; every one of them is part of the identity
+    (``CompileOptions.identity_part``, a100c/driver.py:222-244), so two artifacts compiled
+    under different kernel choices never share a cache entry.  The choices are the
+    ``B200OPS_*`` switches of ``KERNEL_SWITCHES``, sampled when the options are created."""
+    switches: dict = field(default_factory=_kernel_switches)
     device: int = field(default_factory=lambda: int(os.environ.get("B200OPS_DEVICE", "0")))
 
+    @property
+    def attn_p_location(self) -> str:
+        return self.switches.get("B200OPS_ATTN_P") or "tmem"
+
     def identity_part(self) -> str:
-        return json.dumps({"attn_p_location": self.attn_p_location}, sort_keys=True)
+        return json.dumps({name: self.switches.get(name, "") for name in KERNEL_SWITCHES},
+                          sort_keys=True)
 
 
 def _scalar_class(value) -> str:

@@ -5,10 +5,15 @@ The reference's harness does this in ``ops/harness/opslib/device.py``:
 kernel signature, ``stage_case`` (:377-415) uploads every array of ``args`` /
 ``allocations`` once (aliased host arrays as one allocation), and
 ``StagedCase.launch`` (:341-349) merges buffers, metas and per-launch overrides
-and calls ``device.launch(kernel, grid, positional, keywords)``.  This module is
-the same contract for hosts that do not have the reference tree (the GPU box):
-a case dict that runs through the reference's ``stage_case`` runs through this
-one unchanged, and ``B200Device`` works with either.
+and calls ``device.launch(kernel, grid, positional, keywords)``.
+
+This module is the CALLER-SIDE STAND-IN for hosts that do not have the reference tree (the
+GPU box): it is not part of the operator path and nothing behind ``B200Device.launch`` uses
+it.  Its users are the tests and the measuring lane (``lane.py``) when they run without the
+reference's ``opslib``; a case dict that runs through the reference's ``stage_case`` runs
+through this one unchanged, and ``B200Device`` works with either
+(``tests/test_reference_objects.py`` drives the device with the reference's own functions
+and real kernel objects and compares the two).
 """
 from __future__ import annotations
 

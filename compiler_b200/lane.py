@@ -149,11 +149,16 @@ def measure(staged, device, *, warmups=3, timer=None, **stop) -> list[float]:
     return times
 
 
+# The function that uploads a case and binds its arguments: this package's stand-in, or the
+# corpus's own ``opslib.device.stage_case`` once ``--corpus`` has put it on the path.
+_stage_case = harness.stage_case
+
+
 def stage_zeroed(case: dict, device):
     """Stage a case with every pure output buffer zeroed, so that a kernel that did not
     write shows up as a mismatch instead of passing on stale data (``run.py:105-113``)."""
     if "inputs" not in case:  # no declaration of what is read: leave every buffer as given
-        return harness.stage_case(case, device)
+        return _stage_case(case, device)
     outputs, inputs = set(case.get("outputs") or ()), set(case.get("inputs") or ())
     scrubbed = dict(case)
     for key in ("args", "allocations"):
@@ -163,7 +168,7 @@ def stage_zeroed(case: dict, device):
                        if isinstance(value, np.ndarray) and name in outputs and name not in inputs
                        else value)
                 for name, value in case[key].items()}
-    return harness.stage_case(scrubbed, device)
+    return _stage_case(scrubbed, device)
 
 
 def verify(staged, case: dict, device) -> float:
@@ -288,6 +293,11 @@ def main(argv=None) -> int:
     out_dir = Path(args.out_dir)
     out_dir.mkdir(parents=True, exist_ok=True)
     corpus = Path(args.corpus)
+    harness_dir = str(corpus / "harness")
+    if harness_dir not in sys.path:
+        sys.path.insert(0, harness_dir)
+    global _stage_case
+    from opslib.device import stage_case as _stage_case  # the corpus's own staging and launch
     rows = []
     for entry in entries:
         dtype = entry.get("dtype", workload["dtype"])

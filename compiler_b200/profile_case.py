@@ -46,6 +46,10 @@ def main(argv=None):
     parser.add_argument("--act", default="gelu_tanh", choices=["none", "gelu_tanh", "gelu_erf"],
                         help="gemm epilogue")
     parser.add_argument("--no-bias", action="store_true", help="gemm without the bias add")
+    parser.add_argument("--sets", type=int, default=1,
+                        help="softmax: rotate over this many input / output buffer sets, so a "
+                             "launch meets the cache state of a steady sequence (dirty lines of "
+                             "the launches before it) instead of its own previous output")
     args = parser.parse_args(argv)
     device = B200Device(args.device)
     rng = np.random.default_rng(0)
@@ -53,9 +57,14 @@ def main(argv=None):
 
     if args.op == "softmax":
         dtype = args.dtype or "float16"
-        x = _upload(device, rng.standard_normal(shape, dtype=np.float32) * 2, dtype)
-        y = device.alloc(shape, dtype)
-        launch = lambda: ops.softmax(x, y, causal_mod=not args.no_mask)  # noqa: E731
+        host = rng.standard_normal(shape, dtype=np.float32) * 2
+        xs = [_upload(device, host, dtype) for _ in range(max(1, args.sets))]
+        ys = [device.alloc(shape, dtype) for _ in xs]
+        turn = iter(range(1 << 30))
+
+        def launch():
+            i = next(turn) % len(xs)
+            ops.softmax(xs[i], ys[i], causal_mod=not args.no_mask)
         work = {"bytes": 2 * int(np.prod(shape)) * abi.DTYPE_SIZES[dtype]}
     elif args.op == "rmsnorm":
         dtype = args.dtype or "float32"

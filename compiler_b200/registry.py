@@ -169,6 +169,20 @@ def _softmax_inner(device, v, grid, name):
                 stream=device.stream)
 
 
+def _softmax_multi_block(device, v, grid, name):
+    """_softmax_multi_block_forward_kernel
+    (ops/suite/dev/softmax_multi_block_forward_kernel.py:12-48): every program walks rows
+    program_id, program_id + num_programs, ... with an online max / sum over BLOCK_SIZE
+    columns at a time -- the algorithm of the native persistent row kernel, which picks its
+    own program count."""
+    rows, cols = int(v["n_rows"]), int(v["n_cols"])
+    _require(_grid_tuple(grid)[0] >= 1, name, "grid", "expected at least one program")
+    _require(int(v["X_row_stride"]) == cols and int(v["Y_row_stride"]) == cols, name,
+             "X_row_stride", "only contiguous rows (row stride == n_cols) have a native kernel")
+    ops.softmax(_View(v["X_ptr"], (rows, cols)), _View(v["Y_ptr"], (rows, cols)),
+                stream=device.stream)
+
+
 def _masked_softmax(device, v, grid, name):
     """Native handle: row softmax with the causal-mod mask (kernels.masked_softmax_kernel)."""
     rows = _grid_tuple(grid)[0]
@@ -562,6 +576,9 @@ def default_registry() -> Registry:
     r.register("softmax_kernel_inner",
                ("output_ptr", "input_ptr", "M", "N", "TILE_N", "ONE_TILE_PER_CTA"),
                _softmax_inner)
+    r.register("_softmax_multi_block_forward_kernel",
+               ("Y_ptr", "Y_row_stride", "X_ptr", "X_row_stride", "n_rows", "n_cols",
+                "BLOCK_SIZE"), _softmax_multi_block)
     r.register("matmul_kernel", ("a_ptr", "b_ptr", "y_ptr", "M", "N", "K"), _matmul_plain)
     r.register("matmul_kernel", _MATMUL_STRIDED, _matmul_strided)
     r.register("linear_act_kernel",

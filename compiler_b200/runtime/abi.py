@@ -97,6 +97,8 @@ PROTOTYPES = {
     "b200_gemm_scatter_rows": (c_int, [_T, _T, _T, POINTER(_PTR), c_int, c_int, c_int64, _PTR]),
     "b200_reduce_slices_broadcast": (c_int, [_PTR, c_uint32, c_int, c_int64, c_int64, c_int64,
                                              POINTER(_PTR), _PTR]),
+    "b200_multimem_allreduce": (c_int, [_PTR, c_uint32, c_int64, c_int64, c_int, c_int, c_int,
+                                        _PTR]),
     "b200_attn_fwd": (c_int, [_T, _T, _T, _T, _T, c_float, c_int, _PTR]),
     "b200_stream_wait_event": (c_int, [_PTR, _PTR]),
     "b200_graph_begin_capture": (c_int, [_PTR]),
@@ -177,17 +179,9 @@ def lib() -> ctypes.CDLL:
     with _lock:
         if _lib is not None:
             return _lib
-        import os
-        from pathlib import Path
-
         from compiler_b200 import build as _build
         path = _build.LIB_PATH
-        override = os.environ.get("B200OPS_LIBRARY")  # a prebuilt library to load as is
-        if override:
-            path = Path(override)
-            if not path.is_file():
-                raise RuntimeError(f"B200OPS_LIBRARY={override} does not exist")
-        elif not _build.is_current():
+        if not _build.is_current():
             try:
                 path = _build.build()
             except Exception as exc:  # noqa: BLE001

@@ -27,7 +27,18 @@ Two ways to sum the partials:
     (``b200_reduce_slices_broadcast``), and a second barrier publishes it.  Buffers come from
     ``torch.distributed._symmetric_memory``; only its barrier is used, the data moves in this
     library's kernels.  The staged partials are 16-bit, their sum is taken in fp32 (every
-    partial is rounded once, the running sum never).  Needs M to be a multiple of 128 * world.
+    partial is rounded once, the running sum never).  Needs M to be a multiple of 128 * world;
+  * ``collective="nvls"``: every rank writes its 16-bit partial into a symmetric buffer that
+    is bound to an NVSwitch multicast object; after a barrier each rank loads the in-switch
+    sum of its 1/world share (``b200_multimem_allreduce``: ``multimem.ld_reduce``, fp32
+    accumulation, one rounding) and stores it to all ranks at once (``multimem.st``), in
+    place; a second barrier publishes it.  No partial crosses a link twice and the GEMM's
+    epilogue stores stay local.  The result is returned in the symmetric buffer itself (no
+    copy) when ``forward`` gets no ``y``.  Needs NVLS (a multicast pointer from
+    ``torch.distributed._symmetric_memory``) and M * hidden to be a multiple of 8 * world.
+
+``forward(x, y, mark=...)`` calls ``mark(name)`` after it has enqueued each phase, so a caller
+can record a CUDA event per phase on the current stream.
 """
 from __future__ import annotations
 
@@ -46,13 +57,15 @@ class TensorParallelMLP:
         self.wg, self.wu, self.wd = wg, wu, wd
         self.group = group
         self.chunks = max(1, int(chunks))
-        if collective not in ("nccl", "peer"):
-            raise ValueError("collective must be 'nccl' or 'peer'")
+        if collective not in ("nccl", "peer", "nvls"):
+            raise ValueError("collective must be 'nccl', 'peer' or 'nvls'")
         self.collective = collective
+        # this library's kernels per forward (NCCL's and the barrier kernels are not counted)
         self.kernels_per_forward = 1 + self.chunks if collective == "nccl" else 3
         self._h = None
         self._partial = None
         self._peer = None  # (rows, staging, staging handle, y, y handle)
+        self._nvls = None  # (key, partial, handle)
 
     @classmethod
     def synthetic(cls, hidden, ffn, rank, world, seed=0, dtype=None, chunks=4, collective="nccl"):
@@ -66,22 +79,31 @@ class TensorParallelMLP:
         return cls(make(hidden, hi - lo), make(hidden, hi - lo), make(hi - lo, hidden),
                    chunks=chunks, collective=collective)
 
-    def forward(self, x, y):
-        """x: [M, hidden] replicated; y: [M, hidden] receives the all-reduced result."""
+    def forward(self, x, y=None, mark=None):
+        """x: [M, hidden] replicated; y: [M, hidden] receives the all-reduced result.  With
+        ``y=None`` the peer and nvls paths return their own symmetric output buffer (valid
+        until the next call) and save the copy; the NCCL path allocates one."""
         torch = self.torch
         import torch.distributed as dist
+        mark = mark or (lambda name: None)
         m = x.shape[0]
         cols = self.wg.shape[1]
         if self._h is None or self._h.shape != (m, cols) or self._h.dtype != x.dtype:
             self._h = torch.empty((m, cols), device=x.device, dtype=x.dtype)
         stream = torch.cuda.current_stream().cuda_stream
         ops.gemm(x, self.wg, self._h, b2=self.wu, act=abi.ACT_SWIGLU, stream=stream)
+        mark("up_projection")
         if self.collective == "peer":
-            return self._forward_peer(y, stream)
+            return self._forward_peer(y, stream, mark)
+        if self.collective == "nvls":
+            return self._forward_nvls(y, stream, mark)
+        if y is None:
+            y = torch.empty((m, self.wd.shape[1]), device=x.device, dtype=x.dtype)
         distributed = dist.is_available() and dist.is_initialized() and dist.get_world_size(
             self.group) > 1
         if not distributed:
             ops.gemm(self._h, self.wd, y, stream=stream)
+            mark("down_projection")
             return y
         # fp32 partials: a 16-bit ring all-reduce rounds the running sum at every hop, which
         # at 4 ranks already exceeds the 2e-2 tolerance against the unsharded result
@@ -92,9 +114,11 @@ class TensorParallelMLP:
             ops.gemm(self._h[lo:hi], self.wd, self._partial[lo:hi], stream=stream)
             pending.append((lo, hi, dist.all_reduce(self._partial[lo:hi], group=self.group,
                                                     async_op=True)))
+        mark("down_projection_chunks_issued")
         for lo, hi, work in pending:
             work.wait()
             y[lo:hi].copy_(self._partial[lo:hi])  # one rounding to the storage type
+        mark("all_reduce_tail_and_rounding")
         return y
 
     # ------------------------------------------------------------------ peer path
@@ -114,7 +138,7 @@ class TensorParallelMLP:
             self._peer = ((m, hidden, dtype), rows, staging, staging_h, out, out_h)
         return self._peer[1:]
 
-    def _forward_peer(self, y, stream):
+    def _forward_peer(self, y, stream, mark):
         """Down-projection with the reduce-scatter in its epilogue, then sum + broadcast."""
         import ctypes
 
@@ -135,12 +159,58 @@ class TensorParallelMLP:
         abi.check(lib.b200_gemm_scatter_rows(ctypes.byref(hd), ctypes.byref(wd),
                                              ctypes.byref(c_like), staging_ptrs, world, rank,
                                              rows, stream))
+        mark("down_projection_scatter")
         staging_h.barrier(channel=0)  # every rank's tiles for my rows have landed
+        mark("barrier_partials")
         abi.check(lib.b200_reduce_slices_broadcast(
             staging.data_ptr(), abi.DTYPE_CODES[abi.dtype_name(out.dtype)], world, rows, hidden,
             rank * rows, out_ptrs, stream))
+        mark("reduce_broadcast")
         out_h.barrier(channel=1)      # every rank's slice is in my output
+        mark("barrier_result")
         if y is not None and y.data_ptr() != out.data_ptr():
             y.copy_(out)
+            mark("copy_out")
             return y
         return out
+
+    # ------------------------------------------------------------------ in-switch path
+    def _nvls_buffer(self, m, hidden, dtype, device):
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm_mem
+        world = dist.get_world_size(self.group)
+        if (m * hidden) % (8 * world):
+            raise ValueError(f"collective='nvls' needs M * hidden ({m * hidden}) to be a "
+                             f"multiple of {8 * world}")
+        key = (m, hidden, dtype)
+        if self._nvls is None or self._nvls[0] != key:
+            group = self.group if self.group is not None else dist.group.WORLD
+            partial = symm_mem.empty((m, hidden), dtype=dtype, device=device)
+            handle = symm_mem.rendezvous(partial, group=group)
+            if not int(getattr(handle, "multicast_ptr", 0) or 0):
+                raise RuntimeError("symmetric memory has no multicast pointer on this system "
+                                   "(NVLS unavailable): use collective='peer'")
+            self._nvls = (key, partial, handle)
+        return self._nvls[1:]
+
+    def _forward_nvls(self, y, stream, mark):
+        """Down-projection into the symmetric partial, then the in-switch all-reduce in place."""
+        import torch.distributed as dist
+        m, hidden = self._h.shape[0], self.wd.shape[1]
+        partial, handle = self._nvls_buffer(m, hidden, self._h.dtype, self._h.device)
+        world, rank = dist.get_world_size(self.group), dist.get_rank(self.group)
+        ops.gemm(self._h, self.wd, partial, stream=stream)
+        mark("down_projection")
+        handle.barrier(channel=0)     # every rank's partial is complete
+        mark("barrier_partials")
+        abi.check(abi.lib().b200_multimem_allreduce(
+            int(handle.multicast_ptr), abi.DTYPE_CODES[abi.dtype_name(partial.dtype)], 0,
+            m * hidden, rank, world, 0, stream))
+        mark("multimem_allreduce")
+        handle.barrier(channel=1)     # every rank's share is in my copy
+        mark("barrier_result")
+        if y is not None and y.data_ptr() != partial.data_ptr():
+            y.copy_(partial)
+            mark("copy_out")
+            return y
+        return partial

@@ -313,6 +313,20 @@ int b200_reduce_slices_broadcast(const void *staging, uint32_t dtype, int world,
                                  int64_t rows, int64_t cols, int64_t dst_row0,
                                  void *const *y_rank, void *stream);
 
+/* All-reduce (sum) of 16-bit partials through NVSwitch.  `multicast_base` is the multicast
+ * address of a buffer that every rank allocated symmetrically and bound to one multicast
+ * object (torch.distributed._symmetric_memory: handle.multicast_ptr); elements
+ * [offset, offset + count) of it are reduced.  This rank loads the sum of all ranks' copies
+ * of its share [offset + rank*count/world, offset + (rank+1)*count/world) with
+ * multimem.ld_reduce (added in the switch in fp32, rounded once) and stores it to all ranks'
+ * copies with multimem.st, in place.  offset and count/world must be multiples of 8
+ * elements.  `ctas` > 0 limits the grid (for running beside another kernel), 0 = default.
+ * The caller puts a cross-rank barrier before the call (all partials written) and after it
+ * (all shares published).  The merge of per-worker partials in the reference is
+ * a100c/plan/stages.py:278-316; it has no multi-device counterpart. */
+int b200_multimem_allreduce(void *multicast_base, uint32_t dtype, int64_t offset,
+                            int64_t count, int rank, int world, int ctas, void *stream);
+
 /* out = x * sigmoid(x) * y elementwise.  Replaces swiglu_fwd_kernel
  * (ops/suite/perf/swiglu_fwd.py:18-36).  [rows, cols], unit column stride. */
 int b200_swiglu_fwd(const b200_tensor *x, const b200_tensor *y,
@@ -327,8 +341,8 @@ int b200_allclose_f32(const void *actual, const void *expected, int64_t count,
                       int64_t *bad_count, double *max_abs_err, void *stream);
 
 /* The same comparison as b200_allclose_f32 for callers that must not allocate device
- * memory: code running while a stream capture is open, services whose memory pool owns the
- * whole device, or latency-critical loops that cannot afford the device-wide
+ * memory: services whose memory pool owns the whole device (a cudaMalloc there fails or
+ * fragments the pool), and latency-critical loops that cannot afford the device-wide
  * synchronisation an allocation and a free imply.  (No counterpart in the reference: its
  * device compare allocates three buffers per call, ops/harness/opslib/devices/cuda.py.)
  * It calls no cudaMalloc / cudaFree and no allocating library routine.  Its scratch is a
@@ -336,12 +350,16 @@ int b200_allclose_f32(const void *actual, const void *expected, int64_t count,
  * library until the process exits; it covers at most 134,201,344 elements per call
  * ((8192 - 1) blocks x 16384 elements) and a larger count is rejected with
  * B200_REJECTED.  The first call on a device looks up the array's device address
- * (cudaGetSymbolAddress, with that device current); make that first call before
- * starting any stream capture.  All calls share the one array, which keeps the previous
- * call's contents (each call overwrites every slot it later reads, so nothing has to be
- * cleared); two calls that overlap on the GPU -- different streams, or several host
- * threads -- race on it and must be serialised by the caller.  Results match
- * b200_allclose_f32.  Synchronises `stream`. */
+ * (cudaGetSymbolAddress, with that device current) and keeps it for the life of the
+ * process (a cudaDeviceReset invalidates it); make that first call before starting any
+ * stream capture.  All calls share the one array, which keeps the previous call's contents
+ * (each call overwrites every slot it later reads, so nothing has to be cleared); two calls
+ * that overlap on the GPU -- different streams, or several host threads -- race on it and
+ * must be serialised by the caller.  Results match b200_allclose_f32.
+ * The call BLOCKS the host: it copies the two result words back and synchronises `stream`
+ * before it returns.  `stream` must therefore not be a stream that is being captured (nor
+ * the legacy default stream while another thread holds a global-mode capture): pass a
+ * stream of your own that is outside the capture. */
 int b200_allclose_f32_static(const void *actual, const void *expected, int64_t count,
                              double rtol, double atol, int equal_nan,
                              int64_t *bad_count, double *max_abs_err, void *stream);

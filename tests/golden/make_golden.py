@@ -37,6 +37,7 @@ OPERATORS = {
     "perf/context_attn_fwd.py": [],
     "perf/swiglu_fwd.py": [(64, 1024)],
     "dev/softmax_kernel_inner.py": [],
+    "dev/softmax_multi_block_forward_kernel.py": [],
     "dev/hidden__rms_norm_loop_kernel.py": [],
     # sibling kernels of the five families
     "perf/softmax_mul.py": [],

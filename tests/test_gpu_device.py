@@ -224,3 +224,25 @@ def test_captured_launches_replay_as_one_graph(device):
         abi.check(abi.lib().b200_graph_begin_capture(None))
     g.close()
     stream.close()
+
+
+def test_decode_scratch_follows_the_stream(device):
+    """Decode attention keeps one scratch buffer per (device, stream) and gives it back when
+    the stream is destroyed through the library: streams created per use do not pile buffers
+    up, and a new stream (whatever handle value it gets) starts clean and gives the oracle's
+    result."""
+    from compiler_b200 import graph
+    rng = np.random.default_rng(9)
+    rows, keys, d = 16, 2000, 128
+    q = oracle.bf16_round(rng.standard_normal((rows, d)).astype(np.float32))
+    k, v = (oracle.bf16_round(rng.standard_normal((rows, keys, d)).astype(np.float32))
+            for _ in range(2))
+    dq, dk, dv = (device.upload(t, "bfloat16") for t in (q, k, v))
+    ref = oracle.flash_decode_ref(q, k, v, 1.0 / np.sqrt(d))
+    for _ in range(6):
+        stream = graph.Stream()
+        out = device.alloc((rows, d), "bfloat16")
+        ops.attention_decode(dq, dk, dv, out, stream=stream.handle)
+        stream.synchronize()
+        oracle.compare(device.download(out).astype(np.float64), ref, 2e-2, 2e-2, name="decode")
+        stream.close()

@@ -71,10 +71,14 @@ def test_gemm_bias_gelu_fullsize(device, shape):
 
 
 def test_attention_fullsize_heads(device):
-    """[8,32,4096,128] causal bf16 is 1 GiB of tensors; two (batch, head) slices of the
-    same shape are checked against the oracle per head, all heads through the row-sum
-    property lse == log sum exp."""
-    z, h, n, d = 2, 4, 4096, 128
+    """The BASELINE tensor itself, [8,32,4096,128] causal bf16 (1 GiB on the device): the
+    kernel's work order depends on the number of (batch, head) pairs (balanced pairs of query
+    blocks dealt head by head over the SMs, in waves of a few heads), so heads are checked
+    where that order changes -- the first and last head, both sides of wave boundaries and of
+    the point where the CTAs wrap around -- against the float64 oracle per head; every head
+    goes through the cheap properties; and one head is launched again on its own, which must
+    give the same numbers whatever work order surrounded it."""
+    z, h, n, d = 8, 32, 4096, 128
     rng = np.random.default_rng(33)
     q, k, v = (oracle.bf16_round(rng.standard_normal((z, h, n, d), dtype=np.float32))
                for _ in range(3))
@@ -86,9 +90,69 @@ def test_attention_fullsize_heads(device):
     device.check_status()
     out, lse = device.download(do), device.download(dl)
     assert np.isfinite(out).all() and np.isfinite(lse).all()
-    for zi, hi in ((0, 0), (1, 3)):
+    for flat in (0, 3, 4, 37, 127, 128, 255):
+        zi, hi = divmod(flat, h)
         out_ref, lse_ref = oracle.attention_head_ref(q[zi, hi], k[zi, hi], v[zi, hi], scale, True)
         oracle.compare(out[zi, hi].astype(np.float64), out_ref, 2e-2, 2e-2, name=f"out[{zi},{hi}]")
         oracle.compare(lse[zi, hi].astype(np.float64), lse_ref, 1e-3, 1e-3, name=f"lse[{zi},{hi}]")
-    # row 0 attends only to key 0: out == v[0], lse == scale * q0.k0
+    # row 0 attends only to key 0: out == v[0], lse == scale * q0.k0 -- all 256 heads
     np.testing.assert_allclose(out[:, :, 0, :], v[:, :, 0, :], rtol=1e-2, atol=1e-2)
+    s00 = scale * np.einsum("zhd,zhd->zh", q[:, :, 0, :].astype(np.float64),
+                            k[:, :, 0, :].astype(np.float64))
+    np.testing.assert_allclose(lse[:, :, 0], s00, rtol=1e-4, atol=1e-4)
+    # row 1 of every head: two keys, closed form
+    s1 = scale * np.einsum("zhd,zhkd->zhk", q[:, :, 1, :].astype(np.float64),
+                           k[:, :, :2, :].astype(np.float64))
+    np.testing.assert_allclose(lse[:, :, 1], np.log(np.exp(s1).sum(-1)), rtol=1e-4, atol=1e-4)
+    # one head on its own ([1,1,4096,128]) gives what it gave inside the 256-head launch
+    zi, hi = 5, 17
+    d1 = [device.upload(np.ascontiguousarray(t[zi:zi + 1, hi:hi + 1]), "bfloat16")
+          for t in (q, k, v)]
+    o1, l1 = device.alloc((1, 1, n, d), "bfloat16"), device.alloc((1, 1, n), "float32")
+    ops.attention(*d1, o1, lse=l1, scale=scale, causal=True)
+    device.check_status()
+    np.testing.assert_allclose(device.download(l1)[0, 0], lse[zi, hi], rtol=0, atol=1e-5)
+    np.testing.assert_allclose(device.download(o1)[0, 0], out[zi, hi], rtol=2 ** -7, atol=1e-6)
+    # batch shards (what each of 8 GPUs would run): slab 3 alone equals slab 3 of the whole
+    d3 = [device.upload(np.ascontiguousarray(t[3:4]), "bfloat16") for t in (q, k, v)]
+    o3, l3 = device.alloc((1, h, n, d), "bfloat16"), device.alloc((1, h, n), "float32")
+    ops.attention(*d3, o3, lse=l3, scale=scale, causal=True)
+    device.check_status()
+    np.testing.assert_allclose(device.download(l3)[0], lse[3], rtol=0, atol=1e-5)
+    np.testing.assert_allclose(device.download(o3)[0], out[3], rtol=2 ** -7, atol=1e-6)
+
+
+def test_row_shards_equal_the_unsharded_result(device):
+    """The BASELINE row operators split 8 ways (what each GPU of a box runs): a block of rows
+    launched on its own, with its global row offset, gives the rows of the unsharded launch."""
+    rng = np.random.default_rng(34)
+    rows, cols, parts = 16384, 4000, 8
+    x = (rng.standard_normal((rows, cols), dtype=np.float32) * 2).astype(np.float16)
+    dx, dy = device.upload(x), device.alloc(x.shape, "float16")
+    ops.softmax(dx, dy, causal_mod=True, row_offset=0)
+    whole = device.download(dy)
+    block = rows // parts
+    for part in (0, 1, 5, 7):
+        lo = part * block
+        sx, sy = device.upload(x[lo:lo + block]), device.alloc((block, cols), "float16")
+        ops.softmax(sx, sy, causal_mod=True, row_offset=lo)
+        got = device.download(sy)
+        np.testing.assert_allclose(got.astype(np.float32), whole[lo:lo + block].astype(np.float32),
+                                   rtol=0, atol=2e-3)
+        for r in (0, block // 2, block - 1):
+            oracle.compare(got[r:r + 1].astype(np.float64),
+                           oracle.masked_softmax_ref(x[lo + r:lo + r + 1], lo + r), 1e-2, 1e-2,
+                           name=f"shard {part} row {r}")
+    xr = rng.standard_normal((8192, 4096), dtype=np.float32)
+    w = rng.uniform(0.5, 1.5, 4096).astype(np.float32)
+    dxr, dw = device.upload(xr), device.upload(w)
+    dyr, dr = device.alloc(xr.shape, "float32"), device.alloc((8192,), "float32")
+    ops.rmsnorm(dxr, dw, dyr, dr, eps=1e-6)
+    whole_y, whole_r = device.download(dyr), device.download(dr)
+    for part in (0, 6):
+        lo = part * 1024
+        sx = device.upload(xr[lo:lo + 1024])
+        sy, sr = device.alloc((1024, 4096), "float32"), device.alloc((1024,), "float32")
+        ops.rmsnorm(sx, dw, sy, sr, eps=1e-6)
+        np.testing.assert_allclose(device.download(sy), whole_y[lo:lo + 1024], rtol=1e-6)
+        np.testing.assert_allclose(device.download(sr), whole_r[lo:lo + 1024], rtol=1e-6)

@@ -63,6 +63,46 @@ ops.device_status(torch.cuda.current_stream().cuda_stream)
 oracle.compare(yp.float().cpu().numpy().astype(np.float64), oracle.swiglu_mlp_ref(xp, wg, wu, wd),
                2e-2, 2e-2, name="tp mlp (peer)")
 
+# the benchmark's shape (CTA-pair GEMMs, 256-row tiles, every collective): a spread of rows of
+# each rank's own output against the float64 oracle of the unsharded MLP
+hidden, ffn, m = 4096, 14336, 4096
+rng_b = np.random.default_rng(6)
+xb = oracle.bf16_round(rng_b.standard_normal((m, hidden), dtype=np.float32))
+wgb = oracle.bf16_round(rng_b.standard_normal((hidden, ffn), dtype=np.float32) * np.float32(0.02))
+wub = oracle.bf16_round(rng_b.standard_normal((hidden, ffn), dtype=np.float32) * np.float32(0.02))
+wdb = oracle.bf16_round(rng_b.standard_normal((ffn, hidden), dtype=np.float32) * np.float32(0.02))
+lo, hi = shard.column_range(ffn, rank, world)
+block = m // world
+sel = sorted({r for k in range(world) for r in (k * block, (k + 1) * block - 1)} | {127, 128, 255, 256})
+expected = np.zeros((len(sel), hidden))
+for c0 in range(0, ffn, 2048):                       # column blocks bound the float64 copies
+    cols_ = slice(c0, c0 + 2048)
+    expected += oracle.swiglu_mlp_ref(xb[sel], wgb[:, cols_], wub[:, cols_], wdb[cols_])
+shards = [bf16(t).contiguous() for t in (wgb[:, lo:hi], wub[:, lo:hi], wdb[lo:hi])]
+dxb = bf16(xb)
+failures = []
+for collective in ("nccl", "peer", "nvls"):
+    try:
+        big = tp_mlp.TensorParallelMLP(*shards, collective=collective)
+        for _ in range(3):
+            yb = big.forward(dxb, None)
+    except RuntimeError as exc:
+        if collective == "nvls" and "multicast" in str(exc):
+            print(f"rank {rank}: nvls unavailable ({exc})")
+            continue
+        raise
+    torch.cuda.synchronize()
+    # a mismatch is reported after the process group is torn down: no rank leaves while its
+    # memory is still bound to the symmetric / multicast buffers the others use
+    try:
+        ops.device_status(torch.cuda.current_stream().cuda_stream)
+        oracle.compare(yb[sel].float().cpu().numpy().astype(np.float64), expected, 2e-2, 2e-2,
+                       name=f"tp mlp at the benchmark shape ({collective})")
+    except Exception as exc:
+        failures.append(f"{collective}: {exc}")
+    dist.barrier()
+    del big
+
 rows, cols = 64, 4000                                # row shards of one masked softmax
 xs = (rng.standard_normal((rows * world, cols)) * 2).astype(np.float16)
 rlo, rhi = shard.block_range(rows * world, rank, world)
@@ -72,7 +112,11 @@ ops.softmax(dx, dy, causal_mod=True, row_offset=rlo, stream=torch.cuda.current_s
 full = oracle.masked_softmax_ref(xs, 0)
 oracle.compare(dy.float().cpu().numpy().astype(np.float64), full[rlo:rhi], 1e-2, 1e-2, name="softmax shard")
 dist.barrier()
+torch.cuda.synchronize()
 dist.destroy_process_group()
+if failures:
+    sys.stderr.write(f"[rank {rank}] " + " | ".join(failures)[-1500:] + "\n")
+    sys.exit(1)
 print(f"rank {rank} ok")
 '''
 

@@ -169,9 +169,23 @@ def test_compile_case_identity_and_counters():
     assert first.identity == second.identity != third.identity
     assert compiler.compile_count == 2 and compiler.cache_hits == 1
     assert first.provenance.startswith("compiler_b200/") and len(first.sha256) == 64
-    # options are part of the key
-    alt = make_compiler(PlanOptions(attn_p_location="smem"))
-    assert alt.identity(case)["key"] != compiler.identity(case)["key"]
+    # every switch that selects a kernel is part of the key
+    from compiler_b200.factory import KERNEL_SWITCHES
+    base_key = compiler.identity(case)["key"]
+    for name in KERNEL_SWITCHES:
+        switches = dict(PlanOptions().switches)
+        switches[name] = "another-choice"
+        alt = make_compiler(PlanOptions(switches=switches))
+        assert alt.identity(case)["key"] != base_key, name
+    assert make_compiler(PlanOptions()).identity(case)["key"] == base_key
+
+
+def test_plan_options_sample_the_environment(monkeypatch):
+    monkeypatch.setenv("B200OPS_GEMM_PAIR", "0")
+    forced = PlanOptions()
+    monkeypatch.delenv("B200OPS_GEMM_PAIR")
+    assert forced.switches["B200OPS_GEMM_PAIR"] == "0"
+    assert forced.identity_part() != PlanOptions().identity_part()
 
 
 def test_compile_case_refuses_unknown_kernels():

@@ -66,6 +66,15 @@ def test_softmax_inner(tag):
                  case["expected"]["output_ptr"], meta["dtype"])
 
 
+@pytest.mark.parametrize("tag", golden_cases.tags("softmax_multi_block_forward_kernel"))
+def test_softmax_multi_block(tag):
+    # this operator file's ref works in float32 (softmax_multi_block_forward_kernel.py:93-98)
+    case, meta = golden_cases.load(tag)
+    y = oracle.softmax_ref(case["args"]["X_ptr"])
+    _assert_same(y.astype(case["expected"]["Y_ptr"].dtype), case["expected"]["Y_ptr"],
+                 meta["dtype"])
+
+
 @pytest.mark.parametrize("tag", golden_cases.tags("matmul"))
 def test_matmul(tag):
     case, meta = golden_cases.load(tag)

@@ -1,13 +1,15 @@
 """The allocation-free comparison entry point, ``b200_allclose_f32_static``.
 
 Some users of this library cannot allocate device memory at the moment they need a
-comparison: a stream capture is open, their allocator owns the whole device, or they are in
-a loop where the device-wide stall of cudaMalloc / cudaFree is not acceptable.  For them the
-library offers a variant whose scratch is an array inside the library image.  This test
-calls it through the C ABI and requires the very same verdict and error metric as the
-allocating entry point -- twice in a row with different data, because the scratch array
-keeps the previous call's contents and a stale slot must never leak into the next result --
-and checks that a size beyond the built-in array is refused.  The file sorts last so a run
+comparison: their own allocator owns the whole device (a cudaMalloc would fail or fragment
+the pool), or they are in a loop where the device-wide stall of cudaMalloc / cudaFree is not
+acceptable.  For them the library offers a variant whose scratch is an array inside the
+library image.  This test calls it through the C ABI and requires the very same verdict and
+error metric as the allocating entry point AND as numpy (the count of elements numpy's
+isclose rejects and the largest |a - b|, computed on the host) -- twice in a row with
+different data, because the scratch array keeps the previous call's contents and a stale
+slot must never leak into the next result -- and checks that a size beyond the built-in
+array is refused.  The file sorts last so a run
 that stops at the first failure has already run everything else.
 """
 import ctypes
@@ -23,6 +25,24 @@ pytestmark = pytest.mark.gpu
 def _same(a, b):
     """(bad count, max error) pairs agree; a NaN error (a lone NaN in the data) equals itself."""
     return a[0] == b[0] and (a[1] == b[1] or (np.isnan(a[1]) and np.isnan(b[1])))
+
+
+def _numpy_expected(got, ref, rtol, atol, equal_nan):
+    """What the device must report: how many elements np.isclose rejects (float32 arithmetic,
+    as the kernel's) and the largest |got - ref| over elements that are not equal (NaN when a
+    lone NaN takes part, as the reference's int64-ordered maximum gives)."""
+    close = np.isclose(got, ref, rtol=np.float32(rtol), atol=np.float32(atol),
+                       equal_nan=equal_nan)
+    both_nan = np.isnan(got) & np.isnan(ref)
+    differs = ~((got == ref) | (both_nan if equal_nan else False))
+    delta = np.abs(got.astype(np.float64) - ref.astype(np.float64))[differs]
+    if delta.size == 0:
+        worst = 0.0
+    elif np.isnan(delta).any():
+        worst = float("nan")
+    else:
+        worst = float(delta.max())
+    return int((~close).sum()), worst
 
 
 def _both(device, got, ref, rtol, atol, equal_nan):
@@ -50,7 +70,8 @@ def test_static_scratch_variant_matches_the_allocating_one(device):
     got[11] = np.nan
     first = _both(device, got, ref, 1e-3, 1e-3, True)
     assert _same(first[0], first[1])
-    assert first[0][0] > 400 and np.isnan(first[0][1])
+    assert _same(first[1], _numpy_expected(got, ref, 1e-3, 1e-3, True))
+    assert first[1][0] > 400 and np.isnan(first[1][1])
     # call 2, right after: fewer blocks and clean data -- leftovers of call 1 in the
     # scratch array must not show up
     n2 = 70_001
@@ -58,10 +79,18 @@ def test_static_scratch_variant_matches_the_allocating_one(device):
     got2 = ref2 + np.float32(1e-6)
     second = _both(device, got2, ref2, 1e-3, 1e-3, False)
     assert _same(second[0], second[1])
-    assert second[0][0] == 0 and 0 < second[0][1] < 1e-5
+    assert _same(second[1], _numpy_expected(got2, ref2, 1e-3, 1e-3, False))
+    assert second[1][0] == 0 and 0 < second[1][1] < 1e-5
     # and once more with the first data: same answer as before
     third = _both(device, got, ref, 1e-3, 1e-3, True)
     assert _same(third[1], first[1])
+    # a comparison with violations but no NaN: exact count and exact largest difference
+    got3 = ref2.copy()
+    hit = rng.choice(n2, 97, replace=False)
+    got3[hit] += (rng.uniform(0.5, 2.0, 97) * rng.choice([-1, 1], 97)).astype(np.float32)
+    fourth = _both(device, got3, ref2, 1e-3, 1e-3, False)
+    expected = _numpy_expected(got3, ref2, 1e-3, 1e-3, False)
+    assert fourth[0] == fourth[1] == expected and expected[0] == 97
 
 
 def test_static_scratch_variant_rejects_sizes_beyond_its_array(device):
