@@ -657,14 +657,15 @@ def _mlp_expected_rows(torch, dist, mlp, x, rows):
     return expected.cpu().numpy()
 
 
-def bench_tp_mlp(torch, ops, dist, launches, peaks, source, collective):
+def bench_tp_mlp(torch, ops, dist, launches, peaks, source, collective, **options):
     """y = (silu(x Wg) * (x Wu)) Wd with the ffn dimension sharded over the ranks (strong
     scaling: the problem is fixed).  Outside the timed region every rank compares a spread of
     rows of ITS y with the float64 oracle of the unsharded MLP, and one more pass records a
     CUDA event after each phase."""
     from compiler_b200 import tp_mlp
     mlp = tp_mlp.TensorParallelMLP.synthetic(hidden=MLP_HIDDEN, ffn=MLP_FFN, rank=dist.rank,
-                                             world=dist.world, seed=34, collective=collective)
+                                             world=dist.world, seed=34, collective=collective,
+                                             **options)
     gen = torch.Generator(device="cuda").manual_seed(35)  # x is replicated: same seed on all ranks
     x = torch.randn((MLP_M, MLP_HIDDEN), generator=gen, device="cuda").to(torch.bfloat16)
     stream = torch.cuda.current_stream().cuda_stream
@@ -723,12 +724,18 @@ def bench_tp_mlp(torch, ops, dist, launches, peaks, source, collective):
     out["window"] = window
     described = {
         "nccl": "fp32 partials, NCCL all-reduce per row chunk overlapped with the next chunk's GEMM",
-        "peer": "reduce-scatter by peer stores in the GEMM epilogue + sum and broadcast kernel",
-        "nvls": "16-bit partials in symmetric memory, in-switch sum and broadcast "
-                "(multimem.ld_reduce / multimem.st), result returned in place",
+        "peer": "reduce-scatter by peer stores in the GEMM epilogue (float16 partials) + sum and "
+                "broadcast kernel",
+        "nvls": f"{str(mlp.partial_dtype).rsplit('.', 1)[-1]} partials in symmetric memory, "
+                "in-switch sum and broadcast (multimem.ld_reduce / multimem.st) per row chunk "
+                "beside the next chunk's GEMM, barriers inside the kernel",
+        "pull": "float16 partials in symmetric memory, summed by plain peer loads and "
+                "broadcast by peer stores per row chunk beside the next chunk's GEMM, "
+                "barriers inside the kernel",
         "none": "one GPU: the two GEMMs alone (anchor of the strong-scaling curve)",
     }
-    partial_bytes = MLP_M * MLP_HIDDEN * (4 if collective == "nccl" else 2)
+    partial_bytes = MLP_M * MLP_HIDDEN * (4 if collective == "nccl"
+                                          else mlp.partial_dtype.itemsize)
     out.update({"workload": f"tp_swiglu_mlp_bf16_tp{dist.world}", "scaling": "strong",
                 "collective": described[collective if dist.enabled else "none"],
                 "ms_per_step": round(region_ms, 5),
@@ -1038,14 +1045,16 @@ def main():
         if not dist.enabled:
             extras["tp_mlp"] = bench_tp_mlp(torch, ops, dist, launches, peaks, source, "nccl")
         else:
-            for key, collective in (("tp_mlp", "nccl"), ("tp_mlp_peer", "peer"),
-                                    ("tp_mlp_nvls", "nvls")):
+            for key, collective, options in (
+                    ("tp_mlp", "nccl", {}), ("tp_mlp_peer", "peer", {}),
+                    ("tp_mlp_nvls", "nvls", {}), ("tp_mlp_pull", "pull", {}),
+                    ("tp_mlp_nvls_f32", "nvls", {"partial_dtype": torch.float32})):
                 if collective == "peer" and MLP_M % (128 * dist.world):
                     continue
                 time.sleep(0.5)
                 try:
                     extras[key] = bench_tp_mlp(torch, ops, dist, launches, peaks, source,
-                                               collective)
+                                               collective, **options)
                 except Exception as exc:  # noqa: BLE001 - symmetric memory / NVLS may be unavailable
                     extras[key] = {"unavailable": f"{type(exc).__name__}: {exc}"[:300]}
     if want("siblings") and not dist.enabled:

@@ -1,22 +1,49 @@
-// All-reduce of 16-bit partial results through NVSwitch (NVLS): the merge step of the
-// tensor-parallel MLP.  Every rank holds its partial [rows, cols] in a buffer that is bound
-// to one multicast address range; a load through that range (multimem.ld_reduce) returns the
-// sum of all ranks' copies, added in the switch in fp32, and a store through it (multimem.st)
-// writes all ranks' copies at once.  Rank r reduces rows [r*rows/world, (r+1)*rows/world) and
-// publishes them, so each rank sends 1/world of the buffer up and receives the rest, and no
-// partial ever crosses a link twice.  The reference's counterpart is the merge of per-worker
-// partial slots behind a stage barrier (a100c/plan/stages.py:278-316); it has no multi-device
-// form.  The caller separates the producer of the partials, this kernel and the consumer of
-// the result with cross-rank barriers.
+// All-reduce of partial results through NVSwitch (NVLS): the merge step of the
+// tensor-parallel MLP.  Every rank holds its partial in a buffer that is bound to one
+// multicast address range; a load through that range (multimem.ld_reduce) returns the sum of
+// all ranks' copies, added in the switch in fp32, and a store through it (multimem.st) writes
+// all ranks' copies at once.  Rank r reduces the r-th share of the range and publishes it, so
+// no partial crosses a link twice.  The reference's counterpart is the merge of per-worker
+// partial slots behind a stage barrier (a100c/plan/stages.py:278-316, runtime barrier
+// a100c/runtime/pool.c:187-190); it has no multi-device form.
+//
+// The kernel can carry its own stage barriers: CTA b of every rank signals CTA b of every
+// other rank through a small symmetric flag array ("signal pad") when it starts -- the
+// producer of this rank's partial ran before it on the same stream, so the signal says "my
+// partial is complete" -- waits for the others' signals, reduces and publishes its part, and
+// signals / waits once more, so that when the kernel has finished on a rank every rank's
+// share has landed in that rank's copy.  Every wait is bounded (about two seconds by
+// %globaltimer): a rank whose peers never arrive records B200_TIMEOUT in the device status
+// word, skips the data phase and returns.
 #include "common.cuh"
 
 namespace b200 {
 namespace {
 
-template <bool BF16>
-__device__ __forceinline__ uint4 multimem_ld_reduce(const void *mc) {
+constexpr int kThreads = 256;  // small enough to be resident beside a persistent GEMM CTA
+constexpr int kMaxCtas = 512;                 // CTAs a signal pad has flags for
+constexpr uint64_t kFlagWaitNs = 2000000000ull;
+constexpr uint32_t kSiteStart = 40, kSiteEnd = 41;
+
+__device__ __forceinline__ uint64_t timer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ void st_release_sys(uint32_t *p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t *p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// 16 bytes of 16-bit partials: the switch adds in fp32 and returns the rounded sum
+template <int KIND>
+__device__ __forceinline__ uint4 multimem_ld_reduce16(const void *mc) {
   uint4 v;
-  if constexpr (BF16) {
+  if constexpr (KIND == B200_DTYPE_BFLOAT16) {
     asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0,%1,%2,%3}, [%4];"
                  : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(mc) : "memory");
   } else {
@@ -25,58 +52,297 @@ __device__ __forceinline__ uint4 multimem_ld_reduce(const void *mc) {
   }
   return v;
 }
-
-__device__ __forceinline__ void multimem_st(void *mc, uint4 v) {
+__device__ __forceinline__ float4 multimem_ld_reduce_f32(const void *mc) {
+  float4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0,%1,%2,%3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(mc) : "memory");
+  return v;
+}
+__device__ __forceinline__ void multimem_st16(void *mc, uint4 v) {
   asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};"
                :: "l"(mc), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
 
-// vecs 16-byte vectors starting at mc: four reduced loads in flight per thread, then the
-// four stores.
-template <bool BF16>
-__global__ void __launch_bounds__(512)
-multimem_allreduce_kernel(uint4 *mc, int64_t vecs) {
+template <int OUT> __device__ __forceinline__ uint32_t pack2(float a, float b) {
+  if constexpr (OUT == B200_DTYPE_BFLOAT16) {
+    const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<const uint32_t *>(&h);
+  } else {
+    const __half2 h = __floats2half2_rn(a, b);
+    return *reinterpret_cast<const uint32_t *>(&h);
+  }
+}
+template <int IN> __device__ __forceinline__ float2 unpack2(uint32_t w) {
+  if constexpr (IN == B200_DTYPE_BFLOAT16)
+    return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
+  else
+    return __half22float2(*reinterpret_cast<const __half2 *>(&w));
+}
+
+// One output vector of 8 elements (16 bytes): the in-switch sum of the 8 input elements that
+// start at element `e` of the partial, rounded once to the output type.
+template <int IN, int OUT>
+__device__ __forceinline__ uint4 reduced_vector(const uint8_t *in_mc, int64_t e) {
+  if constexpr (IN == B200_DTYPE_FLOAT32) {
+    const float4 a = multimem_ld_reduce_f32(in_mc + e * 4);
+    const float4 b = multimem_ld_reduce_f32(in_mc + e * 4 + 16);
+    return make_uint4(pack2<OUT>(a.x, a.y), pack2<OUT>(a.z, a.w), pack2<OUT>(b.x, b.y),
+                      pack2<OUT>(b.z, b.w));
+  } else {
+    uint4 v = multimem_ld_reduce16<IN>(in_mc + e * 2);
+    if constexpr (IN != OUT) {
+      uint32_t *w = &v.x;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 f = unpack2<IN>(w[i]);
+        w[i] = pack2<OUT>(f.x, f.y);
+      }
+    }
+    return v;
+  }
+}
+
+struct SignalPads {
+  uint32_t *pad[8];  // pad[k]: rank k's flag array [2][kMaxCtas][8], mapped into this process
+};
+
+// Signals every rank and waits for every rank, for this CTA's index.  Returns false when a
+// wait ran out.  phase 0 = start of the kernel, 1 = end.
+__device__ __forceinline__ bool cross_rank_barrier(const SignalPads &pads, int rank, int world,
+                                                   int phase, uint32_t epoch,
+                                                   unsigned int *status, uint32_t site) {
+  __shared__ int ok_flag[2];
+  if (threadIdx.x == 0) ok_flag[phase] = 1;
+  __syncthreads();  // also: this CTA's earlier stores are ordered before the signals below
+  if ((int)threadIdx.x < world) {
+    const int peer = (int)threadIdx.x;
+    const size_t slot = ((size_t)phase * kMaxCtas + blockIdx.x) * 8;
+    st_release_sys(pads.pad[peer] + slot + rank, epoch);
+    const uint32_t *mine = pads.pad[rank] + slot + peer;
+    const uint64_t t0 = timer_ns();
+    for (uint32_t it = 0;; ++it) {
+      // flags only grow; a peer can be at most one epoch ahead
+      if ((int32_t)(ld_acquire_sys(mine) - epoch) >= 0) break;
+      if ((it & 0x3f) == 0x3f && timer_ns() - t0 > kFlagWaitNs) {
+        atomicOr(status, (unsigned)B200_TIMEOUT | (site << 8));
+        ok_flag[phase] = 0;
+        break;
+      }
+    }
+  }
+  __syncthreads();
+  return ok_flag[phase] != 0;
+}
+
+// vecs output vectors (8 elements each) of this rank's share; the share starts at element
+// `first` of both buffers.  Four reduced loads in flight per thread, then the four stores.
+template <int IN, int OUT, bool SYNC>
+__global__ void __launch_bounds__(kThreads)
+multimem_allreduce_kernel(const uint8_t *in_mc, uint8_t *out_mc, int64_t first, int64_t vecs,
+                          SignalPads pads, int rank, int world, uint32_t epoch,
+                          unsigned int *status) {
+  if constexpr (SYNC) {
+    if (!cross_rank_barrier(pads, rank, world, 0, epoch, status, kSiteStart)) return;
+  }
   constexpr int U = 4;
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < vecs; i += stride * U) {
     uint4 v[U];
 #pragma unroll
     for (int u = 0; u < U; ++u)
-      if (i + u * stride < vecs) v[u] = multimem_ld_reduce<BF16>(mc + i + u * stride);
+      if (i + u * stride < vecs) v[u] = reduced_vector<IN, OUT>(in_mc, first + (i + u * stride) * 8);
 #pragma unroll
     for (int u = 0; u < U; ++u)
-      if (i + u * stride < vecs) multimem_st(mc + i + u * stride, v[u]);
+      if (i + u * stride < vecs) multimem_st16(out_mc + (first + (i + u * stride) * 8) * 2, v[u]);
   }
+  if constexpr (SYNC) cross_rank_barrier(pads, rank, world, 1, epoch, status, kSiteEnd);
+}
+
+// The same all-reduce without the switch's arithmetic: this rank loads its share of every
+// rank's partial with plain peer loads (16 bytes each, all ranks' loads of a vector in
+// flight together), adds them in fp32 in rank order, rounds once and stores the result into
+// every rank's output with plain peer stores.
+struct RankPointers {
+  void *ptr[8];
+};
+
+template <typename TIn, typename TOut, bool SYNC>
+__global__ void __launch_bounds__(kThreads)
+peer_allreduce_kernel(RankPointers partial, RankPointers out, int64_t first, int64_t vecs,
+                      SignalPads pads, int rank, int world, uint32_t epoch,
+                      unsigned int *status) {
+  if constexpr (SYNC) {
+    if (!cross_rank_barrier(pads, rank, world, 0, epoch, status, kSiteStart)) return;
+  }
+  constexpr int N = 8;  // elements per 16-byte vector of a 16-bit type
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < vecs; i += stride) {
+    const int64_t e = first + i * N;
+    vec16<TIn> v[8];
+#pragma unroll
+    for (int w = 0; w < 8; ++w)
+      if (w < world) v[w].raw = ld_stream16(static_cast<const TIn *>(partial.ptr[w]) + e);
+    float acc[N];
+#pragma unroll
+    for (int j = 0; j < N; ++j) acc[j] = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w)
+      if (w < world) {
+#pragma unroll
+        for (int j = 0; j < N; ++j) acc[j] += io<TIn>::load(v[w].e[j]);
+      }
+    vec16<TOut> r;
+#pragma unroll
+    for (int j = 0; j < N; ++j) r.e[j] = io<TOut>::store(acc[j]);
+#pragma unroll
+    for (int w = 0; w < 8; ++w)
+      if (w < world) *reinterpret_cast<uint4 *>(static_cast<TOut *>(out.ptr[w]) + e) = r.raw;
+  }
+  if constexpr (SYNC) cross_rank_barrier(pads, rank, world, 1, epoch, status, kSiteEnd);
+}
+
+template <typename TIn, typename TOut>
+int launch_peer(const RankPointers &partial, const RankPointers &out, int64_t first, int64_t vecs,
+                const SignalPads &pads, bool sync, int rank, int world, uint32_t epoch, int ctas,
+                cudaStream_t s) {
+  int64_t blocks = (vecs + kThreads - 1) / kThreads;
+  int64_t cap = ctas > 0 ? ctas : (int64_t)sm_count() * 2;
+  if (cap > kMaxCtas) cap = kMaxCtas;
+  if (blocks > cap) blocks = cap;
+  if (blocks < 1) blocks = 1;
+  unsigned int *status = device_status_word();
+  if (status == nullptr) return fail(B200_RESOURCE, "no status word on this device");
+  if (sync)
+    peer_allreduce_kernel<TIn, TOut, true><<<(unsigned)blocks, kThreads, 0, s>>>(
+        partial, out, first, vecs, pads, rank, world, epoch, status);
+  else
+    peer_allreduce_kernel<TIn, TOut, false><<<(unsigned)blocks, kThreads, 0, s>>>(
+        partial, out, first, vecs, pads, rank, world, epoch, status);
+  B200_CUDA_OK(cudaGetLastError());
+  return B200_OK;
+}
+
+template <int IN, int OUT>
+int launch(const void *in_mc, void *out_mc, int64_t first, int64_t vecs, const SignalPads &pads,
+           bool sync, int rank, int world, uint32_t epoch, int ctas, cudaStream_t s) {
+  int64_t blocks = (vecs + kThreads * 4 - 1) / (kThreads * 4);
+  int64_t cap = ctas > 0 ? ctas : (int64_t)sm_count() * 2;
+  if (cap > kMaxCtas) cap = kMaxCtas;
+  if (blocks > cap) blocks = cap;
+  if (blocks < 1) blocks = 1;
+  unsigned int *status = device_status_word();
+  if (status == nullptr) return fail(B200_RESOURCE, "no status word on this device");
+  if (sync)
+    multimem_allreduce_kernel<IN, OUT, true><<<(unsigned)blocks, kThreads, 0, s>>>(
+        (const uint8_t *)in_mc, (uint8_t *)out_mc, first, vecs, pads, rank, world, epoch, status);
+  else
+    multimem_allreduce_kernel<IN, OUT, false><<<(unsigned)blocks, kThreads, 0, s>>>(
+        (const uint8_t *)in_mc, (uint8_t *)out_mc, first, vecs, pads, rank, world, epoch, status);
+  B200_CUDA_OK(cudaGetLastError());
+  return B200_OK;
 }
 
 }  // namespace
 }  // namespace b200
 
-extern "C" int b200_multimem_allreduce(void *multicast_base, uint32_t dtype, int64_t offset,
-                                       int64_t count, int rank, int world, int ctas,
+extern "C" size_t b200_signal_pad_bytes(void) {
+  return (size_t)2 * b200::kMaxCtas * 8 * sizeof(uint32_t);
+}
+
+extern "C" int b200_multimem_allreduce(const void *in_multicast, uint32_t in_dtype,
+                                       void *out_multicast, uint32_t out_dtype, int64_t offset,
+                                       int64_t count, int rank, int world,
+                                       void *const *signal_pads, uint32_t epoch, int ctas,
                                        void *stream) {
   using namespace b200;
-  if (multicast_base == nullptr) return fail(B200_USAGE, "null multicast pointer");
-  B200_REQUIRE(dtype == B200_DTYPE_BFLOAT16 || dtype == B200_DTYPE_FLOAT16,
-               "partials are f16 or bf16");
+  if (in_multicast == nullptr || out_multicast == nullptr)
+    return fail(B200_USAGE, "null multicast pointer");
+  B200_REQUIRE(in_dtype == B200_DTYPE_BFLOAT16 || in_dtype == B200_DTYPE_FLOAT16 ||
+               in_dtype == B200_DTYPE_FLOAT32, "partials are f16, bf16 or f32");
+  B200_REQUIRE(out_dtype == B200_DTYPE_BFLOAT16 || out_dtype == B200_DTYPE_FLOAT16,
+               "the result is f16 or bf16");
   B200_REQUIRE(world >= 1 && world <= 8 && rank >= 0 && rank < world,
                "rank %d / world %d out of range", rank, world);
   B200_REQUIRE(offset >= 0 && count >= 0 && offset % 8 == 0 && count % (8 * world) == 0,
-               "offset and count / world must be multiples of 8 elements (16 bytes)");
-  B200_REQUIRE((uintptr_t)multicast_base % 16 == 0, "multicast pointer is not 16-byte aligned");
-  if (count == 0) return B200_OK;
-  const int64_t share = count / world;  // elements this rank reduces and publishes
+               "offset and count / world must be multiples of 8 elements");
+  B200_REQUIRE((uintptr_t)in_multicast % 16 == 0 && (uintptr_t)out_multicast % 16 == 0,
+               "multicast pointers must be 16-byte aligned");
+  B200_REQUIRE(in_dtype != B200_DTYPE_FLOAT32 || in_multicast != out_multicast,
+               "f32 partials cannot be reduced in place into a 16-bit result");
+  SignalPads pads;
+  for (int k = 0; k < 8; ++k) pads.pad[k] = nullptr;
+  const bool sync = signal_pads != nullptr;
+  if (sync) {
+    B200_REQUIRE(epoch != 0, "epoch 0 is the cleared state of the signal pads: start at 1");
+    for (int k = 0; k < world; ++k) {
+      B200_REQUIRE(signal_pads[k] != nullptr && (uintptr_t)signal_pads[k] % 4 == 0,
+                   "signal pad of rank %d is null or unaligned", k);
+      pads.pad[k] = static_cast<uint32_t *>(signal_pads[k]);
+    }
+  }
+  if (count == 0 && !sync) return B200_OK;
+  const int64_t share = count / world;
+  const int64_t first = offset + (int64_t)rank * share;
   const int64_t vecs = share / 8;
-  uint4 *first = reinterpret_cast<uint4 *>(
-      static_cast<uint8_t *>(multicast_base) + (offset + (int64_t)rank * share) * 2);
-  int64_t blocks = (vecs + 512 * 4 - 1) / (512 * 4);
-  const int64_t cap = ctas > 0 ? ctas : (int64_t)sm_count() * 2;
-  if (blocks > cap) blocks = cap;
   cudaStream_t s = (cudaStream_t)stream;
-  if (dtype == B200_DTYPE_BFLOAT16)
-    multimem_allreduce_kernel<true><<<(unsigned)blocks, 512, 0, s>>>(first, vecs);
-  else
-    multimem_allreduce_kernel<false><<<(unsigned)blocks, 512, 0, s>>>(first, vecs);
-  B200_CUDA_OK(cudaGetLastError());
-  return B200_OK;
+#define B200_AR(IN, OUT) \
+  return launch<IN, OUT>(in_multicast, out_multicast, first, vecs, pads, sync, rank, world, \
+                         epoch, ctas, s)
+  if (out_dtype == B200_DTYPE_BFLOAT16) {
+    if (in_dtype == B200_DTYPE_FLOAT32) B200_AR(B200_DTYPE_FLOAT32, B200_DTYPE_BFLOAT16);
+    if (in_dtype == B200_DTYPE_FLOAT16) B200_AR(B200_DTYPE_FLOAT16, B200_DTYPE_BFLOAT16);
+    B200_AR(B200_DTYPE_BFLOAT16, B200_DTYPE_BFLOAT16);
+  }
+  if (in_dtype == B200_DTYPE_FLOAT32) B200_AR(B200_DTYPE_FLOAT32, B200_DTYPE_FLOAT16);
+  if (in_dtype == B200_DTYPE_BFLOAT16) B200_AR(B200_DTYPE_BFLOAT16, B200_DTYPE_FLOAT16);
+  B200_AR(B200_DTYPE_FLOAT16, B200_DTYPE_FLOAT16);
+#undef B200_AR
+}
+
+extern "C" int b200_peer_allreduce(void *const *partial_rank, uint32_t in_dtype,
+                                   void *const *out_rank, uint32_t out_dtype, int64_t offset,
+                                   int64_t count, int rank, int world, void *const *signal_pads,
+                                   uint32_t epoch, int ctas, void *stream) {
+  using namespace b200;
+  if (partial_rank == nullptr || out_rank == nullptr) return fail(B200_USAGE, "null argument");
+  B200_REQUIRE((in_dtype == B200_DTYPE_BFLOAT16 || in_dtype == B200_DTYPE_FLOAT16) &&
+               (out_dtype == B200_DTYPE_BFLOAT16 || out_dtype == B200_DTYPE_FLOAT16),
+               "partials and result are f16 or bf16");
+  B200_REQUIRE(world >= 1 && world <= 8 && rank >= 0 && rank < world,
+               "rank %d / world %d out of range", rank, world);
+  B200_REQUIRE(offset >= 0 && count >= 0 && offset % 8 == 0 && count % (8 * world) == 0,
+               "offset and count / world must be multiples of 8 elements");
+  RankPointers partial, out;
+  SignalPads pads;
+  for (int k = 0; k < 8; ++k) partial.ptr[k] = out.ptr[k] = nullptr, pads.pad[k] = nullptr;
+  for (int k = 0; k < world; ++k) {
+    B200_REQUIRE(partial_rank[k] != nullptr && (uintptr_t)partial_rank[k] % 16 == 0 &&
+                 out_rank[k] != nullptr && (uintptr_t)out_rank[k] % 16 == 0,
+                 "buffer of rank %d is null or unaligned", k);
+    partial.ptr[k] = partial_rank[k];
+    out.ptr[k] = out_rank[k];
+  }
+  const bool sync = signal_pads != nullptr;
+  if (sync) {
+    B200_REQUIRE(epoch != 0, "epoch 0 is the cleared state of the signal pads: start at 1");
+    for (int k = 0; k < world; ++k) {
+      B200_REQUIRE(signal_pads[k] != nullptr && (uintptr_t)signal_pads[k] % 4 == 0,
+                   "signal pad of rank %d is null or unaligned", k);
+      pads.pad[k] = static_cast<uint32_t *>(signal_pads[k]);
+    }
+  }
+  if (count == 0 && !sync) return B200_OK;
+  const int64_t share = count / world;
+  const int64_t first = offset + (int64_t)rank * share;
+  const int64_t vecs = share / 8;
+  cudaStream_t s = (cudaStream_t)stream;
+#define B200_PAR(TIn, TOut) \
+  return launch_peer<TIn, TOut>(partial, out, first, vecs, pads, sync, rank, world, epoch, ctas, s)
+  if (in_dtype == B200_DTYPE_BFLOAT16 && out_dtype == B200_DTYPE_BFLOAT16)
+    B200_PAR(__nv_bfloat16, __nv_bfloat16);
+  if (in_dtype == B200_DTYPE_FLOAT16 && out_dtype == B200_DTYPE_BFLOAT16)
+    B200_PAR(__half, __nv_bfloat16);
+  if (in_dtype == B200_DTYPE_BFLOAT16) B200_PAR(__nv_bfloat16, __half);
+  B200_PAR(__half, __half);
+#undef B200_PAR
 }

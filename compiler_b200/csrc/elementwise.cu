@@ -117,12 +117,14 @@ allclose_f32_kernel(const float *__restrict__ a, const float *__restrict__ b,
 // there by every rank's GEMM epilogue); each thread sums one 16-byte column group over
 // the slices in fp32, rounds once and stores the result into the owned rows of EVERY
 // rank's output (plain peer stores over NVLink for the other ranks).
-template <typename T>
+template <typename T, typename OutT>
 __global__ void __launch_bounds__(256)
 reduce_slices_broadcast_kernel(const T *__restrict__ staging, int world, int64_t rows, int cols,
-                               int64_t dst_row0, T *y0, T *y1, T *y2, T *y3, T *y4, T *y5, T *y6, T *y7) {
+                               int64_t dst_row0, OutT *y0, OutT *y1, OutT *y2, OutT *y3, OutT *y4,
+                               OutT *y5, OutT *y6, OutT *y7) {
+  static_assert(sizeof(T) == sizeof(OutT), "staged and result elements have one size");
   constexpr int N = vec16<T>::N;
-  T *const y_rank[8] = {y0, y1, y2, y3, y4, y5, y6, y7};
+  OutT *const y_rank[8] = {y0, y1, y2, y3, y4, y5, y6, y7};
   const int vec_per_row = cols / N;
   const int64_t total = rows * vec_per_row;
   const int64_t slice = rows * (int64_t)cols;
@@ -139,9 +141,9 @@ reduce_slices_broadcast_kernel(const T *__restrict__ staging, int world, int64_t
 #pragma unroll
       for (int j = 0; j < N; ++j) acc[j] += io<T>::load(v.e[j]);
     }
-    vec16<T> out;
+    vec16<OutT> out;
 #pragma unroll
-    for (int j = 0; j < N; ++j) out.e[j] = io<T>::store(acc[j]);
+    for (int j = 0; j < N; ++j) out.e[j] = io<OutT>::store(acc[j]);
     const int64_t off = (dst_row0 + r) * cols + c;
 #pragma unroll
     for (int w = 0; w < 8; ++w)
@@ -387,14 +389,16 @@ extern "C" int b200_allclose_f32_static(const void *actual, const void *expected
   return B200_OK;
 }
 
-extern "C" int b200_reduce_slices_broadcast(const void *staging, uint32_t dtype, int world,
-                                            int64_t rows, int64_t cols, int64_t dst_row0,
-                                            void *const *y_rank, void *stream) {
+extern "C" int b200_reduce_slices_broadcast(const void *staging, uint32_t dtype,
+                                            uint32_t out_dtype, int world, int64_t rows,
+                                            int64_t cols, int64_t dst_row0, void *const *y_rank,
+                                            void *stream) {
   using namespace b200;
   if (staging == nullptr || y_rank == nullptr) return fail(B200_USAGE, "null argument");
   B200_REQUIRE(world >= 1 && world <= 8, "world %d out of range", world);
-  B200_REQUIRE(dtype == B200_DTYPE_BFLOAT16 || dtype == B200_DTYPE_FLOAT16,
-               "partials are f16 or bf16");
+  B200_REQUIRE((dtype == B200_DTYPE_BFLOAT16 || dtype == B200_DTYPE_FLOAT16) &&
+               (out_dtype == B200_DTYPE_BFLOAT16 || out_dtype == B200_DTYPE_FLOAT16),
+               "partials and result are f16 or bf16");
   B200_REQUIRE(rows >= 0 && cols > 0 && cols % 8 == 0 && cols < (1 << 30) && dst_row0 >= 0,
                "rows / cols out of range (cols must be a multiple of 8)");
   B200_REQUIRE((uintptr_t)staging % 16 == 0, "staging is not 16-byte aligned");
@@ -410,17 +414,19 @@ extern "C" int b200_reduce_slices_broadcast(const void *staging, uint32_t dtype,
   const int64_t cap = (int64_t)sm_count() * 8;
   if (blocks > cap) blocks = cap;
   cudaStream_t s = (cudaStream_t)stream;
-  if (dtype == B200_DTYPE_BFLOAT16) {
-    using T = __nv_bfloat16;
-    reduce_slices_broadcast_kernel<T><<<(unsigned)blocks, 256, 0, s>>>(
-        (const T *)staging, world, rows, (int)cols, dst_row0, (T *)y[0], (T *)y[1],
-        (T *)y[2], (T *)y[3], (T *)y[4], (T *)y[5], (T *)y[6], (T *)y[7]);
-  } else {
-    using T = __half;
-    reduce_slices_broadcast_kernel<T><<<(unsigned)blocks, 256, 0, s>>>(
-        (const T *)staging, world, rows, (int)cols, dst_row0, (T *)y[0], (T *)y[1],
-        (T *)y[2], (T *)y[3], (T *)y[4], (T *)y[5], (T *)y[6], (T *)y[7]);
-  }
+#define B200_RSB(T, O)                                                                         \
+  reduce_slices_broadcast_kernel<T, O><<<(unsigned)blocks, 256, 0, s>>>(                       \
+      (const T *)staging, world, rows, (int)cols, dst_row0, (O *)y[0], (O *)y[1], (O *)y[2],   \
+      (O *)y[3], (O *)y[4], (O *)y[5], (O *)y[6], (O *)y[7])
+  if (dtype == B200_DTYPE_BFLOAT16 && out_dtype == B200_DTYPE_BFLOAT16)
+    B200_RSB(__nv_bfloat16, __nv_bfloat16);
+  else if (dtype == B200_DTYPE_FLOAT16 && out_dtype == B200_DTYPE_BFLOAT16)
+    B200_RSB(__half, __nv_bfloat16);
+  else if (dtype == B200_DTYPE_BFLOAT16)
+    B200_RSB(__nv_bfloat16, __half);
+  else
+    B200_RSB(__half, __half);
+#undef B200_RSB
   B200_CUDA_OK(cudaGetLastError());
   return B200_OK;
 }

@@ -1035,8 +1035,11 @@ static int gemm_impl(const b200_tensor *a, const b200_tensor *b, const b200_tens
   }
   B200_REQUIRE(is_float_io(a->dtype), "a: dtype %u is not f16/bf16/f32", a->dtype);
   B200_REQUIRE(b->dtype == a->dtype, "a/b dtypes differ (%u/%u)", a->dtype, b->dtype);
-  B200_REQUIRE(c->dtype == a->dtype || c->dtype == B200_DTYPE_FLOAT32,
-               "c dtype %u must be a's dtype or f32", c->dtype);
+  // a 16-bit product may be stored in the other 16-bit type (float16 partials of bfloat16
+  // operands keep three more mantissa bits at the same size)
+  B200_REQUIRE(c->dtype == a->dtype || c->dtype == B200_DTYPE_FLOAT32 ||
+               (a->dtype != B200_DTYPE_FLOAT32 && is_float_io(c->dtype)),
+               "c dtype %u must be a's dtype, the other 16-bit type or f32", c->dtype);
   const int64_t M = a->shape[0], K = a->shape[1], N = b->shape[b_rows_are_n ? 0 : 1];
   B200_REQUIRE(b->shape[b_rows_are_n ? 1 : 0] == K, "a is [%lld,%lld] but b has K = %lld",
                (long long)M, (long long)K, (long long)b->shape[b_rows_are_n ? 1 : 0]);
@@ -1082,6 +1085,9 @@ static int gemm_impl(const b200_tensor *a, const b200_tensor *b, const b200_tens
       B200_REQUIRE(scatter->c_rank[r] != nullptr && (uintptr_t)scatter->c_rank[r] % 16 == 0,
                    "destination pointer of rank %d is null or unaligned", r);
   }
+  if (!tensor_core)
+    B200_REQUIRE(c->dtype == a->dtype || c->dtype == B200_DTYPE_FLOAT32,
+                 "the CUDA-core paths store c in a's dtype or f32 (got %u)", c->dtype);
   if (!tensor_core && act == kActLogSoftmax) {
     B200_REQUIRE(b_rows_are_n, "the CUDA-core log-softmax path takes B as [N, K]");
 #define B200_LLS(T, OutT)                                                                   \
@@ -1099,6 +1105,7 @@ static int gemm_impl(const b200_tensor *a, const b200_tensor *b, const b200_tens
   }
   if (!tensor_core) {
     B200_REQUIRE(!b_rows_are_n, "B as [N, K] is taken by the tensor-core path only");
+
     if (a->dtype == B200_DTYPE_FLOAT32) return launch_simt<float, float>(a, b, b2, bias, c, act, s, row_scale, gn);
     if (a->dtype == B200_DTYPE_FLOAT16) {
       return c->dtype == B200_DTYPE_FLOAT32

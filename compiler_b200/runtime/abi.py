@@ -95,10 +95,13 @@ PROTOTYPES = {
     "b200_elementwise": (c_int, [c_int, _T, _T, _T, c_float, c_float, c_float, _PTR]),
     "b200_gemm_bias_act": (c_int, [_T, _T, _T, _T, _T, c_int, _PTR]),
     "b200_gemm_scatter_rows": (c_int, [_T, _T, _T, POINTER(_PTR), c_int, c_int, c_int64, _PTR]),
-    "b200_reduce_slices_broadcast": (c_int, [_PTR, c_uint32, c_int, c_int64, c_int64, c_int64,
-                                             POINTER(_PTR), _PTR]),
-    "b200_multimem_allreduce": (c_int, [_PTR, c_uint32, c_int64, c_int64, c_int, c_int, c_int,
-                                        _PTR]),
+    "b200_reduce_slices_broadcast": (c_int, [_PTR, c_uint32, c_uint32, c_int, c_int64, c_int64,
+                                             c_int64, POINTER(_PTR), _PTR]),
+    "b200_multimem_allreduce": (c_int, [_PTR, c_uint32, _PTR, c_uint32, c_int64, c_int64, c_int,
+                                        c_int, POINTER(_PTR), c_uint32, c_int, _PTR]),
+    "b200_signal_pad_bytes": (c_size_t, []),
+    "b200_peer_allreduce": (c_int, [POINTER(_PTR), c_uint32, POINTER(_PTR), c_uint32, c_int64,
+                                    c_int64, c_int, c_int, POINTER(_PTR), c_uint32, c_int, _PTR]),
     "b200_attn_fwd": (c_int, [_T, _T, _T, _T, _T, c_float, c_int, _PTR]),
     "b200_stream_wait_event": (c_int, [_PTR, _PTR]),
     "b200_graph_begin_capture": (c_int, [_PTR]),

@@ -35,7 +35,14 @@ Two ways to sum the partials:
     place; a second barrier publishes it.  No partial crosses a link twice and the GEMM's
     epilogue stores stay local.  The result is returned in the symmetric buffer itself (no
     copy) when ``forward`` gets no ``y``.  Needs NVLS (a multicast pointer from
-    ``torch.distributed._symmetric_memory``) and M * hidden to be a multiple of 8 * world.
+    ``torch.distributed._symmetric_memory``) and M * hidden to be a multiple of 8 * world;
+  * ``collective="pull"``: the same structure without the switch's arithmetic
+    (``b200_peer_allreduce``): each rank loads its share of every rank's partial with plain
+    peer loads, adds in fp32 and stores the result to every rank.
+
+The nvls and pull paths cut the down-projection into row chunks; the all-reduce of a chunk
+carries its own cross-rank barriers (flags in symmetric memory, bounded waits) and runs on a
+second stream beside the next chunk's GEMM.
 
 ``forward(x, y, mark=...)`` calls ``mark(name)`` after it has enqueued each phase, so a caller
 can record a CUDA event per phase on the current stream.
@@ -49,26 +56,47 @@ from compiler_b200.runtime import abi
 class TensorParallelMLP:
     kernels_per_forward = None  # set in __init__: 1 fused up-projection + one GEMM per chunk
 
-    def __init__(self, wg, wu, wd, *, group=None, chunks: int = 4, collective: str = "nccl"):
+    def __init__(self, wg, wu, wd, *, group=None, chunks: int = 4, collective: str = "nccl",
+                 partial_dtype=None, comm_ctas: int = 0):
         """wg, wu: this rank's [hidden, ffn/tp] column shards; wd: its [ffn/tp, hidden] row
-        shard (CUDA bf16/fp16 torch tensors, contiguous)."""
+        shard (CUDA bf16/fp16 torch tensors, contiguous).
+
+        ``chunks``: row chunks of the down-projection whose all-reduce overlaps the next
+        chunk's GEMM (nccl and nvls paths).  ``partial_dtype`` (peer and nvls paths): the type
+        the partial products are staged in -- ``torch.float16`` by default: against bfloat16 it
+        keeps three more mantissa bits at the same traffic, which is what keeps the sum of
+        ``world`` partials within 2e-2 of the float64 result where bfloat16 partials of
+        opposite sign cancel; its range is 65504, so operands whose partial products can
+        exceed that need ``torch.float32`` (nvls path only: twice the traffic into the switch,
+        the exact sum) -- or the weights' own type.  ``comm_ctas``: grid limit of the
+        in-switch all-reduce kernel while it runs beside a GEMM (0 = default)."""
         import torch
         self.torch = torch
         self.wg, self.wu, self.wd = wg, wu, wd
         self.group = group
         self.chunks = max(1, int(chunks))
-        if collective not in ("nccl", "peer", "nvls"):
-            raise ValueError("collective must be 'nccl', 'peer' or 'nvls'")
+        if collective not in ("nccl", "peer", "nvls", "pull"):
+            raise ValueError("collective must be 'nccl', 'peer', 'nvls' or 'pull'")
         self.collective = collective
         # this library's kernels per forward (NCCL's and the barrier kernels are not counted)
-        self.kernels_per_forward = 1 + self.chunks if collective == "nccl" else 3
+        self.kernels_per_forward = {"nccl": 1 + self.chunks, "peer": 3,
+                                    "nvls": 1 + 2 * self.chunks,
+                                    "pull": 1 + 2 * self.chunks}[collective]
+        self.partial_dtype = torch.float16 if partial_dtype is None else partial_dtype
+        if collective in ("peer", "pull") and self.partial_dtype not in (torch.float16,
+                                                                         torch.bfloat16):
+            raise ValueError(f"collective='{collective}' stages 16-bit partials")
+        self.comm_ctas = int(comm_ctas)
+        self._epoch = 0
+        self._comm_stream = None
         self._h = None
         self._partial = None
         self._peer = None  # (rows, staging, staging handle, y, y handle)
         self._nvls = None  # (key, partial, handle)
 
     @classmethod
-    def synthetic(cls, hidden, ffn, rank, world, seed=0, dtype=None, chunks=4, collective="nccl"):
+    def synthetic(cls, hidden, ffn, rank, world, seed=0, dtype=None, chunks=4, collective="nccl",
+                  **options):
         """Random-normal(0, 0.02) weights; every rank draws only its own shard, from a
         generator seeded by (seed, rank)."""
         import torch
@@ -77,7 +105,7 @@ class TensorParallelMLP:
         gen = torch.Generator(device="cuda").manual_seed(seed * 1000 + rank)
         make = lambda *s: (torch.randn(s, generator=gen, device="cuda") * 0.02).to(dtype)  # noqa: E731
         return cls(make(hidden, hi - lo), make(hidden, hi - lo), make(hi - lo, hidden),
-                   chunks=chunks, collective=collective)
+                   chunks=chunks, collective=collective, **options)
 
     def forward(self, x, y=None, mark=None):
         """x: [M, hidden] replicated; y: [M, hidden] receives the all-reduced result.  With
@@ -95,7 +123,7 @@ class TensorParallelMLP:
         mark("up_projection")
         if self.collective == "peer":
             return self._forward_peer(y, stream, mark)
-        if self.collective == "nvls":
+        if self.collective in ("nvls", "pull"):
             return self._forward_nvls(y, stream, mark)
         if y is None:
             y = torch.empty((m, self.wd.shape[1]), device=x.device, dtype=x.dtype)
@@ -131,7 +159,8 @@ class TensorParallelMLP:
         if self._peer is None or self._peer[0] != (m, hidden, dtype):
             group = self.group if self.group is not None else dist.group.WORLD
             rows = m // world
-            staging = symm_mem.empty((world, rows, hidden), dtype=dtype, device=device)
+            staging = symm_mem.empty((world, rows, hidden), dtype=self.partial_dtype,
+                                     device=device)
             staging_h = symm_mem.rendezvous(staging, group=group)
             out = symm_mem.empty((m, hidden), dtype=dtype, device=device)
             out_h = symm_mem.rendezvous(out, group=group)
@@ -155,7 +184,7 @@ class TensorParallelMLP:
                              tuple(self._h.stride()))
         wd = abi.make_tensor(self.wd.data_ptr(), self.wd.shape, self.wd.dtype,
                              tuple(self.wd.stride()))
-        c_like = abi.make_tensor(out.data_ptr(), (m, hidden), out.dtype)
+        c_like = abi.make_tensor(out.data_ptr(), (m, hidden), staging.dtype)
         abi.check(lib.b200_gemm_scatter_rows(ctypes.byref(hd), ctypes.byref(wd),
                                              ctypes.byref(c_like), staging_ptrs, world, rank,
                                              rows, stream))
@@ -163,8 +192,9 @@ class TensorParallelMLP:
         staging_h.barrier(channel=0)  # every rank's tiles for my rows have landed
         mark("barrier_partials")
         abi.check(lib.b200_reduce_slices_broadcast(
-            staging.data_ptr(), abi.DTYPE_CODES[abi.dtype_name(out.dtype)], world, rows, hidden,
-            rank * rows, out_ptrs, stream))
+            staging.data_ptr(), abi.DTYPE_CODES[abi.dtype_name(staging.dtype)],
+            abi.DTYPE_CODES[abi.dtype_name(out.dtype)], world, rows, hidden, rank * rows,
+            out_ptrs, stream))
         mark("reduce_broadcast")
         out_h.barrier(channel=1)      # every rank's slice is in my output
         mark("barrier_result")
@@ -175,42 +205,94 @@ class TensorParallelMLP:
         return out
 
     # ------------------------------------------------------------------ in-switch path
-    def _nvls_buffer(self, m, hidden, dtype, device):
+    def _nvls_buffers(self, m, hidden, dtype, device):
+        """(partial, partial handle, out, out handle, pad pointers): the partial in
+        ``partial_dtype``, the result in the operands' type (the same buffer when both are
+        16-bit: reduced in place), and the flag arrays of the kernel's own barriers."""
+        import ctypes
+
         import torch.distributed as dist
         import torch.distributed._symmetric_memory as symm_mem
+        torch = self.torch
         world = dist.get_world_size(self.group)
         if (m * hidden) % (8 * world):
             raise ValueError(f"collective='nvls' needs M * hidden ({m * hidden}) to be a "
                              f"multiple of {8 * world}")
-        key = (m, hidden, dtype)
+        key = (m, hidden, dtype, self.partial_dtype)
         if self._nvls is None or self._nvls[0] != key:
             group = self.group if self.group is not None else dist.group.WORLD
-            partial = symm_mem.empty((m, hidden), dtype=dtype, device=device)
-            handle = symm_mem.rendezvous(partial, group=group)
-            if not int(getattr(handle, "multicast_ptr", 0) or 0):
-                raise RuntimeError("symmetric memory has no multicast pointer on this system "
-                                   "(NVLS unavailable): use collective='peer'")
-            self._nvls = (key, partial, handle)
-        return self._nvls[1:]
+            partial = symm_mem.empty((m, hidden), dtype=self.partial_dtype, device=device)
+            partial_h = symm_mem.rendezvous(partial, group=group)
+            if partial.element_size() == 2:
+                out, out_h = partial.view(dtype), partial_h
+            else:
+                out = symm_mem.empty((m, hidden), dtype=dtype, device=device)
+                out_h = symm_mem.rendezvous(out, group=group)
+            for handle in (partial_h, out_h):
+                if self.collective == "nvls" and not int(getattr(handle, "multicast_ptr", 0)
+                                                         or 0):
+                    raise RuntimeError("symmetric memory has no multicast pointer on this "
+                                       "system (NVLS unavailable): use collective='peer'")
+            words = abi.lib().b200_signal_pad_bytes() // 4
+            pad = symm_mem.empty((words,), dtype=torch.int32, device=device)
+            pad.zero_()
+            pad_h = symm_mem.rendezvous(pad, group=group)
+            torch.cuda.synchronize(device)
+            pad_h.barrier(channel=0)  # every rank's flags are zero before anyone signals
+            torch.cuda.synchronize(device)
+            pads = (ctypes.c_void_p * world)(*[int(p) for p in pad_h.buffer_ptrs])
+            self._epoch = 0
+            self._nvls = (key, partial, partial_h, out, out_h, pads, pad, pad_h)
+        return self._nvls[1:6]
 
     def _forward_nvls(self, y, stream, mark):
-        """Down-projection into the symmetric partial, then the in-switch all-reduce in place."""
+        """Down-projection into the symmetric partial in row chunks; each chunk's all-reduce
+        (in the switch, or over plain peer memory for ``collective="pull"``; with its own
+        cross-rank barriers) runs on a second stream beside the next chunk's GEMM."""
+        import ctypes
+
         import torch.distributed as dist
+        torch = self.torch
         m, hidden = self._h.shape[0], self.wd.shape[1]
-        partial, handle = self._nvls_buffer(m, hidden, self._h.dtype, self._h.device)
+        partial, partial_h, out, out_h, pads = self._nvls_buffers(m, hidden, self._h.dtype,
+                                                                  self._h.device)
         world, rank = dist.get_world_size(self.group), dist.get_rank(self.group)
-        ops.gemm(self._h, self.wd, partial, stream=stream)
-        mark("down_projection")
-        handle.barrier(channel=0)     # every rank's partial is complete
-        mark("barrier_partials")
-        abi.check(abi.lib().b200_multimem_allreduce(
-            int(handle.multicast_ptr), abi.DTYPE_CODES[abi.dtype_name(partial.dtype)], 0,
-            m * hidden, rank, world, 0, stream))
-        mark("multimem_allreduce")
-        handle.barrier(channel=1)     # every rank's share is in my copy
-        mark("barrier_result")
-        if y is not None and y.data_ptr() != partial.data_ptr():
-            y.copy_(partial)
+        if self._comm_stream is None:
+            self._comm_stream = torch.cuda.Stream(device=self._h.device, priority=-1)
+        comm = self._comm_stream
+        main = torch.cuda.current_stream()
+        lib = abi.lib()
+        in_code = abi.DTYPE_CODES[abi.dtype_name(partial.dtype)]
+        out_code = abi.DTYPE_CODES[abi.dtype_name(out.dtype)]
+        pointer_array = ctypes.c_void_p * world
+        partial_ptrs = pointer_array(*[int(p) for p in partial_h.buffer_ptrs])
+        out_ptrs = pointer_array(*[int(p) for p in out_h.buffer_ptrs])
+        chunks = [c for c in shard.row_chunks(m, self.chunks)
+                  if ((c[1] - c[0]) * hidden) % (8 * world) == 0]
+        if sum(hi - lo for lo, hi in chunks) != m:
+            chunks = [(0, m)]
+        for lo, hi in chunks:
+            ops.gemm(self._h[lo:hi], self.wd, partial[lo:hi], stream=stream)
+            ready = torch.cuda.Event()
+            ready.record(main)
+            comm.wait_event(ready)
+            self._epoch += 1
+            if self.collective == "nvls":
+                abi.check(lib.b200_multimem_allreduce(
+                    int(partial_h.multicast_ptr), in_code, int(out_h.multicast_ptr), out_code,
+                    lo * hidden, (hi - lo) * hidden, rank, world, pads, self._epoch,
+                    self.comm_ctas, comm.cuda_stream))
+            else:
+                abi.check(lib.b200_peer_allreduce(
+                    partial_ptrs, in_code, out_ptrs, out_code, lo * hidden, (hi - lo) * hidden,
+                    rank, world, pads, self._epoch, self.comm_ctas, comm.cuda_stream))
+        mark("down_projection_chunks_issued")
+        done = torch.cuda.Event()
+        done.record(comm)
+        main.wait_event(done)
+        mark("all_reduce_tail")
+        if y is not None and y.data_ptr() != out.data_ptr():
+            y.copy_(out)
             mark("copy_out")
             return y
-        return partial
+        return out

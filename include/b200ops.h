@@ -305,27 +305,49 @@ int b200_gemm_scatter_rows(const b200_tensor *a, const b200_tensor *b,
                            int slot, int64_t rows_per_rank, void *stream);
 
 /* Sums the `world` slices of staging ([world, rows, cols], f16/bf16, fp32 accumulation,
- * one rounding) and stores the result into rows [dst_row0, dst_row0 + rows) of every
- * y_rank[k] (contiguous [*, cols]; peer memory for k != this rank).  Together with
- * b200_gemm_scatter_rows this is the all-reduce of the tensor-parallel MLP; the caller
+ * one rounding to out_dtype, f16/bf16) and stores the result into rows [dst_row0, dst_row0 +
+ * rows) of every y_rank[k] (contiguous [*, cols]; peer memory for k != this rank).  Together
+ * with b200_gemm_scatter_rows this is the all-reduce of the tensor-parallel MLP; the caller
  * separates the two with a cross-rank barrier. */
-int b200_reduce_slices_broadcast(const void *staging, uint32_t dtype, int world,
-                                 int64_t rows, int64_t cols, int64_t dst_row0,
+int b200_reduce_slices_broadcast(const void *staging, uint32_t dtype, uint32_t out_dtype,
+                                 int world, int64_t rows, int64_t cols, int64_t dst_row0,
                                  void *const *y_rank, void *stream);
 
-/* All-reduce (sum) of 16-bit partials through NVSwitch.  `multicast_base` is the multicast
- * address of a buffer that every rank allocated symmetrically and bound to one multicast
- * object (torch.distributed._symmetric_memory: handle.multicast_ptr); elements
- * [offset, offset + count) of it are reduced.  This rank loads the sum of all ranks' copies
- * of its share [offset + rank*count/world, offset + (rank+1)*count/world) with
- * multimem.ld_reduce (added in the switch in fp32, rounded once) and stores it to all ranks'
- * copies with multimem.st, in place.  offset and count/world must be multiples of 8
- * elements.  `ctas` > 0 limits the grid (for running beside another kernel), 0 = default.
- * The caller puts a cross-rank barrier before the call (all partials written) and after it
- * (all shares published).  The merge of per-worker partials in the reference is
- * a100c/plan/stages.py:278-316; it has no multi-device counterpart. */
-int b200_multimem_allreduce(void *multicast_base, uint32_t dtype, int64_t offset,
-                            int64_t count, int rank, int world, int ctas, void *stream);
+/* All-reduce (sum) of partial results through NVSwitch.  in_multicast / out_multicast are
+ * the multicast addresses of buffers that every rank allocated symmetrically and bound to a
+ * multicast object (torch.distributed._symmetric_memory: handle.multicast_ptr); elements
+ * [offset, offset + count) are reduced.  This rank loads the sum of all ranks' copies of its
+ * share [offset + rank*count/world, offset + (rank+1)*count/world) of the partial (f16, bf16
+ * or f32) with multimem.ld_reduce -- added in the switch in fp32 -- rounds it once to
+ * out_dtype (f16 / bf16) and stores it to all ranks' copies of the result with multimem.st.
+ * 16-bit partials may be reduced in place (out_multicast == in_multicast).  offset and
+ * count/world must be multiples of 8 elements.  `ctas` > 0 limits the grid (for running
+ * beside another kernel), 0 = default.
+ * signal_pads == NULL: the caller puts a cross-rank barrier before the call (all partials
+ * written) and after it (all shares published).  Otherwise signal_pads[k] is rank k's flag
+ * array of b200_signal_pad_bytes() bytes (symmetric memory, zeroed once, mapped into this
+ * process) and the kernel does both barriers itself: `epoch` must be the same on all ranks,
+ * never 0, and grow by one per call on those pads; calls that share pads must be ordered on
+ * one stream per rank, and every rank must launch the call (a rank that waits about two
+ * seconds in vain records B200_TIMEOUT in the device status word and returns).  The merge of
+ * per-worker partials in the reference is a100c/plan/stages.py:278-316 behind the stage
+ * barrier of a100c/runtime/pool.c:187-190; it has no multi-device counterpart. */
+int b200_multimem_allreduce(const void *in_multicast, uint32_t in_dtype, void *out_multicast,
+                            uint32_t out_dtype, int64_t offset, int64_t count, int rank,
+                            int world, void *const *signal_pads, uint32_t epoch, int ctas,
+                            void *stream);
+size_t b200_signal_pad_bytes(void);
+
+/* The same all-reduce over plain peer memory (no multicast object needed): partial_rank[k] /
+ * out_rank[k] are rank k's partial and result buffers (f16 / bf16; peer memory mapped into
+ * this process for k != rank, e.g. handle.buffer_ptrs of symmetric memory).  This rank loads
+ * its share of every rank's partial with 16-byte peer loads, adds them in fp32 in rank order
+ * (every rank computes the same bits), rounds once and stores the result into every rank's
+ * output.  In place (out_rank == partial_rank) is allowed.  offset / count / signal_pads /
+ * epoch / ctas as for b200_multimem_allreduce. */
+int b200_peer_allreduce(void *const *partial_rank, uint32_t in_dtype, void *const *out_rank,
+                        uint32_t out_dtype, int64_t offset, int64_t count, int rank, int world,
+                        void *const *signal_pads, uint32_t epoch, int ctas, void *stream);
 
 /* out = x * sigmoid(x) * y elementwise.  Replaces swiglu_fwd_kernel
  * (ops/suite/perf/swiglu_fwd.py:18-36).  [rows, cols], unit column stride. */

@@ -246,3 +246,39 @@ def test_decode_scratch_follows_the_stream(device):
         stream.synchronize()
         oracle.compare(device.download(out).astype(np.float64), ref, 2e-2, 2e-2, name="decode")
         stream.close()
+
+
+def test_allreduce_barrier_gives_up_when_a_peer_never_arrives(device):
+    """The in-switch all-reduce kernel carries its own cross-rank barriers.  Here its "peer" is
+    a flag array that nothing ever signals: the start barrier must run out after about two
+    seconds, record B200_TIMEOUT with its site, skip the data phase (the data pointers are
+    never touched) and return, and the context must stay usable."""
+    import ctypes
+    import time
+    from compiler_b200.runtime import abi
+    lib = abi.lib()
+    words = lib.b200_signal_pad_bytes() // 4
+    pads = [device.upload(np.zeros(words, np.int32)) for _ in range(2)]
+    data = device.alloc((1024,), "bfloat16")
+    pad_ptrs = (ctypes.c_void_p * 2)(pads[0].ptr, pads[1].ptr)
+    code = abi.DTYPE_CODES["bfloat16"]
+    start = time.perf_counter()
+    abi.check(lib.b200_multimem_allreduce(data.ptr, code, data.ptr, code, 0, 1024, 0, 2,
+                                          pad_ptrs, 1, 1, device.stream))
+    with pytest.raises(abi.B200Error) as caught:
+        device.check_status()
+    elapsed = time.perf_counter() - start
+    assert caught.value.status == abi.TIMEOUT and "site 40" in str(caught.value)
+    assert 1.0 < elapsed < 10.0
+    device.check_status()  # cleared by the read
+    # rank 0 signalled both arrays (its own flag and the peer's) before it waited
+    assert device.download(pads[0])[0] == 1 and device.download(pads[1])[0] == 1
+    # argument checks never reach the device
+    assert lib.b200_multimem_allreduce(data.ptr, code, data.ptr, code, 0, 1024, 0, 2, pad_ptrs,
+                                       0, 1, device.stream) == abi.REJECTED   # epoch 0
+    assert lib.b200_multimem_allreduce(data.ptr, code, data.ptr, code, 0, 1000, 0, 2, None, 0, 0,
+                                       device.stream) == abi.REJECTED         # count % 16
+    x = np.random.default_rng(13).standard_normal((64, 1000)).astype(np.float32)
+    dx, dy = device.upload(x), device.alloc(x.shape, "float32")
+    ops.softmax(dx, dy)
+    oracle.compare(device.download(dy).astype(np.float64), oracle.softmax_ref(x), 2e-3, 2e-3)

@@ -81,9 +81,10 @@ for c0 in range(0, ffn, 2048):                       # column blocks bound the f
 shards = [bf16(t).contiguous() for t in (wgb[:, lo:hi], wub[:, lo:hi], wdb[lo:hi])]
 dxb = bf16(xb)
 failures = []
-for collective in ("nccl", "peer", "nvls"):
+for collective, options in (("nccl", {}), ("peer", {}), ("nvls", {}), ("pull", {}),
+                            ("nvls", {"partial_dtype": torch.float32, "chunks": 2})):
     try:
-        big = tp_mlp.TensorParallelMLP(*shards, collective=collective)
+        big = tp_mlp.TensorParallelMLP(*shards, collective=collective, **options)
         for _ in range(3):
             yb = big.forward(dxb, None)
     except RuntimeError as exc:
@@ -99,7 +100,7 @@ for collective in ("nccl", "peer", "nvls"):
         oracle.compare(yb[sel].float().cpu().numpy().astype(np.float64), expected, 2e-2, 2e-2,
                        name=f"tp mlp at the benchmark shape ({collective})")
     except Exception as exc:
-        failures.append(f"{collective}: {exc}")
+        failures.append(f"{collective} {options}: {exc}")
     dist.barrier()
     del big
 

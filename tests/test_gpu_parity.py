@@ -754,12 +754,14 @@ def test_repeat_launches_are_bitwise_identical(device):
 
 
 # ------------------------------------------------------------------ fused reduce-scatter path
+@pytest.mark.parametrize("staged", ["bfloat16", "float16"])
 @pytest.mark.parametrize("world", [1, 2, 4])
-def test_scatter_gemm_and_reduce_emulated_ranks(device, world):
+def test_scatter_gemm_and_reduce_emulated_ranks(device, world, staged):
     """The tensor-parallel all-reduce pieces on ONE GPU: every "rank" is a set of local
     buffers.  Rank r multiplies its K-shard and its GEMM epilogue scatters row blocks to the
-    owners' staging slots; each owner then sums its slots and broadcasts the rows to every
-    rank's output.  All outputs must equal the unsharded product."""
+    owners' staging slots (in the operands' type, or as float16: three more mantissa bits for
+    the partials at the same traffic); each owner then sums its slots and broadcasts the rows
+    to every rank's output.  All outputs must equal the unsharded product."""
     import ctypes
     lib = abi.lib()
     rows, n, k = 128, 264, 96 * world
@@ -767,7 +769,7 @@ def test_scatter_gemm_and_reduce_emulated_ranks(device, world):
     rng = np.random.default_rng(21)
     a = _host(rng.standard_normal((m, k)) / np.sqrt(k), "bfloat16")
     b = _host(rng.standard_normal((k, n)), "bfloat16")
-    staging = [_poisoned(device, (world, rows, n), "bfloat16") for _ in range(world)]
+    staging = [_poisoned(device, (world, rows, n), staged) for _ in range(world)]
     outputs = [_poisoned(device, (m, n), "bfloat16") for _ in range(world)]
     ptrs = ctypes.c_void_p * world
     staging_ptrs = ptrs(*[s.ptr for s in staging])
@@ -778,13 +780,13 @@ def test_scatter_gemm_and_reduce_emulated_ranks(device, world):
         db = _up(device, np.ascontiguousarray(b[r * ks:(r + 1) * ks]), "bfloat16")
         ta = abi.make_tensor(da.ptr, (m, ks), "bfloat16")
         tb = abi.make_tensor(db.ptr, (ks, n), "bfloat16")
-        tc = abi.make_tensor(outputs[r].ptr, (m, n), "bfloat16")
+        tc = abi.make_tensor(outputs[r].ptr, (m, n), staged)
         abi.check(lib.b200_gemm_scatter_rows(ctypes.byref(ta), ctypes.byref(tb), ctypes.byref(tc),
                                              staging_ptrs, world, r, rows, device.stream))
     for owner in range(world):
-        abi.check(lib.b200_reduce_slices_broadcast(staging[owner].ptr, abi.DTYPE_CODES["bfloat16"],
-                                                   world, rows, n, owner * rows, output_ptrs,
-                                                   device.stream))
+        abi.check(lib.b200_reduce_slices_broadcast(staging[owner].ptr, abi.DTYPE_CODES[staged],
+                                                   abi.DTYPE_CODES["bfloat16"], world, rows, n,
+                                                   owner * rows, output_ptrs, device.stream))
     device.check_status()
     ref = oracle.matmul_ref(a, b)
     for r in range(world):
@@ -805,5 +807,6 @@ def test_scatter_gemm_rejections(device):
                                       0, 100, device.stream) == abi.REJECTED
     assert lib.b200_gemm_scatter_rows(ctypes.byref(t), ctypes.byref(tb), ctypes.byref(tc), ptrs, 9,
                                       0, 128, device.stream) == abi.REJECTED
-    assert lib.b200_reduce_slices_broadcast(buf.ptr, abi.DTYPE_CODES["float32"], 2, 128, 64, 0,
+    assert lib.b200_reduce_slices_broadcast(buf.ptr, abi.DTYPE_CODES["float32"],
+                                            abi.DTYPE_CODES["bfloat16"], 2, 128, 64, 0,
                                             ptrs, device.stream) == abi.REJECTED
