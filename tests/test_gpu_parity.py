@@ -118,6 +118,29 @@ def test_softmax_sweep(device, shape, dtype, masked):
         assert (y[ref == 0] == 0).all()
 
 
+# masked rows in bulk: many rows of 32 .. 512 vectors, odd row counts, row offsets that put the
+# wrap-around of the mask inside the launch
+MASKED_BULK_CASES = [((64, 256), 0), ((65, 4000), 3999), ((777, 1000), 123), ((3000, 4096), 5),
+                     ((6001, 512), 509), ((14000, 264), 7)]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "float16", "bfloat16"])
+@pytest.mark.parametrize("case", MASKED_BULK_CASES)
+def test_masked_softmax_many_rows(device, case, dtype):
+    shape, offset = case
+    if dtype == "float32" and shape[1] > 2048:
+        shape = (shape[0], shape[1] // 2)   # 512 four-element vectors at most
+    rng = np.random.default_rng(_seed(shape, dtype, True))
+    x = _host(rng.standard_normal(shape) * 2, dtype)
+    dx, dy = _up(device, x, dtype), _poisoned(device, shape, dtype)
+    ops.softmax(dx, dy, causal_mod=True, row_offset=offset)
+    y = device.download(dy)
+    ref = oracle.masked_softmax_ref(x, offset)
+    rtol, atol = (2e-3, 1e-6) if dtype == "float32" else TOL[dtype]
+    oracle.compare(y.astype(np.float64), ref, rtol, atol)
+    assert (y[ref == 0] == 0).all() and np.isfinite(y).all()
+
+
 GEMM_SHAPES = [(128, 256, 64), (256, 512, 256), (1, 8, 8), (129, 264, 72), (257, 520, 200),
                (100, 40, 24), (384, 1024, 1000), (130, 96, 8)]
 
