@@ -863,7 +863,10 @@ def bench_siblings(torch, ops, peaks):
         sets=3)
     report("gemm_swiglu_dual_bf16_8192x8192x4096", lambda i: ops.gemm(
         xs[i], w, outs[i], b2=w2, act=abi.ACT_SWIGLU, stream=S), flop=4 * m * n * k, sets=3)
-    del xs, outs, w, w2, scratch_w
+    wt = rnd((n, k), torch.bfloat16, 0.02)
+    report("linear_weight_rows_of_k_bf16_8192x8192x4096", lambda i: ops.linear(
+        xs[i], wt, outs[i], stream=S), flop=2 * m * n * k, sets=3)
+    del xs, outs, w, w2, wt, scratch_w
     torch.cuda.empty_cache()
     big = 65536
     x2 = [rnd((big, 4096), torch.bfloat16) for _ in range(3)]

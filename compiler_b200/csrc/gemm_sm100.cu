@@ -76,14 +76,13 @@ constexpr int BM = 128;
 constexpr int BN = 256;  // accumulator columns per tile (two 128-column halves when DUAL)
 constexpr int BK = 64;   // 64 16-bit elements = one 128-byte swizzle span
 constexpr int UMMA_K = 16;
-constexpr int STAGES = 4;
+constexpr int STAGES = 4;                     // stages of a full-width (256-column) ring
+constexpr int MAX_STAGES = 8;                 // a narrower B operand leaves room for more
 constexpr int A_STAGE_BYTES = BM * BK * 2;    // 16 KiB
 constexpr int B_BOX_BYTES = BK * 64 * 2;      // one 64(K) x 64(N) box: 8 KiB
 constexpr int B_STAGE_BYTES = 4 * B_BOX_BYTES;  // 32 KiB
-constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
 constexpr int TMEM_COLS = 512;
 constexpr int THREADS = 192;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
 
 constexpr int kActLogSoftmax = 100;  // internal epilogue code: row log-softmax (N <= 256)
 constexpr int kActGroupNormMin = 101;  // internal: group norm over column groups, row minimum
@@ -122,6 +121,13 @@ struct Params {
   int scatter_rows;
   int scatter_slot;
   int group_m;  // m-blocks per raster group
+  // One-CTA kernel: the ring holds `stages` stages of A_STAGE_BYTES + b_stage_bytes.  A single
+  // column block narrower than the tile loads only the B columns that exist (b_boxes boxes of
+  // 64 columns for B as [K,N]; one box of b_stage_bytes / 128 rows for B as [N,K]), so a
+  // product that only streams A keeps eight stages of A in flight instead of four.
+  int stages;
+  int b_stage_bytes;
+  int b_boxes;
 };
 
 __device__ __forceinline__ float gelu_tanh_fast(float z) {
@@ -419,17 +425,20 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t *smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+  const int stages = p.stages;
+  const uint32_t b_stage_bytes = (uint32_t)p.b_stage_bytes;
+  const uint32_t ring_bytes = (uint32_t)stages * (A_STAGE_BYTES + b_stage_bytes);
   const uint32_t a_smem = smem_base;
-  const uint32_t b_smem = smem_base + STAGES * A_STAGE_BYTES;
-  uint64_t *bars = reinterpret_cast<uint64_t *>(smem_gen + STAGES * STAGE_BYTES);
-  // barrier slots: full[STAGES], empty[STAGES], acc_full[2], acc_empty[2], drain
-  const uint32_t bar0 = smem_base + STAGES * STAGE_BYTES;
+  const uint32_t b_smem = smem_base + (uint32_t)stages * A_STAGE_BYTES;
+  uint64_t *bars = reinterpret_cast<uint64_t *>(smem_gen + ring_bytes);
+  // barrier slots: full[MAX_STAGES], empty[MAX_STAGES], acc_full[2], acc_empty[2], drain
+  const uint32_t bar0 = smem_base + ring_bytes;
   auto full_bar = [&](int s) { return bar0 + 8u * s; };
-  auto empty_bar = [&](int s) { return bar0 + 8u * (STAGES + s); };
-  auto acc_full_bar = [&](int a) { return bar0 + 8u * (2 * STAGES + a); };
-  auto acc_empty_bar = [&](int a) { return bar0 + 8u * (2 * STAGES + 2 + a); };
-  const uint32_t drain_bar = bar0 + 8u * (2 * STAGES + 4);
-  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * STAGES + 5);
+  auto empty_bar = [&](int s) { return bar0 + 8u * (MAX_STAGES + s); };
+  auto acc_full_bar = [&](int a) { return bar0 + 8u * (2 * MAX_STAGES + a); };
+  auto acc_empty_bar = [&](int a) { return bar0 + 8u * (2 * MAX_STAGES + 2 + a); };
+  const uint32_t drain_bar = bar0 + 8u * (2 * MAX_STAGES + 4);
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * MAX_STAGES + 5);
   volatile uint32_t *abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5;
@@ -444,7 +453,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
   const int num_kb = (p.K + BK - 1) / BK;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES; ++s) {
+    for (int s = 0; s < stages; ++s) {
       mbar_init(full_bar(s), 1);
       mbar_init(empty_bar(s), 1);
     }
@@ -479,9 +488,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
         tile_coords(tile, m_blocks, n_blocks, p.group_m, mb, nb);
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1u, ctx, 1)) { ok = false; break; }
-          mbar_arrive_expect_tx(full_bar(stage), STAGE_BYTES);
+          mbar_arrive_expect_tx(full_bar(stage), A_STAGE_BYTES + b_stage_bytes);
           tma_load_2d(a_smem + stage * A_STAGE_BYTES, &tm_a, full_bar(stage), kb * BK, mb * BM);
-          const uint32_t bdst = b_smem + stage * B_STAGE_BYTES;
+          const uint32_t bdst = b_smem + (uint32_t)stage * b_stage_bytes;
           if (DUAL) {
             const int n0 = nb * TILE_N;
             tma_load_2d(bdst, &tm_b, full_bar(stage), n0, kb * BK);
@@ -489,23 +498,22 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
             tma_load_2d(bdst + 2 * B_BOX_BYTES, &tm_b2, full_bar(stage), n0, kb * BK);
             tma_load_2d(bdst + 3 * B_BOX_BYTES, &tm_b2, full_bar(stage), n0 + 64, kb * BK);
           } else if (p.b_kmajor) {
-            // B rows are rows of K: one box of 64 (K) x 256 (N), laid out like the A tile
+            // B rows are rows of K: one box of 64 (K) x up to 256 (N), laid out like the A tile
             tma_load_2d(bdst, &tm_b, full_bar(stage), kb * BK, nb * TILE_N);
           } else {
             const int n0 = nb * TILE_N;
-#pragma unroll
-            for (int j = 0; j < 4; ++j)
+            for (int j = 0; j < p.b_boxes; ++j)
               tma_load_2d(bdst + j * B_BOX_BYTES, &tm_b, full_bar(stage), n0 + 64 * j, kb * BK);
           }
           issued_mask |= 1u << stage;
           issued_parity = (issued_parity & ~(1u << stage)) | (phase << stage);
-          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+          if (++stage == stages) { stage = 0; phase ^= 1u; }
         }
       }
       if (!ok) {
         // copies already issued still target this CTA's shared memory: wait for
         // them (bounded) before the CTA is allowed to exit
-        for (int s = 0; s < STAGES; ++s)
+        for (int s = 0; s < stages; ++s)
           if (issued_mask & (1u << s)) mbar_wait_drain(full_bar(s), (issued_parity >> s) & 1u);
       }
     }
@@ -536,7 +544,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
         if (!wait_all(full_bar(stage), phase, 3)) { ok = false; break; }
         tc_fence_after_sync();
         const uint32_t a_lo = a_lo0 + (uint32_t)stage * (A_STAGE_BYTES >> 4);
-        const uint32_t b_lo = b_lo0 + (uint32_t)stage * (B_STAGE_BYTES >> 4);
+        const uint32_t b_lo = b_lo0 + (uint32_t)stage * (b_stage_bytes >> 4);
         if (leader) {
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k) {
@@ -548,7 +556,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
           }
           tc_commit(empty_bar(stage));  // stage reusable once these MMAs retire
         }
-        if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        if (++stage == stages) { stage = 0; phase ^= 1u; }
       }
       if (!ok) break;
       if (leader) tc_commit(acc_full_bar(acc));  // accumulator complete
@@ -700,8 +708,14 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
           const uint32_t full0 = map_to_cta(full_bar(stage), 0);
           tma_load_2d_pair(a_smem + stage * A_STAGE_BYTES, &tm_a, full0, kb * BK, row0);
           const uint32_t bdst = b_smem + stage * PAIR_B_STAGE_BYTES;
-          tma_load_2d_pair(bdst, bmap, full0, col0, kb * BK);
-          tma_load_2d_pair(bdst + B_BOX_BYTES, bmap, full0, col0 + 64, kb * BK);
+          if (p.b_kmajor) {
+            // B rows are rows of K: this CTA's 128 of the tile's 256 columns as one box of
+            // 64 (K) x 128 (N), laid out like the A tile
+            tma_load_2d_pair(bdst, bmap, full0, kb * BK, col0);
+          } else {
+            tma_load_2d_pair(bdst, bmap, full0, col0, kb * BK);
+            tma_load_2d_pair(bdst + B_BOX_BYTES, bmap, full0, col0 + 64, kb * BK);
+          }
           issued_mask |= 1u << stage;
           issued_parity = (issued_parity & ~(1u << stage)) | (phase << stage);
           if (++stage == PAIR_STAGES) { stage = 0; phase ^= 1u; }
@@ -725,9 +739,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
         return __all_sync(0xffffffffu, mbar_wait(bar, parity, ctx, site)) != 0;
       };
       const uint32_t a_lo0 = desc_lo_sw128(a_smem, 16);
-      const uint32_t b_lo0 = desc_lo_sw128(b_smem, B_BOX_BYTES);
+      const uint32_t b_lo0 = desc_lo_sw128(b_smem, p.b_lbo);
       constexpr uint32_t hi = desc_hi_sw128(1024);
-      constexpr uint32_t b_kstep = (UMMA_K * 128) >> 4;
+      const uint32_t b_kstep = p.b_kstep;
       const uint32_t peer_bar0 = map_to_cta(bar0, 1);
       for (int tile = first_tile; ok && tile < num_tiles; tile += tile_step) {
         if (!wait_all(acc_empty_bar(acc), acc_phase ^ 1u, 2)) { ok = false; break; }
@@ -817,8 +831,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
 // rejects (row pitch not a multiple of 16 bytes, fp32 operands).
 template <typename InT, typename OutT>
 __global__ void __launch_bounds__(256)
-gemm_simt_kernel(const InT *__restrict__ a, int64_t lda, const InT *__restrict__ b, int64_t ldb,
-                 const InT *__restrict__ b2, OutT *__restrict__ c, int64_t ldc, int M, int N,
+gemm_simt_kernel(const InT *__restrict__ a, int64_t lda, const InT *__restrict__ b, int64_t ldb_k,
+                 int64_t ldb_n, const InT *__restrict__ b2, OutT *__restrict__ c, int64_t ldc, int M, int N,
                  int K, const void *bias, int bias_kind, int act, const float *row_scale,
                  GroupNormMin gn) {
   __shared__ float sa[32][33];
@@ -835,8 +849,9 @@ gemm_simt_kernel(const InT *__restrict__ a, int64_t lda, const InT *__restrict__
       sa[r][tx] = (am < M && ak < K) ? io<InT>::load(a[(int64_t)am * lda + ak]) : 0.f;
       const int bk = k0 + r, bn = n0 + tx;
       const bool bok = bk < K && bn < N;
-      sb[r][tx] = bok ? io<InT>::load(b[(int64_t)bk * ldb + bn]) : 0.f;
-      if (b2 != nullptr) sb2[r][tx] = bok ? io<InT>::load(b2[(int64_t)bk * ldb + bn]) : 0.f;
+      sb[r][tx] = bok ? io<InT>::load(b[(int64_t)bk * ldb_k + (int64_t)bn * ldb_n]) : 0.f;
+      if (b2 != nullptr)
+        sb2[r][tx] = bok ? io<InT>::load(b2[(int64_t)bk * ldb_k + (int64_t)bn * ldb_n]) : 0.f;
     }
     __syncthreads();
 #pragma unroll 8
@@ -889,8 +904,9 @@ gemm_simt_kernel(const InT *__restrict__ a, int64_t lda, const InT *__restrict__
 template <typename InT, typename OutT>
 static int launch_simt(const b200_tensor *a, const b200_tensor *b, const b200_tensor *b2,
                        const b200_tensor *bias, b200_tensor *c, int act, cudaStream_t stream,
-                       const float *row_scale = nullptr, const GroupNormMin *gn = nullptr) {
-  const int M = (int)a->shape[0], K = (int)a->shape[1], N = (int)b->shape[1];
+                       const float *row_scale = nullptr, const GroupNormMin *gn = nullptr,
+                       bool b_rows_are_n = false) {
+  const int M = (int)a->shape[0], K = (int)a->shape[1], N = (int)b->shape[b_rows_are_n ? 0 : 1];
   GroupNormMin gn_args = {nullptr, nullptr, 0, 0, 0.f, nullptr};
   if (gn != nullptr) {
     B200_REQUIRE(gn->group == 32 && N % 32 == 0,
@@ -900,7 +916,8 @@ static int launch_simt(const b200_tensor *a, const b200_tensor *b, const b200_te
   dim3 grid((N + 31) / 32, (M + 31) / 32);
   B200_REQUIRE(grid.y <= 65535, "M too large for the CUDA-core path");
   gemm_simt_kernel<InT, OutT><<<grid, 256, 0, stream>>>(
-      (const InT *)a->data, a->stride[0], (const InT *)b->data, b->stride[0],
+      (const InT *)a->data, a->stride[0], (const InT *)b->data,
+      b_rows_are_n ? (int64_t)1 : b->stride[0], b_rows_are_n ? b->stride[0] : (int64_t)1,
       b2 ? (const InT *)b2->data : nullptr, (OutT *)c->data, c->stride[0], M, N, K,
       bias ? bias->data : nullptr, bias ? (int)bias->dtype : 0, act, row_scale, gn_args);
   B200_CUDA_OK(cudaGetLastError());
@@ -916,13 +933,14 @@ static int launch_tc(const CUtensorMap &ta, const CUtensorMap &tb, const CUtenso
   auto kernel = gemm_tcgen05_kernel<OutT, DUAL>;
   if (dev < 64 && !configured[dev]) {
     B200_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                      SMEM_BYTES));
+                                      227 * 1024));
     configured[dev] = true;
   }
   constexpr int TILE_N = DUAL ? BN / 2 : BN;
   const int tiles = ((p.M + BM - 1) / BM) * ((p.N + TILE_N - 1) / TILE_N);
   const int grid = tiles < sm_count() ? tiles : sm_count();
-  kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(ta, tb, tb2, p);
+  const int smem = p.stages * (A_STAGE_BYTES + p.b_stage_bytes) + 1024 + 256;
+  kernel<<<grid, THREADS, smem, stream>>>(ta, tb, tb2, p);
   B200_CUDA_OK(cudaGetLastError());
   return B200_OK;
 }
@@ -1104,17 +1122,31 @@ static int gemm_impl(const b200_tensor *a, const b200_tensor *b, const b200_tens
     return B200_OK;
   }
   if (!tensor_core) {
-    B200_REQUIRE(!b_rows_are_n, "B as [N, K] is taken by the tensor-core path only");
-
-    if (a->dtype == B200_DTYPE_FLOAT32) return launch_simt<float, float>(a, b, b2, bias, c, act, s, row_scale, gn);
+    const bool t = b_rows_are_n;
+    if (a->dtype == B200_DTYPE_FLOAT32) return launch_simt<float, float>(a, b, b2, bias, c, act, s, row_scale, gn, t);
     if (a->dtype == B200_DTYPE_FLOAT16) {
       return c->dtype == B200_DTYPE_FLOAT32
-                 ? launch_simt<__half, float>(a, b, b2, bias, c, act, s, row_scale, gn)
-                 : launch_simt<__half, __half>(a, b, b2, bias, c, act, s, row_scale, gn);
+                 ? launch_simt<__half, float>(a, b, b2, bias, c, act, s, row_scale, gn, t)
+                 : launch_simt<__half, __half>(a, b, b2, bias, c, act, s, row_scale, gn, t);
     }
     return c->dtype == B200_DTYPE_FLOAT32
-               ? launch_simt<__nv_bfloat16, float>(a, b, b2, bias, c, act, s, row_scale, gn)
-               : launch_simt<__nv_bfloat16, __nv_bfloat16>(a, b, b2, bias, c, act, s, row_scale, gn);
+               ? launch_simt<__nv_bfloat16, float>(a, b, b2, bias, c, act, s, row_scale, gn, t)
+               : launch_simt<__nv_bfloat16, __nv_bfloat16>(a, b, b2, bias, c, act, s, row_scale, gn, t);
+  }
+
+  // CTA pairs (256-row tiles) when the pair tiles fill at least one wave of SM pairs (a pair
+  // always multiplies 256 columns: not for outputs of at most half a tile, nor for the row
+  // log-softmax, whose epilogue needs the whole row in one CTA); B200OPS_GEMM_PAIR=0 / 1
+  // forces the choice.
+  const bool dual = act == B200_ACT_SWIGLU;
+  bool use_pair;
+  {
+    static const int pair_env =
+        getenv("B200OPS_GEMM_PAIR") ? atoi(getenv("B200OPS_GEMM_PAIR")) : -1;
+    const int tile_n = dual ? BN / 2 : BN;
+    const int64_t pair_tiles = ((M + 2 * BM - 1) / (2 * BM)) * ((N + tile_n - 1) / tile_n);
+    use_pair = act != kActLogSoftmax &&
+               (pair_env >= 0 ? pair_env != 0 : pair_tiles >= sm_count() / 2 && N > tile_n / 2);
   }
 
   CUtensorMap ta, tb, tb2;
@@ -1124,10 +1156,13 @@ static int gemm_impl(const b200_tensor *a, const b200_tensor *b, const b200_tens
     const uint32_t box[2] = {BK, BM};
     if ((st = encode_tensor_map(&ta, a->dtype, a->data, 2, dims, strides, box))) return st;
   }
+  // one column block narrower than the tile (one-CTA kernel): load only the columns that exist
+  const bool narrow = !dual && !use_pair && N < BN && act != kActGroupNormMin;
+  const int n_mma = narrow ? (int)((N + 15) / 16 * 16) : BN;
   if (b_rows_are_n) {
     const uint64_t dims[2] = {(uint64_t)K, (uint64_t)N};
     const uint64_t strides[2] = {es, (uint64_t)b->stride[0] * es};
-    const uint32_t box[2] = {BK, BN};
+    const uint32_t box[2] = {BK, (uint32_t)(use_pair ? BN / 2 : n_mma)};
     if ((st = encode_tensor_map(&tb, b->dtype, b->data, 2, dims, strides, box))) return st;
     tb2 = tb;
   } else {
@@ -1161,6 +1196,10 @@ static int gemm_impl(const b200_tensor *a, const b200_tensor *b, const b200_tens
   p.b_kstep = b_rows_are_n ? (UMMA_K * 2) >> 4 : (UMMA_K * 128) >> 4;
   p.scatter_rows = 0;
   p.scatter_slot = 0;
+  p.b_boxes = narrow ? (int)((N + 63) / 64) : 4;
+  p.b_stage_bytes = b_rows_are_n ? n_mma * BK * 2 : p.b_boxes * B_BOX_BYTES;
+  p.stages = (227 * 1024 - 1024 - 256) / (A_STAGE_BYTES + p.b_stage_bytes);
+  if (p.stages > MAX_STAGES) p.stages = MAX_STAGES;
   {
     // Raster groups: as many m-blocks as keep a group's rows of A (group_m x 128 x K)
     // within about 40 MiB, the part of the L2 that was seen to hold a panel while B streams
@@ -1183,38 +1222,25 @@ static int gemm_impl(const b200_tensor *a, const b200_tensor *b, const b200_tens
     for (int r = 0; r < scatter->world; ++r) p.c_rank[r] = scatter->c_rank[r];
   }
 
-  const bool dual = act == B200_ACT_SWIGLU;
-  if (!dual && N < BN && act != kActGroupNormMin) {
-    // one column block narrower than the tile: the MMAs take only the columns that exist
-    // (rounded up to the instruction's granule of 16) instead of 256 -- a [65536, 4096] x
-    // [4096, 64] product is then bound by reading x, not by the tensor pipe
-    const int n_mma = (int)((N + 15) / 16 * 16);
+  if (narrow) {
+    // the MMAs take only the columns that exist (rounded up to the instruction's granule of
+    // 16) instead of 256 -- a [65536, 4096] x [4096, 64] product is then bound by reading x,
+    // not by the tensor pipe
     p.idesc = sm100::make_idesc_f16(BM, n_mma, a->dtype == B200_DTYPE_BFLOAT16 ? 1 : 0, 0,
                                     b_rows_are_n ? 0 : 1);
   }
-  {
-    // CTA pairs (256-row tiles) for B given as [K, N], when the pair tiles fill at least one
-    // wave of SM pairs; B200OPS_GEMM_PAIR=0 / 1 forces the choice.
-    static const int pair_env =
-        getenv("B200OPS_GEMM_PAIR") ? atoi(getenv("B200OPS_GEMM_PAIR")) : -1;
-    const int tile_n = dual ? BN / 2 : BN;
-    const int64_t pair_tiles = ((M + 2 * BM - 1) / (2 * BM)) * ((N + tile_n - 1) / tile_n);
-    // (a pair always multiplies 256 columns: not for outputs of at most half a tile)
-    const bool use_pair = !b_rows_are_n && act != kActLogSoftmax &&
-                          (pair_env >= 0 ? pair_env != 0
-                                         : pair_tiles >= sm_count() / 2 && N > tile_n / 2);
-    if (use_pair) {
-      Params q = p;
-      q.idesc = sm100::make_idesc_f16(2 * BM, BN, a->dtype == B200_DTYPE_BFLOAT16 ? 1 : 0, 0, 1);
-      if (c->dtype == B200_DTYPE_FLOAT32)
-        return dual ? launch_pair<float, true>(ta, tb, tb2, q, s)
-                    : launch_pair<float, false>(ta, tb, tb2, q, s);
-      if (c->dtype == B200_DTYPE_FLOAT16)
-        return dual ? launch_pair<__half, true>(ta, tb, tb2, q, s)
-                    : launch_pair<__half, false>(ta, tb, tb2, q, s);
-      return dual ? launch_pair<__nv_bfloat16, true>(ta, tb, tb2, q, s)
-                  : launch_pair<__nv_bfloat16, false>(ta, tb, tb2, q, s);
-    }
+  if (use_pair) {
+    Params q = p;
+    q.idesc = sm100::make_idesc_f16(2 * BM, BN, a->dtype == B200_DTYPE_BFLOAT16 ? 1 : 0, 0,
+                                    b_rows_are_n ? 0 : 1);
+    if (c->dtype == B200_DTYPE_FLOAT32)
+      return dual ? launch_pair<float, true>(ta, tb, tb2, q, s)
+                  : launch_pair<float, false>(ta, tb, tb2, q, s);
+    if (c->dtype == B200_DTYPE_FLOAT16)
+      return dual ? launch_pair<__half, true>(ta, tb, tb2, q, s)
+                  : launch_pair<__half, false>(ta, tb, tb2, q, s);
+    return dual ? launch_pair<__nv_bfloat16, true>(ta, tb, tb2, q, s)
+                : launch_pair<__nv_bfloat16, false>(ta, tb, tb2, q, s);
   }
   if (c->dtype == B200_DTYPE_FLOAT32)
     return dual ? launch_tc<float, true>(ta, tb, tb2, p, s) : launch_tc<float, false>(ta, tb, tb2, p, s);
@@ -1228,6 +1254,14 @@ extern "C" int b200_gemm_bias_act(const b200_tensor *a, const b200_tensor *b,
                                   const b200_tensor *b2, const b200_tensor *bias,
                                   b200_tensor *c, int act, void *stream) {
   return gemm_impl(a, b, b2, bias, c, act, stream, nullptr);
+}
+
+extern "C" int b200_linear_bias_act(const b200_tensor *x, const b200_tensor *w,
+                                    const b200_tensor *bias, b200_tensor *y, int act,
+                                    void *stream) {
+  if (act == B200_ACT_SWIGLU)
+    return b200::fail(B200_USAGE, "B200_ACT_SWIGLU takes two [K,N] operands: b200_gemm_bias_act");
+  return gemm_impl(x, w, nullptr, bias, y, act, stream, nullptr, true);
 }
 
 extern "C" int b200_gemm_scatter_rows(const b200_tensor *a, const b200_tensor *b,

@@ -118,11 +118,19 @@ static int dispatch(const b200_tensor *x, const b200_tensor *w, b200_tensor *y,
     case 256: launch_rows<T, 256, VPT>(x, w, y, rinv, eps, gamma_offset, stream); break;
     case 512: launch_rows<T, 512, VPT>(x, w, y, rinv, eps, gamma_offset, stream); break;
     case 1024: launch_rows<T, 1024, VPT>(x, w, y, rinv, eps, gamma_offset, stream); break;
-    default:
+    default: {
+      // wider than one CTA holds in registers: a cluster per row when the layout allows it
+      bool taken = false;
+      if (aligned) {
+        const int st = rmsnorm_cluster_rows<T>(x, w, y, rinv, eps, gamma_offset, stream, &taken);
+        if (st != B200_OK) return st;
+      }
+      if (taken) break;
       rmsnorm_loop_kernel<T><<<(unsigned)rows, kRowThreads, 0, stream>>>(
           (const T *)x->data, x->stride[0], (const T *)w->data, w->stride[0],
           (T *)y->data, y->stride[0], rinv ? (T *)rinv->data : nullptr,
           rinv ? rinv->stride[0] : 0, (int)cols, eps, gamma_offset);
+    }
   }
   B200_CUDA_OK(cudaGetLastError());
   return B200_OK;

@@ -61,6 +61,16 @@ __device__ __forceinline__ float group_reduce(float v, float *scratch, int buf) 
   return v;
 }
 
+// Rows wider than one CTA holds (rowwise_cluster.cu): a cluster of 2, 4 or 8 CTAs per row,
+// partial results merged through distributed shared memory.  *taken = false: nothing launched.
+template <typename T>
+int rmsnorm_cluster_rows(const b200_tensor *x, const b200_tensor *w, b200_tensor *y,
+                         b200_tensor *rinv, float eps, float gamma_offset, cudaStream_t stream,
+                         bool *taken);
+template <typename T>
+int softmax_cluster_rows(const b200_tensor *x, b200_tensor *y, int mask_kind, int64_t row_offset,
+                         cudaStream_t stream, bool *taken);
+
 // Picks the group size: the smallest power of two G in [8, 1024] with
 // G * vpt >= nvec.  Returns 0 when the row does not fit (caller falls back to
 // the looping kernel).

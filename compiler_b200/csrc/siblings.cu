@@ -71,6 +71,81 @@ template <typename T> __device__ __forceinline__ float gelu_tanh_t(float z) {
 
 constexpr int kEwSwiglu = 100;  // internal: x * sigmoid(x) * b (b200_swiglu_fwd on contiguous rows)
 
+// Two fp32 lanes per instruction (fma / mul .f32x2): the erf-based GELUs on 16-bit data are
+// bound by instruction issue, not by memory -- a 16-bit element is half the bytes for the same
+// arithmetic -- and the packed forms halve the multiply-add count at full fp32 precision.
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
+  unsigned long long d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;"
+      : "=l"(d)
+      : "l"(*reinterpret_cast<unsigned long long *>(&a)),
+        "l"(*reinterpret_cast<unsigned long long *>(&b)),
+        "l"(*reinterpret_cast<unsigned long long *>(&c)));
+  return *reinterpret_cast<float2 *>(&d);
+}
+__device__ __forceinline__ float2 mul2(float2 a, float2 b) {
+  unsigned long long d;
+  asm("mul.rn.f32x2 %0, %1, %2;"
+      : "=l"(d)
+      : "l"(*reinterpret_cast<unsigned long long *>(&a)),
+        "l"(*reinterpret_cast<unsigned long long *>(&b)));
+  return *reinterpret_cast<float2 *>(&d);
+}
+__device__ __forceinline__ float2 splat(float v) { return make_float2(v, v); }
+
+// gelu_erf of two values with the short erf above (Abramowitz-Stegun 7.1.26).  With
+// h = z / 2 and E = erf(|z| / sqrt 2) = 1 - poly(t) t exp(-x^2):  gelu(z) = h + |h| E.
+__device__ __forceinline__ float2 gelu_erf_short2(float2 z) {
+  const float2 h = mul2(z, splat(0.5f));
+  const float2 ah = make_float2(fabsf(h.x), fabsf(h.y));
+  const float2 ax = mul2(ah, splat(1.4142135623730951f));  // |z| / sqrt 2
+  const float2 d = fma2(ax, splat(0.3275911f), splat(1.0f));
+  float2 t, e;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(t.x) : "f"(d.x));
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(t.y) : "f"(d.y));
+  const float2 q = mul2(mul2(ax, ax), splat(-1.4426950408889634f));
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e.x) : "f"(q.x));
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e.y) : "f"(q.y));
+  // the polynomial with its sign flipped, so that E = fma(npoly * t, e, 1)
+  float2 np = fma2(splat(-1.061405429f), t, splat(1.453152027f));
+  np = fma2(np, t, splat(-1.421413741f));
+  np = fma2(np, t, splat(0.284496736f));
+  np = fma2(np, t, splat(-0.254829592f));
+  const float2 big_e = fma2(mul2(np, t), e, splat(1.0f));
+  return fma2(ah, big_e, h);
+}
+
+// The operators that have a packed form (16-bit data only): pairs of elements.
+template <typename T, int OP> constexpr bool ew_packed() {
+  return sizeof(T) == 2 && (OP == B200_EW_GELU_ERF || OP == B200_EW_ADD_GELU_ERF ||
+                            OP == B200_EW_BIAS_SCALE_CLAMP_GELU);
+}
+template <int OP>
+__device__ __forceinline__ float2 ew_apply2(float2 x, float2 o, float p0, float p1, float p2) {
+  if constexpr (OP == B200_EW_GELU_ERF) return gelu_erf_short2(x);
+  if constexpr (OP == B200_EW_ADD_GELU_ERF) return gelu_erf_short2(fma2(o, splat(p0), x));
+  float2 z = mul2(make_float2(x.x + o.x, x.y + o.y), splat(p0));
+  z.x = fminf(fmaxf(z.x, p1), p2);
+  z.y = fminf(fmaxf(z.y, p1), p2);
+  return gelu_erf_short2(z);
+}
+template <typename T> __device__ __forceinline__ float2 unpack_pair(uint32_t w);
+template <> __device__ __forceinline__ float2 unpack_pair<__nv_bfloat16>(uint32_t w) {
+  return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
+}
+template <> __device__ __forceinline__ float2 unpack_pair<__half>(uint32_t w) {
+  return __half22float2(*reinterpret_cast<const __half2 *>(&w));
+}
+template <typename T> __device__ __forceinline__ uint32_t pack_pair(float2 v);
+template <> __device__ __forceinline__ uint32_t pack_pair<__nv_bfloat16>(float2 v) {
+  const __nv_bfloat162 h = __floats2bfloat162_rn(v.x, v.y);
+  return *reinterpret_cast<const uint32_t *>(&h);
+}
+template <> __device__ __forceinline__ uint32_t pack_pair<__half>(float2 v) {
+  const __half2 h = __floats2half2_rn(v.x, v.y);
+  return *reinterpret_cast<const uint32_t *>(&h);
+}
+
 template <typename T, int OP> __device__ __forceinline__ float ew_apply(float x, float o, float p0,
                                                                         float p1, float p2) {
   if constexpr (OP == B200_EW_GELU_ERF) return gelu_erf_t<T>(x);
@@ -96,33 +171,59 @@ elementwise_vec_kernel(const T *__restrict__ a, const T *__restrict__ b, T *__re
   constexpr bool kHasB = OP != B200_EW_GELU_ERF;
   constexpr bool kBias = OP == B200_EW_BIAS_SCALE_CLAMP_GELU;
   const int64_t tile = 256 * U;
-  const bool narrow = nvec * N < ((int64_t)1 << 32);
+  // BIAS_SCALE_CLAMP_GELU: the bias column of a vector is (v * N) % n_cols.  One remainder per
+  // thread, before the loop; after that the column advances by constants (the 256 vectors
+  // between a thread's slots, the grid's stride between its tiles) with a conditional
+  // subtraction -- a 64-bit remainder per vector costs more than the GELU.
+  int64_t col0 = 0, slot_step = 0, tile_step = 0;
+  if constexpr (kBias) {
+    col0 = (((int64_t)blockIdx.x * tile + threadIdx.x) * N) % n_cols;
+    slot_step = ((int64_t)256 * N) % n_cols;
+    tile_step = (((int64_t)gridDim.x * tile) % n_cols * N) % n_cols;
+  }
   for (int64_t base = (int64_t)blockIdx.x * tile; base < nvec; base += (int64_t)gridDim.x * tile) {
     vec16<T> va[U], vb[U];
+    int64_t col = col0;
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       const int64_t v = base + u * 256 + threadIdx.x;
       if (v < nvec) {
         va[u].raw = ld_stream16(a + v * N);
         if constexpr (kBias) {
-          // 32-bit remainder when the range allows it: the 64-bit one costs more than the GELU
-          const int64_t col = narrow ? (int64_t)((uint32_t)(v * N) % (uint32_t)n_cols)
-                                     : (v * N) % n_cols;
           vb[u].raw = __ldg(reinterpret_cast<const uint4 *>(b + col));
         } else if constexpr (kHasB) {
           vb[u].raw = ld_stream16(b + v * N);
         }
       }
+      if constexpr (kBias) {
+        col += slot_step;
+        if (col >= n_cols) col -= n_cols;
+      }
+    }
+    if constexpr (kBias) {
+      col0 += tile_step;
+      if (col0 >= n_cols) col0 -= n_cols;
     }
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       const int64_t v = base + u * 256 + threadIdx.x;
       if (v < nvec) {
         vec16<T> o;
+        if constexpr (ew_packed<T, OP>()) {
+          const uint32_t *wa = reinterpret_cast<const uint32_t *>(&va[u].raw);
+          const uint32_t *wb = reinterpret_cast<const uint32_t *>(&vb[u].raw);
+          uint32_t *wo = reinterpret_cast<uint32_t *>(&o.raw);
 #pragma unroll
-        for (int j = 0; j < N; ++j)
-          o.e[j] = io<T>::store(ew_apply<T, OP>(io<T>::load(va[u].e[j]),
-                                                kHasB ? io<T>::load(vb[u].e[j]) : 0.f, p0, p1, p2));
+          for (int j = 0; j < 4; ++j)
+            wo[j] = pack_pair<T>(ew_apply2<OP>(
+                unpack_pair<T>(wa[j]), kHasB ? unpack_pair<T>(wb[j]) : make_float2(0.f, 0.f), p0,
+                p1, p2));
+        } else {
+#pragma unroll
+          for (int j = 0; j < N; ++j)
+            o.e[j] = io<T>::store(ew_apply<T, OP>(io<T>::load(va[u].e[j]),
+                                                  kHasB ? io<T>::load(vb[u].e[j]) : 0.f, p0, p1, p2));
+        }
         st_stream16(out + v * N, o.raw);
       }
     }
@@ -319,7 +420,7 @@ repeat_log_softmax_vec_kernel(const T *__restrict__ x, T *__restrict__ y, int64_
 // Short input rows (at most one 16-byte vector per thread of the group): the vector stays in
 // registers between the maximum and the sum, and the row goes to shared memory as floats once,
 // so the output pass reads its repeated inputs from there instead of from global memory.
-template <typename T, int G>
+template <typename T, int G, int REP>
 __global__ void __launch_bounds__(kRowThreads)
 repeat_log_softmax_cached_kernel(const T *__restrict__ x, T *__restrict__ y, int64_t rows,
                                  int cols, int repeat, int length) {
@@ -353,7 +454,7 @@ repeat_log_softmax_cached_kernel(const T *__restrict__ x, T *__restrict__ y, int
     for (int j = 0; j < N; ++j) {
       const int c = lane * N + j;
       const int count = min(repeat, length - c * repeat);  // the last used input may repeat less
-      if (c < used) s += (float)count * expf(f[j] - m);
+      if (c < used) s += (float)count * (sizeof(T) == 4 ? expf(f[j] - m) : __expf(f[j] - m));
     }
   }
   // the reduction's barrier also publishes the cached row to the whole group
@@ -361,6 +462,22 @@ repeat_log_softmax_cached_kernel(const T *__restrict__ x, T *__restrict__ y, int
   if constexpr (G <= 32) __syncwarp();
   const float lse = m + logf(s);
   const int out_vec = length / N;
+  if constexpr (REP > 0) {
+    // REP divides the vector length and the output length: an output vector is N / REP
+    // cached inputs, each written REP times -- no division, no running remainder
+    constexpr int kIn = N / REP;
+    for (int v = lane; v < out_vec; v += G) {
+      vec16<T> o;
+#pragma unroll
+      for (int i = 0; i < kIn; ++i) {
+        const T value = io<T>::store(cache[group][v * kIn + i] - lse);
+#pragma unroll
+        for (int j = 0; j < REP; ++j) o.e[i * REP + j] = value;
+      }
+      st_stream16(yrow + (int64_t)v * N, o.raw);
+    }
+    return;
+  }
   for (int v = lane; v < out_vec; v += G) {
     int c = (v * N) / repeat;
     int rem = (v * N) - c * repeat;
@@ -390,10 +507,19 @@ static void launch_repeat_vec(const b200_tensor *x, b200_tensor *y, int repeat, 
                                         kRowThreads, 0, s>>>((const T *)x->data, (T *)y->data, rows, \
                                                              cols, repeat, length)
   const int used = (length + repeat - 1) / repeat;
+  // the repeat count as a compile-time constant when it divides the vector and the row
+  const int rep = (length % repeat == 0 && N % repeat == 0 && repeat > 1) ? repeat : 0;
+#define B200_RLC_R(G, R)                                                                    \
+  repeat_log_softmax_cached_kernel<T, G, R><<<(unsigned)((rows + kRowThreads / G - 1) / (kRowThreads / G)), \
+                                              kRowThreads, 0, s>>>((const T *)x->data, (T *)y->data, rows, \
+                                                                   cols, repeat, length)
 #define B200_RLC(G)                                                                         \
-  repeat_log_softmax_cached_kernel<T, G><<<(unsigned)((rows + kRowThreads / G - 1) / (kRowThreads / G)), \
-                                           kRowThreads, 0, s>>>((const T *)x->data, (T *)y->data, rows, \
-                                                                cols, repeat, length)
+  do {                                                                                      \
+    if (rep == 2) B200_RLC_R(G, 2);                                                         \
+    else if (rep == 4) B200_RLC_R(G, 4);                                                    \
+    else if (rep == 8 && N == 8) B200_RLC_R(G, (N == 8 ? 8 : 0));                           \
+    else B200_RLC_R(G, 0);                                                                  \
+  } while (0)
   // the cached form when a group's threads hold the used inputs in one vector each
   if (out_vec <= 32 * 4) { if (used <= 32 * N) B200_RLC(32); else B200_RLV(32); }
   else if (out_vec <= 64 * 4) { if (used <= 64 * N) B200_RLC(64); else B200_RLV(64); }
@@ -401,6 +527,7 @@ static void launch_repeat_vec(const b200_tensor *x, b200_tensor *y, int repeat, 
   else if (used <= 256 * N) B200_RLC(256);
   else B200_RLV(256);
 #undef B200_RLC
+#undef B200_RLC_R
 #undef B200_RLV
 }
 

@@ -477,7 +477,13 @@ static int dispatch(const b200_tensor *x, b200_tensor *y, int mask_kind,
       mask_kind == B200_MASK_NONE
           ? dispatch_rows<T, kSoftmaxPlain, true>(x, nullptr, y, mask_kind, row_offset, stream)
           : dispatch_rows<T, kSoftmaxPlain, false>(x, nullptr, y, mask_kind, row_offset, stream);
-  if (!taken)
+  bool clustered = false;
+  if (!taken && ((uintptr_t)x->data % 16) == 0 && ((uintptr_t)y->data % 16) == 0) {
+    // wider than one CTA holds in registers: a cluster per row
+    const int st = softmax_cluster_rows<T>(x, y, mask_kind, row_offset, stream, &clustered);
+    if (st != B200_OK) return st;
+  }
+  if (!taken && !clustered)
     softmax_loop_kernel<T><<<(unsigned)x->shape[0], kRowThreads, 0, stream>>>(
         (const T *)x->data, (T *)y->data, (int)x->shape[1], mask_kind, row_offset);
   B200_CUDA_OK(cudaGetLastError());

@@ -66,6 +66,15 @@ def gemm(a, b, c, *, bias=None, act=abi.ACT_NONE, b2=None, stream=0):
                                            int(act), stream))
 
 
+def linear(x, w, y, *, bias=None, act=abi.ACT_NONE, stream=0):
+    """y = act(x @ w.T + bias) with the weight as [N, K] (a linear layer's layout; the
+    transposed-B case of matmul_kernel's general strides, ops/suite/perf/matmul_triton2.py:27-30)."""
+    xd, wd, yd = _desc(x), _desc(w), _desc(y)
+    biasd = _desc(bias, shape=(int(w.shape[0]),), strides=(1,)) if bias is not None else None
+    abi.check(abi.lib().b200_linear_bias_act(_ref(xd), _ref(wd), _ref(biasd), _ref(yd), int(act),
+                                             stream))
+
+
 def gemm_groupnorm_rowmin(x, w, gamma, beta, mins, *, bias=None, group_size=32, eps=1e-5,
                           stream=0):
     """mins[m] = min(mins[m], min over n of GroupNorm(x @ w + bias)[m, n]) with groups of

@@ -204,30 +204,42 @@ def _row_major(v, name, prefix_pairs):
                  "only row-major operands (unit inner stride) have a native kernel")
 
 
+def _b_operand(v, name, rows_key, cols_key, k, n):
+    """The B operand of a strided matmul: row-major [K, N] (unit stride along N), or its
+    transpose in memory -- unit stride along K, i.e. a [N, K] weight -- which the native GEMM
+    takes as a K-major operand.  Returns (view, transposed)."""
+    stride_k, stride_n = int(v[rows_key]), int(v[cols_key])
+    if stride_n == 1:
+        return (k, n), (stride_k, 1), False
+    _require(stride_k == 1, name, cols_key,
+             "B needs a unit stride along N (row-major [K,N]) or along K (a [N,K] weight)")
+    return (n, k), (stride_n, 1), True
+
+
 def _matmul_strided(device, v, grid, name):
     """matmul_kernel (ops/suite/perf/matmul_triton2.py:27-30, matmul_triton_autotune.py:28-31)."""
     m, n, k = int(v["M"]), int(v["N"]), int(v["K"])
-    _row_major(v, name, (("stride_am", "stride_ak"), ("stride_bk", "stride_bn"),
-                         ("stride_cm", "stride_cn")))
+    _row_major(v, name, (("stride_am", "stride_ak"), ("stride_cm", "stride_cn")))
+    shape, strides, transposed = _b_operand(v, name, "stride_bk", "stride_bn", k, n)
     leaky = bool(v.get("LEAKY", False))
     if leaky:
         _require(abs(float(v.get("SLOPE", 0.01)) - 0.01) < 1e-12, name, "SLOPE",
                  "the native leaky-ReLU epilogue uses slope 0.01")
-    ops.gemm(_View(v["a_ptr"], (m, k), (int(v["stride_am"]), 1)),
-             _View(v["b_ptr"], (k, n), (int(v["stride_bk"]), 1)),
-             _View(v["c_ptr"], (m, n), (int(v["stride_cm"]), 1)),
-             act=abi.ACT_LEAKY_RELU if leaky else abi.ACT_NONE, stream=device.stream)
+    (ops.linear if transposed else ops.gemm)(
+        _View(v["a_ptr"], (m, k), (int(v["stride_am"]), 1)), _View(v["b_ptr"], shape, strides),
+        _View(v["c_ptr"], (m, n), (int(v["stride_cm"]), 1)),
+        act=abi.ACT_LEAKY_RELU if leaky else abi.ACT_NONE, stream=device.stream)
 
 
 def _linear_act(device, v, grid, name):
     """linear_act_kernel (ops/suite/perf/triton_linear_activation.py:28-30): bias + erf-GELU."""
     m, n, k = int(v["M"]), int(v["N"]), int(v["K"])
-    _row_major(v, name, (("stride_xm", "stride_xk"), ("stride_wk", "stride_wn"),
-                         ("stride_ym", "stride_yn")))
-    ops.gemm(_View(v["x_ptr"], (m, k), (int(v["stride_xm"]), 1)),
-             _View(v["w_ptr"], (k, n), (int(v["stride_wk"]), 1)),
-             _View(v["y_ptr"], (m, n), (int(v["stride_ym"]), 1)),
-             bias=_View(v["b_ptr"], (n,)), act=abi.ACT_GELU_ERF, stream=device.stream)
+    _row_major(v, name, (("stride_xm", "stride_xk"), ("stride_ym", "stride_yn")))
+    shape, strides, transposed = _b_operand(v, name, "stride_wk", "stride_wn", k, n)
+    (ops.linear if transposed else ops.gemm)(
+        _View(v["x_ptr"], (m, k), (int(v["stride_xm"]), 1)), _View(v["w_ptr"], shape, strides),
+        _View(v["y_ptr"], (m, n), (int(v["stride_ym"]), 1)),
+        bias=_View(v["b_ptr"], (n,)), act=abi.ACT_GELU_ERF, stream=device.stream)
 
 
 def _gemm_gn_min(device, v, grid, name):

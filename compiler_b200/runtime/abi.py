@@ -94,6 +94,7 @@ PROTOTYPES = {
     "b200_repeat_log_softmax": (c_int, [_T, _T, c_int, _PTR]),
     "b200_elementwise": (c_int, [c_int, _T, _T, _T, c_float, c_float, c_float, _PTR]),
     "b200_gemm_bias_act": (c_int, [_T, _T, _T, _T, _T, c_int, _PTR]),
+    "b200_linear_bias_act": (c_int, [_T, _T, _T, _T, c_int, _PTR]),
     "b200_gemm_scatter_rows": (c_int, [_T, _T, _T, POINTER(_PTR), c_int, c_int, c_int64, _PTR]),
     "b200_reduce_slices_broadcast": (c_int, [_PTR, c_uint32, c_uint32, c_int, c_int64, c_int64,
                                              c_int64, POINTER(_PTR), _PTR]),

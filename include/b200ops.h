@@ -213,6 +213,15 @@ int b200_gemm_bias_act(const b200_tensor *a, const b200_tensor *b,
                        const b200_tensor *b2, const b200_tensor *bias,
                        b200_tensor *c, int act, void *stream);
 
+/* y = act(x @ w^T + bias) with the weight given as [N, K] rows of K -- the layout of a linear
+ * layer's weight, and of a B operand passed with stride_bk = 1 (the "general strides" of
+ * matmul_kernel, ops/suite/perf/matmul_triton2.py:27-30, and the transposed weight of
+ * linear_act_kernel, ops/suite/perf/triton_linear_activation.py:28-30).  Same epilogues and
+ * tensor-core kernels as b200_gemm_bias_act (the weight is fed as a K-major operand, nothing
+ * is transposed in memory); B200_ACT_SWIGLU is not available here. */
+int b200_linear_bias_act(const b200_tensor *x, const b200_tensor *w, const b200_tensor *bias,
+                         b200_tensor *y, int act, void *stream);
+
 /* mins[m] = min(mins[m], min_n GroupNorm(x @ w + bias)[m, n]): a GEMM whose epilogue
  * normalises groups of group_size consecutive columns (mean / variance inside the group,
  * gamma, beta) and keeps only the minimum of each row.  Replaces fused_gemm_gn_min_kernel

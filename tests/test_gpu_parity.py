@@ -141,6 +141,40 @@ def test_masked_softmax_many_rows(device, case, dtype):
     assert (y[ref == 0] == 0).all() and np.isfinite(y).all()
 
 
+# rows wider than one CTA keeps in registers (32768 16-bit / 16384 32-bit elements): a cluster
+# of 2, 4 or 8 CTAs per row with the partial results merged through distributed shared memory;
+# widths that are not a whole number of CTAs, a width beyond eight CTAs (looping kernel)
+WIDE_ROWS = [(3, 33000), (2, 40000), (5, 65536), (2, 131072 + 8), (3, 262144), (1, 262144 + 512)]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "float16", "bfloat16"])
+@pytest.mark.parametrize("shape", WIDE_ROWS)
+def test_wide_rows_cluster_softmax_and_rmsnorm(device, shape, dtype):
+    rows, cols = shape
+    if dtype == "float32":
+        cols //= 2
+    rng = np.random.default_rng(_seed(shape, dtype, "wide"))
+    x = _host(rng.standard_normal((rows, cols)) * 2, dtype)
+    dx = _up(device, x, dtype)
+    for masked, offset in ((False, 0), (True, cols - 2)):
+        dy = _poisoned(device, (rows, cols), dtype)
+        ops.softmax(dx, dy, causal_mod=masked, row_offset=offset)
+        y = device.download(dy)
+        ref = oracle.masked_softmax_ref(x, offset) if masked else oracle.softmax_ref(x)
+        rtol, atol = (2e-3, 1e-7) if dtype == "float32" else TOL[dtype]
+        oracle.compare(y.astype(np.float64), ref, rtol, atol, name=f"softmax masked={masked}")
+        if masked:
+            assert (y[ref == 0] == 0).all()
+    w = _host(rng.uniform(0.5, 1.5, cols), dtype)
+    dw = _up(device, w, dtype)
+    dyr, dr = _poisoned(device, (rows, cols), dtype), _poisoned(device, (rows,), dtype)
+    ops.rmsnorm(dx, dw, dyr, dr, eps=1e-6)
+    y_ref, r_ref = oracle.rmsnorm_ref(x, w, 1e-6)
+    rtol, atol = (1e-5, 1e-6) if dtype == "float32" else TOL[dtype]
+    oracle.compare(device.download(dyr).astype(np.float64), y_ref, rtol, atol, name="rmsnorm y")
+    oracle.compare(device.download(dr).astype(np.float64), r_ref, rtol, atol, name="rmsnorm r")
+
+
 GEMM_SHAPES = [(128, 256, 64), (256, 512, 256), (1, 8, 8), (129, 264, 72), (257, 520, 200),
                (100, 40, 24), (384, 1024, 1000), (130, 96, 8)]
 
@@ -163,6 +197,58 @@ def test_gemm_sweep(device, shape, dtype, act):
     device.check_status()
     ref = oracle.linear_act_ref(a, b, bias if use_bias else None, act)
     oracle.compare(device.download(dc).astype(np.float64), ref, *TOL[dtype], name=f"C{shape}")
+
+
+# The weight given as [N, K] (a linear layer's layout): small and ragged shapes on the one-CTA
+# kernel, shapes with a wave of 256 x 256 tiles on the CTA-pair kernel, fp32 and unaligned rows
+# on the CUDA-core kernel; cross-checked against the oracle on w.T.
+LINEAR_SHAPES = [(128, 256, 64), (129, 264, 72), (100, 40, 24), (384, 1024, 1000),
+                 (3328, 3072, 192), (3300, 3096, 200), (2050, 4872, 8), (2048, 5000, 520),
+                 (130, 96, 12)]
+
+
+@pytest.mark.parametrize("dtype,act", [("bfloat16", "gelu_erf"), ("float16", "none"),
+                                        ("bfloat16", "leaky_relu"), ("float32", "gelu_tanh")])
+@pytest.mark.parametrize("shape", LINEAR_SHAPES)
+def test_linear_weight_rows_of_k(device, shape, dtype, act):
+    m, n, k = shape
+    if dtype == "float32" and m * n * k > 1 << 28:
+        pytest.skip("the CUDA-core path is for correctness, not for this size")
+    rng = np.random.default_rng(_seed(shape, dtype, act, "linear"))
+    x = _host(rng.standard_normal((m, k)) / np.sqrt(k), dtype)
+    w = _host(rng.standard_normal((n, k)), dtype)
+    bias = _host(rng.normal(0, 0.1, n), dtype)
+    dx, dw, dbias = _up(device, x, dtype), _up(device, w, dtype), _up(device, bias, dtype)
+    dy = _poisoned(device, (m, n), dtype)
+    code = {"none": abi.ACT_NONE, "gelu_tanh": abi.ACT_GELU_TANH, "gelu_erf": abi.ACT_GELU_ERF,
+            "leaky_relu": abi.ACT_LEAKY_RELU}[act]
+    use_bias = act != "none"
+    ops.linear(dx, dw, dy, bias=dbias if use_bias else None, act=code)
+    device.check_status()
+    ref = oracle.linear_act_ref(x, np.ascontiguousarray(w.T), bias if use_bias else None, act)
+    rtol, atol = (2e-3, 2e-3) if dtype == "float32" else TOL[dtype]
+    oracle.compare(device.download(dy).astype(np.float64), ref, rtol, atol, name=f"Y{shape}")
+
+
+def test_strided_matmul_with_transposed_b_through_the_device(device):
+    """matmul_kernel's general strides (ops/suite/perf/matmul_triton2.py:27-30): B handed over
+    as the transpose in memory of a [K, N] matrix (stride_bk = 1, stride_bn = K)."""
+    case, _ = golden_cases.load("matmul_triton2__32x32x32__bfloat16")
+    m, n, k = 200, 264, 136
+    rng = np.random.default_rng(77)
+    a = _host(rng.standard_normal((m, k)) / np.sqrt(k), "bfloat16")
+    bt = _host(rng.standard_normal((n, k)), "bfloat16")          # B^T, contiguous
+    args = dict(case["args"])
+    args.update({"a_ptr": a, "b_ptr": bt, "c_ptr": np.full((m, n), POISON, np.float32),
+                 "M": m, "N": n, "K": k, "stride_am": k, "stride_ak": 1, "stride_bk": 1,
+                 "stride_bn": k, "stride_cm": n, "stride_cn": 1})
+    grown = dict(case, args=args, grid=lambda meta: (-(-m // meta["BLOCK_M"]),
+                                                     -(-n // meta["BLOCK_N"])))
+    out = harness.run_case(grown, device)["c_ptr"]
+    leaky = bool({**case["args"], **case["meta"]}.get("LEAKY", False))
+    ref = oracle.linear_act_ref(a, np.ascontiguousarray(bt.T), None,
+                                "leaky_relu" if leaky else "none")
+    oracle.compare(out.astype(np.float64), ref, *TOL["bfloat16"], name="c_ptr")
 
 
 # Shapes with at least one 256 x 256 tile per pair of SMs take the CTA-pair kernel: whole
@@ -673,9 +759,12 @@ def test_repeat_log_softmax_sweep(device, case, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "float16", "bfloat16"])
-@pytest.mark.parametrize("n", [1, 7, 8, 1000, 4099, 1 << 20, (1 << 20) + 13])
+@pytest.mark.parametrize("n", [1, 7, 8, 1000, 4099, 1 << 20, (1 << 20) + 13, 1_200_000,
+                               12_000_000])
 def test_elementwise_family_sweep(device, n, dtype):
-    """The flat GELU family over lengths with and without a ragged end of the 16-byte vectors."""
+    """The flat GELU family over lengths with and without a ragged end of the 16-byte vectors;
+    the two largest lengths make the bias index of the epilogue operator wrap inside a thread's
+    slots (1.2 M) and across the grid's passes (12 M)."""
     rng = np.random.default_rng(_seed(n, dtype))
     a = _host(rng.standard_normal(n) * 2, dtype)
     b = _host(rng.standard_normal(n), dtype)
@@ -690,7 +779,7 @@ def test_elementwise_family_sweep(device, n, dtype):
     oracle.compare(run(abi.EW_GELU_ERF), oracle.gelu_erf(a.astype(np.float64)), rtol, atol)
     oracle.compare(run(abi.EW_ADD_GELU_ERF, db, p0=1.5), oracle.add_gelu_ref(a, b, 1.5), rtol, atol)
     oracle.compare(run(abi.EW_GEGLU_TANH, db), oracle.geglu_tanh_ref(a, b), rtol, atol)
-    for n_cols in (1, 8, 24, 1000):
+    for n_cols in (1, 8, 24, 1000, 2400, 4096):
         if n % n_cols:
             continue
         bias = _host(rng.standard_normal(n_cols), dtype)
