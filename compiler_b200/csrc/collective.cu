@@ -175,28 +175,39 @@ peer_allreduce_kernel(RankPointers partial, RankPointers out, int64_t first, int
     if (!cross_rank_barrier(pads, rank, world, 0, epoch, status, kSiteStart)) return;
   }
   constexpr int N = 8;  // elements per 16-byte vector of a 16-bit type
+  constexpr int U = 2;  // vectors per thread and step: 2 x world peer loads in flight
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
-  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < vecs; i += stride) {
-    const int64_t e = first + i * N;
-    vec16<TIn> v[8];
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < vecs; i += stride * U) {
+    vec16<TIn> v[U][8];
 #pragma unroll
-    for (int w = 0; w < 8; ++w)
-      if (w < world) v[w].raw = ld_stream16(static_cast<const TIn *>(partial.ptr[w]) + e);
-    float acc[N];
+    for (int u = 0; u < U; ++u) {
+      const int64_t e = first + (i + u * stride) * N;
+      if (i + u * stride < vecs) {
 #pragma unroll
-    for (int j = 0; j < N; ++j) acc[j] = 0.f;
-#pragma unroll
-    for (int w = 0; w < 8; ++w)
-      if (w < world) {
-#pragma unroll
-        for (int j = 0; j < N; ++j) acc[j] += io<TIn>::load(v[w].e[j]);
+        for (int w = 0; w < 8; ++w)
+          if (w < world) v[u][w].raw = ld_stream16(static_cast<const TIn *>(partial.ptr[w]) + e);
       }
-    vec16<TOut> r;
+    }
 #pragma unroll
-    for (int j = 0; j < N; ++j) r.e[j] = io<TOut>::store(acc[j]);
+    for (int u = 0; u < U; ++u) {
+      if (i + u * stride >= vecs) continue;
+      const int64_t e = first + (i + u * stride) * N;
+      float acc[N];
 #pragma unroll
-    for (int w = 0; w < 8; ++w)
-      if (w < world) *reinterpret_cast<uint4 *>(static_cast<TOut *>(out.ptr[w]) + e) = r.raw;
+      for (int j = 0; j < N; ++j) acc[j] = 0.f;
+#pragma unroll
+      for (int w = 0; w < 8; ++w)
+        if (w < world) {
+#pragma unroll
+          for (int j = 0; j < N; ++j) acc[j] += io<TIn>::load(v[u][w].e[j]);
+        }
+      vec16<TOut> r;
+#pragma unroll
+      for (int j = 0; j < N; ++j) r.e[j] = io<TOut>::store(acc[j]);
+#pragma unroll
+      for (int w = 0; w < 8; ++w)
+        if (w < world) *reinterpret_cast<uint4 *>(static_cast<TOut *>(out.ptr[w]) + e) = r.raw;
+    }
   }
   if constexpr (SYNC) cross_rank_barrier(pads, rank, world, 1, epoch, status, kSiteEnd);
 }
@@ -205,7 +216,7 @@ template <typename TIn, typename TOut>
 int launch_peer(const RankPointers &partial, const RankPointers &out, int64_t first, int64_t vecs,
                 const SignalPads &pads, bool sync, int rank, int world, uint32_t epoch, int ctas,
                 cudaStream_t s) {
-  int64_t blocks = (vecs + kThreads - 1) / kThreads;
+  int64_t blocks = (vecs + kThreads * 2 - 1) / (kThreads * 2);
   int64_t cap = ctas > 0 ? ctas : (int64_t)sm_count() * 2;
   if (cap > kMaxCtas) cap = kMaxCtas;
   if (blocks > cap) blocks = cap;

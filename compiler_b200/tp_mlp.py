@@ -56,13 +56,15 @@ from compiler_b200.runtime import abi
 class TensorParallelMLP:
     kernels_per_forward = None  # set in __init__: 1 fused up-projection + one GEMM per chunk
 
-    def __init__(self, wg, wu, wd, *, group=None, chunks: int = 4, collective: str = "nccl",
+    def __init__(self, wg, wu, wd, *, group=None, chunks=None, collective: str = "nccl",
                  partial_dtype=None, comm_ctas: int = 0):
         """wg, wu: this rank's [hidden, ffn/tp] column shards; wd: its [ffn/tp, hidden] row
         shard (CUDA bf16/fp16 torch tensors, contiguous).
 
         ``chunks``: row chunks of the down-projection whose all-reduce overlaps the next
-        chunk's GEMM (nccl and nvls paths).  ``partial_dtype`` (peer and nvls paths): the type
+        chunk's GEMM (default: 4 for the nccl path, whose all-reduce runs on NCCL's own
+        stream and copy engines; 1 for the nvls and pull paths, where an all-reduce kernel
+        beside the GEMM took more from it than the overlap gave back on 2 GPUs).  ``partial_dtype`` (peer and nvls paths): the type
         the partial products are staged in -- ``torch.float16`` by default: against bfloat16 it
         keeps three more mantissa bits at the same traffic, which is what keeps the sum of
         ``world`` partials within 2e-2 of the float64 result where bfloat16 partials of
@@ -74,6 +76,8 @@ class TensorParallelMLP:
         self.torch = torch
         self.wg, self.wu, self.wd = wg, wu, wd
         self.group = group
+        if chunks is None:
+            chunks = 4 if collective == "nccl" else 1
         self.chunks = max(1, int(chunks))
         if collective not in ("nccl", "peer", "nvls", "pull"):
             raise ValueError("collective must be 'nccl', 'peer', 'nvls' or 'pull'")
@@ -95,8 +99,8 @@ class TensorParallelMLP:
         self._nvls = None  # (key, partial, handle)
 
     @classmethod
-    def synthetic(cls, hidden, ffn, rank, world, seed=0, dtype=None, chunks=4, collective="nccl",
-                  **options):
+    def synthetic(cls, hidden, ffn, rank, world, seed=0, dtype=None, chunks=None,
+                  collective="nccl", **options):
         """Random-normal(0, 0.02) weights; every rank draws only its own shard, from a
         generator seeded by (seed, rank)."""
         import torch
@@ -271,26 +275,34 @@ class TensorParallelMLP:
                   if ((c[1] - c[0]) * hidden) % (8 * world) == 0]
         if sum(hi - lo for lo, hi in chunks) != m:
             chunks = [(0, m)]
+        overlapped = len(chunks) > 1
+        reduce_stream = comm.cuda_stream if overlapped else stream
         for lo, hi in chunks:
             ops.gemm(self._h[lo:hi], self.wd, partial[lo:hi], stream=stream)
-            ready = torch.cuda.Event()
-            ready.record(main)
-            comm.wait_event(ready)
+            if overlapped:  # one chunk: nothing to run beside, the all-reduce follows in line
+                ready = torch.cuda.Event()
+                ready.record(main)
+                comm.wait_event(ready)
+            else:
+                mark("down_projection")
             self._epoch += 1
             if self.collective == "nvls":
                 abi.check(lib.b200_multimem_allreduce(
                     int(partial_h.multicast_ptr), in_code, int(out_h.multicast_ptr), out_code,
                     lo * hidden, (hi - lo) * hidden, rank, world, pads, self._epoch,
-                    self.comm_ctas, comm.cuda_stream))
+                    self.comm_ctas, reduce_stream))
             else:
                 abi.check(lib.b200_peer_allreduce(
                     partial_ptrs, in_code, out_ptrs, out_code, lo * hidden, (hi - lo) * hidden,
-                    rank, world, pads, self._epoch, self.comm_ctas, comm.cuda_stream))
-        mark("down_projection_chunks_issued")
-        done = torch.cuda.Event()
-        done.record(comm)
-        main.wait_event(done)
-        mark("all_reduce_tail")
+                    rank, world, pads, self._epoch, self.comm_ctas, reduce_stream))
+        if overlapped:
+            mark("down_projection_chunks_issued")
+            done = torch.cuda.Event()
+            done.record(comm)
+            main.wait_event(done)
+            mark("all_reduce_tail")
+        else:
+            mark("all_reduce_with_its_barriers")
         if y is not None and y.data_ptr() != out.data_ptr():
             y.copy_(out)
             mark("copy_out")

@@ -294,9 +294,11 @@ def test_gemm_f32_bias_and_f32_output(device, shape):
     oracle.compare(device.download(dc).astype(np.float64), ref, 2e-3, 2e-3)
 
 
-# the last two shapes have enough 256 x 128 tiles for the CTA-pair form of the dual GEMM
+# the shapes from the fourth on have enough 256-row tiles for the CTA-pair form of the dual
+# GEMM (whole tiles, ragged last row and column blocks, the MLP's up-projection at 8 ranks)
 @pytest.mark.parametrize("shape", [(128, 128, 64), (130, 200, 72), (256, 384, 512),
-                                   (3328, 1536, 192), (2050, 2440, 72)])
+                                   (3328, 1536, 192), (2050, 2440, 72), (4096, 1792, 136),
+                                   (4090, 1784, 72), (4096, 1792, 4096)])
 def test_gemm_swiglu_dual(device, shape):
     m, n, k = shape
     rng = np.random.default_rng(6)
