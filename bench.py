@@ -727,11 +727,12 @@ def bench_tp_mlp(torch, ops, dist, launches, peaks, source, collective, **option
         "peer": "reduce-scatter by peer stores in the GEMM epilogue (float16 partials) + sum and "
                 "broadcast kernel",
         "nvls": f"{str(mlp.partial_dtype).rsplit('.', 1)[-1]} partials in symmetric memory, "
-                "in-switch sum and broadcast (multimem.ld_reduce / multimem.st) per row chunk "
-                "beside the next chunk's GEMM, barriers inside the kernel",
+                "in-switch sum and broadcast (multimem.ld_reduce / multimem.st), barriers "
+                "inside the kernel",
         "pull": "float16 partials in symmetric memory, summed by plain peer loads and "
-                "broadcast by peer stores per row chunk beside the next chunk's GEMM, "
-                "barriers inside the kernel",
+                "broadcast by peer stores, barriers inside the kernel"
+                + (f"; the MLP runs in {mlp.row_splits} blocks of rows, a block's all-reduce "
+                   "beside both projections of the next block" if mlp.row_splits > 1 else ""),
         "none": "one GPU: the two GEMMs alone (anchor of the strong-scaling curve)",
     }
     partial_bytes = MLP_M * MLP_HIDDEN * (4 if collective == "nccl"
@@ -1051,6 +1052,7 @@ def main():
             for key, collective, options in (
                     ("tp_mlp", "nccl", {}), ("tp_mlp_peer", "peer", {}),
                     ("tp_mlp_nvls", "nvls", {}), ("tp_mlp_pull", "pull", {}),
+                    ("tp_mlp_pull_row_blocks", "pull", {"row_splits": 2, "comm_ctas": 74}),
                     ("tp_mlp_nvls_f32", "nvls", {"partial_dtype": torch.float32})):
                 if collective == "peer" and MLP_M % (128 * dist.world):
                     continue

@@ -57,7 +57,7 @@ class TensorParallelMLP:
     kernels_per_forward = None  # set in __init__: 1 fused up-projection + one GEMM per chunk
 
     def __init__(self, wg, wu, wd, *, group=None, chunks=None, collective: str = "nccl",
-                 partial_dtype=None, comm_ctas: int = 0):
+                 partial_dtype=None, comm_ctas: int = 0, row_splits: int = 1):
         """wg, wu: this rank's [hidden, ffn/tp] column shards; wd: its [ffn/tp, hidden] row
         shard (CUDA bf16/fp16 torch tensors, contiguous).
 
@@ -71,7 +71,9 @@ class TensorParallelMLP:
         opposite sign cancel; its range is 65504, so operands whose partial products can
         exceed that need ``torch.float32`` (nvls path only: twice the traffic into the switch,
         the exact sum) -- or the weights' own type.  ``comm_ctas``: grid limit of the
-        in-switch all-reduce kernel while it runs beside a GEMM (0 = default)."""
+        all-reduce kernel while it runs beside a GEMM (0 = default).  ``row_splits`` (nvls and
+        pull paths): run the whole MLP in this many blocks of rows, the all-reduce of a
+        block's result on a second stream beside both projections of the next block."""
         import torch
         self.torch = torch
         self.wg, self.wu, self.wd = wg, wu, wd
@@ -91,6 +93,7 @@ class TensorParallelMLP:
                                                                          torch.bfloat16):
             raise ValueError(f"collective='{collective}' stages 16-bit partials")
         self.comm_ctas = int(comm_ctas)
+        self.row_splits = max(1, int(row_splits))
         self._epoch = 0
         self._comm_stream = None
         self._h = None
@@ -123,6 +126,8 @@ class TensorParallelMLP:
         if self._h is None or self._h.shape != (m, cols) or self._h.dtype != x.dtype:
             self._h = torch.empty((m, cols), device=x.device, dtype=x.dtype)
         stream = torch.cuda.current_stream().cuda_stream
+        if self.collective in ("nvls", "pull") and self.row_splits > 1:
+            return self._forward_nvls(y, stream, mark, x=x)
         ops.gemm(x, self.wg, self._h, b2=self.wu, act=abi.ACT_SWIGLU, stream=stream)
         mark("up_projection")
         if self.collective == "peer":
@@ -249,7 +254,7 @@ class TensorParallelMLP:
             self._nvls = (key, partial, partial_h, out, out_h, pads, pad, pad_h)
         return self._nvls[1:6]
 
-    def _forward_nvls(self, y, stream, mark):
+    def _forward_nvls(self, y, stream, mark, x=None):
         """Down-projection into the symmetric partial in row chunks; each chunk's all-reduce
         (in the switch, or over plain peer memory for ``collective="pull"``; with its own
         cross-rank barriers) runs on a second stream beside the next chunk's GEMM."""
@@ -271,13 +276,19 @@ class TensorParallelMLP:
         pointer_array = ctypes.c_void_p * world
         partial_ptrs = pointer_array(*[int(p) for p in partial_h.buffer_ptrs])
         out_ptrs = pointer_array(*[int(p) for p in out_h.buffer_ptrs])
-        chunks = [c for c in shard.row_chunks(m, self.chunks)
+        # x given: the whole MLP runs block of rows by block of rows (row_splits blocks), so
+        # that the all-reduce of a block's result runs beside BOTH projections of the next one
+        pieces = self.row_splits if x is not None else self.chunks
+        chunks = [c for c in shard.row_chunks(m, pieces)
                   if ((c[1] - c[0]) * hidden) % (8 * world) == 0]
         if sum(hi - lo for lo, hi in chunks) != m:
             chunks = [(0, m)]
         overlapped = len(chunks) > 1
         reduce_stream = comm.cuda_stream if overlapped else stream
         for lo, hi in chunks:
+            if x is not None:
+                ops.gemm(x[lo:hi], self.wg, self._h[lo:hi], b2=self.wu, act=abi.ACT_SWIGLU,
+                         stream=stream)
             ops.gemm(self._h[lo:hi], self.wd, partial[lo:hi], stream=stream)
             if overlapped:  # one chunk: nothing to run beside, the all-reduce follows in line
                 ready = torch.cuda.Event()
