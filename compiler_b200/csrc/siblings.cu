@@ -71,28 +71,9 @@ template <typename T> __device__ __forceinline__ float gelu_tanh_t(float z) {
 
 constexpr int kEwSwiglu = 100;  // internal: x * sigmoid(x) * b (b200_swiglu_fwd on contiguous rows)
 
-// Two fp32 lanes per instruction (fma / mul .f32x2): the erf-based GELUs on 16-bit data are
-// bound by instruction issue, not by memory -- a 16-bit element is half the bytes for the same
-// arithmetic -- and the packed forms halve the multiply-add count at full fp32 precision.
-__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
-  unsigned long long d;
-  asm("fma.rn.f32x2 %0, %1, %2, %3;"
-      : "=l"(d)
-      : "l"(*reinterpret_cast<unsigned long long *>(&a)),
-        "l"(*reinterpret_cast<unsigned long long *>(&b)),
-        "l"(*reinterpret_cast<unsigned long long *>(&c)));
-  return *reinterpret_cast<float2 *>(&d);
-}
-__device__ __forceinline__ float2 mul2(float2 a, float2 b) {
-  unsigned long long d;
-  asm("mul.rn.f32x2 %0, %1, %2;"
-      : "=l"(d)
-      : "l"(*reinterpret_cast<unsigned long long *>(&a)),
-        "l"(*reinterpret_cast<unsigned long long *>(&b)));
-  return *reinterpret_cast<float2 *>(&d);
-}
-__device__ __forceinline__ float2 splat(float v) { return make_float2(v, v); }
-
+// The erf-based GELUs on 16-bit data are bound by instruction issue, not by memory -- a 16-bit
+// element is half the bytes for the same arithmetic -- and the packed fp32x2 forms
+// (common.cuh: fma2 / mul2) halve the multiply-add count at full fp32 precision.
 // gelu_erf of two values with the short erf above (Abramowitz-Stegun 7.1.26).  With
 // h = z / 2 and E = erf(|z| / sqrt 2) = 1 - poly(t) t exp(-x^2):  gelu(z) = h + |h| E.
 __device__ __forceinline__ float2 gelu_erf_short2(float2 z) {

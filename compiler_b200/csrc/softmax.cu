@@ -65,6 +65,12 @@ template <> struct RowVec<float> {
   }
 };
 
+__device__ __forceinline__ float2 pair_to_float2(__half2 v) { return __half22float2(v); }
+__device__ __forceinline__ float2 pair_to_float2(__nv_bfloat162 v) {
+  const uint32_t w = *reinterpret_cast<const uint32_t *>(&v);
+  return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
+}
+
 // 16-bit rows: the max is taken on packed pairs in the storage type (exact),
 // exp is one FFMA + one ex2 per element: 2^(x*log2e - m*log2e).
 template <typename T2, typename T1> struct RowVec16 {
@@ -81,19 +87,21 @@ template <typename T2, typename T1> struct RowVec16 {
     const T2 a = __hmax2(__hmax2(p[0], p[1]), __hmax2(p[2], p[3]));
     return fmaxf(io<T1>::load(a.x), io<T1>::load(a.y));
   }
-  // e[j] = 2^(x[j] * log2e - m * log2e): one FFMA + one ex2 per element; returns their sum
+  // e[j] = 2^(x[j] * log2e - m * log2e); returns their sum.  The multiply-add and the running
+  // sum take two elements per instruction (fp32x2), the ex2 one each.
   static __device__ __forceinline__ float exps(const uint4 &raw, float, float neg_m_log2e,
                                                float (&e)[N]) {
-    const T1 *x = reinterpret_cast<const T1 *>(&raw);
-    float s0 = 0.f, s1 = 0.f;
+    const T2 *x = reinterpret_cast<const T2 *>(&raw);
+    float2 s = make_float2(0.f, 0.f);
 #pragma unroll
-    for (int j = 0; j < N; j += 2) {
-      e[j] = ex2_approx(fmaf(io<T1>::load(x[j]), 1.4426950408889634f, neg_m_log2e));
-      e[j + 1] = ex2_approx(fmaf(io<T1>::load(x[j + 1]), 1.4426950408889634f, neg_m_log2e));
-      s0 += e[j];
-      s1 += e[j + 1];
+    for (int j = 0; j < N / 2; ++j) {
+      const float2 t = fma2(pair_to_float2(x[j]), splat(1.4426950408889634f), splat(neg_m_log2e));
+      const float2 v = make_float2(ex2_approx(t.x), ex2_approx(t.y));
+      e[2 * j] = v.x;
+      e[2 * j + 1] = v.y;
+      s = add2(s, v);
     }
-    return s0 + s1;
+    return s.x + s.y;
   }
   static __device__ __forceinline__ void unpack(const uint4 &raw, float (&f)[N]) {
     const T1 *x = reinterpret_cast<const T1 *>(&raw);
@@ -110,12 +118,9 @@ template <> struct RowVec<__half> : RowVec16<__half2, __half> {
     const __half2 *w = reinterpret_cast<const __half2 *>(mul);
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      float a = e[2 * j] * r, b = e[2 * j + 1] * r;
-      if (mul) {
-        a *= __low2float(w[j]);
-        b *= __high2float(w[j]);
-      }
-      o[j] = __floats2half2_rn(a, b);
+      float2 v = mul2(make_float2(e[2 * j], e[2 * j + 1]), splat(r));
+      if (mul) v = mul2(v, pair_to_float2(w[j]));
+      o[j] = __floats2half2_rn(v.x, v.y);
     }
     return out;
   }
@@ -127,12 +132,9 @@ template <> struct RowVec<__nv_bfloat16> : RowVec16<__nv_bfloat162, __nv_bfloat1
     const __nv_bfloat162 *w = reinterpret_cast<const __nv_bfloat162 *>(mul);
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      float a = e[2 * j] * r, b = e[2 * j + 1] * r;
-      if (mul) {
-        a *= __low2float(w[j]);
-        b *= __high2float(w[j]);
-      }
-      o[j] = __floats2bfloat162_rn(a, b);
+      float2 v = mul2(make_float2(e[2 * j], e[2 * j + 1]), splat(r));
+      if (mul) v = mul2(v, pair_to_float2(w[j]));
+      o[j] = __floats2bfloat162_rn(v.x, v.y);
     }
     return out;
   }
