@@ -750,6 +750,63 @@ def bench_tp_mlp(torch, ops, dist, launches, peaks, source, collective, **option
     return out
 
 
+def bench_allreduce(torch, dist, launches=30):
+    """The all-reduce kernels of the TP MLP alone: a [4096, 4096] float16 buffer in symmetric
+    memory reduced in place to bfloat16 (the kernels' own barriers on), and a quarter of it;
+    CUDA-event pairs around single launches, mean, max over ranks.  NCCL's all-reduce of the
+    same bytes is timed beside them."""
+    import ctypes
+    import torch.distributed as tdist
+    import torch.distributed._symmetric_memory as symm_mem
+    from compiler_b200.runtime import abi
+    lib = abi.lib()
+    world, rank = dist.world, dist.rank
+    count = MLP_M * MLP_HIDDEN
+    group = tdist.group.WORLD
+    buf = symm_mem.empty((MLP_M, MLP_HIDDEN), dtype=torch.float16, device="cuda")
+    handle = symm_mem.rendezvous(buf, group=group)
+    pad = symm_mem.empty((lib.b200_signal_pad_bytes() // 4,), dtype=torch.int32, device="cuda")
+    pad.zero_()
+    pad_handle = symm_mem.rendezvous(pad, group=group)
+    torch.cuda.synchronize()
+    pad_handle.barrier(channel=0)
+    torch.cuda.synchronize()
+    pointers = ctypes.c_void_p * world
+    pads = pointers(*[int(p) for p in pad_handle.buffer_ptrs])
+    ptrs = pointers(*[int(p) for p in handle.buffer_ptrs])
+    f16, bf16 = abi.DTYPE_CODES["float16"], abi.DTYPE_CODES["bfloat16"]
+    stream = torch.cuda.current_stream().cuda_stream
+    epoch = [0]
+    multicast = int(getattr(handle, "multicast_ptr", 0) or 0)
+
+    def peer_loads(n):
+        epoch[0] += 1
+        abi.check(lib.b200_peer_allreduce(ptrs, f16, ptrs, bf16, 0, n, rank, world, pads,
+                                          epoch[0], 0, stream))
+
+    def in_switch(n):
+        epoch[0] += 1
+        abi.check(lib.b200_multimem_allreduce(multicast, f16, multicast, bf16, 0, n, rank, world,
+                                              pads, epoch[0], 0, stream))
+
+    out = {"protocol": "event pairs around single launches, mean of 30, max over ranks",
+           "buffer": "[4096, 4096] float16 partials -> bfloat16 result, in place"}
+    kernels = [("peer_loads", peer_loads)] + ([("in_switch", in_switch)] if multicast else [])
+    for name, fn in kernels:
+        for label, n in (("32MiB_us", count), ("8MiB_us", count // 4)):
+            buf.normal_()
+            torch.cuda.synchronize()
+            dist.barrier()
+            _, launch_ms, _ = time_event_pairs(torch, dist, lambda i: fn(n), launches, 5)
+            abi.check(lib.b200_last_device_status(stream))
+            out.setdefault(name, {})[label] = round(dist.max(launch_ms) * 1e3, 2)
+    x = torch.randn((MLP_M, MLP_HIDDEN), device="cuda").to(torch.bfloat16)
+    _, launch_ms, _ = time_event_pairs(torch, dist, lambda i: tdist.all_reduce(x), launches, 5)
+    out["nccl_bf16"] = {"32MiB_us": round(dist.max(launch_ms) * 1e3, 2)}
+    out["gpu_launches"] = len(kernels) * 2 * (launches + 5)
+    return out
+
+
 # --------------------------------------------------------------------------- siblings
 def bench_siblings(torch, ops, peaks):
     """Rates of the sibling kernels at sizes well above the L2: four rotating buffer sets,
@@ -974,7 +1031,7 @@ def main():
     parser.add_argument("--impl", default="native", choices=["native", "reference"])
     parser.add_argument("--ops", default="all",
                         help="comma list of extra operators: softmax_unmasked,rmsnorm,gemm,"
-                             "gemm_ragged,attention,attention_decode,siblings,tp_mlp,none,all")
+                             "gemm_ragged,attention,attention_decode,siblings,tp_mlp,allreduce,none,all")
     args = parser.parse_args()
     if args.impl == "reference":
         reference_arm(args)
@@ -1062,6 +1119,11 @@ def main():
                                                collective, **options)
                 except Exception as exc:  # noqa: BLE001 - symmetric memory / NVLS may be unavailable
                     extras[key] = {"unavailable": f"{type(exc).__name__}: {exc}"[:300]}
+    if want("allreduce") and dist.enabled:
+        try:
+            extras["allreduce"] = bench_allreduce(torch, dist)
+        except Exception as exc:  # noqa: BLE001 - symmetric memory may be unavailable
+            extras["allreduce"] = {"unavailable": f"{type(exc).__name__}: {exc}"[:300]}
     if want("siblings") and not dist.enabled:
         extras["siblings"] = bench_siblings(torch, ops, peaks)
 
