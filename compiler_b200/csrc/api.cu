@@ -141,6 +141,7 @@ extern "C" int b200_stream_create(void **out) {
 extern "C" int b200_stream_destroy(void *stream) {
   if (stream != nullptr) {
     b200::release_stream_scratch((cudaStream_t)stream);
+    b200::release_gemm_scratch((cudaStream_t)stream);
     B200_CUDA_OK(cudaStreamDestroy((cudaStream_t)stream));
   }
   return B200_OK;

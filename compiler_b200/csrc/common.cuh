@@ -76,6 +76,8 @@ unsigned int *device_status_word();  // device pointer for the current device
 
 // Frees the decode-attention scratch kept for (current device, stream), if any (attn_decode.cu).
 void release_stream_scratch(cudaStream_t stream);
+// Frees the GEMM's split-wave scratch kept for (current device, stream), if any (gemm_sm100.cu).
+void release_gemm_scratch(cudaStream_t stream);
 
 inline int sm_count() {
   static int cached[64] = {0};

@@ -255,7 +255,10 @@ def test_strided_matmul_with_transposed_b_through_the_device(device):
 # tiles, a ragged edge in both directions, a last row block whose second CTA is all padding,
 # and K shorter / longer than the six-stage ring.
 PAIR_SHAPES = [(3328, 3072, 192), (3300, 3096, 200), (3072 + 100, 3328, 64), (2048, 5000, 520),
-               (2050, 4872, 8)]
+               (2050, 4872, 8),
+               # more tiles than SM pairs with a short last wave: its tiles are cut along K
+               # (4 and 2 slices; whole and ragged K, a ragged last row block)
+               (4096, 4864, 4096), (4096, 4096, 2048), (4000, 4870, 4200)]
 
 
 @pytest.mark.parametrize("dtype,act", [("bfloat16", "gelu_tanh"), ("float16", "none"),
