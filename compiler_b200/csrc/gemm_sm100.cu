@@ -653,8 +653,14 @@ struct PairWork {
 
 // The it-th unit of the pair that starts at tile `first` and strides by `step`: whole tiles
 // while they last, then at most one slice of a split tile.
+template <bool TAIL>
 __device__ __forceinline__ bool pair_work(const Params &p, int it, int first, int step,
                                           int num_tiles, int num_kb, PairWork &w) {
+  if constexpr (!TAIL) {
+    w.tile = first + it * step;
+    w.kb0 = 0; w.kb1 = num_kb; w.slice = 0; w.slices = 1; w.tail = 0;
+    return w.tile < num_tiles;
+  }
   const int main_tiles = num_tiles - p.tail_tiles;
   const int tile = first + it * step;
   if (tile < main_tiles) {
@@ -684,7 +690,9 @@ constexpr int PAIR_B_STAGE_BYTES = 2 * B_BOX_BYTES;                      // 16 K
 constexpr int PAIR_STAGE_BYTES = A_STAGE_BYTES + PAIR_B_STAGE_BYTES;     // 32 KiB per CTA
 constexpr int PAIR_SMEM_BYTES = PAIR_STAGES * PAIR_STAGE_BYTES + 1024 + 256;
 
-template <typename OutT, bool DUAL>
+// TAIL: the instantiation that can cut the last partial wave along K (Params::tail_*); the
+// plain one carries none of that code, so launches without a split run the kernel as it was.
+template <typename OutT, bool DUAL, bool TAIL>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
                  const __grid_constant__ CUtensorMap tm_b,
@@ -754,7 +762,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
       uint32_t issued_mask = 0, issued_parity = 0;
       bool ok = true;
       PairWork w;
-      for (int it = 0; ok && pair_work(p, it, first_tile, tile_step, num_tiles, num_kb, w); ++it) {
+      for (int it = 0; ok && pair_work<TAIL>(p, it, first_tile, tile_step, num_tiles, num_kb, w); ++it) {
         int mp, nb;
         tile_coords(w.tile, m_pairs, n_blocks, group_pairs, mp, nb);
         const int row0 = (mp * 2 + (int)rank) * BM;
@@ -802,7 +810,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
       const uint32_t b_kstep = p.b_kstep;
       const uint32_t peer_bar0 = map_to_cta(bar0, 1);
       PairWork w;
-      for (int it = 0; ok && pair_work(p, it, first_tile, tile_step, num_tiles, num_kb, w); ++it) {
+      for (int it = 0; ok && pair_work<TAIL>(p, it, first_tile, tile_step, num_tiles, num_kb, w); ++it) {
         if (!wait_all(acc_empty_bar(acc), acc_phase ^ 1u, 2)) { ok = false; break; }
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
@@ -844,7 +852,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
     OutT *c = reinterpret_cast<OutT *>(p.c);
     const uint32_t acc_empty0 = map_to_cta(acc_empty_bar(0), 0);
     PairWork w;
-    for (int it = 0; ok && pair_work(p, it, first_tile, tile_step, num_tiles, num_kb, w); ++it) {
+    for (int it = 0; ok && pair_work<TAIL>(p, it, first_tile, tile_step, num_tiles, num_kb, w); ++it) {
       int mp, nb;
       tile_coords(w.tile, m_pairs, n_blocks, group_pairs, mp, nb);
       if (!__all_sync(0xffffffffu, mbar_wait(acc_full_bar(acc), acc_phase, ctx, 4))) {
@@ -857,7 +865,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
       const bool row_ok = row < p.M;
       const uint32_t t_row = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(acc * BN);
       int c0 = 0, c1 = DUAL ? BN / 64 : BN / 32;  // output chunks this pair finishes
-      if (w.slices > 1) {
+      if (TAIL && w.slices > 1) {
         // A slice of a split tile.  Output chunks [c0, c1) are this slice's; with two B
         // operands output chunk c is accumulator chunks c (x Wg) and c + 4 (x Wu).  Partials
         // travel as [column][row] floats: 32 consecutive rows per warp access.
@@ -945,7 +953,10 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
       }
       const int col_base = nb * TILE_N;
       const float row_mul = (p.row_scale != nullptr && row_ok) ? p.row_scale[row] : 1.0f;
-      run_epilogue<OutT, DUAL>(t_row, p, crow, row, col_base, row_ok, row_mul, c0, c1);
+      if constexpr (TAIL)
+        run_epilogue<OutT, DUAL>(t_row, p, crow, row, col_base, row_ok, row_mul, c0, c1);
+      else
+        run_epilogue<OutT, DUAL>(t_row, p, crow, row, col_base, row_ok, row_mul);
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(acc_empty0 + 8u * (uint32_t)acc);
@@ -1129,10 +1140,13 @@ static int launch_pair(const CUtensorMap &ta, const CUtensorMap &tb, const CUten
   static int max_clusters[64] = {0};
   int dev = 0;
   B200_CUDA_OK(cudaGetDevice(&dev));
-  auto kernel = gemm_pair_kernel<OutT, DUAL>;
+  auto kernel = gemm_pair_kernel<OutT, DUAL, false>;
+  auto kernel_tail = gemm_pair_kernel<OutT, DUAL, true>;
   if (dev >= 64) return fail(B200_RESOURCE, "device index %d out of range", dev);
   if (!configured[dev]) {
     B200_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      PAIR_SMEM_BYTES));
+    B200_CUDA_OK(cudaFuncSetAttribute(kernel_tail, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       PAIR_SMEM_BYTES));
     cudaLaunchConfig_t probe = {};
     probe.gridDim = dim3((unsigned)sm_count());
@@ -1167,6 +1181,10 @@ static int launch_pair(const CUtensorMap &ta, const CUtensorMap &tb, const CUten
   if (tail_env != 0 && tiles > clusters && rest > 0 && p.act != kActGroupNormMin) {
     int slices = rest * 4 <= clusters ? 4 : (rest * 2 <= clusters ? 2 : 1);
     while (slices > 1 && num_kb / slices < kTailMinKb) slices /= 2;
+    // the instantiation with the split runs its whole waves about 2 % slower (measured): with
+    // many waves that costs more than the shorter last wave gives back
+    const int waves = tiles / clusters;
+    if ((slices == 4 && waves > 24) || (slices == 2 && waves > 12)) slices = 1;
     TailScratch scratch;
     if (slices >= 2 && tail_scratch(max_clusters[dev], stream, scratch)) {
       p.tail_tiles = rest;
@@ -1175,7 +1193,10 @@ static int launch_pair(const CUtensorMap &ta, const CUtensorMap &tb, const CUten
       p.tail_flags = scratch.flags;
     }
   }
-  kernel<<<2 * clusters, THREADS, PAIR_SMEM_BYTES, stream>>>(ta, tb, tb2, p);
+  if (p.tail_tiles > 0)
+    kernel_tail<<<2 * clusters, THREADS, PAIR_SMEM_BYTES, stream>>>(ta, tb, tb2, p);
+  else
+    kernel<<<2 * clusters, THREADS, PAIR_SMEM_BYTES, stream>>>(ta, tb, tb2, p);
   B200_CUDA_OK(cudaGetLastError());
   return B200_OK;
 }
