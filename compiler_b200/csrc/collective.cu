@@ -135,7 +135,7 @@ __device__ __forceinline__ bool cross_rank_barrier(const SignalPads &pads, int r
 }
 
 // vecs output vectors (8 elements each) of this rank's share; the share starts at element
-// `first` of both buffers.  Four reduced loads in flight per thread, then the four stores.
+// `first` of both buffers.  Eight reduced loads in flight per thread, then the eight stores.
 template <int IN, int OUT, bool SYNC>
 __global__ void __launch_bounds__(kThreads)
 multimem_allreduce_kernel(const uint8_t *in_mc, uint8_t *out_mc, int64_t first, int64_t vecs,
@@ -144,7 +144,7 @@ multimem_allreduce_kernel(const uint8_t *in_mc, uint8_t *out_mc, int64_t first, 
   if constexpr (SYNC) {
     if (!cross_rank_barrier(pads, rank, world, 0, epoch, status, kSiteStart)) return;
   }
-  constexpr int U = 4;
+  constexpr int U = 8;
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < vecs; i += stride * U) {
     uint4 v[U];
@@ -166,7 +166,7 @@ struct RankPointers {
   void *ptr[8];
 };
 
-template <typename TIn, typename TOut, bool SYNC>
+template <typename TIn, typename TOut, bool SYNC, int U, int W>
 __global__ void __launch_bounds__(kThreads)
 peer_allreduce_kernel(RankPointers partial, RankPointers out, int64_t first, int64_t vecs,
                       SignalPads pads, int rank, int world, uint32_t epoch,
@@ -175,16 +175,18 @@ peer_allreduce_kernel(RankPointers partial, RankPointers out, int64_t first, int
     if (!cross_rank_barrier(pads, rank, world, 0, epoch, status, kSiteStart)) return;
   }
   constexpr int N = 8;  // elements per 16-byte vector of a 16-bit type
-  constexpr int U = 2;  // vectors per thread and step: 2 x world peer loads in flight
+  // U vectors per thread and step, W >= world: U x W = 16 peer loads of 16 bytes in flight per
+  // thread (the links' latency, not the adder, sets the pace: 2 ranks moved 16 MiB each way in
+  // 53 us with four loads in flight per thread)
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < vecs; i += stride * U) {
-    vec16<TIn> v[U][8];
+    vec16<TIn> v[U][W];
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       const int64_t e = first + (i + u * stride) * N;
       if (i + u * stride < vecs) {
 #pragma unroll
-        for (int w = 0; w < 8; ++w)
+        for (int w = 0; w < W; ++w)
           if (w < world) v[u][w].raw = ld_stream16(static_cast<const TIn *>(partial.ptr[w]) + e);
       }
     }
@@ -196,7 +198,7 @@ peer_allreduce_kernel(RankPointers partial, RankPointers out, int64_t first, int
 #pragma unroll
       for (int j = 0; j < N; ++j) acc[j] = 0.f;
 #pragma unroll
-      for (int w = 0; w < 8; ++w)
+      for (int w = 0; w < W; ++w)
         if (w < world) {
 #pragma unroll
           for (int j = 0; j < N; ++j) acc[j] += io<TIn>::load(v[u][w].e[j]);
@@ -205,18 +207,18 @@ peer_allreduce_kernel(RankPointers partial, RankPointers out, int64_t first, int
 #pragma unroll
       for (int j = 0; j < N; ++j) r.e[j] = io<TOut>::store(acc[j]);
 #pragma unroll
-      for (int w = 0; w < 8; ++w)
+      for (int w = 0; w < W; ++w)
         if (w < world) *reinterpret_cast<uint4 *>(static_cast<TOut *>(out.ptr[w]) + e) = r.raw;
     }
   }
   if constexpr (SYNC) cross_rank_barrier(pads, rank, world, 1, epoch, status, kSiteEnd);
 }
 
-template <typename TIn, typename TOut>
-int launch_peer(const RankPointers &partial, const RankPointers &out, int64_t first, int64_t vecs,
-                const SignalPads &pads, bool sync, int rank, int world, uint32_t epoch, int ctas,
-                cudaStream_t s) {
-  int64_t blocks = (vecs + kThreads * 2 - 1) / (kThreads * 2);
+template <typename TIn, typename TOut, int U, int W>
+int launch_peer_u(const RankPointers &partial, const RankPointers &out, int64_t first,
+                  int64_t vecs, const SignalPads &pads, bool sync, int rank, int world,
+                  uint32_t epoch, int ctas, cudaStream_t s) {
+  int64_t blocks = (vecs + kThreads * U - 1) / (kThreads * U);
   int64_t cap = ctas > 0 ? ctas : (int64_t)sm_count() * 2;
   if (cap > kMaxCtas) cap = kMaxCtas;
   if (blocks > cap) blocks = cap;
@@ -224,19 +226,34 @@ int launch_peer(const RankPointers &partial, const RankPointers &out, int64_t fi
   unsigned int *status = device_status_word();
   if (status == nullptr) return fail(B200_RESOURCE, "no status word on this device");
   if (sync)
-    peer_allreduce_kernel<TIn, TOut, true><<<(unsigned)blocks, kThreads, 0, s>>>(
+    peer_allreduce_kernel<TIn, TOut, true, U, W><<<(unsigned)blocks, kThreads, 0, s>>>(
         partial, out, first, vecs, pads, rank, world, epoch, status);
   else
-    peer_allreduce_kernel<TIn, TOut, false><<<(unsigned)blocks, kThreads, 0, s>>>(
+    peer_allreduce_kernel<TIn, TOut, false, U, W><<<(unsigned)blocks, kThreads, 0, s>>>(
         partial, out, first, vecs, pads, rank, world, epoch, status);
   B200_CUDA_OK(cudaGetLastError());
   return B200_OK;
 }
 
+// sixteen 16-byte loads in flight per thread whatever the number of ranks
+template <typename TIn, typename TOut>
+int launch_peer(const RankPointers &partial, const RankPointers &out, int64_t first, int64_t vecs,
+                const SignalPads &pads, bool sync, int rank, int world, uint32_t epoch, int ctas,
+                cudaStream_t s) {
+  if (world <= 2)
+    return launch_peer_u<TIn, TOut, 8, 2>(partial, out, first, vecs, pads, sync, rank, world, epoch,
+                                       ctas, s);
+  if (world <= 4)
+    return launch_peer_u<TIn, TOut, 4, 4>(partial, out, first, vecs, pads, sync, rank, world, epoch,
+                                       ctas, s);
+  return launch_peer_u<TIn, TOut, 2, 8>(partial, out, first, vecs, pads, sync, rank, world, epoch,
+                                     ctas, s);
+}
+
 template <int IN, int OUT>
 int launch(const void *in_mc, void *out_mc, int64_t first, int64_t vecs, const SignalPads &pads,
            bool sync, int rank, int world, uint32_t epoch, int ctas, cudaStream_t s) {
-  int64_t blocks = (vecs + kThreads * 4 - 1) / (kThreads * 4);
+  int64_t blocks = (vecs + kThreads * 8 - 1) / (kThreads * 8);
   int64_t cap = ctas > 0 ? ctas : (int64_t)sm_count() * 2;
   if (cap > kMaxCtas) cap = kMaxCtas;
   if (blocks > cap) blocks = cap;
