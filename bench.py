@@ -699,8 +699,10 @@ def bench_tp_mlp(torch, ops, dist, launches, peaks, source, collective, **option
               "rows": len(rows), "checked_on": "every rank's own output",
               "oracle": "swiglu_mlp_ref (float64, unsharded), rtol = atol = 2e-2"}
 
-    # ---- per-phase times: events after each phase of `launches` further passes
-    names, samples = [], []
+    # ---- per-phase times: events after each phase of `launches` further passes, enqueued
+    # back to back (no synchronisation between passes, so that the host's launch latency is
+    # hidden behind the device's work as it is in the timed loop) and read at the end
+    passes = []
     for _ in range(launches):
         marks = [torch.cuda.Event(enable_timing=True)]
         marks[0].record()
@@ -713,9 +715,10 @@ def bench_tp_mlp(torch, ops, dist, launches, peaks, source, collective, **option
             labels.append(name)
 
         mlp.forward(x, y_buf, mark=mark)
-        torch.cuda.synchronize()
-        names = labels
-        samples.append([marks[i].elapsed_time(marks[i + 1]) for i in range(len(labels))])
+        passes.append((marks, labels))
+    torch.cuda.synchronize()
+    names = passes[-1][1]
+    samples = [[m[i].elapsed_time(m[i + 1]) for i in range(len(names))] for m, _ in passes[1:]]
     phases = {name: round(dist.max(float(np.mean([s[i] for s in samples]))), 5)
               for i, name in enumerate(names)}
 
