@@ -274,8 +274,8 @@ softmax_rows_kernel(const T *__restrict__ x, const T *__restrict__ mul, T *__res
 // two for the form with the multiplier, which also holds that row's vectors.
 constexpr int stream_ctas_per_sm(int mode) { return mode == kSoftmaxMul ? 2 : 3; }
 
-template <typename T, int G, int VPT, int MODE>
-__global__ void __launch_bounds__(kRowThreads, stream_ctas_per_sm(MODE))
+template <typename T, int G, int VPT, int MODE, bool LEAN = false>
+__global__ void __launch_bounds__(kRowThreads, LEAN ? 4 : stream_ctas_per_sm(MODE))
 softmax_stream_kernel(const T *__restrict__ x, const T *__restrict__ mul, T *__restrict__ y,
                       int64_t rows, int cols, int mask_kind, int64_t row_offset) {
   static_assert(G <= kRowThreads, "one row per group of at most a CTA");
@@ -333,7 +333,9 @@ softmax_stream_kernel(const T *__restrict__ x, const T *__restrict__ mul, T *__r
       }
     }
 
-    float e[VPT][N];
+    // LEAN: the exponentials are taken again for the store instead of being kept (16 packed
+    // registers per row in flight instead of 48): four CTAs per SM
+    float e[LEAN ? 1 : VPT][N];
     float m = -INFINITY;
     bool bad = false;
     T *yrow = y + row * (int64_t)cols;
@@ -374,7 +376,7 @@ softmax_stream_kernel(const T *__restrict__ x, const T *__restrict__ mul, T *__r
             s += e[i][j];
           }
         } else {
-          s += V::exps(raw[i], m, neg_m_log2e, e[i]);
+          s += V::exps(raw[i], m, neg_m_log2e, e[LEAN ? 0 : i]);
         }
       }
     }
@@ -386,9 +388,12 @@ softmax_stream_kernel(const T *__restrict__ x, const T *__restrict__ mul, T *__r
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
       const int v = lane + i * G;
-      if (v < kept_vec)
+      if (v < kept_vec) {
+        if constexpr (LEAN) V::exps(raw[i], m, neg_m_log2e, e[0]);
         st_stream16(yrow + (int64_t)v * N,
-                    V::scaled(e[i], r, MODE == kSoftmaxMul ? &w[MODE == kSoftmaxMul ? i : 0] : nullptr));
+                    V::scaled(e[LEAN ? 0 : i], r,
+                              MODE == kSoftmaxMul ? &w[MODE == kSoftmaxMul ? i : 0] : nullptr));
+      }
     }
   }
 }
@@ -425,13 +430,25 @@ static void launch_rows(const b200_tensor *x, const b200_tensor *mul, b200_tenso
   const int64_t rows = x->shape[0];
   const unsigned grid = (unsigned)((rows + kRowsPerCta - 1) / kRowsPerCta);
   if constexpr (G <= kRowThreads) {
-    // unmasked rows, more than one wave of resident CTAs: the pipelined persistent form
-    // (B200OPS_SOFTMAX_STREAM=0 keeps the one-row-per-group kernel, 2 sends masked rows
-    // through the pipelined one as well).  Masked rows stay with
-    // the one-row-per-group kernel: their cost is the stores, rows differ in length, and
-    // eight small CTAs per SM measured faster there (39.0 against 42.8 us at 16384 x 4000).
+    // more than one wave of resident CTAs: the pipelined persistent forms
+    // (B200OPS_SOFTMAX_STREAM=0 keeps the one-row-per-group kernel for everything, 2 sends
+    // masked rows through the pipelined form of the unmasked ones, 3 sends unmasked rows
+    // through the lean form of the masked ones)
     static const int choice =
         getenv("B200OPS_SOFTMAX_STREAM") ? atoi(getenv("B200OPS_SOFTMAX_STREAM")) : 1;
+    // masked rows, more than one wave: the pipelined form that takes the exponentials again
+    // for the store (63 registers, four CTAs per SM): 34.6 us at 16384 x 4000 fp16 against
+    // 38.6 us for the one-row-per-group kernel and 42.8 us for the pipelined form that keeps
+    // them (B200OPS_SOFTMAX_STREAM=0 / 2 select those)
+    if constexpr (MODE == kSoftmaxPlain) {
+      if ((choice == 3 || (choice == 1 && mask_kind == B200_MASK_CAUSAL_MOD)) &&
+          grid > (unsigned)(sm_count() * 4)) {
+        softmax_stream_kernel<T, G, VPT, MODE, true><<<sm_count() * 4, kRowThreads, 0, stream>>>(
+            (const T *)x->data, nullptr, (T *)y->data, rows, (int)x->shape[1], mask_kind,
+            row_offset);
+        return;
+      }
+    }
     const unsigned resident = (unsigned)(sm_count() * stream_ctas_per_sm(MODE));
     const bool take = choice == 2 || (choice == 1 && mask_kind == B200_MASK_NONE);
     if (take && grid > resident) {
