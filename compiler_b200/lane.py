@@ -257,7 +257,7 @@ def main(argv=None) -> int:
     parser.add_argument("--llc-bytes", type=int, default=None)
     parser.add_argument("--multiple", type=int, default=DEFAULT_MULTIPLE)
     parser.add_argument("--group", default=None, help="memory | reduction | compute")
-    parser.add_argument("--only", default=None)
+    parser.add_argument("--only", default=None, help="comma list of entry ids")
     parser.add_argument("--seed", type=int, default=20261008)
     parser.add_argument("--no-verify", action="store_true")
     parser.add_argument("--verify-only", action="store_true")
@@ -274,7 +274,7 @@ def main(argv=None) -> int:
     workload = json.loads(workload_path.read_text())
     entries = [e for e in workload["entries"]
                if (not args.group or e["class"] == args.group)
-               and (args.only is None or e["id"] == args.only)]
+               and (args.only is None or e["id"] in args.only.split(","))]
     if args.list or not args.corpus:
         llc = args.llc_bytes or (128 << 20)
         for entry in entries:

@@ -72,6 +72,20 @@ class FakeLibrary:
     def b200_status_string(self, status):
         return b"fake"
 
+    def b200_device_query(self, device, props):
+        out = props._obj
+        out.name, out.sm_count, out.l2_bytes, out.hbm_bytes = b"fake", 148, 1 << 20, 1 << 34
+        out.cc_major, out.cc_minor = 10, 0
+        return abi.OK
+
+    def b200_event_create(self, out):
+        out._obj.value = 1
+        return abi.OK
+
+    def b200_event_elapsed_ms(self, start, stop, ms):
+        ms._obj.value = 0.01
+        return abi.OK
+
     def b200_last_error(self):
         return b""
 
@@ -171,3 +185,23 @@ def test_reference_make_device_builds_this_device(fake_library):
     for method in ("alloc", "upload", "download", "pointer", "synchronize", "launch",
                    "upload_aliased", "compare", "timer", "properties", "release"):
         assert callable(getattr(device, method)), method
+
+
+def test_lane_with_the_corpus_stages_through_the_reference(fake_library, tmp_path, monkeypatch):
+    """``python -m compiler_b200.lane --corpus ...``: an entry of the workload file is built by
+    the corpus's own loader and staged and launched by the corpus's own
+    ``opslib.device.stage_case`` (not this package's stand-in) on ``B200Device``; with the
+    recording library every entry must bind, launch and be sampled.  Three entries here (all
+    twenty-odd pass the same way; the case builders' float64 oracles take minutes)."""
+    import json
+    root, _, _ = _reference_modules()
+    from compiler_b200 import lane
+    monkeypatch.setattr(lane, "_stage_case", lane._stage_case)   # main() swaps it: put it back
+    code = lane.main(["--corpus", str(root / "ops"), "--out-dir", str(tmp_path), "--no-verify",
+                      "--multiple", "1", "--min-samples", "3", "--samples", "3", "--only",
+                      "fast_rms_layernorm,softmax,swiglu_fwd"])
+    assert lane._stage_case.__module__ == "opslib.device"
+    report = json.loads((tmp_path / "BENCH_REPORT.json").read_text())
+    failed = [(e["id"], e.get("error")) for e in report["entries"] if e["status"] != "PASS"]
+    assert code == 0 and not failed, failed
+    assert len(report["entries"]) == 3 and fake_library.calls
