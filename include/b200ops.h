@@ -114,9 +114,11 @@ int b200_last_device_status(void *stream);
  * program per process).  `stream` must come from b200_stream_create.  Other streams join a
  * capture through b200_event_record on the capturing stream + b200_stream_wait_event on
  * theirs, and must be joined back the same way before the capture ends.  Every operator
- * used inside a capture must have run once on this device before -- b200_attn_decode once on
- * the capturing stream -- (first calls set kernel attributes and allocate the status word /
- * scratch, which a capture forbids); the entry
+ * used inside a capture must have run once on this device before -- b200_attn_decode and the
+ * GEMM entry points once on the capturing stream, with the shapes of the capture: their scratch
+ * (decode: softmax states of rows cut between CTAs; GEMM: partial sums of a last wave that is
+ * split along K) is kept per stream -- (first calls set kernel attributes and allocate the
+ * status word / scratch, which a capture forbids); the entry
  * points that synchronise (memcpy with NULL stream, *_sync, b200_last_device_status,
  * b200_allclose_f32) cannot be captured. */
 int b200_stream_wait_event(void *stream, void *event);
