@@ -141,7 +141,11 @@ int b200_wait_selftest(unsigned int *gave_up, void *stream);
  *      ops/harness/opslib/devices/cuda.py:71-123, 138-167, 186-262) -------- */
 int b200_malloc(void **out, size_t bytes);
 int b200_free(void *ptr);
-int b200_malloc_host(void **out, size_t bytes); /* pinned */
+/* Page-locked host memory.  It is addressable from the device under unified addressing, so
+ * the row-wise and elementwise entry points also take it as operand memory: the kernel then
+ * loads and stores over PCIe with no staging copy (tensor-map operands -- GEMM, attention --
+ * must be in device memory). */
+int b200_malloc_host(void **out, size_t bytes);
 int b200_free_host(void *ptr);
 int b200_memcpy_h2d(void *dst, const void *src, size_t bytes, void *stream);
 int b200_memcpy_d2h(void *dst, const void *src, size_t bytes, void *stream);

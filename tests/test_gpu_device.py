@@ -101,16 +101,23 @@ def test_pinned_transfers(device):
     assert isinstance(buf, B200Buffer)
 
 
-def test_row_pipeline_matches_single_launch(device):
-    """Chunked, multi-stream host-to-host softmax gives the same bytes as one launch."""
+@pytest.mark.parametrize("schedule", ["in_step", "staged", "direct"])
+def test_row_pipeline_matches_single_launch(device, schedule):
+    """Host-to-host softmax gives the same bytes as one launch on device buffers: whole chunks
+    spread over streams, a stream per stage (events between the stages), and one launch on
+    the page-locked host buffers themselves; a second run over the same buffers gives them
+    again."""
     from compiler_b200 import pipeline
     rows, cols = 1000, 4000
     rng = np.random.default_rng(5)
     hx = device.pinned_empty((rows, cols), np.float16)
     hx.array[...] = (rng.standard_normal((rows, cols)) * 2).astype(np.float16)
     hy = device.pinned_empty((rows, cols), np.float16)
-    pipe = pipeline.RowPipeline(device, rows, cols, "float16", chunks=7, streams=3)
+    pipe = pipeline.RowPipeline(device, rows, cols, "float16", chunks=7, streams=3,
+                                staged=schedule == "staged", direct=schedule == "direct")
     out = pipeline.masked_softmax_host(pipe, hx, hy, row_offset=123).copy()
+    hy.array[...] = 0
+    assert np.array_equal(pipeline.masked_softmax_host(pipe, hx, hy, row_offset=123), out)
     pipe.close()
     dx, dy = device.upload(hx.array), device.alloc((rows, cols), "float16")
     ops.softmax(dx, dy, causal_mod=True, row_offset=123)

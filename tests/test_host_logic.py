@@ -285,3 +285,119 @@ def test_graph_capture_reports_a_failed_end(monkeypatch):
         with graph.capture(stream):
             pass
     stream.close()
+
+
+class _FakePipelineLib:
+    """Host memory as "device memory"; numbered stream / event handles; a log of every call."""
+
+    def __init__(self):
+        self.log, self._blocks, self._next = [], {}, 100
+
+    def _handle(self, out, kind):
+        self._next += 1
+        out._obj.value = self._next
+        self.log.append((kind + "_create", self._next))
+        return 0
+
+    def b200_stream_create(self, out):
+        return self._handle(out, "stream")
+
+    def b200_event_create(self, out):
+        return self._handle(out, "event")
+
+    def b200_malloc(self, out, nbytes):
+        import ctypes
+        block = ctypes.create_string_buffer(int(nbytes) + 64)
+        out._obj.value = (ctypes.addressof(block) + 63) & ~63
+        self._blocks[out._obj.value] = block
+        return 0
+
+    b200_malloc_host = b200_malloc
+
+    def _copy(self, name):
+        def copy(dst, src, nbytes, stream):
+            import ctypes
+            ctypes.memmove(int(dst), int(src), int(nbytes))
+            self.log.append((name, stream.value))
+            return 0
+        return copy
+
+    def __getattr__(self, name):
+        if name in ("b200_memcpy_h2d", "b200_memcpy_d2h"):
+            return self._copy(name[5:])
+        if not name.startswith("b200_"):
+            raise AttributeError(name)
+
+        def call(*args):
+            self.log.append((name[5:],) + tuple(getattr(a, "value", a) for a in args))
+            return 0
+        return call
+
+
+@pytest.mark.parametrize("schedule", ["staged", "in_step", "direct"])
+def test_row_pipeline_schedules(monkeypatch, schedule):
+    """The host-to-host row pipeline: with a stream per stage every inbound copy is on the first
+    stream, every launch on the second after its chunk's copy event, every outbound copy on the
+    third after its chunk's launch event; with whole chunks per stream a chunk's three steps
+    share one stream; ``direct`` is one launch on the host buffers and no copy.  Every way
+    every row arrives."""
+    import ctypes
+    from compiler_b200 import pipeline
+    from compiler_b200.device import PinnedArray
+    from compiler_b200.runtime import abi
+
+    fake = _FakePipelineLib()
+    monkeypatch.setattr(abi, "lib", lambda: fake)
+
+    class Device:
+        def alloc(self, shape, dtype):
+            from compiler_b200.device import B200Buffer
+            out = ctypes.c_void_p()
+            nbytes = int(np.prod(shape)) * 2
+            fake.b200_malloc(ctypes.byref(out), nbytes)
+            return B200Buffer(out.value, dtype, tuple(shape), nbytes, owner=False)
+
+        def release(self, buffers):
+            pass
+
+    rows, cols = 50, 16
+    hx, hy = PinnedArray((rows, cols), np.float16), PinnedArray((rows, cols), np.float16)
+    hx.array[...] = np.arange(rows * cols, dtype=np.float32).reshape(rows, cols) % 251
+    hy.array[...] = -1
+    staged = schedule == "staged"
+    pipe = pipeline.RowPipeline(Device(), rows, cols, "float16", chunks=4, streams=2,
+                                staged=staged, direct=schedule == "direct")
+    launches = []
+
+    def launch(x, y, first_row, stream):
+        ctypes.memmove(y.ptr, x.ptr, x.shape[0] * cols * 2)   # the "operator": a copy
+        launches.append((first_row, x.shape[0], stream))
+        fake.log.append(("launch", stream))
+
+    out = pipe.run(launch, hx, hy)
+    assert np.array_equal(out, hx.array)
+    assert [l[0] for l in launches] == [lo for lo, _ in pipe.chunks]
+    assert sum(l[1] for l in launches) == rows
+    streams = [h for kind, h in (e[:2] for e in fake.log) if kind == "stream_create"]
+    steps = [e for e in fake.log if e[0] in ("memcpy_h2d", "launch", "memcpy_d2h")]
+    if schedule == "direct":
+        assert [e[0] for e in steps] == ["launch"] and launches == [(0, rows, streams[0])]
+        assert (launches[0][2], pipe.x) == (streams[0], None)
+    elif staged:
+        assert len(streams) == 3
+        by_kind = {"memcpy_h2d": streams[0], "launch": streams[1], "memcpy_d2h": streams[2]}
+        assert all(e[1] == by_kind[e[0]] for e in steps)
+        waits = [e for e in fake.log if e[0] == "stream_wait_event"]
+        records = [e for e in fake.log if e[0] == "event_record"]
+        assert len(waits) == len(records) == 2 * len(pipe.chunks)
+        # every wait names an event recorded just before it, on the stage before
+        for (_, event, on), (_, stream, waited) in zip(records, waits):
+            assert waited == event and streams.index(stream) == streams.index(on) + 1
+        assert fake.log[-1] == ("stream_sync", streams[2])
+    else:
+        assert len(streams) == 2
+        for i in range(len(pipe.chunks)):
+            assert {e[1] for e in steps[3 * i:3 * i + 3]} == {streams[i % 2]}
+    pipe.close()
+    hx.free()
+    hy.free()
