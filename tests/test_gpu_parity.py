@@ -911,6 +911,45 @@ def test_scatter_gemm_and_reduce_emulated_ranks(device, world, staged):
                        name=f"rank {r}")
 
 
+@pytest.mark.parametrize("partial_dtype", ["float16", "bfloat16"])
+@pytest.mark.parametrize("world", [2, 3, 4, 8])
+def test_peer_load_allreduce_emulated_ranks(device, world, partial_dtype):
+    """``b200_peer_allreduce`` on ONE GPU: every "rank" is a pair of local buffers and the
+    launches run one after the other without the cross-rank barriers (no signal pads).  Rank r
+    sums its share of every rank's partial in fp32, in rank order, and stores the rounded sums
+    into every rank's output (even ranks on 3 CTAs, so each CTA walks many steps): after all
+    ranks have run, every output holds the sum over the whole range -- bit for bit the fp32
+    sum in rank order rounded once -- and nothing outside [offset, offset + count) is touched.  World sizes 2 / 3-4 / 8 take the three unrollings of
+    the kernel (8 x 2, 4 x 4, 2 x 8 loads in flight)."""
+    import ctypes
+    lib = abi.lib()
+    offset, count = 64, 8 * world * 40_001   # a ragged last step of every unrolling
+    total = offset + count + 40
+    rng = np.random.default_rng(77 + world)
+    partials = [_host(rng.standard_normal(total) * 3, partial_dtype) for _ in range(world)]
+    d_partials = [_up(device, p, partial_dtype) for p in partials]
+    outputs = [_poisoned(device, (total,), "bfloat16") for _ in range(world)]
+    ptrs = ctypes.c_void_p * world
+    partial_ptrs, output_ptrs = ptrs(*[p.ptr for p in d_partials]), ptrs(*[o.ptr for o in outputs])
+    for r in range(world):
+        abi.check(lib.b200_peer_allreduce(partial_ptrs, abi.DTYPE_CODES[partial_dtype],
+                                          output_ptrs, abi.DTYPE_CODES["bfloat16"], offset, count,
+                                          r, world, None, 0, 0 if r % 2 else 3, device.stream))
+    device.check_status()
+    acc = np.zeros(count, np.float32)
+    for p in partials:                              # fp32, rank order: what the kernel does
+        acc = acc + np.asarray(p[offset:offset + count], np.float32)
+    expect = oracle.to_storage(acc, "bfloat16")
+    for r in range(world):
+        got = np.asarray(device.download(outputs[r]), np.float32)
+        assert np.array_equal(got[offset:offset + count], np.asarray(expect, np.float32)), r
+        assert np.all(got[:offset] == POISON) and np.all(got[offset + count:] == POISON), r
+    # a count the ranks cannot share in whole vectors never reaches the device
+    assert lib.b200_peer_allreduce(partial_ptrs, abi.DTYPE_CODES[partial_dtype], output_ptrs,
+                                   abi.DTYPE_CODES["bfloat16"], 0, 8 * world + 8, 0, world, None,
+                                   0, 0, device.stream) == abi.REJECTED
+
+
 def test_scatter_gemm_rejections(device):
     import ctypes
     lib = abi.lib()
