@@ -778,7 +778,11 @@ def bench_tp_mlp(torch, ops, dist, launches, peaks, source, collective, **option
         "pull": "float16 partials in symmetric memory, summed by plain peer loads and "
                 "broadcast by peer stores, barriers inside the kernel"
                 + (f"; the MLP runs in {mlp.row_splits} blocks of rows, a block's all-reduce "
-                   "beside both projections of the next block" if mlp.row_splits > 1 else ""),
+                   "beside both projections of the next block" if mlp.row_splits > 1 else "")
+                + (f"; the all-reduce kernel is the programmatic dependent of the "
+                   f"down-projection and takes each of {mlp.overlap_blocks} blocks of rows as "
+                   "soon as every rank's GEMM has counted it complete"
+                   if mlp.overlap_blocks > 1 else ""),
         "none": "one GPU: the two GEMMs alone (anchor of the strong-scaling curve)",
     }
     partial_bytes = MLP_M * MLP_HIDDEN * (4 if collective == "nccl"
@@ -1156,6 +1160,7 @@ def main():
                     ("tp_mlp", "nccl", {}), ("tp_mlp_peer", "peer", {}),
                     ("tp_mlp_nvls", "nvls", {}), ("tp_mlp_pull", "pull", {}),
                     ("tp_mlp_pull_row_blocks", "pull", {"row_splits": 2, "comm_ctas": 74}),
+                    ("tp_mlp_pull_beside_gemm", "pull", {"overlap_blocks": 4}),
                     ("tp_mlp_nvls_f32", "nvls", {"partial_dtype": torch.float32})):
                 if collective == "peer" and MLP_M % (128 * dist.world):
                     continue

@@ -33,6 +33,17 @@ __device__ __forceinline__ uint64_t timer_ns() {
 __device__ __forceinline__ void st_release_sys(uint32_t *p, uint32_t v) {
   asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
+__device__ __forceinline__ uint32_t ld_acquire_gpu_u32(const unsigned int *p) {
+  uint32_t v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint4 ld_relaxed_sys16(const void *p) {
+  uint4 v;
+  asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
 __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t *p) {
   uint32_t v;
   asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
@@ -166,18 +177,17 @@ struct RankPointers {
   void *ptr[8];
 };
 
-template <typename TIn, typename TOut, bool SYNC, int U, int W>
-__global__ void __launch_bounds__(kThreads)
-peer_allreduce_kernel(RankPointers partial, RankPointers out, int64_t first, int64_t vecs,
-                      SignalPads pads, int rank, int world, uint32_t epoch,
-                      unsigned int *status) {
-  if constexpr (SYNC) {
-    if (!cross_rank_barrier(pads, rank, world, 0, epoch, status, kSiteStart)) return;
-  }
+// This rank's share: vecs output vectors of 8 elements from element `first` on.  U vectors per
+// thread and step, W >= world: U x W = 16 peer loads of 16 bytes in flight per thread (the
+// links' latency, not the adder, sets the pace: 2 ranks moved 16 MiB each way in 53 us with
+// four loads in flight per thread).  COHERENT: the partials were written while this kernel was
+// already running (by the GEMM it was launched behind), so the loads must not take the
+// read-only path.
+template <typename TIn, typename TOut, int U, int W, bool COHERENT>
+__device__ __forceinline__ void peer_reduce_share(const RankPointers &partial,
+                                                  const RankPointers &out, int64_t first,
+                                                  int64_t vecs, int world) {
   constexpr int N = 8;  // elements per 16-byte vector of a 16-bit type
-  // U vectors per thread and step, W >= world: U x W = 16 peer loads of 16 bytes in flight per
-  // thread (the links' latency, not the adder, sets the pace: 2 ranks moved 16 MiB each way in
-  // 53 us with four loads in flight per thread)
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < vecs; i += stride * U) {
     vec16<TIn> v[U][W];
@@ -187,7 +197,10 @@ peer_allreduce_kernel(RankPointers partial, RankPointers out, int64_t first, int
       if (i + u * stride < vecs) {
 #pragma unroll
         for (int w = 0; w < W; ++w)
-          if (w < world) v[u][w].raw = ld_stream16(static_cast<const TIn *>(partial.ptr[w]) + e);
+          if (w < world) {
+            const TIn *src = static_cast<const TIn *>(partial.ptr[w]) + e;
+            v[u][w].raw = COHERENT ? ld_relaxed_sys16(src) : ld_stream16(src);
+          }
       }
     }
 #pragma unroll
@@ -211,7 +224,100 @@ peer_allreduce_kernel(RankPointers partial, RankPointers out, int64_t first, int
         if (w < world) *reinterpret_cast<uint4 *>(static_cast<TOut *>(out.ptr[w]) + e) = r.raw;
     }
   }
+}
+
+template <typename TIn, typename TOut, bool SYNC, int U, int W>
+__global__ void __launch_bounds__(kThreads)
+peer_allreduce_kernel(RankPointers partial, RankPointers out, int64_t first, int64_t vecs,
+                      SignalPads pads, int rank, int world, uint32_t epoch,
+                      unsigned int *status) {
+  if constexpr (SYNC) {
+    if (!cross_rank_barrier(pads, rank, world, 0, epoch, status, kSiteStart)) return;
+  }
+  peer_reduce_share<TIn, TOut, U, W, false>(partial, out, first, vecs, world);
   if constexpr (SYNC) cross_rank_barrier(pads, rank, world, 1, epoch, status, kSiteEnd);
+}
+
+// The same all-reduce, block of rows by block of rows, BESIDE the GEMM that produces the
+// partial.  The kernel is launched as the programmatic dependent of that GEMM, so its CTAs (128
+// threads: they fit beside a persistent GEMM CTA) become resident while the GEMM runs.  For
+// every block of rows: thread 0 waits until this rank's GEMM has counted the block complete
+// (progress[b] >= target[b]; the GEMM is resident and waits for nothing of this kernel), the
+// CTA signals and awaits its peers' CTAs for this block (epoch0 + b), and reduces this rank's
+// share of the block.  So only the last block's all-reduce is left when the GEMM ends.  At the
+// end: the closing cross-rank barrier, the counters put back to zero by the last CTA to have
+// read them, and griddepcontrol.wait, so that this kernel does not end before the GEMM has.
+// Every wait is bounded; a wait that runs out records B200_TIMEOUT and the rest is skipped.
+constexpr int kBlockThreads = 128;
+constexpr int kMaxBlocks = 16;
+constexpr uint32_t kSiteProgress = 42;
+struct BlockPlan {
+  unsigned int target[kMaxBlocks];
+};
+
+template <typename TIn, typename TOut, bool SYNC, int U, int W>
+__global__ void __launch_bounds__(kBlockThreads, 4)  // at most 128 registers: see the launcher
+peer_allreduce_blocks_kernel(const __grid_constant__ RankPointers partial,
+                             const __grid_constant__ RankPointers out, int64_t total,
+                             int64_t block_elems, int nblocks, unsigned int *progress,
+                             const __grid_constant__ BlockPlan plan,
+                             const __grid_constant__ SignalPads pads, int rank, int world,
+                             uint32_t epoch0, unsigned int *status) {
+  __shared__ int ready;
+  bool alive = true;
+  // trace (CTA 0, thread 0; 64-bit nanoseconds after the counters): [0] entry of the kernel,
+  // [1 + 2b] block b counted complete by this rank's GEMM, [2 + 2b] block b reduced
+  unsigned long long *trace =
+      progress != nullptr && blockIdx.x == 0 && threadIdx.x == 0
+          ? reinterpret_cast<unsigned long long *>(progress + kMaxBlocks + 2) : nullptr;
+  if (trace != nullptr) trace[0] = timer_ns();
+  for (int b = 0; b < nblocks && alive; ++b) {
+    if (progress != nullptr) {
+      if (threadIdx.x == 0) {
+        int ok = 1;
+        const uint64_t t0 = timer_ns();
+        while (ld_acquire_gpu_u32(progress + b) < plan.target[b]) {
+          __nanosleep(200);
+          if (timer_ns() - t0 > kFlagWaitNs) {
+            atomicOr(status, (unsigned)B200_TIMEOUT | (kSiteProgress << 8));
+            ok = 0;
+            break;
+          }
+        }
+        ready = ok;
+        if (trace != nullptr) trace[1 + 2 * b] = timer_ns();
+      }
+      __syncthreads();
+      alive = ready != 0;
+      __syncthreads();  // everyone has read `ready` before thread 0 writes it again
+    }
+    if constexpr (SYNC) {
+      if (alive && !cross_rank_barrier(pads, rank, world, 0, epoch0 + (uint32_t)b, status,
+                                       kSiteStart))
+        alive = false;
+    }
+    if (alive) {
+      const int64_t lo = (int64_t)b * block_elems;
+      const int64_t n = total - lo < block_elems ? total - lo : block_elems;
+      const int64_t share = n / world;
+      peer_reduce_share<TIn, TOut, U, W, true>(partial, out, lo + (int64_t)rank * share,
+                                               share / 8, world);
+      if (trace != nullptr) trace[2 + 2 * b] = timer_ns();
+    }
+  }
+  if constexpr (SYNC) {
+    if (alive)
+      cross_rank_barrier(pads, rank, world, 1, epoch0 + (uint32_t)(nblocks - 1), status, kSiteEnd);
+  }
+  if (progress != nullptr && threadIdx.x == 0) {
+    unsigned int *done = progress + kMaxBlocks;
+    if (atomicAdd(done, 1u) == gridDim.x - 1) {
+      for (int b = 0; b < nblocks; ++b) progress[b] = 0u;
+      *done = 0u;
+      __threadfence();
+    }
+  }
+  asm volatile("griddepcontrol.wait;" ::: "memory");
 }
 
 template <typename TIn, typename TOut, int U, int W>
@@ -248,6 +354,72 @@ int launch_peer(const RankPointers &partial, const RankPointers &out, int64_t fi
                                        ctas, s);
   return launch_peer_u<TIn, TOut, 2, 8>(partial, out, first, vecs, pads, sync, rank, world, epoch,
                                      ctas, s);
+}
+
+template <typename TIn, typename TOut, int U, int W>
+int launch_peer_blocks_u(const RankPointers &partial, const RankPointers &out, int64_t total,
+                         int64_t block_elems, int nblocks, unsigned int *progress,
+                         const BlockPlan &plan, const SignalPads &pads, bool sync, int rank,
+                         int world, uint32_t epoch0, int ctas, cudaStream_t s) {
+  // One CTA of 128 threads and at most 128 registers (16 K registers) fits beside every
+  // instantiation of the CTA-pair GEMM (up to 248 registers x 192 threads of an SM's 64 K).
+  // Eight 16-byte loads in flight per thread: 128 CTAs hold 2 MiB in flight, more than the
+  // links' latency x bandwidth.
+  int64_t blocks = ctas > 0 ? ctas : 128;
+  if (blocks > kMaxCtas) blocks = kMaxCtas;
+  unsigned int *status = device_status_word();
+  if (status == nullptr) return fail(B200_RESOURCE, "no status word on this device");
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3((unsigned)blocks);
+  config.blockDim = dim3(kBlockThreads);
+  config.dynamicSmemBytes = 0;
+  config.stream = s;
+  // programmatic dependent of the kernel before it on the stream: may start once that kernel's
+  // CTAs have released their dependents (a kernel that never does releases them at its end)
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr.val.programmaticStreamSerializationAllowed = progress != nullptr ? 1 : 0;
+  config.attrs = &attr;
+  config.numAttrs = 1;
+  // the same shared-memory carve-out as the GEMM it runs beside (which takes the maximum): an
+  // SM does not hold CTAs of kernels that ask for different splits of its L1 / shared memory
+  static bool configured = false;
+  if (!configured) {
+    B200_CUDA_OK(cudaFuncSetAttribute(peer_allreduce_blocks_kernel<TIn, TOut, true, U, W>,
+                                      cudaFuncAttributePreferredSharedMemoryCarveout,
+                                      cudaSharedmemCarveoutMaxShared));
+    B200_CUDA_OK(cudaFuncSetAttribute(peer_allreduce_blocks_kernel<TIn, TOut, false, U, W>,
+                                      cudaFuncAttributePreferredSharedMemoryCarveout,
+                                      cudaSharedmemCarveoutMaxShared));
+    configured = true;
+  }
+  if (sync)
+    B200_CUDA_OK(cudaLaunchKernelEx(&config, peer_allreduce_blocks_kernel<TIn, TOut, true, U, W>,
+                                    partial, out, total, block_elems, nblocks, progress, plan,
+                                    pads, rank, world, epoch0, status));
+  else
+    B200_CUDA_OK(cudaLaunchKernelEx(&config, peer_allreduce_blocks_kernel<TIn, TOut, false, U, W>,
+                                    partial, out, total, block_elems, nblocks, progress, plan,
+                                    pads, rank, world, epoch0, status));
+  return B200_OK;
+}
+
+template <typename TIn, typename TOut>
+int launch_peer_blocks(const RankPointers &partial, const RankPointers &out, int64_t total,
+                       int64_t block_elems, int nblocks, unsigned int *progress,
+                       const BlockPlan &plan, const SignalPads &pads, bool sync, int rank,
+                       int world, uint32_t epoch0, int ctas, cudaStream_t s) {
+  if (world <= 2)
+    return launch_peer_blocks_u<TIn, TOut, 4, 2>(partial, out, total, block_elems, nblocks,
+                                                 progress, plan, pads, sync, rank, world, epoch0,
+                                                 ctas, s);
+  if (world <= 4)
+    return launch_peer_blocks_u<TIn, TOut, 2, 4>(partial, out, total, block_elems, nblocks,
+                                                 progress, plan, pads, sync, rank, world, epoch0,
+                                                 ctas, s);
+  return launch_peer_blocks_u<TIn, TOut, 1, 8>(partial, out, total, block_elems, nblocks,
+                                               progress, plan, pads, sync, rank, world, epoch0,
+                                               ctas, s);
 }
 
 template <int IN, int OUT>
@@ -373,4 +545,65 @@ extern "C" int b200_peer_allreduce(void *const *partial_rank, uint32_t in_dtype,
   if (in_dtype == B200_DTYPE_BFLOAT16) B200_PAR(__nv_bfloat16, __half);
   B200_PAR(__half, __half);
 #undef B200_PAR
+}
+
+extern "C" int b200_peer_allreduce_blocks(void *const *partial_rank, uint32_t in_dtype,
+                                          void *const *out_rank, uint32_t out_dtype,
+                                          int64_t total, int64_t block_elems,
+                                          unsigned int *progress, const unsigned int *targets,
+                                          int rank, int world, void *const *signal_pads,
+                                          uint32_t epoch0, int ctas, void *stream) {
+  using namespace b200;
+  if (partial_rank == nullptr || out_rank == nullptr) return fail(B200_USAGE, "null argument");
+  B200_REQUIRE((in_dtype == B200_DTYPE_BFLOAT16 || in_dtype == B200_DTYPE_FLOAT16) &&
+               (out_dtype == B200_DTYPE_BFLOAT16 || out_dtype == B200_DTYPE_FLOAT16),
+               "partials and result are f16 or bf16");
+  B200_REQUIRE(world >= 1 && world <= 8 && rank >= 0 && rank < world,
+               "rank %d / world %d out of range", rank, world);
+  B200_REQUIRE(total > 0 && block_elems > 0 && block_elems % (8 * world) == 0 &&
+               total % (8 * world) == 0,
+               "total and block size / world must be multiples of 8 elements");
+  const int64_t nblocks = (total + block_elems - 1) / block_elems;
+  B200_REQUIRE(nblocks <= kMaxBlocks, "%lld blocks, at most %d", (long long)nblocks, kMaxBlocks);
+  B200_REQUIRE((progress == nullptr) == (targets == nullptr),
+               "progress counters and their targets come together");
+  B200_REQUIRE(progress == nullptr || (uintptr_t)progress % 4 == 0, "progress is unaligned");
+  RankPointers partial, out;
+  SignalPads pads;
+  BlockPlan plan;
+  for (int k = 0; k < 8; ++k) partial.ptr[k] = out.ptr[k] = nullptr, pads.pad[k] = nullptr;
+  for (int b = 0; b < kMaxBlocks; ++b) plan.target[b] = targets && b < nblocks ? targets[b] : 0u;
+  for (int k = 0; k < world; ++k) {
+    B200_REQUIRE(partial_rank[k] != nullptr && (uintptr_t)partial_rank[k] % 16 == 0 &&
+                 out_rank[k] != nullptr && (uintptr_t)out_rank[k] % 16 == 0,
+                 "buffer of rank %d is null or unaligned", k);
+    partial.ptr[k] = partial_rank[k];
+    out.ptr[k] = out_rank[k];
+  }
+  const bool sync = signal_pads != nullptr;
+  if (sync) {
+    B200_REQUIRE(epoch0 != 0, "epoch 0 is the cleared state of the signal pads: start at 1");
+    for (int k = 0; k < world; ++k) {
+      B200_REQUIRE(signal_pads[k] != nullptr && (uintptr_t)signal_pads[k] % 4 == 0,
+                   "signal pad of rank %d is null or unaligned", k);
+      pads.pad[k] = static_cast<uint32_t *>(signal_pads[k]);
+    }
+  }
+  cudaStream_t s = (cudaStream_t)stream;
+#define B200_PARB(TIn, TOut)                                                                  \
+  return launch_peer_blocks<TIn, TOut>(partial, out, total, block_elems, (int)nblocks, progress, \
+                                       plan, pads, sync, rank, world, epoch0, ctas, s)
+  if (in_dtype == B200_DTYPE_BFLOAT16 && out_dtype == B200_DTYPE_BFLOAT16)
+    B200_PARB(__nv_bfloat16, __nv_bfloat16);
+  if (in_dtype == B200_DTYPE_FLOAT16 && out_dtype == B200_DTYPE_BFLOAT16)
+    B200_PARB(__half, __nv_bfloat16);
+  if (in_dtype == B200_DTYPE_BFLOAT16) B200_PARB(__nv_bfloat16, __half);
+  B200_PARB(__half, __half);
+#undef B200_PARB
+}
+
+// counters [kMaxBlocks], the count of CTAs that are done with them, one word of padding, and
+// the trace: 1 + 2 * kMaxBlocks 64-bit time stamps
+extern "C" int b200_progress_words(void) {
+  return b200::kMaxBlocks + 2 + 2 * (1 + 2 * b200::kMaxBlocks);
 }

@@ -18,6 +18,7 @@
 // no out-of-range address is ever formed.
 #include "sm100.cuh"
 
+#include <algorithm>
 #include <map>
 #include <mutex>
 
@@ -141,6 +142,24 @@ struct Params {
   int tail_slices;
   float *tail_ws;    // [tail_tiles][tail_slices][2 CTAs][256 columns][128 rows]
   unsigned int *tail_flags;  // [tail_tiles][2 CTAs][4 warps][arrived, done], zero between launches
+  // CTA-pair kernel, progress per raster group (a block of group_m x 128 rows of C): when
+  // `progress` is set every epilogue warp, after the stores of its part of a tile (fenced at
+  // system scope), adds one to progress[group of the tile].  A kernel launched behind this one
+  // as its programmatic dependent -- the all-reduce of the tensor-parallel MLP -- starts while
+  // this one runs and takes a block of rows as soon as the block's count is complete, instead
+  // of waiting for the last tile of the product.  The kernel also releases its dependents
+  // (griddepcontrol.launch_dependents) as soon as its CTAs are set up.
+  unsigned int *progress;
+};
+
+// What a launch with progress counters tells its caller (host memory): the count each block
+// of rows reaches when all its tiles are stored.
+struct Progress {
+  unsigned int *counters;   // device, one per block of rows, zero before the launch
+  int64_t rows_per_block;   // a multiple of 256
+  unsigned int *targets;    // host, [max_blocks]
+  int max_blocks;
+  int *blocks;              // host: number of blocks
 };
 
 __device__ __forceinline__ float gelu_tanh_fast(float z) {
@@ -692,8 +711,15 @@ constexpr int PAIR_SMEM_BYTES = PAIR_STAGES * PAIR_STAGE_BYTES + 1024 + 256;
 
 // TAIL: the instantiation that can cut the last partial wave along K (Params::tail_*); the
 // plain one carries none of that code, so launches without a split run the kernel as it was.
+// Registers: the 16-bit instantiations stay at 184 per thread (the split one is held there by
+// __maxnreg__, without spills), because that decides what can run BESIDE this kernel: the six
+// warps of a CTA sit on four SM sub-partitions of 16 K registers each, two of which hold two
+// of them, so a 128-thread CTA of another kernel (one warp per sub-partition) fits only while
+// 2 x this + its own registers per thread stay within 512.  Measured: beside the 248-register
+// form a 128-thread kernel on a second stream started only when this one had ended; beside the
+// 184-register form it ran concurrently (the all-reduce of the tensor-parallel MLP does).
 template <typename OutT, bool DUAL, bool TAIL>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
+__global__ void __cluster_dims__(2, 1, 1) __maxnreg__(TAIL ? 184 : 255)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
                  const __grid_constant__ CUtensorMap tm_b,
                  const __grid_constant__ CUtensorMap tm_b2, const Params p) {
@@ -753,6 +779,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
   cluster_wait();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  // a programmatic dependent may start now: it reads nothing of this kernel's output before
+  // the progress counters say so
+  if (p.progress != nullptr) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
   if (warp == 4) {
     // ------------------------------------------------------------ producer (both CTAs)
@@ -907,33 +936,49 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
         if (!__all_sync(0xffffffffu, arrived)) {
           if (lane == 0) atomicOr(p.status, (unsigned)B200_TIMEOUT | (5u << 8));
         } else {
+          // Two slices: 32 columns at a time, one array of the other slice's partials; four
+          // slices: 16 columns at a time, three arrays -- 64 values live either way (the
+          // register count of this instantiation decides what fits beside it on an SM).
+          // This slice's own partial first, then the others' in slice order: a fixed order, so
+          // repeated launches give the same bits.
 #pragma unroll 1
           for (int a = 0; a < BN / 32; ++a) {
             if (!mine(a)) continue;
-            uint32_t r[32];
-            tmem_ld_32x32b_x32(t_row + (uint32_t)(a * 32), r);
-            float other[3][32];  // every load is issued before the first sum needs one
+            if (S == 2) {
+              uint32_t r[32];
+              tmem_ld_32x32b_x32(t_row + (uint32_t)(a * 32), r);
+              const float *src = tile_ws + (size_t)(1 - w.slice) * 2 * part;
+              float other[32];  // every load is issued before the first sum needs one
 #pragma unroll
-            for (int k = 0; k < 3; ++k) {
-              const int sl = k + (k >= w.slice ? 1 : 0);  // the other slices, in slice order
-              if (k < S - 1) {
+              for (int j = 0; j < 32; ++j) other[j] = __ldcg(src + (size_t)(a * 32 + j) * BM);
+              tmem_ld_wait();
+#pragma unroll
+              for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) + other[j]);
+              tmem_st_32x32b_x32(t_row + (uint32_t)(a * 32), r);
+              continue;
+            }
+#pragma unroll 1
+            for (int h = 0; h < 2; ++h) {
+              const int col = a * 32 + h * 16;
+              uint32_t r[16];
+              tmem_ld_32x32b_x16(t_row + (uint32_t)col, r);
+              float other[3][16];
+#pragma unroll
+              for (int k = 0; k < 3; ++k) {
+                const int sl = k + (k >= w.slice ? 1 : 0);  // the other slices, in slice order
                 const float *src = tile_ws + (size_t)sl * 2 * part;
 #pragma unroll
-                for (int j = 0; j < 32; ++j) other[k][j] = __ldcg(src + (size_t)(a * 32 + j) * BM);
+                for (int j = 0; j < 16; ++j) other[k][j] = __ldcg(src + (size_t)(col + j) * BM);
               }
-            }
-            tmem_ld_wait();
-            // this slice's own partial, then the others' in slice order: a fixed order, so
-            // repeated launches give the same bits
+              tmem_ld_wait();
 #pragma unroll
-            for (int k = 0; k < 3; ++k) {
-              if (k < S - 1) {
+              for (int k = 0; k < 3; ++k) {
 #pragma unroll
-                for (int j = 0; j < 32; ++j)
+                for (int j = 0; j < 16; ++j)
                   r[j] = __float_as_uint(__uint_as_float(r[j]) + other[k][j]);
               }
+              tmem_st_32x32b_x16(t_row + (uint32_t)col, r);
             }
-            tmem_st_32x32b_x32(t_row + (uint32_t)(a * 32), r);
           }
           tmem_st_wait();
         }
@@ -961,6 +1006,12 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(acc_empty0 + 8u * (uint32_t)acc);
       if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+      if (p.progress != nullptr) {
+        // this warp's rows of the tile are stored: visible to every GPU before the count is
+        __threadfence_system();
+        __syncwarp();
+        if (lane == 0) atomicAdd(p.progress + mp / group_pairs, 1u);
+      }
     }
   }
 
@@ -1134,8 +1185,10 @@ static bool tail_scratch(int pairs, cudaStream_t stream, TailScratch &out) {
 
 template <typename OutT, bool DUAL>
 static int launch_pair(const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap &tb2,
-                       const Params &p_in, cudaStream_t stream) {
+                       const Params &p_in, cudaStream_t stream,
+                       const Progress *progress = nullptr) {
   Params p = p_in;
+  p.progress = nullptr;
   static bool configured[64] = {false};
   static int max_clusters[64] = {0};
   int dev = 0;
@@ -1192,6 +1245,25 @@ static int launch_pair(const CUtensorMap &ta, const CUtensorMap &tb, const CUten
       p.tail_ws = scratch.ws;
       p.tail_flags = scratch.flags;
     }
+  }
+  if (progress != nullptr) {
+    // per block of rows (= raster group): eight epilogue warps count once per whole tile and
+    // once per slice of a split tile; the split tiles are the last ones in raster order
+    const int m_pairs = (p.M + 2 * BM - 1) / (2 * BM);
+    const int n_blocks = (p.N + TILE_N - 1) / TILE_N;
+    const int group_pairs = (p.group_m + 1) / 2;
+    const int groups = (m_pairs + group_pairs - 1) / group_pairs;
+    if (groups > progress->max_blocks)
+      return fail(B200_REJECTED, "%d blocks of rows, room for %d", groups, progress->max_blocks);
+    for (int g = 0; g < groups; ++g) {
+      const int pairs = std::min(group_pairs, m_pairs - g * group_pairs);
+      const int first = g * group_pairs * n_blocks, last = first + pairs * n_blocks;
+      const int split_from = std::max(first, tiles - p.tail_tiles);
+      const int split = last > split_from ? last - split_from : 0;
+      progress->targets[g] = 8u * (unsigned)((last - first - split) + split * p.tail_slices);
+    }
+    *progress->blocks = groups;
+    p.progress = progress->counters;
   }
   if (p.tail_tiles > 0)
     kernel_tail<<<2 * clusters, THREADS, PAIR_SMEM_BYTES, stream>>>(ta, tb, tb2, p);
@@ -1269,7 +1341,8 @@ static int gemm_impl(const b200_tensor *a, const b200_tensor *b, const b200_tens
                      const b200_tensor *bias, b200_tensor *c, int act, void *stream,
                      const b200::gemm::Scatter *scatter, bool b_rows_are_n = false,
                      const float *row_scale = nullptr,
-                     const b200::gemm::GroupNormMin *gn = nullptr) {
+                     const b200::gemm::GroupNormMin *gn = nullptr,
+                     const b200::gemm::Progress *progress = nullptr) {
   using namespace b200;
   using namespace b200::gemm;
   int st;
@@ -1451,6 +1524,16 @@ static int gemm_impl(const b200_tensor *a, const b200_tensor *b, const b200_tens
     p.group_m = group_env > 0 ? group_env : (m_blocks + groups - 1) / (groups > 0 ? groups : 1);
     if (p.group_m < 1) p.group_m = 1;
   }
+  p.progress = nullptr;
+  if (progress != nullptr) {
+    B200_REQUIRE(use_pair && b2 == nullptr && scatter == nullptr,
+                 "progress counters exist on the CTA-pair kernel with one B operand");
+    B200_REQUIRE(progress->counters != nullptr && progress->targets != nullptr &&
+                 progress->blocks != nullptr && progress->rows_per_block > 0 &&
+                 progress->rows_per_block % (2 * BM) == 0,
+                 "rows per block must be a positive multiple of %d", 2 * BM);
+    p.group_m = (int)(progress->rows_per_block / BM);  // a block of rows is a raster group
+  }
   for (int r = 0; r < 8; ++r) p.c_rank[r] = nullptr;
   if (scatter != nullptr) {
     p.scatter_rows = (int)scatter->rows;
@@ -1471,12 +1554,12 @@ static int gemm_impl(const b200_tensor *a, const b200_tensor *b, const b200_tens
                                     b_rows_are_n ? 0 : 1);
     if (c->dtype == B200_DTYPE_FLOAT32)
       return dual ? launch_pair<float, true>(ta, tb, tb2, q, s)
-                  : launch_pair<float, false>(ta, tb, tb2, q, s);
+                  : launch_pair<float, false>(ta, tb, tb2, q, s, progress);
     if (c->dtype == B200_DTYPE_FLOAT16)
       return dual ? launch_pair<__half, true>(ta, tb, tb2, q, s)
-                  : launch_pair<__half, false>(ta, tb, tb2, q, s);
+                  : launch_pair<__half, false>(ta, tb, tb2, q, s, progress);
     return dual ? launch_pair<__nv_bfloat16, true>(ta, tb, tb2, q, s)
-                : launch_pair<__nv_bfloat16, false>(ta, tb, tb2, q, s);
+                : launch_pair<__nv_bfloat16, false>(ta, tb, tb2, q, s, progress);
   }
   if (c->dtype == B200_DTYPE_FLOAT32)
     return dual ? launch_tc<float, true>(ta, tb, tb2, p, s) : launch_tc<float, false>(ta, tb, tb2, p, s);
@@ -1509,6 +1592,18 @@ extern "C" int b200_gemm_scatter_rows(const b200_tensor *a, const b200_tensor *b
   if (world >= 1 && world <= 8 && slot >= 0 && slot < world) c.data = c_rank[slot];
   const gemm::Scatter scatter{c_rank, world, slot, rows_per_rank};
   return gemm_impl(a, b, nullptr, nullptr, &c, B200_ACT_NONE, stream, &scatter);
+}
+
+extern "C" int b200_gemm_progress(const b200_tensor *a, const b200_tensor *b, b200_tensor *c,
+                                  int64_t rows_per_block, unsigned int *counters,
+                                  unsigned int *targets, int max_blocks, int *blocks,
+                                  void *stream) {
+  using namespace b200;
+  if (counters == nullptr || targets == nullptr || blocks == nullptr || max_blocks < 1)
+    return fail(B200_USAGE, "null argument");
+  const gemm::Progress progress{counters, rows_per_block, targets, max_blocks, blocks};
+  return gemm_impl(a, b, nullptr, nullptr, c, B200_ACT_NONE, stream, nullptr, false, nullptr,
+                   nullptr, &progress);
 }
 
 extern "C" int b200_linear_log_softmax(const b200_tensor *x, const b200_tensor *w, b200_tensor *y,

@@ -66,6 +66,20 @@ def gemm(a, b, c, *, bias=None, act=abi.ACT_NONE, b2=None, stream=0):
                                            int(act), stream))
 
 
+def gemm_progress(a, b, c, rows_per_block, counters, *, stream=0):
+    """c = a @ b on the CTA-pair kernel with a progress counter per block of
+    ``rows_per_block`` rows of c (``counters``: device int32 array of
+    ``b200_progress_words()`` words, zero before the launch).  Returns the list of counts the
+    blocks reach -- what ``peer_allreduce_blocks`` waits for.  No reference counterpart."""
+    ad, bd, cd = _desc(a), _desc(b), _desc(c)
+    targets = (ctypes.c_uint32 * 16)()
+    blocks = ctypes.c_int(0)
+    abi.check(abi.lib().b200_gemm_progress(_ref(ad), _ref(bd), _ref(cd), int(rows_per_block),
+                                           counters.data_ptr(), targets, 16,
+                                           ctypes.byref(blocks), stream))
+    return [int(targets[i]) for i in range(blocks.value)]
+
+
 def linear(x, w, y, *, bias=None, act=abi.ACT_NONE, stream=0):
     """y = act(x @ w.T + bias) with the weight as [N, K] (a linear layer's layout; the
     transposed-B case of matmul_kernel's general strides, ops/suite/perf/matmul_triton2.py:27-30)."""

@@ -57,7 +57,8 @@ class TensorParallelMLP:
     kernels_per_forward = None  # set in __init__: 1 fused up-projection + one GEMM per chunk
 
     def __init__(self, wg, wu, wd, *, group=None, chunks=None, collective: str = "nccl",
-                 partial_dtype=None, comm_ctas: int = 0, row_splits: int = 1):
+                 partial_dtype=None, comm_ctas: int = 0, row_splits: int = 1,
+                 overlap_blocks: int = 1):
         """wg, wu: this rank's [hidden, ffn/tp] column shards; wd: its [ffn/tp, hidden] row
         shard (CUDA bf16/fp16 torch tensors, contiguous).
 
@@ -73,7 +74,12 @@ class TensorParallelMLP:
         the exact sum) -- or the weights' own type.  ``comm_ctas``: grid limit of the
         all-reduce kernel while it runs beside a GEMM (0 = default).  ``row_splits`` (nvls and
         pull paths): run the whole MLP in this many blocks of rows, the all-reduce of a
-        block's result on a second stream beside both projections of the next block."""
+        block's result on a second stream beside both projections of the next block.
+        ``overlap_blocks`` (pull path, more than 1): ONE down-projection launch that counts
+        its finished tiles per block of rows, and the all-reduce kernel launched behind it as
+        its programmatic dependent: it runs beside the GEMM and takes each block of rows as
+        soon as every rank has counted it complete, so only the last block's all-reduce is
+        left when the GEMM ends -- no second stream and no extra partial waves."""
         import torch
         self.torch = torch
         self.wg, self.wu, self.wd = wg, wu, wd
@@ -94,6 +100,10 @@ class TensorParallelMLP:
             raise ValueError(f"collective='{collective}' stages 16-bit partials")
         self.comm_ctas = int(comm_ctas)
         self.row_splits = max(1, int(row_splits))
+        self.overlap_blocks = max(1, int(overlap_blocks))
+        if self.overlap_blocks > 1 and collective != "pull":
+            raise ValueError("overlap_blocks needs collective='pull'")
+        self._progress = None
         self._epoch = 0
         self._comm_stream = None
         self._h = None
@@ -283,6 +293,27 @@ class TensorParallelMLP:
                   if ((c[1] - c[0]) * hidden) % (8 * world) == 0]
         if sum(hi - lo for lo, hi in chunks) != m:
             chunks = [(0, m)]
+        if self.overlap_blocks > 1 and x is None:
+            rows = max(256, (m // self.overlap_blocks) // 256 * 256)
+            if m % 256 == 0 and (rows * hidden) % (8 * world) == 0:
+                if self._progress is None:
+                    self._progress = torch.zeros((lib.b200_progress_words(),), device=out.device,
+                                                 dtype=torch.int32)
+                targets = ops.gemm_progress(self._h, self.wd, partial, rows, self._progress,
+                                            stream=stream)
+                target_array = (ctypes.c_uint32 * len(targets))(*targets)
+                epoch0 = self._epoch + 1
+                self._epoch += len(targets)
+                abi.check(lib.b200_peer_allreduce_blocks(
+                    partial_ptrs, in_code, out_ptrs, out_code, m * hidden, rows * hidden,
+                    self._progress.data_ptr(), target_array, rank, world, pads, epoch0,
+                    self.comm_ctas, stream))
+                mark("down_projection_with_the_all_reduce_beside_it")
+                if y is not None and y.data_ptr() != out.data_ptr():
+                    y.copy_(out)
+                    mark("copy_out")
+                    return y
+                return out
         overlapped = len(chunks) > 1
         reduce_stream = comm.cuda_stream if overlapped else stream
         for lo, hi in chunks:

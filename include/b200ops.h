@@ -364,6 +364,39 @@ int b200_peer_allreduce(void *const *partial_rank, uint32_t in_dtype, void *cons
                         uint32_t out_dtype, int64_t offset, int64_t count, int rank, int world,
                         void *const *signal_pads, uint32_t epoch, int ctas, void *stream);
 
+/* The product C = A B (B as [K,N], 16-bit operands, the CTA-pair kernel: at least one wave
+ * of 256 x 256 tiles) with PROGRESS COUNTERS, and the all-reduce that runs beside it: the
+ * merge of the tensor-parallel MLP overlapped with the down-projection that produces the
+ * partials, block of rows by block of rows.  No reference counterpart (the reference's
+ * workers meet at a stage barrier, a100c/plan/stages.py:278-316).
+ *
+ * b200_gemm_progress: rows of C in blocks of rows_per_block (a multiple of 256; a block is a
+ * raster group of the kernel, so the blocks finish in order).  counters: device memory of
+ * b200_progress_words() 32-bit words, zero before the first launch (the all-reduce below puts
+ * them back to zero).  Every epilogue warp adds one to its block's counter after its stores
+ * of a tile, fenced at system scope.  targets[b] (host, max_blocks entries) receives the count
+ * block b reaches; *blocks the number of blocks.  The kernel releases its programmatic
+ * dependents as soon as its CTAs are set up.  REJECTED for shapes the CTA-pair kernel does not
+ * take.
+ *
+ * b200_peer_allreduce_blocks: launched on the same stream directly behind it, as its
+ * programmatic dependent (CTAs of 128 threads that fit beside the GEMM's).  total elements in
+ * blocks of block_elems (= rows_per_block x row length; both multiples of 8 x world).  Per
+ * block: wait for progress[b] >= targets[b], cross-rank barrier with epoch0 + b (signal_pads
+ * as for b200_multimem_allreduce; the caller advances its epoch by the number of blocks), then
+ * this rank's share of the block as in b200_peer_allreduce.  Only the last block's all-reduce
+ * is left when the GEMM ends.  progress == NULL (then targets == NULL): no waiting on a
+ * producer, an ordinary launch.  Every wait is bounded (B200_TIMEOUT, sites 40 - 42). */
+int b200_gemm_progress(const b200_tensor *a, const b200_tensor *b, b200_tensor *c,
+                       int64_t rows_per_block, unsigned int *counters, unsigned int *targets,
+                       int max_blocks, int *blocks, void *stream);
+int b200_peer_allreduce_blocks(void *const *partial_rank, uint32_t in_dtype,
+                               void *const *out_rank, uint32_t out_dtype, int64_t total,
+                               int64_t block_elems, unsigned int *progress,
+                               const unsigned int *targets, int rank, int world,
+                               void *const *signal_pads, uint32_t epoch0, int ctas, void *stream);
+int b200_progress_words(void);
+
 /* out = x * sigmoid(x) * y elementwise.  Replaces swiglu_fwd_kernel
  * (ops/suite/perf/swiglu_fwd.py:18-36).  [rows, cols], unit column stride. */
 int b200_swiglu_fwd(const b200_tensor *x, const b200_tensor *y,

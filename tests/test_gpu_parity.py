@@ -950,6 +950,61 @@ def test_peer_load_allreduce_emulated_ranks(device, world, partial_dtype):
                                    0, 0, device.stream) == abi.REJECTED
 
 
+@pytest.mark.parametrize("shape,rows_per_block", [((4096, 4096, 2048), 1024),   # split last wave
+                                                   ((2048, 4096, 512), 512),     # whole tiles only
+                                                   ((4096, 2048, 1024), 768)])   # ragged last block
+def test_gemm_progress_feeds_the_allreduce_beside_it(device, shape, rows_per_block):
+    """``b200_gemm_progress`` + ``b200_peer_allreduce_blocks`` on one GPU (a world of one rank:
+    the "all-reduce" rounds the float16 partial into the bfloat16 result).  The all-reduce
+    kernel is launched behind the GEMM as its programmatic dependent and takes every block of
+    rows when the GEMM has counted it complete: the result must be the product, the counters
+    must be back at zero, and a second pair of launches must give the same bits."""
+    import ctypes
+    lib = abi.lib()
+    m, n, k = shape
+    rng = np.random.default_rng(sum(shape))
+    a = _host(rng.standard_normal((m, k)) / np.sqrt(k), "bfloat16")
+    b = _host(rng.standard_normal((k, n)), "bfloat16")
+    da, db = _up(device, a, "bfloat16"), _up(device, b, "bfloat16")
+    partial = _poisoned(device, (m, n), "float16")
+    out = _poisoned(device, (m, n), "bfloat16")
+    words = lib.b200_progress_words()
+    counters = device.upload(np.zeros(words, np.int32))
+    ta = abi.make_tensor(da.ptr, (m, k), "bfloat16")
+    tb = abi.make_tensor(db.ptr, (k, n), "bfloat16")
+    tc = abi.make_tensor(partial.ptr, (m, n), "float16")
+    partial_ptrs, out_ptrs = (ctypes.c_void_p * 1)(partial.ptr), (ctypes.c_void_p * 1)(out.ptr)
+    results = []
+    for _ in range(2):
+        targets = (ctypes.c_uint32 * 16)()
+        blocks = ctypes.c_int(0)
+        abi.check(lib.b200_gemm_progress(ctypes.byref(ta), ctypes.byref(tb), ctypes.byref(tc),
+                                         rows_per_block, counters.ptr, targets, 16,
+                                         ctypes.byref(blocks), device.stream))
+        assert blocks.value == -(-m // rows_per_block)
+        # eight epilogue warps per tile of 256 x 256, more where the last wave is split
+        tiles = [min(rows_per_block, m - g * rows_per_block) // 256 * (n // 256)
+                 for g in range(blocks.value)]
+        assert all(targets[g] >= 8 * tiles[g] for g in range(blocks.value))
+        assert sum(targets[g] == 8 * tiles[g] for g in range(blocks.value)) >= blocks.value - 1
+        abi.check(lib.b200_peer_allreduce_blocks(
+            partial_ptrs, abi.DTYPE_CODES["float16"], out_ptrs, abi.DTYPE_CODES["bfloat16"],
+            m * n, rows_per_block * n, counters.ptr, targets, 0, 1, None, 0, 0, device.stream))
+        device.check_status()
+        results.append(np.asarray(device.download(out), np.float32).copy())
+        # the counters and the count of CTAs done with them; time stamps follow them
+        assert not device.download(counters)[:17].any()
+    assert np.array_equal(results[0], results[1])
+    oracle.compare(results[0].astype(np.float64), oracle.matmul_ref(a, b), 2e-2, 2e-2)
+    # a shape below one wave of tile pairs has no CTA-pair kernel to count
+    small = abi.make_tensor(da.ptr, (256, k), "bfloat16")
+    small_c = abi.make_tensor(partial.ptr, (256, n), "float16")
+    targets, blocks = (ctypes.c_uint32 * 16)(), ctypes.c_int(0)
+    assert lib.b200_gemm_progress(ctypes.byref(small), ctypes.byref(tb), ctypes.byref(small_c), 256,
+                                  counters.ptr, targets, 16, ctypes.byref(blocks),
+                                  device.stream) == abi.REJECTED
+
+
 def test_scatter_gemm_rejections(device):
     import ctypes
     lib = abi.lib()
