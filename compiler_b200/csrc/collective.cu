@@ -361,11 +361,11 @@ int launch_peer_blocks_u(const RankPointers &partial, const RankPointers &out, i
                          int64_t block_elems, int nblocks, unsigned int *progress,
                          const BlockPlan &plan, const SignalPads &pads, bool sync, int rank,
                          int world, uint32_t epoch0, int ctas, cudaStream_t s) {
-  // One CTA of 128 threads and at most 128 registers (16 K registers) fits beside every
-  // instantiation of the CTA-pair GEMM (up to 248 registers x 192 threads of an SM's 64 K).
-  // Eight 16-byte loads in flight per thread: 128 CTAs hold 2 MiB in flight, more than the
-  // links' latency x bandwidth.
-  int64_t blocks = ctas > 0 ? ctas : 128;
+  // One CTA of 128 threads and at most 128 registers per SM: that fits beside the CTA-pair
+  // GEMM (an SM sub-partition's 16 K registers then hold two GEMM warps of 184 registers and
+  // one warp of this kernel).  Sixteen 16-byte loads in flight per thread: 148 CTAs hold
+  // 4.6 MiB in flight, more than the links' latency x bandwidth.
+  int64_t blocks = ctas > 0 ? ctas : sm_count();
   if (blocks > kMaxCtas) blocks = kMaxCtas;
   unsigned int *status = device_status_word();
   if (status == nullptr) return fail(B200_RESOURCE, "no status word on this device");
@@ -410,14 +410,14 @@ int launch_peer_blocks(const RankPointers &partial, const RankPointers &out, int
                        const BlockPlan &plan, const SignalPads &pads, bool sync, int rank,
                        int world, uint32_t epoch0, int ctas, cudaStream_t s) {
   if (world <= 2)
-    return launch_peer_blocks_u<TIn, TOut, 4, 2>(partial, out, total, block_elems, nblocks,
+    return launch_peer_blocks_u<TIn, TOut, 8, 2>(partial, out, total, block_elems, nblocks,
                                                  progress, plan, pads, sync, rank, world, epoch0,
                                                  ctas, s);
   if (world <= 4)
-    return launch_peer_blocks_u<TIn, TOut, 2, 4>(partial, out, total, block_elems, nblocks,
+    return launch_peer_blocks_u<TIn, TOut, 4, 4>(partial, out, total, block_elems, nblocks,
                                                  progress, plan, pads, sync, rank, world, epoch0,
                                                  ctas, s);
-  return launch_peer_blocks_u<TIn, TOut, 1, 8>(partial, out, total, block_elems, nblocks,
+  return launch_peer_blocks_u<TIn, TOut, 2, 8>(partial, out, total, block_elems, nblocks,
                                                progress, plan, pads, sync, rank, world, epoch0,
                                                ctas, s);
 }

@@ -80,6 +80,21 @@ def gemm_progress(a, b, c, rows_per_block, counters, *, stream=0):
     return [int(targets[i]) for i in range(blocks.value)]
 
 
+def peer_allreduce_blocks(partials, outs, total, block_elems, counters, targets, rank, world,
+                          *, in_dtype, out_dtype, signal_pads=None, epoch0=0, ctas=0, stream=0):
+    """The all-reduce that runs beside ``gemm_progress`` (launch it directly behind it on the
+    same stream).  ``partials`` / ``outs``: one device address per rank; ``counters`` /
+    ``targets``: what ``gemm_progress`` took and returned (None / None: no producer to wait
+    for).  ``signal_pads``: ctypes array of the ranks' flag arrays, or None for one rank."""
+    pointers = ctypes.c_void_p * world
+    target_array = (ctypes.c_uint32 * len(targets))(*targets) if targets is not None else None
+    abi.check(abi.lib().b200_peer_allreduce_blocks(
+        pointers(*[int(p) for p in partials]), abi.DTYPE_CODES[abi.dtype_name(in_dtype)],
+        pointers(*[int(p) for p in outs]), abi.DTYPE_CODES[abi.dtype_name(out_dtype)],
+        int(total), int(block_elems), counters.data_ptr() if counters is not None else None,
+        target_array, int(rank), int(world), signal_pads, int(epoch0), int(ctas), stream))
+
+
 def linear(x, w, y, *, bias=None, act=abi.ACT_NONE, stream=0):
     """y = act(x @ w.T + bias) with the weight as [N, K] (a linear layer's layout; the
     transposed-B case of matmul_kernel's general strides, ops/suite/perf/matmul_triton2.py:27-30)."""

@@ -8,6 +8,14 @@ time a single shape by hand.
     python -m compiler_b200.profile_case attention --shape 2 8 4096 128
     python -m compiler_b200.profile_case attention_decode --shape 256 4096 128
     python -m compiler_b200.profile_case swiglu_gemm --shape 4096 1792 4096
+    python -m compiler_b200.profile_case gemm_allreduce_beside --shape 4096 4096 7168
+
+``gemm_allreduce_beside`` is the down-projection of the tensor-parallel MLP with its all-reduce
+kernel running beside it, as one rank (the "all-reduce" then only rounds the float16 partial to
+bfloat16): the product with progress counters per block of rows and the dependent kernel that
+takes each block when it is counted complete.  Its record carries the kernel's own time
+stamps: when it started and, per block of rows, when the GEMM had counted the block complete
+and when the block was reduced (microseconds after the start of the all-reduce kernel).
 
 Inputs are seeded random values generated on the host and uploaded through ``B200Device``
 (no torch); every launch is timed with CUDA events and the times are printed as JSON.
@@ -33,8 +41,10 @@ def _upload(device, array, dtype):
 def main(argv=None):
     parser = argparse.ArgumentParser(description=__doc__.split("\n")[0])
     parser.add_argument("op", choices=["softmax", "rmsnorm", "gemm", "attention", "attention_decode",
-                                       "linear_log_softmax",
-                                       "swiglu_gemm"])
+                                       "linear_log_softmax", "swiglu_gemm",
+                                       "gemm_allreduce_beside"])
+    parser.add_argument("--blocks", type=int, default=4,
+                        help="gemm_allreduce_beside: blocks of rows")
     parser.add_argument("--shape", type=int, nargs="+", required=True)
     parser.add_argument("--dtype", default=None)
     parser.add_argument("--launches", type=int, default=3)
@@ -90,6 +100,23 @@ def main(argv=None):
             b2 = _upload(device, rng.standard_normal((k, n), dtype=np.float32) / np.sqrt(k), dtype)
             launch = lambda: ops.gemm(a, b, c, b2=b2, act=abi.ACT_SWIGLU)  # noqa: E731
             work = {"flop": 4 * m * n * k}
+    elif args.op == "gemm_allreduce_beside":
+        dtype = "bfloat16"
+        m, n, k = shape
+        a = _upload(device, rng.standard_normal((m, k), dtype=np.float32) / np.sqrt(k), dtype)
+        b = _upload(device, rng.standard_normal((k, n), dtype=np.float32) / np.sqrt(k), dtype)
+        partial, out = device.alloc((m, n), "float16"), device.alloc((m, n), dtype)
+        words = abi.lib().b200_progress_words()
+        counters = device.upload(np.zeros(words, np.int32))
+        rows = max(256, m // max(1, args.blocks) // 256 * 256)
+        extra = {"rows_per_block": rows}
+
+        def launch():
+            targets = ops.gemm_progress(a, b, partial, rows, counters)
+            ops.peer_allreduce_blocks([partial.ptr], [out.ptr], m * n, rows * n, counters, targets,
+                                      0, 1, in_dtype="float16", out_dtype=dtype)
+            extra["blocks"] = len(targets)
+        work = {"flop": 2 * m * n * k}
     elif args.op == "linear_log_softmax":
         dtype = args.dtype or "bfloat16"
         m, n, k = shape
@@ -125,6 +152,13 @@ def main(argv=None):
         times.append(t.seconds / max(1, args.repeat))
     device.check_status()
     record = {"op": args.op, "shape": shape, "dtype": dtype, "launch_seconds": times, **work}
+    if args.op == "gemm_allreduce_beside":
+        stamps = device.download(counters)[18:].view(np.uint64)
+        record.update(extra)
+        record["allreduce_us_after_its_start"] = [
+            {"counted_complete": round((int(stamps[1 + 2 * i]) - int(stamps[0])) / 1e3, 1),
+             "reduced": round((int(stamps[2 + 2 * i]) - int(stamps[0])) / 1e3, 1)}
+            for i in range(extra["blocks"])]
     best = min(times)
     if "bytes" in work:
         record["best_GBps"] = work["bytes"] / best / 1e9

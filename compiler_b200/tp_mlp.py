@@ -301,13 +301,13 @@ class TensorParallelMLP:
                                                  dtype=torch.int32)
                 targets = ops.gemm_progress(self._h, self.wd, partial, rows, self._progress,
                                             stream=stream)
-                target_array = (ctypes.c_uint32 * len(targets))(*targets)
                 epoch0 = self._epoch + 1
                 self._epoch += len(targets)
-                abi.check(lib.b200_peer_allreduce_blocks(
-                    partial_ptrs, in_code, out_ptrs, out_code, m * hidden, rows * hidden,
-                    self._progress.data_ptr(), target_array, rank, world, pads, epoch0,
-                    self.comm_ctas, stream))
+                ops.peer_allreduce_blocks(
+                    partial_h.buffer_ptrs, out_h.buffer_ptrs, m * hidden, rows * hidden,
+                    self._progress, targets, rank, world, in_dtype=partial.dtype,
+                    out_dtype=out.dtype, signal_pads=pads, epoch0=epoch0, ctas=self.comm_ctas,
+                    stream=stream)
                 mark("down_projection_with_the_all_reduce_beside_it")
                 if y is not None and y.data_ptr() != out.data_ptr():
                     y.copy_(out)
