@@ -774,7 +774,11 @@ def bench_tp_mlp(torch, ops, dist, launches, peaks, source, collective, **option
                 "broadcast kernel",
         "nvls": f"{str(mlp.partial_dtype).rsplit('.', 1)[-1]} partials in symmetric memory, "
                 "in-switch sum and broadcast (multimem.ld_reduce / multimem.st), barriers "
-                "inside the kernel",
+                "inside the kernel"
+                + (f"; the all-reduce kernel is the programmatic dependent of the "
+                   f"down-projection and takes each of {mlp.overlap_blocks} blocks of rows as "
+                   "soon as every rank's GEMM has counted it complete"
+                   if mlp.overlap_blocks > 1 else ""),
         "pull": "float16 partials in symmetric memory, summed by plain peer loads and "
                 "broadcast by peer stores, barriers inside the kernel"
                 + (f"; the MLP runs in {mlp.row_splits} blocks of rows, a block's all-reduce "
@@ -1161,6 +1165,7 @@ def main():
                     ("tp_mlp_nvls", "nvls", {}), ("tp_mlp_pull", "pull", {}),
                     ("tp_mlp_pull_row_blocks", "pull", {"row_splits": 2, "comm_ctas": 74}),
                     ("tp_mlp_pull_beside_gemm", "pull", {"overlap_blocks": 4}),
+                    ("tp_mlp_nvls_beside_gemm", "nvls", {"overlap_blocks": 4}),
                     ("tp_mlp_nvls_f32", "nvls", {"partial_dtype": torch.float32})):
                 if collective == "peer" and MLP_M % (128 * dist.world):
                     continue

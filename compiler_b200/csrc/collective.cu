@@ -255,14 +255,39 @@ struct BlockPlan {
   unsigned int target[kMaxBlocks];
 };
 
-template <typename TIn, typename TOut, bool SYNC, int U, int W>
+// What moves a share of a block: plain peer loads and stores, or the switch.
+template <typename TIn, typename TOut, int U, int W> struct PeerMover {
+  RankPointers partial, out;
+  __device__ __forceinline__ void run(int64_t first, int64_t vecs, int world) const {
+    peer_reduce_share<TIn, TOut, U, W, true>(partial, out, first, vecs, world);
+  }
+};
+template <int IN, int OUT> struct SwitchMover {
+  const uint8_t *in_mc;
+  uint8_t *out_mc;
+  __device__ __forceinline__ void run(int64_t first, int64_t vecs, int) const {
+    constexpr int U = 8;
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < vecs; i += stride * U) {
+      uint4 v[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+        if (i + u * stride < vecs)
+          v[u] = reduced_vector<IN, OUT>(in_mc, first + (i + u * stride) * 8);
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+        if (i + u * stride < vecs) multimem_st16(out_mc + (first + (i + u * stride) * 8) * 2, v[u]);
+    }
+  }
+};
+
+template <typename Mover, bool SYNC>
 __global__ void __launch_bounds__(kBlockThreads, 4)  // at most 128 registers: see the launcher
-peer_allreduce_blocks_kernel(const __grid_constant__ RankPointers partial,
-                             const __grid_constant__ RankPointers out, int64_t total,
-                             int64_t block_elems, int nblocks, unsigned int *progress,
-                             const __grid_constant__ BlockPlan plan,
-                             const __grid_constant__ SignalPads pads, int rank, int world,
-                             uint32_t epoch0, unsigned int *status) {
+allreduce_blocks_kernel(const __grid_constant__ Mover mover, int64_t total,
+                        int64_t block_elems, int nblocks, unsigned int *progress,
+                        const __grid_constant__ BlockPlan plan,
+                        const __grid_constant__ SignalPads pads, int rank, int world,
+                        uint32_t epoch0, unsigned int *status) {
   __shared__ int ready;
   bool alive = true;
   // trace (CTA 0, thread 0; 64-bit nanoseconds after the counters): [0] entry of the kernel,
@@ -300,8 +325,7 @@ peer_allreduce_blocks_kernel(const __grid_constant__ RankPointers partial,
       const int64_t lo = (int64_t)b * block_elems;
       const int64_t n = total - lo < block_elems ? total - lo : block_elems;
       const int64_t share = n / world;
-      peer_reduce_share<TIn, TOut, U, W, true>(partial, out, lo + (int64_t)rank * share,
-                                               share / 8, world);
+      mover.run(lo + (int64_t)rank * share, share / 8, world);
       if (trace != nullptr) trace[2 + 2 * b] = timer_ns();
     }
   }
@@ -356,11 +380,10 @@ int launch_peer(const RankPointers &partial, const RankPointers &out, int64_t fi
                                      ctas, s);
 }
 
-template <typename TIn, typename TOut, int U, int W>
-int launch_peer_blocks_u(const RankPointers &partial, const RankPointers &out, int64_t total,
-                         int64_t block_elems, int nblocks, unsigned int *progress,
-                         const BlockPlan &plan, const SignalPads &pads, bool sync, int rank,
-                         int world, uint32_t epoch0, int ctas, cudaStream_t s) {
+template <typename Mover>
+int launch_blocks(const Mover &mover, int64_t total, int64_t block_elems, int nblocks,
+                  unsigned int *progress, const BlockPlan &plan, const SignalPads &pads,
+                  bool sync, int rank, int world, uint32_t epoch0, int ctas, cudaStream_t s) {
   // One CTA of 128 threads and at most 128 registers per SM: that fits beside the CTA-pair
   // GEMM (an SM sub-partition's 16 K registers then hold two GEMM warps of 184 registers and
   // one warp of this kernel).  Sixteen 16-byte loads in flight per thread: 148 CTAs hold
@@ -381,26 +404,25 @@ int launch_peer_blocks_u(const RankPointers &partial, const RankPointers &out, i
   attr.val.programmaticStreamSerializationAllowed = progress != nullptr ? 1 : 0;
   config.attrs = &attr;
   config.numAttrs = 1;
-  // the same shared-memory carve-out as the GEMM it runs beside (which takes the maximum): an
-  // SM does not hold CTAs of kernels that ask for different splits of its L1 / shared memory
+  // the same shared-memory carve-out as the GEMM it runs beside (which takes the maximum)
   static bool configured = false;
   if (!configured) {
-    B200_CUDA_OK(cudaFuncSetAttribute(peer_allreduce_blocks_kernel<TIn, TOut, true, U, W>,
+    B200_CUDA_OK(cudaFuncSetAttribute(allreduce_blocks_kernel<Mover, true>,
                                       cudaFuncAttributePreferredSharedMemoryCarveout,
                                       cudaSharedmemCarveoutMaxShared));
-    B200_CUDA_OK(cudaFuncSetAttribute(peer_allreduce_blocks_kernel<TIn, TOut, false, U, W>,
+    B200_CUDA_OK(cudaFuncSetAttribute(allreduce_blocks_kernel<Mover, false>,
                                       cudaFuncAttributePreferredSharedMemoryCarveout,
                                       cudaSharedmemCarveoutMaxShared));
     configured = true;
   }
   if (sync)
-    B200_CUDA_OK(cudaLaunchKernelEx(&config, peer_allreduce_blocks_kernel<TIn, TOut, true, U, W>,
-                                    partial, out, total, block_elems, nblocks, progress, plan,
-                                    pads, rank, world, epoch0, status));
+    B200_CUDA_OK(cudaLaunchKernelEx(&config, allreduce_blocks_kernel<Mover, true>, mover, total,
+                                    block_elems, nblocks, progress, plan, pads, rank, world,
+                                    epoch0, status));
   else
-    B200_CUDA_OK(cudaLaunchKernelEx(&config, peer_allreduce_blocks_kernel<TIn, TOut, false, U, W>,
-                                    partial, out, total, block_elems, nblocks, progress, plan,
-                                    pads, rank, world, epoch0, status));
+    B200_CUDA_OK(cudaLaunchKernelEx(&config, allreduce_blocks_kernel<Mover, false>, mover, total,
+                                    block_elems, nblocks, progress, plan, pads, rank, world,
+                                    epoch0, status));
   return B200_OK;
 }
 
@@ -410,16 +432,13 @@ int launch_peer_blocks(const RankPointers &partial, const RankPointers &out, int
                        const BlockPlan &plan, const SignalPads &pads, bool sync, int rank,
                        int world, uint32_t epoch0, int ctas, cudaStream_t s) {
   if (world <= 2)
-    return launch_peer_blocks_u<TIn, TOut, 8, 2>(partial, out, total, block_elems, nblocks,
-                                                 progress, plan, pads, sync, rank, world, epoch0,
-                                                 ctas, s);
+    return launch_blocks(PeerMover<TIn, TOut, 8, 2>{partial, out}, total, block_elems, nblocks,
+                         progress, plan, pads, sync, rank, world, epoch0, ctas, s);
   if (world <= 4)
-    return launch_peer_blocks_u<TIn, TOut, 4, 4>(partial, out, total, block_elems, nblocks,
-                                                 progress, plan, pads, sync, rank, world, epoch0,
-                                                 ctas, s);
-  return launch_peer_blocks_u<TIn, TOut, 2, 8>(partial, out, total, block_elems, nblocks,
-                                               progress, plan, pads, sync, rank, world, epoch0,
-                                               ctas, s);
+    return launch_blocks(PeerMover<TIn, TOut, 4, 4>{partial, out}, total, block_elems, nblocks,
+                         progress, plan, pads, sync, rank, world, epoch0, ctas, s);
+  return launch_blocks(PeerMover<TIn, TOut, 2, 8>{partial, out}, total, block_elems, nblocks,
+                       progress, plan, pads, sync, rank, world, epoch0, ctas, s);
 }
 
 template <int IN, int OUT>
@@ -600,6 +619,61 @@ extern "C" int b200_peer_allreduce_blocks(void *const *partial_rank, uint32_t in
   if (in_dtype == B200_DTYPE_BFLOAT16) B200_PARB(__nv_bfloat16, __half);
   B200_PARB(__half, __half);
 #undef B200_PARB
+}
+
+extern "C" int b200_multimem_allreduce_blocks(const void *in_multicast, uint32_t in_dtype,
+                                              void *out_multicast, uint32_t out_dtype,
+                                              int64_t total, int64_t block_elems,
+                                              unsigned int *progress, const unsigned int *targets,
+                                              int rank, int world, void *const *signal_pads,
+                                              uint32_t epoch0, int ctas, void *stream) {
+  using namespace b200;
+  if (in_multicast == nullptr || out_multicast == nullptr)
+    return fail(B200_USAGE, "null multicast pointer");
+  B200_REQUIRE(in_dtype == B200_DTYPE_BFLOAT16 || in_dtype == B200_DTYPE_FLOAT16 ||
+               in_dtype == B200_DTYPE_FLOAT32, "partials are f16, bf16 or f32");
+  B200_REQUIRE(out_dtype == B200_DTYPE_BFLOAT16 || out_dtype == B200_DTYPE_FLOAT16,
+               "the result is f16 or bf16");
+  B200_REQUIRE(in_dtype == B200_DTYPE_FLOAT32 || in_dtype == B200_DTYPE_FLOAT16 ||
+               out_dtype == B200_DTYPE_BFLOAT16, "bf16 partials give a bf16 result");
+  B200_REQUIRE(world >= 1 && world <= 8 && rank >= 0 && rank < world,
+               "rank %d / world %d out of range", rank, world);
+  B200_REQUIRE(total > 0 && block_elems > 0 && block_elems % (8 * world) == 0 &&
+               total % (8 * world) == 0,
+               "total and block size / world must be multiples of 8 elements");
+  B200_REQUIRE((uintptr_t)in_multicast % 16 == 0 && (uintptr_t)out_multicast % 16 == 0,
+               "multicast pointers must be 16-byte aligned");
+  const int64_t nblocks = (total + block_elems - 1) / block_elems;
+  B200_REQUIRE(nblocks <= kMaxBlocks, "%lld blocks, at most %d", (long long)nblocks, kMaxBlocks);
+  B200_REQUIRE((progress == nullptr) == (targets == nullptr),
+               "progress counters and their targets come together");
+  SignalPads pads;
+  BlockPlan plan;
+  for (int k = 0; k < 8; ++k) pads.pad[k] = nullptr;
+  for (int b = 0; b < kMaxBlocks; ++b) plan.target[b] = targets && b < nblocks ? targets[b] : 0u;
+  const bool sync = signal_pads != nullptr;
+  if (sync) {
+    B200_REQUIRE(epoch0 != 0, "epoch 0 is the cleared state of the signal pads: start at 1");
+    for (int k = 0; k < world; ++k) {
+      B200_REQUIRE(signal_pads[k] != nullptr && (uintptr_t)signal_pads[k] % 4 == 0,
+                   "signal pad of rank %d is null or unaligned", k);
+      pads.pad[k] = static_cast<uint32_t *>(signal_pads[k]);
+    }
+  }
+  cudaStream_t s = (cudaStream_t)stream;
+#define B200_SWB(IN, OUT)                                                                      \
+  if (in_dtype == IN && out_dtype == OUT)                                                      \
+    return launch_blocks(SwitchMover<IN, OUT>{(const uint8_t *)in_multicast,                   \
+                                              (uint8_t *)out_multicast},                       \
+                         total, block_elems, (int)nblocks, progress, plan, pads, sync, rank,   \
+                         world, epoch0, ctas, s)
+  B200_SWB(B200_DTYPE_FLOAT32, B200_DTYPE_BFLOAT16);
+  B200_SWB(B200_DTYPE_FLOAT32, B200_DTYPE_FLOAT16);
+  B200_SWB(B200_DTYPE_FLOAT16, B200_DTYPE_BFLOAT16);
+  B200_SWB(B200_DTYPE_FLOAT16, B200_DTYPE_FLOAT16);
+  B200_SWB(B200_DTYPE_BFLOAT16, B200_DTYPE_BFLOAT16);
+#undef B200_SWB
+  return fail(B200_REJECTED, "unsupported type pair");
 }
 
 // counters [kMaxBlocks], the count of CTAs that are done with them, one word of padding, and

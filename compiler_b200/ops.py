@@ -95,6 +95,19 @@ def peer_allreduce_blocks(partials, outs, total, block_elems, counters, targets,
         target_array, int(rank), int(world), signal_pads, int(epoch0), int(ctas), stream))
 
 
+def multimem_allreduce_blocks(in_multicast, out_multicast, total, block_elems, counters, targets,
+                              rank, world, *, in_dtype, out_dtype, signal_pads=None, epoch0=0,
+                              ctas=0, stream=0):
+    """``peer_allreduce_blocks`` through the switch: multicast addresses of the partial and
+    the result (in-switch fp32 sum, store to all ranks)."""
+    target_array = (ctypes.c_uint32 * len(targets))(*targets) if targets is not None else None
+    abi.check(abi.lib().b200_multimem_allreduce_blocks(
+        int(in_multicast), abi.DTYPE_CODES[abi.dtype_name(in_dtype)], int(out_multicast),
+        abi.DTYPE_CODES[abi.dtype_name(out_dtype)], int(total), int(block_elems),
+        counters.data_ptr() if counters is not None else None, target_array, int(rank),
+        int(world), signal_pads, int(epoch0), int(ctas), stream))
+
+
 def linear(x, w, y, *, bias=None, act=abi.ACT_NONE, stream=0):
     """y = act(x @ w.T + bias) with the weight as [N, K] (a linear layer's layout; the
     transposed-B case of matmul_kernel's general strides, ops/suite/perf/matmul_triton2.py:27-30)."""

@@ -108,6 +108,9 @@ PROTOTYPES = {
     "b200_peer_allreduce_blocks": (c_int, [POINTER(_PTR), c_uint32, POINTER(_PTR), c_uint32,
                                            c_int64, c_int64, _PTR, POINTER(c_uint32), c_int,
                                            c_int, POINTER(_PTR), c_uint32, c_int, _PTR]),
+    "b200_multimem_allreduce_blocks": (c_int, [_PTR, c_uint32, _PTR, c_uint32, c_int64, c_int64,
+                                               _PTR, POINTER(c_uint32), c_int, c_int,
+                                               POINTER(_PTR), c_uint32, c_int, _PTR]),
     "b200_progress_words": (c_int, []),
     "b200_attn_fwd": (c_int, [_T, _T, _T, _T, _T, c_float, c_int, _PTR]),
     "b200_stream_wait_event": (c_int, [_PTR, _PTR]),

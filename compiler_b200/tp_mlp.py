@@ -75,7 +75,7 @@ class TensorParallelMLP:
         all-reduce kernel while it runs beside a GEMM (0 = default).  ``row_splits`` (nvls and
         pull paths): run the whole MLP in this many blocks of rows, the all-reduce of a
         block's result on a second stream beside both projections of the next block.
-        ``overlap_blocks`` (pull path, more than 1): ONE down-projection launch that counts
+        ``overlap_blocks`` (pull and nvls paths, more than 1): ONE down-projection launch that counts
         its finished tiles per block of rows, and the all-reduce kernel launched behind it as
         its programmatic dependent: it runs beside the GEMM and takes each block of rows as
         soon as every rank has counted it complete, so only the last block's all-reduce is
@@ -101,8 +101,8 @@ class TensorParallelMLP:
         self.comm_ctas = int(comm_ctas)
         self.row_splits = max(1, int(row_splits))
         self.overlap_blocks = max(1, int(overlap_blocks))
-        if self.overlap_blocks > 1 and collective != "pull":
-            raise ValueError("overlap_blocks needs collective='pull'")
+        if self.overlap_blocks > 1 and collective not in ("pull", "nvls"):
+            raise ValueError("overlap_blocks needs collective='pull' or 'nvls'")
         self._progress = None
         self._epoch = 0
         self._comm_stream = None
@@ -303,11 +303,18 @@ class TensorParallelMLP:
                                             stream=stream)
                 epoch0 = self._epoch + 1
                 self._epoch += len(targets)
-                ops.peer_allreduce_blocks(
-                    partial_h.buffer_ptrs, out_h.buffer_ptrs, m * hidden, rows * hidden,
-                    self._progress, targets, rank, world, in_dtype=partial.dtype,
-                    out_dtype=out.dtype, signal_pads=pads, epoch0=epoch0, ctas=self.comm_ctas,
-                    stream=stream)
+                if self.collective == "nvls":
+                    ops.multimem_allreduce_blocks(
+                        partial_h.multicast_ptr, out_h.multicast_ptr, m * hidden, rows * hidden,
+                        self._progress, targets, rank, world, in_dtype=partial.dtype,
+                        out_dtype=out.dtype, signal_pads=pads, epoch0=epoch0,
+                        ctas=self.comm_ctas, stream=stream)
+                else:
+                    ops.peer_allreduce_blocks(
+                        partial_h.buffer_ptrs, out_h.buffer_ptrs, m * hidden, rows * hidden,
+                        self._progress, targets, rank, world, in_dtype=partial.dtype,
+                        out_dtype=out.dtype, signal_pads=pads, epoch0=epoch0,
+                        ctas=self.comm_ctas, stream=stream)
                 mark("down_projection_with_the_all_reduce_beside_it")
                 if y is not None and y.data_ptr() != out.data_ptr():
                     y.copy_(out)

@@ -395,6 +395,13 @@ int b200_peer_allreduce_blocks(void *const *partial_rank, uint32_t in_dtype,
                                int64_t block_elems, unsigned int *progress,
                                const unsigned int *targets, int rank, int world,
                                void *const *signal_pads, uint32_t epoch0, int ctas, void *stream);
+/* The same through the switch (multicast pointers as for b200_multimem_allreduce). */
+int b200_multimem_allreduce_blocks(const void *in_multicast, uint32_t in_dtype,
+                                   void *out_multicast, uint32_t out_dtype, int64_t total,
+                                   int64_t block_elems, unsigned int *progress,
+                                   const unsigned int *targets, int rank, int world,
+                                   void *const *signal_pads, uint32_t epoch0, int ctas,
+                                   void *stream);
 int b200_progress_words(void);
 
 /* out = x * sigmoid(x) * y elementwise.  Replaces swiglu_fwd_kernel

@@ -82,7 +82,7 @@ shards = [bf16(t).contiguous() for t in (wgb[:, lo:hi], wub[:, lo:hi], wdb[lo:hi
 dxb = bf16(xb)
 failures = []
 for collective, options in (("nccl", {}), ("peer", {}), ("nvls", {}), ("pull", {}),
-                            ("pull", {"overlap_blocks": 4}),
+                            ("pull", {"overlap_blocks": 4}), ("nvls", {"overlap_blocks": 4}),
                             ("nvls", {"partial_dtype": torch.float32, "chunks": 2})):
     try:
         big = tp_mlp.TensorParallelMLP(*shards, collective=collective, **options)
