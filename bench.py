@@ -1175,6 +1175,16 @@ def main():
                                                collective, **options)
                 except Exception as exc:  # noqa: BLE001 - symmetric memory / NVLS may be unavailable
                     extras[key] = {"unavailable": f"{type(exc).__name__}: {exc}"[:300]}
+            valid = {k: v for k, v in extras.items() if k.startswith("tp_mlp") and
+                     v.get("value") is not None and v.get("parity", {}).get("ok")}
+            if valid:
+                best = min(valid, key=lambda k: valid[k]["ms_per_step"])
+                extras["tp_mlp_fastest"] = {
+                    "variant": best, "ms_per_step": valid[best]["ms_per_step"],
+                    "frac": valid[best]["frac"], "value": valid[best]["value"],
+                    "unit": valid[best]["unit"],
+                    "note": "the fastest of the tp_mlp* entries above whose result matched "
+                            "the oracle on every rank; tp_mlp itself is the NCCL baseline"}
     if want("allreduce") and dist.enabled:
         try:
             extras["allreduce"] = bench_allreduce(torch, dist)
