@@ -405,15 +405,18 @@ int launch_blocks(const Mover &mover, int64_t total, int64_t block_elems, int nb
   config.attrs = &attr;
   config.numAttrs = 1;
   // the same shared-memory carve-out as the GEMM it runs beside (which takes the maximum)
-  static bool configured = false;
-  if (!configured) {
+  static bool configured[64] = {false};  // per device: function attributes belong to a context
+  int dev = 0;
+  B200_CUDA_OK(cudaGetDevice(&dev));
+  if (dev >= 64) return fail(B200_RESOURCE, "device index %d out of range", dev);
+  if (!configured[dev]) {
     B200_CUDA_OK(cudaFuncSetAttribute(allreduce_blocks_kernel<Mover, true>,
                                       cudaFuncAttributePreferredSharedMemoryCarveout,
                                       cudaSharedmemCarveoutMaxShared));
     B200_CUDA_OK(cudaFuncSetAttribute(allreduce_blocks_kernel<Mover, false>,
                                       cudaFuncAttributePreferredSharedMemoryCarveout,
                                       cudaSharedmemCarveoutMaxShared));
-    configured = true;
+    configured[dev] = true;
   }
   if (sync)
     B200_CUDA_OK(cudaLaunchKernelEx(&config, allreduce_blocks_kernel<Mover, true>, mover, total,

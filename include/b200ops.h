@@ -386,7 +386,10 @@ int b200_peer_allreduce(void *const *partial_rank, uint32_t in_dtype, void *cons
  * as for b200_multimem_allreduce; the caller advances its epoch by the number of blocks), then
  * this rank's share of the block as in b200_peer_allreduce.  Only the last block's all-reduce
  * is left when the GEMM ends.  progress == NULL (then targets == NULL): no waiting on a
- * producer, an ordinary launch.  Every wait is bounded (B200_TIMEOUT, sites 40 - 42). */
+ * producer, an ordinary launch.  Every wait is bounded (B200_TIMEOUT, sites 40 - 42).  A
+ * b200_gemm_progress launch is always followed by the all-reduce launch that reads its
+ * counters and puts them back to zero: counters left standing would release the next
+ * all-reduce before its GEMM has run. */
 int b200_gemm_progress(const b200_tensor *a, const b200_tensor *b, b200_tensor *c,
                        int64_t rows_per_block, unsigned int *counters, unsigned int *targets,
                        int max_blocks, int *blocks, void *stream);
