@@ -5,6 +5,7 @@ time a single shape by hand.
     python -m compiler_b200.profile_case softmax   --shape 16384 4000 --dtype float16
     python -m compiler_b200.profile_case rmsnorm   --shape 8192 4096  --dtype float32
     python -m compiler_b200.profile_case gemm      --shape 8192 8192 8192
+    python -m compiler_b200.profile_case linear    --shape 8192 8192 4096   (weight as [N,K])
     python -m compiler_b200.profile_case attention --shape 2 8 4096 128
     python -m compiler_b200.profile_case attention_decode --shape 256 4096 128
     python -m compiler_b200.profile_case swiglu_gemm --shape 4096 1792 4096
@@ -41,7 +42,7 @@ def _upload(device, array, dtype):
 def main(argv=None):
     parser = argparse.ArgumentParser(description=__doc__.split("\n")[0])
     parser.add_argument("op", choices=["softmax", "rmsnorm", "gemm", "attention", "attention_decode",
-                                       "linear_log_softmax", "swiglu_gemm",
+                                       "linear", "linear_log_softmax", "swiglu_gemm",
                                        "gemm_allreduce_beside"])
     parser.add_argument("--blocks", type=int, default=4,
                         help="gemm_allreduce_beside: blocks of rows")
@@ -116,6 +117,18 @@ def main(argv=None):
             ops.peer_allreduce_blocks([partial.ptr], [out.ptr], m * n, rows * n, counters, targets,
                                       0, 1, in_dtype="float16", out_dtype=dtype)
             extra["blocks"] = len(targets)
+        work = {"flop": 2 * m * n * k}
+    elif args.op == "linear":
+        dtype = args.dtype or "bfloat16"
+        m, n, k = shape
+        x = _upload(device, rng.standard_normal((m, k), dtype=np.float32) / np.sqrt(k), dtype)
+        w = _upload(device, rng.standard_normal((n, k), dtype=np.float32) / np.sqrt(k), dtype)
+        y = device.alloc((m, n), dtype)
+        bias = None if args.no_bias else _upload(
+            device, rng.normal(0, 0.1, n).astype(np.float32), dtype)
+        act = {"none": abi.ACT_NONE, "gelu_tanh": abi.ACT_GELU_TANH,
+               "gelu_erf": abi.ACT_GELU_ERF}[args.act]
+        launch = lambda: ops.linear(x, w, y, bias=bias, act=act)  # noqa: E731
         work = {"flop": 2 * m * n * k}
     elif args.op == "linear_log_softmax":
         dtype = args.dtype or "bfloat16"
