@@ -778,7 +778,7 @@ def bench_tp_mlp(torch, ops, dist, launches, peaks, source, collective, **option
                 + (f"; the all-reduce kernel is the programmatic dependent of the "
                    f"down-projection and takes each of {mlp.overlap_blocks} blocks of rows as "
                    "soon as every rank's GEMM has counted it complete"
-                   if mlp.overlap_blocks > 1 else ""),
+                   if mlp.overlap_blocks > 0 else ""),
         "pull": "float16 partials in symmetric memory, summed by plain peer loads and "
                 "broadcast by peer stores, barriers inside the kernel"
                 + (f"; the MLP runs in {mlp.row_splits} blocks of rows, a block's all-reduce "
@@ -786,7 +786,7 @@ def bench_tp_mlp(torch, ops, dist, launches, peaks, source, collective, **option
                 + (f"; the all-reduce kernel is the programmatic dependent of the "
                    f"down-projection and takes each of {mlp.overlap_blocks} blocks of rows as "
                    "soon as every rank's GEMM has counted it complete"
-                   if mlp.overlap_blocks > 1 else ""),
+                   if mlp.overlap_blocks > 0 else ""),
         "none": "one GPU: the two GEMMs alone (anchor of the strong-scaling curve)",
     }
     partial_bytes = MLP_M * MLP_HIDDEN * (4 if collective == "nccl"

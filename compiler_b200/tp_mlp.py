@@ -58,7 +58,7 @@ class TensorParallelMLP:
 
     def __init__(self, wg, wu, wd, *, group=None, chunks=None, collective: str = "nccl",
                  partial_dtype=None, comm_ctas: int = 0, row_splits: int = 1,
-                 overlap_blocks: int = 1):
+                 overlap_blocks: int = 0):
         """wg, wu: this rank's [hidden, ffn/tp] column shards; wd: its [ffn/tp, hidden] row
         shard (CUDA bf16/fp16 torch tensors, contiguous).
 
@@ -75,11 +75,14 @@ class TensorParallelMLP:
         all-reduce kernel while it runs beside a GEMM (0 = default).  ``row_splits`` (nvls and
         pull paths): run the whole MLP in this many blocks of rows, the all-reduce of a
         block's result on a second stream beside both projections of the next block.
-        ``overlap_blocks`` (pull and nvls paths, more than 1): ONE down-projection launch that counts
+        ``overlap_blocks`` (pull and nvls paths, 1 or more): ONE down-projection launch that counts
         its finished tiles per block of rows, and the all-reduce kernel launched behind it as
         its programmatic dependent: it runs beside the GEMM and takes each block of rows as
         soon as every rank has counted it complete, so only the last block's all-reduce is
-        left when the GEMM ends -- no second stream and no extra partial waves."""
+        left when the GEMM ends -- no second stream and no extra partial waves.  With 1 the
+        all-reduce kernel still becomes resident while the GEMM runs and starts on the whole
+        result the moment the GEMM has counted it complete (its launch latency and the wait
+        for the peers' kernels to start are hidden), but nothing is reduced early."""
         import torch
         self.torch = torch
         self.wg, self.wu, self.wd = wg, wu, wd
@@ -100,8 +103,8 @@ class TensorParallelMLP:
             raise ValueError(f"collective='{collective}' stages 16-bit partials")
         self.comm_ctas = int(comm_ctas)
         self.row_splits = max(1, int(row_splits))
-        self.overlap_blocks = max(1, int(overlap_blocks))
-        if self.overlap_blocks > 1 and collective not in ("pull", "nvls"):
+        self.overlap_blocks = max(0, int(overlap_blocks))
+        if self.overlap_blocks > 0 and collective not in ("pull", "nvls"):
             raise ValueError("overlap_blocks needs collective='pull' or 'nvls'")
         self._progress = None
         self._epoch = 0
@@ -293,7 +296,7 @@ class TensorParallelMLP:
                   if ((c[1] - c[0]) * hidden) % (8 * world) == 0]
         if sum(hi - lo for lo, hi in chunks) != m:
             chunks = [(0, m)]
-        if self.overlap_blocks > 1 and x is None:
+        if self.overlap_blocks > 0 and x is None:
             rows = max(256, (m // self.overlap_blocks) // 256 * 256)
             if m % 256 == 0 and (rows * hidden) % (8 * world) == 0:
                 if self._progress is None:
