@@ -166,6 +166,7 @@ def main(argv=None):
     device.check_status()
     record = {"op": args.op, "shape": shape, "dtype": dtype, "launch_seconds": times, **work}
     if args.op == "gemm_allreduce_beside":
+        # 16 counters + the count of CTAs done + one word of padding, then the time stamps
         stamps = device.download(counters)[18:].view(np.uint64)
         record.update(extra)
         record["allreduce_us_after_its_start"] = [

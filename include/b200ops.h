@@ -373,7 +373,9 @@ int b200_peer_allreduce(void *const *partial_rank, uint32_t in_dtype, void *cons
  * b200_gemm_progress: rows of C in blocks of rows_per_block (a multiple of 256; a block is a
  * raster group of the kernel, so the blocks finish in order).  counters: device memory of
  * b200_progress_words() 32-bit words, zero before the first launch (the all-reduce below puts
- * them back to zero).  Every epilogue warp adds one to its block's counter after its stores
+ * them back to zero): 16 counters, one count of the all-reduce CTAs that are done with them, one
+ * word of padding, then 64-bit %globaltimer stamps written by the all-reduce kernel's first
+ * CTA (its start; per block: counted complete, reduced).  Every epilogue warp adds one to its block's counter after its stores
  * of a tile, fenced at system scope.  targets[b] (host, max_blocks entries) receives the count
  * block b reaches; *blocks the number of blocks.  The kernel releases its programmatic
  * dependents as soon as its CTAs are set up.  REJECTED for shapes the CTA-pair kernel does not
