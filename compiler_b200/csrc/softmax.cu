@@ -274,15 +274,25 @@ softmax_rows_kernel(const T *__restrict__ x, const T *__restrict__ mul, T *__res
 // two for the form with the multiplier, which also holds that row's vectors.
 constexpr int stream_ctas_per_sm(int mode) { return mode == kSoftmaxMul ? 2 : 3; }
 
+// Rows of more than 256 x VPT vectors (G = 512 or 1024 threads): the CTA is the group, one row
+// at a time with the next one in flight, in the LEAN form only (its 63 registers are what 1024
+// threads leave each other); two CTAs per SM at 512 threads, one at 1024.  Before, such rows
+// had one row in flight per SM and nothing to hide its load -> max -> sum -> store chain behind:
+// fp16 [4096,16384] ran at 3.4 TB/s, [2048,32768] at 2.8 TB/s.
+constexpr int stream_threads(int g) { return g > kRowThreads ? g : kRowThreads; }
+constexpr int stream_lean_ctas_per_sm(int g) { return g > 512 ? 1 : (g > kRowThreads ? 2 : 4); }
+
 template <typename T, int G, int VPT, int MODE, bool LEAN = false>
-__global__ void __launch_bounds__(kRowThreads, LEAN ? 4 : stream_ctas_per_sm(MODE))
+__global__ void __launch_bounds__(stream_threads(G),
+                                  LEAN ? stream_lean_ctas_per_sm(G) : stream_ctas_per_sm(MODE))
 softmax_stream_kernel(const T *__restrict__ x, const T *__restrict__ mul, T *__restrict__ y,
                       int64_t rows, int cols, int mask_kind, int64_t row_offset) {
-  static_assert(G <= kRowThreads, "one row per group of at most a CTA");
-  constexpr int kRowsPerCta = kRowThreads / G;
+  static_assert(G <= kRowThreads || LEAN, "wide rows take the lean form");
+  constexpr int kThreads = G > kRowThreads ? G : kRowThreads;
+  constexpr int kRowsPerCta = kThreads / G;
   using V = RowVec<T>;
   constexpr int N = V::N;
-  __shared__ float scratch[2 * (kRowThreads / 32)];
+  __shared__ float scratch[2 * (kThreads / 32)];
 
   const int lane = threadIdx.x % G;
   const int nvec = cols / N;
@@ -455,6 +465,18 @@ static void launch_rows(const b200_tensor *x, const b200_tensor *mul, b200_tenso
       softmax_stream_kernel<T, G, VPT, MODE><<<resident, kRowThreads, 0, stream>>>(
           (const T *)x->data, mul ? (const T *)mul->data : nullptr, (T *)y->data, rows,
           (int)x->shape[1], mask_kind, row_offset);
+      return;
+    }
+  } else if constexpr (MODE == kSoftmaxPlain) {
+    // wide rows, more rows than resident CTAs: the pipelined lean form with the CTA as the
+    // group (B200OPS_SOFTMAX_STREAM=0 keeps the one-row-per-CTA kernel)
+    static const int choice =
+        getenv("B200OPS_SOFTMAX_STREAM") ? atoi(getenv("B200OPS_SOFTMAX_STREAM")) : 1;
+    const unsigned resident = (unsigned)(sm_count() * stream_lean_ctas_per_sm(G));
+    if (choice != 0 && grid > resident) {
+      softmax_stream_kernel<T, G, VPT, MODE, true><<<resident, kThreads, 0, stream>>>(
+          (const T *)x->data, nullptr, (T *)y->data, rows, (int)x->shape[1], mask_kind,
+          row_offset);
       return;
     }
   }

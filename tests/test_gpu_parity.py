@@ -141,6 +141,33 @@ def test_masked_softmax_many_rows(device, case, dtype):
     assert (y[ref == 0] == 0).all() and np.isfinite(y).all()
 
 
+# many rows of 512 or 1024 threads' width (more rows than resident CTAs): the pipelined form
+# with the CTA as the row group; 16-bit widths, halved for float32 (four-element vectors)
+MANY_WIDE_ROWS = [((700, 16384), 0), ((333, 21840), 21000), ((301, 32768), 5), ((420, 9000), 8000),
+                  ((650, 8200), 3)]
+
+
+@pytest.mark.parametrize("masked", [False, True])
+@pytest.mark.parametrize("dtype", ["float32", "float16", "bfloat16"])
+@pytest.mark.parametrize("case", MANY_WIDE_ROWS)
+def test_softmax_many_wide_rows(device, case, dtype, masked):
+    shape, offset = case
+    if dtype == "float32":
+        shape = (shape[0], shape[1] // 2)
+    rng = np.random.default_rng(_seed(shape, dtype, masked, "many wide"))
+    x = _host(rng.standard_normal(shape) * 2, dtype)
+    dx, dy = _up(device, x, dtype), _poisoned(device, shape, dtype)
+    ops.softmax(dx, dy, causal_mod=masked, row_offset=offset if masked else 0)
+    y = device.download(dy)
+    ref = oracle.masked_softmax_ref(x, offset) if masked else oracle.softmax_ref(x)
+    rtol, atol = (2e-3, 1e-6) if dtype == "float32" else TOL[dtype]
+    oracle.compare(y.astype(np.float64), ref, rtol, atol)
+    assert np.isfinite(y).all()
+    if masked:
+        assert (y[ref == 0] == 0).all()
+    np.testing.assert_allclose(y.astype(np.float64).sum(axis=1), 1.0, atol=2e-2)
+
+
 # rows wider than one CTA keeps in registers (32768 16-bit / 16384 32-bit elements): a cluster
 # of 2, 4 or 8 CTAs per row with the partial results merged through distributed shared memory;
 # widths that are not a whole number of CTAs, a width beyond eight CTAs (looping kernel)
