@@ -61,6 +61,75 @@ rmsnorm_rows_kernel(const T *__restrict__ x, int64_t x_stride,
   }
 }
 
+// Rows of 1024 threads' width, more rows than resident CTAs: a persistent CTA walks down the
+// rows with the next row's vectors in flight while it reduces, scales and stores the current
+// one.  Used for 32-bit rows only (see launch_rows).
+template <typename T, int G, int VPT>
+__global__ void __launch_bounds__(G, G > 512 ? 1 : 2)
+rmsnorm_stream_kernel(const T *__restrict__ x, int64_t x_stride, const T *__restrict__ w,
+                      T *__restrict__ y, int64_t y_stride, T *__restrict__ rinv, int64_t rows,
+                      int cols, float eps, float gamma_offset) {
+  static_assert(G > kRowThreads, "the CTA is the row group");
+  constexpr int N = vec16<T>::N;
+  __shared__ float scratch[2 * (G / 32)];
+  const int lane = threadIdx.x;
+  const int nvec = cols / N;
+  const int64_t stride = gridDim.x;
+  int64_t row = blockIdx.x;
+
+  vec16<T> next[VPT];
+  if (row < rows) {
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int v = lane + i * G;
+      if (v < nvec) next[i].raw = ld_stream16(x + row * x_stride + (int64_t)v * N);
+    }
+  }
+  int buf = 0;  // consecutive rows reduce through alternating scratch halves
+  for (; row < rows; row += stride) {
+    vec16<T> xv[VPT];
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) xv[i] = next[i];
+    if (row + stride < rows) {
+      const T *ahead = x + (row + stride) * x_stride;
+#pragma unroll
+      for (int i = 0; i < VPT; ++i) {
+        const int v = lane + i * G;
+        if (v < nvec) next[i].raw = ld_stream16(ahead + (int64_t)v * N);
+      }
+    }
+    float acc = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      if (lane + i * G < nvec) {
+#pragma unroll
+        for (int j = 0; j < N; ++j) {
+          const float f = io<T>::load(xv[i].e[j]);
+          acc = fmaf(f, f, acc);
+        }
+      }
+    }
+    acc = group_reduce<G, SumOp>(acc, scratch, buf);
+    buf ^= 1;
+    const float inv = 1.0f / sqrtf(acc / (float)cols + eps);
+    if (lane == 0 && rinv != nullptr) rinv[row] = io<T>::store(inv);
+    T *yrow = y + row * y_stride;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int v = lane + i * G;
+      if (v < nvec) {
+        vec16<T> wv, out;
+        wv.raw = *reinterpret_cast<const uint4 *>(w + (int64_t)v * N);
+#pragma unroll
+        for (int j = 0; j < N; ++j)
+          out.e[j] =
+              io<T>::store(io<T>::load(xv[i].e[j]) * inv * (io<T>::load(wv.e[j]) + gamma_offset));
+        st_stream16(yrow + (int64_t)v * N, out.raw);
+      }
+    }
+  }
+}
+
 // Any width / alignment: one CTA per row, scalar loads, the row is re-read
 // from L2 for the scale pass.  Used for ragged widths such as 67.
 template <typename T>
@@ -92,6 +161,23 @@ static void launch_rows(const b200_tensor *x, const b200_tensor *w, b200_tensor 
   constexpr int kRowsPerCta = kThreads / G;
   const int64_t rows = x->shape[0];
   const unsigned grid = (unsigned)((rows + kRowsPerCta - 1) / kRowsPerCta);
+  // Only where it measured faster: 32-bit rows of 1024 threads' width (fp32 [2048,16384]
+  // 4.9 -> 6.1 TB/s).  16-bit rows of the same widths and 512-thread rows are faster with one
+  // row per CTA -- several CTAs of that kernel share an SM and overlap each other's phases
+  // (bf16 [4096,16384] 5.5 against 4.4 TB/s, [2048,32768] 4.7 against 3.7, fp32 [4096,8192]
+  // 6.5 against 5.8).
+  if constexpr (G > 512 && sizeof(T) == 4) {
+    // (B200OPS_RMSNORM_STREAM=0 keeps one row per CTA)
+    static const int choice =
+        getenv("B200OPS_RMSNORM_STREAM") ? atoi(getenv("B200OPS_RMSNORM_STREAM")) : 1;
+    const unsigned resident = (unsigned)(sm_count() * (G > 512 ? 1 : 2));
+    if (choice != 0 && grid > resident) {
+      rmsnorm_stream_kernel<T, G, VPT><<<resident, G, 0, stream>>>(
+          (const T *)x->data, x->stride[0], (const T *)w->data, (T *)y->data, y->stride[0],
+          rinv ? (T *)rinv->data : nullptr, rows, (int)x->shape[1], eps, gamma_offset);
+      return;
+    }
+  }
   rmsnorm_rows_kernel<T, G, VPT><<<grid, kThreads, 0, stream>>>(
       (const T *)x->data, x->stride[0], (const T *)w->data, (T *)y->data,
       y->stride[0], rinv ? (T *)rinv->data : nullptr, rows, (int)x->shape[1], eps, gamma_offset);

@@ -35,7 +35,7 @@ from compiler_b200.runtime import abi
 # library reads each once, at its first use in the process).
 KERNEL_SWITCHES = ("B200OPS_ATTN_KERNEL", "B200OPS_ATTN_P", "B200OPS_ATTN_WAVE",
                    "B200OPS_GEMM_PAIR", "B200OPS_GEMM_GROUP_M", "B200OPS_GEMM_TAIL",
-                   "B200OPS_SOFTMAX_STREAM")
+                   "B200OPS_SOFTMAX_STREAM", "B200OPS_RMSNORM_STREAM")
 
 
 def _kernel_switches() -> dict:

@@ -76,6 +76,28 @@ def test_rmsnorm_sweep(device, shape, dtype):
     oracle.compare(device.download(dr).astype(np.float64), r_ref, rtol, atol, name="r")
 
 
+# many rows of 512 or 1024 threads' width: the persistent form with the next row in flight
+@pytest.mark.parametrize("dtype", ["float32", "float16", "bfloat16"])
+@pytest.mark.parametrize("shape", [(700, 16384), (333, 21840), (301, 32768), (650, 8200)])
+def test_rmsnorm_many_wide_rows(device, shape, dtype):
+    if dtype == "float32":
+        shape = (shape[0], shape[1] // 2)
+    rng = np.random.default_rng(_seed(shape, dtype, "many wide rms"))
+    x = _host(rng.standard_normal(shape), dtype)
+    w = _host(rng.uniform(0.5, 1.5, shape[1]), dtype)
+    dx, dw = _up(device, x, dtype), _up(device, w, dtype)
+    dy, dr = _poisoned(device, shape, dtype), _poisoned(device, (shape[0],), dtype)
+    ops.rmsnorm(dx, dw, dy, dr, eps=1e-6)
+    y_ref, r_ref = oracle.rmsnorm_ref(x, w, 1e-6)
+    rtol, atol = TOL[dtype]
+    oracle.compare(device.download(dy).astype(np.float64), y_ref, rtol, atol, name="Y")
+    oracle.compare(device.download(dr).astype(np.float64), r_ref, rtol, atol, name="r")
+    # the zero-centred weight (gamma + 1) takes the same kernel
+    ops.rmsnorm(dx, dw, dy, dr, eps=1e-6, gamma_offset=1.0)
+    y_ref, _ = oracle.rmsnorm_ref(x, np.asarray(w, np.float64) + 1.0, 1e-6)
+    oracle.compare(device.download(dy).astype(np.float64), y_ref, rtol, atol, name="Y (gamma + 1)")
+
+
 def test_rmsnorm_strided_rows_and_guard(device):
     """Row pitch wider than the row: the gap must stay untouched (masked tails)."""
     rng = np.random.default_rng(11)
