@@ -13,6 +13,21 @@ namespace attn {
 constexpr int kSimtThreads = 256;
 constexpr int kSimtMaxKeys = 8192;  // scores of one row are staged in shared memory
 
+// The other modes of flash_varlen_fwd_kernel (ops/suite/dev/flash_varlen_fwd_kernel.py), on the
+// raw score S = q.k before the softmax scale:
+//   soft-cap  (:121-124)  S = tanh(S * softcap)
+//   ALiBi     (:76-81, :125-133)  causal: S += slope / scale * (j - N_K + 1);
+//             otherwise S -= slope / scale * |j - N_K + N - i|        (slope per batch and head)
+//   local window (:56-61, :137-146)  keys max(0, i + N_K - N - left) .. min(N_K - 1, i + N_K - N + right)
+// A row that sees no key gets zeros and lse = +inf (:309-310).
+struct SimtModes {
+  float softcap;        // 0: off
+  const float *alibi;   // nullptr: off; slope of (z, h) at alibi[z * alibi_z + h]
+  int64_t alibi_z;
+  int local;            // 1: the window below applies
+  int window_left, window_right;
+};
+
 template <typename T>
 __global__ void __launch_bounds__(kSimtThreads)
 attn_simt_kernel(const T *__restrict__ q, const T *__restrict__ k, const T *__restrict__ v,
@@ -20,7 +35,7 @@ attn_simt_kernel(const T *__restrict__ q, const T *__restrict__ k, const T *__re
                  int kv_group, int N, int NK, int D,
                  int64_t qz, int64_t qh, int64_t qm, int64_t kz, int64_t kh, int64_t kn,
                  int64_t vz, int64_t vh, int64_t vn, int64_t oz, int64_t oh, int64_t om,
-                 float scale, int causal) {
+                 float scale, int causal, SimtModes modes) {
   extern __shared__ float sm[];
   float *scores = sm;            // [NK]
   float *qrow = sm + NK;         // [D]
@@ -31,15 +46,32 @@ attn_simt_kernel(const T *__restrict__ q, const T *__restrict__ k, const T *__re
   const T *qp = q + z * qz + h * qh + (int64_t)m * qm;
   const T *kp = k + z * kz + (h / kv_group) * kh;
   const T *vp = v + z * vz + (h / kv_group) * vh;
-  const int keys = causal ? min(NK, m + 1 + (NK - N)) : NK;
+  // keys [first, keys) of this row
+  int first = 0;
+  int keys = causal ? min(NK, m + 1 + (NK - N)) : NK;
+  if (modes.local) {
+    first = max(0, m + (NK - N) - modes.window_left);
+    keys = min(NK, m + 1 + (NK - N) + modes.window_right);
+  }
+  T *op = o + z * oz + h * oh + (int64_t)m * om;
+  if (keys <= first) {  // no key in sight
+    for (int d = threadIdx.x; d < D; d += kSimtThreads) op[d] = io<T>::store(0.f);
+    if (lse != nullptr && threadIdx.x == 0) lse[z * lse_z + h * lse_h + m] = INFINITY;
+    return;
+  }
+  const float slope = modes.alibi != nullptr ? modes.alibi[z * modes.alibi_z + h] : 0.f;
   for (int d = threadIdx.x; d < D; d += kSimtThreads) qrow[d] = io<T>::load(qp[d]);
   __syncthreads();
   float mx = -INFINITY;
-  for (int j = threadIdx.x; j < keys; j += kSimtThreads) {
+  for (int j = first + threadIdx.x; j < keys; j += kSimtThreads) {
     const T *kr = kp + (int64_t)j * kn;
     float acc = 0.f;
     for (int d = 0; d < D; ++d) acc = fmaf(qrow[d], io<T>::load(kr[d]), acc);
+    if (modes.softcap != 0.f) acc = tanhf(acc * modes.softcap);
     acc *= scale;
+    // the bias is slope / scale on the raw score, i.e. slope on the scaled one
+    if (modes.alibi != nullptr)
+      acc += causal ? slope * (float)(j - NK + 1) : -slope * fabsf((float)(j - NK + N - m));
     scores[j] = acc;
     mx = fmaxf(mx, acc);
   }
@@ -50,7 +82,7 @@ attn_simt_kernel(const T *__restrict__ q, const T *__restrict__ k, const T *__re
   for (int i = 1; i < kSimtThreads / 32; ++i) mx = fmaxf(mx, red[i]);
   __syncthreads();
   float sum = 0.f;
-  for (int j = threadIdx.x; j < keys; j += kSimtThreads) {
+  for (int j = first + threadIdx.x; j < keys; j += kSimtThreads) {
     const float e = expf(scores[j] - mx);
     scores[j] = e;
     sum += e;
@@ -61,10 +93,10 @@ attn_simt_kernel(const T *__restrict__ q, const T *__restrict__ k, const T *__re
   sum = 0.f;
   for (int i = 0; i < kSimtThreads / 32; ++i) sum += red[i];
   const float inv = 1.0f / sum;
-  T *op = o + z * oz + h * oh + (int64_t)m * om;
   for (int d = threadIdx.x; d < D; d += kSimtThreads) {
     float acc = 0.f;
-    for (int j = 0; j < keys; ++j) acc = fmaf(scores[j], io<T>::load(vp[(int64_t)j * vn + d]), acc);
+    for (int j = first; j < keys; ++j)
+      acc = fmaf(scores[j], io<T>::load(vp[(int64_t)j * vn + d]), acc);
     op[d] = io<T>::store(acc * inv);
   }
   if (lse != nullptr && threadIdx.x == 0) lse[z * lse_z + h * lse_h + m] = mx + logf(sum);

@@ -439,12 +439,13 @@ static bool p_in_tmem() {
 }  // namespace attn
 }  // namespace b200
 
-extern "C" int b200_attn_fwd(const b200_tensor *q, const b200_tensor *k, const b200_tensor *v,
-                             b200_tensor *o, b200_tensor *lse, float scale, int causal,
-                             void *stream) {
+static int attn_fwd_impl(const b200_tensor *q, const b200_tensor *k, const b200_tensor *v,
+                         b200_tensor *o, b200_tensor *lse, float scale, int causal,
+                         const b200::attn::SimtModes &modes, void *stream) {
   using namespace b200;
   using namespace b200::attn;
   int st;
+  const bool plain = modes.softcap == 0.f && modes.alibi == nullptr && !modes.local;
   if ((st = check_tensor(q, "q", 4)) || (st = check_tensor(k, "k", 4)) ||
       (st = check_tensor(v, "v", 4)) || (st = check_tensor(o, "o", 4)))
     return st;
@@ -466,7 +467,9 @@ extern "C" int b200_attn_fwd(const b200_tensor *q, const b200_tensor *k, const b
     B200_REQUIRE(t->shape[0] == Z && t->shape[1] == HKV && t->shape[2] == NK && t->shape[3] == D,
                  "k and v must both be [Z, H_KV, N_K, D]");
   }
-  B200_REQUIRE(!causal || NK >= N, "the causal mask needs at least as many keys as query rows");
+  // (with the other modes a row that sees no key is defined: zeros and lse = +inf)
+  B200_REQUIRE(!plain || !causal || NK >= N,
+               "the causal mask needs at least as many keys as query rows");
   B200_REQUIRE(NK < (1 << 24), "N_K out of range");
   B200_REQUIRE(HKV > 0 ? H % HKV == 0 : H == 0, "query heads %lld are not a multiple of K/V heads %lld",
                (long long)H, (long long)HKV);
@@ -490,7 +493,7 @@ extern "C" int b200_attn_fwd(const b200_tensor *q, const b200_tensor *k, const b
     return (uintptr_t)t->data % 16 == 0 && (t->stride[0] * es) % 16 == 0 &&
            (t->stride[1] * es) % 16 == 0 && (t->stride[2] * es) % 16 == 0;
   };
-  const bool tensor_core = q->dtype != B200_DTYPE_FLOAT32 && (D == 64 || D == 128) &&
+  const bool tensor_core = plain && q->dtype != B200_DTYPE_FLOAT32 && (D == 64 || D == 128) &&
                            tma_ok(q) && tma_ok(k) && tma_ok(v) &&
                            (uintptr_t)o->data % 16 == 0 && (o->stride[0] * es) % 16 == 0 &&
                            (o->stride[1] * es) % 16 == 0 && (o->stride[2] * es) % 16 == 0;
@@ -505,7 +508,7 @@ extern "C" int b200_attn_fwd(const b200_tensor *q, const b200_tensor *k, const b
       lse ? (float *)lse->data : nullptr, lse ? lse->stride[0] : 0, lse ? lse->stride[1] : 0,   \
       (int)H, kv_group, (int)N, (int)NK, (int)D, q->stride[0], q->stride[1],                    \
       q->stride[2], k->stride[0], k->stride[1], k->stride[2], v->stride[0], v->stride[1],    \
-      v->stride[2], o->stride[0], o->stride[1], o->stride[2], scale, causal ? 1 : 0)
+      v->stride[2], o->stride[0], o->stride[1], o->stride[2], scale, causal ? 1 : 0, modes)
     if (q->dtype == B200_DTYPE_FLOAT32) B200_ATTN_SIMT(float);
     else if (q->dtype == B200_DTYPE_FLOAT16) B200_ATTN_SIMT(__half);
     else B200_ATTN_SIMT(__nv_bfloat16);
@@ -562,5 +565,44 @@ extern "C" int b200_attn_fwd(const b200_tensor *q, const b200_tensor *k, const b
     return D == 128 ? B200_ATTN_TC(__nv_bfloat16, 128) : B200_ATTN_TC(__nv_bfloat16, 64);
   return D == 128 ? B200_ATTN_TC(__half, 128) : B200_ATTN_TC(__half, 64);
 #undef B200_ATTN_TC
+}
+
+extern "C" int b200_attn_fwd(const b200_tensor *q, const b200_tensor *k, const b200_tensor *v,
+                             b200_tensor *o, b200_tensor *lse, float scale, int causal,
+                             void *stream) {
+  const b200::attn::SimtModes none{0.f, nullptr, 0, 0, 0, 0};
+  return attn_fwd_impl(q, k, v, o, lse, scale, causal, none, stream);
+}
+
+extern "C" int b200_attn_fwd_modes(const b200_tensor *q, const b200_tensor *k,
+                                   const b200_tensor *v, b200_tensor *o, b200_tensor *lse,
+                                   float scale, int causal, float softcap,
+                                   const b200_tensor *alibi_slopes, int window_left,
+                                   int window_right, void *stream) {
+  using namespace b200;
+  attn::SimtModes modes{0.f, nullptr, 0, 0, 0, 0};
+  B200_REQUIRE(softcap == softcap && softcap >= 0.f, "softcap must be >= 0 (0: off)");
+  modes.softcap = softcap;
+  if (alibi_slopes != nullptr) {
+    int st;
+    if (q == nullptr) return fail(B200_USAGE, "null argument");
+    const int dims = alibi_slopes->ndim;
+    if ((st = check_tensor(alibi_slopes, "alibi_slopes", dims == 2 ? 2 : 1))) return st;
+    B200_REQUIRE(alibi_slopes->dtype == B200_DTYPE_FLOAT32, "alibi_slopes must be f32");
+    const int64_t heads = q->shape[1];
+    B200_REQUIRE(alibi_slopes->shape[dims - 1] == heads && alibi_slopes->stride[dims - 1] == 1 &&
+                 (dims == 1 || alibi_slopes->shape[0] == q->shape[0]),
+                 "alibi_slopes must be [H] or [Z, H] with unit last stride");
+    modes.alibi = static_cast<const float *>(alibi_slopes->data);
+    modes.alibi_z = dims == 2 ? alibi_slopes->stride[0] : 0;
+  }
+  if (window_left >= 0 || window_right >= 0) {
+    B200_REQUIRE(window_left >= 0 && window_right >= 0,
+                 "a local window needs both sides (negative on both: no window)");
+    modes.local = 1;
+    modes.window_left = window_left;
+    modes.window_right = window_right;
+  }
+  return attn_fwd_impl(q, k, v, o, lse, scale, causal, modes, stream);
 }
 

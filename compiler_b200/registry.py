@@ -374,14 +374,15 @@ def _flash_varlen(device, v, grid, name):
     """flash_varlen_fwd_kernel (ops/suite/dev/flash_varlen_fwd_kernel.py:21-335), the dense
     case its reference covers (:370-418) and the causal one (mask aligned to the last key,
     :138; key length >= query length): packed sequences addressed through cu_seqlens (or
-    fixed lengths with batch strides), query and key lengths that differ, h / hk query heads
-    per K / V head, log-sum-exp laid out [h, total_q].  One launch of the attention operator
-    per sequence, on strided views of the packed buffers.  The sequence boundaries are read
-    back from the device, so this launch is bound afresh every time."""
-    for flag in ("is_softcap", "is_dropout", "return_softmax", "is_local", "is_paged", "is_alibi",
-                 "seqlenq_ngroups_swapped", "is_seqused_k"):
+    fixed lengths with batch strides), key lengths from seqused_k, query and key lengths that
+    differ, h / hk query heads per K / V head, log-sum-exp laid out [h, total_q]; and the
+    soft-cap, ALiBi and local-window modes (:121-146, CUDA-core kernel).  One launch of the
+    attention operator per sequence, on strided views of the packed buffers.  The sequence
+    boundaries are read back from the device, so this launch is bound afresh every time."""
+    for flag in ("is_dropout", "return_softmax", "is_paged", "seqlenq_ngroups_swapped"):
         _require(not v.get(flag, False), name, flag,
-                 "only the dense and the causal variants have a native operator")
+                 "dropout, the returned softmax, paged K / V and the swapped-groups layout "
+                 "have no native operator")
     h, hk, d, batches = int(v["h"]), int(v["hk"]), int(v["d"]), int(v["b"])
     _require(hk > 0 and h % hk == 0, name, "hk", "h must be a multiple of hk")
     total_q = int(v["total_q"])
@@ -391,6 +392,13 @@ def _flash_varlen(device, v, grid, name):
             bounds[side] = [int(x) for x in device.download(v[f"cu_seqlens_{side}_ptr"])]
             _require(len(bounds[side]) >= batches + 1, name, f"cu_seqlens_{side}_ptr",
                      "needs b + 1 entries")
+    used_k = ([int(x) for x in device.download(v["seqused_k_ptr"])]
+              if v.get("is_seqused_k", False) else None)
+    modes = {}
+    if v.get("is_softcap", False):
+        modes["softcap"] = float(v["softcap"])
+    if v.get("is_local", False):
+        modes["window"] = (int(v["window_size_left"]), int(v["window_size_right"]))
     for batch in range(batches):
         span = {}
         for side, rows in (("q", "q"), ("k", "k"), ("v", "k"), ("o", "q")):
@@ -401,6 +409,8 @@ def _flash_varlen(device, v, grid, name):
                 length = int(v[f"seqlen_{rows}"])
                 span[side] = (batch * int(v[f"{side}_batch_stride"]), length, batch * length)
         q_len, k_len = span["q"][1], span["k"][1]
+        if used_k is not None:
+            k_len = used_k[batch]                      # :49-52
         if q_len <= 0:
             continue
         _require(k_len > 0, name, "cu_seqlens_k_ptr", "a sequence without keys")
@@ -412,9 +422,12 @@ def _flash_varlen(device, v, grid, name):
 
         lse = _View(v["softmax_lse_ptr"], (1, h, q_len), (h * total_q, total_q, 1),
                     offset=span["q"][2])
+        if v.get("is_alibi", False):                   # one slope per (batch, head), :76-78
+            modes["alibi_slopes"] = _View(v["alibi_slopes_ptr"], (h,), (1,),
+                                          offset=batch * int(v["alibi_slopes_batch_stride"]))
         ops.attention(view("q", h, q_len), view("k", hk, k_len), view("v", hk, k_len),
                       view("o", h, q_len), lse=lse, scale=float(v["scale_softmax"]),
-                      causal=bool(v.get("is_causal", False)), stream=device.stream)
+                      causal=bool(v.get("is_causal", False)), stream=device.stream, **modes)
 
 
 _flash_varlen.reads_device = True

@@ -278,6 +278,22 @@ int b200_attn_fwd(const b200_tensor *q, const b200_tensor *k,
                   const b200_tensor *v, b200_tensor *o, b200_tensor *lse,
                   float scale, int causal, void *stream);
 
+/* The same with the further modes of flash_varlen_fwd_kernel
+ * (ops/suite/dev/flash_varlen_fwd_kernel.py), applied to the raw score S = q.k before the
+ * softmax scale: soft-cap S = tanh(S * softcap) (:121-124; softcap 0: off); ALiBi (:76-81,
+ * :125-133) with one f32 slope per head ([H]) or per batch and head ([Z,H]) or NULL -- causal:
+ * S += slope / scale * (j - N_K + 1), otherwise S -= slope / scale * |j - N_K + N - i|; local
+ * window (:56-61, :137-146; both sides >= 0, negative on both sides: off): row i sees keys
+ * max(0, i + N_K - N - left) .. min(N_K - 1, i + N_K - N + right).  A row that sees no key gets
+ * zeros and lse = +inf (:309-310).  With every mode off this is b200_attn_fwd; with any of
+ * them on the CUDA-core kernel runs (at most 8192 keys).  The reference's own `ref` covers the
+ * dense case only (:370-418): these modes are checked against a restatement of the kernel's
+ * lines.  Paged K / V and dropout are not taken. */
+int b200_attn_fwd_modes(const b200_tensor *q, const b200_tensor *k, const b200_tensor *v,
+                        b200_tensor *o, b200_tensor *lse, float scale, int causal,
+                        float softcap, const b200_tensor *alibi_slopes, int window_left,
+                        int window_right, void *stream);
+
 /* Causal sliding-window attention with a gate bias and an attention sink.  Replaces
  * parallel_attn_fwd_kernel (ops/suite/dev/parallel_attn_fwd_kernel.py; arithmetic :142-166):
  * logit[t,j] = scale * log2(e) * q[t].k[j] + g[t] - g[j] over max(0, t-window+1) <= j <= t,

@@ -157,6 +157,72 @@ def attention_ref(q, k, v, scale, causal=True):
     return out, lse
 
 
+def attention_modes_head_ref(q, k, v, scale, *, causal=False, softcap=0.0, alibi_slope=None,
+                             window=None):
+    """One (batch, head) slice with the further modes of flash_varlen_fwd_kernel, restated
+    from the KERNEL's lines (its own ``ref``, ops/suite/dev/flash_varlen_fwd_kernel.py:370-418,
+    covers dense attention only, so this part of the oracle is unpinned):
+
+    raw S = q k^T; soft-cap S = 2 / (1 + exp(-2 S softcap)) - 1 (:121-124); ALiBi with
+    slope / scale on the raw score -- causal: + (j - N_K + 1), otherwise - |j - N_K + N - i|
+    (:76-81, :125-133); masks with col_lb = max(0, i + N_K - N - left),
+    col_rb = min(N_K - 1, i + N_K - N + right): causal hides j > col_rb (right = 0), local
+    hides j outside [col_lb, col_rb] (:137-146); softmax of scale * S (:149-160); a row without
+    keys gives zeros and lse = +inf (:309-311).  q [N, D]; k, v [N_K, D]; float64 results."""
+    q = np.asarray(q, dtype=np.float64)
+    k = np.asarray(k, dtype=np.float64)
+    v = np.asarray(v, dtype=np.float64)
+    n, nk = q.shape[0], k.shape[0]
+    s = q @ k.T
+    if softcap:
+        s = 2.0 / (1.0 + np.exp(-2.0 * (s * float(softcap)))) - 1.0
+    rows = np.arange(n)[:, None]
+    cols = np.arange(nk)[None, :]
+    if alibi_slope is not None:
+        slope = float(alibi_slope) / float(scale)
+        if causal:
+            s = s + slope * (cols - nk + 1)
+        else:
+            s = s - slope * np.abs(cols - nk + n - rows)
+    left, right = window if window is not None else (0, 0)
+    col_lb = np.maximum(0, rows + nk - n - left)
+    col_rb = np.minimum(nk - 1, rows + nk - n + (right if window is not None else 0))
+    hidden = np.zeros((n, nk), dtype=bool)
+    if causal:
+        hidden |= cols > col_rb
+    if window is not None:
+        hidden |= (cols > col_rb) | (cols < col_lb)
+    s = np.where(hidden, -np.inf, s) * float(scale)
+    row_max = s.max(axis=1, keepdims=True)
+    safe_max = np.where(np.isinf(row_max), 0.0, row_max)
+    p = np.exp(s - safe_max)
+    denom = p.sum(axis=1, keepdims=True)
+    empty = denom[:, 0] == 0
+    out = (p / np.where(denom == 0, 1.0, denom)) @ v
+    with np.errstate(divide="ignore"):
+        lse = np.where(empty, np.inf, safe_max[:, 0] + np.log(denom[:, 0]))
+    return out, lse
+
+
+def attention_modes_ref(q, k, v, scale, *, causal=False, softcap=0.0, alibi_slopes=None,
+                        window=None):
+    """``attention_modes_head_ref`` over q [Z,H,N,D], k / v [Z,H_KV,N_K,D] (query head h reads
+    K / V head h // (H // H_KV)); ``alibi_slopes`` [H] or [Z,H]."""
+    q = np.asarray(q)
+    z, h, n, d = q.shape
+    group = h // np.asarray(k).shape[1]
+    out = np.empty((z, h, n, d), dtype=np.float64)
+    lse = np.empty((z, h, n), dtype=np.float64)
+    slopes = None if alibi_slopes is None else np.broadcast_to(np.asarray(alibi_slopes), (z, h))
+    for zi in range(z):
+        for hi in range(h):
+            out[zi, hi], lse[zi, hi] = attention_modes_head_ref(
+                q[zi, hi], k[zi, hi // group], v[zi, hi // group], scale, causal=causal,
+                softcap=softcap, alibi_slope=None if slopes is None else slopes[zi, hi],
+                window=window)
+    return out, lse
+
+
 def gemm_groupnorm_rowmin_ref(x, w, bias, gamma, beta, group_size, eps):
     """Row minimum of GroupNorm(x @ w + bias) with groups of ``group_size`` columns (ref of
     ops/suite/dev/fused_gemm_gn_min_kernel.py:88-105), float64 [M]."""

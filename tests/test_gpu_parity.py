@@ -532,6 +532,98 @@ def test_varlen_attention_through_the_launch_surface(device):
                    1e-3, 1e-3, name="lse")
 
 
+ATTENTION_MODES = [
+    dict(softcap=0.5), dict(softcap=0.05, causal=True), dict(window=(7, 0)), dict(window=(3, 5)),
+    dict(window=(0, 0), causal=True), dict(alibi="heads"), dict(alibi="batch", causal=True),
+    dict(alibi="heads", softcap=0.3, window=(9, 2)), dict(window=(64, 64), causal=True, softcap=1.0),
+]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "float16", "bfloat16"])
+@pytest.mark.parametrize("shape", [(2, 4, 2, 33, 47, 16), (1, 6, 6, 70, 70, 64), (2, 2, 1, 40, 12, 32),
+                                   (1, 2, 2, 12, 300, 128)])
+@pytest.mark.parametrize("modes", ATTENTION_MODES, ids=lambda m: "-".join(f"{k}" for k in m))
+def test_attention_modes(device, modes, shape, dtype):
+    """The soft-cap, ALiBi and local-window modes of flash_varlen_fwd_kernel
+    (ops/suite/dev/flash_varlen_fwd_kernel.py:121-146) against the restatement of the kernel's
+    lines: other key lengths (also fewer keys than rows: rows without a key give zeros and
+    lse = +inf), grouped K / V heads, slopes per head and per batch and head."""
+    z, hq, hkv, n, nk, d = shape
+    modes = dict(modes)
+    rng = np.random.default_rng(_seed(shape, dtype, sorted(modes)))
+    q = _host(rng.standard_normal((z, hq, n, d)), dtype)
+    k, v = (_host(rng.standard_normal((z, hkv, nk, d)), dtype) for _ in range(2))
+    slopes = None
+    if "alibi" in modes:
+        per = modes.pop("alibi")
+        slopes = (2.0 ** -np.arange(1, hq + 1, dtype=np.float32) if per == "heads"
+                  else rng.uniform(0.01, 0.5, (z, hq)).astype(np.float32))
+    dq, dk, dv = (_up(device, t, dtype) for t in (q, k, v))
+    do = _poisoned(device, (z, hq, n, d), dtype)
+    dl = device.upload(np.full((z, hq, n), POISON, np.float32))
+    scale = 1.0 / np.sqrt(d)
+    ops.attention(dq, dk, dv, do, lse=dl, scale=scale, causal=modes.get("causal", False),
+                  softcap=modes.get("softcap", 0.0), window=modes.get("window"),
+                  alibi_slopes=device.upload(slopes) if slopes is not None else None)
+    device.check_status()
+    out_ref, lse_ref = oracle.attention_modes_ref(
+        q, k, v, scale, causal=modes.get("causal", False), softcap=modes.get("softcap", 0.0),
+        alibi_slopes=slopes, window=modes.get("window"))
+    rtol, atol = (1e-4, 1e-5) if dtype == "float32" else TOL[dtype]
+    oracle.compare(device.download(do).astype(np.float64), out_ref, rtol, atol, name="out")
+    got_lse = device.download(dl).astype(np.float64)
+    empty = np.isinf(lse_ref)
+    assert np.array_equal(np.isposinf(got_lse), empty)
+    oracle.compare(got_lse[~empty], lse_ref[~empty], 1e-3, 1e-3, name="lse")
+
+
+def test_varlen_attention_modes_through_the_launch_surface(device):
+    """The varlen kernel's flags through the launch surface: key lengths from seqused_k,
+    soft-cap, a local window, ALiBi slopes per (batch, head) -- one case with all of them."""
+    case, _ = golden_cases.load("flash_varlen_fwd_kernel__2x17x19x4x2x16__float32")
+    h, hk, d = 4, 2, 16
+    q_len, k_cache, k_used = [17, 9, 30], [19, 25, 30], [19, 20, 11]
+    cu_q = np.concatenate(([0], np.cumsum(q_len))).astype(np.int32)
+    cu_k = np.concatenate(([0], np.cumsum(k_cache))).astype(np.int32)
+    total_q, total_k = int(cu_q[-1]), int(cu_k[-1])
+    rng = np.random.default_rng(78)
+    q = rng.normal(0, 0.7, (total_q, h, d)).astype(np.float32)
+    k = rng.normal(0, 0.7, (total_k, hk, d)).astype(np.float32)
+    v = rng.normal(0, 0.7, (total_k, hk, d)).astype(np.float32)
+    slopes = rng.uniform(0.05, 0.4, (3, h)).astype(np.float32)
+    scale, softcap, window = 1.0 / np.sqrt(d), 0.4, (6, 3)
+    args = dict(case["args"])
+    args.update({"q_ptr": q.reshape(-1), "k_ptr": k.reshape(-1), "v_ptr": v.reshape(-1),
+                 "o_ptr": np.zeros(total_q * h * d, np.float32),
+                 "softmax_lse_ptr": np.zeros(h * total_q, np.float32),
+                 "q_row_stride": h * d, "o_row_stride": h * d, "k_row_stride": hk * d,
+                 "v_row_stride": hk * d, "q_head_stride": d, "k_head_stride": d,
+                 "v_head_stride": d, "o_head_stride": d, "cu_seqlens_q_ptr": cu_q,
+                 "cu_seqlens_k_ptr": cu_k, "seqused_k_ptr": np.asarray(k_used, np.int32),
+                 "alibi_slopes_ptr": slopes.reshape(-1), "b": 3, "bk": 3,
+                 "seqlen_q": max(q_len), "seqlen_k": max(k_cache), "total_q": total_q})
+    meta = {**case["meta"], "h": h, "hk": hk, "h_hk_ratio": h // hk, "d": d, "d_rounded": d,
+            "scale_softmax": float(scale), "is_cu_seqlens_q": True, "is_cu_seqlens_k": True,
+            "is_seqused_k": True, "is_softcap": True, "softcap": softcap, "is_local": True,
+            "window_size_left": window[0], "window_size_right": window[1], "is_alibi": True,
+            "alibi_slopes_batch_stride": h}
+    case = dict(case, args=args, grid=(30, 3, h), meta=meta)
+    got = harness.run_case(case, device)
+    device.check_status()
+    out = got["o_ptr"].reshape(total_q, h, d).astype(np.float64)
+    lse = got["softmax_lse_ptr"].reshape(h, total_q).astype(np.float64)
+    for b in range(3):
+        qs, ks = slice(cu_q[b], cu_q[b + 1]), slice(cu_k[b], cu_k[b] + k_used[b])
+        ref_o, ref_l = oracle.attention_modes_ref(
+            q[qs].transpose(1, 0, 2)[None], k[ks].transpose(1, 0, 2)[None],
+            v[ks].transpose(1, 0, 2)[None], scale, softcap=softcap, alibi_slopes=slopes[b],
+            window=window)
+        oracle.compare(out[qs].transpose(1, 0, 2), ref_o[0], 1e-4, 1e-5, name=f"o[{b}]")
+        empty = np.isinf(ref_l[0])
+        assert np.array_equal(np.isposinf(lse[:, qs]), empty)
+        oracle.compare(lse[:, qs][~empty], ref_l[0][~empty], 1e-3, 1e-3, name=f"lse[{b}]")
+
+
 @pytest.mark.parametrize("shape", [(1, 1, 8, 16), (2, 2, 16, 32), (1, 2, 100, 80)])
 def test_attention_cuda_core_path(device, shape):
     z, h, n, d = shape

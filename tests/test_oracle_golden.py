@@ -317,3 +317,45 @@ def test_twins(tag):
         out, _ = oracle.attention_ref(a["q_ptr"], a["k_ptr"], a["v_ptr"], a["scale"],
                                       causal=bool(case["meta"]["CAUSAL"]))
         _check(case, "out_ptr", out)
+
+
+def test_attention_modes_restatement_properties():
+    """The restatement of flash_varlen_fwd_kernel's soft-cap / ALiBi / local-window lines has no
+    reference ``ref`` to be pinned to (ops/suite/dev/flash_varlen_fwd_kernel.py:370-373 raises
+    for them), so it is held to what must be true of it: with every mode off it is the dense /
+    causal oracle that IS pinned; a window that covers everything changes nothing; a zero
+    slope changes nothing; a tiny soft-cap makes all kept keys equal (uniform weights); rows
+    without a key give zeros and lse = +inf."""
+    rng = np.random.default_rng(5)
+    q = rng.standard_normal((2, 4, 9, 8))
+    k, v = rng.standard_normal((2, 2, 13, 8)), rng.standard_normal((2, 2, 13, 8))
+    scale = 0.35
+    for causal in (False, True):
+        base_o, base_l = oracle.gqa_attention_ref(q, k, v, scale, causal)
+        o, l = oracle.attention_modes_ref(q, k, v, scale, causal=causal)
+        assert np.allclose(o, base_o) and np.allclose(l, base_l)
+        o, l = oracle.attention_modes_ref(q, k, v, scale, causal=causal,
+                                          alibi_slopes=np.zeros(4))
+        assert np.allclose(o, base_o) and np.allclose(l, base_l)
+    o, l = oracle.attention_modes_ref(q, k, v, scale, window=(100, 100))
+    base_o, base_l = oracle.gqa_attention_ref(q, k, v, scale, False)
+    assert np.allclose(o, base_o) and np.allclose(l, base_l)
+    # causal = a window with nothing to the right and everything to the left
+    o, l = oracle.attention_modes_ref(q, k, v, scale, window=(100, 0))
+    base_o, base_l = oracle.gqa_attention_ref(q, k, v, scale, True)
+    assert np.allclose(o, base_o) and np.allclose(l, base_l)
+    # soft-cap -> 0: every kept score is ~0, the weights are uniform over the window
+    o, _ = oracle.attention_modes_ref(q, k, v, scale, softcap=1e-9, window=(2, 1))
+    rows, shift = np.arange(9), 13 - 9
+    for i in rows:
+        lo, hi = max(0, i + shift - 2), min(12, i + shift + 1)
+        assert np.allclose(o[0, 0, i], v[0, 0, lo:hi + 1].mean(axis=0), atol=1e-6)
+    # ALiBi, non-causal: the bias is -slope * |j - N_K + N - i| on the scaled score
+    o, l = oracle.attention_modes_ref(q[:, :1], k[:, :1], v[:, :1], scale, alibi_slopes=[0.25])
+    s = (q[0, 0] @ k[0, 0].T) * scale - 0.25 * np.abs(np.arange(13)[None, :] - 13 + 9
+                                                     - np.arange(9)[:, None])
+    assert np.allclose(l[0, 0], np.log(np.exp(s).sum(axis=1)))
+    # more rows than keys, causal: the first rows see nothing
+    o, l = oracle.attention_modes_ref(q[:, :, :, :], k[:, :, :3], v[:, :, :3], scale, causal=True,
+                                      softcap=0.5)
+    assert np.isposinf(l[:, :, :6]).all() and not o[:, :, :6].any() and np.isfinite(l[:, :, 6:]).all()
