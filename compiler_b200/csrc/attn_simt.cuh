@@ -26,6 +26,13 @@ struct SimtModes {
   int64_t alibi_z;
   int local;            // 1: the window below applies
   int window_left, window_right;
+  // paged K / V (:91-108): key j of batch z lives in physical page
+  // page_table[z * page_table_z + j / block_size], at page * page_stride +
+  // (j % block_size) * (row stride of k) past the head's base -- for K and V alike
+  const int *page_table;  // nullptr: off
+  int64_t page_table_z;
+  int block_size;
+  int64_t page_stride;
 };
 
 template <typename T>
@@ -60,11 +67,19 @@ attn_simt_kernel(const T *__restrict__ q, const T *__restrict__ k, const T *__re
     return;
   }
   const float slope = modes.alibi != nullptr ? modes.alibi[z * modes.alibi_z + h] : 0.f;
+  const int *pages = modes.page_table != nullptr ? modes.page_table + z * modes.page_table_z
+                                                 : nullptr;
+  // offset of key j's row past the head's base (V shares K's page and row pitch when paged)
+  auto key_row = [&](int j, int64_t pitch) -> int64_t {
+    if (pages == nullptr) return (int64_t)j * pitch;
+    return (int64_t)pages[j / modes.block_size] * modes.page_stride +
+           (int64_t)(j % modes.block_size) * kn;
+  };
   for (int d = threadIdx.x; d < D; d += kSimtThreads) qrow[d] = io<T>::load(qp[d]);
   __syncthreads();
   float mx = -INFINITY;
   for (int j = first + threadIdx.x; j < keys; j += kSimtThreads) {
-    const T *kr = kp + (int64_t)j * kn;
+    const T *kr = kp + key_row(j, kn);
     float acc = 0.f;
     for (int d = 0; d < D; ++d) acc = fmaf(qrow[d], io<T>::load(kr[d]), acc);
     if (modes.softcap != 0.f) acc = tanhf(acc * modes.softcap);
@@ -96,7 +111,7 @@ attn_simt_kernel(const T *__restrict__ q, const T *__restrict__ k, const T *__re
   for (int d = threadIdx.x; d < D; d += kSimtThreads) {
     float acc = 0.f;
     for (int j = first; j < keys; ++j)
-      acc = fmaf(scores[j], io<T>::load(vp[(int64_t)j * vn + d]), acc);
+      acc = fmaf(scores[j], io<T>::load(vp[key_row(j, vn) + d]), acc);
     op[d] = io<T>::store(acc * inv);
   }
   if (lse != nullptr && threadIdx.x == 0) lse[z * lse_z + h * lse_h + m] = mx + logf(sum);

@@ -445,7 +445,8 @@ static int attn_fwd_impl(const b200_tensor *q, const b200_tensor *k, const b200_
   using namespace b200;
   using namespace b200::attn;
   int st;
-  const bool plain = modes.softcap == 0.f && modes.alibi == nullptr && !modes.local;
+  const bool plain = modes.softcap == 0.f && modes.alibi == nullptr && !modes.local &&
+                     modes.page_table == nullptr;
   if ((st = check_tensor(q, "q", 4)) || (st = check_tensor(k, "k", 4)) ||
       (st = check_tensor(v, "v", 4)) || (st = check_tensor(o, "o", 4)))
     return st;
@@ -570,7 +571,7 @@ static int attn_fwd_impl(const b200_tensor *q, const b200_tensor *k, const b200_
 extern "C" int b200_attn_fwd(const b200_tensor *q, const b200_tensor *k, const b200_tensor *v,
                              b200_tensor *o, b200_tensor *lse, float scale, int causal,
                              void *stream) {
-  const b200::attn::SimtModes none{0.f, nullptr, 0, 0, 0, 0};
+  const b200::attn::SimtModes none{0.f, nullptr, 0, 0, 0, 0, nullptr, 0, 1, 0};
   return attn_fwd_impl(q, k, v, o, lse, scale, causal, none, stream);
 }
 
@@ -578,9 +579,10 @@ extern "C" int b200_attn_fwd_modes(const b200_tensor *q, const b200_tensor *k,
                                    const b200_tensor *v, b200_tensor *o, b200_tensor *lse,
                                    float scale, int causal, float softcap,
                                    const b200_tensor *alibi_slopes, int window_left,
-                                   int window_right, void *stream) {
+                                   int window_right, const b200_tensor *page_table,
+                                   int block_size, int64_t page_stride, void *stream) {
   using namespace b200;
-  attn::SimtModes modes{0.f, nullptr, 0, 0, 0, 0};
+  attn::SimtModes modes{0.f, nullptr, 0, 0, 0, 0, nullptr, 0, 1, 0};
   B200_REQUIRE(softcap == softcap && softcap >= 0.f, "softcap must be >= 0 (0: off)");
   modes.softcap = softcap;
   if (alibi_slopes != nullptr) {
@@ -602,6 +604,22 @@ extern "C" int b200_attn_fwd_modes(const b200_tensor *q, const b200_tensor *k,
     modes.local = 1;
     modes.window_left = window_left;
     modes.window_right = window_right;
+  }
+  if (page_table != nullptr) {
+    int st;
+    if ((st = check_tensor(page_table, "page_table", 2))) return st;
+    if (q == nullptr || k == nullptr) return fail(B200_USAGE, "null argument");
+    B200_REQUIRE(page_table->dtype == B200_DTYPE_INT32 && page_table->stride[1] == 1 &&
+                 page_table->shape[0] == q->shape[0],
+                 "page_table must be int32 [Z, pages] with unit last stride");
+    B200_REQUIRE(block_size > 0 && page_stride > 0, "block_size and page_stride must be positive");
+    B200_REQUIRE(page_table->shape[1] * (int64_t)block_size >= k->shape[2],
+                 "the page table covers %lld keys, N_K is %lld",
+                 (long long)(page_table->shape[1] * (int64_t)block_size), (long long)k->shape[2]);
+    modes.page_table = static_cast<const int *>(page_table->data);
+    modes.page_table_z = page_table->stride[0];
+    modes.block_size = block_size;
+    modes.page_stride = page_stride;
   }
   return attn_fwd_impl(q, k, v, o, lse, scale, causal, modes, stream);
 }

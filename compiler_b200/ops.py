@@ -159,26 +159,30 @@ def linear_log_softmax(x, w, y, *, stream=0):
 
 
 def attention(q, k, v, o, *, lse=None, scale=None, causal=True, softcap=0.0, alibi_slopes=None,
-              window=None, stream=0):
+              window=None, page_table=None, block_size=0, page_stride=0, stream=0):
     """o = softmax(scale * q k^T (+ causal mask)) v over [Z,H,N,D]; lse = log-sum-exp.
 
     Native form of attn_fwd_causal_kernel (ops/suite/perf/attn_fwd_causal.py:19-57).
     ``softcap`` / ``alibi_slopes`` ([H] or [Z,H] float32) / ``window=(left, right)`` are the
     further modes of flash_varlen_fwd_kernel
-    (ops/suite/dev/flash_varlen_fwd_kernel.py:121-146), taken by the CUDA-core kernel."""
+    (ops/suite/dev/flash_varlen_fwd_kernel.py:121-146), ``page_table`` (int32 [Z, pages]) with
+    ``block_size`` / ``page_stride`` its paged K / V (:91-108); all taken by the CUDA-core
+    kernel."""
     if scale is None:
         scale = 1.0 / float(q.shape[-1]) ** 0.5
     qd, kd, vd, od = _desc(q), _desc(k), _desc(v), _desc(o)
     ld = _desc(lse) if lse is not None else None
-    if not softcap and alibi_slopes is None and window is None:
+    if not softcap and alibi_slopes is None and window is None and page_table is None:
         abi.check(abi.lib().b200_attn_fwd(_ref(qd), _ref(kd), _ref(vd), _ref(od), _ref(ld),
                                           float(scale), 1 if causal else 0, stream))
         return
     ad = _desc(alibi_slopes) if alibi_slopes is not None else None
     left, right = (int(window[0]), int(window[1])) if window is not None else (-1, -1)
+    pd = _desc(page_table) if page_table is not None else None
     abi.check(abi.lib().b200_attn_fwd_modes(_ref(qd), _ref(kd), _ref(vd), _ref(od), _ref(ld),
                                             float(scale), 1 if causal else 0, float(softcap),
-                                            _ref(ad), left, right, stream))
+                                            _ref(ad), left, right, _ref(pd), int(block_size),
+                                            int(page_stride), stream))
 
 
 def attention_window(q, k, v, o, *, g_cumsum=None, sink_bias=None, lse=None, scale=None,

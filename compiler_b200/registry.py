@@ -376,13 +376,13 @@ def _flash_varlen(device, v, grid, name):
     :138; key length >= query length): packed sequences addressed through cu_seqlens (or
     fixed lengths with batch strides), key lengths from seqused_k, query and key lengths that
     differ, h / hk query heads per K / V head, log-sum-exp laid out [h, total_q]; and the
-    soft-cap, ALiBi and local-window modes (:121-146, CUDA-core kernel).  One launch of the
+    soft-cap, ALiBi, local-window and paged-K/V modes (:91-146, CUDA-core kernel).  One launch of the
     attention operator per sequence, on strided views of the packed buffers.  The sequence
     boundaries are read back from the device, so this launch is bound afresh every time."""
-    for flag in ("is_dropout", "return_softmax", "is_paged", "seqlenq_ngroups_swapped"):
+    for flag in ("is_dropout", "return_softmax", "seqlenq_ngroups_swapped"):
         _require(not v.get(flag, False), name, flag,
-                 "dropout, the returned softmax, paged K / V and the swapped-groups layout "
-                 "have no native operator")
+                 "dropout, the returned softmax and the swapped-groups layout have no native "
+                 "operator")
     h, hk, d, batches = int(v["h"]), int(v["hk"]), int(v["d"]), int(v["b"])
     _require(hk > 0 and h % hk == 0, name, "hk", "h must be a multiple of hk")
     total_q = int(v["total_q"])
@@ -415,10 +415,21 @@ def _flash_varlen(device, v, grid, name):
             continue
         _require(k_len > 0, name, "cu_seqlens_k_ptr", "a sequence without keys")
 
+        paged = bool(v.get("is_paged", False))
+
         def view(side, heads, length):
             head, row = int(v[f"{side}_head_stride"]), int(v[f"{side}_row_stride"])
+            # paged K / V start at the cache's base: the page table places the rows (:91-108)
+            offset = 0 if paged and side in ("k", "v") else span[side][0]
             return _View(v[f"{side}_ptr"], (1, heads, length, d), (heads * head, head, row, 1),
-                         offset=span[side][0])
+                         offset=offset)
+
+        if paged:
+            block = int(v["block_size"])
+            pages = -(-k_len // block)
+            modes["page_table"] = _View(v["page_table_ptr"], (1, pages), (pages, 1),
+                                        offset=batch * int(v["page_table_batch_stride"]))
+            modes["block_size"], modes["page_stride"] = block, int(v["k_page_stride"])
 
         lse = _View(v["softmax_lse_ptr"], (1, h, q_len), (h * total_q, total_q, 1),
                     offset=span["q"][2])

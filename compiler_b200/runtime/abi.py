@@ -114,7 +114,7 @@ PROTOTYPES = {
     "b200_progress_words": (c_int, []),
     "b200_attn_fwd": (c_int, [_T, _T, _T, _T, _T, c_float, c_int, _PTR]),
     "b200_attn_fwd_modes": (c_int, [_T, _T, _T, _T, _T, c_float, c_int, c_float, _T, c_int, c_int,
-                                    _PTR]),
+                                    _T, c_int, c_int64, _PTR]),
     "b200_stream_wait_event": (c_int, [_PTR, _PTR]),
     "b200_graph_begin_capture": (c_int, [_PTR]),
     "b200_graph_end_capture": (c_int, [_PTR, POINTER(c_void_p)]),

@@ -288,11 +288,16 @@ int b200_attn_fwd(const b200_tensor *q, const b200_tensor *k,
  * zeros and lse = +inf (:309-310).  With every mode off this is b200_attn_fwd; with any of
  * them on the CUDA-core kernel runs (at most 8192 keys).  The reference's own `ref` covers the
  * dense case only (:370-418): these modes are checked against a restatement of the kernel's
- * lines.  Paged K / V and dropout are not taken. */
+ * lines.  Paged K / V (:91-108): page_table int32 [Z, pages] or NULL; key j of batch z is
+ * row j % block_size of physical page page_table[z][j / block_size], at page * page_stride +
+ * (j % block_size) * k->stride[2] elements past the head's base k->data + head *
+ * k->stride[1] -- for K and for V alike, as in the kernel; k->shape[2] = v->shape[2] is the
+ * number of keys in use.  Dropout and the returned softmax are not taken. */
 int b200_attn_fwd_modes(const b200_tensor *q, const b200_tensor *k, const b200_tensor *v,
                         b200_tensor *o, b200_tensor *lse, float scale, int causal,
                         float softcap, const b200_tensor *alibi_slopes, int window_left,
-                        int window_right, void *stream);
+                        int window_right, const b200_tensor *page_table, int block_size,
+                        int64_t page_stride, void *stream);
 
 /* Causal sliding-window attention with a gate bias and an attention sink.  Replaces
  * parallel_attn_fwd_kernel (ops/suite/dev/parallel_attn_fwd_kernel.py; arithmetic :142-166):

@@ -624,6 +624,91 @@ def test_varlen_attention_modes_through_the_launch_surface(device):
         oracle.compare(lse[:, qs][~empty], ref_l[0][~empty], 1e-3, 1e-3, name=f"lse[{b}]")
 
 
+def test_varlen_attention_paged_through_the_launch_surface(device):
+    """is_paged through the launch surface: fixed query length, key lengths from seqused_k, the
+    keys of every batch scattered over a page cache by its row of the page table."""
+    case, _ = golden_cases.load("flash_varlen_fwd_kernel__2x17x19x4x2x16__float32")
+    h, hk, d, block = 4, 2, 16, 8
+    batches, q_len, k_used = 3, 11, [19, 8, 30]
+    pages_per_batch = 4
+    num_pages = batches * pages_per_batch + 2
+    rng = np.random.default_rng(79)
+    q = rng.normal(0, 0.7, (batches, q_len, h, d)).astype(np.float32)
+    kcache = rng.normal(0, 0.7, (num_pages, block, hk, d)).astype(np.float32)
+    vcache = rng.normal(0, 0.7, (num_pages, block, hk, d)).astype(np.float32)
+    table = rng.permutation(num_pages)[:batches * pages_per_batch].astype(np.int32)
+    table = table.reshape(batches, pages_per_batch)
+    scale = 1.0 / np.sqrt(d)
+    args = dict(case["args"])
+    args.update({"q_ptr": q.reshape(-1), "k_ptr": kcache.reshape(-1), "v_ptr": vcache.reshape(-1),
+                 "o_ptr": np.zeros(q.size, np.float32),
+                 "softmax_lse_ptr": np.zeros(h * batches * q_len, np.float32),
+                 "q_row_stride": h * d, "o_row_stride": h * d, "k_row_stride": hk * d,
+                 "v_row_stride": hk * d, "q_head_stride": d, "k_head_stride": d,
+                 "v_head_stride": d, "o_head_stride": d, "q_batch_stride": q_len * h * d,
+                 "o_batch_stride": q_len * h * d, "k_batch_stride": 0, "v_batch_stride": 0,
+                 "seqused_k_ptr": np.asarray(k_used, np.int32), "page_table_ptr": table.reshape(-1),
+                 "k_page_stride": block * hk * d, "b": batches, "bk": batches,
+                 "seqlen_q": q_len, "seqlen_k": pages_per_batch * block,
+                 "total_q": batches * q_len})
+    meta = {**case["meta"], "h": h, "hk": hk, "h_hk_ratio": h // hk, "d": d, "d_rounded": d,
+            "scale_softmax": float(scale), "is_cu_seqlens_q": False, "is_cu_seqlens_k": False,
+            "is_seqused_k": True, "is_paged": True, "block_size": block,
+            "page_table_batch_stride": pages_per_batch, "is_causal": True}
+    case = dict(case, args=args, grid=(q_len, batches, h), meta=meta)
+    got = harness.run_case(case, device)
+    device.check_status()
+    out = got["o_ptr"].reshape(batches, q_len, h, d).astype(np.float64)
+    lse = got["softmax_lse_ptr"].reshape(h, batches, q_len).astype(np.float64)
+    for b in range(batches):
+        j = np.arange(k_used[b])
+        kb = kcache[table[b, j // block], j % block].transpose(1, 0, 2)[None]
+        vb = vcache[table[b, j // block], j % block].transpose(1, 0, 2)[None]
+        ref_o, ref_l = oracle.attention_modes_ref(q[b].transpose(1, 0, 2)[None], kb, vb, scale,
+                                                  causal=True)
+        empty = np.isinf(ref_l[0])
+        oracle.compare(out[b].transpose(1, 0, 2), ref_o[0], 1e-4, 1e-5, name=f"o[{b}]")
+        assert np.array_equal(np.isposinf(lse[:, b]), empty)
+        oracle.compare(lse[:, b][~empty], ref_l[0][~empty], 1e-3, 1e-3, name=f"lse[{b}]")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("block_size", [1, 4, 16])
+def test_attention_paged_kv(device, block_size, dtype):
+    """Paged K / V (ops/suite/dev/flash_varlen_fwd_kernel.py:91-108): the keys of a batch are
+    scattered over the pages of a cache in the order its page table gives; the result must be
+    that of attention over the gathered keys (here with a causal mask and a soft-cap on top)."""
+    z, hq, hkv, n, nk, d = 2, 4, 2, 21, 37, 16
+    pages_per_batch = -(-nk // block_size)
+    num_pages = 2 * pages_per_batch + 3
+    rng = np.random.default_rng(_seed(block_size, dtype, "paged"))
+    kcache = _host(rng.standard_normal((num_pages, block_size, hkv, d)), dtype)
+    vcache = _host(rng.standard_normal((num_pages, block_size, hkv, d)), dtype)
+    table = rng.permutation(num_pages)[:z * pages_per_batch].reshape(z, pages_per_batch)
+    table = table.astype(np.int32)
+    q = _host(rng.standard_normal((z, hq, n, d)), dtype)
+    # what the page table means: key j of batch b = row j % block of page table[b, j // block]
+    j = np.arange(nk)
+    k = np.stack([kcache[table[b, j // block_size], j % block_size] for b in range(z)])
+    v = np.stack([vcache[table[b, j // block_size], j % block_size] for b in range(z)])
+    k, v = k.transpose(0, 2, 1, 3), v.transpose(0, 2, 1, 3)          # [Z, H_KV, N_K, D]
+    dq, dkc, dvc = _up(device, q, dtype), _up(device, kcache, dtype), _up(device, vcache, dtype)
+    dt = device.upload(table)
+    do = _poisoned(device, (z, hq, n, d), dtype)
+    dl = device.upload(np.full((z, hq, n), POISON, np.float32))
+    row, page = hkv * d, block_size * hkv * d
+    kview = registry_view(dkc, (z, hkv, nk, d), (0, d, row, 1))
+    vview = registry_view(dvc, (z, hkv, nk, d), (0, d, row, 1))
+    scale = 1.0 / np.sqrt(d)
+    ops.attention(dq, kview, vview, do, lse=dl, scale=scale, causal=True, softcap=0.7,
+                  page_table=dt, block_size=block_size, page_stride=page)
+    device.check_status()
+    out_ref, lse_ref = oracle.attention_modes_ref(q, k, v, scale, causal=True, softcap=0.7)
+    rtol, atol = (1e-4, 1e-5) if dtype == "float32" else TOL[dtype]
+    oracle.compare(device.download(do).astype(np.float64), out_ref, rtol, atol, name="out")
+    oracle.compare(device.download(dl).astype(np.float64), lse_ref, 1e-3, 1e-3, name="lse")
+
+
 @pytest.mark.parametrize("shape", [(1, 1, 8, 16), (2, 2, 16, 32), (1, 2, 100, 80)])
 def test_attention_cuda_core_path(device, shape):
     z, h, n, d = shape
