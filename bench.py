@@ -1193,11 +1193,13 @@ def main():
         else:
             for key, collective, options in (
                     ("tp_mlp", "nccl", {}), ("tp_mlp_peer", "peer", {}),
-                    ("tp_mlp_nvls", "nvls", {}), ("tp_mlp_pull", "pull", {}),
+                    ("tp_mlp_nvls", "nvls", {"overlap_blocks": 0}),
+                    ("tp_mlp_pull", "pull", {"overlap_blocks": 0}),
                     ("tp_mlp_pull_row_blocks", "pull", {"row_splits": 2, "comm_ctas": 74}),
                     ("tp_mlp_pull_beside_gemm", "pull", {"overlap_blocks": 4}),
                     ("tp_mlp_nvls_beside_gemm", "nvls", {"overlap_blocks": 4}),
-                    ("tp_mlp_nvls_f32", "nvls", {"partial_dtype": torch.float32})):
+                    ("tp_mlp_nvls_f32", "nvls", {"partial_dtype": torch.float32,
+                                                 "overlap_blocks": 0})):
                 if collective == "peer" and MLP_M % (128 * dist.world):
                     continue
                 time.sleep(0.5)

@@ -81,8 +81,10 @@ for c0 in range(0, ffn, 2048):                       # column blocks bound the f
 shards = [bf16(t).contiguous() for t in (wgb[:, lo:hi], wub[:, lo:hi], wdb[lo:hi])]
 dxb = bf16(xb)
 failures = []
-for collective, options in (("nccl", {}), ("peer", {}), ("nvls", {}), ("pull", {}),
+for collective, options in (("nccl", {}), ("peer", {}), ("nvls", {"overlap_blocks": 0}),
+                            ("pull", {"overlap_blocks": 0}), ("pull", {}),
                             ("pull", {"overlap_blocks": 4}), ("nvls", {"overlap_blocks": 4}),
+                            ("pull", {"overlap_blocks": 1}),
                             ("nvls", {"partial_dtype": torch.float32, "chunks": 2})):
     try:
         big = tp_mlp.TensorParallelMLP(*shards, collective=collective, **options)
