@@ -41,7 +41,21 @@ __device__ __forceinline__ float group_reduce(float v, float *scratch, int buf) 
     if ((threadIdx.x & 31) == 0) slot[threadIdx.x >> 5] = v;
     // literal barrier ids: a register id would make ptxas reserve all 16 hardware
     // barriers per CTA and cap the CTAs per SM at 4
-    if constexpr (G >= kRowThreads) {
+    if constexpr (G >= 2 * kRowThreads) {
+      // 16 or 32 warps (the CTA is the group): the first warp folds the warps' values with
+      // shuffles and publishes the result, instead of every thread reading 16 or 32 slots
+      // itself -- with 1024 threads those broadcast reads kept the shared-memory queue full
+      // (the wide-row softmax waited 5.7 cycles per issued instruction on it)
+      __syncthreads();
+      if (threadIdx.x < 32) {
+        float t = (int)threadIdx.x < kWarps ? slot[threadIdx.x] : Op::identity();
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) t = Op::apply(t, __shfl_xor_sync(0xffffffffu, t, o));
+        if (threadIdx.x == 0) slot[0] = t;
+      }
+      __syncthreads();
+      return slot[0];
+    } else if constexpr (G >= kRowThreads) {
       __syncthreads();
     } else if constexpr (G == kRowThreads / 2) {
       if (group == 0) asm volatile("bar.sync 1, %0;" ::"n"(G) : "memory");
