@@ -12,8 +12,11 @@
 
 namespace b200 {
 
+// Rows of 512 / 1024 threads' width: at most 32 registers, so that CTAs fill the SM's 2048
+// threads (the bfloat16 form took 48 and left a 1024-thread CTA alone on its SM).
 template <typename T, int G, int VPT>
-__global__ void __launch_bounds__((G > kRowThreads ? G : kRowThreads))
+__global__ void __launch_bounds__((G > kRowThreads ? G : kRowThreads),
+                                  (G > kRowThreads ? 2048 / G : 1))
 rmsnorm_rows_kernel(const T *__restrict__ x, int64_t x_stride,
                     const T *__restrict__ w, T *__restrict__ y, int64_t y_stride,
                     T *__restrict__ rinv, int64_t rows, int cols, float eps, float gamma_offset) {
