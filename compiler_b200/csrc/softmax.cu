@@ -163,7 +163,7 @@ constexpr int kSoftmaxPlain = 0, kSoftmaxMul = 1, kSoftmaxLog = 2;
 // exponentiated and the kernel lives on the loads in flight.
 template <typename T, int G, int VPT, int MODE, bool KEEP>
 __global__ void __launch_bounds__((G > kRowThreads ? G : kRowThreads),
-                                  (G > kRowThreads ? 1 : (KEEP ? 4 : 8)))
+                                  (G > kRowThreads ? (KEEP ? 1 : 2048 / G) : (KEEP ? 4 : 8)))
 softmax_rows_kernel(const T *__restrict__ x, const T *__restrict__ mul, T *__restrict__ y,
                     int64_t rows, int cols, int mask_kind, int64_t row_offset) {
   constexpr int kThreads = G > kRowThreads ? G : kRowThreads;
@@ -468,17 +468,30 @@ static void launch_rows(const b200_tensor *x, const b200_tensor *mul, b200_tenso
       return;
     }
   } else if constexpr (MODE == kSoftmaxPlain) {
-    // wide rows, more rows than resident CTAs: the pipelined lean form with the CTA as the
-    // group (B200OPS_SOFTMAX_STREAM=0 keeps the one-row-per-CTA kernel)
+    // Rows of 512 / 1024 threads' width, by measurement.  Unmasked, more rows than resident
+    // CTAs: the pipelined lean form with the CTA as the group (fp16 [2048,32768] 4.9 TB/s,
+    // fp32 [2048,16384] 5.4 against 4.4 / 4.1 for the form below).  Masked, or few rows: the
+    // one-row-per-CTA form that takes its exponentials again for the store -- it fits 32
+    // registers, so two CTAs of 1024 threads (four of 512) share an SM and overlap each
+    // other's load -> max -> sum -> store chains, and masked rows, which differ in length, gain
+    // more from that than from a prefetched next row (fp16 [2048,32768] masked 4.7 TB/s in
+    // bytes that move against 4.3; [4096,16384] 5.6 against 5.1).  The form that keeps its
+    // exponentials leaves a CTA alone on its SM (3.0 TB/s) and is not used for these widths.
+    // B200OPS_SOFTMAX_STREAM=0: never the pipelined form; 4: also for masked rows.
     static const int choice =
         getenv("B200OPS_SOFTMAX_STREAM") ? atoi(getenv("B200OPS_SOFTMAX_STREAM")) : 1;
     const unsigned resident = (unsigned)(sm_count() * stream_lean_ctas_per_sm(G));
-    if (choice != 0 && grid > resident) {
+    const bool pipelined = choice == 4 || (choice != 0 && mask_kind == B200_MASK_NONE);
+    if (pipelined && grid > resident) {
       softmax_stream_kernel<T, G, VPT, MODE, true><<<resident, kThreads, 0, stream>>>(
           (const T *)x->data, nullptr, (T *)y->data, rows, (int)x->shape[1], mask_kind,
           row_offset);
       return;
     }
+    softmax_rows_kernel<T, G, VPT, MODE, false><<<grid, kThreads, 0, stream>>>(
+        (const T *)x->data, nullptr, (T *)y->data, rows, (int)x->shape[1], mask_kind,
+        row_offset);
+    return;
   }
   softmax_rows_kernel<T, G, VPT, MODE, KEEP><<<grid, kThreads, 0, stream>>>(
       (const T *)x->data, mul ? (const T *)mul->data : nullptr, (T *)y->data, rows,
